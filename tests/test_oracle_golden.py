@@ -1,0 +1,71 @@
+"""Pin the CPU oracle to the reference: every golden vector must match byte for byte.
+
+The vectors in tests/golden/reference_golden.pt.xz were produced by the reference's
+own PyTorch backend (tests/golden/make_golden.py).  They cover all five scale rules,
+1-D and 16x16 blocks, transposed quantization, NVFP4 and IF4, bf16 and fp16 inputs,
+ragged shapes, all-zero input and hand-made rounding ties.
+"""
+
+from __future__ import annotations
+
+import torch
+
+
+def _run(oracle, golden, case):
+    x = golden["inputs"][case["input"]]
+    cfg = case["config"]
+    return oracle.quantize(
+        x, dtype=cfg.get("dtype", "nvfp4"), scale_rule=cfg.get("scale_rule", "mse"),
+        block_scale_2d=cfg.get("block_scale_2d", False), transpose=cfg.get("transpose", False))
+
+
+def test_quantize_matches_reference_bytes(oracle, golden):
+    bad = []
+    for case in golden["cases"]:
+        q = _run(oracle, golden, case)
+        assert q.padded_shape == tuple(case["padded_shape"]), case["name"]
+        assert q.original_shape == tuple(case["original_shape"]), case["name"]
+        assert q.tiled == case["tiled"], case["name"]
+        n_val = int((q.values != case["values"]).sum())
+        n_sf = int((q.scale_factors != case["scale_factors"]).sum())
+        same_amax = torch.equal(q.amax, case["amax"])
+        if n_val or n_sf or not same_amax:
+            bad.append((case["name"], n_val, n_sf, same_amax))
+        # the saturating hardware conversion and the reference's unclamped rounding agree below 7
+        assert q.worst_scaled < 7.0, case["name"]
+    assert not bad, bad[:10]
+
+
+def test_dequantize_matches_reference_bits(oracle, golden):
+    checked = 0
+    for case in golden["cases"]:
+        for key, dt in (("dequant_bf16", torch.bfloat16), ("dequant_fp16", torch.float16),
+                        ("dequant_fp32", torch.float32)):
+            if key not in case:
+                continue
+            cfg = case["config"]
+            out = oracle.dequantize_raw(
+                case["values"], case["scale_factors"], case["amax"], cfg.get("dtype", "nvfp4"),
+                cfg.get("scale_rule", "mse"), tuple(case["original_shape"]), dt, tiled=case["tiled"])
+            ref = case[key]
+            view = torch.int32 if dt == torch.float32 else torch.int16
+            assert torch.equal(out.view(view), ref.contiguous().view(view)), (case["name"], key)
+            checked += 1
+    assert checked > 60
+
+
+def test_matmul_and_alpha_match_reference(oracle, golden):
+    for mm in golden["matmul"]:
+        ca, cb = mm["cfg_a"], mm["cfg_b"]
+        qa = oracle.quantize(mm["a"], dtype=ca.get("dtype", "nvfp4"), scale_rule=ca.get("scale_rule", "mse"),
+                             block_scale_2d=ca.get("block_scale_2d", False))
+        qb = oracle.quantize(mm["b"], dtype=cb.get("dtype", "nvfp4"), scale_rule=cb.get("scale_rule", "mse"))
+        assert oracle.alpha(qa, qb) == mm["alpha"].item()
+        out32 = oracle.matmul(qa, qb, torch.float32)
+        ref32 = mm["out_fp32"]
+        # fp32 accumulation order differs between sgemm implementations: tolerance, not bits
+        denom = ref32.abs().max().clamp_min(1e-30)
+        assert ((out32 - ref32).abs().max() / denom).item() < 1e-5
+        out16 = oracle.matmul(qa, qb, torch.bfloat16)
+        frac = (out16 != mm["out_bf16"]).float().mean().item()
+        assert frac <= 1e-3, frac          # the reference's own cross-backend criterion
