@@ -1,0 +1,355 @@
+"""Benchmark of the hot path: Four-Over-Six NVFP4 quantization and the FP4 GEMM that consumes it.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on stdout (rank 0).  The primary `value` is quantize throughput in GB/s of
+algorithmic traffic (2 B read + 0.5 B codes + 1/16 B scale per element) on the activation
+tensor of the "quantize both operands + NVFP4 GEMM" configuration: A = 8192 x 4096 bf16,
+N(0,1) with 1 % of the K-channels scaled by 20, NVFP4 with 4/6 MSE block selection.  The
+`gemm` object carries the second half of the metric: FP4 GEMM TFLOP/s at M = N = K = 8192
+(and the A x B^T of the same configuration).  Inputs are synthetic and seeded.
+
+A "step" is one quantization of A (amax pass + quantize pass = 2 kernel launches).  Four
+copies of A (256 MiB) are cycled so that every step reads its input from HBM, not from
+the 126 MB L2.  Timing uses CUDA events on the stream the kernels are launched on; with
+N > 1 every rank quantizes its own A (independent stripes, no collective: weak scaling)
+and the slowest rank defines the time.
+
+`--impl reference` times the CPU restatement of the reference's PyTorch path (the oracle)
+on the host cores for the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+A_SHAPE = (8192, 4096)
+B_SHAPE = (4096, 4096)
+BYTES_PER_ELEM = 2.0 + 0.5 + 1.0 / 16.0
+N_ROTATE = 4
+NOMINAL_FP4_TFLOPS = 9000.0
+
+
+def load_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def make_a(seed: int) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(A_SHAPE, generator=g)
+    idx = torch.randperm(A_SHAPE[1], generator=g)[: A_SHAPE[1] // 100]
+    a[:, idx] *= 20.0
+    return a.bfloat16()
+
+
+def make_b(seed: int) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(B_SHAPE, generator=g) * 0.02).bfloat16()
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def time_cuda(fn, steps: int, warmup: int) -> float:
+    """Mean milliseconds per call of fn(i), CUDA events on the current stream."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def cpu_baseline_quantize(a_cpu: torch.Tensor, budget_s: float = 10.0) -> dict:
+    from oracle import fos_oracle
+
+    fos_oracle.quantize(a_cpu[:256])
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while time.perf_counter() < t_end or len(times) < 3:
+        t0 = time.perf_counter()
+        fos_oracle.quantize(a_cpu, dtype="nvfp4", scale_rule="mse")
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return {"value": BYTES_PER_ELEM * a_cpu.numel() / med / 1e9, "unit": "GB/s", "cores": fos_oracle.num_threads(),
+            "kind": "port",
+            "sample": f"full {A_SHAPE[0]}x{A_SHAPE[1]} tensor, median of {len(times)} runs of the C oracle "
+                      f"(OpenMP, {fos_oracle.num_threads()} threads), {med * 1e3:.0f} ms each"}
+
+
+def run_reference(args, rank: int) -> None:
+    """CPU arm: the oracle (restatement of the reference's PyTorch path) on the host cores."""
+    if rank != 0:
+        return
+    from oracle import fos_oracle
+
+    a = make_a(1)
+    for _ in range(max(args.warmup, 1)):
+        fos_oracle.quantize(a)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fos_oracle.quantize(a, dtype="nvfp4", scale_rule="mse")
+    ms = (time.perf_counter() - t0) / args.steps * 1e3
+    value = BYTES_PER_ELEM * a.numel() / (ms * 1e-3) / 1e9
+    threads = fos_oracle.num_threads()
+    line = {
+        "impl": "reference", "metric": "quantize GB/s (frac of HBM peak); FP4 GEMM TFLOP/s at 8192^3 (frac of FP4 peak)",
+        "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "quantize A 8192x4096 bf16 (N(0,1), 1% K-channels x20) to NVFP4 4/6-MSE, 1x16 blocks"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": "every step is one full 8192x4096 quantization by the C oracle"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank: int, world: int, local_rank: int) -> None:
+    import fouroversix_b200 as fos
+    from fouroversix_b200.matmul import B200MatmulBackend
+    from fouroversix_b200.quantize.backend import B200QuantizeBackend
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    cfg_mse = fos.QuantizationConfig(scale_rule="mse")
+
+    a_cpu = make_a(1 + 100 * rank)
+    a_sets = [a_cpu.to(dev)] + [make_a(1 + 100 * rank + 7 * i).to(dev) for i in range(1, N_ROTATE)]
+    n_elem = a_cpu.numel()
+
+    def step(i):
+        return fos.quantize(a_sets[i % N_ROTATE], cfg_mse)
+
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = time_cuda(step, args.steps, args.warmup)
+    # a sustained second pass so that the clock sampler sees the kernels under load
+    if rank == 0:
+        t_end = time.perf_counter() + 1.0
+        while time.perf_counter() < t_end:
+            for i in range(50):
+                step(i)
+            torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = BYTES_PER_ELEM * n_elem * world / (ms * 1e-3) / 1e9
+
+    if rank != 0:
+        # the other ranks still take part in the sharded GEMM section below
+        gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks)
+        return
+
+    # other quantize modes of the same tensor (each: the whole call, both launches)
+    modes = {}
+    for name, c in (("static_6", fos.QuantizationConfig(scale_rule="static_6")),
+                    ("mse_amax_given", None),
+                    ("if4_mse", fos.QuantizationConfig(dtype="if4")),
+                    ("mse_2d", fos.QuantizationConfig(block_scale_2d=True)),
+                    ("mse_transposed", fos.QuantizationConfig(transpose=True))):
+        if c is None:
+            amaxes = [x.abs().max().float().reshape(1) for x in a_sets]
+            fn = lambda i: B200QuantizeBackend.quantize(a_sets[i % N_ROTATE], cfg_mse, amax=amaxes[i % N_ROTATE])  # noqa: E731
+        else:
+            fn = lambda i, c=c: fos.quantize(a_sets[i % N_ROTATE], c)  # noqa: E731
+        t = time_cuda(fn, max(args.steps, 10), 3)
+        modes[name] = {"ms": t, "GB/s": BYTES_PER_ELEM * n_elem / (t * 1e-3) / 1e9}
+
+    # end to end through the public API with host buffers
+    pinned_in = a_cpu.pin_memory()
+    q0 = fos.quantize(a_sets[0], cfg_mse)
+    host_vals = torch.empty(q0.values.shape, dtype=torch.uint8).pin_memory()
+    host_sf = torch.empty(q0.scale_factors.numel(), dtype=torch.uint8).pin_memory()
+    host_amax = torch.empty(1, dtype=torch.float32).pin_memory()
+    staging = torch.empty_like(a_sets[0])
+
+    def e2e_step(i):
+        staging.copy_(pinned_in, non_blocking=True)
+        q = fos.quantize(staging, cfg_mse)
+        host_vals.copy_(q.values, non_blocking=True)
+        host_sf.copy_(q.scale_factors.view(torch.uint8), non_blocking=True)
+        host_amax.copy_(q.amax, non_blocking=True)
+
+    e2e_ms = time_cuda(e2e_step, max(3, min(args.steps, 20)), 2)
+    h2d = a_cpu.numel() * 2
+    d2h = host_vals.numel() + host_sf.numel() + 4
+    e2e_value = BYTES_PER_ELEM * n_elem / (e2e_ms * 1e-3) / 1e9
+
+    gemm = gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks)
+    cpu = cpu_baseline_quantize(a_cpu) if world == 1 else None
+
+    achieved = BYTES_PER_ELEM * n_elem / (ms * 1e-3) / 1e9 if world == 1 else value / world
+    line = {
+        "metric": "quantize GB/s (frac of HBM peak); FP4 GEMM TFLOP/s at 8192^3 (frac of FP4 peak)",
+        "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {
+            "workload": "quantize A 8192x4096 bf16 (N(0,1), 1% K-channels x20) to NVFP4 4/6-MSE, 1x16 blocks; "
+                        "per rank when n_gpus > 1",
+            "l2": f"{N_ROTATE} rotating copies of A (256 MiB) so each step reads HBM-cold input",
+            "bytes_per_element": BYTES_PER_ELEM,
+        },
+        "roofline": {
+            "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": achieved / peaks["hbm_gbs"], "frac_of_nominal_8TBps": achieved / 8000.0,
+            "peak_source": peaks["source"], "traffic": None,
+            "kernels": "amax_kernel + quantize_kernel (both launches of one call are timed together)",
+        },
+        "quantize_modes": modes,
+        "gemm": gemm,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms},
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+
+
+def gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks):
+    """FP4 GEMM numbers: 8192^3 (and the 8192x4096x4096 of the configuration) on one GPU;
+    with more GPUs the N dimension of B is split across ranks (column parallel, no
+    collective) and the slowest rank defines the time."""
+    out = {}
+    for name, (m, n, k) in (("square_8192", (8192, 8192, 8192)), ("act_x_weight", (8192, 4096, 4096))):
+        n_local = n // world
+        g = torch.Generator(device=dev).manual_seed(3 + rank)
+        a = torch.randn(m, k, generator=g, device=dev).bfloat16()
+        b = (torch.randn(n_local, k, generator=g, device=dev) * (1.0 if name == "square_8192" else 0.02)).bfloat16()
+        qa, qb = fos.quantize(a), fos.quantize(b)
+        d = torch.empty(m, n_local, dtype=torch.bfloat16, device=dev)
+        del a, b
+        fn = lambda i: B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType.bfloat16, out=d)  # noqa: E731
+        if world > 1:
+            dist.barrier()
+        ms = time_cuda(fn, max(args.steps, 10), max(args.warmup, 3))
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        tflops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        derived = NOMINAL_FP4_TFLOPS * peaks["bf16_tflops"] / 2250.0
+        out[name] = {
+            "value": tflops, "unit": "TFLOP/s", "ms": ms, "m": m, "n": n, "k": k, "n_gpus": world,
+            "sharding": "none" if world == 1 else f"column-parallel, N/{world} per rank, no collective",
+            "roofline": {"bound": "tensor", "achieved": tflops / world, "peak": NOMINAL_FP4_TFLOPS,
+                         "unit": "TFLOP/s", "frac": tflops / world / NOMINAL_FP4_TFLOPS,
+                         "peak_source": "nominal dense FP4 (no measured FP4 figure exists)",
+                         "frac_of_bf16_scaled_peak": tflops / world / derived,
+                         "bf16_scaled_peak": derived},
+            "gpu_launches_per_step": 2, "l2": "operands + output (200 MiB at 8192^3) exceed L2",
+        }
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the GPU path has no CPU fallback")
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

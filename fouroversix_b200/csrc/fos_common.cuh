@@ -1,0 +1,123 @@
+// Shared device helpers for the fouroversix_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fouroversix_b200.h"
+
+#if defined(__CUDA_ARCH__) && !(defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM103_ALL))
+#error "fouroversix_b200 kernels must be compiled for sm_100a"
+#endif
+
+namespace fos {
+
+// Records a failed runtime call for fos_last_cuda_error() and maps it to FOS_ERR_CUDA.
+int note_cuda_error(cudaError_t e);
+// FOS_OK when the current device is compute capability 10.x, else FOS_ERR_ARCH / FOS_ERR_CUDA.
+int check_device();
+
+#define FOS_CUDA_TRY(expr)                                         \
+    do {                                                           \
+        cudaError_t fos_e_ = (expr);                               \
+        if (fos_e_ != cudaSuccess) return fos::note_cuda_error(fos_e_); \
+    } while (0)
+
+static inline int64_t round_up64(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+// (max representable value) * (largest scale) used to undo the two-level scaling.
+__host__ __device__ inline float dequant_divisor(int format, int rule) {
+    if (format == FOS_IF4) return 2688.0f;
+    if (rule == FOS_RULE_STATIC_6) return 2688.0f;
+    if (rule == FOS_RULE_STATIC_4) return 1792.0f;
+    return 1536.0f;
+}
+
+#ifdef __CUDACC__
+
+// Offset of the scale of (row r, block column cb) when scales are stored as 128x4 tiles
+// of 512 bytes: 32 groups of 16 bytes, group g = r % 32, inside it four quarters of
+// 4 bytes (r / 32 within the tile), inside a quarter the four block columns.
+__device__ __forceinline__ int64_t sf_offset(int64_t r, int64_t cb, int64_t n_cb, bool tiled) {
+    if (!tiled) return r * n_cb + cb;
+    int64_t tile = (r >> 7) * (n_cb >> 2) + (cb >> 2);
+    return tile * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (cb & 3);
+}
+
+// ---- format conversions (all round-to-nearest-even, saturating) ----
+
+// Two floats -> one byte of two E2M1 codes; `hi` lands in the upper nibble.
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float hi, float lo) {
+    uint32_t r;
+    asm("{ .reg .b8 b; cvt.rn.satfinite.e2m1x2.f32 b, %1, %2; cvt.u32.u8 %0, b; }" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// Eight floats (x[0] = lowest nibble) -> 32 bits of E2M1 codes.
+__device__ __forceinline__ uint32_t cvt_e2m1x8(const float *x) {
+    uint32_t r;
+    asm("{ .reg .b8 b0, b1, b2, b3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+        "mov.b32 %0, {b0, b1, b2, b3}; }"
+        : "=r"(r)
+        : "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]), "f"(x[4]), "f"(x[5]), "f"(x[6]), "f"(x[7]));
+    return r;
+}
+
+// One byte of two E2M1 codes -> the two values as floats (lo = low nibble).
+__device__ __forceinline__ float2 e2m1x2_to_float2(uint32_t byte) {
+    uint32_t h2;
+    asm("{ .reg .b8 b; cvt.u8.u32 b, %1; cvt.rn.f16x2.e2m1x2 %0, b; }" : "=r"(h2) : "r"(byte));
+    return __half22float2(*reinterpret_cast<__half2 *>(&h2));
+}
+
+__device__ __forceinline__ uint32_t cvt_e4m3(float x) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.0f), "f"(x));
+    return r & 0xffu;
+}
+
+__device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
+    uint32_t h2;
+    uint16_t b = static_cast<uint16_t>(byte & 0xffu);
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(b));
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(h2 & 0xffffu)));
+}
+
+// ---- memory ----
+
+__device__ __forceinline__ uint4 ldg_nc_16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// 32-byte load (sm_100 and later); `p` must be 32-byte aligned.
+__device__ __forceinline__ void ldg_nc_32(const void *p, uint32_t (&v)[8]) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "l"(p));
+}
+
+template <typename T> __device__ __forceinline__ float elem_to_float(T v);
+template <> __device__ __forceinline__ float elem_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float elem_to_float<__half>(__half v) { return __half2float(v); }
+
+// Two packed 16-bit elements -> floats (x = low half).
+template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t w);
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
+    return __half22float2(*reinterpret_cast<__half2 *>(&w));
+}
+
+#endif  // __CUDACC__
+
+}  // namespace fos

@@ -1,0 +1,479 @@
+// Block-scaled NVFP4 GEMM for sm_100a: D[m, n] = alpha * sum_k A[m, k] * B[n, k].
+//
+// Both operands are K-major packed E2M1 with one UE4M3 scale per 16 values, stored as
+// fos_quantize writes them (scales in 128-row x 4-block tiles of 512 bytes). The kernel
+// is persistent (one CTA per SM, static tile schedule) and warp specialised:
+//
+//   warp 0      one lane issues TMA loads of the A / B tiles (128-byte swizzle, no
+//               multicast) and plain bulk copies of the scale tiles into a ring of
+//               shared-memory stages guarded by full / empty mbarriers
+//   warp 1      allocates tensor memory; one lane copies the scale tiles shared -> tensor
+//               memory (tcgen05.cp 32x128b.warpx4, which is exactly the 512-byte tile) and
+//               issues tcgen05.mma kind::mxf4nvf4.block_scale (K = 64 per instruction) with
+//               the fp32 accumulator in tensor memory; tcgen05.commit releases the stage
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp owns the 32 lanes of its
+//               quadrant), multiply by alpha, convert, store rows < m and columns < n
+//
+// Every mbarrier wait is bounded by a wall-clock limit. A wait that gives up records where
+// in *status, raises a CTA-wide abort flag, and all roles fall through to the common exit,
+// which lets in-flight copies land, releases tensor memory and returns.
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "fos_common.cuh"
+
+namespace fos {
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K_BYTES = 128;                 // 256 E2M1 values: one 128-byte swizzle row
+constexpr int KB_PER_STAGE = 4;                    // MMA K-blocks (64 values, 32 bytes) per stage
+constexpr int SF_TILE_BYTES = 512;                 // scales of 128 rows x 64 values
+constexpr int A_BYTES = BLOCK_M * BLOCK_K_BYTES;   // 16 KiB
+constexpr int SFA_BYTES = KB_PER_STAGE * SF_TILE_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int SFA_COL = 256;                       // tensor-memory columns: accumulators first,
+constexpr int SFB_COL = 272;                       // then 16 columns of A scales, 32 of B scales
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+template <int BLOCK_N> struct Cfg {
+    static constexpr int B_BYTES = BLOCK_N * BLOCK_K_BYTES;
+    static constexpr int N_GROUPS = BLOCK_N / 128;                 // 128-row scale groups of B
+    static constexpr int SFB_BYTES = N_GROUPS * KB_PER_STAGE * SF_TILE_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+    static constexpr int STAGES = BLOCK_N == 256 ? 4 : 6;
+    static constexpr int ACC_STAGES = BLOCK_N == 256 ? 1 : 2;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
+    static_assert(ACC_STAGES * BLOCK_N <= SFA_COL, "accumulators overlap the scale columns");
+};
+
+struct GemmParams {
+    const uint8_t *a_sf;
+    const uint8_t *b_sf;
+    const float *alpha;
+    void *d;
+    int32_t *status;
+    int64_t m_p, n_p, k_p;   // padded problem (k_p in values)
+    int64_t m, n, ldd;       // region of D that is written
+    int out_dtype;
+};
+
+// ---------------------------------------------------------------------------- PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p; }\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Bounded wait. Returns false when the CTA is aborting (this wait or another one timed out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          int32_t *status, int where) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+#pragma unroll 1
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            if (status) atomicCAS(status, 0, where);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_copy_sf(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p; }\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+__device__ __forceinline__ void tc_load_32cols(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor. Bits: [0,14) start address >> 4, [16,30) leading byte
+// offset >> 4, [32,46) stride byte offset >> 4, [46,48) version = 1 on sm_100, [61,64)
+// swizzle mode (0 none, 2 128-byte).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t swizzle) {
+    return static_cast<uint64_t>((addr & 0x3ffffu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
+           (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (static_cast<uint64_t>(swizzle) << 61);
+}
+
+// Instruction descriptor of kind::mxf4nvf4 block-scaled MMA: A and B E2M1 (code 1 in bits
+// [7,10) and [10,13)), both K-major, N >> 3 in [17,23), UE4M3 scales (bit 23 = 0), M >> 4 in
+// [24,29), scale-factor byte ids 0, dense K = 64.
+__device__ __forceinline__ uint32_t mma_idesc(int n) {
+    return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
+}
+
+// Tile order: bands of GROUP_M row blocks, column blocks inside a band, so that the CTAs
+// running at the same time share a few A and B panels in L2.
+constexpr int GROUP_M = 8;
+__device__ __forceinline__ void tile_coords(int64_t t, int64_t num_m, int64_t num_n, int64_t &mb, int64_t &nb) {
+    const int64_t band = GROUP_M * num_n;
+    const int64_t g = t / band, r = t - g * band;
+    const int64_t first = g * GROUP_M;
+    const int64_t rows = (num_m - first) < GROUP_M ? (num_m - first) : GROUP_M;
+    mb = first + r % rows;
+    nb = r / rows;
+}
+
+// One accumulator row chunk (32 columns) -> alpha * acc -> OUT, to `dst`; `valid` columns exist.
+template <typename OUT>
+__device__ __forceinline__ void store_chunk(OUT *dst, const uint32_t (&acc)[32], float alpha, int valid, bool vec_ok) {
+    __align__(16) OUT tmp[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const float v = alpha * __uint_as_float(acc[i]);
+        if constexpr (std::is_same<OUT, float>::value) tmp[i] = v;
+        else if constexpr (std::is_same<OUT, __half>::value) tmp[i] = __float2half_rn(v);
+        else tmp[i] = __float2bfloat16_rn(v);
+    }
+    if (valid >= 32 && vec_ok) {
+        const uint4 *s = reinterpret_cast<const uint4 *>(tmp);
+#pragma unroll
+        for (int i = 0; i < static_cast<int>(sizeof(OUT)) * 2; ++i) reinterpret_cast<uint4 *>(dst)[i] = s[i];
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < valid) dst[i] = tmp[i];
+    }
+}
+
+// ---------------------------------------------------------------------------- kernel
+
+template <int BLOCK_N, typename OUT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const GemmParams p) {
+    using C = Cfg<BLOCK_N>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    // barriers live after the stages
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + C::STAGES * C::STAGE_BYTES);
+    const uint32_t full_bar = smem_u32(bars);                       // [STAGES]
+    const uint32_t empty_bar = full_bar + 8 * C::STAGES;            // [STAGES]
+    const uint32_t acc_full_bar = empty_bar + 8 * C::STAGES;        // [ACC_STAGES]
+    const uint32_t acc_empty_bar = acc_full_bar + 8 * C::ACC_STAGES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::STAGES + 2 * C::ACC_STAGES);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int a = 0; a < C::ACC_STAGES; ++a) {
+            mbar_init(acc_full_bar + 8 * a, 1);
+            mbar_init(acc_empty_bar + 8 * a, 4);   // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t num_m = p.m_p / BLOCK_M;
+    const int64_t num_n = (p.n_p + BLOCK_N - 1) / BLOCK_N;
+    const int64_t num_tiles = num_m * num_n;
+    const int64_t k_blocks = p.k_p / 64;                       // MMA K-blocks in the problem
+    const int64_t k_tiles = (k_blocks + KB_PER_STAGE - 1) / KB_PER_STAGE;
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            int64_t mb, nb;
+            tile_coords(t, num_m, num_n, mb, nb);
+            const int64_t m0 = mb * BLOCK_M, n0 = nb * BLOCK_N;
+            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+                ok = mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 1);
+                if (!ok) break;
+                const int64_t kb0 = kt * KB_PER_STAGE;
+                const int nkb = static_cast<int>((k_blocks - kb0) < KB_PER_STAGE ? (k_blocks - kb0) : KB_PER_STAGE);
+                int groups = 0;
+                for (int g = 0; g < C::N_GROUPS; ++g)
+                    if (n0 + 128 * g < p.n_p) ++groups;
+                const uint32_t stage = smem_base + s * C::STAGE_BYTES;
+                const uint32_t bar = full_bar + 8 * s;
+                mbar_expect_tx(bar, A_BYTES + C::B_BYTES + (1 + groups) * nkb * SF_TILE_BYTES);
+                tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), static_cast<int>(m0), bar);
+                tma_load_2d(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES), static_cast<int>(n0), bar);
+                bulk_load(stage + A_BYTES + C::B_BYTES, p.a_sf + ((m0 / 128) * k_blocks + kb0) * SF_TILE_BYTES,
+                          nkb * SF_TILE_BYTES, bar);
+                for (int g = 0; g < groups; ++g)
+                    bulk_load(stage + A_BYTES + C::B_BYTES + SFA_BYTES + g * KB_PER_STAGE * SF_TILE_BYTES,
+                              p.b_sf + ((n0 / 128 + g) * k_blocks + kb0) * SF_TILE_BYTES, nkb * SF_TILE_BYTES, bar);
+            }
+        }
+        if (!ok) {
+            // give copies that are still in flight time to land before the CTA exits
+            const unsigned long long t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer
+        uint32_t it = 0, tile_i = 0;
+        bool ok = true;
+        for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
+            int64_t mb, nb;
+            tile_coords(t, num_m, num_n, mb, nb);
+            const int64_t n0 = nb * BLOCK_N;
+            const int n_valid = static_cast<int>((p.n_p - n0) < BLOCK_N ? (p.n_p - n0) : BLOCK_N);
+            const uint32_t idesc = mma_idesc(n_valid);
+            const uint32_t acc = tile_i % C::ACC_STAGES, acc_ph = (tile_i / C::ACC_STAGES) & 1u;
+            ok = mbar_wait(acc_empty_bar + 8 * acc, acc_ph ^ 1u, abort_flag, p.status, 3);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+                ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const int64_t kb0 = kt * KB_PER_STAGE;
+                const int nkb = static_cast<int>((k_blocks - kb0) < KB_PER_STAGE ? (k_blocks - kb0) : KB_PER_STAGE);
+                const uint32_t stage = smem_base + s * C::STAGE_BYTES;
+                const uint32_t sfa_smem = stage + A_BYTES + C::B_BYTES, sfb_smem = sfa_smem + SFA_BYTES;
+                // scale tiles: 32 rows of 16 bytes, 8-row groups 128 bytes apart, no swizzle
+                for (int kb = 0; kb < nkb; ++kb) {
+                    tc_copy_sf(tmem_base + SFA_COL + 4 * kb, smem_desc(sfa_smem + kb * SF_TILE_BYTES, 0, 128, 0));
+                    for (int g = 0; g < C::N_GROUPS; ++g)
+                        if (n0 + 128 * g < p.n_p)
+                            tc_copy_sf(tmem_base + SFB_COL + (BLOCK_N / 32) * kb + 4 * g,
+                                       smem_desc(sfb_smem + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES, 0, 128, 0));
+                }
+                // operands: 128-byte swizzled rows, 8-row groups 1024 bytes apart; each K-block
+                // of 64 values is 32 bytes further along the row
+                const uint64_t a_desc = smem_desc(stage, 16, 1024, 2);
+                const uint64_t b_desc = smem_desc(stage + A_BYTES, 16, 1024, 2);
+                for (int kb = 0; kb < nkb; ++kb)
+                    tc_mma_nvf4(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc, tmem_base + SFA_COL + 4 * kb,
+                                tmem_base + SFB_COL + (BLOCK_N / 32) * kb, (kt > 0 || kb > 0) ? 1u : 0u);
+                tc_commit(empty_bar + 8 * s);          // stage reusable once these MMAs have read it
+            }
+            if (ok) tc_commit(acc_full_bar + 8 * acc);  // accumulator complete
+        }
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------------ epilogue
+        const int quad = warp & 3;                       // tensor-memory lanes 32*quad .. +31
+        const float alpha = __ldg(p.alpha);
+        OUT *out = static_cast<OUT *>(p.d);
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((p.ldd * sizeof(OUT)) % 16 == 0);
+        uint32_t tile_i = 0;
+        bool ok = true;
+        for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
+            int64_t mb, nb;
+            tile_coords(t, num_m, num_n, mb, nb);
+            const int64_t row = mb * BLOCK_M + quad * 32 + lane, n0 = nb * BLOCK_N;
+            const uint32_t acc = tile_i % C::ACC_STAGES, acc_ph = (tile_i / C::ACC_STAGES) & 1u;
+            ok = mbar_wait(acc_full_bar + 8 * acc, acc_ph, abort_flag, p.status, 4);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BLOCK_N;
+#pragma unroll 1
+            for (int c = 0; c < BLOCK_N / 32; ++c) {
+                const int64_t col = n0 + 32 * c;
+                if (col >= p.n) break;                   // uniform across the warp
+                uint32_t v[32];
+                tc_load_32cols(t_acc + 32 * c, v);
+                const int64_t left = p.n - col;
+                if (row < p.m)
+                    store_chunk<OUT>(out + row * p.ldd + col, v, alpha, left < 32 ? static_cast<int>(left) : 32, vec_ok);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar + 8 * acc);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------- host side
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up through the runtime, so the library has no link-time
+// dependency on libcuda and can be loaded (not run) on a machine without a GPU driver.
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            sym = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+// codes[rows, k_bytes] uint8 row-major; box = 128 bytes x box_rows, 128-byte swizzle.
+int make_operand_map(CUtensorMap *map, const uint8_t *codes, int64_t rows, int64_t k_bytes, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return FOS_ERR_CUDA;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(k_bytes), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(k_bytes)};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(BLOCK_K_BYTES), static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(codes), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? FOS_OK : FOS_ERR_CUDA;
+}
+
+template <int BLOCK_N, typename OUT>
+int launch(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p, int sms, cudaStream_t stream) {
+    using C = Cfg<BLOCK_N>;
+    auto kernel = gemm_nvfp4_kernel<BLOCK_N, OUT>;
+    static bool configured[64] = {};   // per instantiation and per device
+    int dev = 0;
+    FOS_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        FOS_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    const int64_t tiles = (p.m_p / BLOCK_M) * ((p.n_p + BLOCK_N - 1) / BLOCK_N);
+    const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+    kernel<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ma, mb, p);
+    FOS_CUDA_TRY(cudaGetLastError());
+    return FOS_OK;
+}
+
+template <int BLOCK_N>
+int launch_out(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p, int sms, cudaStream_t stream) {
+    if (p.out_dtype == FOS_BF16) return launch<BLOCK_N, __nv_bfloat16>(ma, mb, p, sms, stream);
+    if (p.out_dtype == FOS_FP16) return launch<BLOCK_N, __half>(ma, mb, p, sms, stream);
+    return launch<BLOCK_N, float>(ma, mb, p, sms, stream);
+}
+
+int g_force_block_n = 0;
+
+}  // namespace
+}  // namespace fos
+
+extern "C" int fos_set_option(int key, int value) {
+    if (key == FOS_OPT_GEMM_BLOCK_N && (value == 0 || value == 128 || value == 256)) {
+        fos::g_force_block_n = value;
+        return FOS_OK;
+    }
+    return FOS_ERR_INVALID_ARGUMENT;
+}
+
+extern "C" int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                              const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
+                              int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, int32_t *status,
+                              void *stream_) {
+    using namespace fos;
+    if (!a_codes || !a_sf || !b_codes || !b_sf || !alpha || !d) return FOS_ERR_INVALID_ARGUMENT;
+    if (m_p <= 0 || n_p <= 0 || k_p < 64 || m_p % 128 || n_p % 128 || k_p % 64) return FOS_ERR_INVALID_ARGUMENT;
+    if (m <= 0 || n <= 0 || m > m_p || n > n_p || ldd < n) return FOS_ERR_INVALID_ARGUMENT;
+    if (out_dtype != FOS_BF16 && out_dtype != FOS_FP16 && out_dtype != FOS_FP32) return FOS_ERR_INVALID_ARGUMENT;
+    if (reinterpret_cast<uintptr_t>(a_codes) % 16 || reinterpret_cast<uintptr_t>(b_codes) % 16 ||
+        reinterpret_cast<uintptr_t>(a_sf) % 16 || reinterpret_cast<uintptr_t>(b_sf) % 16)
+        return FOS_ERR_MISALIGNED;
+    if (m_p > INT32_MAX || n_p > INT32_MAX || k_p / 2 > INT32_MAX) return FOS_ERR_TOO_LARGE;
+    int st = check_device();
+    if (st != FOS_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+    int dev = 0, sms = 0;
+    FOS_CUDA_TRY(cudaGetDevice(&dev));
+    FOS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+
+    // 128 x 256 tiles unless the problem is too small to give every SM one of them
+    const int64_t tiles_256 = (m_p / BLOCK_M) * ((n_p + 255) / 256);
+    bool wide = n_p >= 256 && tiles_256 >= sms;
+    if (g_force_block_n == 128) wide = false;
+    if (g_force_block_n == 256) wide = true;
+
+    CUtensorMap map_a, map_b;
+    st = make_operand_map(&map_a, a_codes, m_p, k_p / 2, BLOCK_M);
+    if (st != FOS_OK) return st;
+    st = make_operand_map(&map_b, b_codes, n_p, k_p / 2, wide ? 256 : 128);
+    if (st != FOS_OK) return st;
+
+    GemmParams p{a_sf, b_sf, alpha, d, status, m_p, n_p, k_p, m, n, ldd, out_dtype};
+    if (status) FOS_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    return wide ? launch_out<256>(map_a, map_b, p, sms, stream) : launch_out<128>(map_a, map_b, p, sms, stream);
+}

@@ -1,0 +1,87 @@
+"""The one matmul back end: the hand-written tcgen05 block-scaled FP4 GEMM.
+
+It fills the role of the reference's CUTLASS back end
+(src/fouroversix/matmul/cutlass/backend.py:10-155; shape check from
+src/fouroversix/matmul/backend.py:32-38): `input @ other.T` for two NVFP4
+`QuantizedTensor`s with `alpha = amax_a * amax_b / (divisor_a * divisor_b)` applied in
+the epilogue.  alpha is computed on the device, so the call never synchronises.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from fouroversix_b200 import _native
+from fouroversix_b200.quantize import QuantizedTensor
+from fouroversix_b200.quantize.backend import B200QuantizeBackend
+from fouroversix_b200.utils import DataType
+
+_OUT = {DataType.bfloat16: torch.bfloat16, DataType.float16: torch.float16, DataType.float32: torch.float32}
+
+
+class B200MatmulBackend:
+    """FP4 x FP4 -> bf16 / fp16 / fp32 on the 5th-generation tensor cores."""
+
+    @classmethod
+    def is_available(cls) -> bool:
+        return B200QuantizeBackend.is_available()
+
+    @classmethod
+    def unsupported_reason(cls, input: QuantizedTensor, other: QuantizedTensor, *, out_dtype: DataType) -> str | None:
+        if input.original_shape[1] != other.original_shape[1]:
+            # same wording as the reference's shape check
+            raise ValueError(
+                "The first input must be in row-major layout, the second input must be"
+                "in column-major layout, and both inputs must have the same inner "
+                "dimension")
+        if input.dtype != DataType.nvfp4 or other.dtype != DataType.nvfp4:
+            return "both operands must be nvfp4 (the IF4 GEMM is a separate entry point)"
+        if input.device.type != "cuda" or other.device != input.device:
+            return "both operands must live on the same CUDA device"
+        if not (input.scale_factors_are_in_blackwell_layout and other.scale_factors_are_in_blackwell_layout):
+            return "scale factors must be in the 128x4 tile layout"
+        if DataType(out_dtype) not in _OUT:
+            return f"output type {out_dtype} is not supported"
+        return None
+
+    @classmethod
+    def is_supported(cls, input: QuantizedTensor, other: QuantizedTensor, *, out_dtype: DataType) -> bool:
+        return cls.unsupported_reason(input, other, out_dtype=out_dtype) is None and cls.is_available()
+
+    @classmethod
+    def quantized_matmul(cls, input: QuantizedTensor, other: QuantizedTensor, *, out_dtype: DataType,
+                         out: torch.Tensor | None = None, check_status: bool = False) -> torch.Tensor:
+        """`input @ other.T`, cropped to (input rows, other rows).  `check_status` reads the
+        kernel's device status word back (one synchronisation) and raises on a timeout."""
+        reason = cls.unsupported_reason(input, other, out_dtype=out_dtype)
+        if reason is not None:
+            raise ValueError(f"B200 matmul: {reason}")
+        dev = input.device
+        m, n = input.original_shape[0], other.original_shape[0]
+        m_p, k_p = input.padded_shape
+        n_p = other.padded_shape[0]
+        if other.padded_shape[1] != k_p:
+            raise ValueError("B200 matmul: operands are padded to different inner dimensions")
+        torch_out = _OUT[DataType(out_dtype)]
+        if out is None:
+            out = torch.empty(m, n, dtype=torch_out, device=dev)
+        elif out.shape != (m, n) or out.dtype != torch_out or out.stride(1) != 1:
+            raise ValueError("B200 matmul: `out` has the wrong shape, dtype or layout")
+        alpha = torch.empty(1, dtype=torch.float32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev) if check_status else None
+        a_vals, b_vals = input.values.contiguous(), other.values.contiguous()
+        a_sf, b_sf = input.scale_factors.contiguous(), other.scale_factors.contiguous()
+        fmt = _native.FOS_NVFP4
+        with torch.cuda.device(dev):
+            lib, stream = _native.lib(), _native.stream_ptr(dev)
+            _native.check(lib.fos_gemm_alpha(
+                input.amax.data_ptr(), fmt, input.scale_rule.cuda_id,
+                other.amax.data_ptr(), fmt, other.scale_rule.cuda_id, alpha.data_ptr(), stream), "fos_gemm_alpha")
+            _native.check(lib.fos_gemm_nvfp4(
+                a_vals.data_ptr(), a_sf.data_ptr(), b_vals.data_ptr(), b_sf.data_ptr(), alpha.data_ptr(),
+                out.data_ptr(), _native.elem_code(torch_out), m_p, n_p, k_p, m, n, out.stride(0),
+                0 if status is None else status.data_ptr(), stream), "fos_gemm_nvfp4")
+        if status is not None and int(status.item()) != 0:
+            raise _native.NativeLibraryError(
+                f"fos_gemm_nvfp4: a bounded device-side wait timed out (site {int(status.item())})")
+        return out

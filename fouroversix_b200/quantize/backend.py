@@ -1,0 +1,137 @@
+"""The one quantization back end of this package: hand-written sm_100a kernels behind
+the C ABI in include/fouroversix_b200.h.
+
+It fills the role of the reference's back-end plug-ins (class-method interface of
+src/fouroversix/quantize/backend.py:16-234) for CUDA tensors on a B200 and takes over
+what the reference splits between its CUDA back end (src/fouroversix/quantize/cuda/
+backend.py:13-93: untransposed 1-D NVFP4 only) and its Triton back end
+(src/fouroversix/quantize/triton.py: 2-D blocks, transposed input, IF4).
+"""
+
+from __future__ import annotations
+
+import functools
+
+import torch
+
+from fouroversix_b200 import _native
+from fouroversix_b200.utils import DataType, RoundStyle, ScaleType
+
+from .config import QuantizationConfig
+from .quantized_tensor import QuantizedTensor, padded_shape_for
+
+_FORMATS = {DataType.nvfp4: _native.FOS_NVFP4, DataType.if4: _native.FOS_IF4}
+
+
+def _is_tiled(dtype: DataType) -> bool:
+    # like the reference's PyTorch back end, IF4 keeps its scales row-major
+    # (src/fouroversix/quantize/pytorch/backend.py:107-120)
+    return dtype == DataType.nvfp4
+
+
+class B200QuantizeBackend:
+    """Quantize / dequantize on a B200 through libfouroversix_b200.so."""
+
+    @classmethod
+    @functools.lru_cache
+    def is_available(cls) -> bool:
+        if not torch.cuda.is_available() or torch.cuda.get_device_capability()[0] != 10:
+            return False
+        _native.lib()  # a missing extension on a GPU machine is an error, not "unavailable"
+        return True
+
+    @classmethod
+    def unsupported_reason(cls, x: torch.Tensor, config: QuantizationConfig) -> str | None:
+        """Why this back end cannot run the request, or None when it can."""
+        if x.ndim != 2:
+            return "input must be 2-D"
+        if config.dtype not in _FORMATS:
+            return f"dtype {config.dtype.value} is not implemented (nvfp4 and if4 are)"
+        if config.scale_rule not in config.dtype.supported_scale_rules:
+            return f"scale rule {config.scale_rule.value} is not defined for {config.dtype.value}"
+        if config.round_style != RoundStyle.nearest:
+            return "only round-to-nearest is implemented"
+        if config.rht:
+            return "the random Hadamard transform is not implemented"
+        if x.device.type != "cuda":
+            return "input must be a CUDA tensor (there is no CPU path)"
+        if x.dtype not in (torch.bfloat16, torch.float16):
+            return "input must be bfloat16 or float16"
+        return None
+
+    @classmethod
+    def can_quantize(cls, x: torch.Tensor, config: QuantizationConfig) -> bool:
+        return cls.unsupported_reason(x, config) is None and cls.is_available()
+
+    @classmethod
+    def quantize(cls, x: torch.Tensor, config: QuantizationConfig, *, amax: torch.Tensor | None = None,
+                 exact_only: bool = False) -> QuantizedTensor:
+        """Quantize `x` (or its transpose). `amax`, when given, is a CUDA fp32 tensor that
+        already holds max|x| and saves the extra pass that computes it."""
+        reason = cls.unsupported_reason(x, config)
+        if reason is not None:
+            raise ValueError(f"B200 quantize: {reason}")
+        if x.stride(1) != 1:
+            x = x.contiguous()
+        rows, cols = x.shape
+        out_shape = (cols, rows) if config.transpose else (rows, cols)
+        rows_p, cols_p = padded_shape_for(out_shape, config.dtype)
+        dev = x.device
+        values = torch.empty(rows_p, cols_p // 2, dtype=torch.uint8, device=dev)
+        scales = torch.empty(rows_p * cols_p // 16, dtype=torch.uint8, device=dev)
+        amax_out = torch.empty(1, dtype=torch.float32, device=dev)
+        if amax is not None:
+            amax = amax.detach().reshape(1).to(device=dev, dtype=torch.float32)
+        tiled = _is_tiled(config.dtype)
+        with torch.cuda.device(dev):
+            status = _native.lib().fos_quantize(
+                x.data_ptr(), _native.elem_code(x.dtype), rows, cols, x.stride(0),
+                _FORMATS[config.dtype], config.scale_rule.cuda_id, int(config.block_scale_2d),
+                int(config.transpose), _native.FOS_SF_TILED if tiled else _native.FOS_SF_ROWMAJOR,
+                0 if amax is None else amax.data_ptr(), values.data_ptr(), scales.data_ptr(),
+                amax_out.data_ptr(), _native.FOS_QUANTIZE_EXACT_ONLY if exact_only else 0,
+                _native.stream_ptr(dev))
+        _native.check(status, "fos_quantize")
+        return QuantizedTensor(
+            values, scales.view(torch.float8_e4m3fn), amax_out, config.dtype, out_shape,
+            config.scale_rule, config.round_style, (rows_p, cols_p),
+            scale_factors_are_in_blackwell_layout=tiled)
+
+    @classmethod
+    def can_dequantize(cls, tensor: QuantizedTensor) -> bool:
+        return tensor.dtype in _FORMATS and tensor.device.type == "cuda" and cls.is_available()
+
+    @classmethod
+    def dequantize(cls, tensor: QuantizedTensor, dtype: torch.dtype = torch.bfloat16, *,
+                   intermediate_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+        """High-precision copy of `tensor`, cropped to its original shape. The kernel
+        implements the reference's default fp16 intermediate."""
+        if tensor.dtype not in _FORMATS:
+            raise ValueError(f"B200 dequantize: dtype {tensor.dtype.value} is not implemented")
+        if tensor.device.type != "cuda":
+            raise ValueError("B200 dequantize: tensor must live on a CUDA device (there is no CPU path)")
+        if intermediate_dtype != torch.float16:
+            raise ValueError("B200 dequantize: only the float16 intermediate is implemented")
+        if tensor.dtype.scale_type in (ScaleType.nv, ScaleType.nv_if) and tensor.amax is None:
+            raise ValueError("B200 dequantize: amax is required")
+        rows, cols = tensor.original_shape
+        rows_p, cols_p = tensor.padded_shape
+        dev = tensor.device
+        out = torch.empty(rows, cols, dtype=dtype, device=dev)
+        values = tensor.values.contiguous()
+        scales = tensor.scale_factors.contiguous()
+        amax = tensor.amax.to(device=dev, dtype=torch.float32)
+        with torch.cuda.device(dev):
+            status = _native.lib().fos_dequantize(
+                values.data_ptr(), scales.data_ptr(), amax.data_ptr(), _FORMATS[tensor.dtype],
+                tensor.scale_rule.cuda_id,
+                _native.FOS_SF_TILED if tensor.scale_factors_are_in_blackwell_layout else _native.FOS_SF_ROWMAJOR,
+                rows_p, cols_p, rows, cols, out.data_ptr(), _native.elem_code(dtype), out.stride(0),
+                _native.stream_ptr(dev))
+        _native.check(status, "fos_dequantize")
+        return out
+
+    @classmethod
+    def pseudo_quantize(cls, x: torch.Tensor, config: QuantizationConfig) -> torch.Tensor:
+        """Quantize then dequantize back to x's dtype (two kernels, no host round trip)."""
+        return cls.dequantize(cls.quantize(x, config), dtype=x.dtype)

@@ -1,0 +1,145 @@
+/*
+ * fouroversix_b200 - C ABI of the B200 (sm_100a) kernels for NVFP4 / IF4 block-scaled
+ * quantization with Four-Over-Six adaptive block scaling, and for the FP4 GEMM that
+ * consumes the result.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless stated otherwise. The caller owns every
+ *     buffer; the library never allocates, frees or keeps a pointer after the call.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream). Work is
+ *     enqueued on it and the call returns without synchronising.
+ *   - Return value: FOS_OK (0) or a negative FOS_ERR_* code; fos_status_string() names it.
+ *   - A quantized tensor "Y" is described by three buffers:
+ *       codes  [rows_p, cols_p / 2] bytes, row-major, low nibble = even column
+ *       sf     rows_p * cols_p / 16 bytes of E4M3 block scales, either in the
+ *              128-row x 4-block tile order that tcgen05 block-scaled MMA consumes
+ *              (FOS_SF_TILED) or row-major [rows_p, cols_p / 16] (FOS_SF_ROWMAJOR)
+ *       amax   one float, max |x| of the source tensor
+ *     with rows_p = rows rounded up to 128 and cols_p = cols rounded up to 64.
+ *   - The entry points are re-entrant; calls on different streams may overlap.
+ *
+ * The "replaces" notes cite the reference project (mit-han-lab/fouroversix) by path.
+ */
+#ifndef FOUROVERSIX_B200_H
+#define FOUROVERSIX_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FOS_OK 0
+#define FOS_ERR_INVALID_ARGUMENT (-1)  /* bad enum value, negative size, NULL pointer */
+#define FOS_ERR_UNSUPPORTED (-2)       /* combination this library does not implement */
+#define FOS_ERR_MISALIGNED (-3)        /* pointer or stride breaks a stated alignment rule */
+#define FOS_ERR_CUDA (-4)              /* a CUDA runtime call failed; see fos_last_cuda_error */
+#define FOS_ERR_ARCH (-5)              /* the current device is not compute capability 10.x */
+#define FOS_ERR_TIMEOUT (-6)           /* a bounded device-side wait gave up (status word) */
+#define FOS_ERR_TOO_LARGE (-7)         /* size beyond a documented maximum */
+
+/* element type of a high-precision tensor */
+#define FOS_BF16 0
+#define FOS_FP16 1
+#define FOS_FP32 2                     /* outputs only */
+
+/* 4-bit format */
+#define FOS_NVFP4 0                    /* E2M1 values, E4M3 scale per 16 */
+#define FOS_IF4 1                      /* per block E2M1 or INT4*(6/7); scale sign bit = int */
+
+/* scale rule; same numbers as ScaleRule.cuda_id, src/fouroversix/utils.py:271-280 */
+#define FOS_RULE_STATIC_6 0
+#define FOS_RULE_STATIC_4 1
+#define FOS_RULE_MAE 2
+#define FOS_RULE_MSE 3
+#define FOS_RULE_ABS_MAX 4
+
+#define FOS_SF_ROWMAJOR 0
+#define FOS_SF_TILED 1
+
+/* fos_quantize flags */
+#define FOS_QUANTIZE_EXACT_ONLY 1      /* skip the fast 4-vs-6 pre-filter (testing aid) */
+
+int fos_version(void);
+const char *fos_status_string(int status);
+/* cudaError_t of the most recent FOS_ERR_CUDA on the calling host thread, as an int. */
+int fos_last_cuda_error(void);
+
+/*
+ * Quantize a row-major 2-D tensor x[rows, cols] (bf16 or fp16, row stride `ld`
+ * elements, unit column stride) to Y = x, or to Y = x^T when `transpose` is set.
+ * Writes all of codes / sf (padding included, no pre-zeroing needed) and amax_out.
+ *
+ *   format      FOS_NVFP4 (all five rules) or FOS_IF4 (mae / mse / abs_max)
+ *   block_2d    0: one scale per 1x16 block of Y; 1: one scale per 16x16 block of Y
+ *   sf_layout   FOS_SF_TILED or FOS_SF_ROWMAJOR
+ *   amax_in     NULL: the library computes max|x| itself (one extra pass over x);
+ *               else a device float holding it (skips that pass)
+ *   amax_out    device float; receives the amax that was used (may equal amax_in)
+ *
+ * Results are bit-identical to the reference's PyTorch backend
+ * (src/fouroversix/quantize/pytorch/reference.py:555-679 behind
+ * src/fouroversix/quantize/pytorch/backend.py:40-121) for finite inputs whose scaled
+ * magnitudes stay below 7 (always, unless a block's scale underflows E4M3).
+ *
+ * Replaces: torch.ops.fouroversix.quantize, src/fouroversix/csrc/bindings.cpp:28 and
+ * src/fouroversix/csrc/quantize/fp4_quant.cu:99-239 (which supports only untransposed
+ * 1-D NVFP4); for transposed / 2-D / IF4 it replaces the Triton entry
+ * src/fouroversix/kernels/triton/ops.py:17-209.
+ */
+int fos_quantize(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                 int format, int scale_rule, int block_2d, int transpose, int sf_layout,
+                 const float *amax_in, uint8_t *codes, uint8_t *sf, float *amax_out,
+                 int flags, void *stream);
+
+/*
+ * Dequantize Y (padded shape rows_p x cols_p) into out[rows, cols] (row stride
+ * ld_out elements), cropping the padding: fp16(value) * fp16(|scale|) in fp16, then
+ * (fp32 * amax) / (max value * max scale) and a cast to out_dtype.
+ *
+ * Replaces: QuantizeBackendBase.dequantize, src/fouroversix/quantize/backend.py:88-160
+ * with src/fouroversix/quantize/dequantize_utils.py:4-86; the Triton kernel
+ * src/fouroversix/kernels/triton/dequantize.py:110-154 for IF4.
+ */
+int fos_dequantize(const uint8_t *codes, const uint8_t *sf, const float *amax, int format,
+                   int scale_rule, int sf_layout, int64_t rows_p, int64_t cols_p,
+                   int64_t rows, int64_t cols, void *out, int out_dtype, int64_t ld_out,
+                   void *stream);
+
+/*
+ * alpha[0] = amax_a[0] * amax_b[0] / (divisor(format_a, rule_a) * divisor(format_b, rule_b))
+ * computed on the device (no host synchronisation).
+ *
+ * Replaces: the tensor expression in src/fouroversix/matmul/cutlass/backend.py:85-98.
+ */
+int fos_gemm_alpha(const float *amax_a, int format_a, int rule_a, const float *amax_b,
+                   int format_b, int rule_b, float *alpha, void *stream);
+
+/*
+ * D[m, n] = alpha[0] * sum_k A[m, k] * B[n, k]   ("TN": both operands K-major)
+ * A: codes [m_p, k_p/2] + tiled scales, B: codes [n_p, k_p/2] + tiled scales, both NVFP4
+ * as written by fos_quantize(FOS_SF_TILED). m_p / n_p multiples of 128, k_p a multiple
+ * of 64 (>= 64). Block-scaled tcgen05 MMA (kind::mxf4nvf4, UE4M3 scales per 16), fp32
+ * accumulation in tensor memory, bf16 / fp16 / fp32 output. Only rows < m and columns
+ * < n of D are written (row stride ldd elements; ldd * sizeof(out) a multiple of 16).
+ * `status` is an optional device int32: it stays 0 unless a bounded wait timed out.
+ *
+ * Replaces: gemm_nvfp4nvfp4_accum_fp32_out_{bf16,fp16}_tnt,
+ * src/fouroversix/csrc/bindings.cpp:31-33 and src/fouroversix/csrc/fp4_gemm.cu:40-186.
+ */
+int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                   const uint8_t *b_sf, const float *alpha, void *d, int out_dtype,
+                   int64_t m_p, int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd,
+                   int32_t *status, void *stream);
+
+/*
+ * Process-wide tuning / testing knobs. No counterpart in the reference.
+ *   FOS_OPT_GEMM_BLOCK_N   0 = choose the GEMM tile width per problem (default), 128 or 256
+ */
+#define FOS_OPT_GEMM_BLOCK_N 1
+int fos_set_option(int key, int value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FOUROVERSIX_B200_H */

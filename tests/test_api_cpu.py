@@ -1,0 +1,108 @@
+"""CPU-only checks: the C-ABI library loads and exports what include/*.h declares, and the
+host-side mirror of the reference API behaves like the reference's."""
+
+from __future__ import annotations
+
+import re
+from pathlib import Path
+
+import pytest
+import torch
+import torch.nn as nn
+
+import fouroversix_b200 as fos
+from fouroversix_b200 import _native
+from fouroversix_b200.quantize import from_blocked, to_blocked
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "fouroversix_b200.h").read_text()
+    declared = set(re.findall(r"\b(fos_[a-z0-9_]+)\s*\(", header))
+    assert {"fos_quantize", "fos_dequantize", "fos_gemm_nvfp4", "fos_gemm_alpha"} <= declared
+    lib = _native.lib()
+    missing = [name for name in sorted(declared) if not hasattr(lib, name)]
+    assert not missing, missing
+    # the Python binding table and the header agree
+    assert declared == set(_native.SIGNATURES), declared ^ set(_native.SIGNATURES)
+    assert lib.fos_version() >= 100
+    assert lib.fos_status_string(0) == b"ok"
+    assert b"invalid" in lib.fos_status_string(-1)
+
+
+def test_argument_validation_needs_no_gpu():
+    lib = _native.lib()
+    # NULL pointers and bad enums are rejected before any CUDA call
+    assert lib.fos_quantize(0, 0, 128, 64, 64, 0, 3, 0, 0, 1, 0, 0, 0, 0, 0, 0) == -1
+    assert lib.fos_set_option(1, 192) == -1
+    assert lib.fos_set_option(1, 0) == 0
+
+
+def test_enums_and_config_coercion():
+    cfg = fos.QuantizationConfig(dtype="if4", scale_rule="mae", round_style="nearest", backend="cuda")
+    assert cfg.dtype is fos.DataType.if4 and cfg.scale_rule is fos.ScaleRule.mae
+    assert cfg.backend is fos.QuantizeBackend.cuda
+    assert fos.QuantizationConfig().scale_rule is fos.ScaleRule.mse
+    assert fos.ScaleRule.mse.cuda_id == 3 and fos.ScaleRule.static_6.cuda_id == 0
+    assert fos.DataType.nvfp4.block_size == 16 and fos.DataType.mxfp4.block_size == 32
+    assert fos.DataType.if4.supported_scale_rules == {fos.ScaleRule.mse, fos.ScaleRule.mae, fos.ScaleRule.abs_max}
+    assert fos.DataType.nvfp4.scale_type.get_maximum_value(fos.ScaleRule.mse) == 256
+    assert fos.DataType.nvfp4.scale_type.get_maximum_value(fos.ScaleRule.static_6) == 448
+
+
+def test_quantize_rejects_what_it_cannot_do():
+    x = torch.zeros(128, 64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="No backend found"):
+        fos.quantize(x)                                   # CPU tensor: there is no CPU path
+    with pytest.raises(ValueError, match="does not support"):
+        fos.quantize(x, fos.QuantizationConfig(backend="pytorch"))
+    with pytest.raises(ValueError):
+        fos.quantize(x, fos.QuantizationConfig(dtype="if4", scale_rule="static_6"))
+    with pytest.raises(ValueError):
+        fos.quantize(x.reshape(2, 64, 64))
+
+
+def test_scale_tile_layout_round_trip():
+    a = torch.arange(256 * 8, dtype=torch.int32).reshape(256, 8)
+    b = to_blocked(a)
+    assert torch.equal(from_blocked(b, (256, 8)), a)
+    # element (r, c) of tile t sits at t*512 + (r%32)*16 + (r//32)*4 + c
+    r, c = 77, 6
+    off = ((r // 128) * 2 + c // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + c % 4
+    assert b[off] == a[r, c]
+
+
+def test_quantized_tensor_pads_like_the_reference():
+    values = torch.zeros(100, 40, dtype=torch.uint8)
+    scales = torch.ones(100, 5, dtype=torch.float32).to(torch.float8_e4m3fn)
+    q = fos.QuantizedTensor(values, scales, torch.ones(1), "nvfp4", (100, 80), "mse", "nearest")
+    assert q.padded_shape == (128, 128)
+    assert q.values.shape == (128, 64) and q.scale_factors.numel() == 128 * 8
+    with pytest.raises(ValueError):
+        fos.QuantizedTensor(values, torch.ones(7).to(torch.float8_e4m3fn), torch.ones(1), "nvfp4", (100, 80),
+                            "mse", "nearest")
+
+
+def test_quantize_model_swaps_linear_layers():
+    model = nn.Sequential(nn.Linear(64, 128), nn.ReLU(), nn.Linear(128, 64))
+    model.add_module("lm_head", nn.Linear(64, 10))
+    fos.quantize_model(model, fos.ModelQuantizationConfig(module_config_overrides={"2": {"scale_rule": "static_6"}}))
+    assert isinstance(model[0], fos.FourOverSixLinear) and isinstance(model[2], fos.FourOverSixLinear)
+    assert not isinstance(model.lm_head, fos.FourOverSixLinear)
+    assert model[2].config.weight_scale_rule is fos.ScaleRule.static_6
+    assert model[0].config.weight_scale_rule is fos.ScaleRule.mse
+    sd = model[0].state_dict()
+    assert sd["quantized_weight_values"].shape == (128, 32)
+    assert sd["quantized_weight_scale_factors"].shape == (128 * 64 // 16,)
+    assert sd["quantized_weight_metadata"].shape == (6,)
+    with pytest.raises(ValueError):
+        fos.QuantizedModule.register(nn.Linear)
+
+
+def test_module_config_inherits_defaults():
+    c = fos.ModuleQuantizationConfig(dtype="nvfp4", scale_rule="static_6", weight_scale_2d=True)
+    assert c.get_weight_config(transpose=True) == fos.QuantizationConfig(
+        block_scale_2d=True, scale_rule="static_6", transpose=True)
+    assert c.get_gradient_config().round_style is fos.RoundStyle.stochastic
+    assert isinstance(fos.ModelQuantizationConfig().__hash__(), str)

@@ -1,0 +1,174 @@
+"""Parity of the tcgen05 block-scaled FP4 GEMM with the reference's matmul semantics.
+
+Operands are quantized once and fed to both sides, as in the reference's
+tests/test_matmul.py:19-88.  The other side is the oracle: bf16(deq32(a) @ deq32(b).T).
+Criteria: at most 0.1 % of bf16 outputs differ (the reference's own cross-backend bar,
+tests/test_matmul.py:15) and max |error| <= 1e-2 * max |reference| against the fp32
+product of the dequantized operands.
+"""
+
+from __future__ import annotations
+
+import itertools
+
+import pytest
+import torch
+
+import fouroversix_b200 as fos
+from fouroversix_b200 import _native
+from fouroversix_b200.matmul import B200MatmulBackend
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+MISMATCH_TOLERANCE = 1e-3
+REL_TOLERANCE = 1e-2
+
+
+def _dense_reference(qa: fos.QuantizedTensor, qb: fos.QuantizedTensor) -> torch.Tensor:
+    """fp32 product of the dequantized operands, on the GPU with TF32 off (the dequantize
+    kernel itself is checked bit for bit against the oracle elsewhere)."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        return fos.dequantize(qa, torch.float32) @ fos.dequantize(qb, torch.float32).T
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def _check(out: torch.Tensor, ref32: torch.Tensor, what: str):
+    torch.cuda.synchronize()
+    assert out.shape == ref32.shape, what
+    assert torch.isfinite(out.float()).all(), what
+    denom = ref32.abs().max().clamp_min(1e-30)
+    rel = ((out.float() - ref32).abs().max() / denom).item()
+    assert rel <= REL_TOLERANCE, f"{what}: max relative error {rel}"
+    frac = (out != ref32.to(out.dtype)).float().mean().item()
+    assert frac <= MISMATCH_TOLERANCE, f"{what}: {frac:.3%} of outputs differ"
+
+
+def _synthetic(rows: int, k: int, code_byte: int, scale_byte: int) -> fos.QuantizedTensor:
+    """A quantized tensor built by hand: every code byte and scale byte the same, amax chosen
+    so that alpha = 1 for static_6 operands."""
+    values = torch.full((rows, k // 2), code_byte, dtype=torch.uint8, device=DEV)
+    scales = torch.full((rows * k // 16,), scale_byte, dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+    amax = torch.full((1,), 2688.0, dtype=torch.float32, device=DEV)
+    return fos.QuantizedTensor(values, scales, amax, "nvfp4", (rows, k), "static_6", "nearest", (rows, k))
+
+
+@pytest.mark.parametrize("block_n", [128, 256])
+def test_hand_built_operands(block_n):
+    """All ones times all ones is K; then a scale that differs per row and a code pattern
+    that differs along K catch a wrong scale-tile or swizzle mapping."""
+    lib = _native.lib()
+    assert lib.fos_set_option(1, block_n) == 0
+    try:
+        m, n, k = 256, 256, 512
+        a, b = _synthetic(m, k, 0x22, 0x38), _synthetic(n, k, 0x22, 0x38)     # 1.0 values, 1.0 scales
+        out = B200MatmulBackend.quantized_matmul(a, b, out_dtype=fos.DataType.float32, check_status=True)
+        assert torch.equal(out, torch.full((m, n), float(k), device=DEV))
+
+        g = torch.Generator().manual_seed(0)
+        a.values.copy_(torch.randint(0, 256, a.values.shape, generator=g, dtype=torch.uint8))
+        b.values.copy_(torch.randint(0, 256, b.values.shape, generator=g, dtype=torch.uint8))
+        # positive, finite E4M3 scales between 2^-3 and 8
+        a.scale_factors.view(torch.uint8).copy_(torch.randint(0x20, 0x50, (m * k // 16,), generator=g, dtype=torch.uint8))
+        b.scale_factors.view(torch.uint8).copy_(torch.randint(0x20, 0x50, (n * k // 16,), generator=g, dtype=torch.uint8))
+        out = B200MatmulBackend.quantized_matmul(a, b, out_dtype=fos.DataType.float32, check_status=True)
+        ref = _dense_reference(a, b)
+        # every product is exactly representable and the sums stay below 2^24 ulps: tight bound
+        assert ((out - ref).abs().max() / ref.abs().max()).item() < 1e-5
+    finally:
+        lib.fos_set_option(1, 0)
+
+
+@pytest.mark.parametrize(("m", "n", "k"), list(itertools.product([256, 512, 1024], repeat=3)))
+@pytest.mark.parametrize("scale_rule", ["static_6", "static_4", "mse"])
+def test_matmul_against_oracle(oracle, m, n, k, scale_rule):
+    for seed in range(2):
+        g = torch.Generator().manual_seed(seed)
+        x = torch.randn(m, k, generator=g).bfloat16()
+        y = torch.randn(n, k, generator=g).bfloat16()
+        cfg = fos.QuantizationConfig(scale_rule=scale_rule)
+        qx, qy = fos.quantize(x.to(DEV), cfg), fos.quantize(y.to(DEV), cfg)
+        out = B200MatmulBackend.quantized_matmul(qx, qy, out_dtype=fos.DataType.bfloat16, check_status=True)
+        ox, oy = oracle.quantize(x, scale_rule=scale_rule), oracle.quantize(y, scale_rule=scale_rule)
+        want = oracle.matmul(ox, oy, torch.bfloat16) if m * n * k <= 256 * 512 * 1024 else None
+        ref32 = _dense_reference(qx, qy)
+        _check(out, ref32, f"{m}x{n}x{k} {scale_rule} seed {seed}")
+        if want is not None:
+            frac = (out.cpu() != want).float().mean().item()
+            assert frac <= MISMATCH_TOLERANCE, f"vs oracle matmul: {frac:.3%} differ"
+
+
+def test_golden_matmul_cases(golden):
+    for mm in golden["matmul"]:
+        ca, cb = mm["cfg_a"], mm["cfg_b"]
+        if ca.get("dtype", "nvfp4") != "nvfp4":
+            continue
+        out = fos.quantized_matmul(mm["a"].to(DEV), mm["b"].to(DEV), input_config=fos.QuantizationConfig(**ca),
+                                   other_config=fos.QuantizationConfig(**cb), check_status=True)
+        want = mm["out_bf16"]
+        assert out.shape == want.shape
+        frac = (out.cpu() != want).float().mean().item()
+        assert frac <= MISMATCH_TOLERANCE, (ca, cb, frac)
+        rel = ((out.cpu().float() - mm["out_fp32"]).abs().max() / mm["out_fp32"].abs().max()).item()
+        assert rel <= REL_TOLERANCE
+
+
+@pytest.mark.parametrize("shape", [(100, 72, 80), (130, 300, 192), (128, 128, 64), (257, 129, 1000), (384, 640, 448)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float16", "float32"])
+def test_ragged_shapes_and_output_types(shape, out_dtype):
+    m, n, k = shape
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(m, k, generator=g).bfloat16().to(DEV)
+    y = (torch.randn(n, k, generator=g) * 0.05).bfloat16().to(DEV)
+    qx, qy = fos.quantize(x), fos.quantize(y)
+    for block_n in (128, 256):
+        _native.lib().fos_set_option(1, block_n)
+        try:
+            out = B200MatmulBackend.quantized_matmul(qx, qy, out_dtype=fos.DataType(out_dtype), check_status=True)
+        finally:
+            _native.lib().fos_set_option(1, 0)
+        ref32 = _dense_reference(qx, qy)
+        if out_dtype == "float32":
+            assert ((out - ref32).abs().max() / ref32.abs().max()).item() < 1e-5
+        else:
+            _check(out, ref32, f"{shape} {out_dtype} block_n={block_n}")
+
+
+def test_output_is_cropped_and_nothing_else_is_written():
+    m, n, k = 100, 72, 128
+    g = torch.Generator().manual_seed(3)
+    qx = fos.quantize(torch.randn(m, k, generator=g).bfloat16().to(DEV))
+    qy = fos.quantize(torch.randn(n, k, generator=g).bfloat16().to(DEV))
+    canvas = torch.full((m + 2, n + 8), 7.0, dtype=torch.bfloat16, device=DEV)
+    view = canvas[1:m + 1, :n]
+    B200MatmulBackend.quantized_matmul(qx, qy, out_dtype=fos.DataType.bfloat16, out=view, check_status=True)
+    torch.cuda.synchronize()
+    assert (canvas[0] == 7).all() and (canvas[-1] == 7).all() and (canvas[:, n:] == 7).all()
+    _check(view, _dense_reference(qx, qy), "cropped")
+
+
+@pytest.mark.parametrize("name,m,n,k,rule", [
+    ("c2-act-x-weight-static6", 8192, 4096, 4096, "static_6"),
+    ("c2-act-x-weight-4over6", 8192, 4096, 4096, "mse"),
+    ("c2-square-8192", 8192, 8192, 8192, "mse"),
+])
+def test_full_size_configs(name, m, n, k, rule):
+    g = torch.Generator().manual_seed(1)
+    a = torch.randn(m, k, generator=g)
+    if "act" in name:
+        a[:, torch.randperm(k, generator=g)[: k // 100]] *= 20
+        b = torch.randn(n, k, generator=g) * 0.02
+    else:
+        b = torch.randn(n, k, generator=g)
+    cfg = fos.QuantizationConfig(scale_rule=rule)
+    qa, qb = fos.quantize(a.bfloat16().to(DEV), cfg), fos.quantize(b.bfloat16().to(DEV), cfg)
+    out = B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType.bfloat16, check_status=True)
+    _check(out, _dense_reference(qa, qb), name)
+    # linearity in alpha: doubling one operand's amax doubles every output exactly (power of two)
+    qa2 = fos.QuantizedTensor(qa.values, qa.scale_factors, qa.amax * 2, qa.dtype, qa.original_shape,
+                              qa.scale_rule, qa.round_style, qa.padded_shape)
+    out2 = B200MatmulBackend.quantized_matmul(qa2, qb, out_dtype=fos.DataType.bfloat16, check_status=True)
+    assert torch.equal(out2.float(), out.float() * 2)

@@ -1,0 +1,165 @@
+"""Parity of the CUDA quantize / dequantize kernels with the reference, on a B200.
+
+Three layers, all bit-exact (codes, scales, amax, hence every 4-vs-6 / int-vs-float
+block choice):
+  1. the committed golden vectors produced by the reference's PyTorch backend,
+  2. the CPU oracle on larger seeded inputs, following the parameter sweep of the
+     reference's tests/test_quantize.py:23-314 (input kinds, shapes, rules, 2-D blocks,
+     transposition, formats, several seeds),
+  3. the benchmark's full-size tensors against the oracle.
+Every comparison also asserts that no scaled magnitude reached 7, the point where the
+reference's unclamped rounding and the hardware's saturating conversion would part ways.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import fouroversix_b200 as fos
+from fouroversix_b200.quantize.backend import B200QuantizeBackend
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _cfg(d: dict) -> fos.QuantizationConfig:
+    return fos.QuantizationConfig(**{k: v for k, v in d.items() if k != "backend"})
+
+
+def _assert_same(q: fos.QuantizedTensor, values, scales, amax, name):
+    torch.cuda.synchronize()
+    got_v, got_s = q.values.cpu(), q.scale_factors.view(torch.uint8).flatten().cpu()
+    n_v, n_s = int((got_v != values).sum()), int((got_s != scales).sum())
+    assert n_v == 0 and n_s == 0, f"{name}: {n_v} code bytes and {n_s} scale bytes differ"
+    assert torch.equal(q.amax.cpu().reshape(1), amax.reshape(1)), name
+
+
+@pytest.mark.parametrize("exact_only", [False, True], ids=["fast-filter", "exact-only"])
+def test_golden_vectors(golden, exact_only):
+    for case in golden["cases"]:
+        x = golden["inputs"][case["input"]].to(DEV)
+        cfg = _cfg(case["config"])
+        q = B200QuantizeBackend.quantize(x, cfg, exact_only=exact_only)
+        assert q.padded_shape == tuple(case["padded_shape"]) and q.original_shape == tuple(case["original_shape"])
+        assert q.scale_factors_are_in_blackwell_layout == case["tiled"]
+        _assert_same(q, case["values"], case["scale_factors"], case["amax"], case["name"])
+        for key, dt in (("dequant_bf16", torch.bfloat16), ("dequant_fp16", torch.float16),
+                        ("dequant_fp32", torch.float32)):
+            if key in case:
+                out = fos.dequantize(q, dt).cpu()
+                view = torch.int32 if dt == torch.float32 else torch.int16
+                assert torch.equal(out.view(view), case[key].contiguous().view(view)), (case["name"], key)
+
+
+def _make_input(kind: str, shape, seed: int) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed)
+    if kind == "zeros":
+        return torch.zeros(shape, dtype=torch.bfloat16)
+    if kind == "ones":
+        return torch.ones(shape, dtype=torch.bfloat16)
+    if kind == "rand01":
+        return torch.rand(shape, generator=g).bfloat16()
+    if kind == "outlier":
+        a = torch.randn(shape, generator=g)
+        a[:, torch.randperm(shape[1], generator=g)[: max(1, shape[1] // 100)]] *= 20
+        return a.bfloat16()
+    if kind == "small":
+        return (torch.randn(shape, generator=g) * 0.02).bfloat16()
+    return torch.randn(shape, generator=g).bfloat16()
+
+
+SWEEP_RULES = {"nvfp4": ["abs_max", "mae", "mse", "static_4", "static_6"], "if4": ["abs_max", "mae", "mse"]}
+
+
+@pytest.mark.parametrize("kind", ["zeros", "ones", "rand01", "randn", "outlier", "small"])
+@pytest.mark.parametrize("shape", [(1024, 1024), (1024, 512), (512, 1024)])
+def test_sweep_against_oracle(oracle, kind, shape):
+    seeds = [0] if kind in ("zeros", "ones") else [0, 1, 2]
+    for seed in seeds:
+        x = _make_input(kind, shape, seed)
+        xd = x.to(DEV)
+        for dtype, rules in SWEEP_RULES.items():
+            for rule in rules:
+                for two_d in (False, True):
+                    for transpose in (False, True):
+                        cfg = fos.QuantizationConfig(dtype=dtype, scale_rule=rule, block_scale_2d=two_d,
+                                                     transpose=transpose)
+                        q = fos.quantize(xd, cfg)
+                        ref = oracle.quantize(x, dtype=dtype, scale_rule=rule, block_scale_2d=two_d,
+                                              transpose=transpose)
+                        assert ref.worst_scaled < 7.0
+                        name = f"{kind}{shape} seed{seed} {dtype} {rule} 2d={two_d} t={transpose}"
+                        _assert_same(q, ref.values, ref.scale_factors, ref.amax, name)
+
+
+def test_dequantize_against_oracle(oracle):
+    x = _make_input("randn", (384, 320), 5)
+    for dtype, rule in [("nvfp4", "mse"), ("nvfp4", "static_6"), ("nvfp4", "static_4"), ("if4", "mse")]:
+        q = fos.quantize(x.to(DEV), fos.QuantizationConfig(dtype=dtype, scale_rule=rule))
+        ref = oracle.quantize(x, dtype=dtype, scale_rule=rule)
+        for out_dtype, view in [(torch.bfloat16, torch.int16), (torch.float16, torch.int16),
+                                (torch.float32, torch.int32)]:
+            got = fos.dequantize(q, out_dtype).cpu()
+            want = oracle.dequantize(ref, out_dtype)
+            assert torch.equal(got.view(view), want.view(view)), (dtype, rule, out_dtype)
+        # fused fake-quantization = quantize then dequantize in the input's dtype
+        fake = fos.quantize(x.to(DEV), fos.QuantizationConfig(dtype=dtype, scale_rule=rule, pseudo_quantize=True))
+        assert torch.equal(fake.cpu().view(torch.int16), oracle.dequantize(ref, torch.bfloat16).view(torch.int16))
+
+
+def test_ragged_unaligned_strided_and_fp16_inputs(oracle):
+    g = torch.Generator().manual_seed(11)
+    wide = torch.randn(256, 512, generator=g).bfloat16()
+    wide_dev = wide.to(DEV)
+    cases = [  # (CPU tensor, the same tensor on the GPU)
+        (a, a.to(DEV)) for a in (
+            torch.randn(100, 80, generator=g).bfloat16(),
+            torch.randn(37, 53, generator=g).bfloat16(),        # nothing aligned, partial blocks
+            torch.randn(130, 200, generator=g).half(),
+        )
+    ] + [
+        (wide[:, 8:264], wide_dev[:, 8:264]),                    # row stride != width, 16-byte aligned only
+        (wide[:, 3:200], wide_dev[:, 3:200]),                    # unaligned start, ragged width
+        (wide[5:200, 16:80], wide_dev[5:200, 16:80]),
+    ]
+    for x, xd in cases:
+        assert xd.stride() == x.stride()
+        for cfg in (dict(), dict(scale_rule="static_6"), dict(dtype="if4"), dict(block_scale_2d=True)):
+            q = fos.quantize(xd, fos.QuantizationConfig(**cfg))
+            ref = oracle.quantize(x, **cfg)
+            _assert_same(q, ref.values, ref.scale_factors, ref.amax, f"{tuple(x.shape)} {x.dtype} {cfg}")
+            got = fos.dequantize(q).cpu()
+            assert got.shape == x.shape
+            assert torch.equal(got.view(torch.int16), oracle.dequantize(ref).view(torch.int16))
+
+
+def test_caller_supplied_amax_skips_the_reduction(oracle):
+    x = _make_input("randn", (256, 256), 3)
+    xd = x.to(DEV)
+    amax = xd.abs().max().float().reshape(1)
+    q = B200QuantizeBackend.quantize(xd, fos.QuantizationConfig(), amax=amax)
+    ref = oracle.quantize(x)
+    _assert_same(q, ref.values, ref.scale_factors, ref.amax, "amax given")
+
+
+@pytest.mark.parametrize("name,shape,seed,cfg", [
+    ("c1-4096x4096-mse", (4096, 4096), 0, dict()),
+    ("c1-4096x4096-static6", (4096, 4096), 0, dict(scale_rule="static_6")),
+    ("c2-act-8192x4096-mse", (8192, 4096), 1, dict()),
+    ("c3-if4-4096x4096", (4096, 4096), 5, dict(dtype="if4")),
+    ("c4-weight-2d", (4096, 4096), 10, dict(block_scale_2d=True)),
+    ("c4-act-transposed", (4096, 4096), 9, dict(transpose=True)),
+])
+def test_full_size_configs_bit_exact(oracle, name, shape, seed, cfg):
+    kind = "outlier" if name.startswith("c2") else ("small" if "weight" in name else "randn")
+    x = _make_input(kind, shape, seed)
+    q = fos.quantize(x.to(DEV), fos.QuantizationConfig(**cfg))
+    ref = oracle.quantize(x, **cfg)
+    assert ref.worst_scaled < 7.0
+    _assert_same(q, ref.values, ref.scale_factors, ref.amax, name)
+    # round trip: dequantize(quantize(x)) stays within half an FP4 step of x everywhere
+    back = fos.dequantize(q, torch.float32).cpu()
+    xf = x.float().T if cfg.get("transpose") else x.float()
+    assert (back - xf).abs().max() <= 0.26 * x.float().abs().max()
