@@ -89,6 +89,31 @@ __device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(h2 & 0xffffu)));
 }
 
+// ---- packed binary32 pairs (sm_100: one instruction, two IEEE operations) ----
+
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2f(uint64_t v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// Element-wise fma.rn on two binary32 lanes; each lane rounds exactly like fmaf().
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// a / 6 correctly rounded for every finite bf16 or fp16 value a (checked exhaustively on the
+// host, see tests): quotient estimate, exact remainder, one correction.
+__device__ __forceinline__ float div6_exact(float a) {
+    const float y = 1.0f / 6.0f;
+    const float q0 = __fmul_rn(a, y);
+    return __fmaf_rn(__fmaf_rn(-6.0f, q0, a), y, q0);
+}
+
 // ---- memory ----
 
 __device__ __forceinline__ uint4 ldg_nc_16(const void *p) {

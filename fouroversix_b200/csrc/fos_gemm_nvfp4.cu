@@ -59,6 +59,7 @@ struct GemmParams {
     int64_t m_p, n_p, k_p;   // padded problem (k_p in values)
     int64_t m, n, ldd;       // region of D that is written
     int out_dtype;
+    int debug;               // FOS_OPT_GEMM_DEBUG bits (timing experiments only; results are wrong)
 };
 
 // ---------------------------------------------------------------------------- PTX wrappers
@@ -149,6 +150,64 @@ __device__ __forceinline__ void tc_load_32cols(uint32_t taddr, uint32_t (&r)[32]
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- wrappers used by the CTA-pair (cta_group::2) kernel ----
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;"
+                 ::"r"(cluster_bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                 "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA tile loads whose completion is signalled on a barrier that may live in the peer CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1,
+                                                 uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2,
+                                                 uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tc_copy_sf_pair(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p; }\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+// Arrive on the barrier at the same shared-memory offset in both CTAs of the pair once all
+// tcgen05 operations issued so far by this thread have completed.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(static_cast<uint16_t>(3)) : "memory");
+}
+
 // Shared-memory matrix descriptor. Bits: [0,14) start address >> 4, [16,30) leading byte
 // offset >> 4, [32,46) stride byte offset >> 4, [46,48) version = 1 on sm_100, [61,64)
 // swizzle mode (0 none, 2 128-byte).
@@ -160,8 +219,8 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
 // Instruction descriptor of kind::mxf4nvf4 block-scaled MMA: A and B E2M1 (code 1 in bits
 // [7,10) and [10,13)), both K-major, N >> 3 in [17,23), UE4M3 scales (bit 23 = 0), M >> 4 in
 // [24,29), scale-factor byte ids 0, dense K = 64.
-__device__ __forceinline__ uint32_t mma_idesc(int n) {
-    return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
+__device__ __forceinline__ uint32_t mma_idesc(int n, int m = BLOCK_M) {
+    return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 // Tile order: bands of GROUP_M row blocks, column blocks inside a band, so that the CTAs
@@ -249,7 +308,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int64_t k_blocks = p.k_p / 64;                       // MMA K-blocks in the problem
     const int64_t k_tiles = (k_blocks + KB_PER_STAGE - 1) / KB_PER_STAGE;
 
-    if (warp == 0 && lane == 0) {
+    const bool dbg_no_sf = p.debug & 1, dbg_no_load = p.debug & 2, dbg_no_store = p.debug & 4;
+    if (warp == 0 && lane == 0 && !dbg_no_load) {
         // ------------------------------------------------------------------ TMA producer
         uint32_t it = 0;
         bool ok = true;
@@ -300,7 +360,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
             for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
                 const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-                ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
+                if (!dbg_no_load) ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
                 if (!ok) break;
                 tc_fence_after();
                 const int64_t kb0 = kt * KB_PER_STAGE;
@@ -308,7 +368,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const uint32_t stage = smem_base + s * C::STAGE_BYTES;
                 const uint32_t sfa_smem = stage + A_BYTES + C::B_BYTES, sfb_smem = sfa_smem + SFA_BYTES;
                 // scale tiles: 32 rows of 16 bytes, 8-row groups 128 bytes apart, no swizzle
-                for (int kb = 0; kb < nkb; ++kb) {
+                for (int kb = 0; kb < nkb && !(dbg_no_sf && it > 0); ++kb) {
                     tc_copy_sf(tmem_base + SFA_COL + 4 * kb, smem_desc(sfa_smem + kb * SF_TILE_BYTES, 0, 128, 0));
                     for (int g = 0; g < C::N_GROUPS; ++g)
                         if (n0 + 128 * g < p.n_p)
@@ -351,7 +411,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 uint32_t v[32];
                 tc_load_32cols(t_acc + 32 * c, v);
                 const int64_t left = p.n - col;
-                if (row < p.m)
+                if (row < p.m && !dbg_no_store)
                     store_chunk<OUT>(out + row * p.ldd + col, v, alpha, left < 32 ? static_cast<int>(left) : 32, vec_ok);
             }
             tc_fence_before();
@@ -367,6 +427,188 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
+
+// ---------------------------------------------------------------------------- CTA-pair kernel
+//
+// Two CTAs of a cluster (two SMs) compute one 256 x 256 tile with cta_group::2 MMAs: CTA r of
+// the pair holds rows m0 + 128 r .. of A and rows n0 + 128 r .. of B in its shared memory,
+// and the tensor cores of both SMs read both halves of B. Each byte of B fetched from L2
+// therefore feeds twice as many multiply-adds as in the single-CTA kernel, which is what
+// that kernel is short of. Only the even CTA (the leader) issues scale copies and MMAs;
+// both CTAs run a TMA producer and an epilogue for their own 128 rows of the tile.
+//
+//   full[s]      leader's barrier, 2 arrivals: each producer announces its own bytes and its
+//                TMA loads (cta_group::2 form) complete on the leader's barrier
+//   empty[s]     one per CTA, released in both CTAs by the leader's tcgen05.commit
+//   acc_full     one per CTA, same mechanism
+//   acc_empty    leader's barrier, 16 arrivals: 8 epilogue warps of each CTA
+namespace pair {
+
+constexpr int TILE_N = 256;
+constexpr int B_HALF_BYTES = 128 * BLOCK_K_BYTES;                         // this CTA's 128 rows of B
+constexpr int SFB_BYTES = 2 * KB_PER_STAGE * SF_TILE_BYTES;               // scales of all 256 B rows
+constexpr int STAGE_BYTES = A_BYTES + B_HALF_BYTES + SFA_BYTES + SFB_BYTES;  // 38 KiB
+constexpr int STAGES = 5;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
+static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
+
+template <typename OUT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                       const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + STAGES * STAGE_BYTES);
+    const uint32_t full_bar = smem_u32(bars);                 // [STAGES], used in the leader only
+    const uint32_t empty_bar = full_bar + 8 * STAGES;         // [STAGES]
+    const uint32_t acc_full_bar = empty_bar + 8 * STAGES;
+    const uint32_t acc_empty_bar = acc_full_bar + 8;          // used in the leader only
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();                 // 0 = leader
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar + 8 * s, 2);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        mbar_init(acc_full_bar, 1);
+        mbar_init(acc_empty_bar, 2 * EPI_WARPS);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();            // both CTAs have initialised their barriers and tensor memory
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t num_m = p.m_p / 256, num_n = p.n_p / TILE_N;
+    const int64_t num_tiles = num_m * num_n;
+    const int64_t k_blocks = p.k_p / 64;
+    const int64_t k_tiles = (k_blocks + KB_PER_STAGE - 1) / KB_PER_STAGE;
+    const int64_t pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+    const bool dbg_no_sf = p.debug & 1, dbg_no_load = p.debug & 2, dbg_no_store = p.debug & 4;
+    if (warp == 0 && lane == 0 && !dbg_no_load) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
+            int64_t mb, nb;
+            tile_coords(t, num_m, num_n, mb, nb);
+            const int m0 = static_cast<int>(mb * 256 + rank * 128), n0 = static_cast<int>(nb * TILE_N);
+            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                ok = mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 1);
+                if (!ok) break;
+                const uint32_t stage = smem_base + s * STAGE_BYTES;
+                const uint32_t bar = map_to_cta(full_bar + 8 * s, 0);
+                const int kb0 = static_cast<int>(kt * KB_PER_STAGE);
+                // out-of-range parts of a box are zero-filled and still counted, so the byte count is fixed
+                mbar_expect_tx_cluster(bar, STAGE_BYTES);
+                tma_load_2d_pair(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), m0, bar);
+                tma_load_2d_pair(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES),
+                                 n0 + static_cast<int>(rank) * 128, bar);
+                tma_load_3d_pair(stage + A_BYTES + B_HALF_BYTES, &map_sfa, 0, kb0, m0 / 128, bar);
+                tma_load_3d_pair(stage + A_BYTES + B_HALF_BYTES + SFA_BYTES, &map_sfb, 0, kb0, n0 / 128, bar);
+            }
+        }
+        if (!ok) {
+            const unsigned long long t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+    } else if (warp == 1 && lane == 0 && leader) {
+        // ------------------------------------------------------------------ MMA issuer (leader only)
+        const uint32_t idesc = mma_idesc(TILE_N, 256);
+        uint32_t it = 0, tile_i = 0;
+        bool ok = true;
+        for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs, ++tile_i) {
+            ok = mbar_wait(acc_empty_bar, (tile_i & 1u) ^ 1u, abort_flag, p.status, 3);
+            if (!ok) break;
+            tc_fence_after();
+            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                if (!dbg_no_load) ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const int64_t kb0 = kt * KB_PER_STAGE;
+                const int nkb = static_cast<int>((k_blocks - kb0) < KB_PER_STAGE ? (k_blocks - kb0) : KB_PER_STAGE);
+                const uint32_t stage = smem_base + s * STAGE_BYTES;
+                const uint32_t sfa_smem = stage + A_BYTES + B_HALF_BYTES, sfb_smem = sfa_smem + SFA_BYTES;
+                for (int kb = 0; kb < nkb && !(dbg_no_sf && it > 0); ++kb) {
+                    tc_copy_sf_pair(tmem_base + SFA_COL + 4 * kb, smem_desc(sfa_smem + kb * SF_TILE_BYTES, 0, 128, 0));
+                    for (int g = 0; g < 2; ++g)
+                        tc_copy_sf_pair(tmem_base + SFB_COL + 8 * kb + 4 * g,
+                                        smem_desc(sfb_smem + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES, 0, 128, 0));
+                }
+                const uint64_t a_desc = smem_desc(stage, 16, 1024, 2);
+                const uint64_t b_desc = smem_desc(stage + A_BYTES, 16, 1024, 2);
+                for (int kb = 0; kb < nkb; ++kb)
+                    tc_mma_nvf4_pair(tmem_base, a_desc + 2 * kb, b_desc + 2 * kb, idesc, tmem_base + SFA_COL + 4 * kb,
+                                     tmem_base + SFB_COL + 8 * kb, (kt > 0 || kb > 0) ? 1u : 0u);
+                tc_commit_pair(empty_bar + 8 * s);
+            }
+            if (ok) tc_commit_pair(acc_full_bar);
+        }
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------------ epilogue (both CTAs)
+        const int quad = warp & 3;                       // tensor-memory lanes 32*quad .. +31
+        const int half = (warp - 2) >> 2;                // which 128 of the 256 columns
+        const float alpha = __ldg(p.alpha);
+        OUT *out = static_cast<OUT *>(p.d);
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((p.ldd * sizeof(OUT)) % 16 == 0);
+        const uint32_t leader_acc_empty = map_to_cta(acc_empty_bar, 0);
+        uint32_t tile_i = 0;
+        bool ok = true;
+        for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs, ++tile_i) {
+            int64_t mb, nb;
+            tile_coords(t, num_m, num_n, mb, nb);
+            const int64_t row = mb * 256 + rank * 128 + quad * 32 + lane, n0 = nb * TILE_N + half * 128;
+            ok = mbar_wait(acc_full_bar, tile_i & 1u, abort_flag, p.status, 4);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + half * 128;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                const int64_t col = n0 + 32 * c;
+                if (col >= p.n) break;
+                uint32_t v[32];
+                tc_load_32cols(t_acc + 32 * c, v);
+                const int64_t left = p.n - col;
+                if (row < p.m && !dbg_no_store)
+                    store_chunk<OUT>(out + row * p.ldd + col, v, alpha, left < 32 ? static_cast<int>(left) : 32, vec_ok);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();            // nobody leaves while the peer may still touch this CTA's memory
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace pair
 
 // ---------------------------------------------------------------------------- host side
 
@@ -402,6 +644,54 @@ int make_operand_map(CUtensorMap *map, const uint8_t *codes, int64_t rows, int64
     return r == CUDA_SUCCESS ? FOS_OK : FOS_ERR_CUDA;
 }
 
+// Scale tiles as a 3-D tensor [row groups][K-blocks][512 bytes]; box = `groups` x 4 K-blocks.
+int make_scale_map(CUtensorMap *map, const uint8_t *sf, int64_t row_groups, int64_t k_blocks, int groups) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return FOS_ERR_CUDA;
+    cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(k_blocks), static_cast<cuuint64_t>(row_groups)};
+    cuuint64_t strides[2] = {512, static_cast<cuuint64_t>(k_blocks) * 512};
+    cuuint32_t box[3] = {128, static_cast<cuuint32_t>(KB_PER_STAGE), static_cast<cuuint32_t>(groups)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t *>(sf), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? FOS_OK : FOS_ERR_CUDA;
+}
+
+template <typename OUT>
+int launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &msa, const CUtensorMap &msb,
+                const GemmParams &p, cudaStream_t stream) {
+    auto kernel = pair::gemm_nvfp4_pair_kernel<OUT>;
+    static int max_clusters[64] = {};   // per device: how many CTA pairs can be resident at once
+    int dev = 0;
+    FOS_CUDA_TRY(cudaGetDevice(&dev));
+    const int slot = (dev >= 0 && dev < 64) ? dev : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(pair::THREADS);
+    cfg.dynamicSmemBytes = pair::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (max_clusters[slot] == 0) {
+        FOS_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES));
+        int sms = 0, n = 0;
+        FOS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1));
+        FOS_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+        max_clusters[slot] = n > 0 ? n : 1;
+    }
+    const int64_t tiles = (p.m_p / 256) * (p.n_p / 256);
+    const int64_t pairs = tiles < max_clusters[slot] ? tiles : max_clusters[slot];
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    FOS_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ma, mb, msa, msb, p));
+    return FOS_OK;
+}
+
 template <int BLOCK_N, typename OUT>
 int launch(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p, int sms, cudaStream_t stream) {
     using C = Cfg<BLOCK_N>;
@@ -427,14 +717,19 @@ int launch_out(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p
     return launch<BLOCK_N, float>(ma, mb, p, sms, stream);
 }
 
-int g_force_block_n = 0;
+int g_gemm_variant = 0;   // FOS_OPT_GEMM_VARIANT
+int g_gemm_debug = 0;     // FOS_OPT_GEMM_DEBUG
 
 }  // namespace
 }  // namespace fos
 
 extern "C" int fos_set_option(int key, int value) {
-    if (key == FOS_OPT_GEMM_BLOCK_N && (value == 0 || value == 128 || value == 256)) {
-        fos::g_force_block_n = value;
+    if (key == FOS_OPT_GEMM_VARIANT && (value == 0 || value == 128 || value == 256 || value == 2)) {
+        fos::g_gemm_variant = value;
+        return FOS_OK;
+    }
+    if (key == FOS_OPT_GEMM_DEBUG && value >= 0 && value < 8) {
+        fos::g_gemm_debug = value;
         return FOS_OK;
     }
     return FOS_ERR_INVALID_ARGUMENT;
@@ -461,19 +756,32 @@ extern "C" int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const
     FOS_CUDA_TRY(cudaGetDevice(&dev));
     FOS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
 
-    // 128 x 256 tiles unless the problem is too small to give every SM one of them
+    GemmParams p{a_sf, b_sf, alpha, d, status, m_p, n_p, k_p, m, n, ldd, out_dtype, g_gemm_debug};
+    if (status) FOS_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    CUtensorMap map_a, map_b;
+
+    // CTA pairs on 256 x 256 tiles when the shape allows it and there is enough work for most pairs
+    const bool pair_fits = m_p % 256 == 0 && n_p % 256 == 0;
+    bool use_pair = pair_fits && (m_p / 256) * (n_p / 256) >= sms / 4;
+    if (g_gemm_variant == 2) use_pair = pair_fits;
+    if (g_gemm_variant == 128 || g_gemm_variant == 256) use_pair = false;
+    if (use_pair) {
+        CUtensorMap map_sfa, map_sfb;
+        if ((st = make_operand_map(&map_a, a_codes, m_p, k_p / 2, 128)) != FOS_OK) return st;
+        if ((st = make_operand_map(&map_b, b_codes, n_p, k_p / 2, 128)) != FOS_OK) return st;
+        if ((st = make_scale_map(&map_sfa, a_sf, m_p / 128, k_p / 64, 1)) != FOS_OK) return st;
+        if ((st = make_scale_map(&map_sfb, b_sf, n_p / 128, k_p / 64, 2)) != FOS_OK) return st;
+        if (out_dtype == FOS_BF16) return launch_pair<__nv_bfloat16>(map_a, map_b, map_sfa, map_sfb, p, stream);
+        if (out_dtype == FOS_FP16) return launch_pair<__half>(map_a, map_b, map_sfa, map_sfb, p, stream);
+        return launch_pair<float>(map_a, map_b, map_sfa, map_sfb, p, stream);
+    }
+
+    // single-CTA kernel: 128 x 256 tiles unless that would leave SMs without a tile
     const int64_t tiles_256 = (m_p / BLOCK_M) * ((n_p + 255) / 256);
     bool wide = n_p >= 256 && tiles_256 >= sms;
-    if (g_force_block_n == 128) wide = false;
-    if (g_force_block_n == 256) wide = true;
-
-    CUtensorMap map_a, map_b;
-    st = make_operand_map(&map_a, a_codes, m_p, k_p / 2, BLOCK_M);
-    if (st != FOS_OK) return st;
-    st = make_operand_map(&map_b, b_codes, n_p, k_p / 2, wide ? 256 : 128);
-    if (st != FOS_OK) return st;
-
-    GemmParams p{a_sf, b_sf, alpha, d, status, m_p, n_p, k_p, m, n, ldd, out_dtype};
-    if (status) FOS_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    if (g_gemm_variant == 128) wide = false;
+    if (g_gemm_variant == 256) wide = true;
+    if ((st = make_operand_map(&map_a, a_codes, m_p, k_p / 2, BLOCK_M)) != FOS_OK) return st;
+    if ((st = make_operand_map(&map_b, b_codes, n_p, k_p / 2, wide ? 256 : 128)) != FOS_OK) return st;
     return wide ? launch_out<256>(map_a, map_b, p, sms, stream) : launch_out<128>(map_a, map_b, p, sms, stream);
 }

@@ -46,27 +46,38 @@ struct QuantParams {
 // ------------------------------------------------------------------------------------
 
 template <typename T>
+__device__ __forceinline__ float abs_max8(uint4 w) {
+    float2 a = unpack2<T>(w.x), b = unpack2<T>(w.y), c = unpack2<T>(w.z), d = unpack2<T>(w.w);
+    return fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))),
+                 fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(d.x), fabsf(d.y))));
+}
+
+// max |x| with 16-byte loads, four of them in flight per thread, then one atomicMax per CTA.
+template <typename T>
 __global__ void __launch_bounds__(256) amax_kernel(const T *__restrict__ x, int64_t rows, int64_t cols,
                                                    int64_t ld, int vec16, float *amax) {
     float m = 0.0f;
+    const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     if (vec16) {
         const int64_t chunks_per_row = cols >> 3;
         const int64_t total = rows * chunks_per_row;
-        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
-             i += (int64_t)gridDim.x * blockDim.x) {
-            int64_t r = i / chunks_per_row, c = i - r * chunks_per_row;
-            uint4 w = ldg_nc_16(x + r * ld + c * 8);
-            uint32_t ws[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                float2 f = unpack2<T>(ws[k]);
-                m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
-            }
+        const bool flat = ld == cols;
+        auto chunk_ptr = [&](int64_t i) {
+            if (flat) return x + i * 8;
+            const int64_t r = i / chunks_per_row;
+            return x + r * ld + (i - r * chunks_per_row) * 8;
+        };
+        int64_t i = tid;
+        for (; i + 3 * stride < total; i += 4 * stride) {
+            const uint4 w0 = ldg_nc_16(chunk_ptr(i)), w1 = ldg_nc_16(chunk_ptr(i + stride));
+            const uint4 w2 = ldg_nc_16(chunk_ptr(i + 2 * stride)), w3 = ldg_nc_16(chunk_ptr(i + 3 * stride));
+            m = fmaxf(m, fmaxf(fmaxf(abs_max8<T>(w0), abs_max8<T>(w1)), fmaxf(abs_max8<T>(w2), abs_max8<T>(w3))));
         }
+        for (; i < total; i += stride) m = fmaxf(m, abs_max8<T>(ldg_nc_16(chunk_ptr(i))));
     } else {
         const int64_t total = rows * cols;
-        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
-             i += (int64_t)gridDim.x * blockDim.x) {
+        for (int64_t i = tid; i < total; i += stride) {
             int64_t r = i / cols, c = i - r * cols;
             m = fmaxf(m, fabsf(elem_to_float<T>(x[r * ld + c])));
         }
@@ -87,18 +98,59 @@ __global__ void __launch_bounds__(256) amax_kernel(const T *__restrict__ x, int6
 // building blocks
 // ------------------------------------------------------------------------------------
 
-// E2M1 codes of v[i] * r; `guard` re-adds +0.0 so that a product that underflows to
-// -0.0 encodes as +0 (the reference multiplies by sign(x_scaled), which is 0 there).
+// E2M1 codes of v[i] * r. The reference multiplies the rounded magnitude by sign(x_scaled),
+// which is 0 for a zero of either sign, so a scaled value of -0.0 must encode as +0 (code
+// 0x0, not 0x8). fma(v, r, +0.0) rounds exactly like v * r and turns (-0.0) * r into +0.0;
+// `guard` adds +0.0 once more for a NEGATIVE product that underflows to -0.0.
 __device__ __forceinline__ void encode_e2m1(const float (&v)[16], float r, bool guard, uint32_t &lo, uint32_t &hi) {
     float xs[16];
+    const uint64_t r2 = pack2(r, r), zero2 = pack2(0.0f, 0.0f);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) xs[i] = __fmul_rn(v[i], r);
+    for (int k = 0; k < 8; ++k) unpack2f(fma2(pack2(v[2 * k], v[2 * k + 1]), r2, zero2), xs[2 * k], xs[2 * k + 1]);
     if (guard) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) xs[i] = __fadd_rn(xs[i], 0.0f);
     }
     lo = cvt_e2m1x8(xs);
     hi = cvt_e2m1x8(xs + 8);
+}
+
+// E2M1 codes of eight scaled values v[i] * r (as encode_e2m1 without the guard) and the
+// rounding residuals t[i] = q[i] - v[i] * r, each one IEEE subtraction of the binary32
+// scaled value from the binary16 code value.
+__device__ __forceinline__ uint32_t encode8_with_residuals(const float *v, uint64_t r2, float (&t)[8]) {
+    float x[8];
+    const uint64_t zero2 = pack2(0.0f, 0.0f);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) unpack2f(fma2(pack2(v[2 * k], v[2 * k + 1]), r2, zero2), x[2 * k], x[2 * k + 1]);
+    uint32_t codes;
+    asm("{ .reg .b8 b0, b1, b2, b3;\n"
+        ".reg .b32 h;\n"
+        ".reg .f16 l, u;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %10, %9;\n"
+        "cvt.rn.f16x2.e2m1x2 h, b0;\n"
+        "mov.b32 {l, u}, h;\n"
+        "sub.rn.f32.f16 %1, l, %9;\n"
+        "sub.rn.f32.f16 %2, u, %10;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %12, %11;\n"
+        "cvt.rn.f16x2.e2m1x2 h, b1;\n"
+        "mov.b32 {l, u}, h;\n"
+        "sub.rn.f32.f16 %3, l, %11;\n"
+        "sub.rn.f32.f16 %4, u, %12;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %14, %13;\n"
+        "cvt.rn.f16x2.e2m1x2 h, b2;\n"
+        "mov.b32 {l, u}, h;\n"
+        "sub.rn.f32.f16 %5, l, %13;\n"
+        "sub.rn.f32.f16 %6, u, %14;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %16, %15;\n"
+        "cvt.rn.f16x2.e2m1x2 h, b3;\n"
+        "mov.b32 {l, u}, h;\n"
+        "sub.rn.f32.f16 %7, l, %15;\n"
+        "sub.rn.f32.f16 %8, u, %16;\n"
+        "mov.b32 %0, {b0, b1, b2, b3}; }"
+        : "=r"(codes), "=f"(t[0]), "=f"(t[1]), "=f"(t[2]), "=f"(t[3]), "=f"(t[4]), "=f"(t[5]), "=f"(t[6]), "=f"(t[7])
+        : "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]), "f"(x[4]), "f"(x[5]), "f"(x[6]), "f"(x[7]));
+    return codes;
 }
 
 // Two's-complement INT4 codes of round(clamp(v * r * (7/6), -7, 7)).
@@ -225,25 +277,48 @@ __device__ __forceinline__ float block_error(const float (&e)[16], int rule, flo
 // one block of 16 values (one row of a 16x16 block in 2-D mode)
 // ------------------------------------------------------------------------------------
 
+// Per-tensor constants: encode = (max value * max scale) / amax and decode = 1 / encode.
+struct TensorConsts {
+    float amax, maxq, encode, decode;
+    bool filter_ok;   // amax is in the range where the fast pre-filter's error bound holds
+};
+
+template <int KIND>
+__device__ __forceinline__ TensorConsts tensor_consts(float amax, int rule) {
+    TensorConsts c;
+    c.amax = amax;
+    c.maxq = (KIND == KIND_STATIC && rule == FOS_RULE_STATIC_4) ? 4.0f : 6.0f;
+    const float maxsf = (KIND == KIND_ADAPTIVE) ? 256.0f : 448.0f;
+    c.encode = __fdiv_rn(c.maxq * maxsf, amax);
+    c.decode = __frcp_rn(c.encode);
+    c.filter_ok = amax > 0x1p-100f && amax < 0x1p100f;
+    return c;
+}
+
+// What a block needs to know about a scale byte b: s = its value, r = 1 / (decode * s) as the
+// reference rounds it, g = s * amax / (6 * 256) (approximate, pre-filter only) and g * g.
+// The 1-D kernel tabulates this once per CTA for all 128 bytes; other callers compute it.
+__device__ __forceinline__ float4 scale_entry(uint32_t sfb, const TensorConsts &tc) {
+    const float s = e4m3_to_float(sfb);
+    const float g = s * tc.amax * (1.0f / 1536.0f);
+    return make_float4(s, __frcp_rn(__fmul_rn(tc.decode, s)), g, g * g);
+}
+
 template <int KIND, bool TWO_D, bool TRANSPOSED>
-__device__ __forceinline__ void quantize_block(const float (&v)[16], float amax, int rule, bool exact_only,
-                                               float *scratch, int lane, uint32_t &lo, uint32_t &hi,
-                                               uint32_t &sf_byte) {
+__device__ __forceinline__ void quantize_block(const float (&v)[16], const TensorConsts &tc, int rule,
+                                               bool exact_only, float *scratch, int lane, const float4 *lut,
+                                               uint32_t &lo, uint32_t &hi, uint32_t &sf_byte) {
+    const float amax = tc.amax;
     float bmax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(v[i]));
     bmax = block_max<TWO_D, TRANSPOSED>(bmax);
-
-    const float maxq = (KIND == KIND_STATIC && rule == FOS_RULE_STATIC_4) ? 4.0f : 6.0f;
-    const float maxsf = (KIND == KIND_ADAPTIVE) ? 256.0f : 448.0f;
-    const float range = maxq * maxsf;
-    const float encode = __fdiv_rn(range, amax);
-    const float decode = __frcp_rn(encode);
-    float hp = (amax == 0.0f) ? 0.0f : __fmul_rn(__fdiv_rn(bmax, maxq), encode);
+    const float q = tc.maxq == 6.0f ? div6_exact(bmax) : __fmul_rn(bmax, 0.25f);   // bmax / maxq
+    float hp = (amax == 0.0f) ? 0.0f : __fmul_rn(q, tc.encode);
 
     const uint32_t sfb_a = cvt_e4m3(hp);
-    const float s_a = e4m3_to_float(sfb_a);
-    const float r_a = __frcp_rn(__fmul_rn(decode, s_a));
+    const float4 ea = lut ? lut[sfb_a] : scale_entry(sfb_a, tc);
+    const float s_a = ea.x, r_a = ea.y;
 
     if (KIND == KIND_STATIC) {
         lo = hi = 0u;
@@ -254,43 +329,42 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], float amax,
 
     if (KIND == KIND_ADAPTIVE) {
         const uint32_t sfb_b = cvt_e4m3(__fmul_rn(hp, 1.5f));
-        const float s_b = e4m3_to_float(sfb_b);
-        const float r_b = __frcp_rn(__fmul_rn(decode, s_b));
+        const float4 eb = lut ? lut[sfb_b] : scale_entry(sfb_b, tc);
+        const float s_b = eb.x, r_b = eb.y;
 
-        // Fast pre-filter (1-D blocks, mean-squared error, both scales normal E4M3 numbers,
-        // no underflow in sight). With g = scale * amax / 1536, the reference's dequantized
-        // value is q*g up to 5 ulp, |q*g| <= 6g and |d| <= 1.01g, so each estimated sum is
-        // within 1500 * 2^-24 * g^2 of the reference's sum (see the derivation in the design
-        // notes); 2^-13 * (g4^2 + g6^2) leaves a 25% margin on top of both.
-        if (!TWO_D && rule == FOS_RULE_MSE && !exact_only && sfb_a >= 8u && sfb_b >= 8u &&
-            amax > 0x1p-100f && amax < 0x1p100f && r_a >= 0x1p-16f && r_b >= 0x1p-16f) {
-            const float inv = 1.0f / 1536.0f;
-            const float g_a = s_a * amax * inv, g_b = s_b * amax * inv;
+        // Fast pre-filter: 1-D blocks, mean-squared error, both scales normal E4M3 numbers (so
+        // |x*r| <= 6.4 and a rounding residual t = q - x*r is at most 1.01), amax and r in a range
+        // without underflow. In units of G = s*amax/1536 the reference's error term is
+        // (deq - x)/G = t + eta with |eta| <= 47 ulp(1) (two roundings in deq, five between x*r
+        // and x/G, |q| <= 6, |x*r| <= 6.4), so its sum differs from G^2 * sum(t^2) by at most
+        // 2 * 47u * sum|t| * G^2 <= 376u * sqrt(sum t^2) * G^2 (Cauchy-Schwarz over 16 terms) plus
+        // 40u relative for the roundings of the two summations. `tau` is 1.5 times that, for
+        // both candidates together; a difference inside tau is re-decided exactly below.
+        if (!TWO_D && rule == FOS_RULE_MSE && !exact_only && sfb_a >= 8u && sfb_b >= 8u && tc.filter_ok &&
+            r_a >= 0x1p-16f && r_b >= 0x1p-16f) {
+            const uint64_t ra2 = pack2(r_a, r_a), rb2 = pack2(r_b, r_b);
             uint32_t ca[2], cb[2];
-            float acc_a = 0.0f, acc_b = 0.0f;
+            uint64_t acc_a = pack2(0.0f, 0.0f), acc_b = acc_a;
 #pragma unroll
             for (int w = 0; w < 2; ++w) {
-                float xa[8], xb[8];
+                float ta[8], tb[8];
+                ca[w] = encode8_with_residuals(&v[8 * w], ra2, ta);
+                cb[w] = encode8_with_residuals(&v[8 * w], rb2, tb);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    xa[i] = __fmul_rn(v[8 * w + i], r_a);
-                    xb[i] = __fmul_rn(v[8 * w + i], r_b);
-                }
-                ca[w] = cvt_e2m1x8(xa);
-                cb[w] = cvt_e2m1x8(xb);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float2 qa = e2m1x2_to_float2((ca[w] >> (8 * j)) & 0xffu);
-                    float2 qb = e2m1x2_to_float2((cb[w] >> (8 * j)) & 0xffu);
-                    float d;
-                    d = fmaf(qa.x, g_a, -v[8 * w + 2 * j]);     acc_a = fmaf(d, d, acc_a);
-                    d = fmaf(qa.y, g_a, -v[8 * w + 2 * j + 1]); acc_a = fmaf(d, d, acc_a);
-                    d = fmaf(qb.x, g_b, -v[8 * w + 2 * j]);     acc_b = fmaf(d, d, acc_b);
-                    d = fmaf(qb.y, g_b, -v[8 * w + 2 * j + 1]); acc_b = fmaf(d, d, acc_b);
+                for (int k = 0; k < 4; ++k) {
+                    const uint64_t pa = pack2(ta[2 * k], ta[2 * k + 1]), pb = pack2(tb[2 * k], tb[2 * k + 1]);
+                    acc_a = fma2(pa, pa, acc_a);
+                    acc_b = fma2(pb, pb, acc_b);
                 }
             }
-            const float tau = 0x1p-13f * (g_a * g_a + g_b * g_b);
-            const float diff = acc_b - acc_a;
+            float a0, a1, b0, b1;
+            unpack2f(acc_a, a0, a1);
+            unpack2f(acc_b, b0, b1);
+            const float sum_a = a0 + a1, sum_b = b0 + b1;                 // sum of t^2, scaled units
+            const float err_a = sum_a * ea.w, err_b = sum_b * eb.w;       // times G^2
+            const float tau = 0x1p-24f * 1.5f *
+                              (376.0f * (sqrtf(sum_a) * ea.w + sqrtf(sum_b) * eb.w) + 40.0f * (err_a + err_b));
+            const float diff = err_b - err_a;
             if (fabsf(diff) > tau) {
                 const bool pick_b = diff < 0.0f;
                 lo = pick_b ? cb[0] : ca[0];
@@ -399,18 +473,127 @@ __global__ void __launch_bounds__(CTA_THREADS) quantize_kernel(const QuantParams
         for (int i = 0; i < 16; ++i) v[i] = elem_to_float<T>(stage[(b * 16 + i) * 128 + jr]);
         if (TWO_D) __syncthreads();  // the staging area is reused as reduction scratch
     }
-    // -0.0 inputs count as +0.0 (sign() of a zero is zero in the reference)
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __fadd_rn(v[i], 0.0f);
-
     float *scratch = TWO_D ? reinterpret_cast<float *>(smem) + warp * 512 : nullptr;
-    const float amax = __ldg(p.amax);
+    const TensorConsts tc = tensor_consts<KIND>(__ldg(p.amax), p.rule);
     uint32_t lo, hi, sf_byte;
-    quantize_block<KIND, TWO_D, TRANSPOSED>(v, amax, p.rule, p.exact_only != 0, scratch, lane, lo, hi, sf_byte);
+    quantize_block<KIND, TWO_D, TRANSPOSED>(v, tc, p.rule, p.exact_only != 0, scratch, lane, nullptr, lo, hi, sf_byte);
 
     // rows_p / cols_p are multiples of the tile, so every thread owns a valid output block
     *reinterpret_cast<uint2 *>(p.codes + row * (p.cols_p >> 1) + cb * 8) = make_uint2(lo, hi);
     p.sf[sf_offset(row, cb, p.cols_p >> 4, p.sf_tiled != 0)] = static_cast<uint8_t>(sf_byte);
+}
+
+// ------------------------------------------------------------------------------------
+// the common case: 1-D blocks of an untransposed tensor
+// ------------------------------------------------------------------------------------
+//
+// Persistent CTAs of 256 threads walk over 64-row x 64-column tiles (warp w: rows 8w..8w+7;
+// lane: row lane/4, block lane%4, so four lanes read one 128-byte line). The 32 bytes of
+// the NEXT tile are requested before the current block is processed, which keeps a load in
+// flight per thread while the arithmetic runs.
+
+constexpr int ROWS_CTA_THREADS = 256;
+
+// The 16 values of block (row, cb) as eight words of two 16-bit elements; zeros outside x.
+template <typename T>
+__device__ __forceinline__ void load_block_words(const QuantParams &p, int64_t row, int64_t cb, uint32_t (&w)[8]) {
+    const T *x = static_cast<const T *>(p.x);
+    const int64_t col0 = cb * 16;
+    if (row < p.out_rows && col0 + 16 <= p.out_cols && p.vec_bytes != 0) {
+        const T *src = x + row * p.ld + col0;
+        if (p.vec_bytes == 32) {
+            ldg_nc_32(src, w);
+        } else {
+            const uint4 a = ldg_nc_16(src), b = ldg_nc_16(src + 8);
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+            w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+        }
+    } else {
+        const uint16_t *xs = reinterpret_cast<const uint16_t *>(x);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            uint32_t lo = 0u, hi = 0u;
+            if (row < p.out_rows) {
+                if (col0 + 2 * k < p.out_cols) lo = xs[row * p.ld + col0 + 2 * k];
+                if (col0 + 2 * k + 1 < p.out_cols) hi = xs[row * p.ld + col0 + 2 * k + 1];
+            }
+            w[k] = lo | (hi << 16);
+        }
+    }
+}
+
+template <typename T, int KIND>
+__global__ void __launch_bounds__(ROWS_CTA_THREADS, KIND == KIND_STATIC ? 5 : 4)
+quantize_rows_kernel(const QuantParams p) {
+    __shared__ float4 lut[128];                  // scale byte -> {s, r, g, g^2}, see scale_entry()
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_c = static_cast<int>(p.cols_p >> 6), tiles_r = static_cast<int>(p.rows_p >> 6);
+    const int r_in_tile = warp * 8 + (lane >> 2), cb_in_tile = lane & 3;
+    const int64_t n_cb = p.cols_p >> 4;
+
+    // tile coordinates advance by gridDim.x tiles per step without dividing inside the loop
+    const int step_r = static_cast<int>(gridDim.x) / tiles_c, step_c = static_cast<int>(gridDim.x) % tiles_c;
+    int tr = static_cast<int>(blockIdx.x) / tiles_c, tc_ = static_cast<int>(blockIdx.x) % tiles_c;
+    if (tr >= tiles_r) return;                   // never taken: the grid has at most one CTA per tile
+
+    uint32_t w[8];
+    load_block_words<T>(p, static_cast<int64_t>(tr) * 64 + r_in_tile, tc_ * 4 + cb_in_tile, w);
+    // amax comes from the previous kernel in the stream; nothing above needed it
+    const TensorConsts tc = tensor_consts<KIND>(__ldg(p.amax), p.rule);
+    if (threadIdx.x < 128) lut[threadIdx.x] = scale_entry(threadIdx.x, tc);
+    __syncthreads();
+
+    while (true) {
+        int nr = tr + step_r, nc = tc_ + step_c;
+        if (nc >= tiles_c) { nc -= tiles_c; ++nr; }
+        const bool more = nr < tiles_r;
+        uint32_t wn[8];
+        if (more) load_block_words<T>(p, static_cast<int64_t>(nr) * 64 + r_in_tile, nc * 4 + cb_in_tile, wn);
+
+        float v[16];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float2 f = unpack2<T>(w[k]);
+            v[2 * k] = f.x;
+            v[2 * k + 1] = f.y;
+        }
+        uint32_t lo, hi, sf_byte;
+        quantize_block<KIND, false, false>(v, tc, p.rule, p.exact_only != 0, nullptr, lane, lut, lo, hi, sf_byte);
+        const int64_t row = static_cast<int64_t>(tr) * 64 + r_in_tile, cb = tc_ * 4 + cb_in_tile;
+        *reinterpret_cast<uint2 *>(p.codes + row * (p.cols_p >> 1) + cb * 8) = make_uint2(lo, hi);
+        p.sf[sf_offset(row, cb, n_cb, p.sf_tiled != 0)] = static_cast<uint8_t>(sf_byte);
+
+        if (!more) break;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) w[k] = wn[k];
+        tr = nr;
+        tc_ = nc;
+    }
+}
+
+template <typename T, int KIND>
+cudaError_t launch_rows(const QuantParams &p, cudaStream_t stream) {
+    auto kernel = quantize_rows_kernel<T, KIND>;
+    static int ctas_per_sm[64] = {};
+    static int sm_count[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const int slot = (dev >= 0 && dev < 64) ? dev : 0;
+    if (ctas_per_sm[slot] == 0) {
+        int n = 0, sms = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, ROWS_CTA_THREADS, 0);
+        if (e != cudaSuccess) return e;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+        ctas_per_sm[slot] = n > 0 ? n : 1;
+        sm_count[slot] = sms;
+    }
+    const int64_t n_tiles = (p.rows_p >> 6) * (p.cols_p >> 6);
+    int64_t grid = static_cast<int64_t>(ctas_per_sm[slot]) * sm_count[slot];
+    if (grid > n_tiles) grid = n_tiles;
+    kernel<<<static_cast<unsigned>(grid), ROWS_CTA_THREADS, 0, stream>>>(p);
+    return cudaGetLastError();
 }
 
 template <typename T, int KIND>
@@ -425,6 +608,11 @@ cudaError_t launch_kind(const QuantParams &p, bool two_d, bool transposed, cudaS
 
 template <typename T>
 cudaError_t launch_all(const QuantParams &p, int kind, bool two_d, bool transposed, cudaStream_t stream) {
+    if (!two_d && !transposed) {
+        if (kind == KIND_STATIC) return launch_rows<T, KIND_STATIC>(p, stream);
+        if (kind == KIND_ADAPTIVE) return launch_rows<T, KIND_ADAPTIVE>(p, stream);
+        return launch_rows<T, KIND_IF4>(p, stream);
+    }
     if (kind == KIND_STATIC) return launch_kind<T, KIND_STATIC>(p, two_d, transposed, stream);
     if (kind == KIND_ADAPTIVE) return launch_kind<T, KIND_ADAPTIVE>(p, two_d, transposed, stream);
     return launch_kind<T, KIND_IF4>(p, two_d, transposed, stream);

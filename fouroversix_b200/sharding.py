@@ -1,0 +1,179 @@
+"""Tensor-parallel sharding of the FP4 linear layers across the GPUs of one node.
+
+The reference has no distributed code of its own; it runs tensor-parallel only inside
+vLLM (`--tensor-parallel-size`, scripts/ptq/__main__.py:281-287), where each rank
+quantizes ITS shard of a weight with that shard's own amax
+(src/fouroversix/integrations/vllm_quantization.py:100-124).  This module provides the
+same decomposition natively, one process per GPU over torch.distributed (NCCL):
+
+  column parallel   W[N, K] is split by rows; rank r holds W[r*N/g : (r+1)*N/g].
+                    y_r = x @ W_r^T is a slice of the output; no communication.
+  row parallel      W is split by columns; rank r holds W[:, r*K/g : (r+1)*K/g] and
+                    receives the matching slice of the activations (the output of a
+                    column-parallel layer). Every rank computes a full-size partial
+                    product; the partials are summed with an all-reduce.
+
+For row-parallel layers the all-reduce of a [tokens, N] bf16 tensor costs more than the
+shard's GEMM at large token counts, so the token dimension is cut into chunks: the
+all-reduce of chunk i runs on a communication stream while the GEMM of chunk i+1 runs
+on the compute stream.
+
+Two ways to obtain shards:
+  * quantize each shard by itself (`quantize(w_shard)`), the reference's behaviour; or
+  * slice an already quantized tensor (`slice_rows`, `slice_cols`): bit-identical to the
+    unsharded tensor, amax and therefore alpha stay global.  Row slices and K slices of
+    the 128x4-tiled scale array are plain views / one gather because tiles are stored
+    row-group major.
+"""
+
+from __future__ import annotations
+
+from collections.abc import Callable
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from fouroversix_b200.matmul import quantized_matmul
+from fouroversix_b200.quantize import QuantizationConfig, QuantizedTensor, quantize
+from fouroversix_b200.utils import DataType
+
+from .model.config import ModuleQuantizationConfig
+
+
+def shard_bounds(size: int, rank: int, world: int, multiple: int) -> tuple[int, int]:
+    """[lo, hi) of rank's equal share of `size`; the share must be a multiple of `multiple`."""
+    if size % world:
+        raise ValueError(f"cannot split {size} evenly over {world} ranks")
+    part = size // world
+    if part % multiple:
+        raise ValueError(f"a shard of {part} is not a multiple of {multiple}")
+    return rank * part, (rank + 1) * part
+
+
+def slice_rows(q: QuantizedTensor, lo: int, hi: int) -> QuantizedTensor:
+    """Rows [lo, hi) of a quantized tensor (multiples of 128) without requantizing."""
+    if lo % 128 or hi % 128 or not 0 <= lo < hi <= q.padded_shape[0]:
+        raise ValueError("row slices must be multiples of 128 inside the padded shape")
+    cols_p = q.padded_shape[1]
+    per_row_scales = cols_p // q.dtype.block_size
+    sf = q.scale_factors.reshape(-1)
+    # tiled: 128-row groups are contiguous runs of (cols_p/64) tiles of 512 bytes; row-major: rows are
+    sf = sf[lo * per_row_scales: hi * per_row_scales]
+    rows = min(hi, q.original_shape[0]) - lo
+    return QuantizedTensor(q.values[lo:hi], sf, q.amax, q.dtype, (rows, q.original_shape[1]), q.scale_rule,
+                           q.round_style, (hi - lo, cols_p),
+                           scale_factors_are_in_blackwell_layout=q.scale_factors_are_in_blackwell_layout)
+
+
+def slice_cols(q: QuantizedTensor, lo: int, hi: int) -> QuantizedTensor:
+    """Columns [lo, hi) of a quantized tensor (multiples of 64) without requantizing."""
+    rows_p, cols_p = q.padded_shape
+    if lo % 64 or hi % 64 or not 0 <= lo < hi <= cols_p:
+        raise ValueError("column slices must be multiples of 64 inside the padded shape")
+    values = q.values[:, lo // 2: hi // 2].contiguous()
+    if q.scale_factors_are_in_blackwell_layout:
+        tiles = q.scale_factors.reshape(rows_p // 128, cols_p // 64, 512)
+        sf = tiles[:, lo // 64: hi // 64].contiguous().reshape(-1)
+    else:
+        sf = q.scale_factors.reshape(rows_p, cols_p // 16)[:, lo // 16: hi // 16].contiguous().reshape(-1)
+    cols = min(hi, q.original_shape[1]) - lo
+    return QuantizedTensor(values, sf, q.amax, q.dtype, (q.original_shape[0], cols), q.scale_rule, q.round_style,
+                           (rows_p, hi - lo),
+                           scale_factors_are_in_blackwell_layout=q.scale_factors_are_in_blackwell_layout)
+
+
+MatmulFn = Callable[..., torch.Tensor]
+
+
+class TensorParallelLinear(nn.Module):
+    """One rank's part of a column- or row-parallel FP4 linear layer (inference).
+
+    `weight` is this rank's shard, either high precision (quantized here with the
+    shard's own amax, like the reference under vLLM) or already a `QuantizedTensor`.
+    `matmul_fn(x, w, input_config=..., out_dtype=...)` defaults to the FP4 GEMM; tests of
+    the host logic substitute a CPU stand-in.
+    """
+
+    def __init__(self, weight: torch.Tensor | QuantizedTensor, config: ModuleQuantizationConfig, mode: str, *,
+                 group: dist.ProcessGroup | None = None, bias: torch.Tensor | None = None, chunks: int = 4,
+                 matmul_fn: MatmulFn | None = None, quantize_fn: Callable | None = None) -> None:
+        super().__init__()
+        if mode not in ("column", "row"):
+            raise ValueError("mode must be 'column' or 'row'")
+        self.mode, self.config, self.group, self.chunks = mode, config, group, max(1, chunks)
+        self._matmul = matmul_fn or quantized_matmul
+        self._quantize = quantize_fn or quantize
+        self.weight = weight if isinstance(weight, QuantizedTensor) else self._quantize(weight, config.get_weight_config())
+        self.bias = bias
+        self._comm_stream: torch.cuda.Stream | None = None
+
+    @property
+    def world_size(self) -> int:
+        return dist.get_world_size(self.group) if dist.is_initialized() else 1
+
+    def _gemm(self, x: torch.Tensor | QuantizedTensor, act_cfg: QuantizationConfig,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+        extra = {} if out is None else {"out": out}
+        return self._matmul(x, self.weight, input_config=act_cfg, out_dtype=self.config.output_dtype, **extra)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x2d = x.reshape(-1, x.shape[-1])
+        act_cfg = self.config.get_activation_config()
+        if self.mode == "column" or self.world_size == 1:
+            out = self._gemm(x2d, act_cfg)
+        else:
+            out = self._row_parallel(x2d, act_cfg)
+        if self.bias is not None:
+            out = out + self.bias
+        return out.reshape(*lead, out.shape[-1])
+
+    def _row_parallel(self, x2d: torch.Tensor, act_cfg: QuantizationConfig) -> torch.Tensor:
+        """Partial product per chunk of tokens, each chunk's all-reduce overlapped with the
+        next chunk's GEMM. The local activations are quantized once (one amax for all
+        chunks) and sliced by rows."""
+        tokens = x2d.shape[0]
+        n_chunks = self.chunks
+        while n_chunks > 1 and (tokens % (128 * n_chunks) != 0):
+            n_chunks -= 1
+        xq = self._quantize(x2d, act_cfg)
+        on_gpu = x2d.device.type == "cuda"
+        if n_chunks == 1:
+            out = self._gemm(xq, act_cfg)
+            dist.all_reduce(out, group=self.group)
+            return out
+        step = tokens // n_chunks
+        n_out = self.weight.original_shape[0]
+        out = torch.empty(tokens, n_out, dtype=DataType(self.config.output_dtype).torch_dtype, device=x2d.device)
+        works = []
+        if on_gpu:
+            if self._comm_stream is None:
+                self._comm_stream = torch.cuda.Stream(device=x2d.device)
+            compute = torch.cuda.current_stream(x2d.device)
+        for i in range(n_chunks):
+            part = out[i * step: (i + 1) * step]
+            self._gemm(slice_rows(xq, i * step, (i + 1) * step), act_cfg, out=part)
+            if on_gpu:
+                done = torch.cuda.Event()
+                done.record(compute)
+                with torch.cuda.stream(self._comm_stream):
+                    self._comm_stream.wait_event(done)
+                    dist.all_reduce(part, group=self.group)
+            else:
+                works.append(dist.all_reduce(part, group=self.group, async_op=True))
+        if on_gpu:
+            compute.wait_stream(self._comm_stream)
+        for w in works:
+            w.wait()
+        return out
+
+
+def shard_linear_weight(weight: torch.Tensor, mode: str, rank: int, world: int) -> torch.Tensor:
+    """The slice of a full [N, K] weight that `rank` owns in a `mode`-parallel layer."""
+    n, k = weight.shape
+    if mode == "column":
+        lo, hi = shard_bounds(n, rank, world, 128)
+        return weight[lo:hi]
+    lo, hi = shard_bounds(k, rank, world, 64)
+    return weight[:, lo:hi]

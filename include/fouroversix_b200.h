@@ -134,9 +134,16 @@ int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b
 
 /*
  * Process-wide tuning / testing knobs. No counterpart in the reference.
- *   FOS_OPT_GEMM_BLOCK_N   0 = choose the GEMM tile width per problem (default), 128 or 256
+ *   FOS_OPT_GEMM_VARIANT   0 = choose the GEMM kernel per problem (default);
+ *                          128 / 256 = single-CTA kernel with 128 x 128 / 128 x 256 tiles;
+ *                          2 = CTA-pair kernel (256 x 256 tiles, cta_group::2) where the
+ *                          padded M and N are multiples of 256, else the single-CTA kernel
+ *   FOS_OPT_GEMM_DEBUG     timing experiments that make the GEMM's RESULT WRONG: bit 0 skips the
+ *                          scale copies, bit 1 the operand loads, bit 2 the output stores.
+ *                          Default 0. Only the profiling scripts set it.
  */
-#define FOS_OPT_GEMM_BLOCK_N 1
+#define FOS_OPT_GEMM_VARIANT 1
+#define FOS_OPT_GEMM_DEBUG 2
 int fos_set_option(int key, int value);
 
 #ifdef __cplusplus

@@ -448,6 +448,25 @@ int fos_oracle_matmul(const uint8_t *a_codes, const uint8_t *a_sf, const float *
     return 0;
 }
 
+/* The CUDA kernels divide a block maximum by 6 with one multiply and two fused multiply-adds
+ * instead of an IEEE division. A block maximum is always a bf16 or fp16 value, so the
+ * shortcut can be checked against a true division for every possible input. Returns the
+ * number of inputs for which the two differ (expected: 0). */
+long fos_oracle_check_div6(void) {
+    long bad = 0;
+    const float y = 1.0f / 6.0f;
+    for (int fmt = 0; fmt < 2; ++fmt)
+        for (uint32_t h = 0; h < 0x8000u; ++h) {
+            float a = fmt == 0 ? bf16_bits_to_f32((uint16_t)h) : f16_bits_to_f32((uint16_t)h);
+            if (!isfinite(a)) continue;
+            float q0 = a * y;
+            float q1 = fmaf(fmaf(-6.0f, q0, a), y, q0);
+            if (q1 != a / 6.0f) ++bad;
+            if (a * 0.25f != a / 4.0f) ++bad;
+        }
+    return bad;
+}
+
 int fos_oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -44,7 +44,10 @@ def _check(out: torch.Tensor, ref32: torch.Tensor, what: str):
     rel = ((out.float() - ref32).abs().max() / denom).item()
     assert rel <= REL_TOLERANCE, f"{what}: max relative error {rel}"
     frac = (out != ref32.to(out.dtype)).float().mean().item()
-    assert frac <= MISMATCH_TOLERANCE, f"{what}: {frac:.3%} of outputs differ"
+    # the 0.1 % bar is the reference's for bf16 outputs; fp16 keeps 3 more mantissa bits, so the
+    # same fp32 summation-order noise flips 8 times as many roundings
+    tol = MISMATCH_TOLERANCE * (8 if out.dtype == torch.float16 else 1)
+    assert frac <= tol, f"{what}: {frac:.3%} of outputs differ"
 
 
 def _synthetic(rows: int, k: int, code_byte: int, scale_byte: int) -> fos.QuantizedTensor:
@@ -56,10 +59,11 @@ def _synthetic(rows: int, k: int, code_byte: int, scale_byte: int) -> fos.Quanti
     return fos.QuantizedTensor(values, scales, amax, "nvfp4", (rows, k), "static_6", "nearest", (rows, k))
 
 
-@pytest.mark.parametrize("block_n", [128, 256])
+@pytest.mark.parametrize("block_n", [128, 256, 2])
 def test_hand_built_operands(block_n):
-    """All ones times all ones is K; then a scale that differs per row and a code pattern
-    that differs along K catch a wrong scale-tile or swizzle mapping."""
+    """All ones times all ones is K; then random codes and scales catch a wrong scale-tile or
+    swizzle mapping. `block_n` selects the kernel: single-CTA 128- or 256-wide tiles, or 2 =
+    the CTA-pair kernel."""
     lib = _native.lib()
     assert lib.fos_set_option(1, block_n) == 0
     try:
@@ -84,7 +88,16 @@ def test_hand_built_operands(block_n):
 
 @pytest.mark.parametrize(("m", "n", "k"), list(itertools.product([256, 512, 1024], repeat=3)))
 @pytest.mark.parametrize("scale_rule", ["static_6", "static_4", "mse"])
-def test_matmul_against_oracle(oracle, m, n, k, scale_rule):
+@pytest.mark.parametrize("variant", [0, 2], ids=["auto", "cta-pair"])
+def test_matmul_against_oracle(oracle, m, n, k, scale_rule, variant):
+    _native.lib().fos_set_option(1, variant)
+    try:
+        _matmul_against_oracle(oracle, m, n, k, scale_rule)
+    finally:
+        _native.lib().fos_set_option(1, 0)
+
+
+def _matmul_against_oracle(oracle, m, n, k, scale_rule):
     for seed in range(2):
         g = torch.Generator().manual_seed(seed)
         x = torch.randn(m, k, generator=g).bfloat16()
@@ -116,7 +129,8 @@ def test_golden_matmul_cases(golden):
         assert rel <= REL_TOLERANCE
 
 
-@pytest.mark.parametrize("shape", [(100, 72, 80), (130, 300, 192), (128, 128, 64), (257, 129, 1000), (384, 640, 448)])
+@pytest.mark.parametrize("shape", [(100, 72, 80), (130, 300, 192), (128, 128, 64), (257, 129, 1000), (384, 640, 448),
+                                   (512, 768, 448), (256, 256, 64), (500, 1000, 320)])
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float16", "float32"])
 def test_ragged_shapes_and_output_types(shape, out_dtype):
     m, n, k = shape
@@ -124,7 +138,7 @@ def test_ragged_shapes_and_output_types(shape, out_dtype):
     x = torch.randn(m, k, generator=g).bfloat16().to(DEV)
     y = (torch.randn(n, k, generator=g) * 0.05).bfloat16().to(DEV)
     qx, qy = fos.quantize(x), fos.quantize(y)
-    for block_n in (128, 256):
+    for block_n in (128, 256, 2):
         _native.lib().fos_set_option(1, block_n)
         try:
             out = B200MatmulBackend.quantized_matmul(qx, qy, out_dtype=fos.DataType(out_dtype), check_status=True)

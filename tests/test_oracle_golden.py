@@ -69,3 +69,11 @@ def test_matmul_and_alpha_match_reference(oracle, golden):
         out16 = oracle.matmul(qa, qb, torch.bfloat16)
         frac = (out16 != mm["out_bf16"]).float().mean().item()
         assert frac <= 1e-3, frac          # the reference's own cross-backend criterion
+
+
+def test_division_shortcut_used_by_the_kernels_is_exact(oracle):
+    """bmax / 6 via multiply + two FMAs equals the IEEE quotient for every bf16 and fp16 value."""
+    import ctypes
+    fn = oracle.lib().fos_oracle_check_div6
+    fn.restype = ctypes.c_long
+    assert fn() == 0
