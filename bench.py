@@ -9,9 +9,10 @@ N(0,1) with 1 % of the K-channels scaled by 20, NVFP4 with 4/6 MSE block selecti
 `gemm` object carries the second half of the metric: FP4 GEMM TFLOP/s at M = N = K = 8192
 (and the A x B^T of the same configuration).  Inputs are synthetic and seeded.
 
-A "step" is one quantization of A (amax pass + quantize pass = 2 kernel launches).  Four
+A "step" is one quantization of A (amax pass + quantize pass = 2 kernel launches), replayed
+as a CUDA graph so that the Python launch cost does not hide the device time.  Four
 copies of A (256 MiB) are cycled so that every step reads its input from HBM, not from
-the 126 MB L2.  Timing uses CUDA events on the stream the kernels are launched on; with
+the 126 MB L2.  Timing uses CUDA events on the stream the graphs are replayed on; with
 N > 1 every rank quantizes its own A (independent stripes, no collective: weak scaling)
 and the slowest rank defines the time.
 
@@ -114,7 +115,8 @@ class ClockSampler:
 
 
 def time_cuda(fn, steps: int, warmup: int) -> float:
-    """Mean milliseconds per call of fn(i), CUDA events on the current stream."""
+    """Mean milliseconds per call of fn(i), CUDA events on the current stream (eager launches:
+    host-side launch cost is part of the number)."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
@@ -122,6 +124,32 @@ def time_cuda(fn, steps: int, warmup: int) -> float:
     e0.record()
     for i in range(steps):
         fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def time_graphs(fn, n_variants: int, steps: int, warmup: int) -> float:
+    """Mean milliseconds per step when step i is a replay of a CUDA graph that captured
+    fn(i % n_variants). The kernels are short (tens of microseconds), so launching them from
+    Python one by one would time the interpreter; a graph replay leaves the device work and
+    the gaps between the kernels of one step. Events are recorded on the replay stream."""
+    for i in range(max(n_variants, 1)):
+        fn(i)
+    torch.cuda.synchronize()
+    graphs = []
+    for i in range(n_variants):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn(i)
+        graphs.append(g)
+    for i in range(max(warmup, n_variants)):
+        graphs[i % n_variants].replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        graphs[i % n_variants].replay()
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / steps
@@ -196,7 +224,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms = time_cuda(step, args.steps, args.warmup)
+    ms = time_graphs(step, N_ROTATE, args.steps, args.warmup)
+    eager_ms = time_cuda(step, args.steps, args.warmup)
     # a sustained second pass so that the clock sampler sees the kernels under load
     if rank == 0:
         t_end = time.perf_counter() + 1.0
@@ -228,7 +257,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             fn = lambda i: B200QuantizeBackend.quantize(a_sets[i % N_ROTATE], cfg_mse, amax=amaxes[i % N_ROTATE])  # noqa: E731
         else:
             fn = lambda i, c=c: fos.quantize(a_sets[i % N_ROTATE], c)  # noqa: E731
-        t = time_cuda(fn, max(args.steps, 10), 3)
+        t = time_graphs(fn, N_ROTATE, max(args.steps, 10), 3)
         modes[name] = {"ms": t, "GB/s": BYTES_PER_ELEM * n_elem / (t * 1e-3) / 1e9}
 
     # end to end through the public API with host buffers
@@ -265,7 +294,10 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                         "per rank when n_gpus > 1",
             "l2": f"{N_ROTATE} rotating copies of A (256 MiB) so each step reads HBM-cold input",
             "bytes_per_element": BYTES_PER_ELEM,
+            "timing": "each step is one CUDA-graph replay of the library call (memset + 2 kernels); "
+                      "ms_per_step_eager is the same call launched from Python",
         },
+        "ms_per_step_eager": eager_ms,
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": achieved / peaks["hbm_gbs"], "frac_of_nominal_8TBps": achieved / 8000.0,
@@ -300,7 +332,7 @@ def gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks):
         fn = lambda i: B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType.bfloat16, out=d)  # noqa: E731
         if world > 1:
             dist.barrier()
-        ms = time_cuda(fn, max(args.steps, 10), max(args.warmup, 3))
+        ms = time_graphs(fn, 1, max(args.steps, 10), max(args.warmup, 3))
         if world > 1:
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)

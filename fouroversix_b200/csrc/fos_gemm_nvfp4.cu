@@ -7,12 +7,19 @@
 //   warp 0      one lane issues TMA loads of the A / B tiles (128-byte swizzle, no
 //               multicast) and plain bulk copies of the scale tiles into a ring of
 //               shared-memory stages guarded by full / empty mbarriers
-//   warp 1      allocates tensor memory; one lane copies the scale tiles shared -> tensor
-//               memory (tcgen05.cp 32x128b.warpx4, which is exactly the 512-byte tile) and
-//               issues tcgen05.mma kind::mxf4nvf4.block_scale (K = 64 per instruction) with
-//               the fp32 accumulator in tensor memory; tcgen05.commit releases the stage
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp owns the 32 lanes of its
-//               quadrant), multiply by alpha, convert, store rows < m and columns < n
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma kind::mxf4nvf4.block_scale
+//               (K = 64 per instruction) with the fp32 accumulator in tensor memory;
+//               tcgen05.commit releases the stage
+//   warps 2..9  epilogue: tcgen05.ld the accumulator (each warp owns the 32 lanes of its
+//               quadrant and half of the tile's columns), multiply by alpha, convert, store
+//               rows < m and columns < n; the accumulator is handed back to the MMA warp as
+//               soon as the last tcgen05.ld has landed, before the stores of that data
+//   warps 10..13 scale movers: copy each stage's scale tiles shared -> registers -> tensor
+//               memory (tcgen05.st) into a ring of scale columns, one slot per stage. A
+//               512-byte scale tile is 32 rows of 16 bytes and every 32-lane quadrant of tensor
+//               memory needs the same 16 bytes per lane, so each of the four warps reads row
+//               `lane` and writes its own quadrant. (Issuing tcgen05.cp from the MMA thread
+//               instead serialises with the MMAs and cost 40 % of the run time when measured.)
 //
 // Every mbarrier wait is bounded by a wall-clock limit. A wait that gives up records where
 // in *status, raises a CTA-wide abort flag, and all roles fall through to the common exit,
@@ -32,10 +39,10 @@ constexpr int KB_PER_STAGE = 4;                    // MMA K-blocks (64 values, 3
 constexpr int SF_TILE_BYTES = 512;                 // scales of 128 rows x 64 values
 constexpr int A_BYTES = BLOCK_M * BLOCK_K_BYTES;   // 16 KiB
 constexpr int SFA_BYTES = KB_PER_STAGE * SF_TILE_BYTES;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 448;                   // TMA, MMA, 8 epilogue warps, 4 scale-mover warps
 constexpr int TMEM_COLS = 512;
-constexpr int SFA_COL = 256;                       // tensor-memory columns: accumulators first,
-constexpr int SFB_COL = 272;                       // then 16 columns of A scales, 32 of B scales
+constexpr int SF_COL0 = 256;                       // tensor-memory columns: accumulators first, then per
+                                                   // stage 16 columns of A scales and N/8 of B scales
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 template <int BLOCK_N> struct Cfg {
@@ -46,8 +53,11 @@ template <int BLOCK_N> struct Cfg {
     static constexpr int STAGES = BLOCK_N == 256 ? 4 : 6;
     static constexpr int ACC_STAGES = BLOCK_N == 256 ? 1 : 2;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int SFB_COLS = KB_PER_STAGE * (BLOCK_N / 32);  // per stage
+    static constexpr int SF_STAGE_COLS = 16 + SFB_COLS;
     static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
-    static_assert(ACC_STAGES * BLOCK_N <= SFA_COL, "accumulators overlap the scale columns");
+    static_assert(ACC_STAGES * BLOCK_N <= SF_COL0, "accumulators overlap the scale columns");
+    static_assert(SF_COL0 + STAGES * SF_STAGE_COLS <= TMEM_COLS, "scale ring does not fit tensor memory");
 };
 
 struct GemmParams {
@@ -126,9 +136,6 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_copy_sf(uint32_t taddr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
 __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
     asm volatile(
@@ -138,16 +145,30 @@ __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, ui
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
         : "memory");
 }
-__device__ __forceinline__ void tc_load_32cols(uint32_t taddr, uint32_t (&r)[32]) {
+// Two 32-column loads and the wait in ONE asm statement, so that no use of the destination
+// registers can be scheduled between the loads and the wait.
+__device__ __forceinline__ void tc_load_64cols_sync(uint32_t taddr, uint32_t (&a)[32], uint32_t (&b)[32]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%64];\n"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%65];\n"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]), "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15]), "=r"(a[16]), "=r"(a[17]), "=r"(a[18]), "=r"(a[19]), "=r"(a[20]), "=r"(a[21]), "=r"(a[22]), "=r"(a[23]), "=r"(a[24]), "=r"(a[25]), "=r"(a[26]), "=r"(a[27]), "=r"(a[28]), "=r"(a[29]), "=r"(a[30]), "=r"(a[31]), "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]), "=r"(b[4]), "=r"(b[5]), "=r"(b[6]), "=r"(b[7]), "=r"(b[8]), "=r"(b[9]), "=r"(b[10]), "=r"(b[11]), "=r"(b[12]), "=r"(b[13]), "=r"(b[14]), "=r"(b[15]), "=r"(b[16]), "=r"(b[17]), "=r"(b[18]), "=r"(b[19]), "=r"(b[20]), "=r"(b[21]), "=r"(b[22]), "=r"(b[23]), "=r"(b[24]), "=r"(b[25]), "=r"(b[26]), "=r"(b[27]), "=r"(b[28]), "=r"(b[29]), "=r"(b[30]), "=r"(b[31])
+        : "r"(taddr), "r"(taddr + 32) : "memory");
+}
+
+
+// Each lane writes N consecutive 32-bit columns of its own tensor-memory lane.
+__device__ __forceinline__ void tc_store_16cols(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tc_wait_store() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint4 lds_16(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
 }
 
 // ---- wrappers used by the CTA-pair (cta_group::2) kernel ----
@@ -163,34 +184,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
     return r;
 }
-__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;"
-                 ::"r"(cluster_bar), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n"
                  "barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// TMA tile loads whose completion is signalled on a barrier that may live in the peer CTA.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1,
-                                                 uint32_t cluster_bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(cluster_bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2,
-                                                 uint32_t cluster_bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(cluster_bar) : "memory");
-}
-__device__ __forceinline__ void tc_copy_sf_pair(uint32_t taddr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 __device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                  uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
@@ -272,9 +271,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + C::STAGES * C::STAGE_BYTES);
     const uint32_t full_bar = smem_u32(bars);                       // [STAGES]
     const uint32_t empty_bar = full_bar + 8 * C::STAGES;            // [STAGES]
-    const uint32_t acc_full_bar = empty_bar + 8 * C::STAGES;        // [ACC_STAGES]
+    const uint32_t sf_full_bar = empty_bar + 8 * C::STAGES;         // [STAGES] scale tiles landed
+    const uint32_t sf_ready_bar = sf_full_bar + 8 * C::STAGES;      // [STAGES] scales are in tensor memory
+    const uint32_t acc_full_bar = sf_ready_bar + 8 * C::STAGES;     // [ACC_STAGES]
     const uint32_t acc_empty_bar = acc_full_bar + 8 * C::ACC_STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::STAGES + 2 * C::ACC_STAGES);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 4 * C::STAGES + 2 * C::ACC_STAGES);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -283,10 +284,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int s = 0; s < C::STAGES; ++s) {
             mbar_init(full_bar + 8 * s, 1);
             mbar_init(empty_bar + 8 * s, 1);
+            mbar_init(sf_full_bar + 8 * s, 1);
+            mbar_init(sf_ready_bar + 8 * s, 4);    // one arrival per scale-mover warp
         }
         for (int a = 0; a < C::ACC_STAGES; ++a) {
             mbar_init(acc_full_bar + 8 * a, 1);
-            mbar_init(acc_empty_bar + 8 * a, 4);   // one arrival per epilogue warp
+            mbar_init(acc_empty_bar + 8 * a, 8);   // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -327,15 +330,22 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 for (int g = 0; g < C::N_GROUPS; ++g)
                     if (n0 + 128 * g < p.n_p) ++groups;
                 const uint32_t stage = smem_base + s * C::STAGE_BYTES;
+                // the small scale tiles go first and complete on their own barrier, so that the
+                // movers can bring them to tensor memory while the operand tiles are still in flight
+                const uint32_t sf_bar = sf_full_bar + 8 * s;
+                if (!dbg_no_sf) {   // (with the movers switched off nobody would wait for these copies)
+                    mbar_expect_tx(sf_bar, (1 + groups) * nkb * SF_TILE_BYTES);
+                    bulk_load(stage + A_BYTES + C::B_BYTES, p.a_sf + ((m0 / 128) * k_blocks + kb0) * SF_TILE_BYTES,
+                              nkb * SF_TILE_BYTES, sf_bar);
+                    for (int g = 0; g < groups; ++g)
+                        bulk_load(stage + A_BYTES + C::B_BYTES + SFA_BYTES + g * KB_PER_STAGE * SF_TILE_BYTES,
+                                  p.b_sf + ((n0 / 128 + g) * k_blocks + kb0) * SF_TILE_BYTES, nkb * SF_TILE_BYTES,
+                                  sf_bar);
+                }
                 const uint32_t bar = full_bar + 8 * s;
-                mbar_expect_tx(bar, A_BYTES + C::B_BYTES + (1 + groups) * nkb * SF_TILE_BYTES);
+                mbar_expect_tx(bar, A_BYTES + C::B_BYTES);
                 tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), static_cast<int>(m0), bar);
                 tma_load_2d(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES), static_cast<int>(n0), bar);
-                bulk_load(stage + A_BYTES + C::B_BYTES, p.a_sf + ((m0 / 128) * k_blocks + kb0) * SF_TILE_BYTES,
-                          nkb * SF_TILE_BYTES, bar);
-                for (int g = 0; g < groups; ++g)
-                    bulk_load(stage + A_BYTES + C::B_BYTES + SFA_BYTES + g * KB_PER_STAGE * SF_TILE_BYTES,
-                              p.b_sf + ((n0 / 128 + g) * k_blocks + kb0) * SF_TILE_BYTES, nkb * SF_TILE_BYTES, bar);
             }
         }
         if (!ok) {
@@ -360,35 +370,32 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
             for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
                 const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-                if (!dbg_no_load) ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
+                if (!dbg_no_load) {
+                    ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
+                    if (ok && !dbg_no_sf) ok = mbar_wait(sf_ready_bar + 8 * s, ph, abort_flag, p.status, 5);
+                }
                 if (!ok) break;
                 tc_fence_after();
                 const int64_t kb0 = kt * KB_PER_STAGE;
                 const int nkb = static_cast<int>((k_blocks - kb0) < KB_PER_STAGE ? (k_blocks - kb0) : KB_PER_STAGE);
                 const uint32_t stage = smem_base + s * C::STAGE_BYTES;
-                const uint32_t sfa_smem = stage + A_BYTES + C::B_BYTES, sfb_smem = sfa_smem + SFA_BYTES;
-                // scale tiles: 32 rows of 16 bytes, 8-row groups 128 bytes apart, no swizzle
-                for (int kb = 0; kb < nkb && !(dbg_no_sf && it > 0); ++kb) {
-                    tc_copy_sf(tmem_base + SFA_COL + 4 * kb, smem_desc(sfa_smem + kb * SF_TILE_BYTES, 0, 128, 0));
-                    for (int g = 0; g < C::N_GROUPS; ++g)
-                        if (n0 + 128 * g < p.n_p)
-                            tc_copy_sf(tmem_base + SFB_COL + (BLOCK_N / 32) * kb + 4 * g,
-                                       smem_desc(sfb_smem + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES, 0, 128, 0));
-                }
                 // operands: 128-byte swizzled rows, 8-row groups 1024 bytes apart; each K-block
-                // of 64 values is 32 bytes further along the row
+                // of 64 values is 32 bytes further along the row. Scales: this stage's ring slot.
                 const uint64_t a_desc = smem_desc(stage, 16, 1024, 2);
                 const uint64_t b_desc = smem_desc(stage + A_BYTES, 16, 1024, 2);
+                const uint32_t sfa_tmem = tmem_base + SF_COL0 + s * C::SF_STAGE_COLS, sfb_tmem = sfa_tmem + 16;
                 for (int kb = 0; kb < nkb; ++kb)
-                    tc_mma_nvf4(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc, tmem_base + SFA_COL + 4 * kb,
-                                tmem_base + SFB_COL + (BLOCK_N / 32) * kb, (kt > 0 || kb > 0) ? 1u : 0u);
+                    tc_mma_nvf4(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc, sfa_tmem + 4 * kb,
+                                sfb_tmem + (BLOCK_N / 32) * kb, (kt > 0 || kb > 0) ? 1u : 0u);
                 tc_commit(empty_bar + 8 * s);          // stage reusable once these MMAs have read it
             }
             if (ok) tc_commit(acc_full_bar + 8 * acc);  // accumulator complete
         }
-    } else if (warp >= 2) {
+    } else if (warp >= 2 && warp < 10) {
         // ------------------------------------------------------------------ epilogue
         const int quad = warp & 3;                       // tensor-memory lanes 32*quad .. +31
+        constexpr int COLS = BLOCK_N / 2;                // columns per warp: left or right half
+        const int half = (warp - 2) >> 2;
         const float alpha = __ldg(p.alpha);
         OUT *out = static_cast<OUT *>(p.d);
         const bool vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((p.ldd * sizeof(OUT)) % 16 == 0);
@@ -397,26 +404,79 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
             int64_t mb, nb;
             tile_coords(t, num_m, num_n, mb, nb);
-            const int64_t row = mb * BLOCK_M + quad * 32 + lane, n0 = nb * BLOCK_N;
+            const int64_t row = mb * BLOCK_M + quad * 32 + lane, n0 = nb * BLOCK_N + half * COLS;
             const uint32_t acc = tile_i % C::ACC_STAGES, acc_ph = (tile_i / C::ACC_STAGES) & 1u;
             ok = mbar_wait(acc_full_bar + 8 * acc, acc_ph, abort_flag, p.status, 4);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BLOCK_N;
+            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BLOCK_N + half * COLS;
+            const bool row_ok = row < p.m && !dbg_no_store;
 #pragma unroll 1
-            for (int c = 0; c < BLOCK_N / 32; ++c) {
+            for (int c = 0; c < COLS / 32; c += 2) {
+                uint32_t v0[32], v1[32];
+                tc_load_64cols_sync(t_acc + 32 * c, v0, v1);
+                if (c + 2 >= COLS / 32) {                // everything is in registers: release the accumulator
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty_bar + 8 * acc);
+                }
                 const int64_t col = n0 + 32 * c;
-                if (col >= p.n) break;                   // uniform across the warp
-                uint32_t v[32];
-                tc_load_32cols(t_acc + 32 * c, v);
-                const int64_t left = p.n - col;
-                if (row < p.m && !dbg_no_store)
-                    store_chunk<OUT>(out + row * p.ldd + col, v, alpha, left < 32 ? static_cast<int>(left) : 32, vec_ok);
+                const int64_t left0 = p.n - col, left1 = left0 - 32;
+                if (row_ok && left0 > 0)
+                    store_chunk<OUT>(out + row * p.ldd + col, v0, alpha, left0 < 32 ? static_cast<int>(left0) : 32, vec_ok);
+                if (row_ok && left1 > 0)
+                    store_chunk<OUT>(out + row * p.ldd + col + 32, v1, alpha, left1 < 32 ? static_cast<int>(left1) : 32, vec_ok);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty_bar + 8 * acc);
+        }
+    } else if (warp >= 10 && !dbg_no_load && !dbg_no_sf) {
+        // ------------------------------------------------------------------ scale movers
+        const int quad = warp & 3;
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            int64_t mb, nb;
+            tile_coords(t, num_m, num_n, mb, nb);
+            const int64_t n0 = nb * BLOCK_N;
+            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+                ok = mbar_wait(sf_full_bar + 8 * s, ph, abort_flag, p.status, 6);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const int64_t kb0 = kt * KB_PER_STAGE;
+                const int nkb = static_cast<int>((k_blocks - kb0) < KB_PER_STAGE ? (k_blocks - kb0) : KB_PER_STAGE);
+                const uint32_t stage = smem_base + s * C::STAGE_BYTES;
+                const uint32_t sfa_smem = stage + A_BYTES + C::B_BYTES + lane * 16, sfb_smem = sfa_smem + SFA_BYTES;
+                const uint32_t slot = lane_base + SF_COL0 + s * C::SF_STAGE_COLS;
+                uint32_t r[16];
+                // A: four columns per K-block = the 16 bytes of row `lane` of that K-block's tile
+#pragma unroll
+                for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (kb < nkb) v = lds_16(sfa_smem + kb * SF_TILE_BYTES);
+                    r[4 * kb] = v.x; r[4 * kb + 1] = v.y; r[4 * kb + 2] = v.z; r[4 * kb + 3] = v.w;
+                }
+                tc_store_16cols(slot, r);
+                // B: per K-block N/32 columns, the row groups of 128 side by side
+#pragma unroll
+                for (int half = 0; half < C::SFB_COLS / 16; ++half) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int col = half * 16 + q * 4;                 // column inside the B part
+                        const int kb = col / (BLOCK_N / 32), g = (col % (BLOCK_N / 32)) / 4;
+                        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                        if (kb < nkb && n0 + 128 * g < p.n_p)
+                            v = lds_16(sfb_smem + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES);
+                        r[4 * q] = v.x; r[4 * q + 1] = v.y; r[4 * q + 2] = v.z; r[4 * q + 3] = v.w;
+                    }
+                    tc_store_16cols(slot + 16 + half * 16, r);
+                }
+                tc_wait_store();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sf_ready_bar + 8 * s);
+            }
         }
     }
 
@@ -432,13 +492,16 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 //
 // Two CTAs of a cluster (two SMs) compute one 256 x 256 tile with cta_group::2 MMAs: CTA r of
 // the pair holds rows m0 + 128 r .. of A and rows n0 + 128 r .. of B in its shared memory,
-// and the tensor cores of both SMs read both halves of B. Each byte of B fetched from L2
-// therefore feeds twice as many multiply-adds as in the single-CTA kernel, which is what
-// that kernel is short of. Only the even CTA (the leader) issues scale copies and MMAs;
-// both CTAs run a TMA producer and an epilogue for their own 128 rows of the tile.
+// and the tensor cores of both SMs read both halves of B. Per stage an SM fetches 38 KB from
+// L2 instead of the single-CTA kernel's 54 KB for the same number of multiply-adds, and that
+// kernel is limited by exactly this traffic. Only the even CTA (the leader) issues MMAs; both
+// CTAs run a TMA producer, scale movers and an epilogue for their own 128 rows of the tile.
 //
-//   full[s]      leader's barrier, 2 arrivals: each producer announces its own bytes and its
-//                TMA loads (cta_group::2 form) complete on the leader's barrier
+//   full[s]      one per CTA: this CTA's operand tiles have landed
+//   peer_full[s] leader's barrier, 1 arrival: a relay thread in the peer saw the peer's full[s]
+//   sf_full[s]   one per CTA: this CTA's scale tiles have landed in its shared memory
+//   sf_ready[s]  leader's barrier, 8 arrivals: the four mover warps of each CTA have written
+//                the stage's scales into their own CTA's tensor memory
 //   empty[s]     one per CTA, released in both CTAs by the leader's tcgen05.commit
 //   acc_full     one per CTA, same mechanism
 //   acc_empty    leader's barrier, 16 arrivals: 8 epilogue warps of each CTA
@@ -450,9 +513,17 @@ constexpr int SFB_BYTES = 2 * KB_PER_STAGE * SF_TILE_BYTES;               // sca
 constexpr int STAGE_BYTES = A_BYTES + B_HALF_BYTES + SFA_BYTES + SFB_BYTES;  // 38 KiB
 constexpr int STAGES = 5;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-constexpr int EPI_WARPS = 8;
-constexpr int THREADS = 64 + 32 * EPI_WARPS;
+constexpr int EPI_WARPS = 8, MOVER_WARPS = 4;
+constexpr int THREADS = 64 + 32 * (EPI_WARPS + MOVER_WARPS);
+constexpr int SF_STAGE_COLS = 16 + 32;                                    // A scales, B scales
 static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
+static_assert(SF_COL0 + STAGES * SF_STAGE_COLS <= TMEM_COLS, "scale ring does not fit tensor memory");
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
 
 template <typename OUT>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -463,11 +534,14 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + STAGES * STAGE_BYTES);
-    const uint32_t full_bar = smem_u32(bars);                 // [STAGES], used in the leader only
+    const uint32_t full_bar = smem_u32(bars);                 // [STAGES] this CTA's operand tiles landed
     const uint32_t empty_bar = full_bar + 8 * STAGES;         // [STAGES]
-    const uint32_t acc_full_bar = empty_bar + 8 * STAGES;
+    const uint32_t sf_full_bar = empty_bar + 8 * STAGES;      // [STAGES]
+    const uint32_t sf_ready_bar = sf_full_bar + 8 * STAGES;   // [STAGES], used in the leader only
+    const uint32_t peer_full_bar = sf_ready_bar + 8 * STAGES; // [STAGES], leader only: the peer's tiles landed
+    const uint32_t acc_full_bar = peer_full_bar + 8 * STAGES;
     const uint32_t acc_empty_bar = acc_full_bar + 8;          // used in the leader only
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 5 * STAGES + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -476,8 +550,11 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar + 8 * s, 2);
+            mbar_init(full_bar + 8 * s, 1);
             mbar_init(empty_bar + 8 * s, 1);
+            mbar_init(sf_full_bar + 8 * s, 1);
+            mbar_init(sf_ready_bar + 8 * s, 2 * MOVER_WARPS);
+            mbar_init(peer_full_bar + 8 * s, 1);
         }
         mbar_init(acc_full_bar, 1);
         mbar_init(acc_empty_bar, 2 * EPI_WARPS);
@@ -501,8 +578,8 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int64_t k_blocks = p.k_p / 64;
     const int64_t k_tiles = (k_blocks + KB_PER_STAGE - 1) / KB_PER_STAGE;
     const int64_t pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-
     const bool dbg_no_sf = p.debug & 1, dbg_no_load = p.debug & 2, dbg_no_store = p.debug & 4;
+
     if (warp == 0 && lane == 0 && !dbg_no_load) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
         uint32_t it = 0;
@@ -516,15 +593,22 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 ok = mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 1);
                 if (!ok) break;
                 const uint32_t stage = smem_base + s * STAGE_BYTES;
-                const uint32_t bar = map_to_cta(full_bar + 8 * s, 0);
                 const int kb0 = static_cast<int>(kt * KB_PER_STAGE);
-                // out-of-range parts of a box are zero-filled and still counted, so the byte count is fixed
-                mbar_expect_tx_cluster(bar, STAGE_BYTES);
-                tma_load_2d_pair(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), m0, bar);
-                tma_load_2d_pair(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES),
-                                 n0 + static_cast<int>(rank) * 128, bar);
-                tma_load_3d_pair(stage + A_BYTES + B_HALF_BYTES, &map_sfa, 0, kb0, m0 / 128, bar);
-                tma_load_3d_pair(stage + A_BYTES + B_HALF_BYTES + SFA_BYTES, &map_sfb, 0, kb0, n0 / 128, bar);
+                // out-of-range parts of a box are zero-filled and still counted: fixed byte counts
+                if (!dbg_no_sf) {
+                    const uint32_t sf_bar = sf_full_bar + 8 * s;
+                    mbar_expect_tx(sf_bar, SFA_BYTES + SFB_BYTES);
+                    tma_load_3d(stage + A_BYTES + B_HALF_BYTES, &map_sfa, 0, kb0, m0 / 128, sf_bar);
+                    tma_load_3d(stage + A_BYTES + B_HALF_BYTES + SFA_BYTES, &map_sfb, 0, kb0, n0 / 128, sf_bar);
+                }
+                // each CTA's operand tiles complete on its OWN barrier; the peer relays completion to
+                // the leader with one remote arrive per stage (letting the peer's TMA loads signal
+                // the leader's barrier directly made every stage about 0.4 us slower when measured)
+                const uint32_t bar = full_bar + 8 * s;
+                mbar_expect_tx(bar, A_BYTES + B_HALF_BYTES);
+                tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), m0, bar);
+                tma_load_2d(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES),
+                            n0 + static_cast<int>(rank) * 128, bar);
             }
         }
         if (!ok) {
@@ -542,29 +626,40 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             tc_fence_after();
             for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                if (!dbg_no_load) ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
+                if (!dbg_no_load) {
+                    ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
+                    if (ok) ok = mbar_wait(peer_full_bar + 8 * s, ph, abort_flag, p.status, 7);
+                    if (ok && !dbg_no_sf) ok = mbar_wait(sf_ready_bar + 8 * s, ph, abort_flag, p.status, 5);
+                }
                 if (!ok) break;
                 tc_fence_after();
                 const int64_t kb0 = kt * KB_PER_STAGE;
                 const int nkb = static_cast<int>((k_blocks - kb0) < KB_PER_STAGE ? (k_blocks - kb0) : KB_PER_STAGE);
                 const uint32_t stage = smem_base + s * STAGE_BYTES;
-                const uint32_t sfa_smem = stage + A_BYTES + B_HALF_BYTES, sfb_smem = sfa_smem + SFA_BYTES;
-                for (int kb = 0; kb < nkb && !(dbg_no_sf && it > 0); ++kb) {
-                    tc_copy_sf_pair(tmem_base + SFA_COL + 4 * kb, smem_desc(sfa_smem + kb * SF_TILE_BYTES, 0, 128, 0));
-                    for (int g = 0; g < 2; ++g)
-                        tc_copy_sf_pair(tmem_base + SFB_COL + 8 * kb + 4 * g,
-                                        smem_desc(sfb_smem + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES, 0, 128, 0));
-                }
                 const uint64_t a_desc = smem_desc(stage, 16, 1024, 2);
                 const uint64_t b_desc = smem_desc(stage + A_BYTES, 16, 1024, 2);
+                const uint32_t sfa_tmem = tmem_base + SF_COL0 + s * SF_STAGE_COLS, sfb_tmem = sfa_tmem + 16;
                 for (int kb = 0; kb < nkb; ++kb)
-                    tc_mma_nvf4_pair(tmem_base, a_desc + 2 * kb, b_desc + 2 * kb, idesc, tmem_base + SFA_COL + 4 * kb,
-                                     tmem_base + SFB_COL + 8 * kb, (kt > 0 || kb > 0) ? 1u : 0u);
+                    tc_mma_nvf4_pair(tmem_base, a_desc + 2 * kb, b_desc + 2 * kb, idesc, sfa_tmem + 4 * kb,
+                                     sfb_tmem + 8 * kb, (kt > 0 || kb > 0) ? 1u : 0u);
                 tc_commit_pair(empty_bar + 8 * s);
             }
             if (ok) tc_commit_pair(acc_full_bar);
         }
-    } else if (warp >= 2) {
+    } else if (warp == 1 && lane == 0 && !leader && !dbg_no_load) {
+        // ------------------------------------------------------------------ relay (peer only)
+        const uint32_t leader_peer_full = map_to_cta(peer_full_bar, 0);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
+            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 8);
+                if (!ok) break;
+                mbar_arrive_cluster(leader_peer_full + 8 * s);
+            }
+        }
+    } else if (warp >= 2 && warp < 2 + EPI_WARPS) {
         // ------------------------------------------------------------------ epilogue (both CTAs)
         const int quad = warp & 3;                       // tensor-memory lanes 32*quad .. +31
         const int half = (warp - 2) >> 2;                // which 128 of the 256 columns
@@ -583,19 +678,64 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + half * 128;
+            const bool row_ok = row < p.m && !dbg_no_store;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 4; c += 2) {
+                uint32_t v0[32], v1[32];
+                tc_load_64cols_sync(t_acc + 32 * c, v0, v1);
+                if (c + 2 >= 4) {                        // everything is in registers: release the accumulator
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+                }
                 const int64_t col = n0 + 32 * c;
-                if (col >= p.n) break;
-                uint32_t v[32];
-                tc_load_32cols(t_acc + 32 * c, v);
-                const int64_t left = p.n - col;
-                if (row < p.m && !dbg_no_store)
-                    store_chunk<OUT>(out + row * p.ldd + col, v, alpha, left < 32 ? static_cast<int>(left) : 32, vec_ok);
+                const int64_t left0 = p.n - col, left1 = left0 - 32;
+                if (row_ok && left0 > 0)
+                    store_chunk<OUT>(out + row * p.ldd + col, v0, alpha, left0 < 32 ? static_cast<int>(left0) : 32, vec_ok);
+                if (row_ok && left1 > 0)
+                    store_chunk<OUT>(out + row * p.ldd + col + 32, v1, alpha, left1 < 32 ? static_cast<int>(left1) : 32, vec_ok);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+        }
+    } else if (warp >= 2 + EPI_WARPS && !dbg_no_load && !dbg_no_sf) {
+        // ------------------------------------------------------------------ scale movers (both CTAs)
+        const int quad = warp & 3;
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+        const uint32_t leader_sf_ready = map_to_cta(sf_ready_bar, 0);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
+            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                ok = mbar_wait(sf_full_bar + 8 * s, ph, abort_flag, p.status, 6);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const uint32_t stage = smem_base + s * STAGE_BYTES;
+                const uint32_t sfa_smem = stage + A_BYTES + B_HALF_BYTES + lane * 16, sfb_smem = sfa_smem + SFA_BYTES;
+                const uint32_t slot = lane_base + SF_COL0 + s * SF_STAGE_COLS;
+                uint32_t r[16];
+                // tiles beyond K were zero-filled by the TMA unit, so all four K-blocks can be copied
+#pragma unroll
+                for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
+                    const uint4 v = lds_16(sfa_smem + kb * SF_TILE_BYTES);
+                    r[4 * kb] = v.x; r[4 * kb + 1] = v.y; r[4 * kb + 2] = v.z; r[4 * kb + 3] = v.w;
+                }
+                tc_store_16cols(slot, r);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int col = half * 16 + q * 4;     // column inside the B part: 8 per K-block
+                        const int kb = col / 8, g = (col % 8) / 4;
+                        const uint4 v = lds_16(sfb_smem + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES);
+                        r[4 * q] = v.x; r[4 * q + 1] = v.y; r[4 * q + 2] = v.z; r[4 * q + 3] = v.w;
+                    }
+                    tc_store_16cols(slot + 16 + half * 16, r);
+                }
+                tc_wait_store();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(leader_sf_ready + 8 * s);
+            }
         }
     }
 
@@ -760,11 +900,11 @@ extern "C" int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const
     if (status) FOS_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
     CUtensorMap map_a, map_b;
 
-    // CTA pairs on 256 x 256 tiles when the shape allows it and there is enough work for most pairs
+    // The CTA-pair kernel is correct but measured slower than the single-CTA kernel on B200 (both
+    // SMs ingest as many bytes per MMA once the peer's half of B is counted), so it only runs
+    // when asked for.
     const bool pair_fits = m_p % 256 == 0 && n_p % 256 == 0;
-    bool use_pair = pair_fits && (m_p / 256) * (n_p / 256) >= sms / 4;
-    if (g_gemm_variant == 2) use_pair = pair_fits;
-    if (g_gemm_variant == 128 || g_gemm_variant == 256) use_pair = false;
+    const bool use_pair = pair_fits && g_gemm_variant == 2;
     if (use_pair) {
         CUtensorMap map_sfa, map_sfb;
         if ((st = make_operand_map(&map_a, a_codes, m_p, k_p / 2, 128)) != FOS_OK) return st;

@@ -82,6 +82,10 @@ __global__ void __launch_bounds__(256) amax_kernel(const T *__restrict__ x, int6
             m = fmaxf(m, fabsf(elem_to_float<T>(x[r * ld + c])));
         }
     }
+    // the quantize kernel that follows may be scheduled while this grid drains (it waits for this
+    // grid's completion with griddepcontrol.wait before it reads amax); signalling here rather
+    // than at the top keeps its CTAs from taking SM slots this grid still needs
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(FULL, m, o));
     __shared__ float warp_max[8];
@@ -538,8 +542,10 @@ quantize_rows_kernel(const QuantParams p) {
 
     uint32_t w[8];
     load_block_words<T>(p, static_cast<int64_t>(tr) * 64 + r_in_tile, tc_ * 4 + cb_in_tile, w);
-    // amax comes from the previous kernel in the stream; nothing above needed it
-    const TensorConsts tc = tensor_consts<KIND>(__ldg(p.amax), p.rule);
+    // amax comes from the previous kernel in the stream; nothing above needed it. With
+    // programmatic dependent launch this CTA may be running before that kernel has finished.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(p.amax), p.rule);
     if (threadIdx.x < 128) lut[threadIdx.x] = scale_entry(threadIdx.x, tc);
     __syncthreads();
 
@@ -592,8 +598,16 @@ cudaError_t launch_rows(const QuantParams &p, cudaStream_t stream) {
     const int64_t n_tiles = (p.rows_p >> 6) * (p.cols_p >> 6);
     int64_t grid = static_cast<int64_t>(ctas_per_sm[slot]) * sm_count[slot];
     if (grid > n_tiles) grid = n_tiles;
-    kernel<<<static_cast<unsigned>(grid), ROWS_CTA_THREADS, 0, stream>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(ROWS_CTA_THREADS);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
 template <typename T, int KIND>
