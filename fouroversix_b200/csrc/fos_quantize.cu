@@ -311,7 +311,7 @@ __device__ __forceinline__ float4 scale_entry(uint32_t sfb, const TensorConsts &
 template <int KIND, bool TWO_D, bool TRANSPOSED>
 __device__ __forceinline__ void quantize_block(const float (&v)[16], const TensorConsts &tc, int rule,
                                                bool exact_only, float *scratch, int lane, const float4 *lut,
-                                               uint32_t &lo, uint32_t &hi, uint32_t &sf_byte) {
+                                               float *coop, uint32_t &lo, uint32_t &hi, uint32_t &sf_byte) {
     const float amax = tc.amax;
     float bmax = 0.0f;
 #pragma unroll
@@ -344,10 +344,12 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
         // 2 * 47u * sum|t| * G^2 <= 376u * sqrt(sum t^2) * G^2 (Cauchy-Schwarz over 16 terms) plus
         // 40u relative for the roundings of the two summations. `tau` is 1.5 times that, for
         // both candidates together; a difference inside tau is re-decided exactly below.
-        if (!TWO_D && rule == FOS_RULE_MSE && !exact_only && sfb_a >= 8u && sfb_b >= 8u && tc.filter_ok &&
-            r_a >= 0x1p-16f && r_b >= 0x1p-16f) {
+        const bool eligible = !TWO_D && rule == FOS_RULE_MSE && !exact_only && sfb_a >= 8u && sfb_b >= 8u &&
+                              tc.filter_ok && r_a >= 0x1p-16f && r_b >= 0x1p-16f;
+        bool decided = false, pick_b = false;
+        uint32_t ca[2] = {0u, 0u}, cb[2] = {0u, 0u};
+        if (eligible) {
             const uint64_t ra2 = pack2(r_a, r_a), rb2 = pack2(r_b, r_b);
-            uint32_t ca[2], cb[2];
             uint64_t acc_a = pack2(0.0f, 0.0f), acc_b = acc_a;
 #pragma unroll
             for (int w = 0; w < 2; ++w) {
@@ -369,13 +371,53 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
             const float tau = 0x1p-24f * 1.5f *
                               (376.0f * (sqrtf(sum_a) * ea.w + sqrtf(sum_b) * eb.w) + 40.0f * (err_a + err_b));
             const float diff = err_b - err_a;
-            if (fabsf(diff) > tau) {
-                const bool pick_b = diff < 0.0f;
-                lo = pick_b ? cb[0] : ca[0];
-                hi = pick_b ? cb[1] : ca[1];
-                sf_byte = pick_b ? sfb_b : sfb_a;
-                return;
+            decided = fabsf(diff) > tau;
+            pick_b = diff < 0.0f;
+        }
+
+        // Undecided blocks are re-decided with the reference's exact sequence. When the caller
+        // provides a per-warp exchange buffer (and calls this function from converged code) the
+        // whole warp works on one such block at a time: lane 16c+i evaluates element i under
+        // candidate c, and the 16 terms are added in the reference's order with shuffles. That
+        // costs the warp about 60 instructions per undecided block instead of running the
+        // 16-element exact loop on every lane of a diverged warp.
+        if (coop != nullptr) {
+            unsigned pending = __ballot_sync(FULL, eligible && !decided);
+            while (pending) {
+                const int src = __ffs(pending) - 1;
+                pending &= pending - 1;
+                if (lane == src) {
+                    float4 *x4 = reinterpret_cast<float4 *>(coop);
+                    x4[0] = make_float4(v[0], v[1], v[2], v[3]);
+                    x4[1] = make_float4(v[4], v[5], v[6], v[7]);
+                    x4[2] = make_float4(v[8], v[9], v[10], v[11]);
+                    x4[3] = make_float4(v[12], v[13], v[14], v[15]);
+                    x4[4] = make_float4(s_a, r_a, s_b, r_b);
+                }
+                __syncwarp();
+                const int cand = lane >> 4, i = lane & 15;
+                const float x = coop[i];
+                const float s = coop[16 + 2 * cand], r = coop[17 + 2 * cand];
+                const float2 q = e2m1x2_to_float2(cvt_e2m1x2(0.0f, __fmaf_rn(x, r, 0.0f)));
+                const float d = __fsub_rn(__fdiv_rn(__fmul_rn(__fmul_rn(q.x, s), amax), 1536.0f), x);
+                const float e = __fmul_rn(d, d);
+                const float p = __fadd_rn(e, __shfl_down_sync(FULL, e, 8));      // valid in lanes with i < 8
+                float total = __shfl_sync(FULL, p, cand * 16);
+#pragma unroll
+                for (int k = 1; k < 8; ++k) total = __fadd_rn(total, __shfl_sync(FULL, p, cand * 16 + k));
+                const float exact_a = __shfl_sync(FULL, total, 0), exact_b = __shfl_sync(FULL, total, 16);
+                if (lane == src) {
+                    decided = true;
+                    pick_b = exact_b < exact_a;
+                }
+                __syncwarp();
             }
+        }
+        if (eligible && decided) {
+            lo = pick_b ? cb[0] : ca[0];
+            hi = pick_b ? cb[1] : ca[1];
+            sf_byte = pick_b ? sfb_b : sfb_a;
+            return;
         }
 
         uint32_t lo_a = 0u, hi_a = 0u, lo_b = 0u, hi_b = 0u;
@@ -386,7 +428,7 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
         const float err_b = block_error<TWO_D, TRANSPOSED>(e, rule, scratch, lane);
         exact_error_terms<false>(v, lo_a, hi_a, s_a, amax, 1536.0f, rule, e);
         const float err_a = block_error<TWO_D, TRANSPOSED>(e, rule, scratch, lane);
-        const bool pick_b = err_b < err_a;
+        pick_b = err_b < err_a;
         lo = pick_b ? lo_b : lo_a;
         hi = pick_b ? hi_b : hi_a;
         sf_byte = pick_b ? sfb_b : sfb_a;
@@ -480,7 +522,8 @@ __global__ void __launch_bounds__(CTA_THREADS) quantize_kernel(const QuantParams
     float *scratch = TWO_D ? reinterpret_cast<float *>(smem) + warp * 512 : nullptr;
     const TensorConsts tc = tensor_consts<KIND>(__ldg(p.amax), p.rule);
     uint32_t lo, hi, sf_byte;
-    quantize_block<KIND, TWO_D, TRANSPOSED>(v, tc, p.rule, p.exact_only != 0, scratch, lane, nullptr, lo, hi, sf_byte);
+    quantize_block<KIND, TWO_D, TRANSPOSED>(v, tc, p.rule, p.exact_only != 0, scratch, lane, nullptr, nullptr, lo, hi,
+                                            sf_byte);
 
     // rows_p / cols_p are multiples of the tile, so every thread owns a valid output block
     *reinterpret_cast<uint2 *>(p.codes + row * (p.cols_p >> 1) + cb * 8) = make_uint2(lo, hi);
@@ -530,6 +573,7 @@ template <typename T, int KIND>
 __global__ void __launch_bounds__(ROWS_CTA_THREADS, KIND == KIND_STATIC ? 5 : 4)
 quantize_rows_kernel(const QuantParams p) {
     __shared__ float4 lut[128];                  // scale byte -> {s, r, g, g^2}, see scale_entry()
+    __shared__ __align__(16) float coop[ROWS_CTA_THREADS / 32][20];   // per warp: one block + its two scales
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_c = static_cast<int>(p.cols_p >> 6), tiles_r = static_cast<int>(p.rows_p >> 6);
     const int r_in_tile = warp * 8 + (lane >> 2), cb_in_tile = lane & 3;
@@ -564,7 +608,7 @@ quantize_rows_kernel(const QuantParams p) {
             v[2 * k + 1] = f.y;
         }
         uint32_t lo, hi, sf_byte;
-        quantize_block<KIND, false, false>(v, tc, p.rule, p.exact_only != 0, nullptr, lane, lut, lo, hi, sf_byte);
+        quantize_block<KIND, false, false>(v, tc, p.rule, p.exact_only != 0, nullptr, lane, lut, coop[warp], lo, hi, sf_byte);
         const int64_t row = static_cast<int64_t>(tr) * 64 + r_in_tile, cb = tc_ * 4 + cb_in_tile;
         *reinterpret_cast<uint2 *>(p.codes + row * (p.cols_p >> 1) + cb * 8) = make_uint2(lo, hi);
         p.sf[sf_offset(row, cb, n_cb, p.sf_tiled != 0)] = static_cast<uint8_t>(sf_byte);

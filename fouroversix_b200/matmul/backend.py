@@ -17,10 +17,16 @@ from fouroversix_b200.quantize.backend import B200QuantizeBackend
 from fouroversix_b200.utils import DataType
 
 _OUT = {DataType.bfloat16: torch.bfloat16, DataType.float16: torch.float16, DataType.float32: torch.float32}
+_FORMATS = {DataType.nvfp4: _native.FOS_NVFP4, DataType.if4: _native.FOS_IF4}
+
+
+def _layout(q: QuantizedTensor) -> int:
+    return _native.FOS_SF_TILED if q.scale_factors_are_in_blackwell_layout else _native.FOS_SF_ROWMAJOR
 
 
 class B200MatmulBackend:
-    """FP4 x FP4 -> bf16 / fp16 / fp32 on the 5th-generation tensor cores."""
+    """FP4 x FP4 -> bf16 / fp16 / fp32 on the 5th-generation tensor cores: block-scaled
+    kind::mxf4nvf4 MMAs for NVFP4 operands, expand-to-fp16 + kind::f16 MMAs for IF4."""
 
     @classmethod
     def is_available(cls) -> bool:
@@ -34,12 +40,10 @@ class B200MatmulBackend:
                 "The first input must be in row-major layout, the second input must be"
                 "in column-major layout, and both inputs must have the same inner "
                 "dimension")
-        if input.dtype != DataType.nvfp4 or other.dtype != DataType.nvfp4:
-            return "both operands must be nvfp4 (the IF4 GEMM is a separate entry point)"
+        if input.dtype not in _FORMATS or other.dtype not in _FORMATS:
+            return "operands must be nvfp4 or if4"
         if input.device.type != "cuda" or other.device != input.device:
             return "both operands must live on the same CUDA device"
-        if not (input.scale_factors_are_in_blackwell_layout and other.scale_factors_are_in_blackwell_layout):
-            return "scale factors must be in the 128x4 tile layout"
         if DataType(out_dtype) not in _OUT:
             return f"output type {out_dtype} is not supported"
         return None
@@ -71,16 +75,29 @@ class B200MatmulBackend:
         status = torch.zeros(1, dtype=torch.int32, device=dev) if check_status else None
         a_vals, b_vals = input.values.contiguous(), other.values.contiguous()
         a_sf, b_sf = input.scale_factors.contiguous(), other.scale_factors.contiguous()
-        fmt = _native.FOS_NVFP4
+        fa, fb = _FORMATS[input.dtype], _FORMATS[other.dtype]
+        # block-scaled FP4 tensor cores when both operands are NVFP4 in the tile layout; otherwise
+        # (IF4, or row-major scales) the fp16 path, which needs a scratch buffer for the expanded operands
+        native_fp4 = (fa == fb == _native.FOS_NVFP4 and _layout(input) == _layout(other) == _native.FOS_SF_TILED)
         with torch.cuda.device(dev):
             lib, stream = _native.lib(), _native.stream_ptr(dev)
             _native.check(lib.fos_gemm_alpha(
-                input.amax.data_ptr(), fmt, input.scale_rule.cuda_id,
-                other.amax.data_ptr(), fmt, other.scale_rule.cuda_id, alpha.data_ptr(), stream), "fos_gemm_alpha")
-            _native.check(lib.fos_gemm_nvfp4(
-                a_vals.data_ptr(), a_sf.data_ptr(), b_vals.data_ptr(), b_sf.data_ptr(), alpha.data_ptr(),
-                out.data_ptr(), _native.elem_code(torch_out), m_p, n_p, k_p, m, n, out.stride(0),
-                0 if status is None else status.data_ptr(), stream), "fos_gemm_nvfp4")
+                input.amax.data_ptr(), fa, input.scale_rule.cuda_id,
+                other.amax.data_ptr(), fb, other.scale_rule.cuda_id, alpha.data_ptr(), stream), "fos_gemm_alpha")
+            status_ptr = 0 if status is None else status.data_ptr()
+            if native_fp4:
+                _native.check(lib.fos_gemm_nvfp4(
+                    a_vals.data_ptr(), a_sf.data_ptr(), b_vals.data_ptr(), b_sf.data_ptr(), alpha.data_ptr(),
+                    out.data_ptr(), _native.elem_code(torch_out), m_p, n_p, k_p, m, n, out.stride(0),
+                    status_ptr, stream), "fos_gemm_nvfp4")
+            else:
+                nbytes = int(lib.fos_gemm_if4_workspace_bytes(m_p, n_p, k_p))
+                workspace = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+                _native.check(lib.fos_gemm_if4(
+                    a_vals.data_ptr(), a_sf.data_ptr(), fa, _layout(input),
+                    b_vals.data_ptr(), b_sf.data_ptr(), fb, _layout(other), alpha.data_ptr(),
+                    out.data_ptr(), _native.elem_code(torch_out), m_p, n_p, k_p, m, n, out.stride(0),
+                    workspace.data_ptr(), nbytes, status_ptr, stream), "fos_gemm_if4")
         if status is not None and int(status.item()) != 0:
             raise _native.NativeLibraryError(
                 f"fos_gemm_nvfp4: a bounded device-side wait timed out (site {int(status.item())})")

@@ -133,6 +133,26 @@ int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b
                    int32_t *status, void *stream);
 
 /*
+ * D[m, n] = alpha[0] * sum_k A[m, k] * B[n, k] for operands in FOS_IF4 or FOS_NVFP4 (any mix),
+ * scales in either layout. Each element is expanded to fp16(value) * fp16(|scale|) (integer
+ * blocks: fp16(int * 6/7) first), the fp16 matrices are multiplied on the tensor cores
+ * (kind::f16) with fp32 accumulation. `workspace` is device scratch of at least
+ * fos_gemm_if4_workspace_bytes(m_p, n_p, k_p) = (m_p + n_p) * k_p * 2 bytes, 128-byte aligned; it
+ * holds the expanded operands during the call and nothing afterwards. Other arguments as for
+ * fos_gemm_nvfp4.
+ *
+ * Replaces: the reference's only IF4 matmuls, PyTorchMatmulBackend
+ * (src/fouroversix/matmul/pytorch.py:33-52) and the disabled Triton kernel
+ * (src/fouroversix/kernels/triton/matmul.py:14-233, src/fouroversix/matmul/triton.py:14-47).
+ */
+int64_t fos_gemm_if4_workspace_bytes(int64_t m_p, int64_t n_p, int64_t k_p);
+int fos_gemm_if4(const uint8_t *a_codes, const uint8_t *a_sf, int a_format, int a_sf_layout,
+                 const uint8_t *b_codes, const uint8_t *b_sf, int b_format, int b_sf_layout,
+                 const float *alpha, void *d, int out_dtype, int64_t m_p, int64_t n_p, int64_t k_p,
+                 int64_t m, int64_t n, int64_t ldd, void *workspace, int64_t workspace_bytes,
+                 int32_t *status, void *stream);
+
+/*
  * Process-wide tuning / testing knobs. No counterpart in the reference.
  *   FOS_OPT_GEMM_VARIANT   0 = choose the GEMM kernel per problem (default);
  *                          128 / 256 = single-CTA kernel with 128 x 128 / 128 x 256 tiles;

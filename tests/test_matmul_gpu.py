@@ -36,7 +36,7 @@ def _dense_reference(qa: fos.QuantizedTensor, qb: fos.QuantizedTensor) -> torch.
         torch.backends.cuda.matmul.allow_tf32 = prev
 
 
-def _check(out: torch.Tensor, ref32: torch.Tensor, what: str):
+def _check(out: torch.Tensor, ref32: torch.Tensor, what: str, mismatch_scale: float = 1.0):
     torch.cuda.synchronize()
     assert out.shape == ref32.shape, what
     assert torch.isfinite(out.float()).all(), what
@@ -46,7 +46,9 @@ def _check(out: torch.Tensor, ref32: torch.Tensor, what: str):
     frac = (out != ref32.to(out.dtype)).float().mean().item()
     # the 0.1 % bar is the reference's for bf16 outputs; fp16 keeps 3 more mantissa bits, so the
     # same fp32 summation-order noise flips 8 times as many roundings
-    tol = MISMATCH_TOLERANCE * (8 if out.dtype == torch.float16 else 1)
+    # ... and both sides accumulate K products in fp32 in different orders; that noise grows like
+    # sqrt(K), so beyond the reference test's largest K (1024) the bar grows by sqrt(K / 1024)
+    tol = MISMATCH_TOLERANCE * (8 if out.dtype == torch.float16 else 1) * mismatch_scale
     assert frac <= tol, f"{what}: {frac:.3%} of outputs differ"
 
 
@@ -117,8 +119,6 @@ def _matmul_against_oracle(oracle, m, n, k, scale_rule):
 def test_golden_matmul_cases(golden):
     for mm in golden["matmul"]:
         ca, cb = mm["cfg_a"], mm["cfg_b"]
-        if ca.get("dtype", "nvfp4") != "nvfp4":
-            continue
         out = fos.quantized_matmul(mm["a"].to(DEV), mm["b"].to(DEV), input_config=fos.QuantizationConfig(**ca),
                                    other_config=fos.QuantizationConfig(**cb), check_status=True)
         want = mm["out_bf16"]
@@ -180,9 +180,43 @@ def test_full_size_configs(name, m, n, k, rule):
     cfg = fos.QuantizationConfig(scale_rule=rule)
     qa, qb = fos.quantize(a.bfloat16().to(DEV), cfg), fos.quantize(b.bfloat16().to(DEV), cfg)
     out = B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType.bfloat16, check_status=True)
-    _check(out, _dense_reference(qa, qb), name)
+    _check(out, _dense_reference(qa, qb), name, mismatch_scale=(k / 1024) ** 0.5)
     # linearity in alpha: doubling one operand's amax doubles every output exactly (power of two)
     qa2 = fos.QuantizedTensor(qa.values, qa.scale_factors, qa.amax * 2, qa.dtype, qa.original_shape,
                               qa.scale_rule, qa.round_style, qa.padded_shape)
     out2 = B200MatmulBackend.quantized_matmul(qa2, qb, out_dtype=fos.DataType.bfloat16, check_status=True)
     assert torch.equal(out2.float(), out.float() * 2)
+
+
+@pytest.mark.parametrize(("m", "n", "k"), [(256, 256, 256), (512, 256, 1024), (100, 72, 80), (384, 640, 448)])
+@pytest.mark.parametrize(("dtype_a", "dtype_b"), [("if4", "if4"), ("if4", "nvfp4"), ("nvfp4", "if4")])
+def test_if4_matmul_against_oracle(oracle, m, n, k, dtype_a, dtype_b):
+    """IF4 operands (and IF4 x NVFP4 mixes) go through the expand-to-fp16 GEMM."""
+    g = torch.Generator().manual_seed(17)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    y = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    ca, cb = fos.QuantizationConfig(dtype=dtype_a), fos.QuantizationConfig(dtype=dtype_b)
+    qx, qy = fos.quantize(x.to(DEV), ca), fos.quantize(y.to(DEV), cb)
+    out = B200MatmulBackend.quantized_matmul(qx, qy, out_dtype=fos.DataType.bfloat16, check_status=True)
+    want = oracle.matmul(oracle.quantize(x, dtype=dtype_a), oracle.quantize(y, dtype=dtype_b), torch.bfloat16)
+    torch.cuda.synchronize()
+    frac = (out.cpu() != want).float().mean().item()
+    assert frac <= MISMATCH_TOLERANCE, f"{frac:.3%} of outputs differ from the oracle"
+    _check(out, _dense_reference(qx, qy), f"if4 {m}x{n}x{k} {dtype_a}x{dtype_b}")
+    out32 = B200MatmulBackend.quantized_matmul(qx, qy, out_dtype=fos.DataType.float32, check_status=True)
+    ref32 = _dense_reference(qx, qy)
+    assert ((out32 - ref32).abs().max() / ref32.abs().max()).item() < 1e-5
+
+
+@pytest.mark.parametrize("name,tokens,k,n", [("c3-up-gate", 4096, 4096, 14336), ("c3-down", 4096, 14336, 4096)])
+def test_if4_llama_mlp_shapes(name, tokens, k, n):
+    """IF4 quantize + GEMM on Llama-3-8B MLP shapes: Student-t(4)*0.5 activations, N(0, 0.02^2) weights."""
+    g = torch.Generator().manual_seed(5)
+    z = torch.randn(tokens, k, generator=g)
+    chi = (torch.randn(4, tokens, k, generator=g) ** 2).sum(0)
+    x = (0.5 * z / (chi / 4).sqrt()).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.02).bfloat16().to(DEV)
+    cfg = fos.QuantizationConfig(dtype="if4")
+    qx, qw = fos.quantize(x, cfg), fos.quantize(w, cfg)
+    out = B200MatmulBackend.quantized_matmul(qx, qw, out_dtype=fos.DataType.bfloat16, check_status=True)
+    _check(out, _dense_reference(qx, qw), name, mismatch_scale=(k / 1024) ** 0.5)

@@ -1,0 +1,126 @@
+"""`FourOverSixLinear` and `quantize_model` on the GPU: forward, backward, packed buffers.
+
+The layer only orchestrates `quantize` and `quantized_matmul` (both checked against the
+oracle elsewhere), so these tests check the orchestration: which operand is quantized how,
+which transposes are taken, that the packed state dict round-trips, and that the result is
+what the reference's formulas give when evaluated with dequantized operands.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+import torch.nn as nn
+
+import fouroversix_b200 as fos
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _fp32_matmul(a, b):
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        return a.float() @ b.float()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def _close(out, ref32, tol=1e-2):
+    rel = ((out.float() - ref32).abs().max() / ref32.abs().max().clamp_min(1e-30)).item()
+    assert rel <= tol, rel
+
+
+def test_ptq_linear_forward_matches_dequantized_matmul():
+    torch.manual_seed(0)
+    lin = nn.Linear(512, 384, bias=True, device=DEV, dtype=torch.bfloat16)
+    w, b = lin.weight.data.clone(), lin.bias.data.clone()
+    q = fos.FourOverSixLinear(lin, fos.ModuleQuantizationConfig()).quantize_weight_()
+    assert q.weight is None and int(q.quantized_weight_metadata[0]) == 384
+    x = torch.randn(3, 40, 512, device=DEV, dtype=torch.bfloat16)
+    y = q(x)
+    assert y.shape == (3, 40, 384) and y.dtype == torch.bfloat16
+    xq = fos.dequantize(fos.quantize(x.reshape(-1, 512)), torch.float32)
+    wq = fos.dequantize(fos.quantize(w), torch.float32)
+    ref = (_fp32_matmul(xq, wq.T) + b.float()).reshape(3, 40, 384)
+    _close(y, ref)
+    assert torch.equal(q.dequantized_weight(torch.float32), wq)
+
+
+def test_packed_state_dict_round_trips_between_modules():
+    torch.manual_seed(1)
+    src = fos.FourOverSixLinear(nn.Linear(256, 128, bias=False, device=DEV, dtype=torch.bfloat16),
+                                fos.ModuleQuantizationConfig(scale_rule="static_6")).quantize_weight_()
+    sd = {k: v for k, v in src.state_dict().items() if k.startswith("quantized_")}
+    assert set(sd) == {"quantized_weight_values", "quantized_weight_scale_factors", "quantized_weight_amax",
+                       "quantized_weight_metadata"}
+    dst = fos.FourOverSixLinear(nn.Linear(256, 128, bias=False, device=DEV, dtype=torch.bfloat16),
+                                fos.ModuleQuantizationConfig(scale_rule="static_6"))
+    dst.weight = None
+    dst.load_state_dict(sd, strict=False)
+    x = torch.randn(64, 256, device=DEV, dtype=torch.bfloat16)
+    assert torch.equal(src(x), dst(x))
+
+
+def test_quantize_model_on_a_small_mlp_stack():
+    torch.manual_seed(2)
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.up, self.gate, self.down = nn.Linear(256, 512, bias=False), nn.Linear(256, 512, bias=False), \
+                nn.Linear(512, 256, bias=False)
+
+        def forward(self, x):
+            return self.down(torch.nn.functional.silu(self.gate(x)) * self.up(x))
+
+    model = nn.Sequential(Block(), Block()).to(DEV, torch.bfloat16)
+    model.add_module("lm_head", nn.Linear(256, 100, bias=False, device=DEV, dtype=torch.bfloat16))
+    x = torch.randn(2, 128, 256, device=DEV, dtype=torch.bfloat16)
+    want = model(x)
+    fos.quantize_model(model, fos.ModelQuantizationConfig(keep_master_weights=True))
+    assert all(isinstance(m, fos.FourOverSixLinear) for m in (model[0].up, model[0].gate, model[0].down, model[1].down))
+    assert not isinstance(model.lm_head, fos.FourOverSixLinear)
+    got = model(x)
+    # FP4 on both operands of six GEMMs and two gated non-linearities: the output keeps its direction
+    # (cosine similarity) but carries tens of percent of quantization noise
+    cos = torch.nn.functional.cosine_similarity(got.float().flatten(), want.float().flatten(), dim=0).item()
+    assert cos > 0.85, cos
+    assert torch.isfinite(got.float()).all()
+
+
+@pytest.mark.parametrize("tokens,k,n", [(256, 256, 384), (4096, 4096, 4096)])
+def test_training_forward_dgrad_wgrad(tokens, k, n):
+    """keep_master_weights + 2-D weight blocks + nearest gradient rounding: the three FP4 GEMMs of a
+    step equal the formulas evaluated on dequantized operands (the transposed quantizations included)."""
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(1, tokens, k, generator=g).bfloat16().to(DEV).requires_grad_(True)
+    lin = nn.Linear(k, n, bias=False, device=DEV, dtype=torch.bfloat16)
+    with torch.no_grad():
+        lin.weight.copy_((torch.randn(n, k, generator=g) * 0.02).bfloat16())
+    dy = (torch.randn(1, tokens, n, generator=g) * 1e-3).bfloat16().to(DEV)
+    cfg = fos.ModuleQuantizationConfig(keep_master_weights=True, weight_scale_2d=True, gradient_round_style="nearest")
+    layer = fos.FourOverSixLinear(lin, cfg)
+    y = layer(x)
+    y.backward(dy)
+
+    x2, dy2, w = x.detach().reshape(tokens, k), dy.reshape(tokens, n), lin.weight.data
+    deq = lambda t, **c: fos.dequantize(fos.quantize(t, fos.QuantizationConfig(**c)), torch.float32)  # noqa: E731
+    w_q = deq(w, block_scale_2d=True)
+    _close(y.reshape(tokens, n), _fp32_matmul(deq(x2), w_q.T))
+    # dgrad: q(dy) @ q(W^T)^T ; with 16x16 blocks q(W^T) == q(W)^T
+    wt_q = deq(w, block_scale_2d=True, transpose=True)
+    assert torch.equal(wt_q, w_q.T)
+    _close(x.grad.reshape(tokens, k), _fp32_matmul(deq(dy2), wt_q.T))
+    # wgrad: q(dy^T) @ q(x^T)^T
+    _close(lin.weight.grad, _fp32_matmul(deq(dy2, transpose=True), deq(x2, transpose=True).T))
+
+
+def test_stochastic_gradient_rounding_is_refused_clearly():
+    lin = nn.Linear(128, 128, bias=False, device=DEV, dtype=torch.bfloat16)
+    layer = fos.FourOverSixLinear(lin, fos.ModuleQuantizationConfig(keep_master_weights=True))
+    x = torch.randn(1, 128, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    with pytest.raises(NotImplementedError, match="stochastic"):
+        layer(x).sum().backward()
