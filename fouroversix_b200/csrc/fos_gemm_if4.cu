@@ -17,6 +17,8 @@
 //
 // Expanding once per operand instead of inside the GEMM's producer costs 2 * 2 B per element of
 // extra HBM traffic but decodes every element once rather than once per tile that uses it.
+#include <mutex>
+
 #include "fos_tcgen05.cuh"
 
 namespace fos {
@@ -280,6 +282,10 @@ extern "C" int64_t fos_gemm_if4_workspace_bytes(int64_t m_p, int64_t n_p, int64_
 namespace fos {
 namespace {
 
+// Scratch for fos_gemm_if4_static: lives in the library image, one copy per GPU that loads it.
+constexpr int64_t STATIC_WORKSPACE_BYTES = int64_t(FOS_GEMM_IF4_STATIC_WORKSPACE_BYTES);
+static __device__ __align__(256) unsigned char g_static_workspace[STATIC_WORKSPACE_BYTES];
+
 // Validates the arguments shared by both entry points, expands both operands into `workspace`
 // and runs the fp16 GEMM. Allocates nothing.
 int gemm_if4_impl(const uint8_t *a_codes, const uint8_t *a_sf, int a_format, int a_sf_layout, const uint8_t *b_codes,
@@ -333,6 +339,40 @@ extern "C" int fos_gemm_if4(const uint8_t *a_codes, const uint8_t *a_sf, int a_f
     if (!workspace || workspace_bytes < fos_gemm_if4_workspace_bytes(m_p, n_p, k_p)) return FOS_ERR_INVALID_ARGUMENT;
     if (reinterpret_cast<uintptr_t>(workspace) % 128) return FOS_ERR_MISALIGNED;
     if ((st = check_device()) != FOS_OK) return st;
+    return gemm_if4_impl(a_codes, a_sf, a_format, a_sf_layout, b_codes, b_sf, b_format, b_sf_layout, alpha, d, out_dtype,
+                         m_p, n_p, k_p, m, n, ldd, workspace, status, static_cast<cudaStream_t>(stream_));
+}
+
+// fos_gemm_if4 for callers that cannot hand over scratch memory: the expanded operands go into
+// g_static_workspace. The array's name is a host-side handle, not a device address, so the
+// address is asked for once per device (with that device current) and cached; that first call
+// is the only set-up and should happen outside any stream capture.
+extern "C" int fos_gemm_if4_static(const uint8_t *a_codes, const uint8_t *a_sf, int a_format, int a_sf_layout,
+                                   const uint8_t *b_codes, const uint8_t *b_sf, int b_format, int b_sf_layout,
+                                   const float *alpha, void *d, int out_dtype, int64_t m_p, int64_t n_p, int64_t k_p,
+                                   int64_t m, int64_t n, int64_t ldd, int32_t *status, void *stream_) {
+    using namespace fos;
+    int st = check_gemm_if4_args(a_codes, a_sf, a_format, a_sf_layout, b_codes, b_sf, b_format, b_sf_layout, alpha, d,
+                                 out_dtype, m_p, n_p, k_p, m, n, ldd);
+    if (st != FOS_OK) return st;
+    if (fos_gemm_if4_workspace_bytes(m_p, n_p, k_p) > STATIC_WORKSPACE_BYTES) return FOS_ERR_TOO_LARGE;
+    if ((st = check_device()) != FOS_OK) return st;
+
+    static void *device_address[64] = {};
+    static std::mutex setup_lock;
+    int dev = 0;
+    FOS_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return FOS_ERR_UNSUPPORTED;
+    void *workspace = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(setup_lock);
+        if (device_address[dev] == nullptr) {
+            void *ptr = nullptr;
+            FOS_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_workspace));
+            device_address[dev] = ptr;
+        }
+        workspace = device_address[dev];
+    }
     return gemm_if4_impl(a_codes, a_sf, a_format, a_sf_layout, b_codes, b_sf, b_format, b_sf_layout, alpha, d, out_dtype,
                          m_p, n_p, k_p, m, n, ldd, workspace, status, static_cast<cudaStream_t>(stream_));
 }

@@ -153,6 +153,29 @@ int fos_gemm_if4(const uint8_t *a_codes, const uint8_t *a_sf, int a_format, int 
                  int32_t *status, void *stream);
 
 /*
+ * fos_gemm_if4 without a workspace argument, for callers that have no way to obtain device
+ * scratch: code that runs where allocating is forbidden or impossible - inside a host callback
+ * or another library's plug-in hook, under a memory pool that is already fully handed out, or in
+ * a process whose allocator belongs to a different runtime. The expanded fp16 operands are kept
+ * in a buffer of FOS_GEMM_IF4_STATIC_WORKSPACE_BYTES that is part of the library image (each GPU
+ * that loads the library holds that much memory until the process exits). The caller still passes
+ * every input and output; the call performs no cudaMalloc / cudaFree and uses no allocating
+ * library routine.
+ *   - Limit: (m_p + n_p) * k_p * 2 <= FOS_GEMM_IF4_STATIC_WORKSPACE_BYTES, else FOS_ERR_TOO_LARGE.
+ *   - The first call on a device looks up the buffer's device address (a one-time host-side
+ *     set-up with that device current); make that first call outside any stream capture.
+ *   - All calls on a device share the one buffer. It holds nothing between calls (every byte a
+ *     call reads was written by that call), but two calls whose kernels overlap on the GPU, e.g.
+ *     on different streams, overwrite each other's operands: serialise them.
+ * No counterpart in the reference.
+ */
+#define FOS_GEMM_IF4_STATIC_WORKSPACE_BYTES (32 * 1024 * 1024)
+int fos_gemm_if4_static(const uint8_t *a_codes, const uint8_t *a_sf, int a_format, int a_sf_layout,
+                        const uint8_t *b_codes, const uint8_t *b_sf, int b_format, int b_sf_layout,
+                        const float *alpha, void *d, int out_dtype, int64_t m_p, int64_t n_p, int64_t k_p,
+                        int64_t m, int64_t n, int64_t ldd, int32_t *status, void *stream);
+
+/*
  * Process-wide tuning / testing knobs. No counterpart in the reference.
  *   FOS_OPT_GEMM_VARIANT   0 = choose the GEMM kernel per problem (default);
  *                          128 / 256 = single-CTA kernel with 128 x 128 / 128 x 256 tiles;
