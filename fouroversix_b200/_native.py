@@ -40,6 +40,7 @@ SIGNATURES = {
     "fos_gemm_if4_static": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int,
                                      _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
     "fos_set_option": (_c_int, [_c_int, _c_int]),
+    "fos_wait_failure_site": (_c_int, [_c_ptr]),
 }
 
 

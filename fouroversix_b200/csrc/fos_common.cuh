@@ -16,6 +16,8 @@ namespace fos {
 
 // Records a failed runtime call for fos_last_cuda_error() and maps it to FOS_ERR_CUDA.
 int note_cuda_error(cudaError_t e);
+// FOS_OPT_QUANTIZE_VARIANT: 0 = pick the kernel by the input's alignment, 1 = never the TMA-fed kernel.
+extern int g_quantize_variant;
 // FOS_OK when the current device is compute capability 10.x, else FOS_ERR_ARCH / FOS_ERR_CUDA.
 int check_device();
 

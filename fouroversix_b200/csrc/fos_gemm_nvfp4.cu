@@ -679,6 +679,10 @@ extern "C" int fos_set_option(int key, int value) {
         fos::g_gemm_debug = value;
         return FOS_OK;
     }
+    if (key == FOS_OPT_QUANTIZE_VARIANT && (value == 0 || value == 1)) {
+        fos::g_quantize_variant = value;
+        return FOS_OK;
+    }
     return FOS_ERR_INVALID_ARGUMENT;
 }
 

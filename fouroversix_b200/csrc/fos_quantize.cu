@@ -13,9 +13,12 @@
 // when the two error sums differ by more than a proven bound on its own inaccuracy,
 // otherwise the block is re-evaluated with the exact sequence. The result is therefore
 // identical to always running the exact sequence.
-#include "fos_common.cuh"
+#include "fos_tcgen05.cuh"
 
 namespace fos {
+
+int g_quantize_variant = 0;   // FOS_OPT_QUANTIZE_VARIANT
+
 namespace {
 
 constexpr int KIND_STATIC = 0;    // NVFP4, one candidate (static_6 / static_4)
@@ -39,7 +42,12 @@ struct QuantParams {
     int sf_tiled;
     int exact_only;
     int vec_bytes;               // 32, 16 or 0: widest aligned load usable on x
+    int x_is_ready;              // x was complete before the previous kernel in the stream started
 };
+
+// Site of the first bounded wait that gave up, 0 if none did (never expected to change).
+__device__ int32_t g_wait_failures = 0;
+
 
 // ------------------------------------------------------------------------------------
 // per-tensor amax
@@ -341,9 +349,10 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
         // without underflow. In units of G = s*amax/1536 the reference's error term is
         // (deq - x)/G = t + eta with |eta| <= 47 ulp(1) (two roundings in deq, five between x*r
         // and x/G, |q| <= 6, |x*r| <= 6.4), so its sum differs from G^2 * sum(t^2) by at most
-        // 2 * 47u * sum|t| * G^2 <= 376u * sqrt(sum t^2) * G^2 (Cauchy-Schwarz over 16 terms) plus
-        // 40u relative for the roundings of the two summations. `tau` is 1.5 times that, for
-        // both candidates together; a difference inside tau is re-decided exactly below.
+        // 2 * 47u * sum|t| * G^2 <= 376u * sqrt(sum t^2) * G^2 (Cauchy-Schwarz over 16 terms)
+        // <= 188u * (sum t^2 + 1) * G^2 (arithmetic over geometric mean), plus 40u relative for the
+        // roundings of the two summations. `tau` is 1.5 times that, for both candidates
+        // together; a difference inside tau is re-decided exactly below.
         const bool eligible = !TWO_D && rule == FOS_RULE_MSE && !exact_only && sfb_a >= 8u && sfb_b >= 8u &&
                               tc.filter_ok && r_a >= 0x1p-16f && r_b >= 0x1p-16f;
         bool decided = false, pick_b = false;
@@ -368,8 +377,7 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
             unpack2f(acc_b, b0, b1);
             const float sum_a = a0 + a1, sum_b = b0 + b1;                 // sum of t^2, scaled units
             const float err_a = sum_a * ea.w, err_b = sum_b * eb.w;       // times G^2
-            const float tau = 0x1p-24f * 1.5f *
-                              (376.0f * (sqrtf(sum_a) * ea.w + sqrtf(sum_b) * eb.w) + 40.0f * (err_a + err_b));
+            const float tau = 0x1p-24f * 1.5f * (228.0f * (err_a + err_b) + 188.0f * (ea.w + eb.w));
             const float diff = err_b - err_a;
             decided = fabsf(diff) > tau;
             pick_b = diff < 0.0f;
@@ -621,8 +629,214 @@ quantize_rows_kernel(const QuantParams p) {
     }
 }
 
+
+// ------------------------------------------------------------------------------------
+// the common case, fed by the TMA unit
+// ------------------------------------------------------------------------------------
+//
+// Same arithmetic and thread-to-block assignment as quantize_rows_kernel, but x arrives through a
+// ring of shared-memory stages filled by bulk tensor copies: one producer thread keeps
+// FEED_STAGES tiles of 128 rows x 64 columns (16 KB each) in flight per CTA whatever the
+// occupancy, the copy engine zero-fills what lies outside x (so ragged shapes cost nothing), and
+// the 256 consumer threads spend no instructions on global addresses or bounds. Consumer lane
+// l of warp w owns rows 8w + l/4 and 64 + 8w + l/4 of the tile and block column l%4; with the
+// 128-byte swizzle the two 16-byte pieces of a block sit at chunk (2*(l%4) + h) ^ (l/4) of
+// the row, which makes every quarter-warp read 128 distinct bytes (no bank conflicts).
+//
+// Needs x 16-byte aligned with a row stride that is a multiple of 16 bytes.
+
+constexpr int FEED_TILE_ROWS = 128;
+constexpr int FEED_STAGES = 4;
+constexpr int FEED_STAGE_BYTES = FEED_TILE_ROWS * 128;
+constexpr int FEED_CONSUMERS = 256;
+constexpr int FEED_THREADS = FEED_CONSUMERS + 32;
+constexpr int FEED_SMEM_BYTES = FEED_STAGES * FEED_STAGE_BYTES + 1024;
+
+template <typename T, int KIND>
+__global__ void __launch_bounds__(FEED_THREADS, 3)
+quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantParams p) {
+    extern __shared__ uint8_t feed_smem_raw[];
+    __shared__ float4 lut[128];
+    __shared__ __align__(16) float coop[FEED_CONSUMERS / 32][20];
+    __shared__ __align__(8) uint64_t full_bar[FEED_STAGES], empty_bar[FEED_STAGES];
+    __shared__ int abort_flag;
+
+    const uint32_t stage0 = (smem_u32(feed_smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_c = static_cast<int>(p.cols_p >> 6), tiles_r = static_cast<int>(p.rows_p >> 7);
+    const int64_t n_tiles = static_cast<int64_t>(tiles_c) * tiles_r;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+#pragma unroll
+        for (int s = 0; s < FEED_STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), FEED_CONSUMERS / 32);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ... in row-major tile order
+    const int step_r = static_cast<int>(gridDim.x) / tiles_c, step_c = static_cast<int>(gridDim.x) % tiles_c;
+    int tr = static_cast<int>(blockIdx.x) / tiles_c, tc_ = static_cast<int>(blockIdx.x) % tiles_c;
+    const int my_tiles = static_cast<int>((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
+
+    if (warp == FEED_CONSUMERS / 32) {
+        // ---------------- producer ----------------
+        if (lane != 0) return;
+        // x may be the output of the previous kernel in the stream unless the caller knows better
+        if (!p.x_is_ready) asm volatile("griddepcontrol.wait;" ::: "memory");
+        int issued = 0, s = 0;
+        uint32_t parity = 1;   // of the "stage is free" barrier; the first round finds every stage free
+        for (; issued < my_tiles; ++issued) {
+            if (issued >= FEED_STAGES && !mbar_wait(smem_u32(&empty_bar[s]), parity, &abort_flag, &g_wait_failures, 1))
+                break;
+            mbar_expect_tx(smem_u32(&full_bar[s]), FEED_STAGE_BYTES);
+            tma_load_2d(stage0 + s * FEED_STAGE_BYTES, &map_x, tc_ * 128, tr * FEED_TILE_ROWS, smem_u32(&full_bar[s]));
+            if (++s == FEED_STAGES) { s = 0; parity ^= 1u; }
+            tr += step_r;
+            tc_ += step_c;
+            if (tc_ >= tiles_c) { tc_ -= tiles_c; ++tr; }
+        }
+        // stay until every copy this thread issued has landed: shared memory must outlive them
+        for (int j = issued > FEED_STAGES ? issued - FEED_STAGES : 0; j < issued; ++j) {
+            const uint32_t bar = smem_u32(&full_bar[j % FEED_STAGES]);
+            const uint32_t landed = static_cast<uint32_t>(j / FEED_STAGES) & 1u;
+            const unsigned long long t0 = global_timer_ns();
+            while (!mbar_try_wait(bar, landed) && global_timer_ns() - t0 < WAIT_LIMIT_NS) {}
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    // amax comes from the previous kernel in the stream; with programmatic dependent launch this
+    // CTA may be running before that kernel has finished.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(p.amax), p.rule);
+    if (threadIdx.x < 128) lut[threadIdx.x] = scale_entry(threadIdx.x, tc);
+    asm volatile("bar.sync 1, %0;" ::"n"(FEED_CONSUMERS) : "memory");
+
+    // What depends on the thread alone is computed here once. The empty asm statements make these
+    // values opaque, so that they stay in registers: left alone, the compiler recomputes them
+    // for every block (dozens of integer instructions) to save those registers.
+    const int q = lane >> 2, cb = lane & 3;
+    const int64_t code_ld = p.cols_p >> 1, n_cb = p.cols_p >> 4;
+    uint32_t piece0 = stage0 + static_cast<uint32_t>((warp * 8 + q) * 128 + ((2 * cb) ^ q) * 16);
+    uint32_t piece1 = stage0 + static_cast<uint32_t>((warp * 8 + q) * 128 + ((2 * cb + 1) ^ q) * 16);
+    uint8_t *code_ptr = p.codes + (warp * 8 + q) * code_ld + cb * 8;
+    uint8_t *sf_ptr = p.sf + (p.sf_tiled ? ((warp & 3) * 8 + q) * 16 + (warp >> 2) * 4 + cb : (warp * 8 + q) * n_cb + cb);
+    asm volatile("" : "+r"(piece0), "+r"(piece1), "+l"(code_ptr), "+l"(sf_ptr));
+
+    // offsets of the tile (uniform over the CTA), advanced without multiplications
+    const int64_t code_half = 64 * code_ld, sf_half = p.sf_tiled ? 8 : 64 * n_cb;
+    const int64_t code_step = static_cast<int64_t>(step_r) * 128 * code_ld + step_c * 32, code_wrap = 127 * code_ld;
+    const int64_t sf_step = p.sf_tiled ? static_cast<int64_t>(gridDim.x) * 512 : static_cast<int64_t>(step_r) * 128 * n_cb + step_c * 4;
+    const int64_t sf_wrap = p.sf_tiled ? 0 : 127 * n_cb;
+    int64_t code_off = static_cast<int64_t>(tr) * 128 * code_ld + tc_ * 32;
+    int64_t sf_off = p.sf_tiled ? static_cast<int64_t>(blockIdx.x) * 512 : static_cast<int64_t>(tr) * 128 * n_cb + tc_ * 4;
+
+    int s = 0;
+    uint32_t parity = 0;
+    for (int k = 0; k < my_tiles; ++k) {
+        if (!mbar_wait(smem_u32(&full_bar[s]), parity, &abort_flag, &g_wait_failures, 2)) break;
+        uint8_t *codes = code_ptr + code_off;
+        uint8_t *sf = sf_ptr + sf_off;
+        const uint32_t stage = s * FEED_STAGE_BYTES;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint4 a = lds_16(piece0 + stage + j * 64 * 128), b = lds_16(piece1 + stage + j * 64 * 128);
+            const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 f = unpack2<T>(w[i]);
+                v[2 * i] = f.x;
+                v[2 * i + 1] = f.y;
+            }
+            uint32_t lo, hi, sf_byte;
+            quantize_block<KIND, false, false>(v, tc, p.rule, p.exact_only != 0, nullptr, lane, lut, coop[warp], lo, hi, sf_byte);
+            *reinterpret_cast<uint2 *>(codes + j * code_half) = make_uint2(lo, hi);
+            sf[j * sf_half] = static_cast<uint8_t>(sf_byte);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));
+        if (++s == FEED_STAGES) { s = 0; parity ^= 1u; }
+        code_off += code_step;
+        sf_off += sf_step;
+        tc_ += step_c;
+        if (tc_ >= tiles_c) {
+            tc_ -= tiles_c;
+            code_off += code_wrap;
+            sf_off += sf_wrap;
+        }
+    }
+}
+
+// Tensor map over x as bytes: [rows][cols * 2] with a row pitch of ld * 2, boxes of 128 rows x 128 bytes.
+inline bool make_x_map(CUtensorMap *map, const QuantParams &p) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.cols * 2), static_cast<cuuint64_t>(p.rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.ld * 2)};
+    cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(FEED_TILE_ROWS)};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(p.x), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Launches the TMA-fed kernel when x qualifies; *launched tells whether it did.
+template <typename T, int KIND>
+cudaError_t launch_rows_tma(const QuantParams &p, cudaStream_t stream, bool *launched) {
+    *launched = false;
+    if (reinterpret_cast<uintptr_t>(p.x) % 16 != 0 || (p.ld * 2) % 16 != 0) return cudaSuccess;
+    if (p.cols * 2 >= (int64_t(1) << 31) || p.rows >= (int64_t(1) << 31) || p.ld * 2 >= (int64_t(1) << 40)) return cudaSuccess;
+    CUtensorMap map;
+    if (!make_x_map(&map, p)) return cudaSuccess;
+    auto kernel = quantize_rows_tma_kernel<T, KIND>;
+    static int ctas_per_sm[64] = {};
+    static int sm_count[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const int slot = (dev >= 0 && dev < 64) ? dev : 0;
+    if (ctas_per_sm[slot] == 0) {
+        int n = 0, sms = 0;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FEED_SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, FEED_THREADS, FEED_SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+        sm_count[slot] = sms;
+        ctas_per_sm[slot] = n > 0 ? n : 1;
+    }
+    const int64_t n_tiles = (p.rows_p >> 7) * (p.cols_p >> 6);
+    int64_t grid = static_cast<int64_t>(ctas_per_sm[slot]) * sm_count[slot];
+    if (grid > n_tiles) grid = n_tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(FEED_THREADS);
+    cfg.dynamicSmemBytes = FEED_SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kernel, map, p);
+    if (e == cudaSuccess) *launched = true;
+    return e;
+}
+
 template <typename T, int KIND>
 cudaError_t launch_rows(const QuantParams &p, cudaStream_t stream) {
+    if (g_quantize_variant != 1) {
+        bool launched = false;
+        const cudaError_t e = launch_rows_tma<T, KIND>(p, stream, &launched);
+        if (e != cudaSuccess || launched) return e;
+    }
     auto kernel = quantize_rows_kernel<T, KIND>;
     static int ctas_per_sm[64] = {};
     static int sm_count[64] = {};
@@ -736,10 +950,19 @@ extern "C" int fos_quantize(const void *x, int x_dtype, int64_t rows, int64_t co
                          : launch_amax<__half>(x, rows, cols, ld, vec16, amax_out, stream));
     }
     p.amax = amax_out;
+    // When this call launched the amax pass itself, the kernel before the quantize kernel is that
+    // pass: it does not write x, so x can be fetched while it drains.
+    p.x_is_ready = amax_in == nullptr;
 
     const int kind = format == FOS_IF4 ? KIND_IF4 : (is_static ? KIND_STATIC : KIND_ADAPTIVE);
     FOS_CUDA_TRY(x_dtype == FOS_BF16
                      ? launch_all<__nv_bfloat16>(p, kind, block_2d != 0, transpose != 0, stream)
                      : launch_all<__half>(p, kind, block_2d != 0, transpose != 0, stream));
+    return FOS_OK;
+}
+
+extern "C" int fos_wait_failure_site(int32_t *site) {
+    if (!site) return FOS_ERR_INVALID_ARGUMENT;
+    FOS_CUDA_TRY(cudaMemcpyFromSymbol(site, fos::g_wait_failures, sizeof(int32_t)));
     return FOS_OK;
 }

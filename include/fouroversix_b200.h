@@ -184,10 +184,22 @@ int fos_gemm_if4_static(const uint8_t *a_codes, const uint8_t *a_sf, int a_forma
  *   FOS_OPT_GEMM_DEBUG     timing experiments that make the GEMM's RESULT WRONG: bit 0 skips the
  *                          scale copies, bit 1 the operand loads, bit 2 the output stores.
  *                          Default 0. Only the profiling scripts set it.
+ *   FOS_OPT_QUANTIZE_VARIANT  0 = 1-D, untransposed inputs that are 16-byte aligned (base and row
+ *                          stride) go through the kernel fed by the TMA unit, the rest through
+ *                          the kernel that loads from registers (default); 1 = never the
+ *                          TMA-fed kernel. Both produce the same bytes.
  */
 #define FOS_OPT_GEMM_VARIANT 1
 #define FOS_OPT_GEMM_DEBUG 2
+#define FOS_OPT_QUANTIZE_VARIANT 3
 int fos_set_option(int key, int value);
+
+/*
+ * Diagnostics for the quantize kernels, which have no status argument: *site (host memory)
+ * receives 0, or a small positive number naming the first bounded device-side wait that ever
+ * gave up on the current device. Synchronises the device. No counterpart in the reference.
+ */
+int fos_wait_failure_site(int32_t *site);
 
 #ifdef __cplusplus
 }

@@ -163,3 +163,38 @@ def test_full_size_configs_bit_exact(oracle, name, shape, seed, cfg):
     back = fos.dequantize(q, torch.float32).cpu()
     xf = x.float().T if cfg.get("transpose") else x.float()
     assert (back - xf).abs().max() <= 0.26 * x.float().abs().max()
+
+
+@pytest.mark.parametrize("variant", [0, 1], ids=["tma-fed", "register-loads"])
+def test_both_row_kernels_match_the_oracle(oracle, variant):
+    """1-D untransposed inputs have two kernels (fed by the TMA unit / loading into registers);
+    both must give the reference's bytes, with and without a caller-supplied amax (the first
+    walks the tiles forwards, the second backwards), on full, ragged and tiny shapes."""
+    import ctypes
+
+    from fouroversix_b200 import _native
+
+    lib = _native.lib()
+    g = torch.Generator().manual_seed(21)
+    shapes = [(8, 16), (100, 80), (129, 72), (128, 64), (640, 4096), (1000, 328), (257, 8200)]
+    assert lib.fos_set_option(3, variant) == 0
+    try:
+        for shape in shapes:
+            x = torch.randn(shape, generator=g).bfloat16()
+            x[:, :: 7] *= 9.0
+            xd = x.to(DEV)
+            amax = xd.abs().max().float().reshape(1)
+            for cfg in (dict(), dict(scale_rule="static_6"), dict(scale_rule="static_4"), dict(scale_rule="mae"),
+                        dict(scale_rule="abs_max"), dict(dtype="if4")):
+                ref = oracle.quantize(x, **cfg)
+                for given in (None, amax):
+                    q = B200QuantizeBackend.quantize(xd, fos.QuantizationConfig(**cfg), amax=given)
+                    _assert_same(q, ref.values, ref.scale_factors, ref.amax, f"{shape} {cfg} amax given={given is not None}")
+        xh = torch.randn(300, 264, generator=g).half()
+        ref = oracle.quantize(xh)
+        q = fos.quantize(xh.to(DEV), fos.QuantizationConfig())
+        _assert_same(q, ref.values, ref.scale_factors, ref.amax, "fp16 300x264")
+    finally:
+        lib.fos_set_option(3, 0)
+    site = ctypes.c_int32(-1)
+    assert lib.fos_wait_failure_site(ctypes.byref(site)) == 0 and site.value == 0
