@@ -25,6 +25,7 @@ NVCC_FLAGS = [
     "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
+    *os.environ.get("FOS_NVCC_EXTRA", "").split(),   # e.g. -DFOS_FEED_STAGES=3 for tuning experiments
 ]
 
 

@@ -84,6 +84,13 @@ __device__ __forceinline__ uint32_t cvt_e4m3(float x) {
     return r & 0xffu;
 }
 
+// Two floats -> two E4M3 bytes, `hi` in bits 8..15.
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float hi, float lo) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
 __device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
     uint32_t h2;
     uint16_t b = static_cast<uint16_t>(byte & 0xffu);
@@ -130,6 +137,12 @@ __device__ __forceinline__ void ldg_nc_32(const void *p, uint32_t (&v)[8]) {
     asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                  : "l"(p));
+}
+
+// 32-byte store (sm_100 and later); `p` must be 32-byte aligned.
+__device__ __forceinline__ void stg_32(void *p, const uint32_t *v) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
 }
 
 template <typename T> __device__ __forceinline__ float elem_to_float(T v);

@@ -4,24 +4,36 @@
 // fos_quantize writes them (scales in 128-row x 4-block tiles of 512 bytes). The kernel
 // is persistent (one CTA per SM, static tile schedule) and warp specialised:
 //
-//   warp 0      one lane issues TMA loads of the A / B tiles (128-byte swizzle, no
-//               multicast) and plain bulk copies of the scale tiles into a ring of
-//               shared-memory stages guarded by full / empty mbarriers
+//   warp 0      one lane issues the TMA loads of the A / B tiles (128-byte swizzle, no multicast)
+//               into a ring of shared-memory stages guarded by full / empty mbarriers
+//   warp 15     one lane issues the TMA loads of the scale tiles (two tensor copies per stage)
+//               into a ring of its own, one slot longer than the operand ring and one stage
+//               ahead of it. A separate thread because a thread issues a copy every hundred
+//               cycles or so: with all copies of a stage on one thread, that thread set the pace.
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma kind::mxf4nvf4.block_scale
 //               (K = 64 per instruction) with the fp32 accumulator in tensor memory;
 //               tcgen05.commit releases the stage
 //   warps 2..9  epilogue: tcgen05.ld the accumulator (each warp owns the 32 lanes of its
 //               quadrant and half of the tile's columns), multiply by alpha, convert, store
-//               rows < m and columns < n; the accumulator is handed back to the MMA warp as
-//               soon as the last tcgen05.ld has landed, before the stores of that data
+//               rows < m and columns < n. 16-bit outputs are packed while they are read, so the
+//               warp's whole row segment sits in registers and the accumulator is handed back
+//               to the MMA warp before the first store; stores are 32 bytes per lane.
 //   warps 10..13 scale movers: copy each stage's scale tiles shared -> registers -> tensor
-//               memory (tcgen05.st) into a ring of scale columns, one slot per stage. A
+//               memory (tcgen05.st) into a ring of scale columns, one slot per scale stage. A
 //               512-byte scale tile is 32 rows of 16 bytes and every 32-lane quadrant of tensor
 //               memory needs the same 16 bytes per lane, so each of the four warps reads row
 //               `lane` and writes its own quadrant. (Issuing tcgen05.cp from the MMA thread
-//               instead serialises with the MMAs and cost 40 % of the run time when measured.)
+//               instead serialises with the MMAs and cost 40 % of the run time when measured;
+//               loading the scales from global memory in the mover warps made those warps the
+//               slowest role.)
+//   warp 14     spare (takes the B loads when built with FOS_GEMM_SPLIT_AB=1; no gain measured)
 //
-// Every mbarrier wait is bounded by a wall-clock limit. A wait that gives up records where
+// What bounds the kernel: the round trip "stage released -> reload issued -> data back from L2"
+// (about 1.4 us unloaded) against only four 48 KB stages of shared memory. Shorter stages do
+// not help: the single threads that issue copies and MMAs need a few hundred cycles per stage
+// whatever its size.
+//
+// Every mbarrier wait is bounded (in SM cycles). A wait that gives up records where
 // in *status, raises a CTA-wide abort flag, and all roles fall through to the common exit,
 // which lets in-flight copies land, releases tensor memory and returns.
 #include "fos_tcgen05.cuh"
@@ -35,7 +47,18 @@ constexpr int KB_PER_STAGE = 4;                    // MMA K-blocks (64 values, 3
 constexpr int SF_TILE_BYTES = 512;                 // scales of 128 rows x 64 values
 constexpr int A_BYTES = BLOCK_M * BLOCK_K_BYTES;   // 16 KiB
 constexpr int SFA_BYTES = KB_PER_STAGE * SF_TILE_BYTES;
-constexpr int NUM_THREADS = 448;                   // TMA, MMA, 8 epilogue warps, 4 scale-mover warps
+#ifndef FOS_GEMM_SF_LEAD
+#define FOS_GEMM_SF_LEAD 1
+#endif
+constexpr int SF_LEAD = FOS_GEMM_SF_LEAD;   // 0 or 1: how many stages the scales are requested ahead of the operands
+#ifndef FOS_GEMM_ST256
+#define FOS_GEMM_ST256 1
+#endif
+#ifndef FOS_GEMM_SPLIT_AB
+#define FOS_GEMM_SPLIT_AB 0
+#endif
+constexpr bool SPLIT_OPERAND_ISSUE = FOS_GEMM_SPLIT_AB != 0;
+constexpr int NUM_THREADS = 512;                   // TMA (A), MMA, 8 epilogue warps, 4 scale-mover warps, TMA (B), TMA (scales)
 constexpr int SF_COL0 = 256;                       // tensor-memory columns: accumulators first, then per
                                                    // stage 16 columns of A scales and N/8 of B scales
 
@@ -43,15 +66,22 @@ template <int BLOCK_N> struct Cfg {
     static constexpr int B_BYTES = BLOCK_N * BLOCK_K_BYTES;
     static constexpr int N_GROUPS = BLOCK_N / 128;                 // 128-row scale groups of B
     static constexpr int SFB_BYTES = N_GROUPS * KB_PER_STAGE * SF_TILE_BYTES;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;          // operand tiles of one stage
+    static constexpr int SF_SLOT_BYTES = SFA_BYTES + SFB_BYTES;    // scale tiles of one stage
     static constexpr int STAGES = BLOCK_N == 256 ? 4 : 6;
+    // The scales of a stage are requested one stage earlier than its operands and have a ring of
+    // their own (shared memory and tensor memory) with one slot more than there are stages.
+    static constexpr int SF_SLOTS = STAGES + SF_LEAD;
     static constexpr int ACC_STAGES = BLOCK_N == 256 ? 1 : 2;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int BARRIER_BYTES = 512;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SF_SLOTS * SF_SLOT_BYTES + 1024 /*alignment slack*/ + BARRIER_BYTES;
     static constexpr int SFB_COLS = KB_PER_STAGE * (BLOCK_N / 32);  // per stage
     static constexpr int SF_STAGE_COLS = 16 + SFB_COLS;
     static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
     static_assert(ACC_STAGES * BLOCK_N <= SF_COL0, "accumulators overlap the scale columns");
-    static_assert(SF_COL0 + STAGES * SF_STAGE_COLS <= TMEM_COLS, "scale ring does not fit tensor memory");
+    static_assert(SF_COL0 + SF_SLOTS * SF_STAGE_COLS <= TMEM_COLS, "scale ring does not fit tensor memory");
+    static_assert(SMEM_BYTES <= 232448, "more shared memory than a CTA can have");
+    static_assert((2 * STAGES + 2 * SF_SLOTS + 2 * ACC_STAGES) * 8 + 8 <= BARRIER_BYTES, "barrier area too small");
 };
 
 struct GemmParams {
@@ -100,31 +130,35 @@ __device__ __forceinline__ uint32_t mma_idesc(int n, int m = BLOCK_M) {
 template <int BLOCK_N, typename OUT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                   const GemmParams p) {
     using C = Cfg<BLOCK_N>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    // barriers live after the stages
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + C::STAGES * C::STAGE_BYTES);
-    const uint32_t full_bar = smem_u32(bars);                       // [STAGES]
-    const uint32_t empty_bar = full_bar + 8 * C::STAGES;            // [STAGES]
-    const uint32_t sf_full_bar = empty_bar + 8 * C::STAGES;         // [STAGES] scale tiles landed
-    const uint32_t sf_ready_bar = sf_full_bar + 8 * C::STAGES;      // [STAGES] scales are in tensor memory
-    const uint32_t acc_full_bar = sf_ready_bar + 8 * C::STAGES;     // [ACC_STAGES]
+    // shared memory: operand stages, scale slots, barriers
+    const uint32_t sf_base = smem_base + C::STAGES * C::STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + C::STAGES * C::STAGE_BYTES + C::SF_SLOTS * C::SF_SLOT_BYTES);
+    const uint32_t full_bar = smem_u32(bars);                       // [STAGES] operand tiles landed
+    const uint32_t empty_bar = full_bar + 8 * C::STAGES;            // [STAGES] the stage's MMAs are done
+    const uint32_t sf_full_bar = empty_bar + 8 * C::STAGES;         // [SF_SLOTS] scale tiles landed
+    const uint32_t sf_ready_bar = sf_full_bar + 8 * C::SF_SLOTS;    // [SF_SLOTS] scales are in tensor memory
+    const uint32_t acc_full_bar = sf_ready_bar + 8 * C::SF_SLOTS;   // [ACC_STAGES]
     const uint32_t acc_empty_bar = acc_full_bar + 8 * C::ACC_STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 4 * C::STAGES + 2 * C::ACC_STAGES);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::STAGES + 2 * C::SF_SLOTS + 2 * C::ACC_STAGES);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
-            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(full_bar + 8 * s, SPLIT_OPERAND_ISSUE ? 2 : 1);   // one arrival per operand producer
             mbar_init(empty_bar + 8 * s, 1);
-            mbar_init(sf_full_bar + 8 * s, 1);
-            mbar_init(sf_ready_bar + 8 * s, 4);    // one arrival per scale-mover warp
+        }
+        for (int j = 0; j < C::SF_SLOTS; ++j) {
+            mbar_init(sf_full_bar + 8 * j, 1);
+            mbar_init(sf_ready_bar + 8 * j, 4);    // one arrival per scale-mover warp
         }
         for (int a = 0; a < C::ACC_STAGES; ++a) {
             mbar_init(acc_full_bar + 8 * a, 1);
@@ -151,40 +185,27 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int64_t k_tiles = (k_blocks + KB_PER_STAGE - 1) / KB_PER_STAGE;
 
     const bool dbg_no_sf = p.debug & 1, dbg_no_load = p.debug & 2, dbg_no_store = p.debug & 4;
-    if (warp == 0 && lane == 0 && !dbg_no_load) {
-        // ------------------------------------------------------------------ TMA producer
-        uint32_t it = 0;
+    const bool dbg_no_mma = p.debug & 16;
+    if ((warp == 0 || (SPLIT_OPERAND_ISSUE && warp == 14)) && lane == 0 && !dbg_no_load) {
+        // ------------------------------------------------------------------ TMA producer(s): operands
+        // With SPLIT_OPERAND_ISSUE warp 0 loads A and warp 14 loads B; otherwise warp 0 loads both.
+        const bool do_a = warp == 0, do_b = !SPLIT_OPERAND_ISSUE || warp == 14;
+        const uint32_t bytes = (do_a ? A_BYTES : 0) + (do_b ? C::B_BYTES : 0);
+        uint32_t s = 0, ph = 0;
         bool ok = true;
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             int64_t mb, nb;
             tile_coords(t, num_m, num_n, mb, nb);
-            const int64_t m0 = mb * BLOCK_M, n0 = nb * BLOCK_N;
-            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
-                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+            const int m0 = static_cast<int>(mb * BLOCK_M), n0 = static_cast<int>(nb * BLOCK_N);
+            for (int64_t kt = 0; kt < k_tiles; ++kt) {
                 ok = mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 1);
                 if (!ok) break;
-                const int64_t kb0 = kt * KB_PER_STAGE;
-                const int nkb = static_cast<int>((k_blocks - kb0) < KB_PER_STAGE ? (k_blocks - kb0) : KB_PER_STAGE);
-                int groups = 0;
-                for (int g = 0; g < C::N_GROUPS; ++g)
-                    if (n0 + 128 * g < p.n_p) ++groups;
-                const uint32_t stage = smem_base + s * C::STAGE_BYTES;
-                // the small scale tiles go first and complete on their own barrier, so that the
-                // movers can bring them to tensor memory while the operand tiles are still in flight
-                const uint32_t sf_bar = sf_full_bar + 8 * s;
-                if (!dbg_no_sf) {   // (with the movers switched off nobody would wait for these copies)
-                    mbar_expect_tx(sf_bar, (1 + groups) * nkb * SF_TILE_BYTES);
-                    bulk_load(stage + A_BYTES + C::B_BYTES, p.a_sf + ((m0 / 128) * k_blocks + kb0) * SF_TILE_BYTES,
-                              nkb * SF_TILE_BYTES, sf_bar);
-                    for (int g = 0; g < groups; ++g)
-                        bulk_load(stage + A_BYTES + C::B_BYTES + SFA_BYTES + g * KB_PER_STAGE * SF_TILE_BYTES,
-                                  p.b_sf + ((n0 / 128 + g) * k_blocks + kb0) * SF_TILE_BYTES, nkb * SF_TILE_BYTES,
-                                  sf_bar);
-                }
-                const uint32_t bar = full_bar + 8 * s;
-                mbar_expect_tx(bar, A_BYTES + C::B_BYTES);
-                tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), static_cast<int>(m0), bar);
-                tma_load_2d(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES), static_cast<int>(n0), bar);
+                const uint32_t stage = smem_base + s * C::STAGE_BYTES, bar = full_bar + 8 * s;
+                // rows beyond N and bytes beyond K are zero-filled by the TMA unit and still counted
+                mbar_expect_tx(bar, bytes);
+                if (do_a) tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), m0, bar);
+                if (do_b) tma_load_2d(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES), n0, bar);
+                if (++s == C::STAGES) { s = 0; ph ^= 1u; }
             }
         }
         if (!ok) {
@@ -192,9 +213,59 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const unsigned long long t0 = global_timer_ns();
             while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
         }
+    } else if (warp == 15 && lane == 0 && !dbg_no_load && !dbg_no_sf) {
+        // ------------------------------------------------------------------ TMA producer: scales
+        // A thread of its own (one thread issues a copy every hundred cycles or so, and five copies
+        // per stage from a single thread set the pace of the pipeline when measured), and SF_LEAD
+        // stages ahead of the operands: the scales' way into the MMA is longer (shared memory ->
+        // mover warps -> tensor memory), and with the same start they arrive last.
+        int64_t f_t = blockIdx.x, f_kt = 0;          // the stage whose scales are requested next
+        uint32_t slot = 0;
+        int a_group = 0, b_group = 0;
+        auto enter_tile = [&]() {
+            if (f_t >= num_tiles) return;
+            int64_t mb, nb;
+            tile_coords(f_t, num_m, num_n, mb, nb);
+            a_group = static_cast<int>(mb);
+            b_group = static_cast<int>(nb * C::N_GROUPS);
+        };
+        auto issue_next = [&]() {
+            if (f_t >= num_tiles) return;
+            // two tensor copies per stage: [K-blocks kb0 .. kb0+3] x [one / N_GROUPS row groups] of
+            // 512-byte tiles; what lies beyond K or N is zero-filled and still counted
+            const int kb0 = static_cast<int>(f_kt * KB_PER_STAGE);
+            const uint32_t dst = sf_base + slot * C::SF_SLOT_BYTES, bar = sf_full_bar + 8 * slot;
+            mbar_expect_tx(bar, C::SF_SLOT_BYTES);
+            tma_load_3d(dst, &map_sfa, 0, kb0, a_group, bar);
+            tma_load_3d(dst + SFA_BYTES, &map_sfb, 0, kb0, b_group, bar);
+            if (++slot == C::SF_SLOTS) slot = 0;
+            if (++f_kt == k_tiles) {
+                f_kt = 0;
+                f_t += gridDim.x;
+                enter_tile();
+            }
+        };
+        enter_tile();
+        for (int i = 0; i < SF_LEAD; ++i) issue_next();
+        uint32_t s = 0, ph = 0;
+        bool ok = true;
+        for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int64_t kt = 0; kt < k_tiles; ++kt) {
+                // when the MMAs of the iteration STAGES back are done, the scale slot of the iteration
+                // SF_LEAD ahead of this one (SF_SLOTS = STAGES + SF_LEAD back from it) is free
+                ok = mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 7);
+                if (!ok) break;
+                issue_next();
+                if (++s == C::STAGES) { s = 0; ph ^= 1u; }
+            }
+        }
+        if (!ok) {
+            const unsigned long long t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
     } else if (warp == 1 && lane == 0) {
         // ------------------------------------------------------------------ MMA issuer
-        uint32_t it = 0, tile_i = 0;
+        uint32_t s = 0, ph = 0, j = 0, jph = 0, tile_i = 0;      // operand stage / scale slot and their phases
         bool ok = true;
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
             int64_t mb, nb;
@@ -207,11 +278,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
-            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
-                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+            for (int64_t kt = 0; kt < k_tiles; ++kt) {
                 if (!dbg_no_load) {
                     ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
-                    if (ok && !dbg_no_sf) ok = mbar_wait(sf_ready_bar + 8 * s, ph, abort_flag, p.status, 5);
+                    if (ok && !dbg_no_sf) ok = mbar_wait(sf_ready_bar + 8 * j, jph, abort_flag, p.status, 5);
                 }
                 if (!ok) break;
                 tc_fence_after();
@@ -219,14 +289,16 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const int nkb = static_cast<int>((k_blocks - kb0) < KB_PER_STAGE ? (k_blocks - kb0) : KB_PER_STAGE);
                 const uint32_t stage = smem_base + s * C::STAGE_BYTES;
                 // operands: 128-byte swizzled rows, 8-row groups 1024 bytes apart; each K-block
-                // of 64 values is 32 bytes further along the row. Scales: this stage's ring slot.
+                // of 64 values is 32 bytes further along the row. Scales: this iteration's ring slot.
                 const uint64_t a_desc = smem_desc(stage, 16, 1024, 2);
                 const uint64_t b_desc = smem_desc(stage + A_BYTES, 16, 1024, 2);
-                const uint32_t sfa_tmem = tmem_base + SF_COL0 + s * C::SF_STAGE_COLS, sfb_tmem = sfa_tmem + 16;
-                for (int kb = 0; kb < nkb; ++kb)
+                const uint32_t sfa_tmem = tmem_base + SF_COL0 + j * C::SF_STAGE_COLS, sfb_tmem = sfa_tmem + 16;
+                for (int kb = 0; kb < nkb && !dbg_no_mma; ++kb)
                     tc_mma_nvf4(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc, sfa_tmem + 4 * kb,
                                 sfb_tmem + (BLOCK_N / 32) * kb, (kt > 0 || kb > 0) ? 1u : 0u);
-                tc_commit(empty_bar + 8 * s);          // stage reusable once these MMAs have read it
+                tc_commit(empty_bar + 8 * s);          // stage (and scale slot) reusable once these MMAs are done
+                if (++s == C::STAGES) { s = 0; ph ^= 1u; }
+                if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
             }
             if (ok) tc_commit(acc_full_bar + 8 * acc);  // accumulator complete
         }
@@ -238,6 +310,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const float alpha = __ldg(p.alpha);
         OUT *out = static_cast<OUT *>(p.d);
         const bool vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((p.ldd * sizeof(OUT)) % 16 == 0);
+        const bool vec32_ok = FOS_GEMM_ST256 && (reinterpret_cast<uintptr_t>(out) % 32 == 0) && ((p.ldd * sizeof(OUT)) % 32 == 0);
         uint32_t tile_i = 0;
         bool ok = true;
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
@@ -251,43 +324,79 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BLOCK_N + half * COLS;
             const bool row_ok = row < p.m && !dbg_no_store;
-#pragma unroll 1
-            for (int c = 0; c < COLS / 32; c += 2) {
-                uint32_t v0[32], v1[32];
-                tc_load_64cols_sync(t_acc + 32 * c, v0, v1);
-                if (c + 2 >= COLS / 32) {                // everything is in registers: release the accumulator
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(acc_empty_bar + 8 * acc);
+            if constexpr (sizeof(OUT) == 2) {
+                // 16-bit outputs: scale, convert and pack while reading, so that the warp's whole
+                // row segment fits in registers and the accumulator goes back to the MMA warp
+                // before the first store is issued
+                uint32_t pk[COLS / 2];
+#pragma unroll
+                for (int c = 0; c < COLS / 32; ++c) {
+                    uint32_t v[32];
+                    tc_load_32cols_sync(t_acc + 32 * c, v);
+                    if (c + 1 == COLS / 32) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty_bar + 8 * acc);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        pk[16 * c + i] = pack_pair<OUT>(alpha * __uint_as_float(v[2 * i]), alpha * __uint_as_float(v[2 * i + 1]));
                 }
-                const int64_t col = n0 + 32 * c;
-                const int64_t left0 = p.n - col, left1 = left0 - 32;
-                if (row_ok && left0 > 0)
-                    store_chunk<OUT>(out + row * p.ldd + col, v0, alpha, left0 < 32 ? static_cast<int>(left0) : 32, vec_ok);
-                if (row_ok && left1 > 0)
-                    store_chunk<OUT>(out + row * p.ldd + col + 32, v1, alpha, left1 < 32 ? static_cast<int>(left1) : 32, vec_ok);
+                const int64_t left = p.n - n0;
+                if (row_ok && left > 0) {
+                    OUT *dst = out + row * p.ldd + n0;
+                    if (left >= COLS && vec32_ok) {
+                        // 32 bytes per store: every instruction of the warp fills whole 32-byte sectors
+#pragma unroll
+                        for (int i = 0; i < COLS / 16; ++i) stg_32(reinterpret_cast<uint8_t *>(dst) + 32 * i, &pk[8 * i]);
+                    } else if (left >= COLS && vec_ok) {
+#pragma unroll
+                        for (int i = 0; i < COLS / 8; ++i)
+                            reinterpret_cast<uint4 *>(dst)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                    } else {
+                        uint16_t *d16 = reinterpret_cast<uint16_t *>(dst);
+#pragma unroll
+                        for (int i = 0; i < COLS; ++i)
+                            if (i < left) d16[i] = static_cast<uint16_t>(pk[i >> 1] >> ((i & 1) * 16));
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < COLS / 32; c += 2) {
+                    uint32_t v0[32], v1[32];
+                    tc_load_64cols_sync(t_acc + 32 * c, v0, v1);
+                    if (c + 2 >= COLS / 32) {                // everything is in registers: release the accumulator
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty_bar + 8 * acc);
+                    }
+                    const int64_t col = n0 + 32 * c;
+                    const int64_t left0 = p.n - col, left1 = left0 - 32;
+                    if (row_ok && left0 > 0)
+                        store_chunk<OUT>(out + row * p.ldd + col, v0, alpha, left0 < 32 ? static_cast<int>(left0) : 32, vec_ok);
+                    if (row_ok && left1 > 0)
+                        store_chunk<OUT>(out + row * p.ldd + col + 32, v1, alpha, left1 < 32 ? static_cast<int>(left1) : 32, vec_ok);
+                }
             }
         }
-    } else if (warp >= 10 && !dbg_no_load && !dbg_no_sf) {
+    } else if (warp >= 10 && warp < 14 && !dbg_no_load && !dbg_no_sf) {
         // ------------------------------------------------------------------ scale movers
         const int quad = warp & 3;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-        uint32_t it = 0;
+        uint32_t j = 0, jph = 0;
         bool ok = true;
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             int64_t mb, nb;
             tile_coords(t, num_m, num_n, mb, nb);
             const int64_t n0 = nb * BLOCK_N;
-            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
-                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-                ok = mbar_wait(sf_full_bar + 8 * s, ph, abort_flag, p.status, 6);
+            for (int64_t kt = 0; kt < k_tiles; ++kt) {
+                ok = mbar_wait(sf_full_bar + 8 * j, jph, abort_flag, p.status, 6);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 const int64_t kb0 = kt * KB_PER_STAGE;
                 const int nkb = static_cast<int>((k_blocks - kb0) < KB_PER_STAGE ? (k_blocks - kb0) : KB_PER_STAGE);
-                const uint32_t stage = smem_base + s * C::STAGE_BYTES;
-                const uint32_t sfa_smem = stage + A_BYTES + C::B_BYTES + lane * 16, sfb_smem = sfa_smem + SFA_BYTES;
-                const uint32_t slot = lane_base + SF_COL0 + s * C::SF_STAGE_COLS;
+                const uint32_t sfa_smem = sf_base + j * C::SF_SLOT_BYTES + lane * 16, sfb_smem = sfa_smem + SFA_BYTES;
+                const uint32_t slot = lane_base + SF_COL0 + j * C::SF_STAGE_COLS;
                 uint32_t r[16];
                 // A: four columns per K-block = the 16 bytes of row `lane` of that K-block's tile
 #pragma unroll
@@ -314,7 +423,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 tc_wait_store();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(sf_ready_bar + 8 * s);
+                if (lane == 0) mbar_arrive(sf_ready_bar + 8 * j);
+                if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
             }
         }
     }
@@ -332,9 +442,13 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 // Two CTAs of a cluster (two SMs) compute one 256 x 256 tile with cta_group::2 MMAs: CTA r of
 // the pair holds rows m0 + 128 r .. of A and rows n0 + 128 r .. of B in its shared memory,
 // and the tensor cores of both SMs read both halves of B. Per stage an SM fetches 38 KB from
-// L2 instead of the single-CTA kernel's 54 KB for the same number of multiply-adds, and that
-// kernel is limited by exactly this traffic. Only the even CTA (the leader) issues MMAs; both
+// L2 instead of the single-CTA kernel's 54 KB for the same number of multiply-adds, and reads a
+// third less from shared memory per MMA. Only the even CTA (the leader) issues MMAs; both
 // CTAs run a TMA producer, scale movers and an epilogue for their own 128 rows of the tile.
+// Measured slower than the single-CTA kernel so far: every hand-over between the two SMs
+// (relay, remote arrive, multicast commit) lengthens the load round trip, which five stages
+// do not cover. Remote arrives use the default (CTA-scope release) form: the cluster-scope
+// release form cost about a microsecond each.
 //
 //   full[s]      one per CTA: this CTA's operand tiles have landed
 //   peer_full[s] leader's barrier, 1 arrival: a relay thread in the peer saw the peer's full[s]
@@ -358,11 +472,6 @@ constexpr int SF_STAGE_COLS = 16 + 32;                                    // A s
 static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
 static_assert(SF_COL0 + STAGES * SF_STAGE_COLS <= TMEM_COLS, "scale ring does not fit tensor memory");
 
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
-}
 
 template <typename OUT>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -418,6 +527,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int64_t k_tiles = (k_blocks + KB_PER_STAGE - 1) / KB_PER_STAGE;
     const int64_t pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     const bool dbg_no_sf = p.debug & 1, dbg_no_load = p.debug & 2, dbg_no_store = p.debug & 4;
+    const bool dbg_no_mma = p.debug & 16;
 
     if (warp == 0 && lane == 0 && !dbg_no_load) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -429,7 +539,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             const int m0 = static_cast<int>(mb * 256 + rank * 128), n0 = static_cast<int>(nb * TILE_N);
             for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                ok = mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 1);
+                ok = mbar_wait_poll(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 1);
                 if (!ok) break;
                 const uint32_t stage = smem_base + s * STAGE_BYTES;
                 const int kb0 = static_cast<int>(kt * KB_PER_STAGE);
@@ -460,15 +570,15 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         uint32_t it = 0, tile_i = 0;
         bool ok = true;
         for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs, ++tile_i) {
-            ok = mbar_wait(acc_empty_bar, (tile_i & 1u) ^ 1u, abort_flag, p.status, 3);
+            ok = mbar_wait_poll(acc_empty_bar, (tile_i & 1u) ^ 1u, abort_flag, p.status, 3);
             if (!ok) break;
             tc_fence_after();
             for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                 if (!dbg_no_load) {
                     ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
-                    if (ok) ok = mbar_wait(peer_full_bar + 8 * s, ph, abort_flag, p.status, 7);
-                    if (ok && !dbg_no_sf) ok = mbar_wait(sf_ready_bar + 8 * s, ph, abort_flag, p.status, 5);
+                    if (ok) ok = mbar_wait_poll(peer_full_bar + 8 * s, ph, abort_flag, p.status, 7);
+                    if (ok && !dbg_no_sf) ok = mbar_wait_poll(sf_ready_bar + 8 * s, ph, abort_flag, p.status, 5);
                 }
                 if (!ok) break;
                 tc_fence_after();
@@ -478,7 +588,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const uint64_t a_desc = smem_desc(stage, 16, 1024, 2);
                 const uint64_t b_desc = smem_desc(stage + A_BYTES, 16, 1024, 2);
                 const uint32_t sfa_tmem = tmem_base + SF_COL0 + s * SF_STAGE_COLS, sfb_tmem = sfa_tmem + 16;
-                for (int kb = 0; kb < nkb; ++kb)
+                for (int kb = 0; kb < nkb && !dbg_no_mma; ++kb)
                     tc_mma_nvf4_pair(tmem_base, a_desc + 2 * kb, b_desc + 2 * kb, idesc, sfa_tmem + 4 * kb,
                                      sfb_tmem + 8 * kb, (kt > 0 || kb > 0) ? 1u : 0u);
                 tc_commit_pair(empty_bar + 8 * s);
@@ -512,8 +622,9 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             int64_t mb, nb;
             tile_coords(t, num_m, num_n, mb, nb);
             const int64_t row = mb * 256 + rank * 128 + quad * 32 + lane, n0 = nb * TILE_N + half * 128;
-            ok = mbar_wait(acc_full_bar, tile_i & 1u, abort_flag, p.status, 4);
-            ok = __all_sync(0xffffffffu, ok);
+            // in the peer this barrier is arrived on from the leader's SM: one lane polls for the warp
+            if (lane == 0) ok = mbar_wait_poll(acc_full_bar, tile_i & 1u, abort_flag, p.status, 4);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + half * 128;
@@ -640,7 +751,8 @@ int launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap 
 }
 
 template <int BLOCK_N, typename OUT>
-int launch(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p, int sms, cudaStream_t stream) {
+int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &msa, const CUtensorMap &msb,
+           const GemmParams &p, int sms, cudaStream_t stream) {
     using C = Cfg<BLOCK_N>;
     auto kernel = gemm_nvfp4_kernel<BLOCK_N, OUT>;
     static bool configured[64] = {};   // per instantiation and per device
@@ -652,16 +764,17 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p, in
     }
     const int64_t tiles = (p.m_p / BLOCK_M) * ((p.n_p + BLOCK_N - 1) / BLOCK_N);
     const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
-    kernel<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ma, mb, p);
+    kernel<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ma, mb, msa, msb, p);
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;
 }
 
 template <int BLOCK_N>
-int launch_out(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p, int sms, cudaStream_t stream) {
-    if (p.out_dtype == FOS_BF16) return launch<BLOCK_N, __nv_bfloat16>(ma, mb, p, sms, stream);
-    if (p.out_dtype == FOS_FP16) return launch<BLOCK_N, __half>(ma, mb, p, sms, stream);
-    return launch<BLOCK_N, float>(ma, mb, p, sms, stream);
+int launch_out(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &msa, const CUtensorMap &msb,
+               const GemmParams &p, int sms, cudaStream_t stream) {
+    if (p.out_dtype == FOS_BF16) return launch<BLOCK_N, __nv_bfloat16>(ma, mb, msa, msb, p, sms, stream);
+    if (p.out_dtype == FOS_FP16) return launch<BLOCK_N, __half>(ma, mb, msa, msb, p, sms, stream);
+    return launch<BLOCK_N, float>(ma, mb, msa, msb, p, sms, stream);
 }
 
 int g_gemm_variant = 0;   // FOS_OPT_GEMM_VARIANT
@@ -675,7 +788,7 @@ extern "C" int fos_set_option(int key, int value) {
         fos::g_gemm_variant = value;
         return FOS_OK;
     }
-    if (key == FOS_OPT_GEMM_DEBUG && value >= 0 && value < 8) {
+    if (key == FOS_OPT_GEMM_DEBUG && value >= 0 && value < 32 && !(value & 8)) {
         fos::g_gemm_debug = value;
         return FOS_OK;
     }
@@ -711,9 +824,9 @@ extern "C" int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const
     if (status) FOS_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
     CUtensorMap map_a, map_b;
 
-    // The CTA-pair kernel is correct but measured slower than the single-CTA kernel on B200 (both
-    // SMs ingest as many bytes per MMA once the peer's half of B is counted), so it only runs
-    // when asked for.
+    // The CTA-pair kernel is correct but still measures slower than the single-CTA kernel on B200
+    // (its hand-overs between the two SMs lengthen the load round trip), so it only runs when
+    // asked for.
     const bool pair_fits = m_p % 256 == 0 && n_p % 256 == 0;
     const bool use_pair = pair_fits && g_gemm_variant == 2;
     if (use_pair) {
@@ -734,5 +847,9 @@ extern "C" int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const
     if (g_gemm_variant == 256) wide = true;
     if ((st = make_operand_map(&map_a, a_codes, m_p, k_p / 2, BLOCK_M)) != FOS_OK) return st;
     if ((st = make_operand_map(&map_b, b_codes, n_p, k_p / 2, wide ? 256 : 128)) != FOS_OK) return st;
-    return wide ? launch_out<256>(map_a, map_b, p, sms, stream) : launch_out<128>(map_a, map_b, p, sms, stream);
+    CUtensorMap map_sfa, map_sfb;
+    if ((st = make_scale_map(&map_sfa, a_sf, m_p / 128, k_p / 64, 1)) != FOS_OK) return st;
+    if ((st = make_scale_map(&map_sfb, b_sf, n_p / 128, k_p / 64, wide ? 2 : 1)) != FOS_OK) return st;
+    return wide ? launch_out<256>(map_a, map_b, map_sfa, map_sfb, p, sms, stream)
+                : launch_out<128>(map_a, map_b, map_sfa, map_sfb, p, sms, stream);
 }

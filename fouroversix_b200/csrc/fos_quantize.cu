@@ -35,7 +35,8 @@ struct QuantParams {
     int64_t rows, cols, ld;      // source tensor
     int64_t out_rows, out_cols;  // Y before padding
     int64_t rows_p, cols_p;      // Y after padding
-    const float *amax;           // device, already final
+    const float *amax;           // device, final by the time the quantize kernel reads it
+    float *amax_store;           // where the quantize kernel copies amax to, or null
     uint8_t *codes;
     uint8_t *sf;
     int rule;
@@ -292,6 +293,7 @@ __device__ __forceinline__ float block_error(const float (&e)[16], int rule, flo
 // Per-tensor constants: encode = (max value * max scale) / amax and decode = 1 / encode.
 struct TensorConsts {
     float amax, maxq, encode, decode;
+    float encode0;    // encode, or 0 when amax is 0 (every block scale is then 0)
     bool filter_ok;   // amax is in the range where the fast pre-filter's error bound holds
 };
 
@@ -303,17 +305,23 @@ __device__ __forceinline__ TensorConsts tensor_consts(float amax, int rule) {
     const float maxsf = (KIND == KIND_ADAPTIVE) ? 256.0f : 448.0f;
     c.encode = __fdiv_rn(c.maxq * maxsf, amax);
     c.decode = __frcp_rn(c.encode);
+    c.encode0 = amax == 0.0f ? 0.0f : c.encode;
     c.filter_ok = amax > 0x1p-100f && amax < 0x1p100f;
     return c;
 }
 
 // What a block needs to know about a scale byte b: s = its value, r = 1 / (decode * s) as the
-// reference rounds it, g = s * amax / (6 * 256) (approximate, pre-filter only) and g * g.
-// The 1-D kernel tabulates this once per CTA for all 128 bytes; other callers compute it.
-__device__ __forceinline__ float4 scale_entry(uint32_t sfb, const TensorConsts &tc) {
+// reference rounds it, g = s * amax / (6 * 256) (approximate, pre-filter only) and g * g, the
+// last one replaced by -1 when the fast pre-filter must not be used with this scale: the
+// caller rules it out (`filter_allowed`: wrong rule, exact-only run, amax out of range), the
+// scale is zero or subnormal, or r is so small that x * r can underflow.
+// The 1-D kernels tabulate this once per CTA for all 128 bytes; other callers compute it.
+__device__ __forceinline__ float4 scale_entry(uint32_t sfb, const TensorConsts &tc, bool filter_allowed) {
     const float s = e4m3_to_float(sfb);
+    const float r = __frcp_rn(__fmul_rn(tc.decode, s));
     const float g = s * tc.amax * (1.0f / 1536.0f);
-    return make_float4(s, __frcp_rn(__fmul_rn(tc.decode, s)), g, g * g);
+    const bool usable = filter_allowed && sfb >= 8u && r >= 0x1p-16f;
+    return make_float4(s, r, g, usable ? g * g : -1.0f);
 }
 
 template <int KIND, bool TWO_D, bool TRANSPOSED>
@@ -326,22 +334,31 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
     for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(v[i]));
     bmax = block_max<TWO_D, TRANSPOSED>(bmax);
     const float q = tc.maxq == 6.0f ? div6_exact(bmax) : __fmul_rn(bmax, 0.25f);   // bmax / maxq
-    float hp = (amax == 0.0f) ? 0.0f : __fmul_rn(q, tc.encode);
-
-    const uint32_t sfb_a = cvt_e4m3(hp);
-    const float4 ea = lut ? lut[sfb_a] : scale_entry(sfb_a, tc);
-    const float s_a = ea.x, r_a = ea.y;
+    const float hp = __fmul_rn(q, tc.encode0);
+    const bool filter_allowed = !TWO_D && rule == FOS_RULE_MSE && !exact_only && tc.filter_ok;   // unused with a table
 
     if (KIND == KIND_STATIC) {
+        const uint32_t sfb = cvt_e4m3(hp);
+        const float4 ea = lut ? lut[sfb] : scale_entry(sfb, tc, false);
         lo = hi = 0u;
-        if (s_a != 0.0f) encode_e2m1(v, r_a, r_a < 0x1p-16f, lo, hi);
-        sf_byte = sfb_a;
+        if (ea.x != 0.0f) encode_e2m1(v, ea.y, ea.y < 0x1p-16f, lo, hi);
+        sf_byte = sfb;
         return;
     }
 
+    uint32_t sfb_a, sfb_b = 0u;
     if (KIND == KIND_ADAPTIVE) {
-        const uint32_t sfb_b = cvt_e4m3(__fmul_rn(hp, 1.5f));
-        const float4 eb = lut ? lut[sfb_b] : scale_entry(sfb_b, tc);
+        const uint32_t both = cvt_e4m3x2(__fmul_rn(hp, 1.5f), hp);   // "4" candidate in the upper byte
+        sfb_a = both & 0xffu;
+        sfb_b = both >> 8;
+    } else {
+        sfb_a = cvt_e4m3(hp);
+    }
+    const float4 ea = lut ? lut[sfb_a] : scale_entry(sfb_a, tc, filter_allowed);
+    const float s_a = ea.x, r_a = ea.y;
+
+    if (KIND == KIND_ADAPTIVE) {
+        const float4 eb = lut ? lut[sfb_b] : scale_entry(sfb_b, tc, filter_allowed);
         const float s_b = eb.x, r_b = eb.y;
 
         // Fast pre-filter: 1-D blocks, mean-squared error, both scales normal E4M3 numbers (so
@@ -353,8 +370,7 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
         // <= 188u * (sum t^2 + 1) * G^2 (arithmetic over geometric mean), plus 40u relative for the
         // roundings of the two summations. `tau` is 1.5 times that, for both candidates
         // together; a difference inside tau is re-decided exactly below.
-        const bool eligible = !TWO_D && rule == FOS_RULE_MSE && !exact_only && sfb_a >= 8u && sfb_b >= 8u &&
-                              tc.filter_ok && r_a >= 0x1p-16f && r_b >= 0x1p-16f;
+        const bool eligible = !TWO_D && fminf(ea.w, eb.w) >= 0.0f;
         bool decided = false, pick_b = false;
         uint32_t ca[2] = {0u, 0u}, cb[2] = {0u, 0u};
         if (eligible) {
@@ -529,6 +545,7 @@ __global__ void __launch_bounds__(CTA_THREADS) quantize_kernel(const QuantParams
     }
     float *scratch = TWO_D ? reinterpret_cast<float *>(smem) + warp * 512 : nullptr;
     const TensorConsts tc = tensor_consts<KIND>(__ldg(p.amax), p.rule);
+    if (p.amax_store != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) *p.amax_store = tc.amax;
     uint32_t lo, hi, sf_byte;
     quantize_block<KIND, TWO_D, TRANSPOSED>(v, tc, p.rule, p.exact_only != 0, scratch, lane, nullptr, nullptr, lo, hi,
                                             sf_byte);
@@ -598,7 +615,9 @@ quantize_rows_kernel(const QuantParams p) {
     // programmatic dependent launch this CTA may be running before that kernel has finished.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(p.amax), p.rule);
-    if (threadIdx.x < 128) lut[threadIdx.x] = scale_entry(threadIdx.x, tc);
+    if (p.amax_store != nullptr && threadIdx.x == 0 && blockIdx.x == 0) *p.amax_store = tc.amax;
+    if (threadIdx.x < 128)
+        lut[threadIdx.x] = scale_entry(threadIdx.x, tc, p.rule == FOS_RULE_MSE && !p.exact_only && tc.filter_ok);
     __syncthreads();
 
     while (true) {
@@ -646,14 +665,20 @@ quantize_rows_kernel(const QuantParams p) {
 // Needs x 16-byte aligned with a row stride that is a multiple of 16 bytes.
 
 constexpr int FEED_TILE_ROWS = 128;
-constexpr int FEED_STAGES = 4;
+#ifndef FOS_FEED_STAGES
+#define FOS_FEED_STAGES 4
+#endif
+#ifndef FOS_FEED_CTAS
+#define FOS_FEED_CTAS 3
+#endif
+constexpr int FEED_STAGES = FOS_FEED_STAGES;
 constexpr int FEED_STAGE_BYTES = FEED_TILE_ROWS * 128;
 constexpr int FEED_CONSUMERS = 256;
 constexpr int FEED_THREADS = FEED_CONSUMERS + 32;
 constexpr int FEED_SMEM_BYTES = FEED_STAGES * FEED_STAGE_BYTES + 1024;
 
 template <typename T, int KIND>
-__global__ void __launch_bounds__(FEED_THREADS, 3)
+__global__ void __launch_bounds__(FEED_THREADS, FOS_FEED_CTAS)
 quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantParams p) {
     extern __shared__ uint8_t feed_smem_raw[];
     __shared__ float4 lut[128];
@@ -714,7 +739,9 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
     // CTA may be running before that kernel has finished.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(p.amax), p.rule);
-    if (threadIdx.x < 128) lut[threadIdx.x] = scale_entry(threadIdx.x, tc);
+    if (p.amax_store != nullptr && threadIdx.x == 0 && blockIdx.x == 0) *p.amax_store = tc.amax;
+    if (threadIdx.x < 128)
+        lut[threadIdx.x] = scale_entry(threadIdx.x, tc, p.rule == FOS_RULE_MSE && !p.exact_only && tc.filter_ok);
     asm volatile("bar.sync 1, %0;" ::"n"(FEED_CONSUMERS) : "memory");
 
     // What depends on the thread alone is computed here once. The empty asm statements make these
@@ -941,15 +968,17 @@ extern "C" int fos_quantize(const void *x, int x_dtype, int64_t rows, int64_t co
     const bool vec16 = p.vec_bytes != 0 && cols % 8 == 0;
 
     if (amax_in) {
-        if (amax_in != amax_out)
-            FOS_CUDA_TRY(cudaMemcpyAsync(amax_out, amax_in, sizeof(float), cudaMemcpyDeviceToDevice, stream));
+        // the quantize kernel copies the value over: no separate copy operation in the stream
+        p.amax = amax_in;
+        p.amax_store = amax_in != amax_out ? amax_out : nullptr;
     } else {
         FOS_CUDA_TRY(cudaMemsetAsync(amax_out, 0, sizeof(float), stream));
         FOS_CUDA_TRY(x_dtype == FOS_BF16
                          ? launch_amax<__nv_bfloat16>(x, rows, cols, ld, vec16, amax_out, stream)
                          : launch_amax<__half>(x, rows, cols, ld, vec16, amax_out, stream));
+        p.amax = amax_out;
+        p.amax_store = nullptr;
     }
-    p.amax = amax_out;
     // When this call launched the amax pass itself, the kernel before the quantize kernel is that
     // pass: it does not write x, so x can be fetched while it drains.
     p.x_is_ready = amax_in == nullptr;

@@ -10,7 +10,8 @@
 namespace fos {
 namespace {
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // every device-side wait gives up after 2 s
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // waits timed with the global timer give up after 2 s
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;         // waits timed in SM cycles: about 2 s at 2 GHz, 4 s at 1 GHz
 constexpr int TMEM_COLS = 512;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -41,17 +42,52 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait. Returns false when the CTA is aborting (this wait or another one timed out).
+// The limit is counted in SM clock cycles: reading %globaltimer inside the polling loop would add
+// its own latency to every hand-over between the roles of a kernel.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                           int32_t *status, int where) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
         if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_timer_ns();
+    const long long t0 = clock64();
 #pragma unroll 1
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            if (status) atomicCAS(status, 0, where);
+            return false;
+        }
+    }
+}
+
+// Non-suspending probe of a barrier phase.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p; }\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// mbar_wait that polls instead of letting the hardware suspend the thread. For barriers that
+// another CTA of the cluster arrives on: a thread suspended in try_wait is not woken by such
+// an arrival before the suspension runs out, which costs over a microsecond per hand-over.
+__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                               int32_t *status, int where) {
+    const long long t0 = clock64();
+#pragma unroll 1
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_test_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;
             if (status) atomicCAS(status, 0, where);
             return false;
@@ -63,6 +99,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -86,6 +127,14 @@ __device__ __forceinline__ void tc_load_64cols_sync(uint32_t taddr, uint32_t (&a
         : "r"(taddr), "r"(taddr + 32) : "memory");
 }
 
+// One 32-column load and the wait, again in one asm statement.
+__device__ __forceinline__ void tc_load_32cols_sync(uint32_t taddr, uint32_t (&a)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]), "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15]), "=r"(a[16]), "=r"(a[17]), "=r"(a[18]), "=r"(a[19]), "=r"(a[20]), "=r"(a[21]), "=r"(a[22]), "=r"(a[23]), "=r"(a[24]), "=r"(a[25]), "=r"(a[26]), "=r"(a[27]), "=r"(a[28]), "=r"(a[29]), "=r"(a[30]), "=r"(a[31])
+        : "r"(taddr) : "memory");
+}
 
 // Each lane writes N consecutive 32-bit columns of its own tensor-memory lane.
 __device__ __forceinline__ void tc_store_16cols(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -94,7 +143,28 @@ __device__ __forceinline__ void tc_store_16cols(uint32_t taddr, const uint32_t (
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
+__device__ __forceinline__ void tc_store_8cols(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+template <int N> __device__ __forceinline__ void tc_store_cols(uint32_t taddr, const uint32_t (&r)[N]) {
+    static_assert(N == 8 || N % 16 == 0, "8 columns or a multiple of 16");
+    if constexpr (N == 8) {
+        tc_store_8cols(taddr, r);
+    } else {
+#pragma unroll
+        for (int c = 0; c < N; c += 16) tc_store_16cols(taddr + c, *reinterpret_cast<const uint32_t (*)[16]>(&r[c]));
+    }
+}
 __device__ __forceinline__ void tc_wait_store() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// 16-byte read-only load that may stay in L1 (for small data several warps of an SM re-read).
+__device__ __forceinline__ uint4 ldg_16_cached(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void prefetch_l1(const void *p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 __device__ __forceinline__ uint4 lds_16(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -115,7 +185,7 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
     return r;
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n"
@@ -147,6 +217,18 @@ __device__ __forceinline__ void tile_coords(int64_t t, int64_t num_m, int64_t nu
     const int64_t rows = (num_m - first) < GROUP_M ? (num_m - first) : GROUP_M;
     mb = first + r % rows;
     nb = r / rows;
+}
+
+// Two floats -> one word of two 16-bit outputs (`lo` in the lower half).
+template <typename OUT>
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
+    if constexpr (std::is_same<OUT, __half>::value) {
+        const __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    } else {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
 }
 
 // One accumulator row chunk (32 columns) -> alpha * acc -> OUT, to `dst`; `valid` columns exist.
@@ -191,17 +273,19 @@ inline EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// K-major operand [rows, row_bytes] (bytes, row-major); box = 128 bytes x box_rows, 128-byte swizzle.
-inline int make_operand_map(CUtensorMap *map, const void *base, int64_t rows, int64_t row_bytes, int box_rows) {
+// K-major operand [rows, row_bytes] (bytes, row-major); box = `box_bytes` x box_rows with the
+// swizzle whose span equals the box width (128 or 64 bytes).
+inline int make_operand_map(CUtensorMap *map, const void *base, int64_t rows, int64_t row_bytes, int box_rows,
+                            int box_bytes = 128) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return FOS_ERR_CUDA;
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(rows)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
-    cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes), static_cast<cuuint32_t>(box_rows)};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? FOS_OK : FOS_ERR_CUDA;
 }
 
