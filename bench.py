@@ -12,7 +12,9 @@ N(0,1) with 1 % of the K-channels scaled by 20, NVFP4 with 4/6 MSE block selecti
 A "step" is one quantization of A (amax pass + quantize pass = 2 kernel launches), replayed
 as a CUDA graph so that the Python launch cost does not hide the device time.  Four
 copies of A (256 MiB) are cycled so that every step reads its input from HBM, not from
-the 126 MB L2.  Timing uses CUDA events on the stream the graphs are replayed on; with
+the 126 MB L2.  The `roofline` object is about the dominant kernel of a step alone, the
+quantize kernel: it is launched with amax given (then the call is that one kernel), four
+launches per graph replay, and its algorithmic bytes are divided by the time per launch.  Timing uses CUDA events on the stream the graphs are replayed on; with
 N > 1 every rank quantizes its own A (independent stripes, no collective: weak scaling)
 and the slowest rank defines the time.
 
@@ -44,6 +46,8 @@ B_SHAPE = (4096, 4096)
 BYTES_PER_ELEM = 2.0 + 0.5 + 1.0 / 16.0
 N_ROTATE = 4
 NOMINAL_FP4_TFLOPS = 9000.0
+# DRAM bytes (read + write) of one launch of the quantize kernel on the 8192x4096 tensor, from ncu
+QUANTIZE_KERNEL_DRAM_BYTES = 69.96e6   # 67.16 MB read + 2.80 MB written (the rest of the output is still in L2)
 
 
 def load_peaks() -> dict:
@@ -245,6 +249,15 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks)
         return
 
+    # the dominant kernel alone: with amax given a call is one launch of the quantize kernel
+    amaxes = [x.abs().max().float().reshape(1) for x in a_sets]
+
+    def four_kernels(_):
+        for i in range(N_ROTATE):
+            B200QuantizeBackend.quantize(a_sets[i], cfg_mse, amax=amaxes[i])
+
+    kernel_ms = time_graphs(four_kernels, 1, max(args.steps, 20), 3) / N_ROTATE
+
     # other quantize modes of the same tensor (each: the whole call, both launches)
     modes = {}
     for name, c in (("static_6", fos.QuantizationConfig(scale_rule="static_6")),
@@ -253,7 +266,6 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                     ("mse_2d", fos.QuantizationConfig(block_scale_2d=True)),
                     ("mse_transposed", fos.QuantizationConfig(transpose=True))):
         if c is None:
-            amaxes = [x.abs().max().float().reshape(1) for x in a_sets]
             fn = lambda i: B200QuantizeBackend.quantize(a_sets[i % N_ROTATE], cfg_mse, amax=amaxes[i % N_ROTATE])  # noqa: E731
         else:
             fn = lambda i, c=c: fos.quantize(a_sets[i % N_ROTATE], c)  # noqa: E731
@@ -283,7 +295,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     gemm = gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks)
     cpu = cpu_baseline_quantize(a_cpu) if world == 1 else None
 
-    achieved = BYTES_PER_ELEM * n_elem / (ms * 1e-3) / 1e9 if world == 1 else value / world
+    achieved = BYTES_PER_ELEM * n_elem / (kernel_ms * 1e-3) / 1e9
+    step_rate = value / world
     line = {
         "metric": "quantize GB/s (frac of HBM peak); FP4 GEMM TFLOP/s at 8192^3 (frac of FP4 peak)",
         "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -294,21 +307,29 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                         "per rank when n_gpus > 1",
             "l2": f"{N_ROTATE} rotating copies of A (256 MiB) so each step reads HBM-cold input",
             "bytes_per_element": BYTES_PER_ELEM,
-            "timing": "each step is one CUDA-graph replay of the library call (memset + 2 kernels); "
+            "timing": "each step is one CUDA-graph replay of the library call (3 kernels: zero amax, amax pass, quantize); "
                       "ms_per_step_eager is the same call launched from Python",
         },
         "ms_per_step_eager": eager_ms,
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": achieved / peaks["hbm_gbs"], "frac_of_nominal_8TBps": achieved / 8000.0,
-            "peak_source": peaks["source"], "traffic": None,
-            "kernels": "amax_kernel + quantize_kernel (both launches of one call are timed together)",
+            "peak_source": peaks["source"],
+            "kernel": "quantize_rows_tma_kernel<bf16, adaptive> (the longer of the step's two kernels), launched alone "
+                      "with amax given",
+            "kernel_us": kernel_ms * 1e3,
+            "algorithmic_bytes_per_launch": BYTES_PER_ELEM * n_elem,
+            "traffic": QUANTIZE_KERNEL_DRAM_BYTES,
+            "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel on this "
+                              "tensor shape (profiles/quantize_rows_tma_kernel_8192x4096_mse.md)",
+            "whole_step": {"achieved": step_rate, "frac": step_rate / peaks["hbm_gbs"],
+                           "note": "amax pass + quantize kernel together (= value per GPU)"},
         },
         "quantize_modes": modes,
         "gemm": gemm,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": 3 * args.steps,
         "clocks": clocks,
     }
     if cpu is not None:

@@ -61,7 +61,20 @@ __device__ __forceinline__ float abs_max8(uint4 w) {
                  fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(d.x), fabsf(d.y))));
 }
 
+// Sets the amax word to zero. A kernel rather than a memset so that the chain "previous kernel ->
+// this -> amax pass -> quantize kernel" consists of kernels only and every link can be a
+// programmatic dependent launch: this kernel may be scheduled while the previous one drains, it
+// waits for that kernel's completion (amax_out may still be read by it, and x may be written by
+// it), and only then lets the amax pass start.
+__global__ void zero_amax_kernel(float *amax) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) *amax = 0.0f;
+}
+
 // max |x| with 16-byte loads, four of them in flight per thread, then one atomicMax per CTA.
+// Launched behind zero_amax_kernel as its programmatic dependent: CTAs of this kernel exist only
+// after that kernel has seen its predecessor complete, so x is final; the wait below makes
+// the zero visible before the atomics.
 template <typename T>
 __global__ void __launch_bounds__(256) amax_kernel(const T *__restrict__ x, int64_t rows, int64_t cols,
                                                    int64_t ld, int vec16, float *amax) {
@@ -95,6 +108,7 @@ __global__ void __launch_bounds__(256) amax_kernel(const T *__restrict__ x, int6
     // grid's completion with griddepcontrol.wait before it reads amax); signalling here rather
     // than at the top keeps its CTAs from taking SM slots this grid still needs
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(FULL, m, o));
     __shared__ float warp_max[8];
@@ -798,6 +812,10 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
             sf_off += sf_wrap;
         }
     }
+    // A kernel launched behind this one with programmatic stream serialization (the next quantize
+    // call's kernel, for one) may take the SM slots of CTAs that are done while the others finish
+    // their last tile; it waits for this grid's completion before it reads anything this grid wrote.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // Tensor map over x as bytes: [rows][cols * 2] with a row pitch of ld * 2, boxes of 128 rows x 128 bytes.
@@ -917,17 +935,46 @@ cudaError_t launch_all(const QuantParams &p, int kind, bool two_d, bool transpos
     return launch_kind<T, KIND_IF4>(p, two_d, transposed, stream);
 }
 
+inline cudaLaunchConfig_t dependent_launch_config(unsigned grid, unsigned block, cudaStream_t stream,
+                                                  cudaLaunchAttribute *attr) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.stream = stream;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cfg;
+}
+
 template <typename T>
 cudaError_t launch_amax(const void *x, int64_t rows, int64_t cols, int64_t ld, bool vec16, float *amax,
                         cudaStream_t stream) {
+    cudaLaunchAttribute attr[1];
+    cudaLaunchConfig_t cfg = dependent_launch_config(1, 32, stream, attr);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, zero_amax_kernel, amax);
+    if (e != cudaSuccess) return e;
+    // one wave: as many CTAs as can be resident at once (a partial second wave would run alone)
+    static int resident[64] = {};
+    int dev = 0;
+    e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const int slot = (dev >= 0 && dev < 64) ? dev : 0;
+    if (resident[slot] == 0) {
+        int per_sm = 0, sms = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, amax_kernel<T>, 256, 0);
+        if (e != cudaSuccess) return e;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+        resident[slot] = (per_sm > 0 ? per_sm : 1) * sms;
+    }
     const int64_t work = vec16 ? rows * (cols >> 3) : rows * cols;
     int64_t blocks = (work + 255) / 256;
-    const int64_t cap = 148 * 8;
-    if (blocks > cap) blocks = cap;
+    if (blocks > resident[slot]) blocks = resident[slot];
     if (blocks < 1) blocks = 1;
-    amax_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const T *>(x), rows, cols, ld,
-                                                                     vec16 ? 1 : 0, amax);
-    return cudaGetLastError();
+    cfg = dependent_launch_config(static_cast<unsigned>(blocks), 256, stream, attr);
+    return cudaLaunchKernelEx(&cfg, amax_kernel<T>, static_cast<const T *>(x), rows, cols, ld, vec16 ? 1 : 0, amax);
 }
 
 }  // namespace
@@ -972,7 +1019,6 @@ extern "C" int fos_quantize(const void *x, int x_dtype, int64_t rows, int64_t co
         p.amax = amax_in;
         p.amax_store = amax_in != amax_out ? amax_out : nullptr;
     } else {
-        FOS_CUDA_TRY(cudaMemsetAsync(amax_out, 0, sizeof(float), stream));
         FOS_CUDA_TRY(x_dtype == FOS_BF16
                          ? launch_amax<__nv_bfloat16>(x, rows, cols, ld, vec16, amax_out, stream)
                          : launch_amax<__half>(x, rows, cols, ld, vec16, amax_out, stream));

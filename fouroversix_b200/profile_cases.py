@@ -2,13 +2,17 @@
 
     python -m fouroversix_b200.profile_cases quantize --rows 8192 --cols 8192 --rule mse [--amax-given]
     python -m fouroversix_b200.profile_cases dequantize --rows 8192 --cols 8192
-    python -m fouroversix_b200.profile_cases gemm --m 4096 --n 4096 --k 4096 [--variant 0|128|256|2]
+    python -m fouroversix_b200.profile_cases gemm --m 4096 --n 4096 --k 4096 [--variant 0|128|256|2] [--debug BITS] [--graph]
     python -m fouroversix_b200.profile_cases gemm-if4 --m 4096 --n 4096 --k 4096
 
 Each case allocates its inputs, runs the call `--iters` times (default 6) and prints the mean
 time per call measured with CUDA events, so the same command gives a plain timing without a
 profiler and a few identical launches to capture with one (`ncu -k regex:<kernel> -s 2 -c 2`).
 Inputs are larger than the 126 MB L2 when the default sizes are kept for quantize.
+`--graph` times replays of a CUDA graph of the call instead of launches from Python (the
+kernels are short). `--debug BITS` sets the GEMM's timing-experiment bits (1: no scale copies,
+2: no operand loads, 4: no output stores, 16: no MMAs; the RESULT IS WRONG with any of them):
+switching parts off one at a time shows what each costs.
 """
 
 from __future__ import annotations
@@ -23,9 +27,16 @@ from fouroversix_b200.matmul import B200MatmulBackend
 from fouroversix_b200.quantize.backend import B200QuantizeBackend
 
 
-def _timed(fn, iters: int) -> float:
+def _timed(fn, iters: int, graph: bool = False) -> float:
     fn()
     torch.cuda.synchronize()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        g.replay()
+        torch.cuda.synchronize()
+        fn = g.replay
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
@@ -51,6 +62,8 @@ def main() -> None:
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--iters", type=int, default=6)
+    ap.add_argument("--debug", type=int, default=0)
+    ap.add_argument("--graph", action="store_true")
     args = ap.parse_args()
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(0)
@@ -61,13 +74,13 @@ def main() -> None:
                                      transpose=args.transpose)
         amax = x.abs().max().float().reshape(1) if args.amax_given else None
         if args.case == "quantize":
-            ms = _timed(lambda: B200QuantizeBackend.quantize(x, cfg, amax=amax, exact_only=args.exact_only), args.iters)
+            ms = _timed(lambda: B200QuantizeBackend.quantize(x, cfg, amax=amax, exact_only=args.exact_only), args.iters, args.graph)
         else:
             q = fos.quantize(x, cfg)
-            ms = _timed(lambda: fos.dequantize(q), args.iters)
+            ms = _timed(lambda: fos.dequantize(q), args.iters, args.graph)
         gbs = 2.5625 * args.rows * args.cols / (ms * 1e-3) / 1e9
         print(f"{args.case} {args.rows}x{args.cols} {args.dtype} {args.rule}: {ms * 1e3:.1f} us per call "
-              f"(eager launches), {gbs:.0f} GB/s algorithmic")
+              f"({'graph replays' if args.graph else 'eager launches'}), {gbs:.0f} GB/s algorithmic")
         return
 
     dtype = "if4" if args.case == "gemm-if4" else "nvfp4"
@@ -77,12 +90,14 @@ def main() -> None:
     qb = fos.quantize(b, fos.QuantizationConfig(dtype=dtype))
     out = torch.empty(args.m, args.n, dtype=torch.bfloat16, device=dev)
     _native.lib().fos_set_option(1, args.variant)
+    _native.check(_native.lib().fos_set_option(2, args.debug), "fos_set_option")
     try:
         ms = _timed(lambda: B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType.bfloat16, out=out),
-                    args.iters)
+                    args.iters, args.graph)
     finally:
         _native.lib().fos_set_option(1, 0)
-    print(f"{args.case} {args.m}x{args.n}x{args.k} variant {args.variant}: {ms * 1e3:.1f} us per call, "
+        _native.lib().fos_set_option(2, 0)
+    print(f"{args.case} {args.m}x{args.n}x{args.k} variant {args.variant} debug {args.debug}: {ms * 1e3:.1f} us per call, "
           f"{2.0 * args.m * args.n * args.k / (ms * 1e-3) / 1e12:.0f} TFLOP/s")
 
 
