@@ -162,6 +162,7 @@ def time_graphs(fn, n_variants: int, steps: int, warmup: int) -> float:
 def cpu_baseline_quantize(a_cpu: torch.Tensor, budget_s: float = 10.0) -> dict:
     from oracle import fos_oracle
 
+    fos_oracle.set_num_threads(len(os.sched_getaffinity(0)))
     fos_oracle.quantize(a_cpu[:256])
     times = []
     t_end = time.perf_counter() + budget_s
@@ -182,6 +183,7 @@ def run_reference(args, rank: int) -> None:
         return
     from oracle import fos_oracle
 
+    fos_oracle.set_num_threads(len(os.sched_getaffinity(0)))   # torchrun exports OMP_NUM_THREADS=1
     a = make_a(1)
     for _ in range(max(args.warmup, 1)):
         fos_oracle.quantize(a)

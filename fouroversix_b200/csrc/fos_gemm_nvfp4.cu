@@ -54,6 +54,10 @@ constexpr int SF_LEAD = FOS_GEMM_SF_LEAD;   // 0 or 1: how many stages the scale
 #ifndef FOS_GEMM_ST256
 #define FOS_GEMM_ST256 1
 #endif
+#ifndef FOS_GEMM_SF_CP
+#define FOS_GEMM_SF_CP 0
+#endif
+constexpr bool SF_BY_CP = FOS_GEMM_SF_CP != 0;   // scales reach tensor memory by tcgen05.cp from the MMA thread instead of the mover warps
 #ifndef FOS_GEMM_SPLIT_AB
 #define FOS_GEMM_SPLIT_AB 0
 #endif
@@ -106,6 +110,12 @@ __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, ui
         "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p; }\n"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
         : "memory");
+}
+
+// One 512-byte scale tile (32 rows of 16 bytes) from shared memory into 4 columns of all four
+// 32-lane quadrants of tensor memory.
+__device__ __forceinline__ void tc_copy_sf(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 
 __device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -267,6 +277,34 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // ------------------------------------------------------------------ MMA issuer
         uint32_t s = 0, ph = 0, j = 0, jph = 0, tile_i = 0;      // operand stage / scale slot and their phases
         bool ok = true;
+        // SF_BY_CP: this thread also copies the scales shared -> tensor memory (tcgen05.cp reads a
+        // tile once for all four lane quadrants; the mover warps read it four times), one stage
+        // ahead of the MMAs that use them, so that the copy runs under the previous stage's MMAs.
+        uint32_t cj = 0, cjph = 0;                                // slot / phase of the next scales to copy
+        int64_t to_copy = 0;
+        if (SF_BY_CP && !dbg_no_load && !dbg_no_sf) {
+            const int64_t my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+            to_copy = my_tiles * k_tiles;
+        }
+        auto copy_next_scales = [&]() {
+            if (to_copy == 0) return;
+            --to_copy;
+            ok = mbar_wait(sf_full_bar + 8 * cj, cjph, abort_flag, p.status, 5);
+            if (!ok) return;
+            tc_fence_after();
+            const uint32_t src = sf_base + cj * C::SF_SLOT_BYTES, dst = tmem_base + SF_COL0 + cj * C::SF_STAGE_COLS;
+            // tiles: 32 rows of 16 bytes, 8-row groups 128 bytes apart, no swizzle
+#pragma unroll
+            for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
+                tc_copy_sf(dst + 4 * kb, smem_desc(src + kb * SF_TILE_BYTES, 0, 128, 0));
+#pragma unroll
+                for (int g = 0; g < C::N_GROUPS; ++g)
+                    tc_copy_sf(dst + 16 + (BLOCK_N / 32) * kb + 4 * g,
+                               smem_desc(src + SFA_BYTES + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES, 0, 128, 0));
+            }
+            if (++cj == C::SF_SLOTS) { cj = 0; cjph ^= 1u; }
+        };
+        copy_next_scales();                                       // scales of the very first stage
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
             int64_t mb, nb;
             tile_coords(t, num_m, num_n, mb, nb);
@@ -279,9 +317,13 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
             for (int64_t kt = 0; kt < k_tiles; ++kt) {
+                if (SF_BY_CP) {
+                    copy_next_scales();                           // of the stage after this one
+                    if (!ok) break;
+                }
                 if (!dbg_no_load) {
                     ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
-                    if (ok && !dbg_no_sf) ok = mbar_wait(sf_ready_bar + 8 * j, jph, abort_flag, p.status, 5);
+                    if (ok && !dbg_no_sf && !SF_BY_CP) ok = mbar_wait(sf_ready_bar + 8 * j, jph, abort_flag, p.status, 5);
                 }
                 if (!ok) break;
                 tc_fence_after();
@@ -379,7 +421,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
             }
         }
-    } else if (warp >= 10 && warp < 14 && !dbg_no_load && !dbg_no_sf) {
+    } else if (!SF_BY_CP && warp >= 10 && warp < 14 && !dbg_no_load && !dbg_no_sf) {
         // ------------------------------------------------------------------ scale movers
         const int quad = warp & 3;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);

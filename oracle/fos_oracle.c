@@ -474,3 +474,12 @@ int fos_oracle_num_threads(void) {
     return 1;
 #endif
 }
+
+/* Threads for the following calls (launchers such as torchrun export OMP_NUM_THREADS=1). */
+void fos_oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

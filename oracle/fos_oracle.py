@@ -151,3 +151,8 @@ def matmul(qa: OracleQuantized, qb: OracleQuantized, out_dtype: torch.dtype = to
 
 def num_threads() -> int:
     return int(lib().fos_oracle_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    """Use `n` OpenMP threads from now on (launchers like torchrun export OMP_NUM_THREADS=1)."""
+    lib().fos_oracle_set_num_threads(ctypes.c_int(int(n)))
