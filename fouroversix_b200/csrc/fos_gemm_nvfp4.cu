@@ -22,16 +22,20 @@
 //               memory (tcgen05.st) into a ring of scale columns, one slot per scale stage. A
 //               512-byte scale tile is 32 rows of 16 bytes and every 32-lane quadrant of tensor
 //               memory needs the same 16 bytes per lane, so each of the four warps reads row
-//               `lane` and writes its own quadrant. (Issuing tcgen05.cp from the MMA thread
-//               instead serialises with the MMAs and cost 40 % of the run time when measured;
-//               loading the scales from global memory in the mover warps made those warps the
-//               slowest role.)
-//   warp 14     spare (takes the B loads when built with FOS_GEMM_SPLIT_AB=1; no gain measured)
+//               `lane` and writes its own quadrant. (Measured slower: tcgen05.cp from the MMA
+//               thread, even into a ring and a stage ahead, about 30 ns per 512-byte copy in line
+//               with the MMAs; the scales straight from global memory in one or two sets of
+//               mover warps, which then need a microsecond per stage; operand loads split over two
+//               issuing threads changed nothing.)
+//   warp 14     spare
 //
-// What bounds the kernel: the round trip "stage released -> reload issued -> data back from L2"
-// (about 1.4 us unloaded) against only four 48 KB stages of shared memory. Shorter stages do
-// not help: the single threads that issue copies and MMAs need a few hundred cycles per stage
-// whatever its size.
+// What bounds the kernel: shared-memory bandwidth. Per K-block of 64 values the TMA unit writes
+// 13.5 KB (A 4, B 8, scales 1.5), the MMA reads 12 KB and the movers read the scales four times
+// (6 KB): 31.5 KB at 128 bytes per cycle are 246 cycles, against about 190 for the MMA itself.
+// The measured times with parts switched off follow that sum to a few percent, and the kernel
+// runs at nine tenths of it. (A CTA pair moves a third less per MMA: see the pair kernel.)
+// Shorter stages do not help: the single threads that issue copies and MMAs need a few hundred
+// cycles per stage whatever its size.
 //
 // Every mbarrier wait is bounded (in SM cycles). A wait that gives up records where
 // in *status, raises a CTA-wide abort flag, and all roles fall through to the common exit,
@@ -54,15 +58,7 @@ constexpr int SF_LEAD = FOS_GEMM_SF_LEAD;   // 0 or 1: how many stages the scale
 #ifndef FOS_GEMM_ST256
 #define FOS_GEMM_ST256 1
 #endif
-#ifndef FOS_GEMM_SF_CP
-#define FOS_GEMM_SF_CP 0
-#endif
-constexpr bool SF_BY_CP = FOS_GEMM_SF_CP != 0;   // scales reach tensor memory by tcgen05.cp from the MMA thread instead of the mover warps
-#ifndef FOS_GEMM_SPLIT_AB
-#define FOS_GEMM_SPLIT_AB 0
-#endif
-constexpr bool SPLIT_OPERAND_ISSUE = FOS_GEMM_SPLIT_AB != 0;
-constexpr int NUM_THREADS = 512;                   // TMA (A), MMA, 8 epilogue warps, 4 scale-mover warps, TMA (B), TMA (scales)
+constexpr int NUM_THREADS = 512;                   // warps: 0 TMA (operands), 1 MMA, 2-9 epilogue, 10-13 scale movers, 14 spare, 15 TMA (scales)
 constexpr int SF_COL0 = 256;                       // tensor-memory columns: accumulators first, then per
                                                    // stage 16 columns of A scales and N/8 of B scales
 
@@ -112,12 +108,6 @@ __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, ui
         : "memory");
 }
 
-// One 512-byte scale tile (32 rows of 16 bytes) from shared memory into 4 columns of all four
-// 32-lane quadrants of tensor memory.
-__device__ __forceinline__ void tc_copy_sf(uint32_t taddr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-
 __device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                  uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
     asm volatile(
@@ -163,7 +153,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
-            mbar_init(full_bar + 8 * s, SPLIT_OPERAND_ISSUE ? 2 : 1);   // one arrival per operand producer
+            mbar_init(full_bar + 8 * s, 1);
             mbar_init(empty_bar + 8 * s, 1);
         }
         for (int j = 0; j < C::SF_SLOTS; ++j) {
@@ -196,11 +186,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
     const bool dbg_no_sf = p.debug & 1, dbg_no_load = p.debug & 2, dbg_no_store = p.debug & 4;
     const bool dbg_no_mma = p.debug & 16;
-    if ((warp == 0 || (SPLIT_OPERAND_ISSUE && warp == 14)) && lane == 0 && !dbg_no_load) {
-        // ------------------------------------------------------------------ TMA producer(s): operands
-        // With SPLIT_OPERAND_ISSUE warp 0 loads A and warp 14 loads B; otherwise warp 0 loads both.
-        const bool do_a = warp == 0, do_b = !SPLIT_OPERAND_ISSUE || warp == 14;
-        const uint32_t bytes = (do_a ? A_BYTES : 0) + (do_b ? C::B_BYTES : 0);
+    if (warp == 0 && lane == 0 && !dbg_no_load) {
+        // ------------------------------------------------------------------ TMA producer: operands
         uint32_t s = 0, ph = 0;
         bool ok = true;
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
@@ -212,9 +199,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 if (!ok) break;
                 const uint32_t stage = smem_base + s * C::STAGE_BYTES, bar = full_bar + 8 * s;
                 // rows beyond N and bytes beyond K are zero-filled by the TMA unit and still counted
-                mbar_expect_tx(bar, bytes);
-                if (do_a) tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), m0, bar);
-                if (do_b) tma_load_2d(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES), n0, bar);
+                mbar_expect_tx(bar, C::STAGE_BYTES);
+                tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), m0, bar);
+                tma_load_2d(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES), n0, bar);
                 if (++s == C::STAGES) { s = 0; ph ^= 1u; }
             }
         }
@@ -277,34 +264,6 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // ------------------------------------------------------------------ MMA issuer
         uint32_t s = 0, ph = 0, j = 0, jph = 0, tile_i = 0;      // operand stage / scale slot and their phases
         bool ok = true;
-        // SF_BY_CP: this thread also copies the scales shared -> tensor memory (tcgen05.cp reads a
-        // tile once for all four lane quadrants; the mover warps read it four times), one stage
-        // ahead of the MMAs that use them, so that the copy runs under the previous stage's MMAs.
-        uint32_t cj = 0, cjph = 0;                                // slot / phase of the next scales to copy
-        int64_t to_copy = 0;
-        if (SF_BY_CP && !dbg_no_load && !dbg_no_sf) {
-            const int64_t my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-            to_copy = my_tiles * k_tiles;
-        }
-        auto copy_next_scales = [&]() {
-            if (to_copy == 0) return;
-            --to_copy;
-            ok = mbar_wait(sf_full_bar + 8 * cj, cjph, abort_flag, p.status, 5);
-            if (!ok) return;
-            tc_fence_after();
-            const uint32_t src = sf_base + cj * C::SF_SLOT_BYTES, dst = tmem_base + SF_COL0 + cj * C::SF_STAGE_COLS;
-            // tiles: 32 rows of 16 bytes, 8-row groups 128 bytes apart, no swizzle
-#pragma unroll
-            for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
-                tc_copy_sf(dst + 4 * kb, smem_desc(src + kb * SF_TILE_BYTES, 0, 128, 0));
-#pragma unroll
-                for (int g = 0; g < C::N_GROUPS; ++g)
-                    tc_copy_sf(dst + 16 + (BLOCK_N / 32) * kb + 4 * g,
-                               smem_desc(src + SFA_BYTES + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES, 0, 128, 0));
-            }
-            if (++cj == C::SF_SLOTS) { cj = 0; cjph ^= 1u; }
-        };
-        copy_next_scales();                                       // scales of the very first stage
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
             int64_t mb, nb;
             tile_coords(t, num_m, num_n, mb, nb);
@@ -317,13 +276,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
             for (int64_t kt = 0; kt < k_tiles; ++kt) {
-                if (SF_BY_CP) {
-                    copy_next_scales();                           // of the stage after this one
-                    if (!ok) break;
-                }
                 if (!dbg_no_load) {
                     ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
-                    if (ok && !dbg_no_sf && !SF_BY_CP) ok = mbar_wait(sf_ready_bar + 8 * j, jph, abort_flag, p.status, 5);
+                    if (ok && !dbg_no_sf) ok = mbar_wait(sf_ready_bar + 8 * j, jph, abort_flag, p.status, 5);
                 }
                 if (!ok) break;
                 tc_fence_after();
@@ -421,7 +376,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
             }
         }
-    } else if (!SF_BY_CP && warp >= 10 && warp < 14 && !dbg_no_load && !dbg_no_sf) {
+    } else if (warp >= 10 && warp < 14 && !dbg_no_load && !dbg_no_sf) {
         // ------------------------------------------------------------------ scale movers
         const int quad = warp & 3;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
@@ -483,37 +438,48 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 //
 // Two CTAs of a cluster (two SMs) compute one 256 x 256 tile with cta_group::2 MMAs: CTA r of
 // the pair holds rows m0 + 128 r .. of A and rows n0 + 128 r .. of B in its shared memory,
-// and the tensor cores of both SMs read both halves of B. Per stage an SM fetches 38 KB from
-// L2 instead of the single-CTA kernel's 54 KB for the same number of multiply-adds, and reads a
-// third less from shared memory per MMA. Only the even CTA (the leader) issues MMAs; both
-// CTAs run a TMA producer, scale movers and an epilogue for their own 128 rows of the tile.
-// Measured slower than the single-CTA kernel so far: every hand-over between the two SMs
-// (relay, remote arrive, multicast commit) lengthens the load round trip, which five stages
-// do not cover. Remote arrives use the default (CTA-scope release) form: the cluster-scope
-// release form cost about a microsecond each.
+// and the tensor cores of both SMs read both halves of B. Per MMA an SM moves a third less
+// through shared memory than the single-CTA kernel, whose limit that is. Only the even CTA (the
+// leader) issues MMAs; both CTAs run the two TMA producers, scale movers and an epilogue for their
+// own 128 rows of the tile, with the same roles per warp as the single-CTA kernel.
 //
-//   full[s]      one per CTA: this CTA's operand tiles have landed
-//   peer_full[s] leader's barrier, 1 arrival: a relay thread in the peer saw the peer's full[s]
-//   sf_full[s]   one per CTA: this CTA's scale tiles have landed in its shared memory
-//   sf_ready[s]  leader's barrier, 8 arrivals: the four mover warps of each CTA have written
-//                the stage's scales into their own CTA's tensor memory
-//   empty[s]     one per CTA, released in both CTAs by the leader's tcgen05.commit
-//   acc_full     one per CTA, same mechanism
+//   full[s]      leader's barrier: one arrive.expect_tx by the leader's producer for the bytes of
+//                BOTH CTAs; the peer's TMA loads complete on it too (cta_group::2 form of the copy)
+//   empty[s]     one per CTA, released in both CTAs by the leader's multicast tcgen05.commit
+//   sf_full[j]   one per CTA: this CTA's scale tiles have landed in its shared memory
+//   sf_ready[j]  leader's barrier, 8 arrivals: the four mover warps of each CTA have written
+//                the slot's scales into their own CTA's tensor memory
+//   acc_full     one per CTA, multicast commit
 //   acc_empty    leader's barrier, 16 arrivals: 8 epilogue warps of each CTA
+//
+// Barriers that the other SM arrives on are polled (test_wait) by their single waiting thread: a
+// thread suspended in try_wait did not see such arrivals promptly. Remote arrives use the
+// default (CTA-scope release) form: the cluster-scope release form cost about a microsecond each.
 namespace pair {
 
 constexpr int TILE_N = 256;
 constexpr int B_HALF_BYTES = 128 * BLOCK_K_BYTES;                         // this CTA's 128 rows of B
+constexpr int STAGE_BYTES = A_BYTES + B_HALF_BYTES;                       // 32 KiB
 constexpr int SFB_BYTES = 2 * KB_PER_STAGE * SF_TILE_BYTES;               // scales of all 256 B rows
-constexpr int STAGE_BYTES = A_BYTES + B_HALF_BYTES + SFA_BYTES + SFB_BYTES;  // 38 KiB
-constexpr int STAGES = 5;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-constexpr int EPI_WARPS = 8, MOVER_WARPS = 4;
-constexpr int THREADS = 64 + 32 * (EPI_WARPS + MOVER_WARPS);
+constexpr int SF_SLOT_BYTES = SFA_BYTES + SFB_BYTES;                      // 6 KiB
+constexpr int STAGES = 6;
+constexpr int SF_SLOTS = 5;                                               // what tensor memory has room for
+constexpr int BARRIER_BYTES = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SF_SLOTS * SF_SLOT_BYTES + 1024 + BARRIER_BYTES;
+constexpr int THREADS = 512;
 constexpr int SF_STAGE_COLS = 16 + 32;                                    // A scales, B scales
 static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
-static_assert(SF_COL0 + STAGES * SF_STAGE_COLS <= TMEM_COLS, "scale ring does not fit tensor memory");
+static_assert(SF_COL0 + SF_SLOTS * SF_STAGE_COLS <= TMEM_COLS, "scale ring does not fit tensor memory");
+static_assert(SMEM_BYTES <= 232448, "more shared memory than a CTA can have");
+static_assert((2 * STAGES + 2 * SF_SLOTS + 2) * 8 + 8 <= BARRIER_BYTES, "barrier area too small");
+static_assert(SF_SLOTS <= STAGES, "the scale producer's wait assumes no more slots than stages");
 
+// TMA tile load whose completion is signalled on a barrier of either CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(cluster_bar) : "memory");
+}
 
 template <typename OUT>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -523,15 +489,15 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + STAGES * STAGE_BYTES);
-    const uint32_t full_bar = smem_u32(bars);                 // [STAGES] this CTA's operand tiles landed
+    const uint32_t sf_base = smem_base + STAGES * STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + STAGES * STAGE_BYTES + SF_SLOTS * SF_SLOT_BYTES);
+    const uint32_t full_bar = smem_u32(bars);                 // [STAGES], used in the leader only
     const uint32_t empty_bar = full_bar + 8 * STAGES;         // [STAGES]
-    const uint32_t sf_full_bar = empty_bar + 8 * STAGES;      // [STAGES]
-    const uint32_t sf_ready_bar = sf_full_bar + 8 * STAGES;   // [STAGES], used in the leader only
-    const uint32_t peer_full_bar = sf_ready_bar + 8 * STAGES; // [STAGES], leader only: the peer's tiles landed
-    const uint32_t acc_full_bar = peer_full_bar + 8 * STAGES;
+    const uint32_t sf_full_bar = empty_bar + 8 * STAGES;      // [SF_SLOTS]
+    const uint32_t sf_ready_bar = sf_full_bar + 8 * SF_SLOTS; // [SF_SLOTS], used in the leader only
+    const uint32_t acc_full_bar = sf_ready_bar + 8 * SF_SLOTS;
     const uint32_t acc_empty_bar = acc_full_bar + 8;          // used in the leader only
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 5 * STAGES + 2);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2 * SF_SLOTS + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -542,12 +508,13 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar + 8 * s, 1);
             mbar_init(empty_bar + 8 * s, 1);
-            mbar_init(sf_full_bar + 8 * s, 1);
-            mbar_init(sf_ready_bar + 8 * s, 2 * MOVER_WARPS);
-            mbar_init(peer_full_bar + 8 * s, 1);
+        }
+        for (int j = 0; j < SF_SLOTS; ++j) {
+            mbar_init(sf_full_bar + 8 * j, 1);
+            mbar_init(sf_ready_bar + 8 * j, 8);
         }
         mbar_init(acc_full_bar, 1);
-        mbar_init(acc_empty_bar, 2 * EPI_WARPS);
+        mbar_init(acc_empty_bar, 16);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -572,34 +539,56 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const bool dbg_no_mma = p.debug & 16;
 
     if (warp == 0 && lane == 0 && !dbg_no_load) {
-        // ------------------------------------------------------------------ TMA producer (both CTAs)
-        uint32_t it = 0;
+        // ------------------------------------------------------------------ TMA producer: operands (both CTAs)
+        const uint32_t leader_full = map_to_cta(full_bar, 0);
+        uint32_t s = 0, ph = 0;
         bool ok = true;
         for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
             int64_t mb, nb;
             tile_coords(t, num_m, num_n, mb, nb);
-            const int m0 = static_cast<int>(mb * 256 + rank * 128), n0 = static_cast<int>(nb * TILE_N);
-            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
-                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+            const int m0 = static_cast<int>(mb * 256 + rank * 128), n0 = static_cast<int>(nb * TILE_N + rank * 128);
+            for (int64_t kt = 0; kt < k_tiles; ++kt) {
                 ok = mbar_wait_poll(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 1);
                 if (!ok) break;
-                const uint32_t stage = smem_base + s * STAGE_BYTES;
-                const int kb0 = static_cast<int>(kt * KB_PER_STAGE);
-                // out-of-range parts of a box are zero-filled and still counted: fixed byte counts
-                if (!dbg_no_sf) {
-                    const uint32_t sf_bar = sf_full_bar + 8 * s;
-                    mbar_expect_tx(sf_bar, SFA_BYTES + SFB_BYTES);
-                    tma_load_3d(stage + A_BYTES + B_HALF_BYTES, &map_sfa, 0, kb0, m0 / 128, sf_bar);
-                    tma_load_3d(stage + A_BYTES + B_HALF_BYTES + SFA_BYTES, &map_sfb, 0, kb0, n0 / 128, sf_bar);
+                const uint32_t stage = smem_base + s * STAGE_BYTES, bar = leader_full + 8 * s;
+                // out-of-range parts of a box are zero-filled and still counted: fixed byte counts.
+                // The leader announces the bytes of both CTAs; its barrier may see the peer's bytes
+                // first, which only makes the pending count negative for a moment.
+                if (leader) mbar_expect_tx(full_bar + 8 * s, 2 * STAGE_BYTES);
+                tma_load_2d_pair(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), m0, bar);
+                tma_load_2d_pair(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES), n0, bar);
+                if (++s == STAGES) { s = 0; ph ^= 1u; }
+            }
+        }
+        if (!ok) {
+            const unsigned long long t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+    } else if (warp == 15 && lane == 0 && !dbg_no_load && !dbg_no_sf) {
+        // ------------------------------------------------------------------ TMA producer: scales (both CTAs)
+        uint32_t j = 0;
+        bool ok = true;
+        int64_t i = 0;                                   // stage counter over all tiles of this pair
+        for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
+            int64_t mb, nb;
+            tile_coords(t, num_m, num_n, mb, nb);
+            const int a_group = static_cast<int>(mb * 2 + rank), b_group = static_cast<int>(nb * 2);
+            for (int64_t kt = 0; kt < k_tiles; ++kt, ++i) {
+                if (i >= SF_SLOTS) {
+                    // the slot is free when the MMAs of the stage SF_SLOTS back are done; the next
+                    // completion of that stage's barrier needs the scales requested here, so the
+                    // parity cannot be lapped
+                    const int64_t k = i - SF_SLOTS;
+                    ok = mbar_wait_poll(empty_bar + 8 * static_cast<uint32_t>(k % STAGES),
+                                        static_cast<uint32_t>(k / STAGES) & 1u, abort_flag, p.status, 7);
+                    if (!ok) break;
                 }
-                // each CTA's operand tiles complete on its OWN barrier; the peer relays completion to
-                // the leader with one remote arrive per stage (letting the peer's TMA loads signal
-                // the leader's barrier directly made every stage about 0.4 us slower when measured)
-                const uint32_t bar = full_bar + 8 * s;
-                mbar_expect_tx(bar, A_BYTES + B_HALF_BYTES);
-                tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), m0, bar);
-                tma_load_2d(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES),
-                            n0 + static_cast<int>(rank) * 128, bar);
+                const int kb0 = static_cast<int>(kt * KB_PER_STAGE);
+                const uint32_t dst = sf_base + j * SF_SLOT_BYTES, bar = sf_full_bar + 8 * j;
+                mbar_expect_tx(bar, SF_SLOT_BYTES);
+                tma_load_3d(dst, &map_sfa, 0, kb0, a_group, bar);
+                tma_load_3d(dst + SFA_BYTES, &map_sfb, 0, kb0, b_group, bar);
+                if (++j == SF_SLOTS) j = 0;
             }
         }
         if (!ok) {
@@ -609,18 +598,16 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     } else if (warp == 1 && lane == 0 && leader) {
         // ------------------------------------------------------------------ MMA issuer (leader only)
         const uint32_t idesc = mma_idesc(TILE_N, 256);
-        uint32_t it = 0, tile_i = 0;
+        uint32_t s = 0, ph = 0, j = 0, jph = 0, tile_i = 0;
         bool ok = true;
         for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs, ++tile_i) {
             ok = mbar_wait_poll(acc_empty_bar, (tile_i & 1u) ^ 1u, abort_flag, p.status, 3);
             if (!ok) break;
             tc_fence_after();
-            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
-                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+            for (int64_t kt = 0; kt < k_tiles; ++kt) {
                 if (!dbg_no_load) {
-                    ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
-                    if (ok) ok = mbar_wait_poll(peer_full_bar + 8 * s, ph, abort_flag, p.status, 7);
-                    if (ok && !dbg_no_sf) ok = mbar_wait_poll(sf_ready_bar + 8 * s, ph, abort_flag, p.status, 5);
+                    ok = mbar_wait_poll(full_bar + 8 * s, ph, abort_flag, p.status, 2);
+                    if (ok && !dbg_no_sf) ok = mbar_wait_poll(sf_ready_bar + 8 * j, jph, abort_flag, p.status, 5);
                 }
                 if (!ok) break;
                 tc_fence_after();
@@ -629,81 +616,104 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const uint32_t stage = smem_base + s * STAGE_BYTES;
                 const uint64_t a_desc = smem_desc(stage, 16, 1024, 2);
                 const uint64_t b_desc = smem_desc(stage + A_BYTES, 16, 1024, 2);
-                const uint32_t sfa_tmem = tmem_base + SF_COL0 + s * SF_STAGE_COLS, sfb_tmem = sfa_tmem + 16;
+                const uint32_t sfa_tmem = tmem_base + SF_COL0 + j * SF_STAGE_COLS, sfb_tmem = sfa_tmem + 16;
                 for (int kb = 0; kb < nkb && !dbg_no_mma; ++kb)
                     tc_mma_nvf4_pair(tmem_base, a_desc + 2 * kb, b_desc + 2 * kb, idesc, sfa_tmem + 4 * kb,
                                      sfb_tmem + 8 * kb, (kt > 0 || kb > 0) ? 1u : 0u);
                 tc_commit_pair(empty_bar + 8 * s);
+                if (++s == STAGES) { s = 0; ph ^= 1u; }
+                if (++j == SF_SLOTS) { j = 0; jph ^= 1u; }
             }
             if (ok) tc_commit_pair(acc_full_bar);
         }
-    } else if (warp == 1 && lane == 0 && !leader && !dbg_no_load) {
-        // ------------------------------------------------------------------ relay (peer only)
-        const uint32_t leader_peer_full = map_to_cta(peer_full_bar, 0);
-        uint32_t it = 0;
-        bool ok = true;
-        for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
-            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
-                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 8);
-                if (!ok) break;
-                mbar_arrive_cluster(leader_peer_full + 8 * s);
-            }
-        }
-    } else if (warp >= 2 && warp < 2 + EPI_WARPS) {
+    } else if (warp >= 2 && warp < 10) {
         // ------------------------------------------------------------------ epilogue (both CTAs)
         const int quad = warp & 3;                       // tensor-memory lanes 32*quad .. +31
         const int half = (warp - 2) >> 2;                // which 128 of the 256 columns
+        constexpr int COLS = 128;
         const float alpha = __ldg(p.alpha);
         OUT *out = static_cast<OUT *>(p.d);
         const bool vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((p.ldd * sizeof(OUT)) % 16 == 0);
+        const bool vec32_ok = FOS_GEMM_ST256 && (reinterpret_cast<uintptr_t>(out) % 32 == 0) && ((p.ldd * sizeof(OUT)) % 32 == 0);
         const uint32_t leader_acc_empty = map_to_cta(acc_empty_bar, 0);
         uint32_t tile_i = 0;
         bool ok = true;
         for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs, ++tile_i) {
             int64_t mb, nb;
             tile_coords(t, num_m, num_n, mb, nb);
-            const int64_t row = mb * 256 + rank * 128 + quad * 32 + lane, n0 = nb * TILE_N + half * 128;
+            const int64_t row = mb * 256 + rank * 128 + quad * 32 + lane, n0 = nb * TILE_N + half * COLS;
             // in the peer this barrier is arrived on from the leader's SM: one lane polls for the warp
             if (lane == 0) ok = mbar_wait_poll(acc_full_bar, tile_i & 1u, abort_flag, p.status, 4);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             tc_fence_after();
-            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + half * 128;
+            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + half * COLS;
             const bool row_ok = row < p.m && !dbg_no_store;
-#pragma unroll 1
-            for (int c = 0; c < 4; c += 2) {
-                uint32_t v0[32], v1[32];
-                tc_load_64cols_sync(t_acc + 32 * c, v0, v1);
-                if (c + 2 >= 4) {                        // everything is in registers: release the accumulator
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+            if constexpr (sizeof(OUT) == 2) {
+                uint32_t pk[COLS / 2];
+#pragma unroll
+                for (int c = 0; c < COLS / 32; ++c) {
+                    uint32_t v[32];
+                    tc_load_32cols_sync(t_acc + 32 * c, v);
+                    if (c + 1 == COLS / 32) {            // everything is in registers: release the accumulator
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        pk[16 * c + i] = pack_pair<OUT>(alpha * __uint_as_float(v[2 * i]), alpha * __uint_as_float(v[2 * i + 1]));
                 }
-                const int64_t col = n0 + 32 * c;
-                const int64_t left0 = p.n - col, left1 = left0 - 32;
-                if (row_ok && left0 > 0)
-                    store_chunk<OUT>(out + row * p.ldd + col, v0, alpha, left0 < 32 ? static_cast<int>(left0) : 32, vec_ok);
-                if (row_ok && left1 > 0)
-                    store_chunk<OUT>(out + row * p.ldd + col + 32, v1, alpha, left1 < 32 ? static_cast<int>(left1) : 32, vec_ok);
+                const int64_t left = p.n - n0;
+                if (row_ok && left > 0) {
+                    OUT *dst = out + row * p.ldd + n0;
+                    if (left >= COLS && vec32_ok) {
+#pragma unroll
+                        for (int i = 0; i < COLS / 16; ++i) stg_32(reinterpret_cast<uint8_t *>(dst) + 32 * i, &pk[8 * i]);
+                    } else if (left >= COLS && vec_ok) {
+#pragma unroll
+                        for (int i = 0; i < COLS / 8; ++i)
+                            reinterpret_cast<uint4 *>(dst)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                    } else {
+                        uint16_t *d16 = reinterpret_cast<uint16_t *>(dst);
+#pragma unroll
+                        for (int i = 0; i < COLS; ++i)
+                            if (i < left) d16[i] = static_cast<uint16_t>(pk[i >> 1] >> ((i & 1) * 16));
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < 4; c += 2) {
+                    uint32_t v0[32], v1[32];
+                    tc_load_64cols_sync(t_acc + 32 * c, v0, v1);
+                    if (c + 2 >= 4) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+                    }
+                    const int64_t col = n0 + 32 * c;
+                    const int64_t left0 = p.n - col, left1 = left0 - 32;
+                    if (row_ok && left0 > 0)
+                        store_chunk<OUT>(out + row * p.ldd + col, v0, alpha, left0 < 32 ? static_cast<int>(left0) : 32, vec_ok);
+                    if (row_ok && left1 > 0)
+                        store_chunk<OUT>(out + row * p.ldd + col + 32, v1, alpha, left1 < 32 ? static_cast<int>(left1) : 32, vec_ok);
+                }
             }
         }
-    } else if (warp >= 2 + EPI_WARPS && !dbg_no_load && !dbg_no_sf) {
+    } else if (warp >= 10 && warp < 14 && !dbg_no_load && !dbg_no_sf) {
         // ------------------------------------------------------------------ scale movers (both CTAs)
         const int quad = warp & 3;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
         const uint32_t leader_sf_ready = map_to_cta(sf_ready_bar, 0);
-        uint32_t it = 0;
+        uint32_t j = 0, jph = 0;
         bool ok = true;
         for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
-            for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
-                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                ok = mbar_wait(sf_full_bar + 8 * s, ph, abort_flag, p.status, 6);
+            for (int64_t kt = 0; kt < k_tiles; ++kt) {
+                ok = mbar_wait(sf_full_bar + 8 * j, jph, abort_flag, p.status, 6);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                const uint32_t stage = smem_base + s * STAGE_BYTES;
-                const uint32_t sfa_smem = stage + A_BYTES + B_HALF_BYTES + lane * 16, sfb_smem = sfa_smem + SFA_BYTES;
-                const uint32_t slot = lane_base + SF_COL0 + s * SF_STAGE_COLS;
+                const uint32_t sfa_smem = sf_base + j * SF_SLOT_BYTES + lane * 16, sfb_smem = sfa_smem + SFA_BYTES;
+                const uint32_t slot = lane_base + SF_COL0 + j * SF_STAGE_COLS;
                 uint32_t r[16];
                 // tiles beyond K were zero-filled by the TMA unit, so all four K-blocks can be copied
 #pragma unroll
@@ -713,20 +723,21 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 }
                 tc_store_16cols(slot, r);
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
+                for (int hf = 0; hf < 2; ++hf) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        const int col = half * 16 + q * 4;     // column inside the B part: 8 per K-block
+                        const int col = hf * 16 + q * 4;       // column inside the B part: 8 per K-block
                         const int kb = col / 8, g = (col % 8) / 4;
                         const uint4 v = lds_16(sfb_smem + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES);
                         r[4 * q] = v.x; r[4 * q + 1] = v.y; r[4 * q + 2] = v.z; r[4 * q + 3] = v.w;
                     }
-                    tc_store_16cols(slot + 16 + half * 16, r);
+                    tc_store_16cols(slot + 16 + hf * 16, r);
                 }
                 tc_wait_store();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(leader_sf_ready + 8 * s);
+                if (lane == 0) mbar_arrive_cluster(leader_sf_ready + 8 * j);
+                if (++j == SF_SLOTS) { j = 0; jph ^= 1u; }
             }
         }
     }
