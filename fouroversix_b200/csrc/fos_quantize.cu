@@ -145,11 +145,15 @@ __device__ __forceinline__ void encode_e2m1(const float (&v)[16], float r, bool 
 // E2M1 codes of eight scaled values v[i] * r (as encode_e2m1 without the guard) and the
 // rounding residuals t[i] = q[i] - v[i] * r, each one IEEE subtraction of the binary32
 // scaled value from the binary16 code value.
-__device__ __forceinline__ uint32_t encode8_with_residuals(const float *v, uint64_t r2, float (&t)[8]) {
+__device__ __forceinline__ uint32_t encode8_with_residuals(const float *v, uint64_t r2, float (&t)[8], uint64_t *scaled = nullptr) {
     float x[8];
     const uint64_t zero2 = pack2(0.0f, 0.0f);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) unpack2f(fma2(pack2(v[2 * k], v[2 * k + 1]), r2, zero2), x[2 * k], x[2 * k + 1]);
+    for (int k = 0; k < 4; ++k) {
+        const uint64_t xs = fma2(pack2(v[2 * k], v[2 * k + 1]), r2, zero2);
+        if (scaled != nullptr) scaled[k] = xs;
+        unpack2f(xs, x[2 * k], x[2 * k + 1]);
+    }
     uint32_t codes;
     asm("{ .reg .b8 b0, b1, b2, b3;\n"
         ".reg .b32 h;\n"
@@ -190,6 +194,26 @@ __device__ __forceinline__ void encode_int4(const float (&v)[16], float r, uint3
         t = fminf(fmaxf(t, -7.0f), 7.0f);
         int q = __float2int_rn(t);
         w[i >> 3] |= (static_cast<uint32_t>(q) & 0xfu) << ((i & 7) * 4);
+    }
+    lo = w[0];
+    hi = w[1];
+}
+
+// The same codes for |v * r * (7/6)| < 7.5 (no clamp needed), without float-to-int conversions:
+// adding 1.5 * 2^23 rounds to the nearest integer (ties to even) and leaves it, in two's
+// complement, in the low mantissa bits.
+__device__ __forceinline__ void encode_int4_small(const float (&v)[16], float r, uint32_t &lo, uint32_t &hi) {
+    const uint64_t r2 = pack2(r, r), zero2 = pack2(0.0f, 0.0f), one2 = pack2(1.0f, 1.0f);
+    const uint64_t to_int2 = pack2(1.16666666f, 1.16666666f), magic2 = pack2(12582912.0f, 12582912.0f);
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const uint64_t xs = fma2(pack2(v[2 * k], v[2 * k + 1]), r2, zero2);
+        const uint64_t qm = fma2(fma2(xs, to_int2, zero2), one2, magic2);
+        float a, b;
+        unpack2f(qm, a, b);
+        const uint32_t pair = (__float_as_uint(a) & 0xfu) | ((__float_as_uint(b) & 0xfu) << 4);
+        w[k >> 2] |= pair << ((k & 3) * 8);
     }
     lo = w[0];
     hi = w[1];
@@ -473,7 +497,103 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
         return;
     }
 
-    // IF4: one scale; E2M1 grid versus INT4 grid scaled by 6/7
+    // IF4: one scale; E2M1 grid versus INT4 grid scaled by 6/7.
+    //
+    // Fast pre-filter, as for NVFP4 (same conditions, from the same table entry), in units of
+    // G = s * amax / 2688. Float grid: the reference's term is t_f + eta, t_f = q_f - x*r,
+    // |eta| <= 47u as above. Integer grid: q_i = rint(u), u = (x*r) * fl(7/6), |u| < 7.5 whenever
+    // |x*r| <= 6.42 (checked), so no clamp; with d = q_i - u (exact: a multiple of ulp(u) below 1)
+    // the reference's term ((q_i * s) * amax * fl(6/7)) / 2688 - x is (6/7) * d + eta_i in units
+    // of G with |eta_i| <= 24u (three roundings and the constant, |deq| <= 6 G) + 45u (x*r against
+    // x/G: five roundings, the constant 7/6 and one product, |x*r| <= 6.4) + 1u < 80u. Hence
+    // err_i differs from (6/7)^2 * sum(d^2) * G^2 by at most 2 * 80u * sum|t| <= 640u * sqrt(S_i)
+    // <= 320u * (S_i + 1), plus 40u relative for the summations; likewise 188u * (S_f + 1) + 40u.
+    // The two candidates share G, so the comparison is made on S_i and S_f themselves.
+    const bool if4_eligible = KIND == KIND_IF4 && !TWO_D && ea.w >= 0.0f && __fmul_rn(bmax, r_a) <= 6.42f;
+    bool if4_decided = false, pick_int_fast = false;
+    uint32_t cf[2] = {0u, 0u};
+    if (if4_eligible) {
+        const uint64_t r2 = pack2(r_a, r_a), zero2 = pack2(0.0f, 0.0f), one2 = pack2(1.0f, 1.0f), minus2 = pack2(-1.0f, -1.0f);
+        const uint64_t to_int2 = pack2(1.16666666f, 1.16666666f), magic2 = pack2(12582912.0f, 12582912.0f);
+        const uint64_t unmagic2 = pack2(-12582912.0f, -12582912.0f);
+        uint64_t acc_f = zero2, acc_i = zero2;
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+            float tf[8];
+            uint64_t xs[4];
+            cf[w] = encode8_with_residuals(&v[8 * w], r2, tf, xs);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint64_t pf = pack2(tf[2 * k], tf[2 * k + 1]);
+                acc_f = fma2(pf, pf, acc_f);
+                const uint64_t u = fma2(xs[k], to_int2, zero2);                    // (x*r) * fl(7/6), as the reference rounds it
+                const uint64_t q = fma2(fma2(u, one2, magic2), one2, unmagic2);    // rint(u), ties to even
+                const uint64_t d = fma2(u, minus2, q);                            // q - u, exact
+                acc_i = fma2(d, d, acc_i);
+            }
+        }
+        float f0, f1, i0, i1;
+        unpack2f(acc_f, f0, f1);
+        unpack2f(acc_i, i0, i1);
+        const float from_int = 0.8571428571f;
+        const float s_f = f0 + f1, s_i = (i0 + i1) * (from_int * from_int);
+        const float tau = 0x1p-24f * 1.5f * (360.0f * s_i + 228.0f * s_f + 508.0f);
+        const float diff = s_i - s_f;
+        if4_decided = fabsf(diff) > tau;
+        pick_int_fast = diff < 0.0f;
+    }
+    // undecided blocks (ties, mostly): the whole warp evaluates one block at a time exactly, lane
+    // 16c + i taking element i under candidate c (0: float grid, 1: integer grid), as for NVFP4
+    if (KIND == KIND_IF4 && coop != nullptr) {
+        unsigned pending = __ballot_sync(FULL, if4_eligible && !if4_decided);
+        while (pending) {
+            const int src = __ffs(pending) - 1;
+            pending &= pending - 1;
+            if (lane == src) {
+                float4 *x4 = reinterpret_cast<float4 *>(coop);
+                x4[0] = make_float4(v[0], v[1], v[2], v[3]);
+                x4[1] = make_float4(v[4], v[5], v[6], v[7]);
+                x4[2] = make_float4(v[8], v[9], v[10], v[11]);
+                x4[3] = make_float4(v[12], v[13], v[14], v[15]);
+                x4[4] = make_float4(s_a, r_a, 0.0f, 0.0f);
+            }
+            __syncwarp();
+            const int cand = lane >> 4, i = lane & 15;
+            const float x = coop[i], s = coop[16], r = coop[17];
+            const float xs = __fmaf_rn(x, r, 0.0f);
+            float t;
+            if (cand == 0) {
+                t = __fmul_rn(__fmul_rn(e2m1x2_to_float2(cvt_e2m1x2(0.0f, xs)).x, s), amax);
+            } else {
+                const float q = rintf(fminf(fmaxf(__fmul_rn(xs, 1.16666666f), -7.0f), 7.0f));
+                t = __fmul_rn(__fmul_rn(__fmul_rn(q, s), amax), 0.8571428571f);
+            }
+            const float d = __fsub_rn(__fdiv_rn(t, 2688.0f), x);
+            const float e = __fmul_rn(d, d);
+            const float p = __fadd_rn(e, __shfl_down_sync(FULL, e, 8));          // valid in lanes with i < 8
+            float total = __shfl_sync(FULL, p, cand * 16);
+#pragma unroll
+            for (int k = 1; k < 8; ++k) total = __fadd_rn(total, __shfl_sync(FULL, p, cand * 16 + k));
+            const float exact_f = __shfl_sync(FULL, total, 0), exact_i = __shfl_sync(FULL, total, 16);
+            if (lane == src) {
+                if4_decided = true;
+                pick_int_fast = exact_i < exact_f;
+            }
+            __syncwarp();
+        }
+    }
+    if (if4_eligible && if4_decided) {
+        if (pick_int_fast) {
+            encode_int4_small(v, r_a, lo, hi);
+            sf_byte = sfb_a + 128u;
+        } else {
+            lo = cf[0];
+            hi = cf[1];
+            sf_byte = sfb_a;
+        }
+        return;
+    }
+
     uint32_t lo_f = 0u, hi_f = 0u, lo_i = 0u, hi_i = 0u;
     if (s_a != 0.0f) {
         encode_e2m1(v, r_a, true, lo_f, hi_f);
@@ -818,28 +938,151 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// ------------------------------------------------------------------------------------
+// transposed input, 1-D blocks, fed by the TMA unit
+// ------------------------------------------------------------------------------------
+//
+// Y = x^T: a block of Y is 16 consecutive ROWS of x at one column. One tile of Y (128 rows x 64
+// columns) is 64 rows x 128 columns of x, fetched as one 16 KB box (256-byte rows, no swizzle: a
+// warp reads 32 neighbouring 2-byte elements of one x row at a time, which is conflict-free).
+// Consumer thread t owns row t % 128 of the tile and the two blocks 2 * (t / 128) and the next:
+// 16 bytes of codes and 2 scale bytes per tile, both contiguous. Everything else (ring, table,
+// cooperative fallback, launch chain) is as in quantize_rows_tma_kernel.
+
+constexpr int COLS_BOX_ROWS = 64, COLS_BOX_BYTES = 256;
+
+template <typename T, int KIND>
+__global__ void __launch_bounds__(FEED_THREADS, FOS_FEED_CTAS)
+quantize_cols_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantParams p) {
+    extern __shared__ uint8_t feed_smem_raw[];
+    __shared__ float4 lut[128];
+    __shared__ __align__(16) float coop[FEED_CONSUMERS / 32][20];
+    __shared__ __align__(8) uint64_t full_bar[FEED_STAGES], empty_bar[FEED_STAGES];
+    __shared__ int abort_flag;
+
+    const uint32_t stage0 = (smem_u32(feed_smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // tiles of Y: tiles_r along its rows (x's columns), tiles_c along its columns (x's rows);
+    // neighbours in the order of processing are neighbours along x's rows
+    const int tiles_r = static_cast<int>(p.rows_p >> 7), tiles_c = static_cast<int>(p.cols_p >> 6);
+    const int64_t n_tiles = static_cast<int64_t>(tiles_c) * tiles_r;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+#pragma unroll
+        for (int s = 0; s < FEED_STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), FEED_CONSUMERS / 32);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int step_c = static_cast<int>(gridDim.x) / tiles_r, step_r = static_cast<int>(gridDim.x) % tiles_r;
+    int tc_ = static_cast<int>(blockIdx.x) / tiles_r, tr = static_cast<int>(blockIdx.x) % tiles_r;
+    const int my_tiles = static_cast<int>((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
+
+    if (warp == FEED_CONSUMERS / 32) {
+        // ---------------- producer ----------------
+        if (lane != 0) return;
+        if (!p.x_is_ready) asm volatile("griddepcontrol.wait;" ::: "memory");
+        int issued = 0, s = 0;
+        uint32_t parity = 1;
+        for (; issued < my_tiles; ++issued) {
+            if (issued >= FEED_STAGES && !mbar_wait(smem_u32(&empty_bar[s]), parity, &abort_flag, &g_wait_failures, 3))
+                break;
+            mbar_expect_tx(smem_u32(&full_bar[s]), FEED_STAGE_BYTES);
+            tma_load_2d(stage0 + s * FEED_STAGE_BYTES, &map_x, tr * COLS_BOX_BYTES, tc_ * COLS_BOX_ROWS, smem_u32(&full_bar[s]));
+            if (++s == FEED_STAGES) { s = 0; parity ^= 1u; }
+            tc_ += step_c;
+            tr += step_r;
+            if (tr >= tiles_r) { tr -= tiles_r; ++tc_; }
+        }
+        for (int j = issued > FEED_STAGES ? issued - FEED_STAGES : 0; j < issued; ++j) {
+            const uint32_t bar = smem_u32(&full_bar[j % FEED_STAGES]);
+            const uint32_t landed = static_cast<uint32_t>(j / FEED_STAGES) & 1u;
+            const unsigned long long t0 = global_timer_ns();
+            while (!mbar_try_wait(bar, landed) && global_timer_ns() - t0 < WAIT_LIMIT_NS) {}
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(p.amax), p.rule);
+    if (p.amax_store != nullptr && threadIdx.x == 0 && blockIdx.x == 0) *p.amax_store = tc.amax;
+    if (threadIdx.x < 128)
+        lut[threadIdx.x] = scale_entry(threadIdx.x, tc, p.rule == FOS_RULE_MSE && !p.exact_only && tc.filter_ok);
+    asm volatile("bar.sync 1, %0;" ::"n"(FEED_CONSUMERS) : "memory");
+
+    const int jr = threadIdx.x & 127, pair = threadIdx.x >> 7;          // row of the tile, which two of its four blocks
+    const int64_t code_ld = p.cols_p >> 1, n_cb = p.cols_p >> 4;
+    uint32_t src = stage0 + static_cast<uint32_t>(pair * 32 * COLS_BOX_BYTES + jr * 2);
+    uint8_t *code_ptr = p.codes + jr * code_ld + pair * 16;
+    uint8_t *sf_ptr = p.sf + (p.sf_tiled ? (jr & 31) * 16 + (jr >> 5) * 4 + pair * 2 : jr * n_cb + pair * 2);
+    asm volatile("" : "+r"(src), "+l"(code_ptr), "+l"(sf_ptr));
+
+    int s = 0;
+    uint32_t parity = 0;
+    for (int k = 0; k < my_tiles; ++k) {
+        if (!mbar_wait(smem_u32(&full_bar[s]), parity, &abort_flag, &g_wait_failures, 4)) break;
+        uint8_t *codes = code_ptr + static_cast<int64_t>(tr) * 128 * code_ld + tc_ * 32;
+        uint8_t *sf = sf_ptr + (p.sf_tiled ? (static_cast<int64_t>(tr) * tiles_c + tc_) * 512
+                                           : static_cast<int64_t>(tr) * 128 * n_cb + tc_ * 4);
+        const uint32_t stage = src + s * FEED_STAGE_BYTES;
+        uint32_t words[4], sf_pair = 0u;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                uint16_t h;
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(stage + (j * 16 + i) * COLS_BOX_BYTES));
+                v[i] = elem_to_float<T>(reinterpret_cast<const T &>(h));
+            }
+            uint32_t lo, hi, sf_byte;
+            quantize_block<KIND, false, false>(v, tc, p.rule, p.exact_only != 0, nullptr, lane, lut, coop[warp], lo, hi, sf_byte);
+            words[2 * j] = lo;
+            words[2 * j + 1] = hi;
+            sf_pair |= sf_byte << (8 * j);
+        }
+        *reinterpret_cast<uint4 *>(codes) = make_uint4(words[0], words[1], words[2], words[3]);
+        *reinterpret_cast<uint16_t *>(sf) = static_cast<uint16_t>(sf_pair);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));
+        if (++s == FEED_STAGES) { s = 0; parity ^= 1u; }
+        tc_ += step_c;
+        tr += step_r;
+        if (tr >= tiles_r) { tr -= tiles_r; ++tc_; }
+    }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // Tensor map over x as bytes: [rows][cols * 2] with a row pitch of ld * 2, boxes of 128 rows x 128 bytes.
-inline bool make_x_map(CUtensorMap *map, const QuantParams &p) {
+inline bool make_x_map(CUtensorMap *map, const QuantParams &p, bool transposed) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.cols * 2), static_cast<cuuint64_t>(p.rows)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.ld * 2)};
-    cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(FEED_TILE_ROWS)};
+    cuuint32_t box[2] = {transposed ? static_cast<cuuint32_t>(COLS_BOX_BYTES) : 128u,
+                         static_cast<cuuint32_t>(transposed ? COLS_BOX_ROWS : FEED_TILE_ROWS)};
     cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(p.x), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+              CU_TENSOR_MAP_INTERLEAVE_NONE, transposed ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // Launches the TMA-fed kernel when x qualifies; *launched tells whether it did.
-template <typename T, int KIND>
+template <typename T, int KIND, bool TRANSPOSED>
 cudaError_t launch_rows_tma(const QuantParams &p, cudaStream_t stream, bool *launched) {
     *launched = false;
     if (reinterpret_cast<uintptr_t>(p.x) % 16 != 0 || (p.ld * 2) % 16 != 0) return cudaSuccess;
+    // the transposed kernel stores 16 bytes of codes and 2 scale bytes at a time
+    if (TRANSPOSED && (reinterpret_cast<uintptr_t>(p.codes) % 16 != 0 || reinterpret_cast<uintptr_t>(p.sf) % 2 != 0)) return cudaSuccess;
     if (p.cols * 2 >= (int64_t(1) << 31) || p.rows >= (int64_t(1) << 31) || p.ld * 2 >= (int64_t(1) << 40)) return cudaSuccess;
     CUtensorMap map;
-    if (!make_x_map(&map, p)) return cudaSuccess;
-    auto kernel = quantize_rows_tma_kernel<T, KIND>;
+    if (!make_x_map(&map, p, TRANSPOSED)) return cudaSuccess;
+    auto kernel = TRANSPOSED ? quantize_cols_tma_kernel<T, KIND> : quantize_rows_tma_kernel<T, KIND>;
     static int ctas_per_sm[64] = {};
     static int sm_count[64] = {};
     int dev = 0;
@@ -879,7 +1122,7 @@ template <typename T, int KIND>
 cudaError_t launch_rows(const QuantParams &p, cudaStream_t stream) {
     if (g_quantize_variant != 1) {
         bool launched = false;
-        const cudaError_t e = launch_rows_tma<T, KIND>(p, stream, &launched);
+        const cudaError_t e = launch_rows_tma<T, KIND, false>(p, stream, &launched);
         if (e != cudaSuccess || launched) return e;
     }
     auto kernel = quantize_rows_kernel<T, KIND>;
@@ -923,8 +1166,22 @@ cudaError_t launch_kind(const QuantParams &p, bool two_d, bool transposed, cudaS
     return cudaGetLastError();
 }
 
+template <typename T, int KIND>
+cudaError_t launch_cols(const QuantParams &p, cudaStream_t stream, bool *launched) {
+    *launched = false;
+    if (g_quantize_variant == 1) return cudaSuccess;
+    return launch_rows_tma<T, KIND, true>(p, stream, launched);
+}
+
 template <typename T>
 cudaError_t launch_all(const QuantParams &p, int kind, bool two_d, bool transposed, cudaStream_t stream) {
+    if (!two_d && transposed) {
+        bool launched = false;
+        const cudaError_t e = kind == KIND_STATIC     ? launch_cols<T, KIND_STATIC>(p, stream, &launched)
+                              : kind == KIND_ADAPTIVE ? launch_cols<T, KIND_ADAPTIVE>(p, stream, &launched)
+                                                      : launch_cols<T, KIND_IF4>(p, stream, &launched);
+        if (e != cudaSuccess || launched) return e;
+    }
     if (!two_d && !transposed) {
         if (kind == KIND_STATIC) return launch_rows<T, KIND_STATIC>(p, stream);
         if (kind == KIND_ADAPTIVE) return launch_rows<T, KIND_ADAPTIVE>(p, stream);

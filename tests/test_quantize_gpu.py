@@ -190,6 +190,18 @@ def test_both_row_kernels_match_the_oracle(oracle, variant):
                 for given in (None, amax):
                     q = B200QuantizeBackend.quantize(xd, fos.QuantizationConfig(**cfg), amax=given)
                     _assert_same(q, ref.values, ref.scale_factors, ref.amax, f"{shape} {cfg} amax given={given is not None}")
+        # transposed inputs have the same pair of kernels (sizes the reference accepts: multiples of 128)
+        for shape in [(128, 256), (640, 4096), (1152, 384)]:
+            x = torch.randn(shape, generator=g).bfloat16()
+            x[:: 5, :] *= 7.0
+            xd = x.to(DEV)
+            amax = xd.abs().max().float().reshape(1)
+            for cfg in (dict(transpose=True), dict(transpose=True, scale_rule="static_6"), dict(transpose=True, dtype="if4"),
+                        dict(transpose=True, scale_rule="abs_max")):
+                ref = oracle.quantize(x, **cfg)
+                for given in (None, amax):
+                    q = B200QuantizeBackend.quantize(xd, fos.QuantizationConfig(**cfg), amax=given)
+                    _assert_same(q, ref.values, ref.scale_factors, ref.amax, f"{shape} {cfg} amax given={given is not None}")
         xh = torch.randn(300, 264, generator=g).half()
         ref = oracle.quantize(xh)
         q = fos.quantize(xh.to(DEV), fos.QuantizationConfig())
