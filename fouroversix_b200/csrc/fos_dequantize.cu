@@ -4,7 +4,7 @@
 // src/fouroversix/quantize/dequantize_utils.py:15-86): value and scale are first
 // represented in fp16 and multiplied in fp16 (IF4 integer blocks multiply the integer
 // by 6/7 in fp16 first), then (fp32(product) * amax) / divisor in fp32, then the cast.
-#include "fos_common.cuh"
+#include "fos_dequant.cuh"
 
 namespace fos {
 namespace {
@@ -19,57 +19,36 @@ struct DequantParams {
     float divisor;
 };
 
-template <typename OUT> __device__ __forceinline__ OUT to_out(float v);
-template <> __device__ __forceinline__ float to_out<float>(float v) { return v; }
-template <> __device__ __forceinline__ __half to_out<__half>(float v) { return __float2half_rn(v); }
-template <> __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
-
-__device__ __forceinline__ float as_fp16(float v) { return __half2float(__float2half_rn(v)); }
-
-// One thread per 16-value block: 8 bytes of codes and one scale in, 16 values out.
+// One thread per 16-value block: 8 bytes of codes and one scale in, 16 values out. A CTA takes
+// runs of 256 blocks of one row at a time (contiguous codes in, contiguous values out).
 template <typename OUT>
 __global__ void __launch_bounds__(256) dequantize_kernel(const DequantParams p) {
     const int64_t n_cb = p.cols_p >> 4;
-    const int64_t cb_used = (p.cols + 15) >> 4;
-    const int64_t total = p.rows * cb_used;
-    const float amax = __ldg(p.amax);
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / cb_used, cb = i - r * cb_used;
+    const int cb_used = static_cast<int>((p.cols + 15) >> 4);
+    const int chunks = (cb_used + 255) >> 8;
+    const int64_t units = p.rows * chunks;
+    const DequantConsts k = dequant_consts(__ldg(p.amax), p.divisor);
+    for (int64_t u = blockIdx.x; u < units; u += gridDim.x) {
+        const int64_t r = u / chunks;
+        const int cb = static_cast<int>(u - r * chunks) * 256 + static_cast<int>(threadIdx.x);
+        if (cb >= cb_used) continue;
         const uint2 c = *reinterpret_cast<const uint2 *>(p.codes + r * (p.cols_p >> 1) + cb * 8);
-        uint32_t sfb = p.sf[sf_offset(r, cb, n_cb, p.sf_tiled != 0)];
-        const bool is_int = p.format == FOS_IF4 && (sfb & 0x80u);
-        if (p.format == FOS_IF4) sfb &= 0x7fu;
-        const float s16 = e4m3_to_float(sfb);   // every E4M3 value is an fp16 value
+        const uint32_t sfb = p.sf[sf_offset(r, cb, n_cb, p.sf_tiled != 0)];
         float v[16];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t byte = ((j < 4 ? c.x : c.y) >> ((j & 3) * 8)) & 0xffu;
-            float2 q;
-            if (is_int) {
-                const float six_sevenths = static_cast<float>(6.0 / 7.0);
-                q.x = as_fp16(__fmul_rn(static_cast<float>(static_cast<int>(byte << 28) >> 28), six_sevenths));
-                q.y = as_fp16(__fmul_rn(static_cast<float>(static_cast<int>(byte << 24) >> 28), six_sevenths));
-            } else {
-                q = e2m1x2_to_float2(byte);
-            }
-            v[2 * j] = __fdiv_rn(__fmul_rn(as_fp16(__fmul_rn(q.x, s16)), amax), p.divisor);
-            v[2 * j + 1] = __fdiv_rn(__fmul_rn(as_fp16(__fmul_rn(q.y, s16)), amax), p.divisor);
-        }
+        dequantize_block(c, sfb, p.format == FOS_IF4, k, v);
         OUT *dst = static_cast<OUT *>(p.out) + r * p.ld_out + cb * 16;
-        const int64_t left = p.cols - cb * 16;
-        const bool aligned = (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
-        if (left >= 16 && aligned) {
-            OUT tmp[16];
+        const int64_t left = p.cols - static_cast<int64_t>(cb) * 16;
+        if (left >= 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+            __align__(16) OUT tmp[16];
 #pragma unroll
-            for (int k = 0; k < 16; ++k) tmp[k] = to_out<OUT>(v[k]);
+            for (int i = 0; i < 16; ++i) tmp[i] = to_out<OUT>(v[i]);
             const uint4 *src4 = reinterpret_cast<const uint4 *>(tmp);
 #pragma unroll
-            for (int k = 0; k < static_cast<int>(sizeof(OUT)); ++k) reinterpret_cast<uint4 *>(dst)[k] = src4[k];
+            for (int i = 0; i < static_cast<int>(sizeof(OUT)); ++i) reinterpret_cast<uint4 *>(dst)[i] = src4[i];
         } else {
 #pragma unroll
-            for (int k = 0; k < 16; ++k)
-                if (k < left) dst[k] = to_out<OUT>(v[k]);
+            for (int i = 0; i < 16; ++i)
+                if (i < left) dst[i] = to_out<OUT>(v[i]);
         }
     }
 }
@@ -99,9 +78,9 @@ extern "C" int fos_dequantize(const uint8_t *codes, const uint8_t *sf, const flo
 
     DequantParams p{codes, sf, amax, out, rows_p, cols_p, rows, cols, ld_out, format,
                     sf_layout == FOS_SF_TILED, dequant_divisor(format, scale_rule)};
-    const int64_t total = rows * ((cols + 15) / 16);
-    int64_t blocks = (total + 255) / 256;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    const int64_t units = rows * ((((cols + 15) / 16) + 255) / 256);     // runs of 256 blocks of one row
+    int64_t blocks = units;
+    if (blocks > 148 * 8) blocks = 148 * 8;
     const unsigned g = static_cast<unsigned>(blocks);
     if (out_dtype == FOS_BF16) dequantize_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(p);
     else if (out_dtype == FOS_FP16) dequantize_kernel<__half><<<g, 256, 0, stream>>>(p);

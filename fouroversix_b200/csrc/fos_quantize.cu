@@ -14,6 +14,7 @@
 // otherwise the block is re-evaluated with the exact sequence. The result is therefore
 // identical to always running the exact sequence.
 #include "fos_tcgen05.cuh"
+#include "fos_dequant.cuh"
 
 namespace fos {
 
@@ -44,6 +45,10 @@ struct QuantParams {
     int exact_only;
     int vec_bytes;               // 32, 16 or 0: widest aligned load usable on x
     int x_is_ready;              // x was complete before the previous kernel in the stream started
+    // fused fake quantization (quantize_rows_tma_kernel<.., true>): dequantized values instead of codes
+    void *fake_out;              // [rows][fake_ld] elements of x's type
+    int64_t fake_ld;
+    float fake_divisor;
 };
 
 // Site of the first bounded wait that gave up, 0 if none did (never expected to change).
@@ -811,7 +816,7 @@ constexpr int FEED_CONSUMERS = 256;
 constexpr int FEED_THREADS = FEED_CONSUMERS + 32;
 constexpr int FEED_SMEM_BYTES = FEED_STAGES * FEED_STAGE_BYTES + 1024;
 
-template <typename T, int KIND>
+template <typename T, int KIND, bool FAKE = false>
 __global__ void __launch_bounds__(FEED_THREADS, FOS_FEED_CTAS)
 quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantParams p) {
     extern __shared__ uint8_t feed_smem_raw[];
@@ -897,6 +902,8 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
     int64_t code_off = static_cast<int64_t>(tr) * 128 * code_ld + tc_ * 32;
     int64_t sf_off = p.sf_tiled ? static_cast<int64_t>(blockIdx.x) * 512 : static_cast<int64_t>(tr) * 128 * n_cb + tc_ * 4;
 
+    int fake_tr = tr;                                   // tile row, tracked only for the fused fake quantization
+    const DequantConsts dk = dequant_consts(tc.amax, p.fake_divisor);
     int s = 0;
     uint32_t parity = 0;
     for (int k = 0; k < my_tiles; ++k) {
@@ -917,12 +924,39 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
             }
             uint32_t lo, hi, sf_byte;
             quantize_block<KIND, false, false>(v, tc, p.rule, p.exact_only != 0, nullptr, lane, lut, coop[warp], lo, hi, sf_byte);
-            *reinterpret_cast<uint2 *>(codes + j * code_half) = make_uint2(lo, hi);
-            sf[j * sf_half] = static_cast<uint8_t>(sf_byte);
+            if (!FAKE) {
+                *reinterpret_cast<uint2 *>(codes + j * code_half) = make_uint2(lo, hi);
+                sf[j * sf_half] = static_cast<uint8_t>(sf_byte);
+            } else {
+                // fused fake quantization: what dequantize would make of this block, in x's type,
+                // into the un-padded output
+                const int64_t row = static_cast<int64_t>(fake_tr) * 128 + j * 64 + warp * 8 + q;
+                const int64_t col = (static_cast<int64_t>(tc_) * 4 + cb) * 16;
+                if (row < p.rows && col < p.cols) {
+                    float dq[16];
+                    dequantize_block(make_uint2(lo, hi), sf_byte, KIND == KIND_IF4, dk, dq);
+                    T *dst = static_cast<T *>(p.fake_out) + row * p.fake_ld + col;
+                    __align__(16) T tmp[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) tmp[i] = to_out<T>(dq[i]);
+                    if (col + 16 <= p.cols && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                        reinterpret_cast<uint4 *>(dst)[0] = reinterpret_cast<const uint4 *>(tmp)[0];
+                        reinterpret_cast<uint4 *>(dst)[1] = reinterpret_cast<const uint4 *>(tmp)[1];
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (col + i < p.cols) dst[i] = tmp[i];
+                    }
+                }
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));
         if (++s == FEED_STAGES) { s = 0; parity ^= 1u; }
+        if (FAKE) {
+            fake_tr += step_r;
+            if (tc_ + step_c >= tiles_c) ++fake_tr;
+        }
         code_off += code_step;
         sf_off += sf_step;
         tc_ += step_c;
@@ -1073,7 +1107,7 @@ inline bool make_x_map(CUtensorMap *map, const QuantParams &p, bool transposed) 
 }
 
 // Launches the TMA-fed kernel when x qualifies; *launched tells whether it did.
-template <typename T, int KIND, bool TRANSPOSED>
+template <typename T, int KIND, bool TRANSPOSED, bool FAKE = false>
 cudaError_t launch_rows_tma(const QuantParams &p, cudaStream_t stream, bool *launched) {
     *launched = false;
     if (reinterpret_cast<uintptr_t>(p.x) % 16 != 0 || (p.ld * 2) % 16 != 0) return cudaSuccess;
@@ -1082,7 +1116,7 @@ cudaError_t launch_rows_tma(const QuantParams &p, cudaStream_t stream, bool *lau
     if (p.cols * 2 >= (int64_t(1) << 31) || p.rows >= (int64_t(1) << 31) || p.ld * 2 >= (int64_t(1) << 40)) return cudaSuccess;
     CUtensorMap map;
     if (!make_x_map(&map, p, TRANSPOSED)) return cudaSuccess;
-    auto kernel = TRANSPOSED ? quantize_cols_tma_kernel<T, KIND> : quantize_rows_tma_kernel<T, KIND>;
+    auto kernel = TRANSPOSED ? quantize_cols_tma_kernel<T, KIND> : quantize_rows_tma_kernel<T, KIND, FAKE>;
     static int ctas_per_sm[64] = {};
     static int sm_count[64] = {};
     int dev = 0;
@@ -1234,8 +1268,63 @@ cudaError_t launch_amax(const void *x, int64_t rows, int64_t cols, int64_t ld, b
     return cudaLaunchKernelEx(&cfg, amax_kernel<T>, static_cast<const T *>(x), rows, cols, ld, vec16 ? 1 : 0, amax);
 }
 
+template <typename T>
+cudaError_t launch_fake(const QuantParams &p, int kind, cudaStream_t stream, bool *launched) {
+    if (kind == KIND_STATIC) return launch_rows_tma<T, KIND_STATIC, false, true>(p, stream, launched);
+    if (kind == KIND_ADAPTIVE) return launch_rows_tma<T, KIND_ADAPTIVE, false, true>(p, stream, launched);
+    return launch_rows_tma<T, KIND_IF4, false, true>(p, stream, launched);
+}
+
 }  // namespace
 }  // namespace fos
+
+extern "C" int fos_pseudo_quantize(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int format,
+                                   int scale_rule, const float *amax_in, void *out, int64_t ld_out, float *amax_out,
+                                   int flags, void *stream_) {
+    using namespace fos;
+    if (!x || !out || !amax_out) return FOS_ERR_INVALID_ARGUMENT;
+    if (rows <= 0 || cols <= 0 || ld < cols || ld_out < cols) return FOS_ERR_INVALID_ARGUMENT;
+    if (x_dtype != FOS_BF16 && x_dtype != FOS_FP16) return FOS_ERR_INVALID_ARGUMENT;
+    if (format != FOS_NVFP4 && format != FOS_IF4) return FOS_ERR_INVALID_ARGUMENT;
+    if (scale_rule < FOS_RULE_STATIC_6 || scale_rule > FOS_RULE_ABS_MAX) return FOS_ERR_INVALID_ARGUMENT;
+    const bool is_static = scale_rule == FOS_RULE_STATIC_6 || scale_rule == FOS_RULE_STATIC_4;
+    if (format == FOS_IF4 && is_static) return FOS_ERR_UNSUPPORTED;
+    // only inputs the TMA-fed kernel takes; the caller runs fos_quantize + fos_dequantize otherwise
+    if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || (ld * 2) % 16 != 0) return FOS_ERR_UNSUPPORTED;
+    int st = check_device();
+    if (st != FOS_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+    QuantParams p{};
+    p.x = x;
+    p.rows = rows; p.cols = cols; p.ld = ld;
+    p.out_rows = rows; p.out_cols = cols;
+    p.rows_p = round_up64(rows, TILE_ROWS);
+    p.cols_p = round_up64(cols, TILE_COLS);
+    p.rule = scale_rule;
+    p.sf_tiled = 1;
+    p.exact_only = (flags & FOS_QUANTIZE_EXACT_ONLY) != 0;
+    p.fake_out = out;
+    p.fake_ld = ld_out;
+    p.fake_divisor = dequant_divisor(format, scale_rule);
+    const bool vec16 = cols % 8 == 0;
+    if (amax_in) {
+        p.amax = amax_in;
+        p.amax_store = amax_in != amax_out ? amax_out : nullptr;
+    } else {
+        FOS_CUDA_TRY(x_dtype == FOS_BF16
+                         ? launch_amax<__nv_bfloat16>(x, rows, cols, ld, vec16, amax_out, stream)
+                         : launch_amax<__half>(x, rows, cols, ld, vec16, amax_out, stream));
+        p.amax = amax_out;
+    }
+    p.x_is_ready = amax_in == nullptr;
+    const int kind = format == FOS_IF4 ? KIND_IF4 : (is_static ? KIND_STATIC : KIND_ADAPTIVE);
+    bool launched = false;
+    FOS_CUDA_TRY(x_dtype == FOS_BF16 ? launch_fake<__nv_bfloat16>(p, kind, stream, &launched)
+                                     : launch_fake<__half>(p, kind, stream, &launched));
+    // (the amax pass, if any, has been enqueued already: harmless, the caller's fallback repeats it)
+    return launched ? FOS_OK : FOS_ERR_UNSUPPORTED;
+}
 
 extern "C" int fos_quantize(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int format,
                             int scale_rule, int block_2d, int transpose, int sf_layout, const float *amax_in,

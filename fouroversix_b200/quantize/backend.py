@@ -133,5 +133,25 @@ class B200QuantizeBackend:
 
     @classmethod
     def pseudo_quantize(cls, x: torch.Tensor, config: QuantizationConfig) -> torch.Tensor:
-        """Quantize then dequantize back to x's dtype (two kernels, no host round trip)."""
+        """Quantize then dequantize back to x's dtype: one fused kernel for 1-D blocks of an
+        untransposed, 16-byte-aligned input (fos_pseudo_quantize), otherwise the quantize and the
+        dequantize kernel one after the other. Same bits either way."""
+        reason = cls.unsupported_reason(x, config)
+        if reason is not None:
+            raise ValueError(f"B200 quantize: {reason}")
+        if not config.block_scale_2d and not config.transpose:
+            if x.stride(1) != 1:
+                x = x.contiguous()
+            rows, cols = x.shape
+            out = torch.empty(rows, cols, dtype=x.dtype, device=x.device)
+            amax_out = torch.empty(1, dtype=torch.float32, device=x.device)
+            with torch.cuda.device(x.device):
+                status = _native.lib().fos_pseudo_quantize(
+                    x.data_ptr(), _native.elem_code(x.dtype), rows, cols, x.stride(0), _FORMATS[config.dtype],
+                    config.scale_rule.cuda_id, 0, out.data_ptr(), out.stride(0), amax_out.data_ptr(), 0,
+                    _native.stream_ptr(x.device))
+            if status == 0:
+                return out
+            if status != -2:   # anything but "this input needs the two-kernel path"
+                _native.check(status, "fos_pseudo_quantize")
         return cls.dequantize(cls.quantize(x, config), dtype=x.dtype)

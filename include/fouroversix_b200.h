@@ -176,6 +176,20 @@ int fos_gemm_if4_static(const uint8_t *a_codes, const uint8_t *a_sf, int a_forma
                         int64_t m, int64_t n, int64_t ldd, int32_t *status, void *stream);
 
 /*
+ * Fused fake quantization: out = dequantize(quantize(x)) in x's element type, one pass over x
+ * after the amax pass, nothing packed is written. 1-D blocks, untransposed; `out` is
+ * [rows][ld_out] elements and only rows x cols of it are written. amax_in / amax_out / flags as
+ * in fos_quantize. Returns FOS_ERR_UNSUPPORTED when x is not 16-byte aligned (base and row
+ * stride): the caller then runs fos_quantize followed by fos_dequantize, which give the same bits.
+ *
+ * Replaces: QuantizeBackendBase.pseudo_quantize (src/fouroversix/quantize/backend.py:162-234) and the
+ * Triton fake-quantization kernel (src/fouroversix/kernels/triton/quantize.py:1143-1246).
+ */
+int fos_pseudo_quantize(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int format,
+                        int scale_rule, const float *amax_in, void *out, int64_t ld_out, float *amax_out,
+                        int flags, void *stream);
+
+/*
  * Process-wide tuning / testing knobs. No counterpart in the reference.
  *   FOS_OPT_GEMM_VARIANT   0 = choose the GEMM kernel per problem (default);
  *                          128 / 256 = single-CTA kernel with 128 x 128 / 128 x 256 tiles;

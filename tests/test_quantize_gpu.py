@@ -210,3 +210,26 @@ def test_both_row_kernels_match_the_oracle(oracle, variant):
         lib.fos_set_option(3, 0)
     site = ctypes.c_int32(-1)
     assert lib.fos_wait_failure_site(ctypes.byref(site)) == 0 and site.value == 0
+
+
+def test_fused_fake_quantization_equals_quantize_then_dequantize(oracle):
+    """pseudo_quantize: the fused kernel (aligned inputs) and the two-kernel path (anything else) give
+    the bits of the oracle's quantize followed by its dequantize, in the input's dtype, on full,
+    ragged and strided inputs."""
+    g = torch.Generator().manual_seed(31)
+    wide = torch.randn(300, 520, generator=g).bfloat16()
+    wide_dev = wide.to(DEV)
+    cases = [(a, a.to(DEV)) for a in (
+        torch.randn(256, 512, generator=g).bfloat16(),
+        torch.randn(100, 80, generator=g).bfloat16(),
+        torch.randn(37, 53, generator=g).bfloat16(),            # unaligned rows: two-kernel path
+        torch.randn(130, 200, generator=g).half(),
+        (torch.randn(1024, 4096, generator=g) * 0.02).bfloat16(),
+    )] + [(wide[:, 8:264], wide_dev[:, 8:264]), (wide[3:200, 16:500], wide_dev[3:200, 16:500])]
+    for x, xd in cases:
+        for cfg in (dict(), dict(scale_rule="static_6"), dict(dtype="if4"), dict(scale_rule="mae")):
+            ref = oracle.quantize(x, **cfg)
+            want = oracle.dequantize(ref, x.dtype)
+            got = fos.quantize(xd, fos.QuantizationConfig(pseudo_quantize=True, **cfg))
+            assert got.dtype == x.dtype and got.shape == x.shape
+            assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16)), (tuple(x.shape), x.dtype, cfg)
