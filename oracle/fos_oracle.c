@@ -467,6 +467,30 @@ long fos_oracle_check_div6(void) {
     return bad;
 }
 
+/* How many finite binary32 a with |a| >= min_abs (bit patterns start, start + stride, ...) have
+ * fma(fma(-d, a * y, a), y, a * y) != a / d, y = fl(1 / d), ignoring the sign of a zero: the
+ * division-free quotient of the dequantize kernel. stride 1 is the exhaustive check. */
+int64_t fos_oracle_check_div_const(float d, uint32_t start, uint32_t stride, float min_abs) {
+    const float y = 1.0f / d;
+    int64_t bad = 0;
+    if (stride == 0) stride = 1;
+    const int64_t n = ((1LL << 32) - start + stride - 1) / stride;
+#ifdef _OPENMP
+#pragma omp parallel for reduction(+ : bad) schedule(static)
+#endif
+    for (int64_t i = 0; i < n; ++i) {
+        const uint32_t bits = (uint32_t)(start + i * stride);
+        float a;
+        memcpy(&a, &bits, 4);
+        if (!isfinite(a) || fabsf(a) < min_abs) continue;
+        const float q0 = a * y;
+        const float q1 = fmaf(fmaf(-d, q0, a), y, q0);
+        const float ref = a / d;
+        if (q1 != ref && !(q1 == 0.0f && ref == 0.0f)) ++bad;
+    }
+    return bad;
+}
+
 int fos_oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
