@@ -340,6 +340,27 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     e2e_serial_value = BYTES_PER_ELEM * n_elem / (serial_ms * 1e-3) / 1e9
 
     gemm = gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks)
+
+    # the configuration as a whole: quantize both operands (activation 4/6 MSE per call, weight too)
+    # and multiply, through the public front end; plus the other kernels of the path on the same tensor
+    b_dev = make_b(2).to(dev)
+    pipeline = {}
+    t = time_graphs(lambda i: fos.quantized_matmul(a_sets[i % N_ROTATE], b_dev), N_ROTATE, max(args.steps, 10), 3)
+    pipeline["quantize_both_and_multiply"] = {
+        "ms": t, "shape": "A 8192x4096 @ B(4096x4096)^T",
+        "note": "fouroversix_b200.quantized_matmul on two bf16 tensors: 2 x (zero, amax, quantize) + alpha + GEMM"}
+    qb = fos.quantize(b_dev)
+    t = time_graphs(lambda i: fos.quantized_matmul(a_sets[i % N_ROTATE], qb), N_ROTATE, max(args.steps, 10), 3)
+    pipeline["quantize_activation_and_multiply"] = {"ms": t, "note": "weight quantized once, outside the timed region"}
+    q_sets = [fos.quantize(x, cfg_mse) for x in a_sets]
+    t = time_graphs(lambda i: fos.dequantize(q_sets[i % N_ROTATE]), N_ROTATE, max(args.steps, 10), 3)
+    pipeline["dequantize"] = {"ms": t, "GB/s": BYTES_PER_ELEM * n_elem / (t * 1e-3) / 1e9}
+    cfg_fake = fos.QuantizationConfig(scale_rule="mse", pseudo_quantize=True)
+    t = time_graphs(lambda i: fos.quantize(a_sets[i % N_ROTATE], cfg_fake), N_ROTATE, max(args.steps, 10), 3)
+    pipeline["pseudo_quantize"] = {"ms": t, "GB/s": 4.0 * n_elem / (t * 1e-3) / 1e9,
+                                   "note": "fused fake quantization, 2 B read + 2 B written per element"}
+    del q_sets
+
     cpu = cpu_baseline_quantize(a_cpu) if world == 1 else None
 
     achieved = BYTES_PER_ELEM * n_elem / (kernel_ms * 1e-3) / 1e9
@@ -374,6 +395,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         },
         "quantize_modes": modes,
         "gemm": gemm,
+        "pipeline": pipeline,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms,
                 "how": "fouroversix_b200.quantize() on a staging tensor; every step copies its input from pinned host "

@@ -413,9 +413,10 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
         // <= 188u * (sum t^2 + 1) * G^2 (arithmetic over geometric mean), plus 40u relative for the
         // roundings of the two summations. `tau` is 1.5 times that, for both candidates
         // together; a difference inside tau is re-decided exactly below.
-        const bool eligible = !TWO_D && fminf(ea.w, eb.w) >= 0.0f;
+        const bool eligible = fminf(ea.w, eb.w) >= 0.0f;     // (callers without a table rule 2-D blocks out)
         bool decided = false, pick_b = false;
         uint32_t ca[2] = {0u, 0u}, cb[2] = {0u, 0u};
+        float row_a = 0.0f, row_b = 0.0f;                    // 2-D: this row's share of the block's sums
         if (eligible) {
             const uint64_t ra2 = pack2(r_a, r_a), rb2 = pack2(r_b, r_b);
             uint64_t acc_a = pack2(0.0f, 0.0f), acc_b = acc_a;
@@ -435,11 +436,34 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
             unpack2f(acc_a, a0, a1);
             unpack2f(acc_b, b0, b1);
             const float sum_a = a0 + a1, sum_b = b0 + b1;                 // sum of t^2, scaled units
-            const float err_a = sum_a * ea.w, err_b = sum_b * eb.w;       // times G^2
-            const float tau = 0x1p-24f * 1.5f * (228.0f * (err_a + err_b) + 188.0f * (ea.w + eb.w));
+            if (!TWO_D) {
+                const float err_a = sum_a * ea.w, err_b = sum_b * eb.w;   // times G^2
+                const float tau = 0x1p-24f * 1.5f * (228.0f * (err_a + err_b) + 188.0f * (ea.w + eb.w));
+                const float diff = err_b - err_a;
+                decided = fabsf(diff) > tau;
+                pick_b = diff < 0.0f;
+            } else {
+                row_a = sum_a;
+                row_b = sum_b;
+            }
+        }
+        if (TWO_D) {
+            // 16 x 16 blocks: the 16 lanes that hold a block's rows add their row sums (any order:
+            // this is the estimate). Same per-element bound; over 256 terms Cauchy-Schwarz gives
+            // 2 * 47u * 16 * sqrt(S) <= 752u * (S + 1), and 100u covers the roundings of both
+            // 256-term summations. The block's lanes share the scales, so `eligible` is uniform
+            // over them. The exact path below is collective over the warp (shared scratch), so it
+            // is taken by the whole warp as soon as one of its two blocks needs it.
+#pragma unroll
+            for (int sh = 0; sh < 4; ++sh) {
+                row_a += __shfl_xor_sync(FULL, row_a, LaneMap<TWO_D, TRANSPOSED>::XOR0 << sh);
+                row_b += __shfl_xor_sync(FULL, row_b, LaneMap<TWO_D, TRANSPOSED>::XOR0 << sh);
+            }
+            const float err_a = row_a * ea.w, err_b = row_b * eb.w;
+            const float tau = 0x1p-24f * 1.5f * (852.0f * (err_a + err_b) + 752.0f * (ea.w + eb.w));
             const float diff = err_b - err_a;
-            decided = fabsf(diff) > tau;
             pick_b = diff < 0.0f;
+            decided = __all_sync(FULL, eligible && fabsf(diff) > tau);
         }
 
         // Undecided blocks are re-decided with the reference's exact sequence. When the caller
@@ -448,7 +472,7 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
         // candidate c, and the 16 terms are added in the reference's order with shuffles. That
         // costs the warp about 60 instructions per undecided block instead of running the
         // 16-element exact loop on every lane of a diverged warp.
-        if (coop != nullptr) {
+        if (!TWO_D && coop != nullptr) {
             unsigned pending = __ballot_sync(FULL, eligible && !decided);
             while (pending) {
                 const int src = __ffs(pending) - 1;
@@ -816,12 +840,15 @@ constexpr int FEED_CONSUMERS = 256;
 constexpr int FEED_THREADS = FEED_CONSUMERS + 32;
 constexpr int FEED_SMEM_BYTES = FEED_STAGES * FEED_STAGE_BYTES + 1024;
 
-template <typename T, int KIND, bool FAKE = false>
+template <typename T, int KIND, bool FAKE = false, bool TWO_D = false>
 __global__ void __launch_bounds__(FEED_THREADS, FOS_FEED_CTAS)
 quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantParams p) {
+    static_assert(!(FAKE && TWO_D), "the fused fake quantization is built for 1-D blocks");
     extern __shared__ uint8_t feed_smem_raw[];
     __shared__ float4 lut[128];
     __shared__ __align__(16) float coop[FEED_CONSUMERS / 32][20];
+    // 2-D blocks: per warp 2 x 256 floats for the exact 256-term sums of its two 16 x 16 blocks
+    __shared__ __align__(16) float scratch2d[TWO_D ? (FEED_CONSUMERS / 32) * 512 : 4];
     __shared__ __align__(8) uint64_t full_bar[FEED_STAGES], empty_bar[FEED_STAGES];
     __shared__ int abort_flag;
 
@@ -886,16 +913,21 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
     // What depends on the thread alone is computed here once. The empty asm statements make these
     // values opaque, so that they stay in registers: left alone, the compiler recomputes them
     // for every block (dozens of integer instructions) to save those registers.
-    const int q = lane >> 2, cb = lane & 3;
+    // 1-D blocks: lane l of warp w owns rows 8w + l/4 and 64 + 8w + l/4 of the tile and block column l%4.
+    // 2-D blocks: warp w owns rows 16w .. 16w+15 (one row per lane pair), lane l block columns l%2 and
+    // 2 + l%2, so that the 16 lanes of equal parity hold the 16 rows of one 16 x 16 block.
+    const int q = TWO_D ? lane >> 1 : lane >> 2, cb = TWO_D ? lane & 1 : lane & 3;
+    const int row_in_tile = TWO_D ? warp * 16 + q : warp * 8 + q;
     const int64_t code_ld = p.cols_p >> 1, n_cb = p.cols_p >> 4;
-    uint32_t piece0 = stage0 + static_cast<uint32_t>((warp * 8 + q) * 128 + ((2 * cb) ^ q) * 16);
-    uint32_t piece1 = stage0 + static_cast<uint32_t>((warp * 8 + q) * 128 + ((2 * cb + 1) ^ q) * 16);
-    uint8_t *code_ptr = p.codes + (warp * 8 + q) * code_ld + cb * 8;
-    uint8_t *sf_ptr = p.sf + (p.sf_tiled ? ((warp & 3) * 8 + q) * 16 + (warp >> 2) * 4 + cb : (warp * 8 + q) * n_cb + cb);
+    uint32_t piece0 = stage0 + static_cast<uint32_t>(row_in_tile * 128 + ((2 * cb) ^ (row_in_tile & 7)) * 16);
+    uint32_t piece1 = stage0 + static_cast<uint32_t>(row_in_tile * 128 + ((2 * cb + 1) ^ (row_in_tile & 7)) * 16);
+    uint8_t *code_ptr = p.codes + row_in_tile * code_ld + cb * 8;
+    uint8_t *sf_ptr = p.sf + (p.sf_tiled ? (row_in_tile & 31) * 16 + (row_in_tile >> 5) * 4 + cb : row_in_tile * n_cb + cb);
     asm volatile("" : "+r"(piece0), "+r"(piece1), "+l"(code_ptr), "+l"(sf_ptr));
 
     // offsets of the tile (uniform over the CTA), advanced without multiplications
-    const int64_t code_half = 64 * code_ld, sf_half = p.sf_tiled ? 8 : 64 * n_cb;
+    // second block of the thread: 64 rows further down (1-D) or two block columns to the right (2-D)
+    const int64_t code_half = TWO_D ? 16 : 64 * code_ld, sf_half = TWO_D ? 2 : (p.sf_tiled ? 8 : 64 * n_cb);
     const int64_t code_step = static_cast<int64_t>(step_r) * 128 * code_ld + step_c * 32, code_wrap = 127 * code_ld;
     const int64_t sf_step = p.sf_tiled ? static_cast<int64_t>(gridDim.x) * 512 : static_cast<int64_t>(step_r) * 128 * n_cb + step_c * 4;
     const int64_t sf_wrap = p.sf_tiled ? 0 : 127 * n_cb;
@@ -913,7 +945,9 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
         const uint32_t stage = s * FEED_STAGE_BYTES;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            const uint4 a = lds_16(piece0 + stage + j * 64 * 128), b = lds_16(piece1 + stage + j * 64 * 128);
+            // (two block columns to the right = four 16-byte chunks = bit 6 of the swizzled address)
+            const uint4 a = lds_16(TWO_D ? (piece0 + stage) ^ (j * 64) : piece0 + stage + j * 64 * 128);
+            const uint4 b = lds_16(TWO_D ? (piece1 + stage) ^ (j * 64) : piece1 + stage + j * 64 * 128);
             const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
             float v[16];
 #pragma unroll
@@ -923,7 +957,8 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
                 v[2 * i + 1] = f.y;
             }
             uint32_t lo, hi, sf_byte;
-            quantize_block<KIND, false, false>(v, tc, p.rule, p.exact_only != 0, nullptr, lane, lut, coop[warp], lo, hi, sf_byte);
+            quantize_block<KIND, TWO_D, false>(v, tc, p.rule, p.exact_only != 0, TWO_D ? scratch2d + warp * 512 : nullptr, lane,
+                                               lut, TWO_D ? nullptr : coop[warp], lo, hi, sf_byte);
             if (!FAKE) {
                 *reinterpret_cast<uint2 *>(codes + j * code_half) = make_uint2(lo, hi);
                 sf[j * sf_half] = static_cast<uint8_t>(sf_byte);
@@ -985,12 +1020,14 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
 
 constexpr int COLS_BOX_ROWS = 64, COLS_BOX_BYTES = 256;
 
-template <typename T, int KIND>
+template <typename T, int KIND, bool TWO_D = false>
 __global__ void __launch_bounds__(FEED_THREADS, FOS_FEED_CTAS)
 quantize_cols_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantParams p) {
     extern __shared__ uint8_t feed_smem_raw[];
     __shared__ float4 lut[128];
     __shared__ __align__(16) float coop[FEED_CONSUMERS / 32][20];
+    // 2-D blocks: lanes 0-15 and 16-31 of a warp hold the rows of two 16 x 16 blocks
+    __shared__ __align__(16) float scratch2d[TWO_D ? (FEED_CONSUMERS / 32) * 512 : 4];
     __shared__ __align__(8) uint64_t full_bar[FEED_STAGES], empty_bar[FEED_STAGES];
     __shared__ int abort_flag;
 
@@ -1075,7 +1112,8 @@ quantize_cols_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
                 v[i] = elem_to_float<T>(reinterpret_cast<const T &>(h));
             }
             uint32_t lo, hi, sf_byte;
-            quantize_block<KIND, false, false>(v, tc, p.rule, p.exact_only != 0, nullptr, lane, lut, coop[warp], lo, hi, sf_byte);
+            quantize_block<KIND, TWO_D, TWO_D>(v, tc, p.rule, p.exact_only != 0, TWO_D ? scratch2d + warp * 512 : nullptr, lane,
+                                               lut, TWO_D ? nullptr : coop[warp], lo, hi, sf_byte);
             words[2 * j] = lo;
             words[2 * j + 1] = hi;
             sf_pair |= sf_byte << (8 * j);
@@ -1107,7 +1145,7 @@ inline bool make_x_map(CUtensorMap *map, const QuantParams &p, bool transposed) 
 }
 
 // Launches the TMA-fed kernel when x qualifies; *launched tells whether it did.
-template <typename T, int KIND, bool TRANSPOSED, bool FAKE = false>
+template <typename T, int KIND, bool TRANSPOSED, bool FAKE = false, bool TWO_D = false>
 cudaError_t launch_rows_tma(const QuantParams &p, cudaStream_t stream, bool *launched) {
     *launched = false;
     if (reinterpret_cast<uintptr_t>(p.x) % 16 != 0 || (p.ld * 2) % 16 != 0) return cudaSuccess;
@@ -1116,7 +1154,7 @@ cudaError_t launch_rows_tma(const QuantParams &p, cudaStream_t stream, bool *lau
     if (p.cols * 2 >= (int64_t(1) << 31) || p.rows >= (int64_t(1) << 31) || p.ld * 2 >= (int64_t(1) << 40)) return cudaSuccess;
     CUtensorMap map;
     if (!make_x_map(&map, p, TRANSPOSED)) return cudaSuccess;
-    auto kernel = TRANSPOSED ? quantize_cols_tma_kernel<T, KIND> : quantize_rows_tma_kernel<T, KIND, FAKE>;
+    auto kernel = TRANSPOSED ? quantize_cols_tma_kernel<T, KIND, TWO_D> : quantize_rows_tma_kernel<T, KIND, FAKE, TWO_D>;
     static int ctas_per_sm[64] = {};
     static int sm_count[64] = {};
     int dev = 0;
@@ -1200,20 +1238,25 @@ cudaError_t launch_kind(const QuantParams &p, bool two_d, bool transposed, cudaS
     return cudaGetLastError();
 }
 
+// The TMA-fed kernel for (2-D blocks or not) x (transposed or not); *launched tells whether x qualified.
 template <typename T, int KIND>
-cudaError_t launch_cols(const QuantParams &p, cudaStream_t stream, bool *launched) {
+cudaError_t launch_fed(const QuantParams &p, bool two_d, bool transposed, cudaStream_t stream, bool *launched) {
     *launched = false;
     if (g_quantize_variant == 1) return cudaSuccess;
-    return launch_rows_tma<T, KIND, true>(p, stream, launched);
+    if (two_d) {
+        return transposed ? launch_rows_tma<T, KIND, true, false, true>(p, stream, launched)
+                          : launch_rows_tma<T, KIND, false, false, true>(p, stream, launched);
+    }
+    return transposed ? launch_rows_tma<T, KIND, true>(p, stream, launched) : cudaSuccess;   // (1-D rows: launch_rows)
 }
 
 template <typename T>
 cudaError_t launch_all(const QuantParams &p, int kind, bool two_d, bool transposed, cudaStream_t stream) {
-    if (!two_d && transposed) {
+    if (two_d || transposed) {
         bool launched = false;
-        const cudaError_t e = kind == KIND_STATIC     ? launch_cols<T, KIND_STATIC>(p, stream, &launched)
-                              : kind == KIND_ADAPTIVE ? launch_cols<T, KIND_ADAPTIVE>(p, stream, &launched)
-                                                      : launch_cols<T, KIND_IF4>(p, stream, &launched);
+        const cudaError_t e = kind == KIND_STATIC     ? launch_fed<T, KIND_STATIC>(p, two_d, transposed, stream, &launched)
+                              : kind == KIND_ADAPTIVE ? launch_fed<T, KIND_ADAPTIVE>(p, two_d, transposed, stream, &launched)
+                                                      : launch_fed<T, KIND_IF4>(p, two_d, transposed, stream, &launched);
         if (e != cudaSuccess || launched) return e;
     }
     if (!two_d && !transposed) {

@@ -185,7 +185,8 @@ def test_both_row_kernels_match_the_oracle(oracle, variant):
             xd = x.to(DEV)
             amax = xd.abs().max().float().reshape(1)
             for cfg in (dict(), dict(scale_rule="static_6"), dict(scale_rule="static_4"), dict(scale_rule="mae"),
-                        dict(scale_rule="abs_max"), dict(dtype="if4")):
+                        dict(scale_rule="abs_max"), dict(dtype="if4"), dict(block_scale_2d=True),
+                        dict(block_scale_2d=True, scale_rule="static_6"), dict(block_scale_2d=True, dtype="if4")):
                 ref = oracle.quantize(x, **cfg)
                 for given in (None, amax):
                     q = B200QuantizeBackend.quantize(xd, fos.QuantizationConfig(**cfg), amax=given)
@@ -197,7 +198,8 @@ def test_both_row_kernels_match_the_oracle(oracle, variant):
             xd = x.to(DEV)
             amax = xd.abs().max().float().reshape(1)
             for cfg in (dict(transpose=True), dict(transpose=True, scale_rule="static_6"), dict(transpose=True, dtype="if4"),
-                        dict(transpose=True, scale_rule="abs_max")):
+                        dict(transpose=True, scale_rule="abs_max"), dict(transpose=True, block_scale_2d=True),
+                        dict(transpose=True, block_scale_2d=True, scale_rule="mae")):
                 ref = oracle.quantize(x, **cfg)
                 for given in (None, amax):
                     q = B200QuantizeBackend.quantize(xd, fos.QuantizationConfig(**cfg), amax=given)
