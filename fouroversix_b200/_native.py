@@ -19,6 +19,7 @@ FOS_BF16, FOS_FP16, FOS_FP32 = 0, 1, 2
 FOS_NVFP4, FOS_IF4 = 0, 1
 FOS_SF_ROWMAJOR, FOS_SF_TILED = 0, 1
 FOS_QUANTIZE_EXACT_ONLY = 1
+FOS_QUANTIZE_RHT = 2
 
 _c_i64, _c_int, _c_ptr = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
 

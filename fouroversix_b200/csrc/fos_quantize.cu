@@ -45,6 +45,7 @@ struct QuantParams {
     int exact_only;
     int vec_bytes;               // 32, 16 or 0: widest aligned load usable on x
     int x_is_ready;              // x was complete before the previous kernel in the stream started
+    int rht;                     // rotate every block of 16 (random Hadamard transform) before quantizing
     // fused fake quantization (quantize_rows_tma_kernel<.., true>): dequantized values instead of codes
     void *fake_out;              // [rows][fake_ld] elements of x's type
     int64_t fake_ld;
@@ -122,6 +123,77 @@ __global__ void __launch_bounds__(256) amax_kernel(const T *__restrict__ x, int6
     if (threadIdx.x == 0) {
         for (int w = 1; w < 8; ++w) m = fmaxf(m, warp_max[w]);
         // non-negative floats order like their bit patterns
+        atomicMax(reinterpret_cast<int *>(amax), __float_as_int(m));
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// 16-point random Hadamard transform
+// ------------------------------------------------------------------------------------
+
+// y = v @ (diag(signs) @ H16 / 4) for the fixed sign vector of the reference
+// (src/fouroversix/quantize/utils.py:19-85), as a fast Walsh-Hadamard transform in binary32 (four
+// stages of 16 additions / subtractions, the same operations in the same order as the host-side
+// restatement), rounded once to T like the reference's matrix product in T.
+template <typename T>
+__device__ __forceinline__ void rotate16(float (&v)[16]) {
+    // signs: + + + - + - - - - - - + - + - -
+    v[3] = -v[3]; v[5] = -v[5]; v[6] = -v[6]; v[7] = -v[7]; v[8] = -v[8]; v[9] = -v[9]; v[10] = -v[10];
+    v[12] = -v[12]; v[14] = -v[14]; v[15] = -v[15];
+#pragma unroll
+    for (int h = 1; h < 16; h *= 2) {
+#pragma unroll
+        for (int base = 0; base < 16; base += 2 * h) {
+#pragma unroll
+            for (int k = 0; k < h; ++k) {
+                const float a = v[base + k], b = v[base + h + k];
+                v[base + k] = __fadd_rn(a, b);
+                v[base + h + k] = __fsub_rn(a, b);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float y = __fmul_rn(v[i], 0.25f);
+        if constexpr (std::is_same<T, __half>::value) v[i] = __half2float(__float2half_rn(y));
+        else v[i] = __bfloat162float(__float2bfloat16_rn(y));
+    }
+}
+
+// max |rotated x|: one thread per block of 16 along the rotated axis (x's rows, or x's columns when
+// the tensor is quantized transposed; lanes then walk along a row of x, so loads stay coalesced).
+// Same launch chain as amax_kernel.
+template <typename T>
+__global__ void __launch_bounds__(256) amax_rht_kernel(const T *__restrict__ x, int64_t rows, int64_t cols, int64_t ld,
+                                                       int transposed, float *amax) {
+    float m = 0.0f;
+    const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t units = transposed ? (rows >> 4) * cols : rows * (cols >> 4);
+    for (int64_t u = tid; u < units; u += stride) {
+        float v[16];
+        if (transposed) {
+            const int64_t rb = u / cols, c = u - rb * cols;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = elem_to_float<T>(x[(rb * 16 + i) * ld + c]);
+        } else {
+            const int64_t per_row = cols >> 4, r = u / per_row, cb = u - r * per_row;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = elem_to_float<T>(x[r * ld + cb * 16 + i]);
+        }
+        rotate16<T>(v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+    }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(FULL, m, o));
+    __shared__ float warp_max[8];
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) m = fmaxf(m, warp_max[w]);
         atomicMax(reinterpret_cast<int *>(amax), __float_as_int(m));
     }
 }
@@ -710,6 +782,7 @@ __global__ void __launch_bounds__(CTA_THREADS) quantize_kernel(const QuantParams
     const TensorConsts tc = tensor_consts<KIND>(__ldg(p.amax), p.rule);
     if (p.amax_store != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) *p.amax_store = tc.amax;
     uint32_t lo, hi, sf_byte;
+    if (p.rht) rotate16<T>(v);
     quantize_block<KIND, TWO_D, TRANSPOSED>(v, tc, p.rule, p.exact_only != 0, scratch, lane, nullptr, nullptr, lo, hi,
                                             sf_byte);
 
@@ -798,6 +871,7 @@ quantize_rows_kernel(const QuantParams p) {
             v[2 * k + 1] = f.y;
         }
         uint32_t lo, hi, sf_byte;
+        if (p.rht) rotate16<T>(v);
         quantize_block<KIND, false, false>(v, tc, p.rule, p.exact_only != 0, nullptr, lane, lut, coop[warp], lo, hi, sf_byte);
         const int64_t row = static_cast<int64_t>(tr) * 64 + r_in_tile, cb = tc_ * 4 + cb_in_tile;
         *reinterpret_cast<uint2 *>(p.codes + row * (p.cols_p >> 1) + cb * 8) = make_uint2(lo, hi);
@@ -957,6 +1031,7 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
                 v[2 * i + 1] = f.y;
             }
             uint32_t lo, hi, sf_byte;
+            if (p.rht) rotate16<T>(v);
             quantize_block<KIND, TWO_D, false>(v, tc, p.rule, p.exact_only != 0, TWO_D ? scratch2d + warp * 512 : nullptr, lane,
                                                lut, TWO_D ? nullptr : coop[warp], lo, hi, sf_byte);
             if (!FAKE) {
@@ -1112,6 +1187,7 @@ quantize_cols_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
                 v[i] = elem_to_float<T>(reinterpret_cast<const T &>(h));
             }
             uint32_t lo, hi, sf_byte;
+            if (p.rht) rotate16<T>(v);
             quantize_block<KIND, TWO_D, TWO_D>(v, tc, p.rule, p.exact_only != 0, TWO_D ? scratch2d + warp * 512 : nullptr, lane,
                                                lut, TWO_D ? nullptr : coop[warp], lo, hi, sf_byte);
             words[2 * j] = lo;
@@ -1284,11 +1360,20 @@ inline cudaLaunchConfig_t dependent_launch_config(unsigned grid, unsigned block,
 
 template <typename T>
 cudaError_t launch_amax(const void *x, int64_t rows, int64_t cols, int64_t ld, bool vec16, float *amax,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, bool rht = false, bool transposed = false) {
     cudaLaunchAttribute attr[1];
     cudaLaunchConfig_t cfg = dependent_launch_config(1, 32, stream, attr);
     cudaError_t e = cudaLaunchKernelEx(&cfg, zero_amax_kernel, amax);
     if (e != cudaSuccess) return e;
+    if (rht) {
+        // amax of the ROTATED tensor: 6 resident CTAs per SM is a safe single wave
+        const int64_t units = transposed ? (rows >> 4) * cols : rows * (cols >> 4);
+        int64_t blocks = (units + 255) / 256;
+        if (blocks > 148 * 6) blocks = 148 * 6;
+        if (blocks < 1) blocks = 1;
+        cfg = dependent_launch_config(static_cast<unsigned>(blocks), 256, stream, attr);
+        return cudaLaunchKernelEx(&cfg, amax_rht_kernel<T>, static_cast<const T *>(x), rows, cols, ld, transposed ? 1 : 0, amax);
+    }
     // one wave: as many CTAs as can be resident at once (a partial second wave would run alone)
     static int resident[64] = {};
     int dev = 0;
@@ -1332,6 +1417,7 @@ extern "C" int fos_pseudo_quantize(const void *x, int x_dtype, int64_t rows, int
     if (scale_rule < FOS_RULE_STATIC_6 || scale_rule > FOS_RULE_ABS_MAX) return FOS_ERR_INVALID_ARGUMENT;
     const bool is_static = scale_rule == FOS_RULE_STATIC_6 || scale_rule == FOS_RULE_STATIC_4;
     if (format == FOS_IF4 && is_static) return FOS_ERR_UNSUPPORTED;
+    if (flags & FOS_QUANTIZE_RHT) return FOS_ERR_UNSUPPORTED;
     // only inputs the TMA-fed kernel takes; the caller runs fos_quantize + fos_dequantize otherwise
     if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || (ld * 2) % 16 != 0) return FOS_ERR_UNSUPPORTED;
     int st = check_device();
@@ -1398,6 +1484,8 @@ extern "C" int fos_quantize(const void *x, int x_dtype, int64_t rows, int64_t co
     p.rule = scale_rule;
     p.sf_tiled = sf_layout == FOS_SF_TILED;
     p.exact_only = (flags & FOS_QUANTIZE_EXACT_ONLY) != 0;
+    p.rht = (flags & FOS_QUANTIZE_RHT) != 0;
+    if (p.rht && p.out_cols % 16 != 0) return FOS_ERR_INVALID_ARGUMENT;   // blocks of 16 along the quantized axis
     const uintptr_t addr = reinterpret_cast<uintptr_t>(x);
     const int64_t ld_bytes = ld * 2;
     p.vec_bytes = (addr % 32 == 0 && ld_bytes % 32 == 0) ? 32 : ((addr % 16 == 0 && ld_bytes % 16 == 0) ? 16 : 0);
@@ -1409,8 +1497,8 @@ extern "C" int fos_quantize(const void *x, int x_dtype, int64_t rows, int64_t co
         p.amax_store = amax_in != amax_out ? amax_out : nullptr;
     } else {
         FOS_CUDA_TRY(x_dtype == FOS_BF16
-                         ? launch_amax<__nv_bfloat16>(x, rows, cols, ld, vec16, amax_out, stream)
-                         : launch_amax<__half>(x, rows, cols, ld, vec16, amax_out, stream));
+                         ? launch_amax<__nv_bfloat16>(x, rows, cols, ld, vec16, amax_out, stream, p.rht != 0, transpose != 0)
+                         : launch_amax<__half>(x, rows, cols, ld, vec16, amax_out, stream, p.rht != 0, transpose != 0));
         p.amax = amax_out;
         p.amax_store = nullptr;
     }

@@ -51,8 +51,8 @@ class B200QuantizeBackend:
             return f"scale rule {config.scale_rule.value} is not defined for {config.dtype.value}"
         if config.round_style != RoundStyle.nearest:
             return "only round-to-nearest is implemented"
-        if config.rht:
-            return "the random Hadamard transform is not implemented"
+        if config.rht and x.ndim == 2 and x.shape[0 if config.transpose else 1] % 16 != 0:
+            return "the random Hadamard transform needs a multiple of 16 values along the quantized axis"
         if x.device.type != "cuda":
             return "input must be a CUDA tensor (there is no CPU path)"
         if x.dtype not in (torch.bfloat16, torch.float16):
@@ -89,7 +89,8 @@ class B200QuantizeBackend:
                 _FORMATS[config.dtype], config.scale_rule.cuda_id, int(config.block_scale_2d),
                 int(config.transpose), _native.FOS_SF_TILED if tiled else _native.FOS_SF_ROWMAJOR,
                 0 if amax is None else amax.data_ptr(), values.data_ptr(), scales.data_ptr(),
-                amax_out.data_ptr(), _native.FOS_QUANTIZE_EXACT_ONLY if exact_only else 0,
+                amax_out.data_ptr(),
+                (_native.FOS_QUANTIZE_EXACT_ONLY if exact_only else 0) | (_native.FOS_QUANTIZE_RHT if config.rht else 0),
                 _native.stream_ptr(dev))
         _native.check(status, "fos_quantize")
         return QuantizedTensor(
@@ -139,7 +140,7 @@ class B200QuantizeBackend:
         reason = cls.unsupported_reason(x, config)
         if reason is not None:
             raise ValueError(f"B200 quantize: {reason}")
-        if not config.block_scale_2d and not config.transpose:
+        if not config.block_scale_2d and not config.transpose and not config.rht:
             if x.stride(1) != 1:
                 x = x.contiguous()
             rows, cols = x.shape

@@ -24,7 +24,7 @@ class QuantizationConfig:
     dtype: target format (`nvfp4` or `if4` here).
     kwargs: free-form extras (unused by the kernels, kept for interface parity).
     pseudo_quantize: return the dequantized high-precision tensor instead.
-    rht: apply the 16-point randomised Hadamard transform first (not implemented here).
+    rht: apply the 16-point randomised Hadamard transform to every block of 16 first.
     round_style: `nearest` (implemented) or stochastic variants (not implemented here).
     scale_rule: 4-versus-6 selection rule; default `mse`.
     transpose: quantize the transposed input (output is K-major for the other operand).

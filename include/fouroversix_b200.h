@@ -59,6 +59,10 @@ extern "C" {
 
 /* fos_quantize flags */
 #define FOS_QUANTIZE_EXACT_ONLY 1      /* skip the fast 4-vs-6 pre-filter (testing aid) */
+#define FOS_QUANTIZE_RHT 2             /* rotate every block of 16 along the quantized axis with the reference's
+                                          16-point random Hadamard transform (QuantizationConfig.rht,
+                                          src/fouroversix/quantize/utils.py:19-85) before quantizing; the length of
+                                          that axis (cols, or rows when transposing) must be a multiple of 16 */
 
 int fos_version(void);
 const char *fos_status_string(int status);

@@ -467,6 +467,48 @@ long fos_oracle_check_div6(void) {
     return bad;
 }
 
+/* The 16-point random Hadamard transform the reference applies before quantizing when
+ * QuantizationConfig.rht is set (src/fouroversix/quantize/pytorch/reference.py:568-570 with the
+ * matrix of src/fouroversix/quantize/utils.py:19-85): y = x_block @ (diag(signs) @ H16 / 4), computed
+ * per block of 16 along the last axis of x (of x^T when `transpose`), in binary32, rounded once to
+ * x's type. The sum is evaluated as a fast Walsh-Hadamard transform (four stages of 16 additions
+ * and subtractions); against the reference's matrix product the result is identical unless the
+ * 16 values span more than about ten binades, where single last-place differences occur in a few
+ * values per million. `out` is the rotated tensor, [R][C] or, when `transpose`, [C][R], contiguous.
+ * Returns -1 when the rotated axis is not a multiple of 16. */
+int fos_oracle_rht(const uint16_t *x, int x_is_fp16, int64_t R, int64_t C, int64_t ld, int transpose,
+                   uint16_t *out) {
+    static const float signs[16] = {1, 1, 1, -1, 1, -1, -1, -1, -1, -1, -1, 1, -1, 1, -1, -1};
+    const int64_t Ro = transpose ? C : R, Co = transpose ? R : C;
+    if (Co % 16 != 0) return -1;
+#ifdef _OPENMP
+#pragma omp parallel for schedule(static)
+#endif
+    for (int64_t r = 0; r < Ro; ++r) {
+        for (int64_t c0 = 0; c0 < Co; c0 += 16) {
+            float v[16];
+            for (int i = 0; i < 16; ++i) {
+                const uint16_t h = transpose ? x[(c0 + i) * ld + r] : x[r * ld + c0 + i];
+                v[i] = signs[i] * (x_is_fp16 ? f16_bits_to_f32(h) : bf16_bits_to_f32(h));
+            }
+            for (int h = 1; h < 16; h *= 2) {
+                for (int base = 0; base < 16; base += 2 * h) {
+                    for (int k = 0; k < h; ++k) {
+                        const float a = v[base + k], b = v[base + h + k];
+                        v[base + k] = a + b;
+                        v[base + h + k] = a - b;
+                    }
+                }
+            }
+            for (int i = 0; i < 16; ++i) {
+                const float y = v[i] * 0.25f;
+                out[r * Co + c0 + i] = x_is_fp16 ? f32_to_f16_bits(y) : f32_to_bf16_bits(y);
+            }
+        }
+    }
+    return 0;
+}
+
 /* How many finite binary32 a with |a| >= min_abs (bit patterns start, start + stride, ...) have
  * fma(fma(-d, a * y, a), y, a * y) != a / d, y = fl(1 / d), ignoring the sign of a zero: the
  * division-free quotient of the dequantize kernel. stride 1 is the exhaustive check. */

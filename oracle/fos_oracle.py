@@ -66,6 +66,19 @@ class OracleQuantized:
     tiled: bool
 
 
+def rht(x: torch.Tensor, *, transpose: bool = False) -> torch.Tensor:
+    """The reference's 16-point random Hadamard transform of x (of x^T when `transpose`), in x's dtype."""
+    assert x.device.type == "cpu" and x.ndim == 2 and x.stride(1) == 1
+    assert x.dtype in (torch.bfloat16, torch.float16)
+    R, C = x.shape
+    out = torch.empty((C, R) if transpose else (R, C), dtype=x.dtype)
+    rc = lib().fos_oracle_rht(_ptr(x), ctypes.c_int(x.dtype == torch.float16), ctypes.c_int64(R), ctypes.c_int64(C),
+                              ctypes.c_int64(x.stride(0)), ctypes.c_int(transpose), _ptr(out))
+    if rc != 0:
+        raise ValueError("the rotated axis must be a multiple of 16")
+    return out
+
+
 def quantize(
     x: torch.Tensor,
     *,
@@ -74,7 +87,12 @@ def quantize(
     block_scale_2d: bool = False,
     transpose: bool = False,
     amax: torch.Tensor | None = None,
+    rht: bool = False,
 ) -> OracleQuantized:
+    if rht:
+        # rotate first (after the transposition, as the reference does), then quantize as usual
+        return quantize(globals()["rht"](x, transpose=transpose), dtype=dtype, scale_rule=scale_rule,
+                        block_scale_2d=block_scale_2d, transpose=False, amax=amax)
     dtype, scale_rule = _name(dtype), _name(scale_rule)
     assert x.device.type == "cpu" and x.ndim == 2 and x.stride(1) == 1
     assert x.dtype in (torch.bfloat16, torch.float16)

@@ -92,3 +92,23 @@ def test_division_free_quotient_of_the_dequantize_kernel_is_exact(oracle):
         assert fn(d, 3, 61, 2.0 ** -100) == 0
     # and the guard is needed: below it the remainder underflows and the sequence can be off
     assert fn(1536.0, 5, 1021, 0.0) > 0
+
+
+def test_oracle_reproduces_the_reference_with_the_hadamard_transform(oracle):
+    """Quantization behind the 16-point random Hadamard transform (QuantizationConfig.rht), plain and
+    transposed, NVFP4 and IF4: codes, scales and amax equal the reference's, byte for byte."""
+    import io
+    import lzma
+    from pathlib import Path
+
+    raw = lzma.decompress((Path(__file__).parent / "golden" / "reference_golden_rht.pt.xz").read_bytes())
+    gold = torch.load(io.BytesIO(raw), weights_only=False)
+    assert len(gold["cases"]) >= 28
+    for case in gold["cases"]:
+        x = gold["inputs"][case["input"]]
+        got = oracle.quantize(x, rht=True, **case["config"])
+        v = case["values"]
+        assert torch.equal(got.values[: v.shape[0], : v.shape[1]], v), (case["input"], case["config"])
+        n = case["scale_factors"].numel()
+        assert torch.equal(got.scale_factors[:n], case["scale_factors"]), (case["input"], case["config"])
+        assert torch.equal(got.amax.reshape(1), case["amax"]), (case["input"], case["config"])

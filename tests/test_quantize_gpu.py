@@ -235,3 +235,40 @@ def test_fused_fake_quantization_equals_quantize_then_dequantize(oracle):
             got = fos.quantize(xd, fos.QuantizationConfig(pseudo_quantize=True, **cfg))
             assert got.dtype == x.dtype and got.shape == x.shape
             assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16)), (tuple(x.shape), x.dtype, cfg)
+
+
+@pytest.mark.parametrize("variant", [0, 1], ids=["tma-fed", "register-loads"])
+def test_random_hadamard_transform_matches_reference_and_oracle(oracle, variant):
+    """QuantizationConfig.rht: the committed vectors of the reference (rotation + quantization on
+    CPU) and larger seeded inputs against the oracle, plain and transposed, with both kernel families."""
+    import io
+    import lzma
+    from pathlib import Path
+
+    from fouroversix_b200 import _native
+
+    raw = lzma.decompress((Path(__file__).parent / "golden" / "reference_golden_rht.pt.xz").read_bytes())
+    gold = torch.load(io.BytesIO(raw), weights_only=False)
+    lib = _native.lib()
+    assert lib.fos_set_option(3, variant) == 0
+    try:
+        for case in gold["cases"]:
+            x = gold["inputs"][case["input"]]
+            q = fos.quantize(x.to(DEV), fos.QuantizationConfig(rht=True, **case["config"]))
+            torch.cuda.synchronize()
+            v = case["values"]
+            assert torch.equal(q.values.cpu()[: v.shape[0], : v.shape[1]], v), (case["input"], case["config"])
+            n = case["scale_factors"].numel()
+            assert torch.equal(q.scale_factors.view(torch.uint8).flatten().cpu()[:n], case["scale_factors"])
+            assert torch.equal(q.amax.cpu().reshape(1), case["amax"])
+        g = torch.Generator().manual_seed(41)
+        for shape in [(1024, 512), (640, 4096), (384, 1152)]:
+            x = (torch.randn(shape, generator=g) * 3e-3).bfloat16()
+            xd = x.to(DEV)
+            for cfg in (dict(), dict(transpose=True), dict(transpose=True, scale_rule="static_6"), dict(dtype="if4"),
+                        dict(transpose=True, block_scale_2d=True)):
+                ref = oracle.quantize(x, rht=True, **cfg)
+                q = fos.quantize(xd, fos.QuantizationConfig(rht=True, **cfg))
+                _assert_same(q, ref.values, ref.scale_factors, ref.amax, f"rht {shape} {cfg}")
+    finally:
+        lib.fos_set_option(3, 0)
