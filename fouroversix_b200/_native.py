@@ -30,6 +30,8 @@ SIGNATURES = {
     "fos_last_cuda_error": (_c_int, []),
     "fos_quantize": (_c_int, [_c_ptr, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_int, _c_int, _c_int,
                               _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr]),
+    "fos_quantize_stochastic": (_c_int, [_c_ptr, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                         _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, ctypes.c_uint64, _c_ptr]),
     "fos_pseudo_quantize": (_c_int, [_c_ptr, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr, _c_i64,
                                      _c_ptr, _c_int, _c_ptr]),
     "fos_dequantize": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_i64,

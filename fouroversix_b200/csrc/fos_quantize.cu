@@ -46,6 +46,8 @@ struct QuantParams {
     int vec_bytes;               // 32, 16 or 0: widest aligned load usable on x
     int x_is_ready;              // x was complete before the previous kernel in the stream started
     int rht;                     // rotate every block of 16 (random Hadamard transform) before quantizing
+    int stochastic;              // stochastic rounding (1-D blocks, NVFP4, TMA-fed kernels only)
+    uint32_t seed_lo, seed_hi;
     // fused fake quantization (quantize_rows_tma_kernel<.., true>): dequantized values instead of codes
     void *fake_out;              // [rows][fake_ld] elements of x's type
     int64_t fake_ld;
@@ -439,10 +441,54 @@ __device__ __forceinline__ float4 scale_entry(uint32_t sfb, const TensorConsts &
     return make_float4(s, r, g, usable ? g * g : -1.0f);
 }
 
+// ---- stochastic rounding (RoundStyle.stochastic) ----
+//
+// The reference adds uniform noise in [-0.5, 0.5) grid steps to the magnitude and then rounds to
+// the nearest point of the local grid (src/fouroversix/quantize/pytorch/reference.py:39-51): step
+// 0.5 below 2, 1 below 4, 2 above, the choice made on the magnitude BEFORE the noise, results
+// above 6 clamped. Its random numbers come from torch's generator and cannot be reproduced, so
+// parity here is in distribution (the reference's own test pins distances, tests/test_quantize.py:
+// 317-388). The noise below is a counter-based hash of (seed, block, candidate, element): the
+// same call with the same seed gives the same bytes.
+struct StochasticArgs {
+    uint32_t on;       // 0: round to nearest
+    uint32_t key;      // hash of the seed and the high bits of the block number
+    uint32_t block;    // low bits of the block number
+};
+
+__device__ __forceinline__ uint32_t hash32(uint32_t h) {
+    h ^= h >> 16; h *= 0x7feb352du; h ^= h >> 15; h *= 0x846ca68bu; h ^= h >> 16;
+    return h;
+}
+
+// Codes and quantization residuals t = q - x*r of 16 values rounded stochastically; returns sum t^2.
+__device__ __forceinline__ float encode_stochastic(const float (&v)[16], float r, const StochasticArgs &sr, uint32_t candidate,
+                                                   uint32_t &lo, uint32_t &hi) {
+    float q[16], sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float xs = __fmaf_rn(v[i], r, 0.0f);
+        const float a = fabsf(xs);
+        const float inv = a < 2.0f ? 2.0f : (a < 4.0f ? 1.0f : 0.5f);          // 1 / grid step at |x*r|
+        const float step = a < 2.0f ? 0.5f : (a < 4.0f ? 1.0f : 2.0f);
+        const uint32_t h = hash32(sr.key ^ (sr.block * 32u + candidate * 16u + i));
+        const float noise = __uint_as_float((h >> 9) | 0x3f800000u) - 1.5f;       // uniform in [-0.5, 0.5)
+        const float steps = (__fmaf_rn(a, inv, noise) + 12582912.0f) - 12582912.0f;   // rint, ties to even
+        const float mag = fminf(fmaxf(steps, 0.0f) * step, 6.0f);
+        q[i] = copysignf(mag, xs);
+        const float t = q[i] - xs;
+        sum = __fmaf_rn(t, t, sum);
+    }
+    lo = cvt_e2m1x8(q);          // exact: every q is a grid point
+    hi = cvt_e2m1x8(q + 8);
+    return sum;
+}
+
 template <int KIND, bool TWO_D, bool TRANSPOSED>
 __device__ __forceinline__ void quantize_block(const float (&v)[16], const TensorConsts &tc, int rule,
                                                bool exact_only, float *scratch, int lane, const float4 *lut,
-                                               float *coop, uint32_t &lo, uint32_t &hi, uint32_t &sf_byte) {
+                                               float *coop, uint32_t &lo, uint32_t &hi, uint32_t &sf_byte,
+                                               const StochasticArgs sr = StochasticArgs{0u, 0u, 0u}) {
     const float amax = tc.amax;
     float bmax = 0.0f;
 #pragma unroll
@@ -456,7 +502,11 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
         const uint32_t sfb = cvt_e4m3(hp);
         const float4 ea = lut ? lut[sfb] : scale_entry(sfb, tc, false);
         lo = hi = 0u;
-        if (ea.x != 0.0f) encode_e2m1(v, ea.y, ea.y < 0x1p-16f, lo, hi);
+        if (sr.on) {
+            if (ea.x != 0.0f) encode_stochastic(v, ea.y, sr, 0u, lo, hi);
+        } else if (ea.x != 0.0f) {
+            encode_e2m1(v, ea.y, ea.y < 0x1p-16f, lo, hi);
+        }
         sf_byte = sfb;
         return;
     }
@@ -475,6 +525,20 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
     if (KIND == KIND_ADAPTIVE) {
         const float4 eb = lut ? lut[sfb_b] : scale_entry(sfb_b, tc, filter_allowed);
         const float s_b = eb.x, r_b = eb.y;
+
+        if (sr.on) {
+            // both candidates rounded stochastically with independent noise, the one with the smaller
+            // error of THIS draw wins (mean-squared error; g = s * amax / 1536 converts to x's units)
+            uint32_t lo_a = 0u, hi_a = 0u, lo_b = 0u, hi_b = 0u;
+            const float ga = s_a * amax * (1.0f / 1536.0f), gb = s_b * amax * (1.0f / 1536.0f);
+            const float err_a = s_a != 0.0f ? encode_stochastic(v, r_a, sr, 0u, lo_a, hi_a) * ga * ga : 0.0f;
+            const float err_b = s_b != 0.0f ? encode_stochastic(v, r_b, sr, 1u, lo_b, hi_b) * gb * gb : 0.0f;
+            const bool take_b = err_b < err_a;
+            lo = take_b ? lo_b : lo_a;
+            hi = take_b ? hi_b : hi_a;
+            sf_byte = take_b ? sfb_b : sfb_a;
+            return;
+        }
 
         // Fast pre-filter: 1-D blocks, mean-squared error, both scales normal E4M3 numbers (so
         // |x*r| <= 6.4 and a rounding residual t = q - x*r is at most 1.01), amax and r in a range
@@ -709,6 +773,15 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
     lo = pick_int ? lo_i : lo_f;
     hi = pick_int ? hi_i : hi_f;
     sf_byte = sfb_a + (pick_int ? 128u : 0u);
+}
+
+// Noise stream of one block for the stochastic rounding: keyed by the seed and the block's number.
+__device__ __forceinline__ StochasticArgs stochastic_args(const QuantParams &p, int64_t block_number) {
+    StochasticArgs a;
+    a.on = static_cast<uint32_t>(p.stochastic);
+    a.key = hash32(hash32(p.seed_hi ^ static_cast<uint32_t>(static_cast<uint64_t>(block_number) >> 27)) ^ p.seed_lo);
+    a.block = static_cast<uint32_t>(block_number);
+    return a;
 }
 
 // ------------------------------------------------------------------------------------
@@ -1008,7 +1081,7 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
     int64_t code_off = static_cast<int64_t>(tr) * 128 * code_ld + tc_ * 32;
     int64_t sf_off = p.sf_tiled ? static_cast<int64_t>(blockIdx.x) * 512 : static_cast<int64_t>(tr) * 128 * n_cb + tc_ * 4;
 
-    int fake_tr = tr;                                   // tile row, tracked only for the fused fake quantization
+    int fake_tr = tr;                                   // tile row of the current tile
     const DequantConsts dk = dequant_consts(tc.amax, p.fake_divisor);
     int s = 0;
     uint32_t parity = 0;
@@ -1032,8 +1105,11 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
             }
             uint32_t lo, hi, sf_byte;
             if (p.rht) rotate16<T>(v);
+            StochasticArgs sr{0u, 0u, 0u};
+            if (!TWO_D && p.stochastic)
+                sr = stochastic_args(p, (static_cast<int64_t>(fake_tr) * 128 + j * 64 + row_in_tile) * n_cb + tc_ * 4 + cb);
             quantize_block<KIND, TWO_D, false>(v, tc, p.rule, p.exact_only != 0, TWO_D ? scratch2d + warp * 512 : nullptr, lane,
-                                               lut, TWO_D ? nullptr : coop[warp], lo, hi, sf_byte);
+                                               lut, TWO_D ? nullptr : coop[warp], lo, hi, sf_byte, sr);
             if (!FAKE) {
                 *reinterpret_cast<uint2 *>(codes + j * code_half) = make_uint2(lo, hi);
                 sf[j * sf_half] = static_cast<uint8_t>(sf_byte);
@@ -1063,10 +1139,8 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));
         if (++s == FEED_STAGES) { s = 0; parity ^= 1u; }
-        if (FAKE) {
-            fake_tr += step_r;
-            if (tc_ + step_c >= tiles_c) ++fake_tr;
-        }
+        fake_tr += step_r;                              // (tile row: used by the fake quantization and the noise stream)
+        if (tc_ + step_c >= tiles_c) ++fake_tr;
         code_off += code_step;
         sf_off += sf_step;
         tc_ += step_c;
@@ -1188,8 +1262,11 @@ quantize_cols_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
             }
             uint32_t lo, hi, sf_byte;
             if (p.rht) rotate16<T>(v);
+            StochasticArgs sr{0u, 0u, 0u};
+            if (!TWO_D && p.stochastic)
+                sr = stochastic_args(p, (static_cast<int64_t>(tr) * 128 + jr) * n_cb + tc_ * 4 + pair * 2 + j);
             quantize_block<KIND, TWO_D, TWO_D>(v, tc, p.rule, p.exact_only != 0, TWO_D ? scratch2d + warp * 512 : nullptr, lane,
-                                               lut, TWO_D ? nullptr : coop[warp], lo, hi, sf_byte);
+                                               lut, TWO_D ? nullptr : coop[warp], lo, hi, sf_byte, sr);
             words[2 * j] = lo;
             words[2 * j + 1] = hi;
             sf_pair |= sf_byte << (8 * j);
@@ -1455,10 +1532,18 @@ extern "C" int fos_pseudo_quantize(const void *x, int x_dtype, int64_t rows, int
     return launched ? FOS_OK : FOS_ERR_UNSUPPORTED;
 }
 
-extern "C" int fos_quantize(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int format,
-                            int scale_rule, int block_2d, int transpose, int sf_layout, const float *amax_in,
-                            uint8_t *codes, uint8_t *sf, float *amax_out, int flags, void *stream_) {
+static int quantize_entry(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int format,
+                          int scale_rule, int block_2d, int transpose, int sf_layout, const float *amax_in,
+                          uint8_t *codes, uint8_t *sf, float *amax_out, int flags, void *stream_, int stochastic,
+                          uint64_t seed) {
     using namespace fos;
+    if (stochastic) {
+        // stochastic rounding lives in the TMA-fed kernels only: NVFP4, 1-D blocks, aligned input
+        if (format != FOS_NVFP4 || block_2d) return FOS_ERR_UNSUPPORTED;
+        if (g_quantize_variant == 1 || reinterpret_cast<uintptr_t>(x) % 16 != 0 || (ld * 2) % 16 != 0) return FOS_ERR_UNSUPPORTED;
+        if (transpose && (reinterpret_cast<uintptr_t>(codes) % 16 != 0 || reinterpret_cast<uintptr_t>(sf) % 2 != 0))
+            return FOS_ERR_UNSUPPORTED;
+    }
     if (!x || !codes || !sf || !amax_out) return FOS_ERR_INVALID_ARGUMENT;
     if (rows <= 0 || cols <= 0 || ld < cols) return FOS_ERR_INVALID_ARGUMENT;
     if (x_dtype != FOS_BF16 && x_dtype != FOS_FP16) return FOS_ERR_INVALID_ARGUMENT;
@@ -1486,6 +1571,9 @@ extern "C" int fos_quantize(const void *x, int x_dtype, int64_t rows, int64_t co
     p.exact_only = (flags & FOS_QUANTIZE_EXACT_ONLY) != 0;
     p.rht = (flags & FOS_QUANTIZE_RHT) != 0;
     if (p.rht && p.out_cols % 16 != 0) return FOS_ERR_INVALID_ARGUMENT;   // blocks of 16 along the quantized axis
+    p.stochastic = stochastic;
+    p.seed_lo = static_cast<uint32_t>(seed);
+    p.seed_hi = static_cast<uint32_t>(seed >> 32);
     const uintptr_t addr = reinterpret_cast<uintptr_t>(x);
     const int64_t ld_bytes = ld * 2;
     p.vec_bytes = (addr % 32 == 0 && ld_bytes % 32 == 0) ? 32 : ((addr % 16 == 0 && ld_bytes % 16 == 0) ? 16 : 0);
@@ -1517,4 +1605,18 @@ extern "C" int fos_wait_failure_site(int32_t *site) {
     if (!site) return FOS_ERR_INVALID_ARGUMENT;
     FOS_CUDA_TRY(cudaMemcpyFromSymbol(site, fos::g_wait_failures, sizeof(int32_t)));
     return FOS_OK;
+}
+
+extern "C" int fos_quantize(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int format,
+                            int scale_rule, int block_2d, int transpose, int sf_layout, const float *amax_in,
+                            uint8_t *codes, uint8_t *sf, float *amax_out, int flags, void *stream) {
+    return quantize_entry(x, x_dtype, rows, cols, ld, format, scale_rule, block_2d, transpose, sf_layout, amax_in, codes, sf,
+                          amax_out, flags, stream, 0, 0);
+}
+
+extern "C" int fos_quantize_stochastic(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int format,
+                                       int scale_rule, int block_2d, int transpose, int sf_layout, const float *amax_in,
+                                       uint8_t *codes, uint8_t *sf, float *amax_out, int flags, uint64_t seed, void *stream) {
+    return quantize_entry(x, x_dtype, rows, cols, ld, format, scale_rule, block_2d, transpose, sf_layout, amax_in, codes, sf,
+                          amax_out, flags, stream, 1, seed);
 }

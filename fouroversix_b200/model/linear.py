@@ -11,12 +11,11 @@ Interface, buffer names and buffer layouts follow the reference module
 [out*in/16], `quantized_weight_amax` f32 [1], `quantized_weight_metadata` i32 [6] =
 (rows, cols, padded rows, padded cols, 1, scales-are-tiled).
 
-Differences, all on the training path: the reference rotates both wgrad operands with a
-16-point randomised Hadamard transform before quantizing them and rounds gradients
-stochastically by default; this package implements neither yet, so the backward pass
-requires `gradient_round_style="nearest"` and skips the rotation (which is orthogonal and
-therefore changes quantization error only, not the quantity being computed). The
-Quartet-II backward is not implemented.
+Like the reference, the backward pass rotates both wgrad operands with the 16-point randomised
+Hadamard transform before quantizing them (the rotation is orthogonal along the contracted
+token axis, so it changes quantization error only) and rounds gradients as
+`gradient_round_style` says (stochastic by default; the noise is seeded from torch's CPU
+generator). Not implemented: `stochastic_unbiased` rounding and the Quartet-II backward.
 """
 
 from __future__ import annotations
@@ -73,10 +72,10 @@ class FourOverSixLinearFunction(torch.autograd.Function):
         cfg: ModuleQuantizationConfig = ctx.config
         if cfg.quartet_ii_dtype is not None:
             raise NotImplementedError("the Quartet-II backward pass is not implemented")
-        if cfg.gradient_round_style != RoundStyle.nearest and not (
+        if cfg.gradient_round_style == RoundStyle.stochastic_unbiased and not (
                 cfg.disable_dgrad_quantization and cfg.disable_wgrad_quantization):
             raise NotImplementedError(
-                "stochastic gradient rounding is not implemented; set gradient_round_style='nearest'")
+                "stochastic_unbiased gradient rounding is not implemented; use 'stochastic' or 'nearest'")
 
         dy = grad_output.reshape(-1, grad_output.shape[-1])     # [tokens, out]
         x = input.reshape(-1, input.shape[-1])                   # [tokens, in]
@@ -92,16 +91,17 @@ class FourOverSixLinearFunction(torch.autograd.Function):
                                   other_config=cfg.get_weight_config(transpose=True), out_dtype=cfg.output_dtype)
         dx = dx.reshape(*grad_output.shape[:-1], w.shape[1])
 
-        # wgrad: dW[out, in] = dy^T @ x = q(dy^T) @ q(x^T)^T
+        # wgrad: dW[out, in] = dy^T @ x = q(rot(dy^T)) @ q(rot(x^T))^T, rotation along the token axis
+        # (src/fouroversix/model/modules/linear.py:245-256)
         if cfg.disable_wgrad_quantization:
             dw = dy.T @ x
         elif cfg.pseudo_quantize:
-            dw = quantize(dy, cfg.get_gradient_config(transpose=True)) @ \
-                quantize(x, cfg.get_activation_config(transpose=True)).T
+            dw = quantize(dy, cfg.get_gradient_config(rht=True, transpose=True)) @ \
+                quantize(x, cfg.get_activation_config(rht=True, transpose=True)).T
         else:
             dw = quantized_matmul(dy, x, backend=cfg.matmul_backend,
-                                  input_config=cfg.get_gradient_config(transpose=True),
-                                  other_config=cfg.get_activation_config(transpose=True),
+                                  input_config=cfg.get_gradient_config(rht=True, transpose=True),
+                                  other_config=cfg.get_activation_config(rht=True, transpose=True),
                                   out_dtype=cfg.output_dtype)
 
         db = dy.sum(0) if bias is not None and ctx.needs_input_grad[3] else None

@@ -49,8 +49,10 @@ class B200QuantizeBackend:
             return f"dtype {config.dtype.value} is not implemented (nvfp4 and if4 are)"
         if config.scale_rule not in config.dtype.supported_scale_rules:
             return f"scale rule {config.scale_rule.value} is not defined for {config.dtype.value}"
-        if config.round_style != RoundStyle.nearest:
-            return "only round-to-nearest is implemented"
+        if config.round_style == RoundStyle.stochastic_unbiased:
+            return "stochastic_unbiased rounding is not implemented (nearest and stochastic are)"
+        if config.round_style == RoundStyle.stochastic and (config.dtype != DataType.nvfp4 or config.block_scale_2d):
+            return "stochastic rounding is implemented for NVFP4 with 1-D blocks"
         if config.rht and x.ndim == 2 and x.shape[0 if config.transpose else 1] % 16 != 0:
             return "the random Hadamard transform needs a multiple of 16 values along the quantized axis"
         if x.device.type != "cuda":
@@ -65,9 +67,11 @@ class B200QuantizeBackend:
 
     @classmethod
     def quantize(cls, x: torch.Tensor, config: QuantizationConfig, *, amax: torch.Tensor | None = None,
-                 exact_only: bool = False) -> QuantizedTensor:
+                 exact_only: bool = False, seed: int | None = None) -> QuantizedTensor:
         """Quantize `x` (or its transpose). `amax`, when given, is a CUDA fp32 tensor that
-        already holds max|x| and saves the extra pass that computes it."""
+        already holds max|x| and saves the extra pass that computes it. With stochastic rounding,
+        `seed` selects the noise (default: drawn from torch's CPU generator, so torch.manual_seed
+        makes a run repeatable)."""
         reason = cls.unsupported_reason(x, config)
         if reason is not None:
             raise ValueError(f"B200 quantize: {reason}")
@@ -83,15 +87,21 @@ class B200QuantizeBackend:
         if amax is not None:
             amax = amax.detach().reshape(1).to(device=dev, dtype=torch.float32)
         tiled = _is_tiled(config.dtype)
-        with torch.cuda.device(dev):
-            status = _native.lib().fos_quantize(
-                x.data_ptr(), _native.elem_code(x.dtype), rows, cols, x.stride(0),
+        args = (x.data_ptr(), _native.elem_code(x.dtype), rows, cols, x.stride(0),
                 _FORMATS[config.dtype], config.scale_rule.cuda_id, int(config.block_scale_2d),
                 int(config.transpose), _native.FOS_SF_TILED if tiled else _native.FOS_SF_ROWMAJOR,
                 0 if amax is None else amax.data_ptr(), values.data_ptr(), scales.data_ptr(),
                 amax_out.data_ptr(),
-                (_native.FOS_QUANTIZE_EXACT_ONLY if exact_only else 0) | (_native.FOS_QUANTIZE_RHT if config.rht else 0),
-                _native.stream_ptr(dev))
+                (_native.FOS_QUANTIZE_EXACT_ONLY if exact_only else 0) | (_native.FOS_QUANTIZE_RHT if config.rht else 0))
+        with torch.cuda.device(dev):
+            if config.round_style == RoundStyle.stochastic:
+                if seed is None:
+                    seed = int(torch.randint(0, 2 ** 62, (1,)).item())
+                status = _native.lib().fos_quantize_stochastic(*args, seed, _native.stream_ptr(dev))
+                if status == -2:
+                    raise ValueError("B200 quantize: stochastic rounding needs a 16-byte aligned input (base and row stride)")
+            else:
+                status = _native.lib().fos_quantize(*args, _native.stream_ptr(dev))
         _native.check(status, "fos_quantize")
         return QuantizedTensor(
             values, scales.view(torch.float8_e4m3fn), amax_out, config.dtype, out_shape,

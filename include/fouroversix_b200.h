@@ -180,6 +180,23 @@ int fos_gemm_if4_static(const uint8_t *a_codes, const uint8_t *a_sf, int a_forma
                         int64_t m, int64_t n, int64_t ldd, int32_t *status, void *stream);
 
 /*
+ * fos_quantize with stochastic rounding (RoundStyle.stochastic of the reference: uniform noise of
+ * +-half a grid step is added to every scaled magnitude before it is rounded; with a 4/6 rule both
+ * candidates get independent noise and the better draw wins). `seed` selects the noise: the same
+ * call with the same seed writes the same bytes. NVFP4, 1-D blocks, x 16-byte aligned (base and row
+ * stride; when transposing also codes 16-byte and sf 2-byte aligned); anything else returns
+ * FOS_ERR_UNSUPPORTED. The reference draws its noise from torch's generator, so the two agree in
+ * distribution, not bit for bit.
+ *
+ * Replaces: the rbits / is_rtn = false path of torch.ops.fouroversix.quantize
+ * (src/fouroversix/csrc/bindings.cpp:28) and fake_quantize_to_e2m1(..., round_style=stochastic)
+ * (src/fouroversix/quantize/pytorch/reference.py:30-51).
+ */
+int fos_quantize_stochastic(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int format,
+                            int scale_rule, int block_2d, int transpose, int sf_layout, const float *amax_in,
+                            uint8_t *codes, uint8_t *sf, float *amax_out, int flags, uint64_t seed, void *stream);
+
+/*
  * Fused fake quantization: out = dequantize(quantize(x)) in x's element type, one pass over x
  * after the amax pass, nothing packed is written. 1-D blocks, untransposed; `out` is
  * [rows][ld_out] elements and only rows x cols of it are written. amax_in / amax_out / flags as

@@ -114,13 +114,48 @@ def test_training_forward_dgrad_wgrad(tokens, k, n):
     wt_q = deq(w, block_scale_2d=True, transpose=True)
     assert torch.equal(wt_q, w_q.T)
     _close(x.grad.reshape(tokens, k), _fp32_matmul(deq(dy2), wt_q.T))
-    # wgrad: q(dy^T) @ q(x^T)^T
-    _close(lin.weight.grad, _fp32_matmul(deq(dy2, transpose=True), deq(x2, transpose=True).T))
+    # wgrad: q(rot(dy^T)) @ q(rot(x^T))^T: both operands rotated along the token axis by the same
+    # orthogonal transform, as in the reference
+    _close(lin.weight.grad, _fp32_matmul(deq(dy2, transpose=True, rht=True), deq(x2, transpose=True, rht=True).T))
+    # and the rotation leaves the product itself alone: the result is the true gradient up to FP4 noise
+    true = _fp32_matmul(dy2.T, x2)
+    cos = torch.nn.functional.cosine_similarity(lin.weight.grad.float().flatten(), true.flatten(), dim=0).item()
+    assert cos > 0.97, cos
 
 
-def test_stochastic_gradient_rounding_is_refused_clearly():
-    lin = nn.Linear(128, 128, bias=False, device=DEV, dtype=torch.bfloat16)
+def test_default_backward_uses_stochastic_gradient_rounding():
+    """The reference's defaults: gradients rounded stochastically (seeded from torch's CPU generator),
+    wgrad operands rotated. Repeatable under torch.manual_seed, different across seeds, unbiased enough
+    that the gradients keep the direction of the exact ones."""
+    g = torch.Generator().manual_seed(3)
+    lin = nn.Linear(512, 256, bias=False, device=DEV, dtype=torch.bfloat16)
     layer = fos.FourOverSixLinear(lin, fos.ModuleQuantizationConfig(keep_master_weights=True))
+    x0 = torch.randn(1, 1024, 512, generator=g).bfloat16().to(DEV)
+    dy = (torch.randn(1, 1024, 256, generator=g) * 1e-3).bfloat16().to(DEV)
+
+    def grads(seed):
+        torch.manual_seed(seed)
+        x = x0.clone().requires_grad_(True)
+        lin.weight.grad = None
+        layer(x).backward(dy)
+        return x.grad.clone(), lin.weight.grad.clone()
+
+    dx_a, dw_a = grads(1)
+    dx_b, dw_b = grads(1)
+    dx_c, dw_c = grads(2)
+    assert torch.equal(dx_a, dx_b) and torch.equal(dw_a, dw_b)
+    assert not torch.equal(dx_a, dx_c) and not torch.equal(dw_a, dw_c)
+    true_dx = _fp32_matmul(dy.reshape(-1, 256), lin.weight.data).reshape(1, 1024, 512)
+    true_dw = _fp32_matmul(dy.reshape(-1, 256).T, x0.reshape(-1, 512))
+    for got, true in ((dx_a, true_dx), (dw_a, true_dw)):
+        cos = torch.nn.functional.cosine_similarity(got.float().flatten(), true.flatten(), dim=0).item()
+        assert cos > 0.95, cos
+
+
+def test_unbiased_stochastic_rounding_is_refused_clearly():
+    lin = nn.Linear(128, 128, bias=False, device=DEV, dtype=torch.bfloat16)
+    layer = fos.FourOverSixLinear(
+        lin, fos.ModuleQuantizationConfig(keep_master_weights=True, gradient_round_style="stochastic_unbiased"))
     x = torch.randn(1, 128, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
-    with pytest.raises(NotImplementedError, match="stochastic"):
+    with pytest.raises(NotImplementedError, match="stochastic_unbiased"):
         layer(x).sum().backward()

@@ -272,3 +272,42 @@ def test_random_hadamard_transform_matches_reference_and_oracle(oracle, variant)
                 _assert_same(q, ref.values, ref.scale_factors, ref.amax, f"rht {shape} {cfg}")
     finally:
         lib.fos_set_option(3, 0)
+
+
+def test_stochastic_rounding_statistics():
+    """RoundStyle.stochastic. The reference's generator cannot be reproduced, so the checks are the
+    ones its own test makes (tests/test_quantize.py:317-388: distance between x and its quantized
+    copy on a 1024 x 1024 N(0,1) tensor, 137 for static_6 and 122 for the 4/6 MSE rule with its
+    Triton kernels, 141 with TransformerEngine, each +-5 %) plus what defines the method: every value
+    lands on one of the two grid points around it, the mean over many seeds approaches x, the same
+    seed repeats and another seed does not."""
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(1024, 1024, generator=g).bfloat16()
+    xd = x.to(DEV)
+    for rule, lo, hi in (("static_6", 137 * 0.95, 141 * 1.05), ("mse", 122 * 0.95, 126 * 1.05)):
+        cfg = fos.QuantizationConfig(scale_rule=rule, round_style="stochastic")
+        q1 = B200QuantizeBackend.quantize(xd, cfg, seed=11)
+        q2 = B200QuantizeBackend.quantize(xd, cfg, seed=11)
+        q3 = B200QuantizeBackend.quantize(xd, cfg, seed=12)
+        assert torch.equal(q1.values, q2.values) and torch.equal(q1.scale_factors.view(torch.uint8), q2.scale_factors.view(torch.uint8))
+        assert not torch.equal(q1.values, q3.values)
+        dist = torch.dist(fos.dequantize(q1, torch.float32), xd.float()).item()
+        assert lo <= dist <= hi, (rule, dist)
+    # static_6: same scales as round-to-nearest, every code within one grid step of the nearest one,
+    # and the average over seeds converges to x (round-to-nearest has a fixed error instead)
+    cfg = fos.QuantizationConfig(scale_rule="static_6", round_style="stochastic")
+    near = fos.quantize(xd, fos.QuantizationConfig(scale_rule="static_6"))
+    acc = torch.zeros_like(xd, dtype=torch.float32)
+    n_seeds = 64
+    for seed in range(n_seeds):
+        q = B200QuantizeBackend.quantize(xd, cfg, seed=seed)
+        assert torch.equal(q.scale_factors.view(torch.uint8), near.scale_factors.view(torch.uint8))
+        acc += fos.dequantize(q, torch.float32)
+    mean_err = (acc / n_seeds - xd.float()).pow(2).mean().sqrt().item()
+    near_err = (fos.dequantize(near, torch.float32) - xd.float()).pow(2).mean().sqrt().item()
+    assert mean_err < 0.35 * near_err, (mean_err, near_err)
+    # transposed + rotated (the wgrad configuration) runs and repeats
+    cfg = fos.QuantizationConfig(round_style="stochastic", transpose=True, rht=True)
+    qa = B200QuantizeBackend.quantize(xd, cfg, seed=5)
+    qb = B200QuantizeBackend.quantize(xd, cfg, seed=5)
+    assert torch.equal(qa.values, qb.values) and qa.padded_shape == (1024, 1024)
