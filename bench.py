@@ -249,6 +249,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     if rank != 0:
         # the other ranks still take part in the sharded GEMM section below
         gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks)
+        stack_section(args, fos, dev, rank, world)
         return
 
     # the dominant kernel alone: with amax given a call is one launch of the quantize kernel
@@ -266,7 +267,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                     ("mse_amax_given", None),
                     ("if4_mse", fos.QuantizationConfig(dtype="if4")),
                     ("mse_2d", fos.QuantizationConfig(block_scale_2d=True)),
-                    ("mse_transposed", fos.QuantizationConfig(transpose=True))):
+                    ("mse_transposed", fos.QuantizationConfig(transpose=True)),
+                    ("mxfp4_static_6", fos.QuantizationConfig(dtype="mxfp4", scale_rule="static_6")),
+                    ("mxfp4_static_6_transposed", fos.QuantizationConfig(dtype="mxfp4", scale_rule="static_6", transpose=True))):
         if c is None:
             fn = lambda i: B200QuantizeBackend.quantize(a_sets[i % N_ROTATE], cfg_mse, amax=amaxes[i % N_ROTATE])  # noqa: E731
         else:
@@ -340,6 +343,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     e2e_serial_value = BYTES_PER_ELEM * n_elem / (serial_ms * 1e-3) / 1e9
 
     gemm = gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks)
+    stack = stack_section(args, fos, dev, rank, world)
 
     # the configuration as a whole: quantize both operands (activation 4/6 MSE per call, weight too)
     # and multiply, through the public front end; plus the other kernels of the path on the same tensor
@@ -395,6 +399,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         },
         "quantize_modes": modes,
         "gemm": gemm,
+        "decoder_linear_stack": stack,
         "pipeline": pipeline,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms,
@@ -415,12 +420,14 @@ def gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks):
     with more GPUs the N dimension of B is split across ranks (column parallel, no
     collective) and the slowest rank defines the time."""
     out = {}
-    for name, (m, n, k) in (("square_8192", (8192, 8192, 8192)), ("act_x_weight", (8192, 4096, 4096))):
+    mx = fos.QuantizationConfig(dtype="mxfp4", scale_rule="static_6")
+    for name, (m, n, k) in (("square_8192", (8192, 8192, 8192)), ("act_x_weight", (8192, 4096, 4096)),
+                            ("square_8192_mxfp4", (8192, 8192, 8192))):
         n_local = n // world
         g = torch.Generator(device=dev).manual_seed(3 + rank)
         a = torch.randn(m, k, generator=g, device=dev).bfloat16()
-        b = (torch.randn(n_local, k, generator=g, device=dev) * (1.0 if name == "square_8192" else 0.02)).bfloat16()
-        qa, qb = fos.quantize(a), fos.quantize(b)
+        b = (torch.randn(n_local, k, generator=g, device=dev) * (0.02 if name == "act_x_weight" else 1.0)).bfloat16()
+        qa, qb = (fos.quantize(a, mx), fos.quantize(b, mx)) if name.endswith("mxfp4") else (fos.quantize(a), fos.quantize(b))
         d = torch.empty(m, n_local, dtype=torch.bfloat16, device=dev)
         del a, b
         fn = lambda i: B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType.bfloat16, out=d)  # noqa: E731
@@ -444,6 +451,78 @@ def gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks):
             "gpu_launches_per_step": 2, "l2": "operands + output (200 MiB at 8192^3) exceed L2",
         }
     return out
+
+
+STACK_TOKENS = 16 * 2048
+STACK_LAYERS = (  # name, parallelism, out features N, in features K: the linear layers of one Llama-3-70B decoder block
+    ("qkv_proj", "column", 10240, 8192),
+    ("o_proj", "row", 8192, 8192),
+    ("gate_proj", "column", 28672, 8192),
+    ("up_proj", "column", 28672, 8192),
+    ("down_proj", "row", 8192, 28672),
+)
+
+
+def stack_section(args, fos, dev, rank, world):
+    """The linear layers of one Llama-3-70B-shaped decoder block on 16 x 2048 tokens, tensor parallel over the
+    ranks: NVFP4 4/6 weights quantized once per shard, activations quantized on every call (4/6 MSE),
+    column-parallel layers without a collective, row-parallel layers followed by an all-reduce that
+    overlaps the GEMM chunk by chunk. Every layer gets its own random input of the right shape (this is
+    the stack of GEMMs, not a transformer). Per layer: time of the whole call (max over ranks), and for
+    row-parallel layers the GEMM part and the all-reduce part on their own."""
+    from fouroversix_b200.sharding import TensorParallelLinear, shard_bounds
+
+    cfg = fos.ModuleQuantizationConfig()
+    steps, warm = max(5, min(args.steps, 10)), 3
+    layers, total_ms, total_flop = {}, 0.0, 0.0
+
+    def timed(fn):
+        if world > 1:
+            dist.barrier()
+        ms = time_cuda(lambda i: fn(), steps, warm)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for idx, (name, mode, n, k) in enumerate(STACK_LAYERS):
+        g = torch.Generator(device=dev).manual_seed(12 + idx + 100 * rank)
+        if mode == "column":
+            lo, hi = shard_bounds(n, rank, world, 128)
+            w_shape, k_local = (hi - lo, k), k
+        else:
+            lo, hi = shard_bounds(k, rank, world, 64)
+            w_shape, k_local = (n, hi - lo), hi - lo
+        w = (torch.randn(*w_shape, generator=g, device=dev) * 0.02).bfloat16()
+        x = torch.randn(STACK_TOKENS, k_local, generator=g, device=dev).bfloat16()
+        layer = TensorParallelLinear(w, cfg, mode)
+        del w
+        ms = timed(lambda: layer(x))
+        flop = 2.0 * STACK_TOKENS * n * k
+        entry = {"mode": mode, "n": n, "k": k, "ms": ms, "TFLOP/s": flop / (ms * 1e-3) / 1e12}
+        if mode == "row" and world > 1:
+            act_cfg = cfg.get_activation_config()
+            entry["ms_quantize_and_gemm"] = timed(lambda: layer._gemm(x, act_cfg))
+            out = torch.empty(STACK_TOKENS, n, dtype=torch.bfloat16, device=dev)
+            entry["ms_all_reduce"] = timed(lambda: dist.all_reduce(out))
+            nbytes = out.numel() * 2
+            entry["all_reduce_bytes"] = nbytes
+            entry["all_reduce_bus_GB/s"] = 2.0 * (world - 1) / world * nbytes / (entry["ms_all_reduce"] * 1e-3) / 1e9
+            entry["nvlink_bound_ms"] = 2.0 * (world - 1) / world * nbytes / 900e9 * 1e3
+            del out
+        layers[name] = entry
+        total_ms += ms
+        total_flop += flop
+        del layer, x
+        torch.cuda.empty_cache()
+    return {
+        "tokens": STACK_TOKENS, "n_gpus": world, "layers": layers, "ms": total_ms,
+        "TFLOP/s": total_flop / (total_ms * 1e-3) / 1e12,
+        "how": "eager calls of sharding.TensorParallelLinear.forward (dynamic activation quantization + FP4 GEMM "
+               "[+ NCCL all-reduce on a second stream, 4 chunks of tokens]); CUDA events, max over ranks; weights "
+               "quantized per shard outside the timed region",
+    }
 
 
 def main() -> None:

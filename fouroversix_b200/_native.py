@@ -16,7 +16,7 @@ _LIB_PATH = Path(__file__).resolve().parent / "libfouroversix_b200.so"
 _lib: ctypes.CDLL | None = None
 
 FOS_BF16, FOS_FP16, FOS_FP32 = 0, 1, 2
-FOS_NVFP4, FOS_IF4 = 0, 1
+FOS_NVFP4, FOS_IF4, FOS_MXFP4 = 0, 1, 2
 FOS_SF_ROWMAJOR, FOS_SF_TILED = 0, 1
 FOS_QUANTIZE_EXACT_ONLY = 1
 FOS_QUANTIZE_RHT = 2
@@ -38,6 +38,8 @@ SIGNATURES = {
                                 _c_ptr, _c_int, _c_i64, _c_ptr]),
     "fos_gemm_alpha": (_c_int, [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr]),
     "fos_gemm_nvfp4": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_i64, _c_i64,
+                                _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
+    "fos_gemm_mxfp4": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_i64, _c_i64,
                                 _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
     "fos_gemm_if4_workspace_bytes": (_c_i64, [_c_i64, _c_i64, _c_i64]),
     "fos_gemm_if4": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int,

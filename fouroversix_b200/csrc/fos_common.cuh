@@ -21,6 +21,12 @@ extern int g_quantize_variant;
 // FOS_OK when the current device is compute capability 10.x, else FOS_ERR_ARCH / FOS_ERR_CUDA.
 int check_device();
 
+// MXFP4 branches of fos_quantize / fos_dequantize (fos_mxfp4.cu); arguments validated by the callers.
+int quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int scale_rule, int block_2d,
+                   int transpose, int sf_layout, uint8_t *codes, uint8_t *sf, float *amax_out, cudaStream_t stream);
+int dequantize_mxfp4(const uint8_t *codes, const uint8_t *sf, int sf_layout, int64_t rows_p, int64_t cols_p, int64_t rows,
+                     int64_t cols, void *out, int out_dtype, int64_t ld_out, cudaStream_t stream);
+
 #define FOS_CUDA_TRY(expr)                                         \
     do {                                                           \
         cudaError_t fos_e_ = (expr);                               \

@@ -64,7 +64,18 @@ extern "C" int fos_dequantize(const uint8_t *codes, const uint8_t *sf, const flo
                               int scale_rule, int sf_layout, int64_t rows_p, int64_t cols_p, int64_t rows,
                               int64_t cols, void *out, int out_dtype, int64_t ld_out, void *stream_) {
     using namespace fos;
-    if (!codes || !sf || !amax || !out) return FOS_ERR_INVALID_ARGUMENT;
+    if (!codes || !sf || !out || (!amax && format != FOS_MXFP4)) return FOS_ERR_INVALID_ARGUMENT;
+    if (format == FOS_MXFP4) {
+        if (sf_layout != FOS_SF_ROWMAJOR && sf_layout != FOS_SF_TILED) return FOS_ERR_INVALID_ARGUMENT;
+        if (rows_p <= 0 || cols_p <= 0 || rows_p % 128 != 0 || cols_p % 128 != 0) return FOS_ERR_INVALID_ARGUMENT;
+        if (rows <= 0 || cols <= 0 || rows > rows_p || cols > cols_p || ld_out < cols) return FOS_ERR_INVALID_ARGUMENT;
+        if (out_dtype != FOS_BF16 && out_dtype != FOS_FP16 && out_dtype != FOS_FP32) return FOS_ERR_INVALID_ARGUMENT;
+        if (reinterpret_cast<uintptr_t>(codes) % 8 != 0) return FOS_ERR_MISALIGNED;
+        const int st_mx = check_device();
+        if (st_mx != FOS_OK) return st_mx;
+        return dequantize_mxfp4(codes, sf, sf_layout, rows_p, cols_p, rows, cols, out, out_dtype, ld_out,
+                                static_cast<cudaStream_t>(stream_));
+    }
     if (format != FOS_NVFP4 && format != FOS_IF4) return FOS_ERR_INVALID_ARGUMENT;
     if (scale_rule < FOS_RULE_STATIC_6 || scale_rule > FOS_RULE_ABS_MAX) return FOS_ERR_INVALID_ARGUMENT;
     if (sf_layout != FOS_SF_ROWMAJOR && sf_layout != FOS_SF_TILED) return FOS_ERR_INVALID_ARGUMENT;

@@ -94,6 +94,7 @@ struct GemmParams {
     int64_t m, n, ldd;       // region of D that is written
     int out_dtype;
     int debug;               // FOS_OPT_GEMM_DEBUG bits (timing experiments only; results are wrong)
+    int mx;                  // operands are MXFP4: E8M0 scales per 32 values, a 512-byte scale tile spans 128 values of K
 };
 
 // ---------------------------------------------------------------------------- MMA wrappers
@@ -104,6 +105,18 @@ __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, ui
         "{ .reg .pred p;\n"
         "setp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p; }\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+
+// MXFP4: two E8M0 scales per row and K-block (scale_vec::2X); which two of the four bytes of a
+// scale column an instruction uses is part of its descriptor.
+__device__ __forceinline__ void tc_mma_mxf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p; }\n"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
         : "memory");
 }
@@ -120,9 +133,14 @@ __device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t d_tmem, uint64_t a_des
 
 // Instruction descriptor of kind::mxf4nvf4 block-scaled MMA: A and B E2M1 (code 1 in bits
 // [7,10) and [10,13)), both K-major, N >> 3 in [17,23), UE4M3 scales (bit 23 = 0), M >> 4 in
-// [24,29), scale-factor byte ids 0, dense K = 64.
+// [24,29), scale-factor byte ids 0, dense K = 64. MXFP4: E8M0 scales (bit 23 = 1) and the byte
+// offset (0 or 2) of the instruction's two scales inside the 32-bit scale column in [4,6) for B
+// and [29,31) for A.
 __device__ __forceinline__ uint32_t mma_idesc(int n, int m = BLOCK_M) {
     return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+__device__ __forceinline__ uint32_t mma_idesc_mx(uint32_t idesc, uint32_t sf_byte) {
+    return idesc | (1u << 23) | (sf_byte << 4) | (sf_byte << 29);
 }
 
 // ---------------------------------------------------------------------------- kernel
@@ -230,7 +248,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             if (f_t >= num_tiles) return;
             // two tensor copies per stage: [K-blocks kb0 .. kb0+3] x [one / N_GROUPS row groups] of
             // 512-byte tiles; what lies beyond K or N is zero-filled and still counted
-            const int kb0 = static_cast<int>(f_kt * KB_PER_STAGE);
+            // (MXFP4: a tile spans two K-blocks, a stage uses the first two tiles of the box)
+            const int kb0 = static_cast<int>(f_kt * (p.mx ? KB_PER_STAGE / 2 : KB_PER_STAGE));
             const uint32_t dst = sf_base + slot * C::SF_SLOT_BYTES, bar = sf_full_bar + 8 * slot;
             mbar_expect_tx(bar, C::SF_SLOT_BYTES);
             tma_load_3d(dst, &map_sfa, 0, kb0, a_group, bar);
@@ -290,9 +309,16 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const uint64_t a_desc = smem_desc(stage, 16, 1024, 2);
                 const uint64_t b_desc = smem_desc(stage + A_BYTES, 16, 1024, 2);
                 const uint32_t sfa_tmem = tmem_base + SF_COL0 + j * C::SF_STAGE_COLS, sfb_tmem = sfa_tmem + 16;
-                for (int kb = 0; kb < nkb && !dbg_no_mma; ++kb)
-                    tc_mma_nvf4(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc, sfa_tmem + 4 * kb,
-                                sfb_tmem + (BLOCK_N / 32) * kb, (kt > 0 || kb > 0) ? 1u : 0u);
+                if (p.mx) {
+                    for (int kb = 0; kb < nkb && !dbg_no_mma; ++kb)
+                        tc_mma_mxf4(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, mma_idesc_mx(idesc, (kb & 1) * 2),
+                                    sfa_tmem + 4 * (kb >> 1), sfb_tmem + (BLOCK_N / 32) * (kb >> 1),
+                                    (kt > 0 || kb > 0) ? 1u : 0u);
+                } else {
+                    for (int kb = 0; kb < nkb && !dbg_no_mma; ++kb)
+                        tc_mma_nvf4(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc, sfa_tmem + 4 * kb,
+                                    sfb_tmem + (BLOCK_N / 32) * kb, (kt > 0 || kb > 0) ? 1u : 0u);
+                }
                 tc_commit(empty_bar + 8 * s);          // stage (and scale slot) reusable once these MMAs are done
                 if (++s == C::STAGES) { s = 0; ph ^= 1u; }
                 if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
@@ -391,7 +417,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 const int64_t kb0 = kt * KB_PER_STAGE;
-                const int nkb = static_cast<int>((k_blocks - kb0) < KB_PER_STAGE ? (k_blocks - kb0) : KB_PER_STAGE);
+                int nkb = static_cast<int>((k_blocks - kb0) < KB_PER_STAGE ? (k_blocks - kb0) : KB_PER_STAGE);
+                if (p.mx) nkb = (nkb + 1) >> 1;          // scale tiles in use: one per two K-blocks
                 const uint32_t sfa_smem = sf_base + j * C::SF_SLOT_BYTES + lane * 16, sfb_smem = sfa_smem + SFA_BYTES;
                 const uint32_t slot = lane_base + SF_COL0 + j * C::SF_STAGE_COLS;
                 uint32_t r[16];
@@ -852,13 +879,13 @@ extern "C" int fos_set_option(int key, int value) {
     return FOS_ERR_INVALID_ARGUMENT;
 }
 
-extern "C" int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
-                              const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
-                              int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, int32_t *status,
-                              void *stream_) {
+static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                          const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
+                          int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, int32_t *status,
+                          void *stream_, int mx) {
     using namespace fos;
     if (!a_codes || !a_sf || !b_codes || !b_sf || !alpha || !d) return FOS_ERR_INVALID_ARGUMENT;
-    if (m_p <= 0 || n_p <= 0 || k_p < 64 || m_p % 128 || n_p % 128 || k_p % 64) return FOS_ERR_INVALID_ARGUMENT;
+    if (m_p <= 0 || n_p <= 0 || k_p < 64 || m_p % 128 || n_p % 128 || k_p % (mx ? 128 : 64)) return FOS_ERR_INVALID_ARGUMENT;
     if (m <= 0 || n <= 0 || m > m_p || n > n_p || ldd < n) return FOS_ERR_INVALID_ARGUMENT;
     if (out_dtype != FOS_BF16 && out_dtype != FOS_FP16 && out_dtype != FOS_FP32) return FOS_ERR_INVALID_ARGUMENT;
     if (reinterpret_cast<uintptr_t>(a_codes) % 16 || reinterpret_cast<uintptr_t>(b_codes) % 16 ||
@@ -873,7 +900,8 @@ extern "C" int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const
     FOS_CUDA_TRY(cudaGetDevice(&dev));
     FOS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
 
-    GemmParams p{a_sf, b_sf, alpha, d, status, m_p, n_p, k_p, m, n, ldd, out_dtype, g_gemm_debug};
+    GemmParams p{a_sf, b_sf, alpha, d, status, m_p, n_p, k_p, m, n, ldd, out_dtype, g_gemm_debug, mx};
+    const int64_t sf_k_tiles = mx ? k_p / 128 : k_p / 64;     // 512-byte scale tiles along K
     if (status) FOS_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
     CUtensorMap map_a, map_b;
 
@@ -881,7 +909,7 @@ extern "C" int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const
     // (its hand-overs between the two SMs lengthen the load round trip), so it only runs when
     // asked for.
     const bool pair_fits = m_p % 256 == 0 && n_p % 256 == 0;
-    const bool use_pair = pair_fits && g_gemm_variant == 2;
+    const bool use_pair = pair_fits && g_gemm_variant == 2 && !mx;
     if (use_pair) {
         CUtensorMap map_sfa, map_sfb;
         if ((st = make_operand_map(&map_a, a_codes, m_p, k_p / 2, 128)) != FOS_OK) return st;
@@ -901,8 +929,22 @@ extern "C" int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const
     if ((st = make_operand_map(&map_a, a_codes, m_p, k_p / 2, BLOCK_M)) != FOS_OK) return st;
     if ((st = make_operand_map(&map_b, b_codes, n_p, k_p / 2, wide ? 256 : 128)) != FOS_OK) return st;
     CUtensorMap map_sfa, map_sfb;
-    if ((st = make_scale_map(&map_sfa, a_sf, m_p / 128, k_p / 64, 1)) != FOS_OK) return st;
-    if ((st = make_scale_map(&map_sfb, b_sf, n_p / 128, k_p / 64, wide ? 2 : 1)) != FOS_OK) return st;
+    if ((st = make_scale_map(&map_sfa, a_sf, m_p / 128, sf_k_tiles, 1)) != FOS_OK) return st;
+    if ((st = make_scale_map(&map_sfb, b_sf, n_p / 128, sf_k_tiles, wide ? 2 : 1)) != FOS_OK) return st;
     return wide ? launch_out<256>(map_a, map_b, map_sfa, map_sfb, p, sms, stream)
                 : launch_out<128>(map_a, map_b, map_sfa, map_sfb, p, sms, stream);
+}
+
+extern "C" int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                              const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
+                              int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, int32_t *status,
+                              void *stream) {
+    return gemm_fp4_entry(a_codes, a_sf, b_codes, b_sf, alpha, d, out_dtype, m_p, n_p, k_p, m, n, ldd, status, stream, 0);
+}
+
+extern "C" int fos_gemm_mxfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                              const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
+                              int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, int32_t *status,
+                              void *stream) {
+    return gemm_fp4_entry(a_codes, a_sf, b_codes, b_sf, alpha, d, out_dtype, m_p, n_p, k_p, m, n, ldd, status, stream, 1);
 }

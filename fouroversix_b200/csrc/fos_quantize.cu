@@ -1490,6 +1490,7 @@ extern "C" int fos_pseudo_quantize(const void *x, int x_dtype, int64_t rows, int
     if (!x || !out || !amax_out) return FOS_ERR_INVALID_ARGUMENT;
     if (rows <= 0 || cols <= 0 || ld < cols || ld_out < cols) return FOS_ERR_INVALID_ARGUMENT;
     if (x_dtype != FOS_BF16 && x_dtype != FOS_FP16) return FOS_ERR_INVALID_ARGUMENT;
+    if (format == FOS_MXFP4) return FOS_ERR_UNSUPPORTED;          // quantize, then dequantize
     if (format != FOS_NVFP4 && format != FOS_IF4) return FOS_ERR_INVALID_ARGUMENT;
     if (scale_rule < FOS_RULE_STATIC_6 || scale_rule > FOS_RULE_ABS_MAX) return FOS_ERR_INVALID_ARGUMENT;
     const bool is_static = scale_rule == FOS_RULE_STATIC_6 || scale_rule == FOS_RULE_STATIC_4;
@@ -1547,9 +1548,19 @@ static int quantize_entry(const void *x, int x_dtype, int64_t rows, int64_t cols
     if (!x || !codes || !sf || !amax_out) return FOS_ERR_INVALID_ARGUMENT;
     if (rows <= 0 || cols <= 0 || ld < cols) return FOS_ERR_INVALID_ARGUMENT;
     if (x_dtype != FOS_BF16 && x_dtype != FOS_FP16) return FOS_ERR_INVALID_ARGUMENT;
-    if (format != FOS_NVFP4 && format != FOS_IF4) return FOS_ERR_INVALID_ARGUMENT;
+    if (format != FOS_NVFP4 && format != FOS_IF4 && format != FOS_MXFP4) return FOS_ERR_INVALID_ARGUMENT;
     if (scale_rule < FOS_RULE_STATIC_6 || scale_rule > FOS_RULE_ABS_MAX) return FOS_ERR_INVALID_ARGUMENT;
     if (sf_layout != FOS_SF_ROWMAJOR && sf_layout != FOS_SF_TILED) return FOS_ERR_INVALID_ARGUMENT;
+    if (format == FOS_MXFP4) {
+        // power-of-two scales per 32 values: static rules only, no rotation, one kernel, no amax pass
+        if ((scale_rule != FOS_RULE_STATIC_6 && scale_rule != FOS_RULE_STATIC_4) || (flags & FOS_QUANTIZE_RHT))
+            return FOS_ERR_UNSUPPORTED;
+        if (reinterpret_cast<uintptr_t>(codes) % 8 != 0) return FOS_ERR_MISALIGNED;
+        const int st_mx = check_device();
+        if (st_mx != FOS_OK) return st_mx;
+        return quantize_mxfp4(x, x_dtype, rows, cols, ld, scale_rule, block_2d, transpose, sf_layout, codes, sf, amax_out,
+                              static_cast<cudaStream_t>(stream_));
+    }
     const bool is_static = scale_rule == FOS_RULE_STATIC_6 || scale_rule == FOS_RULE_STATIC_4;
     if (format == FOS_IF4 && is_static) return FOS_ERR_UNSUPPORTED;
     if (reinterpret_cast<uintptr_t>(codes) % 8 != 0) return FOS_ERR_MISALIGNED;

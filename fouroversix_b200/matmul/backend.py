@@ -17,7 +17,7 @@ from fouroversix_b200.quantize.backend import B200QuantizeBackend
 from fouroversix_b200.utils import DataType
 
 _OUT = {DataType.bfloat16: torch.bfloat16, DataType.float16: torch.float16, DataType.float32: torch.float32}
-_FORMATS = {DataType.nvfp4: _native.FOS_NVFP4, DataType.if4: _native.FOS_IF4}
+_FORMATS = {DataType.nvfp4: _native.FOS_NVFP4, DataType.if4: _native.FOS_IF4, DataType.mxfp4: _native.FOS_MXFP4}
 
 
 def _layout(q: QuantizedTensor) -> int:
@@ -26,7 +26,8 @@ def _layout(q: QuantizedTensor) -> int:
 
 class B200MatmulBackend:
     """FP4 x FP4 -> bf16 / fp16 / fp32 on the 5th-generation tensor cores: block-scaled
-    kind::mxf4nvf4 MMAs for NVFP4 operands, expand-to-fp16 + kind::f16 MMAs for IF4."""
+    kind::mxf4nvf4 MMAs for NVFP4 operands, kind::mxf4 MMAs for MXFP4 operands (alpha = 1, as in
+    src/fouroversix/matmul/cutlass/backend.py:79-84), expand-to-fp16 + kind::f16 MMAs for IF4."""
 
     @classmethod
     def is_available(cls) -> bool:
@@ -41,7 +42,12 @@ class B200MatmulBackend:
                 "in column-major layout, and both inputs must have the same inner "
                 "dimension")
         if input.dtype not in _FORMATS or other.dtype not in _FORMATS:
-            return "operands must be nvfp4 or if4"
+            return "operands must be nvfp4, if4 or mxfp4"
+        if (input.dtype == DataType.mxfp4) != (other.dtype == DataType.mxfp4):
+            return "an mxfp4 operand needs an mxfp4 partner"
+        if input.dtype == DataType.mxfp4 and not (input.scale_factors_are_in_blackwell_layout
+                                                  and other.scale_factors_are_in_blackwell_layout):
+            return "mxfp4 operands need their scales in the tile layout"
         if input.device.type != "cuda" or other.device != input.device:
             return "both operands must live on the same CUDA device"
         if DataType(out_dtype) not in _OUT:
@@ -81,10 +87,20 @@ class B200MatmulBackend:
         native_fp4 = (fa == fb == _native.FOS_NVFP4 and _layout(input) == _layout(other) == _native.FOS_SF_TILED)
         with torch.cuda.device(dev):
             lib, stream = _native.lib(), _native.stream_ptr(dev)
+            status_ptr = 0 if status is None else status.data_ptr()
+            if fa == _native.FOS_MXFP4:
+                alpha.fill_(1.0)
+                _native.check(lib.fos_gemm_mxfp4(
+                    a_vals.data_ptr(), a_sf.data_ptr(), b_vals.data_ptr(), b_sf.data_ptr(), alpha.data_ptr(),
+                    out.data_ptr(), _native.elem_code(torch_out), m_p, n_p, k_p, m, n, out.stride(0),
+                    status_ptr, stream), "fos_gemm_mxfp4")
+                if status is not None and int(status.item()) != 0:
+                    raise _native.NativeLibraryError(
+                        f"fos_gemm_mxfp4: a bounded device-side wait timed out (site {int(status.item())})")
+                return out
             _native.check(lib.fos_gemm_alpha(
                 input.amax.data_ptr(), fa, input.scale_rule.cuda_id,
                 other.amax.data_ptr(), fb, other.scale_rule.cuda_id, alpha.data_ptr(), stream), "fos_gemm_alpha")
-            status_ptr = 0 if status is None else status.data_ptr()
             if native_fp4:
                 _native.check(lib.fos_gemm_nvfp4(
                     a_vals.data_ptr(), a_sf.data_ptr(), b_vals.data_ptr(), b_sf.data_ptr(), alpha.data_ptr(),

@@ -20,13 +20,18 @@ from fouroversix_b200.utils import DataType, RoundStyle, ScaleType
 from .config import QuantizationConfig
 from .quantized_tensor import QuantizedTensor, padded_shape_for
 
-_FORMATS = {DataType.nvfp4: _native.FOS_NVFP4, DataType.if4: _native.FOS_IF4}
+_FORMATS = {DataType.nvfp4: _native.FOS_NVFP4, DataType.if4: _native.FOS_IF4, DataType.mxfp4: _native.FOS_MXFP4}
 
 
 def _is_tiled(dtype: DataType) -> bool:
     # like the reference's PyTorch back end, IF4 keeps its scales row-major
     # (src/fouroversix/quantize/pytorch/backend.py:107-120)
-    return dtype == DataType.nvfp4
+    return dtype in (DataType.nvfp4, DataType.mxfp4)
+
+
+def _scale_view(scales: torch.Tensor, dtype: DataType) -> torch.Tensor:
+    """The scale bytes typed as the reference types them: E4M3, or E8M0 for the MX formats."""
+    return scales.view(torch.float8_e8m0fnu if dtype.scale_type == ScaleType.mx else torch.float8_e4m3fn)
 
 
 class B200QuantizeBackend:
@@ -46,13 +51,15 @@ class B200QuantizeBackend:
         if x.ndim != 2:
             return "input must be 2-D"
         if config.dtype not in _FORMATS:
-            return f"dtype {config.dtype.value} is not implemented (nvfp4 and if4 are)"
+            return f"dtype {config.dtype.value} is not implemented (nvfp4, if4 and mxfp4 are)"
         if config.scale_rule not in config.dtype.supported_scale_rules:
             return f"scale rule {config.scale_rule.value} is not defined for {config.dtype.value}"
         if config.round_style == RoundStyle.stochastic_unbiased:
             return "stochastic_unbiased rounding is not implemented (nearest and stochastic are)"
         if config.round_style == RoundStyle.stochastic and (config.dtype != DataType.nvfp4 or config.block_scale_2d):
             return "stochastic rounding is implemented for NVFP4 with 1-D blocks"
+        if config.rht and config.dtype == DataType.mxfp4:
+            return "the random Hadamard transform is not implemented for mxfp4"
         if config.rht and x.ndim == 2 and x.shape[0 if config.transpose else 1] % 16 != 0:
             return "the random Hadamard transform needs a multiple of 16 values along the quantized axis"
         if x.device.type != "cuda":
@@ -82,7 +89,7 @@ class B200QuantizeBackend:
         rows_p, cols_p = padded_shape_for(out_shape, config.dtype)
         dev = x.device
         values = torch.empty(rows_p, cols_p // 2, dtype=torch.uint8, device=dev)
-        scales = torch.empty(rows_p * cols_p // 16, dtype=torch.uint8, device=dev)
+        scales = torch.empty(rows_p * cols_p // config.dtype.block_size, dtype=torch.uint8, device=dev)
         amax_out = torch.empty(1, dtype=torch.float32, device=dev)
         if amax is not None:
             amax = amax.detach().reshape(1).to(device=dev, dtype=torch.float32)
@@ -104,7 +111,7 @@ class B200QuantizeBackend:
                 status = _native.lib().fos_quantize(*args, _native.stream_ptr(dev))
         _native.check(status, "fos_quantize")
         return QuantizedTensor(
-            values, scales.view(torch.float8_e4m3fn), amax_out, config.dtype, out_shape,
+            values, _scale_view(scales, config.dtype), amax_out, config.dtype, out_shape,
             config.scale_rule, config.round_style, (rows_p, cols_p),
             scale_factors_are_in_blackwell_layout=tiled)
 
@@ -131,10 +138,10 @@ class B200QuantizeBackend:
         out = torch.empty(rows, cols, dtype=dtype, device=dev)
         values = tensor.values.contiguous()
         scales = tensor.scale_factors.contiguous()
-        amax = tensor.amax.to(device=dev, dtype=torch.float32)
+        amax = None if tensor.amax is None else tensor.amax.to(device=dev, dtype=torch.float32)
         with torch.cuda.device(dev):
             status = _native.lib().fos_dequantize(
-                values.data_ptr(), scales.data_ptr(), amax.data_ptr(), _FORMATS[tensor.dtype],
+                values.data_ptr(), scales.data_ptr(), 0 if amax is None else amax.data_ptr(), _FORMATS[tensor.dtype],
                 tensor.scale_rule.cuda_id,
                 _native.FOS_SF_TILED if tensor.scale_factors_are_in_blackwell_layout else _native.FOS_SF_ROWMAJOR,
                 rows_p, cols_p, rows, cols, out.data_ptr(), _native.elem_code(dtype), out.stride(0),
@@ -150,7 +157,7 @@ class B200QuantizeBackend:
         reason = cls.unsupported_reason(x, config)
         if reason is not None:
             raise ValueError(f"B200 quantize: {reason}")
-        if not config.block_scale_2d and not config.transpose and not config.rht:
+        if not config.block_scale_2d and not config.transpose and not config.rht and config.dtype != DataType.mxfp4:
             if x.stride(1) != 1:
                 x = x.contiguous()
             rows, cols = x.shape

@@ -46,6 +46,7 @@ extern "C" {
 /* 4-bit format */
 #define FOS_NVFP4 0                    /* E2M1 values, E4M3 scale per 16 */
 #define FOS_IF4 1                      /* per block E2M1 or INT4*(6/7); scale sign bit = int */
+#define FOS_MXFP4 2                    /* E2M1 values, E8M0 scale per 32, no per-tensor scale */
 
 /* scale rule; same numbers as ScaleRule.cuda_id, src/fouroversix/utils.py:271-280 */
 #define FOS_RULE_STATIC_6 0
@@ -74,7 +75,9 @@ int fos_last_cuda_error(void);
  * elements, unit column stride) to Y = x, or to Y = x^T when `transpose` is set.
  * Writes all of codes / sf (padding included, no pre-zeroing needed) and amax_out.
  *
- *   format      FOS_NVFP4 (all five rules) or FOS_IF4 (mae / mse / abs_max)
+ *   format      FOS_NVFP4 (all five rules), FOS_IF4 (mae / mse / abs_max) or FOS_MXFP4 (static_6 /
+ *               static_4; blocks of 32, cols padded to 128, one scale byte per 32 values, amax_out = 1,
+ *               amax_in ignored; src/fouroversix/quantize/pytorch/reference.py:149-181)
  *   block_2d    0: one scale per 1x16 block of Y; 1: one scale per 16x16 block of Y
  *   sf_layout   FOS_SF_TILED or FOS_SF_ROWMAJOR
  *   amax_in     NULL: the library computes max|x| itself (one extra pass over x);
@@ -135,6 +138,20 @@ int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b
                    const uint8_t *b_sf, const float *alpha, void *d, int out_dtype,
                    int64_t m_p, int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd,
                    int32_t *status, void *stream);
+
+/*
+ * The same GEMM for two MXFP4 operands (E8M0 scale per 32 values, scales in the 128 x 4 tile
+ * order as fos_quantize(FOS_MXFP4, FOS_SF_TILED) writes them): tcgen05.mma kind::mxf4 with
+ * scale_vec::2X. k_p must be a multiple of 128; everything else as for fos_gemm_nvfp4. The
+ * reference passes alpha = 1 (src/fouroversix/matmul/cutlass/backend.py:79-84).
+ *
+ * Replaces: torch.ops.fouroversix.gemm_mxfp4mxfp4_accum_fp32_out_bf16_tnt,
+ * src/fouroversix/csrc/bindings.cpp:29, Python caller src/fouroversix/matmul/cutlass/ops.py:6-20.
+ */
+int fos_gemm_mxfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                   const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
+                   int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, int32_t *status,
+                   void *stream);
 
 /*
  * D[m, n] = alpha[0] * sum_k A[m, k] * B[n, k] for operands in FOS_IF4 or FOS_NVFP4 (any mix),

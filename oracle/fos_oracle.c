@@ -37,7 +37,7 @@
 #include <omp.h>
 #endif
 
-enum { FOS_FMT_NVFP4 = 0, FOS_FMT_IF4 = 1 };
+enum { FOS_FMT_NVFP4 = 0, FOS_FMT_IF4 = 1, FOS_FMT_MXFP4 = 2 };
 /* Same numbering as ScaleRule.cuda_id, src/fouroversix/utils.py:271-280. */
 enum { RULE_STATIC_6 = 0, RULE_STATIC_4 = 1, RULE_MAE = 2, RULE_MSE = 3, RULE_ABS_MAX = 4 };
 enum { OUT_BF16 = 0, OUT_FP16 = 1, OUT_FP32 = 2 };
@@ -263,6 +263,26 @@ static float quantize_block(const float *x, int n, float amax, int format, int r
     return worst;
 }
 
+/* MXFP4 (src/fouroversix/quantize/pytorch/reference.py:149-181): one block of n (32 or 32 x 32)
+ * values, scale = the power of two at or above max|x| / maxq stored as its biased exponent
+ * (E8M0), values divided by it and rounded to E2M1. No per-tensor scale. */
+static float quantize_block_mx(const float *x, int n, int rule, uint8_t *codes, uint8_t *sf_out) {
+    float bmax = 0.0f, worst = 0.0f;
+    for (int i = 0; i < n; ++i) { float a = fabsf(x[i]); if (a > bmax) bmax = a; }
+    const float hp = bmax / (rule == RULE_STATIC_4 ? 4.0f : 6.0f);
+    const uint32_t bits = f32_as_u32(hp);
+    uint8_t e = (uint8_t)((bits >> 23) & 0xff);
+    if (bits & 0x7fffff) e = (uint8_t)(e + 1);            /* round up; uint8 arithmetic as in the reference */
+    const float scale = u32_as_f32((uint32_t)e << 23);
+    for (int i = 0; i < n; ++i) {
+        float xs = e != 0 ? x[i] / scale : 0.0f;
+        if (fabsf(xs) > worst) worst = fabsf(xs);
+        codes[i] = e2m1_code_from_value(fake_e2m1(xs));
+    }
+    *sf_out = e;
+    return worst;
+}
+
 /* ------------------------------------------------------------------ layouts */
 
 static inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
@@ -290,14 +310,18 @@ int fos_oracle_quantize(const uint16_t *x, int x_is_fp16, int64_t R, int64_t C, 
                         int format, int rule, int block_2d, int transpose, int sf_tiled,
                         const float *amax_in, uint8_t *codes, uint8_t *sf, float *amax_out,
                         uint8_t *choice, float *worst_scaled) {
-    if (format != FOS_FMT_NVFP4 && format != FOS_FMT_IF4) return -1;
+    if (format != FOS_FMT_NVFP4 && format != FOS_FMT_IF4 && format != FOS_FMT_MXFP4) return -1;
     if (rule < 0 || rule > 4) return -1;
     if (format == FOS_FMT_IF4 && (rule == RULE_STATIC_6 || rule == RULE_STATIC_4)) return -1;
+    if (format == FOS_FMT_MXFP4 && rule != RULE_STATIC_6 && rule != RULE_STATIC_4) return -1;
+    const int mx = format == FOS_FMT_MXFP4;
+    const int bw = mx ? 32 : 16;                    /* block width; four blocks per scale tile column group */
     const int64_t Ro = transpose ? C : R, Co = transpose ? R : C;
-    const int64_t Rp = round_up(Ro, 128), Cp = round_up(Co, 64), ncb = Cp / 16;
+    const int64_t Rp = round_up(Ro, 128), Cp = round_up(Co, 4 * bw), ncb = Cp / bw;
 
     float amax = 0.0f;
-    if (amax_in) amax = *amax_in;
+    if (mx) amax = 1.0f;                            /* reference.py:573-578: ones for MXFP4 */
+    else if (amax_in) amax = *amax_in;
     else {
         #pragma omp parallel for reduction(max : amax) schedule(static)
         for (int64_t i = 0; i < R; ++i)
@@ -310,30 +334,31 @@ int fos_oracle_quantize(const uint16_t *x, int x_is_fp16, int64_t R, int64_t C, 
     *amax_out = amax;
 
     float worst_all = 0.0f;
-    const int bh = block_2d ? 16 : 1;               /* block height in rows of Y */
+    const int bh = block_2d ? bw : 1;               /* block height in rows of Y */
     #pragma omp parallel for reduction(max : worst_all) schedule(static)
     for (int64_t r0 = 0; r0 < Rp; r0 += bh) {
-        float v[256];
-        uint8_t cd[256];
+        float v[1024];
+        uint8_t cd[1024];
         for (int64_t cb = 0; cb < ncb; ++cb) {
             for (int dr = 0; dr < bh; ++dr)
-                for (int dc = 0; dc < 16; ++dc) {
-                    int64_t i = r0 + dr, j = cb * 16 + dc;
+                for (int dc = 0; dc < bw; ++dc) {
+                    int64_t i = r0 + dr, j = cb * bw + dc;
                     float f = 0.0f;
                     if (i < Ro && j < Co) {
                         uint16_t h = transpose ? x[j * ld + i] : x[i * ld + j];
                         f = x_is_fp16 ? f16_bits_to_f32(h) : bf16_bits_to_f32(h);
                     }
-                    v[dr * 16 + dc] = f;
+                    v[dr * bw + dc] = f;
                 }
-            uint8_t sfb, ch;
-            float w = quantize_block(v, bh * 16, amax, format, rule, cd, &sfb, &ch);
+            uint8_t sfb, ch = 0;
+            float w = mx ? quantize_block_mx(v, bh * bw, rule, cd, &sfb)
+                         : quantize_block(v, bh * bw, amax, format, rule, cd, &sfb, &ch);
             if (w > worst_all) worst_all = w;
             for (int dr = 0; dr < bh; ++dr) {
                 int64_t i = r0 + dr;
-                uint8_t *dst = codes + i * (Cp / 2) + cb * 8;
-                for (int p = 0; p < 8; ++p)
-                    dst[p] = (uint8_t)((cd[dr * 16 + 2 * p + 1] << 4) | (cd[dr * 16 + 2 * p] & 0xf));
+                uint8_t *dst = codes + i * (Cp / 2) + cb * (bw / 2);
+                for (int p = 0; p < bw / 2; ++p)
+                    dst[p] = (uint8_t)((cd[dr * bw + 2 * p + 1] << 4) | (cd[dr * bw + 2 * p] & 0xf));
                 int64_t off = sf_tiled ? sf_tiled_offset(i, cb, ncb) : i * ncb + cb;
                 sf[off] = sfb;
                 if (choice) choice[i * ncb + cb] = ch;
@@ -385,6 +410,22 @@ static inline void store_out(void *out, int64_t idx, int out_type, float v) {
 int fos_oracle_dequantize(const uint8_t *codes, const uint8_t *sf, const float *amax_p,
                           int format, int rule, int sf_tiled, int64_t Rp, int64_t Cp,
                           int64_t R, int64_t C, int out_type, void *out) {
+    if (format == FOS_FMT_MXFP4) {
+        /* quantize/backend.py:88-160: fp16(value) * fp16(2^(e-127)) in fp16, nothing else (the
+         * E8M0 -> fp16 conversion overflows to inf above 2^15 and flushes below 2^-24) */
+        const int64_t nb = Cp / 32;
+        #pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < R; ++i)
+            for (int64_t j = 0; j < C; ++j) {
+                uint8_t byte = codes[i * (Cp / 2) + j / 2];
+                uint8_t nib = (j & 1) ? (byte >> 4) : (byte & 0xf);
+                uint8_t e = sf[sf_tiled ? sf_tiled_offset(i, j / 32, nb) : i * nb + j / 32];
+                float s16 = e == 255 ? NAN : round_to_f16(e == 0 ? 0x1p-127f : u32_as_f32((uint32_t)e << 23));
+                float m = E2M1_VALUE[nib & 7];
+                store_out(out, i * C + j, out_type, round_to_f16(((nib & 8) ? -m : m) * s16));
+            }
+        return 0;
+    }
     const float amax = *amax_p, div = dequant_divisor(format, rule);
     const int64_t ncb = Cp / 16;
     #pragma omp parallel for schedule(static)
@@ -402,6 +443,7 @@ int fos_oracle_dequantize(const uint8_t *codes, const uint8_t *sf, const float *
 
 /* alpha = amaxA * amaxB / (divisorA * divisorB), one rounding per operation. */
 float fos_oracle_alpha(float amax_a, int format_a, int rule_a, float amax_b, int format_b, int rule_b) {
+    if (format_a == FOS_FMT_MXFP4 && format_b == FOS_FMT_MXFP4) return 1.0f;   /* matmul/cutlass/backend.py:79-84 */
     float num = amax_a * amax_b;
     /* the reference multiplies the four integer constants in Python before dividing */
     double den = (double)dequant_divisor(format_a, rule_a) * (double)dequant_divisor(format_b, rule_b);

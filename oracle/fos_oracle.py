@@ -18,7 +18,7 @@ import torch
 _HERE = Path(__file__).resolve().parent
 _LIB: ctypes.CDLL | None = None
 
-FORMATS = {"nvfp4": 0, "if4": 1}
+FORMATS = {"nvfp4": 0, "if4": 1, "mxfp4": 2}
 # Same numbering as the reference's ScaleRule.cuda_id (src/fouroversix/utils.py:271-280).
 RULES = {"static_6": 0, "static_4": 1, "mae": 2, "mse": 3, "abs_max": 4}
 OUT_TYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
@@ -55,7 +55,7 @@ class OracleQuantized:
     """What the reference's PyTorch backend returns for one tensor, plus diagnostics."""
 
     values: torch.Tensor          # uint8 [Rp, Cp/2]
-    scale_factors: torch.Tensor   # uint8 [Rp*Cp/16]; 128x4-tiled for nvfp4, row-major for if4
+    scale_factors: torch.Tensor   # uint8 [Rp*Cp/16] ([Rp*Cp/32] for mxfp4); 128x4-tiled for nvfp4 / mxfp4, row-major for if4
     amax: torch.Tensor            # float32 [1]
     choice: torch.Tensor          # uint8 [Rp, Cp/16]: 1 where "4" (nvfp4) or "int" (if4) won
     worst_scaled: float           # max |x / scale| over all candidates
@@ -98,12 +98,13 @@ def quantize(
     assert x.dtype in (torch.bfloat16, torch.float16)
     R, C = x.shape
     Ro, Co = (C, R) if transpose else (R, C)
-    Rp, Cp = -(-Ro // 128) * 128, -(-Co // 64) * 64
-    tiled = dtype == "nvfp4"
+    bw = 32 if dtype == "mxfp4" else 16                      # block width
+    Rp, Cp = -(-Ro // 128) * 128, -(-Co // (4 * bw)) * (4 * bw)
+    tiled = dtype != "if4"
     values = torch.empty(Rp, Cp // 2, dtype=torch.uint8)
-    sf = torch.empty(Rp * Cp // 16, dtype=torch.uint8)
+    sf = torch.empty(Rp * Cp // bw, dtype=torch.uint8)
     amax_out = torch.empty(1, dtype=torch.float32)
-    choice = torch.empty(Rp, Cp // 16, dtype=torch.uint8)
+    choice = torch.empty(Rp, Cp // bw, dtype=torch.uint8)
     worst = ctypes.c_float(0.0)
     amax_in = None if amax is None else amax.detach().to(torch.float32).reshape(1).contiguous()
     rc = lib().fos_oracle_quantize(

@@ -220,3 +220,52 @@ def test_if4_llama_mlp_shapes(name, tokens, k, n):
     qx, qw = fos.quantize(x, cfg), fos.quantize(w, cfg)
     out = B200MatmulBackend.quantized_matmul(qx, qw, out_dtype=fos.DataType.bfloat16, check_status=True)
     _check(out, _dense_reference(qx, qw), name, mismatch_scale=(k / 1024) ** 0.5)
+
+
+@pytest.mark.parametrize(("m", "n", "k"), [(256, 256, 256), (512, 1024, 1024), (128, 128, 128), (100, 72, 80),
+                                           (130, 300, 384), (384, 640, 448), (1024, 2048, 4096)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_mxfp4_matmul_against_oracle(oracle, m, n, k, out_dtype):
+    """MXFP4 x MXFP4 (kind::mxf4, E8M0 scales per 32 values, alpha = 1) against the oracle's matmul of
+    the same packed operands and against the fp32 product of the dequantized operands. K values that
+    are odd multiples of 128 exercise a last stage with a single scale tile."""
+    g = torch.Generator().manual_seed(m + 3 * n + 7 * k)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    b = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    cfg = fos.QuantizationConfig(dtype="mxfp4", scale_rule="static_6")
+    qa, qb = fos.quantize(a.to(DEV), cfg), fos.quantize(b.to(DEV), cfg)
+    ref32 = _dense_reference(qa, qb)
+    for block_n in (128, 256):
+        _native.lib().fos_set_option(1, block_n)
+        try:
+            out = B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType(out_dtype), check_status=True)
+        finally:
+            _native.lib().fos_set_option(1, 0)
+        what = f"mxfp4 {m}x{n}x{k} {out_dtype} block_n={block_n}"
+        if out_dtype == "float32":
+            assert ((out - ref32).abs().max() / ref32.abs().max()).item() < 1e-5, what
+        else:
+            _check(out, ref32, what, mismatch_scale=max(1.0, (k / 1024) ** 0.5))
+    if m * n * k <= 512 * 1024 * 1024 and out_dtype == "bfloat16":
+        oa = oracle.quantize(a, dtype="mxfp4", scale_rule="static_6")
+        ob = oracle.quantize(b, dtype="mxfp4", scale_rule="static_6")
+        want = oracle.matmul(oa, ob, torch.bfloat16)
+        assert (out.cpu() != want).float().mean().item() <= MISMATCH_TOLERANCE
+
+
+def test_mxfp4_golden_matmul_cases():
+    import io
+    import lzma
+    from pathlib import Path
+
+    raw = lzma.decompress((Path(__file__).parent / "golden" / "reference_golden_mxfp4.pt.xz").read_bytes())
+    gold = torch.load(io.BytesIO(raw), weights_only=False)
+    cfg = fos.QuantizationConfig(dtype="mxfp4", scale_rule="static_6")
+    for mm in gold["matmuls"]:
+        qa, qb = fos.quantize(gold["inputs"][mm["a"]].to(DEV), cfg), fos.quantize(gold["inputs"][mm["b"]].to(DEV), cfg)
+        out = fos.quantized_matmul(qa, qb, out_dtype=mm["out_dtype"]).cpu()
+        ref = mm["out"]
+        rel = ((out.float() - ref.float()).abs().max() / ref.float().abs().max().clamp_min(1e-30)).item()
+        assert rel <= REL_TOLERANCE, (mm["a"], mm["b"], rel)
+        if out.dtype == torch.bfloat16:
+            assert (out != ref).float().mean().item() <= MISMATCH_TOLERANCE

@@ -112,3 +112,44 @@ def test_oracle_reproduces_the_reference_with_the_hadamard_transform(oracle):
         n = case["scale_factors"].numel()
         assert torch.equal(got.scale_factors[:n], case["scale_factors"]), (case["input"], case["config"])
         assert torch.equal(got.amax.reshape(1), case["amax"]), (case["input"], case["config"])
+
+
+def _load_golden(name: str):
+    import io
+    import lzma
+    from pathlib import Path
+
+    raw = lzma.decompress((Path(__file__).parent / "golden" / name).read_bytes())
+    return torch.load(io.BytesIO(raw), weights_only=False)
+
+
+def test_oracle_reproduces_the_reference_for_mxfp4(oracle):
+    """MXFP4 (E8M0 scale per 32 values, static rules): codes, scales, the dequantized tensors in three
+    output types (bit for bit) and the PyTorch matmul of the reference."""
+    gold = _load_golden("reference_golden_mxfp4.pt.xz")
+    assert len(gold["cases"]) >= 31
+    for case in gold["cases"]:
+        x = gold["inputs"][case["input"]]
+        tag = (case["input"], case["config"])
+        got = oracle.quantize(x, dtype="mxfp4", **case["config"])
+        assert got.padded_shape == case["padded_shape"] and got.original_shape == case["original_shape"], tag
+        assert torch.equal(got.values, case["values"]), tag
+        assert torch.equal(got.scale_factors, case["scale_factors"]), tag
+        assert torch.equal(got.amax, case["amax"]), tag
+        assert got.worst_scaled <= 6.0, tag
+        for name, ref in case["dequantized"].items():
+            dt = getattr(torch, name)
+            out = oracle.dequantize(got, dt)
+            view = torch.int32 if dt == torch.float32 else torch.int16
+            assert torch.equal(out.view(view), ref.contiguous().view(view)), (tag, name)
+    cfg = dict(dtype="mxfp4", scale_rule="static_6")
+    for mm in gold["matmuls"]:
+        qa, qb = oracle.quantize(gold["inputs"][mm["a"]], **cfg), oracle.quantize(gold["inputs"][mm["b"]], **cfg)
+        assert oracle.alpha(qa, qb) == 1.0
+        dt = getattr(torch, mm["out_dtype"])
+        out = oracle.matmul(qa, qb, dt)
+        if dt == torch.float32:
+            denom = mm["out"].abs().max().clamp_min(1e-30)
+            assert ((out - mm["out"]).abs().max() / denom).item() < 1e-5
+        else:
+            assert (out != mm["out"]).float().mean().item() <= 1e-3

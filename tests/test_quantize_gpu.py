@@ -311,3 +311,64 @@ def test_stochastic_rounding_statistics():
     qa = B200QuantizeBackend.quantize(xd, cfg, seed=5)
     qb = B200QuantizeBackend.quantize(xd, cfg, seed=5)
     assert torch.equal(qa.values, qb.values) and qa.padded_shape == (1024, 1024)
+
+
+def _load_golden_file(name: str):
+    import io
+    import lzma
+    from pathlib import Path
+
+    raw = lzma.decompress((Path(__file__).parent / "golden" / name).read_bytes())
+    return torch.load(io.BytesIO(raw), weights_only=False)
+
+
+def test_mxfp4_matches_reference_and_oracle(oracle):
+    """MXFP4 (E8M0 scale per 32 values; static_6 / static_4; 1-D and 32 x 32 blocks; transposed):
+    the reference's own outputs (golden file: codes, scales, dequantized bits in three types), then
+    the oracle on larger, ragged, strided and fp16 inputs."""
+    gold = _load_golden_file("reference_golden_mxfp4.pt.xz")
+    for case in gold["cases"]:
+        tag = (case["input"], case["config"])
+        x = gold["inputs"][case["input"]].to(DEV)
+        q = fos.quantize(x, fos.QuantizationConfig(dtype="mxfp4", **case["config"]))
+        assert q.padded_shape == case["padded_shape"] and q.original_shape == case["original_shape"], tag
+        assert q.scale_factors.dtype == torch.float8_e8m0fnu and q.scale_factors_are_in_blackwell_layout
+        _assert_same(q, case["values"], case["scale_factors"], case["amax"], tag)
+        for name, ref in case["dequantized"].items():
+            dt = getattr(torch, name)
+            out = fos.dequantize(q, dt).cpu()
+            view = torch.int32 if dt == torch.float32 else torch.int16
+            assert torch.equal(out.view(view), ref.contiguous().view(view)), (tag, name)
+    g = torch.Generator().manual_seed(77)
+    big = torch.randn(1024, 2048, generator=g)
+    big[:, torch.randperm(2048, generator=g)[:20]] *= 20.0
+    inputs = {
+        "outliers_1024x2048": big.bfloat16(),
+        "weights_384x640": (torch.randn(384, 640, generator=g) * 0.02).bfloat16(),
+        "ragged_333x217": torch.randn(333, 217, generator=g).bfloat16(),
+        "half_200x96": torch.randn(200, 96, generator=g).half(),
+        "odd_129x33": (torch.randn(129, 33, generator=g) * 1e-3).bfloat16(),
+    }
+    for name, x in inputs.items():
+        for kw in (dict(scale_rule="static_6"), dict(scale_rule="static_4"), dict(scale_rule="static_6", transpose=True),
+                   dict(scale_rule="static_6", block_scale_2d=True), dict(scale_rule="static_4", block_scale_2d=True, transpose=True)):
+            ref = oracle.quantize(x, dtype="mxfp4", **kw)
+            q = fos.quantize(x.to(DEV), fos.QuantizationConfig(dtype="mxfp4", **kw))
+            assert q.padded_shape == ref.padded_shape and q.original_shape == ref.original_shape
+            _assert_same(q, ref.values, ref.scale_factors, ref.amax, (name, kw))
+            out = fos.dequantize(q, torch.bfloat16).cpu()
+            assert torch.equal(out.view(torch.int16), oracle.dequantize(ref, torch.bfloat16).view(torch.int16)), (name, kw)
+    # a view with a row stride (every other row of a wider tensor; 16-byte alignment lost)
+    wide = torch.randn(256, 300, generator=g).bfloat16()
+    view = wide.to(DEV)[::2, 3:259]
+    ref = oracle.quantize(wide[::2, 3:259].contiguous(), dtype="mxfp4", scale_rule="static_6")
+    q = fos.quantize(view, fos.QuantizationConfig(dtype="mxfp4", scale_rule="static_6"))
+    _assert_same(q, ref.values, ref.scale_factors, ref.amax, "strided view")
+    # what the format does not define is refused
+    with pytest.raises(ValueError):
+        fos.quantize(view, fos.QuantizationConfig(dtype="mxfp4", scale_rule="mse"))
+    # fake quantization = quantize then dequantize
+    x = inputs["weights_384x640"].to(DEV)
+    cfg = fos.QuantizationConfig(dtype="mxfp4", scale_rule="static_6")
+    fake = fos.quantize(x, fos.QuantizationConfig(dtype="mxfp4", scale_rule="static_6", pseudo_quantize=True))
+    assert torch.equal(fake.view(torch.int16), fos.dequantize(fos.quantize(x, cfg), torch.bfloat16).view(torch.int16))
