@@ -18,20 +18,22 @@
 //               rows < m and columns < n. 16-bit outputs are packed while they are read, so the
 //               warp's whole row segment sits in registers and the accumulator is handed back
 //               to the MMA warp before the first store; stores are 32 bytes per lane.
-//   warps 10..13 scale movers: copy each stage's scale tiles shared -> registers -> tensor
-//               memory (tcgen05.st) into a ring of scale columns, one slot per scale stage. A
-//               512-byte scale tile is 32 rows of 16 bytes and every 32-lane quadrant of tensor
-//               memory needs the same 16 bytes per lane, so each of the four warps reads row
-//               `lane` and writes its own quadrant. (Measured slower: tcgen05.cp from the MMA
-//               thread, even into a ring and a stage ahead, about 30 ns per 512-byte copy in line
-//               with the MMAs; the scales straight from global memory in one or two sets of
-//               mover warps, which then need a microsecond per stage; operand loads split over two
-//               issuing threads changed nothing.)
-//   warp 14     spare
+//   warp 10     one lane copies each stage's scale tiles shared -> tensor memory with
+//               tcgen05.cp 32x128b.warpx4 (a 512-byte tile is 32 rows of 16 bytes, which every
+//               32-lane quadrant of tensor memory needs: the copy broadcasts it) into a ring of
+//               scale columns, one slot per scale stage, and tcgen05.commit's the slot's `ready`
+//               barrier. Issued from THIS thread the copies overlap the MMAs; issued from the MMA
+//               thread they ran in line with them (about 30 ns each) and cost a third of the run
+//               time. The alternative kept behind FOS_GEMM_SF_CP=0: four mover warps, ld.shared +
+//               tcgen05.st per quadrant, which reads every tile four times from shared memory.
+//               (Also measured slower: scales straight from global memory in mover warps; operand
+//               loads split over two issuing threads changed nothing; a second copying thread
+//               changed nothing.)
+//   warps 11..14 spare (the mover warps of FOS_GEMM_SF_CP=0 are 10..13)
 //
 // What bounds the kernel: shared-memory bandwidth. Per K-block of 64 values the TMA unit writes
-// 13.5 KB (A 4, B 8, scales 1.5), the MMA reads 12 KB and the movers read the scales four times
-// (6 KB): 31.5 KB at 128 bytes per cycle are 246 cycles, against about 190 for the MMA itself.
+// 13.5 KB (A 4, B 8, scales 1.5), the MMA reads 12 KB and the scale copy 1.5 KB (the movers: four
+// times that): 27 KB (31.5) at 128 bytes per cycle are 211 (246) cycles, against about 150 for the MMA itself.
 // The measured times with parts switched off follow that sum to a few percent, and the kernel
 // runs at nine tenths of it. (A CTA pair moves a third less per MMA: see the pair kernel.)
 // Shorter stages do not help: the single threads that issue copies and MMAs need a few hundred
@@ -58,6 +60,13 @@ constexpr int SF_LEAD = FOS_GEMM_SF_LEAD;   // 0 or 1: how many stages the scale
 #ifndef FOS_GEMM_ST256
 #define FOS_GEMM_ST256 1
 #endif
+#ifndef FOS_GEMM_SF_CP
+#define FOS_GEMM_SF_CP 1
+#endif
+// 1: the scales reach tensor memory by tcgen05.cp issued from ONE thread of warp 10 (not the MMA
+// thread) instead of the four mover warps: shared memory is read once per tile instead of four times.
+constexpr bool SF_BY_CP = FOS_GEMM_SF_CP != 0;
+constexpr int SF_CP_THREADS = FOS_GEMM_SF_CP == 2 ? 2 : 1;     // issuing threads, taking stages in turn
 constexpr int NUM_THREADS = 512;                   // warps: 0 TMA (operands), 1 MMA, 2-9 epilogue, 10-13 scale movers, 14 spare, 15 TMA (scales)
 constexpr int SF_COL0 = 256;                       // tensor-memory columns: accumulators first, then per
                                                    // stage 16 columns of A scales and N/8 of B scales
@@ -121,6 +130,12 @@ __device__ __forceinline__ void tc_mma_mxf4(uint32_t d_tmem, uint64_t a_desc, ui
         : "memory");
 }
 
+// One 512-byte scale tile (32 rows of 16 bytes) from shared memory into 4 columns of all four
+// 32-lane quadrants of tensor memory.
+__device__ __forceinline__ void tc_copy_sf(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
 __device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                  uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
     asm volatile(
@@ -176,7 +191,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
         for (int j = 0; j < C::SF_SLOTS; ++j) {
             mbar_init(sf_full_bar + 8 * j, 1);
-            mbar_init(sf_ready_bar + 8 * j, 4);    // one arrival per scale-mover warp
+            mbar_init(sf_ready_bar + 8 * j, SF_BY_CP ? 1 : 4);    // one arrival per scale-mover warp (or one commit)
         }
         for (int a = 0; a < C::ACC_STAGES; ++a) {
             mbar_init(acc_full_bar + 8 * a, 1);
@@ -402,7 +417,37 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
             }
         }
-    } else if (warp >= 10 && warp < 14 && !dbg_no_load && !dbg_no_sf) {
+    } else if (SF_BY_CP && warp >= 10 && warp < 10 + SF_CP_THREADS && lane == 0 && !dbg_no_load && !dbg_no_sf) {
+        // ------------------------------------------------------------------ scale copies by tcgen05.cp
+        uint32_t j = 0, jph = 0, turn = 0;
+        bool ok = true;
+        for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int64_t kt = 0; kt < k_tiles; ++kt) {
+                if (SF_CP_THREADS > 1 && (turn++ & 1u) != static_cast<uint32_t>(warp - 10)) {
+                    if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
+                    continue;
+                }
+                ok = mbar_wait(sf_full_bar + 8 * j, jph, abort_flag, p.status, 6);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t src = sf_base + j * C::SF_SLOT_BYTES, dst = tmem_base + SF_COL0 + j * C::SF_STAGE_COLS;
+                // tiles: 32 rows of 16 bytes, 8-row groups 128 bytes apart, no swizzle
+                // (MXFP4: a tile spans two K-blocks, so only the first half of the tiles is in use)
+                const int ntile = p.mx ? KB_PER_STAGE / 2 : KB_PER_STAGE;
+#pragma unroll
+                for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
+                    if (kb >= ntile) break;
+                    tc_copy_sf(dst + 4 * kb, smem_desc(src + kb * SF_TILE_BYTES, 0, 128, 0));
+#pragma unroll
+                    for (int g = 0; g < C::N_GROUPS; ++g)
+                        tc_copy_sf(dst + 16 + (BLOCK_N / 32) * kb + 4 * g,
+                                   smem_desc(src + SFA_BYTES + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES, 0, 128, 0));
+                }
+                tc_commit(sf_ready_bar + 8 * j);     // arrives when the copies above are done
+                if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
+            }
+        }
+    } else if (!SF_BY_CP && warp >= 10 && warp < 14 && !dbg_no_load && !dbg_no_sf) {
         // ------------------------------------------------------------------ scale movers
         const int quad = warp & 3;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);

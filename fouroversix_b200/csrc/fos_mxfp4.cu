@@ -12,7 +12,8 @@
 //
 // quantize_mx_kernel: a CTA of 256 threads takes 128 x 128 tiles of the OUTPUT (x transposed when
 // asked). A thread owns runs of 16 values; two neighbouring lanes make a block. Untransposed 1-D
-// blocks go global -> registers (32 bytes per lane, 256 contiguous bytes per quarter warp);
+// blocks go global -> registers (32 bytes per lane, 256 contiguous bytes per quarter warp, the four
+// loads of a thread in flight together, four CTAs per SM);
 // transposed input and 32 x 32 blocks go through a shared-memory copy of the tile.
 #include "fos_common.cuh"
 
@@ -30,9 +31,11 @@ struct MxParams {
     int64_t rows_p, cols_p;          // padded to multiples of 128
     uint8_t *codes;
     uint8_t *sf;
+    float *amax_out;                 // receives 1.0, the per-tensor scale the reference reports for this format
     float inv_maxq_is_quarter;       // 1 for static_4 (divide by 4), 0 for static_6
     int sf_tiled;
     int vec16;                       // x base and row stride are 16-byte aligned
+    int vec32;                       // ... and 32-byte aligned
 };
 
 // Scale byte of a block with maximum `bmax` and the factor 2^(127-e) that divides by the scale.
@@ -71,7 +74,7 @@ __device__ __forceinline__ float unpack16(const uint32_t (&w)[8], float (&v)[16]
 }
 
 template <typename T, bool TWO_D, bool TRANSPOSED>
-__global__ void __launch_bounds__(MX_THREADS)
+__global__ void __launch_bounds__(MX_THREADS, 4)
 quantize_mx_kernel(const MxParams p) {
     constexpr bool STAGED = TWO_D || TRANSPOSED;
     __shared__ __align__(16) T tile[STAGED ? MX_TILE * MX_PITCH : 1];
@@ -82,6 +85,7 @@ quantize_mx_kernel(const MxParams p) {
     const int64_t tiles_c = p.cols_p / MX_TILE, n_tiles = (p.rows_p / MX_TILE) * tiles_c;
     const int64_t n_cb = p.cols_p / 32;
     const bool quarter = p.inv_maxq_is_quarter != 0.0f;
+    if (blockIdx.x == 0 && tid == 0) *p.amax_out = 1.0f;
 
     for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
         const int64_t i0 = (t / tiles_c) * MX_TILE, j0 = (t % tiles_c) * MX_TILE;   // tile origin in Y
@@ -112,41 +116,43 @@ quantize_mx_kernel(const MxParams p) {
             __syncthreads();
         }
 
-        float vals[4][16];
-        float bmax[4];
+        // all loads of the tile's four runs first (raw 16-bit pairs: 32 registers), then one run at a time
+        uint32_t w[4][8];
 #pragma unroll
         for (int it = 0; it < 4; ++it) {
             const int item = it * MX_THREADS + tid;
             const int r = item >> 3, piece = item & 7;    // row of the tile, run of 16 columns
-            uint32_t w[8];
             if constexpr (STAGED) {
                 const uint32_t *src = reinterpret_cast<const uint32_t *>(tile + r * MX_PITCH + piece * 16);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) w[k] = src[k];
+                for (int k = 0; k < 8; ++k) w[it][k] = src[k];
             } else {
                 const int64_t i = i0 + r, j = j0 + piece * 16;
-                if (i < p.rows && j + 16 <= p.cols && p.vec16) {
+                if (i < p.rows && j + 16 <= p.cols && p.vec32) {
+                    ldg_nc_32(x + i * p.ld + j, w[it]);
+                } else if (i < p.rows && j + 16 <= p.cols && p.vec16) {
                     const uint4 lo = ldg_nc_16(x + i * p.ld + j), hi = ldg_nc_16(x + i * p.ld + j + 8);
-                    w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w;
-                    w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
+                    w[it][0] = lo.x; w[it][1] = lo.y; w[it][2] = lo.z; w[it][3] = lo.w;
+                    w[it][4] = hi.x; w[it][5] = hi.y; w[it][6] = hi.z; w[it][7] = hi.w;
                 } else {
                     const uint16_t *xs = reinterpret_cast<const uint16_t *>(x);
 #pragma unroll
                     for (int k = 0; k < 8; ++k) {
                         const uint32_t a = (i < p.rows && j + 2 * k < p.cols) ? xs[i * p.ld + j + 2 * k] : 0u;
                         const uint32_t b = (i < p.rows && j + 2 * k + 1 < p.cols) ? xs[i * p.ld + j + 2 * k + 1] : 0u;
-                        w[k] = a | (b << 16);
+                        w[it][k] = a | (b << 16);
                     }
                 }
             }
-            const float m = unpack16<T>(w, vals[it]);
-            // the neighbouring lane holds the other half of the 32-value block
-            bmax[it] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-            if constexpr (TWO_D) piece_max[r * 8 + piece] = m;
         }
 
         if constexpr (TWO_D) {
             // 32 x 32 blocks: sixteen per tile, each the maximum of 32 rows x 2 runs
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                float v[16];
+                piece_max[it * MX_THREADS + tid] = unpack16<T>(w[it], v);     // index = row * 8 + run
+            }
             __syncthreads();
             if (tid < 16) {
                 const int br = tid >> 2, bc = tid & 3;
@@ -156,11 +162,6 @@ quantize_mx_kernel(const MxParams p) {
                 block_max[tid] = m;
             }
             __syncthreads();
-#pragma unroll
-            for (int it = 0; it < 4; ++it) {
-                const int item = it * MX_THREADS + tid;
-                bmax[it] = block_max[((item >> 3) >> 5) * 4 + ((item & 7) >> 1)];
-            }
         }
 
 #pragma unroll
@@ -168,9 +169,14 @@ quantize_mx_kernel(const MxParams p) {
             const int item = it * MX_THREADS + tid;
             const int r = item >> 3, piece = item & 7;
             const int64_t i = i0 + r, j = j0 + piece * 16;
+            float v[16];
+            float bmax = unpack16<T>(w[it], v);
+            // the neighbouring lane holds the other half of the 32-value block
+            if constexpr (TWO_D) bmax = block_max[(r >> 5) * 4 + (piece >> 1)];
+            else bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
             float inv;
-            const uint32_t e = mx_scale(bmax[it], quarter, inv);
-            const uint2 c = mx_encode16(vals[it], inv);
+            const uint32_t e = mx_scale(bmax, quarter, inv);
+            const uint2 c = mx_encode16(v, inv);
             *reinterpret_cast<uint2 *>(p.codes + i * (p.cols_p / 2) + j / 2) = c;
             if ((piece & 1) == 0) p.sf[sf_offset(i, j >> 5, n_cb, p.sf_tiled != 0)] = static_cast<uint8_t>(e);
         }
@@ -234,7 +240,7 @@ dequantize_mx_kernel(const MxDequantParams p) {
 template <typename T>
 cudaError_t launch_mx(const MxParams &p, bool two_d, bool transposed, cudaStream_t stream) {
     const int64_t tiles = (p.rows_p / MX_TILE) * (p.cols_p / MX_TILE);
-    const int64_t cap = 148 * 6;
+    const int64_t cap = 148 * 4;
     const unsigned grid = static_cast<unsigned>(tiles < cap ? tiles : cap);
     if (two_d && transposed) quantize_mx_kernel<T, true, true><<<grid, MX_THREADS, 0, stream>>>(p);
     else if (two_d) quantize_mx_kernel<T, true, false><<<grid, MX_THREADS, 0, stream>>>(p);
@@ -242,8 +248,6 @@ cudaError_t launch_mx(const MxParams &p, bool two_d, bool transposed, cudaStream
     else quantize_mx_kernel<T, false, false><<<grid, MX_THREADS, 0, stream>>>(p);
     return cudaGetLastError();
 }
-
-__global__ void store_one_kernel(float *p) { *p = 1.0f; }
 
 }  // namespace
 
@@ -258,12 +262,11 @@ int quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64_t cols, int64
     p.out_cols = transpose ? rows : cols;
     p.rows_p = round_up64(p.out_rows, 128);
     p.cols_p = round_up64(p.out_cols, 128);
-    p.codes = codes; p.sf = sf;
+    p.codes = codes; p.sf = sf; p.amax_out = amax_out;
     p.inv_maxq_is_quarter = scale_rule == FOS_RULE_STATIC_4 ? 1.0f : 0.0f;
     p.sf_tiled = sf_layout == FOS_SF_TILED;
     p.vec16 = reinterpret_cast<uintptr_t>(x) % 16 == 0 && (ld * 2) % 16 == 0;
-    store_one_kernel<<<1, 1, 0, stream>>>(amax_out);
-    FOS_CUDA_TRY(cudaGetLastError());
+    p.vec32 = reinterpret_cast<uintptr_t>(x) % 32 == 0 && (ld * 2) % 32 == 0;
     FOS_CUDA_TRY(x_dtype == FOS_BF16 ? launch_mx<__nv_bfloat16>(p, block_2d != 0, transpose != 0, stream)
                                      : launch_mx<__half>(p, block_2d != 0, transpose != 0, stream));
     return FOS_OK;

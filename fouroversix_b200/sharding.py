@@ -58,7 +58,7 @@ def slice_rows(q: QuantizedTensor, lo: int, hi: int) -> QuantizedTensor:
     cols_p = q.padded_shape[1]
     per_row_scales = cols_p // q.dtype.block_size
     sf = q.scale_factors.reshape(-1)
-    # tiled: 128-row groups are contiguous runs of (cols_p/64) tiles of 512 bytes; row-major: rows are
+    # tiled: 128-row groups are contiguous runs of tiles of 512 bytes (four blocks wide); row-major: rows are
     sf = sf[lo * per_row_scales: hi * per_row_scales]
     rows = min(hi, q.original_shape[0]) - lo
     return QuantizedTensor(q.values[lo:hi], sf, q.amax, q.dtype, (rows, q.original_shape[1]), q.scale_rule,
@@ -67,16 +67,19 @@ def slice_rows(q: QuantizedTensor, lo: int, hi: int) -> QuantizedTensor:
 
 
 def slice_cols(q: QuantizedTensor, lo: int, hi: int) -> QuantizedTensor:
-    """Columns [lo, hi) of a quantized tensor (multiples of 64) without requantizing."""
+    """Columns [lo, hi) of a quantized tensor (multiples of four blocks: 64 values, 128 for MXFP4)
+    without requantizing."""
     rows_p, cols_p = q.padded_shape
-    if lo % 64 or hi % 64 or not 0 <= lo < hi <= cols_p:
-        raise ValueError("column slices must be multiples of 64 inside the padded shape")
+    block = q.dtype.block_size
+    unit = 4 * block                                      # columns covered by one 512-byte scale tile
+    if lo % unit or hi % unit or not 0 <= lo < hi <= cols_p:
+        raise ValueError(f"column slices must be multiples of {unit} inside the padded shape")
     values = q.values[:, lo // 2: hi // 2].contiguous()
     if q.scale_factors_are_in_blackwell_layout:
-        tiles = q.scale_factors.reshape(rows_p // 128, cols_p // 64, 512)
-        sf = tiles[:, lo // 64: hi // 64].contiguous().reshape(-1)
+        tiles = q.scale_factors.reshape(rows_p // 128, cols_p // unit, 512)
+        sf = tiles[:, lo // unit: hi // unit].contiguous().reshape(-1)
     else:
-        sf = q.scale_factors.reshape(rows_p, cols_p // 16)[:, lo // 16: hi // 16].contiguous().reshape(-1)
+        sf = q.scale_factors.reshape(rows_p, cols_p // block)[:, lo // block: hi // block].contiguous().reshape(-1)
     cols = min(hi, q.original_shape[1]) - lo
     return QuantizedTensor(values, sf, q.amax, q.dtype, (q.original_shape[0], cols), q.scale_rule, q.round_style,
                            (rows_p, hi - lo),

@@ -159,3 +159,22 @@ def test_unbiased_stochastic_rounding_is_refused_clearly():
     x = torch.randn(1, 128, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
     with pytest.raises(NotImplementedError, match="stochastic_unbiased"):
         layer(x).sum().backward()
+
+
+def test_mxfp4_linear_forward():
+    """The same layer with the reference's second format: dtype="mxfp4", static_6 (the only kind of
+    rule the format defines). Forward = q(x) @ q(W)^T with alpha = 1."""
+    g = torch.Generator().manual_seed(5)
+    lin = nn.Linear(512, 384, bias=True, device=DEV, dtype=torch.bfloat16)
+    x = torch.randn(2, 100, 512, generator=g).bfloat16().to(DEV)
+    cfg = fos.ModuleQuantizationConfig(dtype="mxfp4", scale_rule="static_6")
+    w = lin.weight.data.clone()
+    layer = fos.FourOverSixLinear(lin, cfg).quantize_weight_()
+    assert layer.quantized_weight_scale_factors.dtype == torch.float8_e8m0fnu
+    assert layer.quantized_weight_scale_factors.numel() == 384 * 512 // 32
+    out = layer(x)
+    qc = fos.QuantizationConfig(dtype="mxfp4", scale_rule="static_6")
+    xq = fos.dequantize(fos.quantize(x.reshape(-1, 512), qc), torch.float32)
+    wq = fos.dequantize(fos.quantize(w, qc), torch.float32)
+    want = (_fp32_matmul(xq, wq) + lin.bias.float()).reshape(2, 100, 384)
+    _close(out, want)

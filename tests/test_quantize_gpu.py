@@ -338,7 +338,10 @@ def test_mxfp4_matches_reference_and_oracle(oracle):
             dt = getattr(torch, name)
             out = fos.dequantize(q, dt).cpu()
             view = torch.int32 if dt == torch.float32 else torch.int16
-            assert torch.equal(out.view(view), ref.contiguous().view(view)), (tag, name)
+            # 0 x inf (a block scale beyond fp16's range) is NaN on both sides; its payload is the platform's
+            nan = torch.isnan(ref)
+            assert torch.equal(torch.isnan(out), nan), (tag, name)
+            assert torch.equal(out.view(view)[~nan], ref.contiguous().view(view)[~nan]), (tag, name)
     g = torch.Generator().manual_seed(77)
     big = torch.randn(1024, 2048, generator=g)
     big[:, torch.randperm(2048, generator=g)[:20]] *= 20.0
