@@ -6,7 +6,7 @@
 //
 //   warp 0      one lane issues the TMA loads of the A / B tiles (128-byte swizzle, no multicast)
 //               into a ring of shared-memory stages guarded by full / empty mbarriers
-//   warp 15     one lane issues the TMA loads of the scale tiles (two tensor copies per stage)
+//   warp 11     (15 with FOS_GEMM_SF_CP=0) one lane issues the TMA loads of the scale tiles (two tensor copies per stage)
 //               into a ring of its own, one slot longer than the operand ring and one stage
 //               ahead of it. A separate thread because a thread issues a copy every hundred
 //               cycles or so: with all copies of a stage on one thread, that thread set the pace.
@@ -29,7 +29,8 @@
 //               (Also measured slower: scales straight from global memory in mover warps; operand
 //               loads split over two issuing threads changed nothing; a second copying thread
 //               changed nothing.)
-//   warps 11..14 spare (the mover warps of FOS_GEMM_SF_CP=0 are 10..13)
+//   12 warps in all (16 with FOS_GEMM_SF_CP=0, whose mover warps are 10..13): with 384 threads the
+//               epilogue's 64 packed registers fit without spills
 //
 // What bounds the kernel: shared-memory bandwidth. Per K-block of 64 values the TMA unit writes
 // 13.5 KB (A 4, B 8, scales 1.5), the MMA reads 12 KB and the scale copy 1.5 KB (the movers: four
@@ -67,7 +68,7 @@ constexpr int SF_LEAD = FOS_GEMM_SF_LEAD;   // 0 or 1: how many stages the scale
 // thread) instead of the four mover warps: shared memory is read once per tile instead of four times.
 constexpr bool SF_BY_CP = FOS_GEMM_SF_CP != 0;
 constexpr int SF_CP_THREADS = FOS_GEMM_SF_CP == 2 ? 2 : 1;     // issuing threads, taking stages in turn
-constexpr int NUM_THREADS = 512;                   // warps: 0 TMA (operands), 1 MMA, 2-9 epilogue, 10-13 scale movers, 14 spare, 15 TMA (scales)
+constexpr int NUM_THREADS = SF_BY_CP ? 384 : 512;                   // warps: 0 TMA (operands), 1 MMA, 2-9 epilogue, 10-13 scale movers, 14 spare, 15 TMA (scales)
 constexpr int SF_COL0 = 256;                       // tensor-memory columns: accumulators first, then per
                                                    // stage 16 columns of A scales and N/8 of B scales
 
@@ -243,7 +244,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const unsigned long long t0 = global_timer_ns();
             while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
         }
-    } else if (warp == 15 && lane == 0 && !dbg_no_load && !dbg_no_sf) {
+    } else if (warp == (SF_BY_CP ? 11 : 15) && lane == 0 && !dbg_no_load && !dbg_no_sf) {
         // ------------------------------------------------------------------ TMA producer: scales
         // A thread of its own (one thread issues a copy every hundred cycles or so, and five copies
         // per stage from a single thread set the pace of the pipeline when measured), and SF_LEAD
@@ -518,9 +519,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 //   full[s]      leader's barrier: one arrive.expect_tx by the leader's producer for the bytes of
 //                BOTH CTAs; the peer's TMA loads complete on it too (cta_group::2 form of the copy)
 //   empty[s]     one per CTA, released in both CTAs by the leader's multicast tcgen05.commit
-//   sf_full[j]   one per CTA: this CTA's scale tiles have landed in its shared memory
-//   sf_ready[j]  leader's barrier, 8 arrivals: the four mover warps of each CTA have written
-//                the slot's scales into their own CTA's tensor memory
+//   sf_full[j]   leader's barrier: the scale tiles of both CTAs have landed (each in its own CTA's
+//                shared memory), announced and completed like full[s]
+//   sf_ready[j]  leader's barrier: the leader's copying thread has moved the slot's scales into
+//                the tensor memory of both CTAs (tcgen05.cp with cta_group::2, one commit)
 //   acc_full     one per CTA, multicast commit
 //   acc_empty    leader's barrier, 16 arrivals: 8 epilogue warps of each CTA
 //
@@ -545,6 +547,24 @@ static_assert(SF_COL0 + SF_SLOTS * SF_STAGE_COLS <= TMEM_COLS, "scale ring does 
 static_assert(SMEM_BYTES <= 232448, "more shared memory than a CTA can have");
 static_assert((2 * STAGES + 2 * SF_SLOTS + 2) * 8 + 8 <= BARRIER_BYTES, "barrier area too small");
 static_assert(SF_SLOTS <= STAGES, "the scale producer's wait assumes no more slots than stages");
+
+// 3-D form of the same (scale tiles).
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(cluster_bar) : "memory");
+}
+
+// One 512-byte scale tile from each CTA's own shared memory into 4 columns of all four lane quadrants
+// of its own tensor memory, in both CTAs of the pair at once.
+__device__ __forceinline__ void tc_copy_sf_pair(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+// Arrive (once, on a barrier of this CTA) when the tcgen05 operations this thread issued for the pair are done.
+__device__ __forceinline__ void tc_commit_pair_local(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
 
 // TMA tile load whose completion is signalled on a barrier of either CTA of the pair.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t cluster_bar) {
@@ -582,8 +602,8 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             mbar_init(empty_bar + 8 * s, 1);
         }
         for (int j = 0; j < SF_SLOTS; ++j) {
-            mbar_init(sf_full_bar + 8 * j, 1);
-            mbar_init(sf_ready_bar + 8 * j, 8);
+            mbar_init(sf_full_bar + 8 * j, 1);     // used in the leader only: the scale tiles of BOTH CTAs have landed
+            mbar_init(sf_ready_bar + 8 * j, 1);    // one commit after the copies into tensor memory
         }
         mbar_init(acc_full_bar, 1);
         mbar_init(acc_empty_bar, 16);
@@ -638,6 +658,9 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         }
     } else if (warp == 15 && lane == 0 && !dbg_no_load && !dbg_no_sf) {
         // ------------------------------------------------------------------ TMA producer: scales (both CTAs)
+        // Each CTA fetches the scales of its own 128 rows of A and of all 256 rows of B into its own
+        // shared memory; both complete on the LEADER's barrier, like the operand copies.
+        const uint32_t leader_sf_full = map_to_cta(sf_full_bar, 0);
         uint32_t j = 0;
         bool ok = true;
         int64_t i = 0;                                   // stage counter over all tiles of this pair
@@ -656,10 +679,10 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     if (!ok) break;
                 }
                 const int kb0 = static_cast<int>(kt * KB_PER_STAGE);
-                const uint32_t dst = sf_base + j * SF_SLOT_BYTES, bar = sf_full_bar + 8 * j;
-                mbar_expect_tx(bar, SF_SLOT_BYTES);
-                tma_load_3d(dst, &map_sfa, 0, kb0, a_group, bar);
-                tma_load_3d(dst + SFA_BYTES, &map_sfb, 0, kb0, b_group, bar);
+                const uint32_t dst = sf_base + j * SF_SLOT_BYTES, bar = leader_sf_full + 8 * j;
+                if (leader) mbar_expect_tx(sf_full_bar + 8 * j, 2 * SF_SLOT_BYTES);
+                tma_load_3d_pair(dst, &map_sfa, 0, kb0, a_group, bar);
+                tma_load_3d_pair(dst + SFA_BYTES, &map_sfb, 0, kb0, b_group, bar);
                 if (++j == SF_SLOTS) j = 0;
             }
         }
@@ -772,43 +795,28 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 }
             }
         }
-    } else if (warp >= 10 && warp < 14 && !dbg_no_load && !dbg_no_sf) {
-        // ------------------------------------------------------------------ scale movers (both CTAs)
-        const int quad = warp & 3;
-        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-        const uint32_t leader_sf_ready = map_to_cta(sf_ready_bar, 0);
+    } else if (warp == 10 && lane == 0 && leader && !dbg_no_load && !dbg_no_sf) {
+        // ------------------------------------------------------------------ scale copies (leader, for both CTAs)
+        // tcgen05.cp with cta_group::2 copies, in each CTA, from that CTA's shared memory into its
+        // tensor memory: one thread of the pair moves the scales of both, and no warp of the peer
+        // has to report back.
         uint32_t j = 0, jph = 0;
         bool ok = true;
         for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
             for (int64_t kt = 0; kt < k_tiles; ++kt) {
-                ok = mbar_wait(sf_full_bar + 8 * j, jph, abort_flag, p.status, 6);
-                ok = __all_sync(0xffffffffu, ok);
+                ok = mbar_wait_poll(sf_full_bar + 8 * j, jph, abort_flag, p.status, 6);
                 if (!ok) break;
-                const uint32_t sfa_smem = sf_base + j * SF_SLOT_BYTES + lane * 16, sfb_smem = sfa_smem + SFA_BYTES;
-                const uint32_t slot = lane_base + SF_COL0 + j * SF_STAGE_COLS;
-                uint32_t r[16];
-                // tiles beyond K were zero-filled by the TMA unit, so all four K-blocks can be copied
+                tc_fence_after();
+                const uint32_t src = sf_base + j * SF_SLOT_BYTES, dst = tmem_base + SF_COL0 + j * SF_STAGE_COLS;
 #pragma unroll
                 for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
-                    const uint4 v = lds_16(sfa_smem + kb * SF_TILE_BYTES);
-                    r[4 * kb] = v.x; r[4 * kb + 1] = v.y; r[4 * kb + 2] = v.z; r[4 * kb + 3] = v.w;
-                }
-                tc_store_16cols(slot, r);
+                    tc_copy_sf_pair(dst + 4 * kb, smem_desc(src + kb * SF_TILE_BYTES, 0, 128, 0));
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int col = hf * 16 + q * 4;       // column inside the B part: 8 per K-block
-                        const int kb = col / 8, g = (col % 8) / 4;
-                        const uint4 v = lds_16(sfb_smem + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES);
-                        r[4 * q] = v.x; r[4 * q + 1] = v.y; r[4 * q + 2] = v.z; r[4 * q + 3] = v.w;
-                    }
-                    tc_store_16cols(slot + 16 + hf * 16, r);
+                    for (int g = 0; g < 2; ++g)
+                        tc_copy_sf_pair(dst + 16 + 8 * kb + 4 * g,
+                                        smem_desc(src + SFA_BYTES + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES, 0, 128, 0));
                 }
-                tc_wait_store();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(leader_sf_ready + 8 * j);
+                tc_commit_pair_local(sf_ready_bar + 8 * j);
                 if (++j == SF_SLOTS) { j = 0; jph ^= 1u; }
             }
         }

@@ -176,5 +176,5 @@ def test_mxfp4_linear_forward():
     qc = fos.QuantizationConfig(dtype="mxfp4", scale_rule="static_6")
     xq = fos.dequantize(fos.quantize(x.reshape(-1, 512), qc), torch.float32)
     wq = fos.dequantize(fos.quantize(w, qc), torch.float32)
-    want = (_fp32_matmul(xq, wq) + lin.bias.float()).reshape(2, 100, 384)
+    want = (_fp32_matmul(xq, wq.T) + layer.bias.float()).reshape(2, 100, 384)
     _close(out, want)
