@@ -20,6 +20,7 @@ FOS_NVFP4, FOS_IF4, FOS_MXFP4 = 0, 1, 2
 FOS_SF_ROWMAJOR, FOS_SF_TILED = 0, 1
 FOS_QUANTIZE_EXACT_ONLY = 1
 FOS_QUANTIZE_RHT = 2
+FOS_OPT_GEMM_MAX_CTAS = 4
 
 _c_i64, _c_int, _c_ptr = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
 

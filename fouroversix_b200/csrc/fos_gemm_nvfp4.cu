@@ -912,6 +912,7 @@ int launch_out(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &
 
 int g_gemm_variant = 0;   // FOS_OPT_GEMM_VARIANT
 int g_gemm_debug = 0;     // FOS_OPT_GEMM_DEBUG
+int g_gemm_max_ctas = 0;  // FOS_OPT_GEMM_MAX_CTAS
 
 }  // namespace
 }  // namespace fos
@@ -923,6 +924,10 @@ extern "C" int fos_set_option(int key, int value) {
     }
     if (key == FOS_OPT_GEMM_DEBUG && value >= 0 && value < 32 && !(value & 8)) {
         fos::g_gemm_debug = value;
+        return FOS_OK;
+    }
+    if (key == FOS_OPT_GEMM_MAX_CTAS && value >= 0) {
+        fos::g_gemm_max_ctas = value;
         return FOS_OK;
     }
     if (key == FOS_OPT_QUANTIZE_VARIANT && (value == 0 || value == 1)) {
@@ -952,6 +957,7 @@ static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uin
     int dev = 0, sms = 0;
     FOS_CUDA_TRY(cudaGetDevice(&dev));
     FOS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (g_gemm_max_ctas > 0 && g_gemm_max_ctas < sms) sms = g_gemm_max_ctas;   // leave SMs to concurrent kernels
 
     GemmParams p{a_sf, b_sf, alpha, d, status, m_p, n_p, k_p, m, n, ldd, out_dtype, g_gemm_debug, mx};
     const int64_t sf_k_tiles = mx ? k_p / 128 : k_p / 64;     // 512-byte scale tiles along K

@@ -95,22 +95,41 @@ quantize_mx_kernel(const MxParams p) {
             __syncthreads();                               // the previous tile's readers are done
             // x rows a0.., x columns b0..: for Y = x^T the tile of Y is x[j0.., i0..]^T
             const int64_t a0 = TRANSPOSED ? j0 : i0, b0 = TRANSPOSED ? i0 : j0;
-#pragma unroll 1
-            for (int c = tid; c < MX_TILE * (MX_TILE / 8); c += MX_THREADS) {
-                const int ar = c >> 4, bc = (c & 15) * 8;  // row of x within the tile, first of 8 columns
+            // A warp takes 8 rows of x by 4 chunks of 8 columns at a time: lanes 0-7 the rows, lane / 8
+            // the chunk. Global: 64 contiguous bytes per row. Shared, transposed: the 8 lanes of a chunk
+            // write 8 neighbouring columns of one tile row and the four chunks land 8 tile rows (8 x 65
+            // words) apart, on four different bank groups: no conflicts.
+            const int lane = tid & 31, wrp = tid >> 5;
+            uint4 raw[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int task = q * (MX_THREADS / 32) + wrp;
+                const int ar = (task >> 2) * 8 + (lane & 7), bc = ((task & 3) * 4 + (lane >> 3)) * 8;
                 const int64_t a = a0 + ar, b = b0 + bc;
-                T e[8];
                 if (a < p.rows && b + 8 <= p.cols && p.vec16) {
-                    *reinterpret_cast<uint4 *>(e) = ldg_nc_16(x + a * p.ld + b);
+                    raw[q] = ldg_nc_16(x + a * p.ld + b);
                 } else {
+                    const uint16_t *xs = reinterpret_cast<const uint16_t *>(x);
+                    uint32_t h[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) h[k] = (a < p.rows && b + k < p.cols) ? xs[a * p.ld + b + k] : 0u;
+                    raw[q] = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+                }
+            }
+            uint16_t *tile16 = reinterpret_cast<uint16_t *>(tile);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int task = q * (MX_THREADS / 32) + wrp;
+                const int ar = (task >> 2) * 8 + (lane & 7), bc = ((task & 3) * 4 + (lane >> 3)) * 8;
+                const uint32_t wv[4] = {raw[q].x, raw[q].y, raw[q].z, raw[q].w};
+                if constexpr (TRANSPOSED) {
 #pragma unroll
                     for (int k = 0; k < 8; ++k)
-                        e[k] = (a < p.rows && b + k < p.cols) ? x[a * p.ld + b + k] : T(0.0f);
-                }
+                        tile16[(bc + k) * MX_PITCH + ar] = static_cast<uint16_t>(wv[k >> 1] >> ((k & 1) * 16));
+                } else {
+                    uint32_t *dst = reinterpret_cast<uint32_t *>(tile16 + ar * MX_PITCH + bc);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    if constexpr (TRANSPOSED) tile[(bc + k) * MX_PITCH + ar] = e[k];
-                    else tile[ar * MX_PITCH + bc + k] = e[k];
+                    for (int k = 0; k < 4; ++k) dst[k] = wv[k];
                 }
             }
             __syncthreads();

@@ -83,11 +83,12 @@ def main() -> None:
               f"({'graph replays' if args.graph else 'eager launches'}), {gbs:.0f} GB/s algorithmic")
         return
 
-    dtype = "if4" if args.case == "gemm-if4" else "nvfp4"
+    dtype = "if4" if args.case == "gemm-if4" else args.dtype
+    rule = "static_6" if dtype == "mxfp4" else "mse"
     a = torch.randn(args.m, args.k, generator=g, device=dev).bfloat16()
     b = torch.randn(args.n, args.k, generator=g, device=dev).bfloat16()
-    qa = fos.quantize(a, fos.QuantizationConfig(dtype=dtype))
-    qb = fos.quantize(b, fos.QuantizationConfig(dtype=dtype))
+    qa = fos.quantize(a, fos.QuantizationConfig(dtype=dtype, scale_rule=rule))
+    qb = fos.quantize(b, fos.QuantizationConfig(dtype=dtype, scale_rule=rule))
     out = torch.empty(args.m, args.n, dtype=torch.bfloat16, device=dev)
     _native.lib().fos_set_option(1, args.variant)
     _native.check(_native.lib().fos_set_option(2, args.debug), "fos_set_option")

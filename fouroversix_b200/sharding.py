@@ -34,6 +34,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from fouroversix_b200 import _native
 from fouroversix_b200.matmul import quantized_matmul
 from fouroversix_b200.quantize import QuantizationConfig, QuantizedTensor, quantize
 from fouroversix_b200.utils import DataType
@@ -95,16 +96,21 @@ class TensorParallelLinear(nn.Module):
     `weight` is this rank's shard, either high precision (quantized here with the
     shard's own amax, like the reference under vLLM) or already a `QuantizedTensor`.
     `matmul_fn(x, w, input_config=..., out_dtype=...)` defaults to the FP4 GEMM; tests of
-    the host logic substitute a CPU stand-in.
+    the host logic substitute a CPU stand-in. `chunks` and `comm_sms` shape the overlap of a
+    row-parallel layer: the tokens are cut into `chunks` pieces, and while pieces are in flight the
+    GEMM leaves `comm_sms` SMs idle, because a persistent grid on every SM would keep the
+    collective's kernel waiting until the GEMM has finished (the option is process-wide:
+    one row-parallel layer at a time per process).
     """
 
     def __init__(self, weight: torch.Tensor | QuantizedTensor, config: ModuleQuantizationConfig, mode: str, *,
                  group: dist.ProcessGroup | None = None, bias: torch.Tensor | None = None, chunks: int = 4,
-                 matmul_fn: MatmulFn | None = None, quantize_fn: Callable | None = None) -> None:
+                 comm_sms: int = 20, matmul_fn: MatmulFn | None = None, quantize_fn: Callable | None = None) -> None:
         super().__init__()
         if mode not in ("column", "row"):
             raise ValueError("mode must be 'column' or 'row'")
         self.mode, self.config, self.group, self.chunks = mode, config, group, max(1, chunks)
+        self.comm_sms = max(0, comm_sms)
         self._matmul = matmul_fn or quantized_matmul
         self._quantize = quantize_fn or quantize
         self.weight = weight if isinstance(weight, QuantizedTensor) else self._quantize(weight, config.get_weight_config())
@@ -154,9 +160,18 @@ class TensorParallelLinear(nn.Module):
             if self._comm_stream is None:
                 self._comm_stream = torch.cuda.Stream(device=x2d.device)
             compute = torch.cuda.current_stream(x2d.device)
+        limit_sms = on_gpu and self.comm_sms > 0 and self._matmul is quantized_matmul
+        if limit_sms:
+            sms = torch.cuda.get_device_properties(x2d.device).multi_processor_count
+            _native.lib().fos_set_option(_native.FOS_OPT_GEMM_MAX_CTAS, max(1, sms - self.comm_sms))
         for i in range(n_chunks):
             part = out[i * step: (i + 1) * step]
-            self._gemm(slice_rows(xq, i * step, (i + 1) * step), act_cfg, out=part)
+            try:
+                self._gemm(slice_rows(xq, i * step, (i + 1) * step), act_cfg, out=part)
+            except BaseException:
+                if limit_sms:
+                    _native.lib().fos_set_option(_native.FOS_OPT_GEMM_MAX_CTAS, 0)
+                raise
             if on_gpu:
                 done = torch.cuda.Event()
                 done.record(compute)
@@ -165,6 +180,8 @@ class TensorParallelLinear(nn.Module):
                     dist.all_reduce(part, group=self.group)
             else:
                 works.append(dist.all_reduce(part, group=self.group, async_op=True))
+        if limit_sms:
+            _native.lib().fos_set_option(_native.FOS_OPT_GEMM_MAX_CTAS, 0)
         if on_gpu:
             compute.wait_stream(self._comm_stream)
         for w in works:

@@ -236,6 +236,9 @@ int fos_pseudo_quantize(const void *x, int x_dtype, int64_t rows, int64_t cols, 
  *   FOS_OPT_GEMM_DEBUG     timing experiments that make the GEMM's RESULT WRONG: bit 0 skips the
  *                          scale copies, bit 1 the operand loads, bit 2 the output stores.
  *                          Default 0. Only the profiling scripts set it.
+ *   FOS_OPT_GEMM_MAX_CTAS  0 = one persistent CTA per SM (default); n > 0 = at most n CTAs, which leaves
+ *                          SMs free for kernels that must run beside the GEMM (a collective on another
+ *                          stream: a persistent grid over every SM would keep it waiting)
  *   FOS_OPT_QUANTIZE_VARIANT  0 = 1-D, untransposed inputs that are 16-byte aligned (base and row
  *                          stride) go through the kernel fed by the TMA unit, the rest through
  *                          the kernel that loads from registers (default); 1 = never the
@@ -244,6 +247,7 @@ int fos_pseudo_quantize(const void *x, int x_dtype, int64_t rows, int64_t cols, 
 #define FOS_OPT_GEMM_VARIANT 1
 #define FOS_OPT_GEMM_DEBUG 2
 #define FOS_OPT_QUANTIZE_VARIANT 3
+#define FOS_OPT_GEMM_MAX_CTAS 4
 int fos_set_option(int key, int value);
 
 /*
