@@ -980,9 +980,11 @@ static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uin
         return launch_pair<float>(map_a, map_b, map_sfa, map_sfb, p, stream);
     }
 
-    // single-CTA kernel: 128 x 256 tiles unless that would leave SMs without a tile
+    // single-CTA kernel: 128 x 256 tiles unless they would fill less than half of the SMs (a 128 x 128
+    // tile takes nine tenths of the time of a 128 x 256 one, so the narrow kernel only pays when it
+    // doubles the number of busy SMs)
     const int64_t tiles_256 = (m_p / BLOCK_M) * ((n_p + 255) / 256);
-    bool wide = n_p >= 256 && tiles_256 >= sms;
+    bool wide = n_p >= 256 && tiles_256 * 2 > sms;
     if (g_gemm_variant == 128) wide = false;
     if (g_gemm_variant == 256) wide = true;
     if ((st = make_operand_map(&map_a, a_codes, m_p, k_p / 2, BLOCK_M)) != FOS_OK) return st;

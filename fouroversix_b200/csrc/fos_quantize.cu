@@ -79,32 +79,58 @@ __global__ void zero_amax_kernel(float *amax) {
     if (threadIdx.x == 0) *amax = 0.0f;
 }
 
-// max |x| with 16-byte loads, four of them in flight per thread, then one atomicMax per CTA.
+// max |x| of the chunks (VB bytes each) that one thread owns: 128 bytes per thread in flight per
+// round, every load of a round predicated (a chunk past the end contributes 0), so that there is
+// no serial tail of single loads, each of which would cost a full memory latency.
+template <typename T, int VB>
+__device__ __forceinline__ float amax_chunks(const T *__restrict__ x, int64_t rows, int64_t cols, int64_t ld,
+                                             int64_t tid, int64_t stride) {
+    constexpr int EL = VB / 2, N = 128 / VB;
+    const int64_t chunks_per_row = cols / EL, total = rows * chunks_per_row;
+    const bool flat = ld == cols;
+    float m = 0.0f;
+    for (int64_t i = tid; i < total; i += N * stride) {
+        uint32_t w[N][VB / 4];
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            const int64_t idx = i + k * stride;
+#pragma unroll
+            for (int j = 0; j < VB / 4; ++j) w[k][j] = 0u;
+            if (idx < total) {
+                const int64_t r = flat ? 0 : idx / chunks_per_row;
+                const T *ptr = flat ? x + idx * EL : x + r * ld + (idx - r * chunks_per_row) * EL;
+                if constexpr (VB == 32) {
+                    ldg_nc_32(ptr, w[k]);
+                } else {
+                    const uint4 v = ldg_nc_16(ptr);
+                    w[k][0] = v.x; w[k][1] = v.y; w[k][2] = v.z; w[k][3] = v.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < N; ++k)
+#pragma unroll
+            for (int j = 0; j < VB / 16; ++j)
+                m = fmaxf(m, abs_max8<T>(make_uint4(w[k][4 * j], w[k][4 * j + 1], w[k][4 * j + 2], w[k][4 * j + 3])));
+    }
+    return m;
+}
+
+// max |x| with 32-byte (or 16-byte) loads, 128 bytes in flight per thread, then one atomicMax per CTA.
 // Launched behind zero_amax_kernel as its programmatic dependent: CTAs of this kernel exist only
 // after that kernel has seen its predecessor complete, so x is final; the wait below makes
-// the zero visible before the atomics.
+// the zero visible before the atomics. `vec` = 32 / 16: x's base and row stride are aligned to that
+// many bytes and a row holds a whole number of such chunks; 0: element loads.
 template <typename T>
 __global__ void __launch_bounds__(256) amax_kernel(const T *__restrict__ x, int64_t rows, int64_t cols,
-                                                   int64_t ld, int vec16, float *amax) {
+                                                   int64_t ld, int vec, float *amax) {
     float m = 0.0f;
     const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    if (vec16) {
-        const int64_t chunks_per_row = cols >> 3;
-        const int64_t total = rows * chunks_per_row;
-        const bool flat = ld == cols;
-        auto chunk_ptr = [&](int64_t i) {
-            if (flat) return x + i * 8;
-            const int64_t r = i / chunks_per_row;
-            return x + r * ld + (i - r * chunks_per_row) * 8;
-        };
-        int64_t i = tid;
-        for (; i + 3 * stride < total; i += 4 * stride) {
-            const uint4 w0 = ldg_nc_16(chunk_ptr(i)), w1 = ldg_nc_16(chunk_ptr(i + stride));
-            const uint4 w2 = ldg_nc_16(chunk_ptr(i + 2 * stride)), w3 = ldg_nc_16(chunk_ptr(i + 3 * stride));
-            m = fmaxf(m, fmaxf(fmaxf(abs_max8<T>(w0), abs_max8<T>(w1)), fmaxf(abs_max8<T>(w2), abs_max8<T>(w3))));
-        }
-        for (; i < total; i += stride) m = fmaxf(m, abs_max8<T>(ldg_nc_16(chunk_ptr(i))));
+    if (vec == 32) {
+        m = amax_chunks<T, 32>(x, rows, cols, ld, tid, stride);
+    } else if (vec == 16) {
+        m = amax_chunks<T, 16>(x, rows, cols, ld, tid, stride);
     } else {
         const int64_t total = rows * cols;
         for (int64_t i = tid; i < total; i += stride) {
@@ -466,18 +492,23 @@ __device__ __forceinline__ float encode_stochastic(const float (&v)[16], float r
                                                    uint32_t &lo, uint32_t &hi) {
     float q[16], sum = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const float xs = __fmaf_rn(v[i], r, 0.0f);
-        const float a = fabsf(xs);
-        const float inv = a < 2.0f ? 2.0f : (a < 4.0f ? 1.0f : 0.5f);          // 1 / grid step at |x*r|
-        const float step = a < 2.0f ? 0.5f : (a < 4.0f ? 1.0f : 2.0f);
+    for (int i = 0; i < 16; i += 2) {
+        // one hash per pair of values: 16 random bits each, centred (the low mantissa bit set)
         const uint32_t h = hash32(sr.key ^ (sr.block * 32u + candidate * 16u + i));
-        const float noise = __uint_as_float((h >> 9) | 0x3f800000u) - 1.5f;       // uniform in [-0.5, 0.5)
-        const float steps = (__fmaf_rn(a, inv, noise) + 12582912.0f) - 12582912.0f;   // rint, ties to even
-        const float mag = fminf(fmaxf(steps, 0.0f) * step, 6.0f);
-        q[i] = copysignf(mag, xs);
-        const float t = q[i] - xs;
-        sum = __fmaf_rn(t, t, sum);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float xs = __fmaf_rn(v[i + k], r, 0.0f);
+            const float a = fabsf(xs);
+            const float inv = a < 2.0f ? 2.0f : (a < 4.0f ? 1.0f : 0.5f);          // 1 / grid step at |x*r|
+            const float step = a < 2.0f ? 0.5f : (a < 4.0f ? 1.0f : 2.0f);
+            const uint32_t bits16 = k == 0 ? (h & 0xffffu) : (h >> 16);
+            const float noise = __uint_as_float((bits16 << 7) | 0x3f800040u) - 1.5f;    // uniform in (-0.5, 0.5)
+            const float steps = (__fmaf_rn(a, inv, noise) + 12582912.0f) - 12582912.0f;   // rint, ties to even
+            const float mag = fminf(fmaxf(steps, 0.0f) * step, 6.0f);
+            q[i + k] = copysignf(mag, xs);
+            const float t = q[i + k] - xs;
+            sum = __fmaf_rn(t, t, sum);
+        }
     }
     lo = cvt_e2m1x8(q);          // exact: every q is a grid point
     hi = cvt_e2m1x8(q + 8);
@@ -1465,12 +1496,14 @@ cudaError_t launch_amax(const void *x, int64_t rows, int64_t cols, int64_t ld, b
         if (e != cudaSuccess) return e;
         resident[slot] = (per_sm > 0 ? per_sm : 1) * sms;
     }
-    const int64_t work = vec16 ? rows * (cols >> 3) : rows * cols;
+    const bool vec32 = vec16 && reinterpret_cast<uintptr_t>(x) % 32 == 0 && (ld * 2) % 32 == 0 && cols % 16 == 0;
+    const int vec = vec32 ? 32 : (vec16 ? 16 : 0);
+    const int64_t work = vec ? rows * (cols / (vec / 2)) : rows * cols;
     int64_t blocks = (work + 255) / 256;
     if (blocks > resident[slot]) blocks = resident[slot];
     if (blocks < 1) blocks = 1;
     cfg = dependent_launch_config(static_cast<unsigned>(blocks), 256, stream, attr);
-    return cudaLaunchKernelEx(&cfg, amax_kernel<T>, static_cast<const T *>(x), rows, cols, ld, vec16 ? 1 : 0, amax);
+    return cudaLaunchKernelEx(&cfg, amax_kernel<T>, static_cast<const T *>(x), rows, cols, ld, vec, amax);
 }
 
 template <typename T>
