@@ -1018,7 +1018,9 @@ constexpr int FEED_CONSUMERS = 256;
 constexpr int FEED_THREADS = FEED_CONSUMERS + 32;
 constexpr int FEED_SMEM_BYTES = FEED_STAGES * FEED_STAGE_BYTES + 1024;
 
-template <typename T, int KIND, bool FAKE = false, bool TWO_D = false>
+// EXTRAS: the instantiation that can rotate blocks (random Hadamard transform) and round
+// stochastically; the plain one carries neither code path, which keeps its register count down.
+template <typename T, int KIND, bool FAKE = false, bool TWO_D = false, bool EXTRAS = false>
 __global__ void __launch_bounds__(FEED_THREADS, FOS_FEED_CTAS)
 quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantParams p) {
     static_assert(!(FAKE && TWO_D), "the fused fake quantization is built for 1-D blocks");
@@ -1135,9 +1137,9 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
                 v[2 * i + 1] = f.y;
             }
             uint32_t lo, hi, sf_byte;
-            if (p.rht) rotate16<T>(v);
+            if (EXTRAS && p.rht) rotate16<T>(v);
             StochasticArgs sr{0u, 0u, 0u};
-            if (!TWO_D && p.stochastic)
+            if (EXTRAS && !TWO_D && p.stochastic)
                 sr = stochastic_args(p, (static_cast<int64_t>(fake_tr) * 128 + j * 64 + row_in_tile) * n_cb + tc_ * 4 + cb);
             quantize_block<KIND, TWO_D, false>(v, tc, p.rule, p.exact_only != 0, TWO_D ? scratch2d + warp * 512 : nullptr, lane,
                                                lut, TWO_D ? nullptr : coop[warp], lo, hi, sf_byte, sr);
@@ -1200,7 +1202,7 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
 
 constexpr int COLS_BOX_ROWS = 64, COLS_BOX_BYTES = 256;
 
-template <typename T, int KIND, bool TWO_D = false>
+template <typename T, int KIND, bool TWO_D = false, bool EXTRAS = false>
 __global__ void __launch_bounds__(FEED_THREADS, FOS_FEED_CTAS)
 quantize_cols_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantParams p) {
     extern __shared__ uint8_t feed_smem_raw[];
@@ -1292,9 +1294,9 @@ quantize_cols_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
                 v[i] = elem_to_float<T>(reinterpret_cast<const T &>(h));
             }
             uint32_t lo, hi, sf_byte;
-            if (p.rht) rotate16<T>(v);
+            if (EXTRAS && p.rht) rotate16<T>(v);
             StochasticArgs sr{0u, 0u, 0u};
-            if (!TWO_D && p.stochastic)
+            if (EXTRAS && !TWO_D && p.stochastic)
                 sr = stochastic_args(p, (static_cast<int64_t>(tr) * 128 + jr) * n_cb + tc_ * 4 + pair * 2 + j);
             quantize_block<KIND, TWO_D, TWO_D>(v, tc, p.rule, p.exact_only != 0, TWO_D ? scratch2d + warp * 512 : nullptr, lane,
                                                lut, TWO_D ? nullptr : coop[warp], lo, hi, sf_byte, sr);
@@ -1329,8 +1331,8 @@ inline bool make_x_map(CUtensorMap *map, const QuantParams &p, bool transposed) 
 }
 
 // Launches the TMA-fed kernel when x qualifies; *launched tells whether it did.
-template <typename T, int KIND, bool TRANSPOSED, bool FAKE = false, bool TWO_D = false>
-cudaError_t launch_rows_tma(const QuantParams &p, cudaStream_t stream, bool *launched) {
+template <typename T, int KIND, bool TRANSPOSED, bool FAKE, bool TWO_D, bool EXTRAS>
+cudaError_t launch_rows_tma_impl(const QuantParams &p, cudaStream_t stream, bool *launched) {
     *launched = false;
     if (reinterpret_cast<uintptr_t>(p.x) % 16 != 0 || (p.ld * 2) % 16 != 0) return cudaSuccess;
     // the transposed kernel stores 16 bytes of codes and 2 scale bytes at a time
@@ -1338,7 +1340,7 @@ cudaError_t launch_rows_tma(const QuantParams &p, cudaStream_t stream, bool *lau
     if (p.cols * 2 >= (int64_t(1) << 31) || p.rows >= (int64_t(1) << 31) || p.ld * 2 >= (int64_t(1) << 40)) return cudaSuccess;
     CUtensorMap map;
     if (!make_x_map(&map, p, TRANSPOSED)) return cudaSuccess;
-    auto kernel = TRANSPOSED ? quantize_cols_tma_kernel<T, KIND, TWO_D> : quantize_rows_tma_kernel<T, KIND, FAKE, TWO_D>;
+    auto kernel = TRANSPOSED ? quantize_cols_tma_kernel<T, KIND, TWO_D, EXTRAS> : quantize_rows_tma_kernel<T, KIND, FAKE, TWO_D, EXTRAS>;
     static int ctas_per_sm[64] = {};
     static int sm_count[64] = {};
     int dev = 0;
@@ -1372,6 +1374,14 @@ cudaError_t launch_rows_tma(const QuantParams &p, cudaStream_t stream, bool *lau
     e = cudaLaunchKernelEx(&cfg, kernel, map, p);
     if (e == cudaSuccess) *launched = true;
     return e;
+}
+
+template <typename T, int KIND, bool TRANSPOSED, bool FAKE = false, bool TWO_D = false>
+cudaError_t launch_rows_tma(const QuantParams &p, cudaStream_t stream, bool *launched) {
+    if constexpr (!FAKE) {
+        if (p.rht || p.stochastic) return launch_rows_tma_impl<T, KIND, TRANSPOSED, FAKE, TWO_D, true>(p, stream, launched);
+    }
+    return launch_rows_tma_impl<T, KIND, TRANSPOSED, FAKE, TWO_D, false>(p, stream, launched);
 }
 
 template <typename T, int KIND>

@@ -100,12 +100,13 @@ class TensorParallelLinear(nn.Module):
     row-parallel layer: the tokens are cut into `chunks` pieces, and while pieces are in flight the
     GEMM leaves `comm_sms` SMs idle, because a persistent grid on every SM would keep the
     collective's kernel waiting until the GEMM has finished (the option is process-wide:
-    one row-parallel layer at a time per process).
+    one row-parallel layer at a time per process). 32 is what NCCL's all-reduce launches on a
+    pair of B200s; with fewer free SMs part of its grid still waits for the GEMM.
     """
 
     def __init__(self, weight: torch.Tensor | QuantizedTensor, config: ModuleQuantizationConfig, mode: str, *,
                  group: dist.ProcessGroup | None = None, bias: torch.Tensor | None = None, chunks: int = 4,
-                 comm_sms: int = 20, matmul_fn: MatmulFn | None = None, quantize_fn: Callable | None = None) -> None:
+                 comm_sms: int = 32, matmul_fn: MatmulFn | None = None, quantize_fn: Callable | None = None) -> None:
         super().__init__()
         if mode not in ("column", "row"):
             raise ValueError("mode must be 'column' or 'row'")
