@@ -87,6 +87,15 @@ quantize_mx_kernel(const MxParams p) {
     const bool quarter = p.inv_maxq_is_quarter != 0.0f;
     if (blockIdx.x == 0 && tid == 0) *p.amax_out = 1.0f;
 
+    // run `it` of a thread: row 32 * it + tid / 8 of the tile, columns 16 * (tid % 8) .. + 15. What
+    // depends on the thread alone is computed once (and made opaque, or the compiler recomputes it).
+    const int r0 = tid >> 3, piece = tid & 7;
+    const int64_t code_ld = p.cols_p / 2;
+    int64_t x_thr = r0 * p.ld + piece * 16, code_thr = r0 * code_ld + piece * 8;
+    int64_t sf_thr = p.sf_tiled ? r0 * 16 + (piece >> 1) : r0 * n_cb + (piece >> 1);
+    asm volatile("" : "+l"(x_thr), "+l"(code_thr), "+l"(sf_thr));
+    const int64_t x_it = 32 * p.ld, code_it = 32 * code_ld, sf_it = p.sf_tiled ? 4 : 32 * n_cb;
+
     for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
         const int64_t i0 = (t / tiles_c) * MX_TILE, j0 = (t % tiles_c) * MX_TILE;   // tile origin in Y
 
@@ -139,15 +148,16 @@ quantize_mx_kernel(const MxParams p) {
         uint32_t w[4][8];
 #pragma unroll
         for (int it = 0; it < 4; ++it) {
-            const int item = it * MX_THREADS + tid;
-            const int r = item >> 3, piece = item & 7;    // row of the tile, run of 16 columns
+            const int r = it * 32 + r0;                   // row of the tile
             if constexpr (STAGED) {
                 const uint32_t *src = reinterpret_cast<const uint32_t *>(tile + r * MX_PITCH + piece * 16);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) w[it][k] = src[k];
             } else {
                 const int64_t i = i0 + r, j = j0 + piece * 16;
-                if (i < p.rows && j + 16 <= p.cols && p.vec32) {
+                if (p.vec32 && i0 + MX_TILE <= p.rows && j0 + MX_TILE <= p.cols) {       // whole tile inside x
+                    ldg_nc_32(x + (i0 * p.ld + j0) + x_thr + it * x_it, w[it]);
+                } else if (i < p.rows && j + 16 <= p.cols && p.vec32) {
                     ldg_nc_32(x + i * p.ld + j, w[it]);
                 } else if (i < p.rows && j + 16 <= p.cols && p.vec16) {
                     const uint4 lo = ldg_nc_16(x + i * p.ld + j), hi = ldg_nc_16(x + i * p.ld + j + 8);
@@ -183,11 +193,11 @@ quantize_mx_kernel(const MxParams p) {
             __syncthreads();
         }
 
+        uint8_t *codes_tile = p.codes + i0 * code_ld + (j0 >> 1);
+        uint8_t *sf_tile = p.sf + (p.sf_tiled ? t * 512 : i0 * n_cb + (j0 >> 5));   // tile t of the tiled layout
 #pragma unroll
         for (int it = 0; it < 4; ++it) {
-            const int item = it * MX_THREADS + tid;
-            const int r = item >> 3, piece = item & 7;
-            const int64_t i = i0 + r, j = j0 + piece * 16;
+            const int r = it * 32 + r0;
             float v[16];
             float bmax = unpack16<T>(w[it], v);
             // the neighbouring lane holds the other half of the 32-value block
@@ -196,8 +206,8 @@ quantize_mx_kernel(const MxParams p) {
             float inv;
             const uint32_t e = mx_scale(bmax, quarter, inv);
             const uint2 c = mx_encode16(v, inv);
-            *reinterpret_cast<uint2 *>(p.codes + i * (p.cols_p / 2) + j / 2) = c;
-            if ((piece & 1) == 0) p.sf[sf_offset(i, j >> 5, n_cb, p.sf_tiled != 0)] = static_cast<uint8_t>(e);
+            *reinterpret_cast<uint2 *>(codes_tile + code_thr + it * code_it) = c;
+            if ((piece & 1) == 0) sf_tile[sf_thr + it * sf_it] = static_cast<uint8_t>(e);
         }
     }
 }
