@@ -1,0 +1,100 @@
+// Second half of the row-parallel exchange. fos_gemm_nvfp4_scatter has written every rank's partial
+// product of slab o (rows o * slab .. + slab - 1 of the output) into rank o's staging buffer, plane by
+// plane, over NVLink while its tiles completed. Here rank o adds the planes of its slab in binary32
+// (in rank order, so the sum does not depend on who computes it: only the owner does), rounds once to
+// the output type and stores the result into the output buffer of EVERY rank (plain peer stores).
+// Between the two kernels, and after this one, the ranks need a barrier in stream order.
+#include "fos_common.cuh"
+
+namespace fos {
+namespace {
+
+struct ReduceGatherParams {
+    const void *staging;     // this rank's staging buffer: [world][slab_rows][ld_staging]
+    void *out_peer[8];       // every rank's output buffer [world * slab_rows][ld_out] (peer mappings)
+    int world, rank;
+    int64_t slab_rows, n, ld_staging, ld_out;
+};
+
+template <typename T> __device__ __forceinline__ float2 pair_to_float2(uint32_t w);
+template <> __device__ __forceinline__ float2 pair_to_float2<__nv_bfloat16>(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 pair_to_float2<__half>(uint32_t w) {
+    return __half22float2(*reinterpret_cast<__half2 *>(&w));
+}
+template <typename T> __device__ __forceinline__ uint32_t float2_to_pair(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t float2_to_pair<__nv_bfloat16>(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+template <> __device__ __forceinline__ uint32_t float2_to_pair<__half>(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+// One thread per 8 output values (16 bytes): world 16-byte loads, one 16-byte store per rank.
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_gather_kernel(const ReduceGatherParams p) {
+    const int64_t chunks_per_row = p.n >> 3, total = p.slab_rows * chunks_per_row;
+    const T *staging = static_cast<const T *>(p.staging);
+    const int64_t plane = p.slab_rows * p.ld_staging;
+    for (int64_t u = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; u < total;
+         u += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t i = u / chunks_per_row, j = (u - i * chunks_per_row) * 8;
+        float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        uint4 w[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+            if (s < p.world) w[s] = *reinterpret_cast<const uint4 *>(staging + s * plane + i * p.ld_staging + j);
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            if (s >= p.world) break;
+            const uint32_t v[4] = {w[s].x, w[s].y, w[s].z, w[s].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = pair_to_float2<T>(v[k]);
+                acc[2 * k] += f.x;
+                acc[2 * k + 1] += f.y;
+            }
+        }
+        const uint4 r = make_uint4(float2_to_pair<T>(acc[0], acc[1]), float2_to_pair<T>(acc[2], acc[3]),
+                                   float2_to_pair<T>(acc[4], acc[5]), float2_to_pair<T>(acc[6], acc[7]));
+        const int64_t off = (static_cast<int64_t>(p.rank) * p.slab_rows + i) * p.ld_out + j;
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+            if (t < p.world) *reinterpret_cast<uint4 *>(static_cast<T *>(p.out_peer[t]) + off) = r;
+    }
+}
+
+}  // namespace
+}  // namespace fos
+
+extern "C" int fos_reduce_gather(const void *staging, void *const *out_peers, int world, int rank, int64_t slab_rows,
+                                 int64_t n, int64_t ld_staging, int64_t ld_out, int dtype, void *stream_) {
+    using namespace fos;
+    if (!staging || !out_peers || world < 2 || world > 8 || rank < 0 || rank >= world) return FOS_ERR_INVALID_ARGUMENT;
+    if (slab_rows <= 0 || n <= 0 || ld_staging < n || ld_out < n) return FOS_ERR_INVALID_ARGUMENT;
+    if (dtype != FOS_BF16 && dtype != FOS_FP16) return FOS_ERR_UNSUPPORTED;
+    if (n % 8 != 0 || ld_staging % 8 != 0 || ld_out % 8 != 0) return FOS_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(staging) % 16 != 0) return FOS_ERR_MISALIGNED;
+    ReduceGatherParams p{};
+    p.staging = staging;
+    for (int i = 0; i < world; ++i) {
+        if (!out_peers[i]) return FOS_ERR_INVALID_ARGUMENT;
+        if (reinterpret_cast<uintptr_t>(out_peers[i]) % 16 != 0) return FOS_ERR_MISALIGNED;
+        p.out_peer[i] = out_peers[i];
+    }
+    p.world = world; p.rank = rank;
+    p.slab_rows = slab_rows; p.n = n; p.ld_staging = ld_staging; p.ld_out = ld_out;
+    const int st = check_device();
+    if (st != FOS_OK) return st;
+    const int64_t total = slab_rows * (n >> 3);
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (dtype == FOS_BF16) reduce_gather_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+    else reduce_gather_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+    FOS_CUDA_TRY(cudaGetLastError());
+    return FOS_OK;
+}

@@ -105,6 +105,14 @@ struct GemmParams {
     int out_dtype;
     int debug;               // FOS_OPT_GEMM_DEBUG bits (timing experiments only; results are wrong)
     int mx;                  // operands are MXFP4: E8M0 scales per 32 values, a 512-byte scale tile spans 128 values of K
+    // Row-parallel layers: this rank's partial product is not stored to d but scattered, tile by tile as
+    // the tiles complete, into the staging buffers of the ranks that will reduce them. Rows are cut into
+    // `scatter_world` slabs of `slab_rows`; slab o belongs to rank o, whose staging buffer d_peer[o]
+    // (a peer mapping unless o is this rank) is [world][slab_rows][ldd]; this rank writes plane scatter_rank.
+    int scatter_world;       // 0: plain store to d
+    int scatter_rank;
+    int64_t slab_rows;
+    void *d_peer[8];
 };
 
 // ---------------------------------------------------------------------------- MMA wrappers
@@ -356,6 +364,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             int64_t mb, nb;
             tile_coords(t, num_m, num_n, mb, nb);
             const int64_t row = mb * BLOCK_M + quad * 32 + lane, n0 = nb * BLOCK_N + half * COLS;
+            if (p.scatter_world > 1) {
+                // the owner of this tile's rows; its buffer's plane `scatter_rank`, addressed by the global row
+                const int o = static_cast<int>((mb * BLOCK_M) / p.slab_rows);
+                out = static_cast<OUT *>(p.d_peer[o]) + (static_cast<int64_t>(p.scatter_rank) - o) * p.slab_rows * p.ldd;
+            }
             const uint32_t acc = tile_i % C::ACC_STAGES, acc_ph = (tile_i / C::ACC_STAGES) & 1u;
             ok = mbar_wait(acc_full_bar + 8 * acc, acc_ph, abort_flag, p.status, 4);
             ok = __all_sync(0xffffffffu, ok);
@@ -940,8 +953,17 @@ extern "C" int fos_set_option(int key, int value) {
 static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
                           const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
                           int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, int32_t *status,
-                          void *stream_, int mx) {
+                          void *stream_, int mx, void *const *d_peers = nullptr, int world = 0, int rank = 0) {
     using namespace fos;
+    if (d_peers) {
+        if (world < 2 || world > 8 || rank < 0 || rank >= world) return FOS_ERR_INVALID_ARGUMENT;
+        if (m_p % (128 * static_cast<int64_t>(world)) != 0) return FOS_ERR_UNSUPPORTED;   // slabs of whole row blocks
+        for (int i = 0; i < world; ++i) {
+            if (!d_peers[i]) return FOS_ERR_INVALID_ARGUMENT;
+            if (reinterpret_cast<uintptr_t>(d_peers[i]) % 32 != 0) return FOS_ERR_MISALIGNED;
+        }
+        d = d_peers[rank];
+    }
     if (!a_codes || !a_sf || !b_codes || !b_sf || !alpha || !d) return FOS_ERR_INVALID_ARGUMENT;
     if (m_p <= 0 || n_p <= 0 || k_p < 64 || m_p % 128 || n_p % 128 || k_p % (mx ? 128 : 64)) return FOS_ERR_INVALID_ARGUMENT;
     if (m <= 0 || n <= 0 || m > m_p || n > n_p || ldd < n) return FOS_ERR_INVALID_ARGUMENT;
@@ -959,7 +981,13 @@ static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uin
     FOS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     if (g_gemm_max_ctas > 0 && g_gemm_max_ctas < sms) sms = g_gemm_max_ctas;   // leave SMs to concurrent kernels
 
-    GemmParams p{a_sf, b_sf, alpha, d, status, m_p, n_p, k_p, m, n, ldd, out_dtype, g_gemm_debug, mx};
+    GemmParams p{a_sf, b_sf, alpha, d, status, m_p, n_p, k_p, m, n, ldd, out_dtype, g_gemm_debug, mx, 0, 0, 0, {}};
+    if (d_peers) {
+        p.scatter_world = world;
+        p.scatter_rank = rank;
+        p.slab_rows = m_p / world;
+        for (int i = 0; i < world; ++i) p.d_peer[i] = d_peers[i];
+    }
     const int64_t sf_k_tiles = mx ? k_p / 128 : k_p / 64;     // 512-byte scale tiles along K
     if (status) FOS_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
     CUtensorMap map_a, map_b;
@@ -968,7 +996,7 @@ static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uin
     // (its hand-overs between the two SMs lengthen the load round trip), so it only runs when
     // asked for.
     const bool pair_fits = m_p % 256 == 0 && n_p % 256 == 0;
-    const bool use_pair = pair_fits && g_gemm_variant == 2 && !mx;
+    const bool use_pair = pair_fits && g_gemm_variant == 2 && !mx && !d_peers;
     if (use_pair) {
         CUtensorMap map_sfa, map_sfb;
         if ((st = make_operand_map(&map_a, a_codes, m_p, k_p / 2, 128)) != FOS_OK) return st;
@@ -1008,4 +1036,14 @@ extern "C" int fos_gemm_mxfp4(const uint8_t *a_codes, const uint8_t *a_sf, const
                               int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, int32_t *status,
                               void *stream) {
     return gemm_fp4_entry(a_codes, a_sf, b_codes, b_sf, alpha, d, out_dtype, m_p, n_p, k_p, m, n, ldd, status, stream, 1);
+}
+
+extern "C" int fos_gemm_nvfp4_scatter(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                                      const uint8_t *b_sf, const float *alpha, void *const *d_peers, int world, int rank,
+                                      int out_dtype, int64_t m_p, int64_t n_p, int64_t k_p, int64_t m, int64_t n,
+                                      int64_t ldd, int32_t *status, void *stream) {
+    if (!d_peers) return FOS_ERR_INVALID_ARGUMENT;
+    if (out_dtype != FOS_BF16 && out_dtype != FOS_FP16) return FOS_ERR_UNSUPPORTED;
+    return gemm_fp4_entry(a_codes, a_sf, b_codes, b_sf, alpha, nullptr, out_dtype, m_p, n_p, k_p, m, n, ldd, status, stream, 0,
+                          d_peers, world, rank);
 }

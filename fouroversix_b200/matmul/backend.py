@@ -118,3 +118,36 @@ class B200MatmulBackend:
             raise _native.NativeLibraryError(
                 f"fos_gemm_nvfp4: a bounded device-side wait timed out (site {int(status.item())})")
         return out
+
+    @classmethod
+    def quantized_matmul_scatter(cls, input: QuantizedTensor, other: QuantizedTensor, *, out_dtype: DataType,
+                                 d_peers, world: int, rank: int) -> None:
+        """First half of a row-parallel layer's exchange: this rank's partial product `input @ other.T`, each
+        tile stored as it completes into plane `rank` of the staging buffer of the rank that owns its rows
+        (fos_gemm_nvfp4_scatter). `d_peers` is a ctypes array of `world` device pointers to the staging
+        buffers [world][rows / world][n] of all ranks as mapped into this process."""
+        reason = cls.unsupported_reason(input, other, out_dtype=out_dtype)
+        if reason is not None:
+            raise ValueError(f"B200 matmul: {reason}")
+        if not (input.dtype == other.dtype == DataType.nvfp4 and _layout(input) == _layout(other) == _native.FOS_SF_TILED):
+            raise ValueError("B200 matmul: the scatter epilogue needs two NVFP4 operands with tiled scales")
+        dev = input.device
+        m, n = input.original_shape[0], other.original_shape[0]
+        m_p, k_p = input.padded_shape
+        n_p = other.padded_shape[0]
+        if other.padded_shape[1] != k_p:
+            raise ValueError("B200 matmul: operands are padded to different inner dimensions")
+        torch_out = _OUT[DataType(out_dtype)]
+        alpha = torch.empty(1, dtype=torch.float32, device=dev)
+        a_vals, b_vals = input.values.contiguous(), other.values.contiguous()
+        a_sf, b_sf = input.scale_factors.contiguous(), other.scale_factors.contiguous()
+        with torch.cuda.device(dev):
+            lib, stream = _native.lib(), _native.stream_ptr(dev)
+            _native.check(lib.fos_gemm_alpha(
+                input.amax.data_ptr(), _native.FOS_NVFP4, input.scale_rule.cuda_id,
+                other.amax.data_ptr(), _native.FOS_NVFP4, other.scale_rule.cuda_id, alpha.data_ptr(), stream), "fos_gemm_alpha")
+            _native.check(lib.fos_gemm_nvfp4_scatter(
+                a_vals.data_ptr(), a_sf.data_ptr(), b_vals.data_ptr(), b_sf.data_ptr(), alpha.data_ptr(),
+                d_peers, world, rank, _native.elem_code(torch_out), m_p, n_p, k_p, m, n, n, 0, stream),
+                "fos_gemm_nvfp4_scatter")
+

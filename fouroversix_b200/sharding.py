@@ -106,12 +106,17 @@ class TensorParallelLinear(nn.Module):
 
     def __init__(self, weight: torch.Tensor | QuantizedTensor, config: ModuleQuantizationConfig, mode: str, *,
                  group: dist.ProcessGroup | None = None, bias: torch.Tensor | None = None, chunks: int = 4,
-                 comm_sms: int = 32, matmul_fn: MatmulFn | None = None, quantize_fn: Callable | None = None) -> None:
+                 comm_sms: int = 32, fused: bool | None = None, matmul_fn: MatmulFn | None = None,
+                 quantize_fn: Callable | None = None) -> None:
         super().__init__()
         if mode not in ("column", "row"):
             raise ValueError("mode must be 'column' or 'row'")
         self.mode, self.config, self.group, self.chunks = mode, config, group, max(1, chunks)
         self.comm_sms = max(0, comm_sms)
+        # row-parallel exchange through peer memory (scatter from the GEMM's epilogue, then reduce + gather):
+        # None = use it when it can be set up, True = require it, False = NCCL all-reduce beside the GEMM
+        self.fused = fused
+        self._peer: dict | None = None
         self._matmul = matmul_fn or quantized_matmul
         self._quantize = quantize_fn or quantize
         self.weight = weight if isinstance(weight, QuantizedTensor) else self._quantize(weight, config.get_weight_config())
@@ -139,10 +144,75 @@ class TensorParallelLinear(nn.Module):
             out = out + self.bias
         return out.reshape(*lead, out.shape[-1])
 
+    def _peer_buffers(self, tokens: int, n_out: int, dtype: torch.dtype, dev: torch.device) -> dict:
+        """Staging [world][tokens / world][n_out] and output [tokens][n_out] of this rank in symmetric
+        memory (every rank maps every rank's buffers), built once per shape."""
+        key = (tokens, n_out, dtype)
+        if self._peer is not None and self._peer["key"] == key:
+            return self._peer
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm
+
+        world = self.world_size
+        group = self.group if self.group is not None else dist.group.WORLD
+        staging = symm.empty((world, tokens // world, n_out), dtype=dtype, device=dev)
+        out = symm.empty((tokens, n_out), dtype=dtype, device=dev)
+        h_staging, h_out = symm.rendezvous(staging, group), symm.rendezvous(out, group)
+
+        def pointers(handle):
+            return (ctypes.c_void_p * world)(*[int(ptr) for ptr in handle.buffer_ptrs])
+
+        self._peer = {"key": key, "staging": staging, "out": out, "h_staging": h_staging, "h_out": h_out,
+                      "staging_ptrs": pointers(h_staging), "out_ptrs": pointers(h_out)}
+        return self._peer
+
+    def _row_parallel_fused(self, x2d: torch.Tensor, act_cfg: QuantizationConfig) -> torch.Tensor | None:
+        """The exchange over peer memory: the GEMM's epilogue scatters this rank's partial tiles into the
+        owners' staging buffers while the GEMM runs (fos_gemm_nvfp4_scatter), a barrier, every rank reduces
+        its slab and stores it into every rank's output (fos_reduce_gather), a barrier. Returns None when the
+        request does not fit (the caller then takes the NCCL path). The result lives in a buffer that the
+        next call of this layer overwrites."""
+        from fouroversix_b200.matmul.backend import B200MatmulBackend
+
+        world, tokens = self.world_size, x2d.shape[0]
+        n_out = self.weight.original_shape[0]
+        out_dtype = DataType(self.config.output_dtype)
+        if (self._matmul is not quantized_matmul or x2d.device.type != "cuda" or not 2 <= world <= 8
+                or tokens % (128 * world) or n_out % 8 or out_dtype not in (DataType.bfloat16, DataType.float16)
+                or self.weight.dtype != DataType.nvfp4 or act_cfg.dtype != DataType.nvfp4
+                or not self.weight.scale_factors_are_in_blackwell_layout):
+            return None
+        try:
+            buf = self._peer_buffers(tokens, n_out, out_dtype.torch_dtype, x2d.device)
+        except Exception:                                  # symmetric memory is not available here
+            if self.fused:
+                raise
+            self.fused = False
+            return None
+        rank = dist.get_rank(self.group)
+        xq = self._quantize(x2d, act_cfg)
+        B200MatmulBackend.quantized_matmul_scatter(xq, self.weight, out_dtype=out_dtype, d_peers=buf["staging_ptrs"],
+                                                   world=world, rank=rank)
+        buf["h_staging"].barrier(channel=0)                # every rank's plane of my slab has arrived
+        with torch.cuda.device(x2d.device):
+            _native.check(_native.lib().fos_reduce_gather(
+                buf["staging"].data_ptr(), buf["out_ptrs"], world, rank, tokens // world, n_out, n_out, n_out,
+                _native.elem_code(out_dtype.torch_dtype), _native.stream_ptr(x2d.device)), "fos_reduce_gather")
+        buf["h_out"].barrier(channel=0)                    # every slab of my output is in
+        return buf["out"]
+
     def _row_parallel(self, x2d: torch.Tensor, act_cfg: QuantizationConfig) -> torch.Tensor:
         """Partial product per chunk of tokens, each chunk's all-reduce overlapped with the
         next chunk's GEMM. The local activations are quantized once (one amax for all
         chunks) and sliced by rows."""
+        if self.fused is not False:
+            out = self._row_parallel_fused(x2d, act_cfg)
+            if out is not None:
+                return out
+            if self.fused:
+                raise ValueError("TensorParallelLinear: this call does not fit the peer-memory exchange "
+                                 "(NVFP4 operands, bf16 / fp16 output, tokens a multiple of 128 * world size)")
         tokens = x2d.shape[0]
         n_chunks = self.chunks
         while n_chunks > 1 and (tokens % (128 * n_chunks) != 0):

@@ -154,6 +154,32 @@ int fos_gemm_mxfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b
                    void *stream);
 
 /*
+ * Row-parallel layers over `world` GPUs of one node (2..8), in two kernels with a barrier between the ranks
+ * after each (in stream order; the caller provides it):
+ *
+ * fos_gemm_nvfp4_scatter: the NVFP4 GEMM of fos_gemm_nvfp4, but the partial product of this rank is not
+ *   stored to one buffer: the rows are cut into `world` slabs of m_p / world rows (m_p must be a multiple of
+ *   128 * world) and every tile is stored, as it completes, into plane `rank` of the staging buffer of the
+ *   rank that owns its slab: d_peers[o] is rank o's buffer [world][m_p / world][ldd] of out_dtype (bf16 or
+ *   fp16), mapped into this process (peer memory over NVLink, e.g. torch symmetric memory; d_peers[rank] is
+ *   local). d_peers is a HOST array of `world` device pointers, each 32-byte aligned.
+ * fos_reduce_gather: rank `rank` adds the `world` planes of its own staging buffer in binary32 (rank
+ *   order), rounds once to `dtype` and stores rows rank * slab_rows .. of the result into out_peers[t] for
+ *   every t (each [world * slab_rows][ld_out], 16-byte aligned; n, ld_staging and ld_out multiples of 8).
+ *
+ * Together they are an all-reduce of the partial products whose first half rides on the GEMM's epilogue.
+ * They stand where the reference relies on vLLM's tensor-parallel all-reduce after a row-parallel layer
+ * (src/fouroversix/integrations/vllm_quantization.py:100-124); nothing in the reference's own package
+ * corresponds to them.
+ */
+int fos_gemm_nvfp4_scatter(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                           const uint8_t *b_sf, const float *alpha, void *const *d_peers, int world, int rank,
+                           int out_dtype, int64_t m_p, int64_t n_p, int64_t k_p, int64_t m, int64_t n,
+                           int64_t ldd, int32_t *status, void *stream);
+int fos_reduce_gather(const void *staging, void *const *out_peers, int world, int rank, int64_t slab_rows,
+                      int64_t n, int64_t ld_staging, int64_t ld_out, int dtype, void *stream);
+
+/*
  * D[m, n] = alpha[0] * sum_k A[m, k] * B[n, k] for operands in FOS_IF4 or FOS_NVFP4 (any mix),
  * scales in either layout. Each element is expanded to fp16(value) * fp16(|scale|) (integer
  * blocks: fp16(int * 6/7) first), the fp16 matrices are multiplied on the tensor cores

@@ -41,10 +41,15 @@ def _worker(rank: int, world: int, port: int, results):
         w_down = (torch.randn(hidden, inner, generator=g) * 0.05).bfloat16().to(dev)
         cfg = fos.ModuleQuantizationConfig()
         up = TensorParallelLinear(shard_linear_weight(w_up, "column", rank, world), cfg, "column")
-        down = TensorParallelLinear(shard_linear_weight(w_down, "row", rank, world).contiguous(), cfg, "row", chunks=4)
+        w_down_shard = shard_linear_weight(w_down, "row", rank, world).contiguous()
+        down = TensorParallelLinear(w_down_shard, cfg, "row", chunks=4, fused=False)      # NCCL beside the GEMM
+        down_peer = TensorParallelLinear(w_down_shard, cfg, "row")                         # peer-memory exchange if it can be set up
         h = up(x)
         y = down(h)
+        y_peer = down_peer(h).clone()
+        y_peer_again = down_peer(h).clone()                # the buffers are reused
         torch.cuda.synchronize()
+        peer_used = down_peer.fused is not False
 
         # the same on this GPU alone: per-shard products in bf16 (what each rank contributes), summed
         want = torch.zeros(tokens, hidden, dtype=torch.float32, device=dev)
@@ -52,6 +57,12 @@ def _worker(rank: int, world: int, port: int, results):
             h_r = fos.quantized_matmul(x, shard_linear_weight(w_up, "column", r, world))
             want += fos.quantized_matmul(h_r, shard_linear_weight(w_down, "row", r, world).contiguous()).float()
         err = ((y.float() - want).abs().max() / want.abs().max()).item()
+        peer_err = ((y_peer.float() - want).abs().max() / want.abs().max()).item()
+        peer_repeatable = torch.equal(y_peer, y_peer_again)
+        # every rank must hold the same bits: only a slab's owner computes it
+        gathered = [torch.empty_like(y_peer) for _ in range(world)]
+        dist.all_gather(gathered, y_peer)
+        peer_same = all(torch.equal(gathered[0], t) for t in gathered)
 
         # shard-after-quantize: slices of one quantized weight reproduce the unsharded GEMM exactly
         qw = fos.quantize(w_up)
@@ -64,7 +75,7 @@ def _worker(rank: int, world: int, port: int, results):
         partial = fos.quantized_matmul(slice_cols(qx, klo, khi), slice_cols(qw, klo, khi), out_dtype=fos.DataType.float32)
         dist.all_reduce(partial)
         k_err = ((partial - full).abs().max() / full.abs().max()).item()
-        results[rank] = (err, rows_equal, k_err, tuple(y.shape))
+        results[rank] = (err, rows_equal, k_err, tuple(y.shape), peer_used, peer_err, peer_repeatable, peer_same)
     finally:
         dist.destroy_process_group()
 
@@ -83,8 +94,13 @@ def test_column_then_row_parallel_on_two_gpus():
         p.join(300)
         assert p.exitcode == 0
     for r in range(world):
-        err, rows_equal, k_err, shape = results[r]
+        err, rows_equal, k_err, shape, peer_used, peer_err, peer_repeatable, peer_same = results[r]
         assert shape == (1024, 512)
+        # the exchange over peer memory (or, where symmetric memory cannot be set up, its NCCL fallback):
+        # partials rounded to bf16 once, summed in binary32 by the slab's owner
+        print(f"rank {r}: peer-memory exchange used: {peer_used}, error {peer_err:.2e}")
+        assert peer_err < 1e-2, peer_err
+        assert peer_repeatable and peer_same
         assert err < 2e-2, err            # bf16 partials summed in bf16 by the all-reduce
         assert rows_equal
         assert k_err < 1e-5, k_err
