@@ -503,6 +503,8 @@ def stack_section(args, fos, dev, rank, world):
         flop = 2.0 * STACK_TOKENS * n * k
         entry = {"mode": mode, "n": n, "k": k, "ms": ms, "TFLOP/s": flop / (ms * 1e-3) / 1e12}
         if mode == "row" and world > 1:
+            entry["exchange"] = ("peer memory: scatter from the GEMM's epilogue, then reduce + gather by the owners"
+                                 if layer._peer is not None else "NCCL all-reduce on a second stream, 4 chunks of tokens")
             act_cfg = cfg.get_activation_config()
             entry["ms_quantize_and_gemm"] = timed(lambda: layer._gemm(x, act_cfg))
             out = torch.empty(STACK_TOKENS, n, dtype=torch.bfloat16, device=dev)
@@ -521,7 +523,7 @@ def stack_section(args, fos, dev, rank, world):
         "tokens": STACK_TOKENS, "n_gpus": world, "layers": layers, "ms": total_ms,
         "TFLOP/s": total_flop / (total_ms * 1e-3) / 1e12,
         "how": "eager calls of sharding.TensorParallelLinear.forward (dynamic activation quantization + FP4 GEMM "
-               "[+ NCCL all-reduce on a second stream, 4 chunks of tokens]); CUDA events, max over ranks; weights "
+               "[+ the row-parallel exchange named per layer]); CUDA events, max over ranks; weights "
                "quantized per shard outside the timed region",
     }
 

@@ -1,6 +1,6 @@
 // Second half of the row-parallel exchange. fos_gemm_nvfp4_scatter has written every rank's partial
-// product of slab o (rows o * slab .. + slab - 1 of the output) into rank o's staging buffer, plane by
-// plane, over NVLink while its tiles completed. Here rank o adds the planes of its slab in binary32
+// product of slab o (the 128-row blocks mb of the output with mb % world == o, in order) into rank o's
+// staging buffer, plane by plane, over NVLink while its tiles completed. Here rank o adds the planes of its slab in binary32
 // (in rank order, so the sum does not depend on who computes it: only the owner does), rounds once to
 // the output type and stores the result into the output buffer of EVERY rank (plain peer stores).
 // Between the two kernels, and after this one, the ranks need a barrier in stream order.
@@ -60,10 +60,66 @@ __global__ void __launch_bounds__(256) reduce_gather_kernel(const ReduceGatherPa
         }
         const uint4 r = make_uint4(float2_to_pair<T>(acc[0], acc[1]), float2_to_pair<T>(acc[2], acc[3]),
                                    float2_to_pair<T>(acc[4], acc[5]), float2_to_pair<T>(acc[6], acc[7]));
-        const int64_t off = (static_cast<int64_t>(p.rank) * p.slab_rows + i) * p.ld_out + j;
+        // slab row i is row i % 128 of the slab's block i / 128, which is row block (i / 128) * world + rank of the output
+        const int64_t off = (((i >> 7) * p.world + p.rank) * 128 + (i & 127)) * p.ld_out + j;
 #pragma unroll
         for (int t = 0; t < 8; ++t)
             if (t < p.world) *reinterpret_cast<uint4 *>(static_cast<T *>(p.out_peer[t]) + off) = r;
+    }
+}
+
+
+// The whole exchange in one kernel, in place, for layers whose GEMM is too short to hide a scatter:
+// every rank has stored its full partial product [rows][ld] into its own buffer; rank r LOADS row blocks
+// mb % world == r from every rank's buffer (peer loads, 512 contiguous bytes per warp), adds them in
+// binary32 in rank order, rounds once and STORES the block back into every rank's buffer. Only rank r
+// touches those rows anywhere, so the buffers can be reduced in place; inbound loads and outbound stores
+// use the two directions of the links at the same time.
+struct PullParams {
+    void *buf_peer[8];       // every rank's buffer [rows][ld] (peer mappings; buf_peer[rank] is local)
+    int world, rank;
+    int64_t rows, n, ld;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) allreduce_pull_kernel(const PullParams p) {
+    constexpr int U = 1;                                   // chunks per thread and round (4 measured no faster: the links are the limit)
+    const int64_t chunks_per_row = p.n >> 3, slab_rows = p.rows / p.world, total = slab_rows * chunks_per_row;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t u0 = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; u0 < total; u0 += U * stride) {
+        int64_t off[U];
+        uint4 w[U][8];
+#pragma unroll
+        for (int q = 0; q < U; ++q) {
+            const int64_t u = u0 + q * stride;
+            const int64_t i = u / chunks_per_row, j = (u - i * chunks_per_row) * 8;
+            off[q] = u < total ? (((i >> 7) * p.world + p.rank) * 128 + (i & 127)) * p.ld + j : -1;
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                if (s < p.world && off[q] >= 0)
+                    w[q][s] = *reinterpret_cast<const uint4 *>(static_cast<const T *>(p.buf_peer[s]) + off[q]);
+        }
+#pragma unroll
+        for (int q = 0; q < U; ++q) {
+            if (off[q] < 0) continue;
+            float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                if (s >= p.world) break;
+                const uint32_t v[4] = {w[q][s].x, w[q][s].y, w[q][s].z, w[q][s].w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = pair_to_float2<T>(v[k]);
+                    acc[2 * k] += f.x;
+                    acc[2 * k + 1] += f.y;
+                }
+            }
+            const uint4 r = make_uint4(float2_to_pair<T>(acc[0], acc[1]), float2_to_pair<T>(acc[2], acc[3]),
+                                       float2_to_pair<T>(acc[4], acc[5]), float2_to_pair<T>(acc[6], acc[7]));
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+                if (t < p.world) *reinterpret_cast<uint4 *>(static_cast<T *>(p.buf_peer[t]) + off[q]) = r;
+        }
     }
 }
 
@@ -74,7 +130,7 @@ extern "C" int fos_reduce_gather(const void *staging, void *const *out_peers, in
                                  int64_t n, int64_t ld_staging, int64_t ld_out, int dtype, void *stream_) {
     using namespace fos;
     if (!staging || !out_peers || world < 2 || world > 8 || rank < 0 || rank >= world) return FOS_ERR_INVALID_ARGUMENT;
-    if (slab_rows <= 0 || n <= 0 || ld_staging < n || ld_out < n) return FOS_ERR_INVALID_ARGUMENT;
+    if (slab_rows <= 0 || slab_rows % 128 != 0 || n <= 0 || ld_staging < n || ld_out < n) return FOS_ERR_INVALID_ARGUMENT;
     if (dtype != FOS_BF16 && dtype != FOS_FP16) return FOS_ERR_UNSUPPORTED;
     if (n % 8 != 0 || ld_staging % 8 != 0 || ld_out % 8 != 0) return FOS_ERR_UNSUPPORTED;
     if (reinterpret_cast<uintptr_t>(staging) % 16 != 0) return FOS_ERR_MISALIGNED;
@@ -95,6 +151,32 @@ extern "C" int fos_reduce_gather(const void *staging, void *const *out_peers, in
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (dtype == FOS_BF16) reduce_gather_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
     else reduce_gather_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+    FOS_CUDA_TRY(cudaGetLastError());
+    return FOS_OK;
+}
+
+extern "C" int fos_allreduce_peer(void *const *buf_peers, int world, int rank, int64_t rows, int64_t n, int64_t ld,
+                                  int dtype, void *stream_) {
+    using namespace fos;
+    if (!buf_peers || world < 2 || world > 8 || rank < 0 || rank >= world) return FOS_ERR_INVALID_ARGUMENT;
+    if (rows <= 0 || n <= 0 || ld < n) return FOS_ERR_INVALID_ARGUMENT;
+    if (dtype != FOS_BF16 && dtype != FOS_FP16) return FOS_ERR_UNSUPPORTED;
+    if (rows % (128 * static_cast<int64_t>(world)) != 0 || n % 8 != 0 || ld % 8 != 0) return FOS_ERR_UNSUPPORTED;
+    PullParams p{};
+    for (int i = 0; i < world; ++i) {
+        if (!buf_peers[i]) return FOS_ERR_INVALID_ARGUMENT;
+        if (reinterpret_cast<uintptr_t>(buf_peers[i]) % 16 != 0) return FOS_ERR_MISALIGNED;
+        p.buf_peer[i] = buf_peers[i];
+    }
+    p.world = world; p.rank = rank; p.rows = rows; p.n = n; p.ld = ld;
+    const int st = check_device();
+    if (st != FOS_OK) return st;
+    const int64_t total = (rows / world) * (n >> 3);
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (dtype == FOS_BF16) allreduce_pull_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+    else allreduce_pull_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;
 }

@@ -106,9 +106,10 @@ struct GemmParams {
     int debug;               // FOS_OPT_GEMM_DEBUG bits (timing experiments only; results are wrong)
     int mx;                  // operands are MXFP4: E8M0 scales per 32 values, a 512-byte scale tile spans 128 values of K
     // Row-parallel layers: this rank's partial product is not stored to d but scattered, tile by tile as
-    // the tiles complete, into the staging buffers of the ranks that will reduce them. Rows are cut into
-    // `scatter_world` slabs of `slab_rows`; slab o belongs to rank o, whose staging buffer d_peer[o]
-    // (a peer mapping unless o is this rank) is [world][slab_rows][ldd]; this rank writes plane scatter_rank.
+    // the tiles complete, into the staging buffers of the ranks that will reduce them. Row block mb (128
+    // rows) belongs to rank mb % scatter_world and is block mb / scatter_world of that rank's slab of
+    // `slab_rows` rows; its staging buffer d_peer[o] (a peer mapping unless o is this rank) is
+    // [world][slab_rows][ldd], and this rank writes plane scatter_rank.
     int scatter_world;       // 0: plain store to d
     int scatter_rank;
     int64_t slab_rows;
@@ -365,9 +366,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             tile_coords(t, num_m, num_n, mb, nb);
             const int64_t row = mb * BLOCK_M + quad * 32 + lane, n0 = nb * BLOCK_N + half * COLS;
             if (p.scatter_world > 1) {
-                // the owner of this tile's rows; its buffer's plane `scatter_rank`, addressed by the global row
-                const int o = static_cast<int>((mb * BLOCK_M) / p.slab_rows);
-                out = static_cast<OUT *>(p.d_peer[o]) + (static_cast<int64_t>(p.scatter_rank) - o) * p.slab_rows * p.ldd;
+                // row block mb belongs to rank mb % world (interleaved, so that the peer traffic is spread
+                // over the whole run instead of coming in one burst per slab) and is block mb / world of
+                // that rank's slab; plane `scatter_rank` of its buffer, addressed here by the global row
+                const int o = static_cast<int>(mb % p.scatter_world);
+                const int64_t first = static_cast<int64_t>(p.scatter_rank) * p.slab_rows + (mb / p.scatter_world) * BLOCK_M - mb * BLOCK_M;
+                out = static_cast<OUT *>(p.d_peer[o]) + first * p.ldd;
             }
             const uint32_t acc = tile_i % C::ACC_STAGES, acc_ph = (tile_i / C::ACC_STAGES) & 1u;
             ok = mbar_wait(acc_full_bar + 8 * acc, acc_ph, abort_flag, p.status, 4);

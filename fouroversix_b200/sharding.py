@@ -106,7 +106,8 @@ class TensorParallelLinear(nn.Module):
 
     def __init__(self, weight: torch.Tensor | QuantizedTensor, config: ModuleQuantizationConfig, mode: str, *,
                  group: dist.ProcessGroup | None = None, bias: torch.Tensor | None = None, chunks: int = 4,
-                 comm_sms: int = 32, fused: bool | None = None, matmul_fn: MatmulFn | None = None,
+                 comm_sms: int = 32, fused: bool | None = None, peer_mode: str = "scatter",
+                 matmul_fn: MatmulFn | None = None,
                  quantize_fn: Callable | None = None) -> None:
         super().__init__()
         if mode not in ("column", "row"):
@@ -116,6 +117,18 @@ class TensorParallelLinear(nn.Module):
         # row-parallel exchange through peer memory (scatter from the GEMM's epilogue, then reduce + gather):
         # None = use it when it can be set up, True = require it, False = NCCL all-reduce beside the GEMM
         self.fused = fused
+        # "scatter": the GEMM's epilogue stores its tiles into the owners' staging buffers while it runs,
+        # then the owners reduce and store to every rank (fos_gemm_nvfp4_scatter + fos_reduce_gather);
+        # "pull": plain GEMM into this rank's symmetric buffer, then ONE kernel that loads every rank's rows
+        # of this rank's slab, adds them and stores the sums back to every rank (fos_allreduce_peer).
+        # Either way every link direction carries (world - 1) / world of the output twice; only the scatter
+        # hides half of that behind the GEMM, and only when the GEMM is long enough: on two B200s, 32768
+        # tokens, down_proj (K 14336 per rank) 3.0-3.1 ms with NCCL, 2.7 scatter, 3.0-3.1 pull; o_proj
+        # (K 4096 per rank) 1.50 NCCL, 1.59 scatter (its peer stores hold the short GEMM back), 1.48 pull.
+        # With fused=None the scatter is taken when the GEMM is at least twice as long as its scatter.
+        if peer_mode not in ("pull", "scatter"):
+            raise ValueError("peer_mode must be 'pull' or 'scatter'")
+        self.peer_mode = peer_mode
         self._peer: dict | None = None
         self._matmul = matmul_fn or quantized_matmul
         self._quantize = quantize_fn or quantize
@@ -156,19 +169,23 @@ class TensorParallelLinear(nn.Module):
 
         world = self.world_size
         group = self.group if self.group is not None else dist.group.WORLD
-        staging = symm.empty((world, tokens // world, n_out), dtype=dtype, device=dev)
-        out = symm.empty((tokens, n_out), dtype=dtype, device=dev)
-        h_staging, h_out = symm.rendezvous(staging, group), symm.rendezvous(out, group)
-
         def pointers(handle):
             return (ctypes.c_void_p * world)(*[int(ptr) for ptr in handle.buffer_ptrs])
 
-        self._peer = {"key": key, "staging": staging, "out": out, "h_staging": h_staging, "h_out": h_out,
-                      "staging_ptrs": pointers(h_staging), "out_ptrs": pointers(h_out)}
+        out = symm.empty((tokens, n_out), dtype=dtype, device=dev)
+        h_out = symm.rendezvous(out, group)
+        self._peer = {"key": key, "out": out, "h_out": h_out, "out_ptrs": pointers(h_out)}
+        if self.peer_mode == "scatter":
+            staging = symm.empty((world, tokens // world, n_out), dtype=dtype, device=dev)
+            h_staging = symm.rendezvous(staging, group)
+            self._peer.update(staging=staging, h_staging=h_staging, staging_ptrs=pointers(h_staging))
         return self._peer
 
     def _row_parallel_fused(self, x2d: torch.Tensor, act_cfg: QuantizationConfig) -> torch.Tensor | None:
-        """The exchange over peer memory: the GEMM's epilogue scatters this rank's partial tiles into the
+        """The exchange over peer memory, in one of two forms (`peer_mode`). "pull": the GEMM stores this rank's
+        partial product into its symmetric buffer, a barrier, one kernel loads the rows of this rank's slab from
+        every rank, adds them and stores the sums into every rank's buffer (fos_allreduce_peer), a barrier.
+        "scatter": the GEMM's epilogue scatters this rank's partial tiles into the
         owners' staging buffers while the GEMM runs (fos_gemm_nvfp4_scatter), a barrier, every rank reduces
         its slab and stores it into every rank's output (fos_reduce_gather), a barrier. Returns None when the
         request does not fit (the caller then takes the NCCL path). The result lives in a buffer that the
@@ -183,6 +200,11 @@ class TensorParallelLinear(nn.Module):
                 or self.weight.dtype != DataType.nvfp4 or act_cfg.dtype != DataType.nvfp4
                 or not self.weight.scale_factors_are_in_blackwell_layout):
             return None
+        if self.fused is None:
+            # GEMM time / scatter time ~ K_local * 1.5e-4 * world / (world - 1)  (4 PFLOP/s against 600 GB/s)
+            k_local = self.weight.original_shape[1]
+            if k_local * 1.5e-4 * world / (world - 1) < 2.0:
+                return None
         try:
             buf = self._peer_buffers(tokens, n_out, out_dtype.torch_dtype, x2d.device)
         except Exception:                                  # symmetric memory is not available here
@@ -192,6 +214,15 @@ class TensorParallelLinear(nn.Module):
             return None
         rank = dist.get_rank(self.group)
         xq = self._quantize(x2d, act_cfg)
+        if self.peer_mode == "pull":
+            B200MatmulBackend.quantized_matmul(xq, self.weight, out_dtype=out_dtype, out=buf["out"])
+            buf["h_out"].barrier(channel=0)                # every rank's partial product is complete
+            with torch.cuda.device(x2d.device):
+                _native.check(_native.lib().fos_allreduce_peer(
+                    buf["out_ptrs"], world, rank, tokens, n_out, n_out, _native.elem_code(out_dtype.torch_dtype),
+                    _native.stream_ptr(x2d.device)), "fos_allreduce_peer")
+            buf["h_out"].barrier(channel=0)                # every slab of my buffer holds the sums
+            return buf["out"]
         B200MatmulBackend.quantized_matmul_scatter(xq, self.weight, out_dtype=out_dtype, d_peers=buf["staging_ptrs"],
                                                    world=world, rank=rank)
         buf["h_staging"].barrier(channel=0)                # every rank's plane of my slab has arrived

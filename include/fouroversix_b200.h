@@ -158,14 +158,16 @@ int fos_gemm_mxfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b
  * after each (in stream order; the caller provides it):
  *
  * fos_gemm_nvfp4_scatter: the NVFP4 GEMM of fos_gemm_nvfp4, but the partial product of this rank is not
- *   stored to one buffer: the rows are cut into `world` slabs of m_p / world rows (m_p must be a multiple of
- *   128 * world) and every tile is stored, as it completes, into plane `rank` of the staging buffer of the
- *   rank that owns its slab: d_peers[o] is rank o's buffer [world][m_p / world][ldd] of out_dtype (bf16 or
- *   fp16), mapped into this process (peer memory over NVLink, e.g. torch symmetric memory; d_peers[rank] is
- *   local). d_peers is a HOST array of `world` device pointers, each 32-byte aligned.
+ *   stored to one buffer: row block mb (128 rows) belongs to rank mb % world (interleaved, so that the
+ *   peer traffic is spread over the whole run) and is block mb / world of that rank's slab of m_p / world
+ *   rows (m_p must be a multiple of 128 * world); every tile is stored, as it completes, into plane `rank`
+ *   of its owner's staging buffer: d_peers[o] is rank o's buffer [world][m_p / world][ldd] of out_dtype
+ *   (bf16 or fp16), mapped into this process (peer memory over NVLink, e.g. torch symmetric memory;
+ *   d_peers[rank] is local). d_peers is a HOST array of `world` device pointers, each 32-byte aligned.
  * fos_reduce_gather: rank `rank` adds the `world` planes of its own staging buffer in binary32 (rank
- *   order), rounds once to `dtype` and stores rows rank * slab_rows .. of the result into out_peers[t] for
- *   every t (each [world * slab_rows][ld_out], 16-byte aligned; n, ld_staging and ld_out multiples of 8).
+ *   order), rounds once to `dtype` and stores the rows of its slab (row blocks mb % world == rank) of the
+ *   result into out_peers[t] for every t (each [world * slab_rows][ld_out], 16-byte aligned; slab_rows a
+ *   multiple of 128; n, ld_staging and ld_out multiples of 8).
  *
  * Together they are an all-reduce of the partial products whose first half rides on the GEMM's epilogue.
  * They stand where the reference relies on vLLM's tensor-parallel all-reduce after a row-parallel layer
@@ -178,6 +180,17 @@ int fos_gemm_nvfp4_scatter(const uint8_t *a_codes, const uint8_t *a_sf, const ui
                            int64_t ldd, int32_t *status, void *stream);
 int fos_reduce_gather(const void *staging, void *const *out_peers, int world, int rank, int64_t slab_rows,
                       int64_t n, int64_t ld_staging, int64_t ld_out, int dtype, void *stream);
+
+/*
+ * The same exchange as ONE kernel after a plain GEMM, in place, for layers whose GEMM is too short to hide a
+ * scatter behind: every rank has stored its full partial product [rows][ld] (rows a multiple of 128 * world;
+ * n and ld multiples of 8; bf16 or fp16) into its own buffer buf_peers[rank]; rank `rank` loads the row blocks
+ * mb % world == rank from every rank's buffer (peer loads), adds them in binary32 in rank order, rounds
+ * once and stores them back into every rank's buffer (peer stores). Loads and stores use the two directions
+ * of the links at once. A barrier between the ranks (in stream order) is needed before and after.
+ */
+int fos_allreduce_peer(void *const *buf_peers, int world, int rank, int64_t rows, int64_t n, int64_t ld,
+                       int dtype, void *stream);
 
 /*
  * D[m, n] = alpha[0] * sum_k A[m, k] * B[n, k] for operands in FOS_IF4 or FOS_NVFP4 (any mix),

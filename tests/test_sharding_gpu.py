@@ -43,13 +43,20 @@ def _worker(rank: int, world: int, port: int, results):
         up = TensorParallelLinear(shard_linear_weight(w_up, "column", rank, world), cfg, "column")
         w_down_shard = shard_linear_weight(w_down, "row", rank, world).contiguous()
         down = TensorParallelLinear(w_down_shard, cfg, "row", chunks=4, fused=False)      # NCCL beside the GEMM
-        down_peer = TensorParallelLinear(w_down_shard, cfg, "row")                         # peer-memory exchange if it can be set up
+        down_peer, down_scatter = (TensorParallelLinear(w_down_shard, cfg, "row", fused=True, peer_mode=mode)
+                                   for mode in ("pull", "scatter"))                         # the exchange over peer memory, both forms
         h = up(x)
         y = down(h)
-        y_peer = down_peer(h).clone()
-        y_peer_again = down_peer(h).clone()                # the buffers are reused
+        try:
+            y_peer = down_peer(h).clone()
+            y_peer_again = down_peer(h).clone()            # the buffers are reused
+            y_scatter = down_scatter(h).clone()
+            peer_used = True
+        except (RuntimeError, OSError, AttributeError, ImportError) as exc:   # symmetric memory cannot be set up on this machine
+            print(f"rank {rank}: peer-memory exchange unavailable: {exc}")
+            y_peer = y_peer_again = y_scatter = y.clone()
+            peer_used = False
         torch.cuda.synchronize()
-        peer_used = down_peer.fused is not False
 
         # the same on this GPU alone: per-shard products in bf16 (what each rank contributes), summed
         want = torch.zeros(tokens, hidden, dtype=torch.float32, device=dev)
@@ -58,7 +65,8 @@ def _worker(rank: int, world: int, port: int, results):
             want += fos.quantized_matmul(h_r, shard_linear_weight(w_down, "row", r, world).contiguous()).float()
         err = ((y.float() - want).abs().max() / want.abs().max()).item()
         peer_err = ((y_peer.float() - want).abs().max() / want.abs().max()).item()
-        peer_repeatable = torch.equal(y_peer, y_peer_again)
+        # both forms add the same bf16 partials in the same order
+        peer_repeatable = torch.equal(y_peer, y_peer_again) and torch.equal(y_peer, y_scatter)
         # every rank must hold the same bits: only a slab's owner computes it
         gathered = [torch.empty_like(y_peer) for _ in range(world)]
         dist.all_gather(gathered, y_peer)
