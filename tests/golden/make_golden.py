@@ -65,7 +65,9 @@ def make_inputs() -> dict[str, torch.Tensor]:
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit(__doc__)
+    ref_root = sys.argv[1]
     fos = import_reference(ref_root)
     from fouroversix import QuantizationConfig, dequantize, quantize, quantized_matmul
 

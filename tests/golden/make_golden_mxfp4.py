@@ -23,7 +23,9 @@ from make_golden import import_reference  # noqa: E402
 
 
 def main() -> None:
-    import_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit(__doc__)
+    import_reference(sys.argv[1])
     from fouroversix import QuantizationConfig, dequantize, quantize, quantized_matmul
     from fouroversix.utils import DataType
 

@@ -25,7 +25,9 @@ from make_golden import import_reference  # noqa: E402
 
 
 def main() -> None:
-    import_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit(__doc__)
+    import_reference(sys.argv[1])
     from fouroversix.quantize.pytorch.reference import quantize as ref_quantize
     from fouroversix.quantize.utils import get_rht_matrix
     from fouroversix.utils import DataType, ScaleRule
