@@ -115,7 +115,8 @@ class TensorParallelLinear(nn.Module):
         self.mode, self.config, self.group, self.chunks = mode, config, group, max(1, chunks)
         self.comm_sms = max(0, comm_sms)
         # row-parallel exchange through peer memory (scatter from the GEMM's epilogue, then reduce + gather):
-        # None = use it when it can be set up, True = require it, False = NCCL all-reduce beside the GEMM
+        # None = use it when the layer's shape favours it (below) and it can be set up, True = require it,
+        # False = NCCL all-reduce beside the GEMM
         self.fused = fused
         # "scatter": the GEMM's epilogue stores its tiles into the owners' staging buffers while it runs,
         # then the owners reduce and store to every rank (fos_gemm_nvfp4_scatter + fos_reduce_gather);
