@@ -122,3 +122,24 @@ def test_column_then_row_parallel_matches_unsharded_sum():
         assert shape == (512, 256)
         assert same, "ranks disagree after the all-reduce"
         assert err < 1e-5, err
+
+
+def test_layer_rejects_unknown_exchange_and_column_slices_follow_the_block_size():
+    w = torch.randn(128, 128).bfloat16()
+    with pytest.raises(ValueError, match="peer_mode"):
+        TensorParallelLinear(w, fos.ModuleQuantizationConfig(), "row", peer_mode="ring", quantize_fn=cpu_quantize)
+    with pytest.raises(ValueError, match="mode"):
+        TensorParallelLinear(w, fos.ModuleQuantizationConfig(), "diagonal", quantize_fn=cpu_quantize)
+    # MXFP4: a 512-byte scale tile covers 128 columns, so column slices come in multiples of 128
+    ref = fos_oracle.quantize(torch.randn(128, 256).bfloat16(), dtype="mxfp4", scale_rule="static_6")
+    q = fos.QuantizedTensor(ref.values, ref.scale_factors.view(torch.float8_e8m0fnu), ref.amax, "mxfp4", ref.original_shape,
+                            "static_6", "nearest", ref.padded_shape, scale_factors_are_in_blackwell_layout=True)
+    right = slice_cols(q, 128, 256)
+    assert right.padded_shape == (128, 128) and right.scale_factors.numel() == 128 * 128 // 32
+    assert torch.equal(right.values, q.values[:, 64:])
+    full = fos_oracle.dequantize_raw(q.values, q.scale_factors, q.amax, "mxfp4", "static_6", (128, 256), torch.float32, tiled=True)
+    part = fos_oracle.dequantize_raw(right.values, right.scale_factors, right.amax, "mxfp4", "static_6", (128, 128), torch.float32,
+                                     tiled=True)
+    assert torch.equal(part, full[:, 128:])
+    with pytest.raises(ValueError, match="multiples of 128"):
+        slice_cols(q, 64, 128)
