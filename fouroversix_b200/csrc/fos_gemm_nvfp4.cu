@@ -273,10 +273,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             if (f_t >= num_tiles) return;
             // two tensor copies per stage: [K-blocks kb0 .. kb0+3] x [one / N_GROUPS row groups] of
             // 512-byte tiles; what lies beyond K or N is zero-filled and still counted
-            // (MXFP4: a tile spans two K-blocks, a stage uses the first two tiles of the box)
+            // (MXFP4: a tile spans two K-blocks, so the box of its maps is two tiles per group)
             const int kb0 = static_cast<int>(f_kt * (p.mx ? KB_PER_STAGE / 2 : KB_PER_STAGE));
             const uint32_t dst = sf_base + slot * C::SF_SLOT_BYTES, bar = sf_full_bar + 8 * slot;
-            mbar_expect_tx(bar, C::SF_SLOT_BYTES);
+            mbar_expect_tx(bar, p.mx ? C::SF_SLOT_BYTES / 2 : C::SF_SLOT_BYTES);   // MXFP4 maps fetch two tiles per group
             tma_load_3d(dst, &map_sfa, 0, kb0, a_group, bar);
             tma_load_3d(dst + SFA_BYTES, &map_sfb, 0, kb0, b_group, bar);
             if (++slot == C::SF_SLOTS) slot = 0;
@@ -450,7 +450,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 tc_fence_after();
                 const uint32_t src = sf_base + j * C::SF_SLOT_BYTES, dst = tmem_base + SF_COL0 + j * C::SF_STAGE_COLS;
                 // tiles: 32 rows of 16 bytes, 8-row groups 128 bytes apart, no swizzle
-                // (MXFP4: a tile spans two K-blocks, so only the first half of the tiles is in use)
+                // (MXFP4: a tile spans two K-blocks, so a stage has two tiles per group)
                 const int ntile = p.mx ? KB_PER_STAGE / 2 : KB_PER_STAGE;
 #pragma unroll
                 for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
@@ -459,7 +459,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 #pragma unroll
                     for (int g = 0; g < C::N_GROUPS; ++g)
                         tc_copy_sf(dst + 16 + (BLOCK_N / 32) * kb + 4 * g,
-                                   smem_desc(src + SFA_BYTES + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES, 0, 128, 0));
+                                   smem_desc(src + SFA_BYTES + (g * ntile + kb) * SF_TILE_BYTES, 0, 128, 0));
                 }
                 tc_commit(sf_ready_bar + 8 * j);     // arrives when the copies above are done
                 if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
@@ -502,7 +502,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         const int kb = col / (BLOCK_N / 32), g = (col % (BLOCK_N / 32)) / 4;
                         uint4 v = make_uint4(0u, 0u, 0u, 0u);
                         if (kb < nkb && n0 + 128 * g < p.n_p)
-                            v = lds_16(sfb_smem + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES);
+                            v = lds_16(sfb_smem + (g * (p.mx ? KB_PER_STAGE / 2 : KB_PER_STAGE) + kb) * SF_TILE_BYTES);
                         r[4 * q] = v.x; r[4 * q + 1] = v.y; r[4 * q + 2] = v.z; r[4 * q + 3] = v.w;
                     }
                     tc_store_16cols(slot + 16 + half * 16, r);
@@ -852,13 +852,15 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
 // ---------------------------------------------------------------------------- host side
 
-// Scale tiles as a 3-D tensor [row groups][K-blocks][512 bytes]; box = `groups` x 4 K-blocks.
-int make_scale_map(CUtensorMap *map, const uint8_t *sf, int64_t row_groups, int64_t k_blocks, int groups) {
+// Scale tiles as a 3-D tensor [row groups][tiles along K][512 bytes]; box = `groups` x the tiles of one stage
+// (four; two for MXFP4, whose tiles span two K-blocks).
+int make_scale_map(CUtensorMap *map, const uint8_t *sf, int64_t row_groups, int64_t k_blocks, int groups,
+                   int tiles_per_stage = KB_PER_STAGE) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return FOS_ERR_CUDA;
     cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(k_blocks), static_cast<cuuint64_t>(row_groups)};
     cuuint64_t strides[2] = {512, static_cast<cuuint64_t>(k_blocks) * 512};
-    cuuint32_t box[3] = {128, static_cast<cuuint32_t>(KB_PER_STAGE), static_cast<cuuint32_t>(groups)};
+    cuuint32_t box[3] = {128, static_cast<cuuint32_t>(tiles_per_stage), static_cast<cuuint32_t>(groups)};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t *>(sf), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1022,8 +1024,9 @@ static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uin
     if ((st = make_operand_map(&map_a, a_codes, m_p, k_p / 2, BLOCK_M)) != FOS_OK) return st;
     if ((st = make_operand_map(&map_b, b_codes, n_p, k_p / 2, wide ? 256 : 128)) != FOS_OK) return st;
     CUtensorMap map_sfa, map_sfb;
-    if ((st = make_scale_map(&map_sfa, a_sf, m_p / 128, sf_k_tiles, 1)) != FOS_OK) return st;
-    if ((st = make_scale_map(&map_sfb, b_sf, n_p / 128, sf_k_tiles, wide ? 2 : 1)) != FOS_OK) return st;
+    const int sf_box_k = mx ? KB_PER_STAGE / 2 : KB_PER_STAGE;
+    if ((st = make_scale_map(&map_sfa, a_sf, m_p / 128, sf_k_tiles, 1, sf_box_k)) != FOS_OK) return st;
+    if ((st = make_scale_map(&map_sfb, b_sf, n_p / 128, sf_k_tiles, wide ? 2 : 1, sf_box_k)) != FOS_OK) return st;
     return wide ? launch_out<256>(map_a, map_b, map_sfa, map_sfb, p, sms, stream)
                 : launch_out<128>(map_a, map_b, map_sfa, map_sfb, p, sms, stream);
 }
