@@ -949,7 +949,7 @@ extern "C" int fos_set_option(int key, int value) {
         fos::g_gemm_max_ctas = value;
         return FOS_OK;
     }
-    if (key == FOS_OPT_QUANTIZE_VARIANT && (value == 0 || value == 1)) {
+    if (key == FOS_OPT_QUANTIZE_VARIANT && value >= 0 && value <= 2) {
         fos::g_quantize_variant = value;
         return FOS_OK;
     }

@@ -464,7 +464,9 @@ __device__ __forceinline__ float4 scale_entry(uint32_t sfb, const TensorConsts &
     const float r = __frcp_rn(__fmul_rn(tc.decode, s));
     const float g = s * tc.amax * (1.0f / 1536.0f);
     const bool usable = filter_allowed && sfb >= 8u && r >= 0x1p-16f;
-    return make_float4(s, r, g, usable ? g * g : -1.0f);
+    // third field: this scale's share of the pre-filter's tolerance, 1.5 * 188u * g^2, or +infinity where the
+    // pre-filter must not be used: a tolerance of infinity leaves every block undecided (quantize_rows_mse_kernel)
+    return make_float4(s, r, usable ? (0x1p-24f * 1.5f * 188.0f) * (g * g) : __int_as_float(0x7f800000), usable ? g * g : -1.0f);
 }
 
 // ---- stochastic rounding (RoundStyle.stochastic) ----
@@ -1006,6 +1008,13 @@ quantize_rows_kernel(const QuantParams p) {
 // Needs x 16-byte aligned with a row stride that is a multiple of 16 bytes.
 
 constexpr int FEED_TILE_ROWS = 128;
+#ifndef FOS_UNPACK_BY_ADD
+#define FOS_UNPACK_BY_ADD 1
+#endif
+#ifndef FOS_EARLY_PDL
+#define FOS_EARLY_PDL 0
+#endif
+
 #ifndef FOS_FEED_STAGES
 #define FOS_FEED_STAGES 4
 #endif
@@ -1190,6 +1199,273 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
 }
 
 // ------------------------------------------------------------------------------------
+// NVFP4 4/6 with the mean-squared-error rule, 1-D blocks, untransposed: the default configuration
+// ------------------------------------------------------------------------------------
+//
+// The ring, the thread-to-block assignment and the arithmetic of quantize_rows_tma_kernel, with the
+// instruction count of the common case cut down:
+//   * the producer thread, which computes every tile's coordinates anyway, leaves the byte offsets
+//     of the tile's codes and scales next to the stage (16 bytes per stage); the consumers read
+//     them with one broadcast load instead of keeping tile coordinates of their own up to date;
+//   * the pre-filter runs without a branch: the per-scale table carries each scale's share of the
+//     tolerance, and that share is +infinity for scales the pre-filter must not be used with, so
+//     "not eligible" is just one more way of being undecided;
+//   * one vote per block sends the whole warp through quantize_block (pre-filter again, then the
+//     cooperative exact evaluation, then the per-lane exact sequence: same results, block by
+//     block) when any of its 32 blocks is undecided.
+// Bit-identical to quantize_rows_tma_kernel<T, KIND_ADAPTIVE>: a decided block takes the decision
+// that kernel takes from the same sums, an undecided one goes through that kernel's code.
+
+// The reference's exact 4-versus-6 decision for one NVFP4 block held by one lane (any rule): what
+// quantize_block does when neither the pre-filter nor the cooperative evaluation applies. Kept out
+// of line: it runs for blocks with a zero or subnormal scale (padding, all-zero blocks) and in
+// exact-only runs, under divergence, and the hot loop should not carry its code.
+struct Block16 { float v[16]; };
+__device__ __noinline__ uint4 exact_pick_nvfp4(const Block16 b, float s_a, float r_a, float s_b, float r_b, float amax,
+                                               int rule, uint32_t sfb_a, uint32_t sfb_b) {
+    uint32_t lo_a = 0u, hi_a = 0u, lo_b = 0u, hi_b = 0u;
+    if (s_a != 0.0f) encode_e2m1(b.v, r_a, true, lo_a, hi_a);
+    if (s_b != 0.0f) encode_e2m1(b.v, r_b, true, lo_b, hi_b);
+    float e[16];
+    exact_error_terms<false>(b.v, lo_b, hi_b, s_b, amax, 1536.0f, rule, e);
+    const float err_b = rule == FOS_RULE_ABS_MAX ? max16(e) : ordered_sum16(e);
+    exact_error_terms<false>(b.v, lo_a, hi_a, s_a, amax, 1536.0f, rule, e);
+    const float err_a = rule == FOS_RULE_ABS_MAX ? max16(e) : ordered_sum16(e);
+    const bool pick_b = err_b < err_a;
+    return make_uint4(pick_b ? lo_b : lo_a, pick_b ? hi_b : hi_a, pick_b ? sfb_b : sfb_a, 0u);
+}
+
+// The reference's exact mean-squared errors of one block under both candidates, evaluated by the
+// whole warp: lane 16c + i takes element i under candidate c, the 16 terms are added in the
+// reference's order with shuffles. `src` is the lane that owns the block; every lane gets the
+// verdict "the 4 candidate wins". `coop` is this warp's exchange buffer (20 floats).
+__device__ __forceinline__ bool coop_pick_nvfp4(const float (&v)[16], float s_a, float r_a, float s_b, float r_b,
+                                                float amax, int src, int lane, float *coop) {
+    if (lane == src) {
+        float4 *x4 = reinterpret_cast<float4 *>(coop);
+        x4[0] = make_float4(v[0], v[1], v[2], v[3]);
+        x4[1] = make_float4(v[4], v[5], v[6], v[7]);
+        x4[2] = make_float4(v[8], v[9], v[10], v[11]);
+        x4[3] = make_float4(v[12], v[13], v[14], v[15]);
+        x4[4] = make_float4(s_a, r_a, s_b, r_b);
+    }
+    __syncwarp();
+    const int cand = lane >> 4, i = lane & 15;
+    const float x = coop[i];
+    const float s = coop[16 + 2 * cand], r = coop[17 + 2 * cand];
+    const float2 q = e2m1x2_to_float2(cvt_e2m1x2(0.0f, __fmaf_rn(x, r, 0.0f)));
+    const float d = __fsub_rn(__fdiv_rn(__fmul_rn(__fmul_rn(q.x, s), amax), 1536.0f), x);
+    const float e = __fmul_rn(d, d);
+    const float p = __fadd_rn(e, __shfl_down_sync(FULL, e, 8));      // valid in lanes with i < 8
+    float total = __shfl_sync(FULL, p, cand * 16);
+#pragma unroll
+    for (int k = 1; k < 8; ++k) total = __fadd_rn(total, __shfl_sync(FULL, p, cand * 16 + k));
+    const float exact_a = __shfl_sync(FULL, total, 0), exact_b = __shfl_sync(FULL, total, 16);
+    __syncwarp();
+    return exact_b < exact_a;
+}
+
+// Two 16-bit elements -> floats. bf16: the mixed-precision add x + (-0.0) is exact for every x,
+// keeps the sign of a zero, and runs on the FMA pipe; shifting and masking would run on the ALU
+// pipe, which this kernel saturates.
+template <typename T> __device__ __forceinline__ void unpack2_fma(uint32_t w, float &lo, float &hi) {
+#if FOS_UNPACK_BY_ADD
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        asm("{ .reg .b16 l, h;\n"
+            "mov.b32 {l, h}, %2;\n"
+            "add.rn.f32.bf16 %0, l, 0f80000000;\n"
+            "add.rn.f32.bf16 %1, h, 0f80000000; }" : "=f"(lo), "=f"(hi) : "r"(w));
+        return;
+    }
+#endif
+    const float2 f = unpack2<T>(w);
+    lo = f.x;
+    hi = f.y;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(FEED_THREADS, FOS_FEED_CTAS)
+quantize_rows_mse_kernel(const __grid_constant__ CUtensorMap map_x, const QuantParams p) {
+    extern __shared__ uint8_t feed_smem_raw[];
+    __shared__ float4 lut[128];
+    __shared__ __align__(16) float coop[FEED_CONSUMERS / 32][20];
+    __shared__ __align__(16) longlong2 tile_meta[FEED_STAGES];     // per stage: byte offsets of the tile's codes and scales
+    __shared__ __align__(8) uint64_t full_bar[FEED_STAGES], empty_bar[FEED_STAGES];
+    __shared__ int abort_flag;
+
+    const uint32_t stage0 = (smem_u32(feed_smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_c = static_cast<int>(p.cols_p >> 6), tiles_r = static_cast<int>(p.rows_p >> 7);
+    const int64_t n_tiles = static_cast<int64_t>(tiles_c) * tiles_r;
+    const int64_t code_ld = p.cols_p >> 1, n_cb = p.cols_p >> 4;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+#pragma unroll
+        for (int s = 0; s < FEED_STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), FEED_CONSUMERS / 32);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+#if FOS_EARLY_PDL
+    // every CTA of this grid is resident by now (the grid is at most one wave), so a dependent grid can
+    // be admitted already: its CTAs take the slots of CTAs of this grid as they exit
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+
+    // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ... in row-major tile order
+    const int my_tiles = static_cast<int>((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
+
+    if (warp == FEED_CONSUMERS / 32) {
+        // ---------------- producer ----------------
+        if (lane != 0) return;
+        const int step_r = static_cast<int>(gridDim.x) / tiles_c, step_c = static_cast<int>(gridDim.x) % tiles_c;
+        int tr = static_cast<int>(blockIdx.x) / tiles_c, tc_ = static_cast<int>(blockIdx.x) % tiles_c;
+        int64_t tile = blockIdx.x;
+        if (!p.x_is_ready) asm volatile("griddepcontrol.wait;" ::: "memory");
+        int issued = 0, s = 0;
+        uint32_t parity = 1;   // of the "stage is free" barrier; the first round finds every stage free
+        for (; issued < my_tiles; ++issued) {
+            if (issued >= FEED_STAGES && !mbar_wait(smem_u32(&empty_bar[s]), parity, &abort_flag, &g_wait_failures, 8))
+                break;
+            // (the arrive below releases this store to the consumers that acquire the barrier's phase)
+            tile_meta[s] = make_longlong2(static_cast<int64_t>(tr) * 128 * code_ld + tc_ * 32,
+                                          p.sf_tiled ? tile * 512 : static_cast<int64_t>(tr) * 128 * n_cb + tc_ * 4);
+            mbar_expect_tx(smem_u32(&full_bar[s]), FEED_STAGE_BYTES);
+            tma_load_2d(stage0 + s * FEED_STAGE_BYTES, &map_x, tc_ * 128, tr * FEED_TILE_ROWS, smem_u32(&full_bar[s]));
+            if (++s == FEED_STAGES) { s = 0; parity ^= 1u; }
+            tile += gridDim.x;
+            tr += step_r;
+            tc_ += step_c;
+            if (tc_ >= tiles_c) { tc_ -= tiles_c; ++tr; }
+        }
+        // stay until every copy this thread issued has landed: shared memory must outlive them
+        for (int j = issued > FEED_STAGES ? issued - FEED_STAGES : 0; j < issued; ++j) {
+            const uint32_t bar = smem_u32(&full_bar[j % FEED_STAGES]);
+            const uint32_t landed = static_cast<uint32_t>(j / FEED_STAGES) & 1u;
+            const unsigned long long t0 = global_timer_ns();
+            while (!mbar_try_wait(bar, landed) && global_timer_ns() - t0 < WAIT_LIMIT_NS) {}
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const TensorConsts tc = tensor_consts<KIND_ADAPTIVE>(*reinterpret_cast<const volatile float *>(p.amax), p.rule);
+    if (p.amax_store != nullptr && threadIdx.x == 0 && blockIdx.x == 0) *p.amax_store = tc.amax;
+    if (threadIdx.x < 128)
+        lut[threadIdx.x] = scale_entry(threadIdx.x, tc, p.rule == FOS_RULE_MSE && !p.exact_only && tc.filter_ok);
+    asm volatile("bar.sync 1, %0;" ::"n"(FEED_CONSUMERS) : "memory");
+
+    // lane l of warp w owns rows 8w + l/4 and 64 + 8w + l/4 of the tile and block column l%4
+    const int q = lane >> 2, cb = lane & 3;
+    const int row_in_tile = warp * 8 + q;
+    uint32_t piece0 = stage0 + static_cast<uint32_t>(row_in_tile * 128 + ((2 * cb) ^ (row_in_tile & 7)) * 16);
+    uint32_t piece1 = stage0 + static_cast<uint32_t>(row_in_tile * 128 + ((2 * cb + 1) ^ (row_in_tile & 7)) * 16);
+    uint8_t *code_ptr = p.codes + row_in_tile * code_ld + cb * 8;
+    uint8_t *sf_ptr = p.sf + (p.sf_tiled ? (row_in_tile & 31) * 16 + (row_in_tile >> 5) * 4 + cb : row_in_tile * n_cb + cb);
+    uint32_t lut_base = smem_u32(lut), meta_addr = smem_u32(tile_meta), full_addr = smem_u32(full_bar), empty_addr = smem_u32(empty_bar);
+    asm volatile("" : "+r"(piece0), "+r"(piece1), "+l"(code_ptr), "+l"(sf_ptr), "+r"(lut_base));
+    const int64_t code_half = 64 * code_ld, sf_half = p.sf_tiled ? 8 : 64 * n_cb;
+    const float encode0 = tc.encode0;
+    const int rule = p.rule;
+
+    uint32_t s_off = 0, s_idx = 0, parity = 0;
+    for (int k = 0; k < my_tiles; ++k) {
+        if (!mbar_wait(full_addr + 8 * s_idx, parity, &abort_flag, &g_wait_failures, 9)) break;
+        int64_t code_off, sf_off;
+        asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(code_off), "=l"(sf_off) : "r"(meta_addr + 16 * s_idx));
+        uint8_t *codes = code_ptr + code_off;
+        uint8_t *sf = sf_ptr + sf_off;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint4 a = lds_16(piece0 + s_off + j * 64 * 128);
+            const uint4 b = lds_16(piece1 + s_off + j * 64 * 128);
+            const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) unpack2_fma<T>(w[i], v[2 * i], v[2 * i + 1]);
+            float bmax = fmaxf(fabsf(v[0]), fabsf(v[1]));
+#pragma unroll
+            for (int i = 2; i < 16; i += 2) bmax = fmaxf(fmaxf(bmax, fabsf(v[i])), fabsf(v[i + 1]));
+            const float hp = __fmul_rn(div6_exact(bmax), encode0);
+            const uint32_t both = cvt_e4m3x2(__fmul_rn(hp, 1.5f), hp);   // "4" candidate in the upper byte
+            float4 ea, eb;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(ea.x), "=f"(ea.y), "=f"(ea.z), "=f"(ea.w)
+                         : "r"(lut_base + ((both & 0xffu) << 4)));
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(eb.x), "=f"(eb.y), "=f"(eb.z), "=f"(eb.w)
+                         : "r"(lut_base + ((both >> 8) << 4)));
+            // both candidates: codes, residuals t = q - x*r, sums of t^2 (see quantize_block for the bound)
+            const uint64_t ra2 = pack2(ea.y, ea.y), rb2 = pack2(eb.y, eb.y);
+            uint64_t acc_a = pack2(0.0f, 0.0f), acc_b = acc_a;
+            uint32_t ca[2], cbk[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float ta[8], tb[8];
+                ca[h] = encode8_with_residuals(&v[8 * h], ra2, ta);
+                cbk[h] = encode8_with_residuals(&v[8 * h], rb2, tb);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint64_t pa = pack2(ta[2 * i], ta[2 * i + 1]), pb = pack2(tb[2 * i], tb[2 * i + 1]);
+                    acc_a = fma2(pa, pa, acc_a);
+                    acc_b = fma2(pb, pb, acc_b);
+                }
+            }
+            float a0, a1, b0, b1;
+            unpack2f(acc_a, a0, a1);
+            unpack2f(acc_b, b0, b1);
+            const float err_a = (a0 + a1) * ea.w, err_b = (b0 + b1) * eb.w;     // times G^2
+            const float tau = fmaf(0x1p-24f * 1.5f * 228.0f, err_a + err_b, ea.z + eb.z);
+            const float diff = err_b - err_a;
+            const bool pick_fast = diff < 0.0f;
+            uint32_t lo = pick_fast ? cbk[0] : ca[0], hi = pick_fast ? cbk[1] : ca[1];
+            uint32_t sf_byte = pick_fast ? both >> 8 : both & 0xffu;
+            const bool undecided = !(fabsf(diff) > tau);
+            if (__any_sync(FULL, undecided)) {
+                // Undecided blocks whose scales the pre-filter accepts (two normal E4M3 numbers) are
+                // re-decided exactly by the whole warp, one block at a time; the others (zero or
+                // subnormal scale, exact-only run, amax out of range) take the per-lane exact sequence.
+                const bool coop_ok = fminf(ea.w, eb.w) >= 0.0f;
+                unsigned pending = __ballot_sync(FULL, undecided && coop_ok);
+#ifdef FOS_COUNT_SLOW
+                if (lane == 0) atomicAdd(&g_wait_failures, FOS_COUNT_SLOW == 1 ? 1 : __popc(pending));
+#endif
+                while (pending) {
+                    const int src = __ffs(pending) - 1;
+                    pending &= pending - 1;
+                    const bool b_wins = coop_pick_nvfp4(v, ea.x, ea.y, eb.x, eb.y, tc.amax, src, lane, coop[warp]);
+                    if (lane == src) {
+                        lo = b_wins ? cbk[0] : ca[0];
+                        hi = b_wins ? cbk[1] : ca[1];
+                        sf_byte = b_wins ? both >> 8 : both & 0xffu;
+                    }
+                }
+                if (undecided && !coop_ok) {
+                    Block16 blk;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) blk.v[i] = v[i];
+                    const uint4 r = exact_pick_nvfp4(blk, ea.x, ea.y, eb.x, eb.y, tc.amax, rule, both & 0xffu, both >> 8);
+                    lo = r.x;
+                    hi = r.y;
+                    sf_byte = r.z;
+                }
+            }
+            *reinterpret_cast<uint2 *>(codes + j * code_half) = make_uint2(lo, hi);
+            sf[j * sf_half] = static_cast<uint8_t>(sf_byte);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_addr + 8 * s_idx);
+        s_off += FEED_STAGE_BYTES;
+        if (++s_idx == FEED_STAGES) { s_idx = 0; s_off = 0; parity ^= 1u; }
+    }
+#if !FOS_EARLY_PDL
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+
+// ------------------------------------------------------------------------------------
 // transposed input, 1-D blocks, fed by the TMA unit
 // ------------------------------------------------------------------------------------
 //
@@ -1331,7 +1607,7 @@ inline bool make_x_map(CUtensorMap *map, const QuantParams &p, bool transposed) 
 }
 
 // Launches the TMA-fed kernel when x qualifies; *launched tells whether it did.
-template <typename T, int KIND, bool TRANSPOSED, bool FAKE, bool TWO_D, bool EXTRAS>
+template <typename T, int KIND, bool TRANSPOSED, bool FAKE, bool TWO_D, bool EXTRAS, bool LEAN = false>
 cudaError_t launch_rows_tma_impl(const QuantParams &p, cudaStream_t stream, bool *launched) {
     *launched = false;
     if (reinterpret_cast<uintptr_t>(p.x) % 16 != 0 || (p.ld * 2) % 16 != 0) return cudaSuccess;
@@ -1340,7 +1616,8 @@ cudaError_t launch_rows_tma_impl(const QuantParams &p, cudaStream_t stream, bool
     if (p.cols * 2 >= (int64_t(1) << 31) || p.rows >= (int64_t(1) << 31) || p.ld * 2 >= (int64_t(1) << 40)) return cudaSuccess;
     CUtensorMap map;
     if (!make_x_map(&map, p, TRANSPOSED)) return cudaSuccess;
-    auto kernel = TRANSPOSED ? quantize_cols_tma_kernel<T, KIND, TWO_D, EXTRAS> : quantize_rows_tma_kernel<T, KIND, FAKE, TWO_D, EXTRAS>;
+    auto kernel = LEAN ? quantize_rows_mse_kernel<T>
+                       : (TRANSPOSED ? quantize_cols_tma_kernel<T, KIND, TWO_D, EXTRAS> : quantize_rows_tma_kernel<T, KIND, FAKE, TWO_D, EXTRAS>);
     static int ctas_per_sm[64] = {};
     static int sm_count[64] = {};
     int dev = 0;
@@ -1388,6 +1665,13 @@ template <typename T, int KIND>
 cudaError_t launch_rows(const QuantParams &p, cudaStream_t stream) {
     if (g_quantize_variant != 1) {
         bool launched = false;
+        if constexpr (KIND == KIND_ADAPTIVE) {
+            // the default configuration (mean-squared error, round to nearest, no rotation) has a kernel of its own
+            if (p.rule == FOS_RULE_MSE && !p.rht && !p.stochastic && g_quantize_variant != 2) {
+                const cudaError_t e = launch_rows_tma_impl<T, KIND, false, false, false, false, true>(p, stream, &launched);
+                if (e != cudaSuccess || launched) return e;
+            }
+        }
         const cudaError_t e = launch_rows_tma<T, KIND, false>(p, stream, &launched);
         if (e != cudaSuccess || launched) return e;
     }

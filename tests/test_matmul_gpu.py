@@ -188,6 +188,35 @@ def test_full_size_configs(name, m, n, k, rule):
     assert torch.equal(out2.float(), out.float() * 2)
 
 
+# the linear layers of a Llama-3-70B-shaped decoder block (hidden 8192, MLP 28672, grouped-query qkv 10240):
+# out features N, in features K; gate_proj and up_proj have the same shape
+DECODER_LAYERS = [("qkv_proj", 10240, 8192), ("o_proj", 8192, 8192), ("gate_up_proj", 28672, 8192),
+                  ("down_proj", 8192, 28672)]
+
+
+@pytest.mark.parametrize(("name", "n", "k"), DECODER_LAYERS)
+def test_decoder_layer_shapes_against_oracle(oracle, name, n, k):
+    """Dynamic 4/6 activation quantization + 4/6 weights + GEMM at the decoder-stack layer shapes, on a
+    2048-token slice: packed operands bit for bit against the oracle, the product against the oracle's
+    matmul (the reference's 0.1 % bar of tests/test_matmul.py:15, scaled by sqrt(K / 1024) for the longer
+    fp32 sums) and within 1e-2 of the fp32 product of the dequantized operands."""
+    tokens = 2048
+    g = torch.Generator().manual_seed(12 + n + k)
+    x = torch.randn(tokens, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.02).bfloat16()
+    qx, qw = fos.quantize(x.to(DEV)), fos.quantize(w.to(DEV))
+    ox, ow = oracle.quantize(x), oracle.quantize(w)
+    for q, o in ((qx, ox), (qw, ow)):
+        assert torch.equal(q.values.cpu(), o.values)
+        assert torch.equal(q.scale_factors.view(torch.uint8).cpu().flatten(), o.scale_factors)
+        assert torch.equal(q.amax.cpu(), o.amax)
+    out = B200MatmulBackend.quantized_matmul(qx, qw, out_dtype=fos.DataType.bfloat16, check_status=True)
+    _check(out, _dense_reference(qx, qw), name, mismatch_scale=(k / 1024) ** 0.5)
+    want = oracle.matmul(ox, ow, torch.bfloat16)
+    frac = (out.cpu() != want).float().mean().item()
+    assert frac <= MISMATCH_TOLERANCE * (k / 1024) ** 0.5, f"{name} vs oracle matmul: {frac:.3%} differ"
+
+
 @pytest.mark.parametrize(("m", "n", "k"), [(256, 256, 256), (512, 256, 1024), (100, 72, 80), (384, 640, 448)])
 @pytest.mark.parametrize(("dtype_a", "dtype_b"), [("if4", "if4"), ("if4", "nvfp4"), ("nvfp4", "if4")])
 def test_if4_matmul_against_oracle(oracle, m, n, k, dtype_a, dtype_b):
