@@ -1,6 +1,7 @@
 """Benchmark of the hot path: Four-Over-Six NVFP4 quantization and the FP4 GEMM that consumes it.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --case quantize|dequantize|gemm [...]      (one kernel on its own, see run_case)
 
 One JSON line on stdout (rank 0).  The primary `value` is quantize throughput in GB/s of
 algorithmic traffic (2 B read + 0.5 B codes + 1/16 B scale per element) on the activation
@@ -528,13 +529,100 @@ def stack_section(args, fos, dev, rank, world):
     }
 
 
+def run_case(args) -> None:
+    """One kernel of the path on its own: a few identical launches with the mean time per call (CUDA
+    events), as a plain timing and as something to capture under a profiler
+    (`ncu -k regex:<kernel> -s 1 -c 1 ... python bench.py --case ...`).
+
+        --case quantize    --rows R --cols C [--rule mse|static_6|...] [--dtype nvfp4|if4|mxfp4] [--two-d]
+                           [--transpose] [--amax-given] [--kernel auto|general|no_tma]
+        --case dequantize  --rows R --cols C [--dtype ...]
+        --case gemm        --m M --n N --k K [--dtype nvfp4|mxfp4|if4] [--variant 0|128|256|2]
+
+    `--graph` times replays of a CUDA graph of the call instead of launches from Python. Inputs are
+    N(0,1) (the bench tensor with its outlier channels when the shape is 8192 x 4096)."""
+    import fouroversix_b200 as fos
+    from fouroversix_b200.matmul import B200MatmulBackend
+    from fouroversix_b200.quantize.backend import B200QuantizeBackend
+
+    dev = "cuda"
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        if args.graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            g.replay()
+            torch.cuda.synchronize()
+            fn = g.replay
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.iters
+
+    if args.case in ("quantize", "dequantize"):
+        rule = args.rule or ("static_6" if args.dtype == "mxfp4" else "mse")
+        if (args.rows, args.cols) == A_SHAPE:
+            x = make_a(1).to(dev)
+        else:
+            x = torch.randn(args.rows, args.cols, generator=torch.Generator().manual_seed(0)).bfloat16().to(dev)
+        cfg = fos.QuantizationConfig(dtype=args.dtype, scale_rule=rule, block_scale_2d=args.two_d, transpose=args.transpose)
+        amax = x.abs().max().float().reshape(1) if args.amax_given else None
+        if args.case == "quantize":
+            ms = timed(lambda: B200QuantizeBackend.quantize(x, cfg, amax=amax, kernel=args.kernel))
+        else:
+            q = fos.quantize(x, cfg)
+            ms = timed(lambda: fos.dequantize(q))
+        per_elem = 2.0 + 0.5 + (1.0 / 32 if args.dtype == "mxfp4" else 1.0 / 16)
+        print(f"{args.case} {args.rows}x{args.cols} {args.dtype} {rule}: {ms * 1e3:.1f} us per call "
+              f"({'graph replays' if args.graph else 'eager launches'}), "
+              f"{per_elem * args.rows * args.cols / (ms * 1e-3) / 1e9:.0f} GB/s algorithmic")
+        return
+    rule = "static_6" if args.dtype == "mxfp4" else "mse"
+    g = torch.Generator(device=dev).manual_seed(0)
+    a = torch.randn(args.m, args.k, generator=g, device=dev).bfloat16()
+    b = torch.randn(args.n, args.k, generator=g, device=dev).bfloat16()
+    cfg = fos.QuantizationConfig(dtype=args.dtype, scale_rule=rule)
+    qa, qb = fos.quantize(a, cfg), fos.quantize(b, cfg)
+    del a, b
+    out = torch.empty(args.m, args.n, dtype=torch.bfloat16, device=dev)
+    ms = timed(lambda: B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType.bfloat16, out=out, variant=args.variant))
+    print(f"gemm {args.m}x{args.n}x{args.k} {args.dtype} variant {args.variant}: {ms * 1e3:.1f} us per call, "
+          f"{2.0 * args.m * args.n * args.k / (ms * 1e-3) / 1e12:.0f} TFLOP/s")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--case", default=None, choices=["quantize", "dequantize", "gemm"], help="one kernel on its own (run_case)")
+    ap.add_argument("--rows", type=int, default=A_SHAPE[0])
+    ap.add_argument("--cols", type=int, default=A_SHAPE[1])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--rule", default=None)
+    ap.add_argument("--dtype", default="nvfp4")
+    ap.add_argument("--two-d", action="store_true")
+    ap.add_argument("--transpose", action="store_true")
+    ap.add_argument("--amax-given", action="store_true")
+    ap.add_argument("--kernel", default="auto", choices=["auto", "general", "no_tma"])
+    ap.add_argument("--variant", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=6)
+    ap.add_argument("--graph", action="store_true")
     args = ap.parse_args()
+    if args.case is not None:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py: no CUDA device; the GPU path has no CPU fallback")
+        run_case(args)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))

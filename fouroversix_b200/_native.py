@@ -20,9 +20,24 @@ FOS_NVFP4, FOS_IF4, FOS_MXFP4 = 0, 1, 2
 FOS_SF_ROWMAJOR, FOS_SF_TILED = 0, 1
 FOS_QUANTIZE_EXACT_ONLY = 1
 FOS_QUANTIZE_RHT = 2
-FOS_OPT_GEMM_MAX_CTAS = 4
+FOS_QUANTIZE_NO_TMA = 4
+FOS_QUANTIZE_GENERAL_KERNEL = 8
 
 _c_i64, _c_int, _c_ptr = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
+
+
+class GemmOpts(ctypes.Structure):
+    """fos_gemm_opts of include/fouroversix_b200.h: per-call kernel variant and CTA cap."""
+
+    _fields_ = [("variant", ctypes.c_int32), ("max_ctas", ctypes.c_int32)]
+
+
+def gemm_opts(variant: int = 0, max_ctas: int = 0):
+    """A pointer argument for the *_ex GEMM entry points (None when everything is default)."""
+    if not variant and not max_ctas:
+        return None
+    return ctypes.byref(GemmOpts(int(variant), int(max_ctas)))
+
 
 # name -> (restype, argtypes); the list mirrors include/fouroversix_b200.h
 SIGNATURES = {
@@ -31,6 +46,7 @@ SIGNATURES = {
     "fos_last_cuda_error": (_c_int, []),
     "fos_quantize": (_c_int, [_c_ptr, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_int, _c_int, _c_int,
                               _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr]),
+    "fos_amax": (_c_int, [_c_ptr, _c_int, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
     "fos_quantize_stochastic": (_c_int, [_c_ptr, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_int, _c_int, _c_int,
                                          _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, ctypes.c_uint64, _c_ptr]),
     "fos_pseudo_quantize": (_c_int, [_c_ptr, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr, _c_i64,
@@ -42,6 +58,10 @@ SIGNATURES = {
                                 _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
     "fos_gemm_mxfp4": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_i64, _c_i64,
                                 _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
+    "fos_gemm_nvfp4_ex": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_i64, _c_i64,
+                                   _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr]),
+    "fos_gemm_mxfp4_ex": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_i64, _c_i64,
+                                   _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr]),
     "fos_gemm_nvfp4_scatter": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_i64, _c_i64,
                                         _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
     "fos_allreduce_peer": (_c_int, [_c_ptr, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_ptr]),
@@ -51,7 +71,6 @@ SIGNATURES = {
                               _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_i64, _c_ptr, _c_ptr]),
     "fos_gemm_if4_static": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int,
                                      _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
-    "fos_set_option": (_c_int, [_c_int, _c_int]),
     "fos_wait_failure_site": (_c_int, [_c_ptr]),
 }
 
@@ -95,6 +114,21 @@ def check(status: int, what: str) -> None:
         msg += f" (cudaError {l.fos_last_cuda_error()})"
     exc = ValueError if status in (-1, -2, -3, -7) else NativeLibraryError
     raise exc(f"{what}: {msg}")
+
+
+def wait_failure_site() -> int:
+    """0, or the site of the first bounded device-side wait that ever gave up on the current device
+    (quantize kernels 1-9, FP4 GEMM 100 + site, fp16 GEMM of the IF4 path 200 + site). Synchronises
+    the device. Once it is non-zero, outputs of the kernels launched since are undefined."""
+    site = ctypes.c_int32(0)
+    check(lib().fos_wait_failure_site(ctypes.byref(site)), "fos_wait_failure_site")
+    return int(site.value)
+
+
+def raise_on_wait_failure() -> None:
+    site = wait_failure_site()
+    if site != 0:
+        raise NativeLibraryError(f"a bounded device-side wait timed out (site {site}); results since then are undefined")
 
 
 def stream_ptr(device: torch.device) -> int:

@@ -24,7 +24,17 @@ int check_device() {
 
 }  // namespace fos
 
-extern "C" int fos_version(void) { return 100; }
+extern "C" int fos_version(void) { return 200; }
+
+extern "C" int fos_wait_failure_site(int32_t *site) {
+    if (!site) return FOS_ERR_INVALID_ARGUMENT;
+    int32_t q = 0, g = 0, f = 0;
+    FOS_CUDA_TRY(fos::quantize_wait_failures(&q));
+    FOS_CUDA_TRY(fos::gemm_wait_failures(&g));
+    FOS_CUDA_TRY(fos::gemm_if4_wait_failures(&f));
+    *site = q != 0 ? q : (g != 0 ? 100 + g : (f != 0 ? 200 + f : 0));
+    return FOS_OK;
+}
 
 extern "C" int fos_last_cuda_error(void) { return fos::g_last_cuda_error; }
 

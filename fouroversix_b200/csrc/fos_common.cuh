@@ -16,10 +16,12 @@ namespace fos {
 
 // Records a failed runtime call for fos_last_cuda_error() and maps it to FOS_ERR_CUDA.
 int note_cuda_error(cudaError_t e);
-// FOS_OPT_QUANTIZE_VARIANT: 0 = pick the kernel by the input's alignment, 1 = never the TMA-fed kernel.
-extern int g_quantize_variant;
 // FOS_OK when the current device is compute capability 10.x, else FOS_ERR_ARCH / FOS_ERR_CUDA.
 int check_device();
+// The sticky wait-failure word of each group of kernels on the current device (0: no bounded wait ever gave up).
+cudaError_t quantize_wait_failures(int32_t *host_value);
+cudaError_t gemm_wait_failures(int32_t *host_value);
+cudaError_t gemm_if4_wait_failures(int32_t *host_value);
 
 // MXFP4 branches of fos_quantize / fos_dequantize (fos_mxfp4.cu); arguments validated by the callers.
 int quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int scale_rule, int block_2d,

@@ -243,18 +243,15 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 template <typename OUT>
 int launch_f16(const CUtensorMap &ma, const CUtensorMap &mb, const F16GemmParams &p, cudaStream_t stream) {
     auto kernel = gemm_f16_kernel<OUT>;
-    static bool configured[64] = {};
-    static int sm_count[64] = {};
-    int dev = 0;
+    static OncePerDevice configured;   // per instantiation
+    int dev = 0, sms = 0;
     FOS_CUDA_TRY(cudaGetDevice(&dev));
-    const int slot = (dev >= 0 && dev < 64) ? dev : 0;
-    if (!configured[slot]) {
-        FOS_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        FOS_CUDA_TRY(cudaDeviceGetAttribute(&sm_count[slot], cudaDevAttrMultiProcessorCount, dev));
-        configured[slot] = true;
-    }
+    FOS_CUDA_TRY(configured.run(dev, [&] {
+        return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    }));
+    FOS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int64_t tiles = (p.m_p / BLOCK_M) * ((p.n_p + BLOCK_N - 1) / BLOCK_N);
-    const unsigned grid = static_cast<unsigned>(tiles < sm_count[slot] ? tiles : sm_count[slot]);
+    const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
     kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;
@@ -273,6 +270,8 @@ int launch_expand(const uint8_t *codes, const uint8_t *sf, int format, int sf_la
 
 }  // namespace
 }  // namespace fos
+
+cudaError_t fos::gemm_if4_wait_failures(int32_t *host_value) { return fos::read_wait_failures(host_value); }
 
 extern "C" int64_t fos_gemm_if4_workspace_bytes(int64_t m_p, int64_t n_p, int64_t k_p) {
     if (m_p <= 0 || n_p <= 0 || k_p <= 0) return 0;
@@ -300,7 +299,11 @@ int gemm_if4_impl(const uint8_t *a_codes, const uint8_t *a_sf, int a_format, int
     CUtensorMap map_a, map_b;
     if ((st = make_operand_map(&map_a, a16, m_p, k_p * 2, BLOCK_M)) != FOS_OK) return st;
     if ((st = make_operand_map(&map_b, b16, n_p, k_p * 2, BLOCK_N)) != FOS_OK) return st;
-    if (status) FOS_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    if (status) {
+        FOS_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    } else {
+        FOS_CUDA_TRY(wait_failures_ptr(&status));   // the library's sticky word
+    }
     F16GemmParams p{alpha, d, status, m_p, n_p, k_p, m, n, ldd};
     if (out_dtype == FOS_BF16) return launch_f16<__nv_bfloat16>(map_a, map_b, p, stream);
     if (out_dtype == FOS_FP16) return launch_f16<__half>(map_a, map_b, p, stream);

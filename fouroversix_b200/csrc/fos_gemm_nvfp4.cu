@@ -61,6 +61,7 @@ constexpr int SF_LEAD = FOS_GEMM_SF_LEAD;   // 0 or 1: how many stages the scale
 #ifndef FOS_GEMM_ST256
 #define FOS_GEMM_ST256 1
 #endif
+
 #ifndef FOS_GEMM_SF_CP
 #define FOS_GEMM_SF_CP 1
 #endif
@@ -99,11 +100,11 @@ struct GemmParams {
     const uint8_t *b_sf;
     const float *alpha;
     void *d;
-    int32_t *status;
+    int32_t *status;         // where a bounded wait that gives up records its site: the caller's word, or the sticky one
     int64_t m_p, n_p, k_p;   // padded problem (k_p in values)
     int64_t m, n, ldd;       // region of D that is written
     int out_dtype;
-    int debug;               // FOS_OPT_GEMM_DEBUG bits (timing experiments only; results are wrong)
+    int debug;               // timing-experiment bits; only read in builds with -DFOS_GEMM_DEBUG (results are wrong with any set)
     int mx;                  // operands are MXFP4: E8M0 scales per 32 values, a 512-byte scale tile spans 128 values of K
     // Row-parallel layers: this rank's partial product is not stored to d but scattered, tile by tile as
     // the tiles complete, into the staging buffers of the ranks that will reduce them. Row block mb (128
@@ -118,16 +119,6 @@ struct GemmParams {
 
 // ---------------------------------------------------------------------------- MMA wrappers
 
-__device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-    asm volatile(
-        "{ .reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p; }\n"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-        : "memory");
-}
-
 // MXFP4: two E8M0 scales per row and K-block (scale_vec::2X); which two of the four bytes of a
 // scale column an instruction uses is part of its descriptor.
 __device__ __forceinline__ void tc_mma_mxf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -140,19 +131,49 @@ __device__ __forceinline__ void tc_mma_mxf4(uint32_t d_tmem, uint64_t a_desc, ui
         : "memory");
 }
 
-// One 512-byte scale tile (32 rows of 16 bytes) from shared memory into 4 columns of all four
-// 32-lane quadrants of tensor memory.
-__device__ __forceinline__ void tc_copy_sf(uint32_t taddr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+// Descriptors in two halves. The upper word of a shared-memory matrix descriptor is the same for every
+// tile of a kind (stride byte offset, version, swizzle) and the lower word is the start address >> 4
+// (shared-memory addresses stay below 2^18, so adding a byte offset >> 4 never carries out of the field):
+// the issuing threads keep one lower word per stage and add constants, instead of rebuilding 64-bit
+// descriptors for every instruction - a single thread issues every copy and every MMA of an SM, and
+// what it executes between two of them is what bounds its rate.
+constexpr uint32_t DESC_HI_OPERAND = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version 1, 128-byte swizzle
+constexpr uint32_t DESC_HI_SCALES = (128u >> 4) | (1u << 14);                   // SBO 128, version 1, no swizzle
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes = 0) {
+    return ((addr & 0x3ffffu) >> 4) | ((lbo_bytes >> 4) << 16);
 }
-
-__device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                 uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+__device__ __forceinline__ void tc_copy_sf_lo(uint32_t taddr, uint32_t lo) {
+    asm volatile("{ .reg .b64 d;\n"
+                 "mov.b64 d, {%1, %2};\n"
+                 "tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d; }" ::"r"(taddr), "r"(lo), "r"(DESC_HI_SCALES) : "memory");
+}
+__device__ __forceinline__ void tc_copy_sf_pair_lo(uint32_t taddr, uint32_t lo) {
+    asm volatile("{ .reg .b64 d;\n"
+                 "mov.b64 d, {%1, %2};\n"
+                 "tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d; }" ::"r"(taddr), "r"(lo), "r"(DESC_HI_SCALES) : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvf4_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
     asm volatile(
         "{ .reg .pred p;\n"
+        ".reg .b64 da, db;\n"
+        "mov.b64 da, {%1, %7};\n"
+        "mov.b64 db, {%2, %7};\n"
         "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p; }\n"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %3, [%5], [%6], p; }\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "r"(DESC_HI_OPERAND)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvf4_pair_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                    uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p;\n"
+        ".reg .b64 da, db;\n"
+        "mov.b64 da, {%1, %7};\n"
+        "mov.b64 db, {%2, %7};\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %3, [%5], [%6], p; }\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "r"(DESC_HI_OPERAND)
         : "memory");
 }
 
@@ -227,8 +248,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int64_t k_blocks = p.k_p / 64;                       // MMA K-blocks in the problem
     const int64_t k_tiles = (k_blocks + KB_PER_STAGE - 1) / KB_PER_STAGE;
 
+#ifdef FOS_GEMM_DEBUG
     const bool dbg_no_sf = p.debug & 1, dbg_no_load = p.debug & 2, dbg_no_store = p.debug & 4;
     const bool dbg_no_mma = p.debug & 16;
+#else
+    constexpr bool dbg_no_sf = false, dbg_no_load = false, dbg_no_store = false, dbg_no_mma = false;
+#endif
     if (warp == 0 && lane == 0 && !dbg_no_load) {
         // ------------------------------------------------------------------ TMA producer: operands
         uint32_t s = 0, ph = 0;
@@ -340,9 +365,13 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                     sfa_tmem + 4 * (kb >> 1), sfb_tmem + (BLOCK_N / 32) * (kb >> 1),
                                     (kt > 0 || kb > 0) ? 1u : 0u);
                 } else {
-                    for (int kb = 0; kb < nkb && !dbg_no_mma; ++kb)
-                        tc_mma_nvf4(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc, sfa_tmem + 4 * kb,
-                                    sfb_tmem + (BLOCK_N / 32) * kb, (kt > 0 || kb > 0) ? 1u : 0u);
+                    const uint32_t a_lo = desc_lo(stage, 16), b_lo = desc_lo(stage + A_BYTES, 16);
+#pragma unroll
+                    for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
+                        if (kb < nkb && !dbg_no_mma)
+                            tc_mma_nvf4_lo(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_tmem + 4 * kb,
+                                           sfb_tmem + (BLOCK_N / 32) * kb, (kt > 0 || kb > 0) ? 1u : 0u);
+                    }
                 }
                 tc_commit(empty_bar + 8 * s);          // stage (and scale slot) reusable once these MMAs are done
                 if (++s == C::STAGES) { s = 0; ph ^= 1u; }
@@ -452,14 +481,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 // tiles: 32 rows of 16 bytes, 8-row groups 128 bytes apart, no swizzle
                 // (MXFP4: a tile spans two K-blocks, so a stage has two tiles per group)
                 const int ntile = p.mx ? KB_PER_STAGE / 2 : KB_PER_STAGE;
+                const uint32_t src_lo = desc_lo(src);
 #pragma unroll
                 for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
                     if (kb >= ntile) break;
-                    tc_copy_sf(dst + 4 * kb, smem_desc(src + kb * SF_TILE_BYTES, 0, 128, 0));
+                    tc_copy_sf_lo(dst + 4 * kb, src_lo + ((kb * SF_TILE_BYTES) >> 4));
 #pragma unroll
                     for (int g = 0; g < C::N_GROUPS; ++g)
-                        tc_copy_sf(dst + 16 + (BLOCK_N / 32) * kb + 4 * g,
-                                   smem_desc(src + SFA_BYTES + (g * ntile + kb) * SF_TILE_BYTES, 0, 128, 0));
+                        tc_copy_sf_lo(dst + 16 + (BLOCK_N / 32) * kb + 4 * g,
+                                      src_lo + ((SFA_BYTES + (g * ntile + kb) * SF_TILE_BYTES) >> 4));
                 }
                 tc_commit(sf_ready_bar + 8 * j);     // arrives when the copies above are done
                 if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
@@ -572,12 +602,6 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(cluster_bar) : "memory");
 }
 
-// One 512-byte scale tile from each CTA's own shared memory into 4 columns of all four lane quadrants
-// of its own tensor memory, in both CTAs of the pair at once.
-__device__ __forceinline__ void tc_copy_sf_pair(uint32_t taddr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-
 // Arrive (once, on a barrier of this CTA) when the tcgen05 operations this thread issued for the pair are done.
 __device__ __forceinline__ void tc_commit_pair_local(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -644,8 +668,12 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int64_t k_blocks = p.k_p / 64;
     const int64_t k_tiles = (k_blocks + KB_PER_STAGE - 1) / KB_PER_STAGE;
     const int64_t pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+#ifdef FOS_GEMM_DEBUG
     const bool dbg_no_sf = p.debug & 1, dbg_no_load = p.debug & 2, dbg_no_store = p.debug & 4;
     const bool dbg_no_mma = p.debug & 16;
+#else
+    constexpr bool dbg_no_sf = false, dbg_no_load = false, dbg_no_store = false, dbg_no_mma = false;
+#endif
 
     if (warp == 0 && lane == 0 && !dbg_no_load) {
         // ------------------------------------------------------------------ TMA producer: operands (both CTAs)
@@ -729,9 +757,13 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const uint64_t a_desc = smem_desc(stage, 16, 1024, 2);
                 const uint64_t b_desc = smem_desc(stage + A_BYTES, 16, 1024, 2);
                 const uint32_t sfa_tmem = tmem_base + SF_COL0 + j * SF_STAGE_COLS, sfb_tmem = sfa_tmem + 16;
-                for (int kb = 0; kb < nkb && !dbg_no_mma; ++kb)
-                    tc_mma_nvf4_pair(tmem_base, a_desc + 2 * kb, b_desc + 2 * kb, idesc, sfa_tmem + 4 * kb,
-                                     sfb_tmem + 8 * kb, (kt > 0 || kb > 0) ? 1u : 0u);
+                const uint32_t a_lo = desc_lo(stage, 16), b_lo = desc_lo(stage + A_BYTES, 16);
+#pragma unroll
+                for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
+                    if (kb < nkb && !dbg_no_mma)
+                        tc_mma_nvf4_pair_lo(tmem_base, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_tmem + 4 * kb,
+                                            sfb_tmem + 8 * kb, (kt > 0 || kb > 0) ? 1u : 0u);
+                }
                 tc_commit_pair(empty_bar + 8 * s);
                 if (++s == STAGES) { s = 0; ph ^= 1u; }
                 if (++j == SF_SLOTS) { j = 0; jph ^= 1u; }
@@ -825,13 +857,14 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t src = sf_base + j * SF_SLOT_BYTES, dst = tmem_base + SF_COL0 + j * SF_STAGE_COLS;
+                const uint32_t src_lo = desc_lo(src);
 #pragma unroll
                 for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
-                    tc_copy_sf_pair(dst + 4 * kb, smem_desc(src + kb * SF_TILE_BYTES, 0, 128, 0));
+                    tc_copy_sf_pair_lo(dst + 4 * kb, src_lo + ((kb * SF_TILE_BYTES) >> 4));
 #pragma unroll
                     for (int g = 0; g < 2; ++g)
-                        tc_copy_sf_pair(dst + 16 + 8 * kb + 4 * g,
-                                        smem_desc(src + SFA_BYTES + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES, 0, 128, 0));
+                        tc_copy_sf_pair_lo(dst + 16 + 8 * kb + 4 * g,
+                                           src_lo + ((SFA_BYTES + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES) >> 4));
                 }
                 tc_commit_pair_local(sf_ready_bar + 8 * j);
                 if (++j == SF_SLOTS) { j = 0; jph ^= 1u; }
@@ -873,9 +906,11 @@ int launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap 
                 const GemmParams &p, cudaStream_t stream) {
     auto kernel = pair::gemm_nvfp4_pair_kernel<OUT>;
     static int max_clusters[64] = {};   // per device: how many CTA pairs can be resident at once
+    static std::mutex mu;
     int dev = 0;
     FOS_CUDA_TRY(cudaGetDevice(&dev));
     const int slot = (dev >= 0 && dev < 64) ? dev : 0;
+    std::lock_guard<std::mutex> lock(mu);
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(pair::THREADS);
     cfg.dynamicSmemBytes = pair::SMEM_BYTES;
@@ -907,13 +942,12 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &msa,
            const GemmParams &p, int sms, cudaStream_t stream) {
     using C = Cfg<BLOCK_N>;
     auto kernel = gemm_nvfp4_kernel<BLOCK_N, OUT>;
-    static bool configured[64] = {};   // per instantiation and per device
+    static OncePerDevice configured;   // per instantiation
     int dev = 0;
     FOS_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
-        FOS_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-        if (dev >= 0 && dev < 64) configured[dev] = true;
-    }
+    FOS_CUDA_TRY(configured.run(dev, [&] {
+        return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    }));
     const int64_t tiles = (p.m_p / BLOCK_M) * ((p.n_p + BLOCK_N - 1) / BLOCK_N);
     const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
     kernel<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ma, mb, msa, msb, p);
@@ -929,38 +963,30 @@ int launch_out(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &
     return launch<BLOCK_N, float>(ma, mb, msa, msb, p, sms, stream);
 }
 
-int g_gemm_variant = 0;   // FOS_OPT_GEMM_VARIANT
-int g_gemm_debug = 0;     // FOS_OPT_GEMM_DEBUG
-int g_gemm_max_ctas = 0;  // FOS_OPT_GEMM_MAX_CTAS
+#ifdef FOS_GEMM_DEBUG
+int g_gemm_debug = 0;     // timing experiments of a debug build (fos_gemm_debug_set)
+#endif
 
 }  // namespace
 }  // namespace fos
 
-extern "C" int fos_set_option(int key, int value) {
-    if (key == FOS_OPT_GEMM_VARIANT && (value == 0 || value == 128 || value == 256 || value == 2)) {
-        fos::g_gemm_variant = value;
-        return FOS_OK;
-    }
-    if (key == FOS_OPT_GEMM_DEBUG && value >= 0 && value < 32 && !(value & 8)) {
-        fos::g_gemm_debug = value;
-        return FOS_OK;
-    }
-    if (key == FOS_OPT_GEMM_MAX_CTAS && value >= 0) {
-        fos::g_gemm_max_ctas = value;
-        return FOS_OK;
-    }
-    if (key == FOS_OPT_QUANTIZE_VARIANT && value >= 0 && value <= 2) {
-        fos::g_quantize_variant = value;
-        return FOS_OK;
-    }
-    return FOS_ERR_INVALID_ARGUMENT;
+#ifdef FOS_GEMM_DEBUG
+// Debug builds only (not declared in the public header): bit 0 skips the scale copies, bit 1 the operand
+// loads, bit 2 the output stores, bit 4 the MMAs. The GEMM's result is wrong with any of them set.
+extern "C" int fos_gemm_debug_set(int bits) {
+    fos::g_gemm_debug = bits;
+    return FOS_OK;
 }
+#endif
 
 static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
                           const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
-                          int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, int32_t *status,
-                          void *stream_, int mx, void *const *d_peers = nullptr, int world = 0, int rank = 0) {
+                          int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, const fos_gemm_opts *opts,
+                          int32_t *status, void *stream_, int mx, void *const *d_peers = nullptr, int world = 0,
+                          int rank = 0) {
     using namespace fos;
+    const int variant = opts ? opts->variant : 0, max_ctas = opts ? opts->max_ctas : 0;
+    if ((variant != 0 && variant != 128 && variant != 256 && variant != 2) || max_ctas < 0) return FOS_ERR_INVALID_ARGUMENT;
     if (d_peers) {
         if (world < 2 || world > 8 || rank < 0 || rank >= world) return FOS_ERR_INVALID_ARGUMENT;
         if (m_p % (128 * static_cast<int64_t>(world)) != 0) return FOS_ERR_UNSUPPORTED;   // slabs of whole row blocks
@@ -985,9 +1011,14 @@ static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uin
     int dev = 0, sms = 0;
     FOS_CUDA_TRY(cudaGetDevice(&dev));
     FOS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    if (g_gemm_max_ctas > 0 && g_gemm_max_ctas < sms) sms = g_gemm_max_ctas;   // leave SMs to concurrent kernels
+    if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;   // leave SMs to concurrent kernels
 
-    GemmParams p{a_sf, b_sf, alpha, d, status, m_p, n_p, k_p, m, n, ldd, out_dtype, g_gemm_debug, mx, 0, 0, 0, {}};
+#ifdef FOS_GEMM_DEBUG
+    const int debug_bits = g_gemm_debug;
+#else
+    const int debug_bits = 0;
+#endif
+    GemmParams p{a_sf, b_sf, alpha, d, status, m_p, n_p, k_p, m, n, ldd, out_dtype, debug_bits, mx, 0, 0, 0, {}};
     if (d_peers) {
         p.scatter_world = world;
         p.scatter_rank = rank;
@@ -995,14 +1026,19 @@ static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uin
         for (int i = 0; i < world; ++i) p.d_peer[i] = d_peers[i];
     }
     const int64_t sf_k_tiles = mx ? k_p / 128 : k_p / 64;     // 512-byte scale tiles along K
-    if (status) FOS_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    if (status) {
+        FOS_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    } else {
+        // no word of the caller's: a wait that gives up leaves its site in the library's sticky word
+        FOS_CUDA_TRY(wait_failures_ptr(&p.status));
+    }
     CUtensorMap map_a, map_b;
 
     // The CTA-pair kernel is correct but still measures slower than the single-CTA kernel on B200
     // (its hand-overs between the two SMs lengthen the load round trip), so it only runs when
     // asked for.
     const bool pair_fits = m_p % 256 == 0 && n_p % 256 == 0;
-    const bool use_pair = pair_fits && g_gemm_variant == 2 && !mx && !d_peers;
+    const bool use_pair = pair_fits && variant == 2 && !mx && !d_peers;
     if (use_pair) {
         CUtensorMap map_sfa, map_sfb;
         if ((st = make_operand_map(&map_a, a_codes, m_p, k_p / 2, 128)) != FOS_OK) return st;
@@ -1019,8 +1055,8 @@ static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uin
     // doubles the number of busy SMs)
     const int64_t tiles_256 = (m_p / BLOCK_M) * ((n_p + 255) / 256);
     bool wide = n_p >= 256 && tiles_256 * 2 > sms;
-    if (g_gemm_variant == 128) wide = false;
-    if (g_gemm_variant == 256) wide = true;
+    if (variant == 128) wide = false;
+    if (variant == 256) wide = true;
     if ((st = make_operand_map(&map_a, a_codes, m_p, k_p / 2, BLOCK_M)) != FOS_OK) return st;
     if ((st = make_operand_map(&map_b, b_codes, n_p, k_p / 2, wide ? 256 : 128)) != FOS_OK) return st;
     CUtensorMap map_sfa, map_sfb;
@@ -1031,18 +1067,34 @@ static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uin
                 : launch_out<128>(map_a, map_b, map_sfa, map_sfb, p, sms, stream);
 }
 
+cudaError_t fos::gemm_wait_failures(int32_t *host_value) { return fos::read_wait_failures(host_value); }
+
 extern "C" int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
                               const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
                               int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, int32_t *status,
                               void *stream) {
-    return gemm_fp4_entry(a_codes, a_sf, b_codes, b_sf, alpha, d, out_dtype, m_p, n_p, k_p, m, n, ldd, status, stream, 0);
+    return gemm_fp4_entry(a_codes, a_sf, b_codes, b_sf, alpha, d, out_dtype, m_p, n_p, k_p, m, n, ldd, nullptr, status, stream, 0);
+}
+
+extern "C" int fos_gemm_nvfp4_ex(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                                 const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
+                                 int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, const fos_gemm_opts *opts,
+                                 int32_t *status, void *stream) {
+    return gemm_fp4_entry(a_codes, a_sf, b_codes, b_sf, alpha, d, out_dtype, m_p, n_p, k_p, m, n, ldd, opts, status, stream, 0);
 }
 
 extern "C" int fos_gemm_mxfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
                               const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
                               int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, int32_t *status,
                               void *stream) {
-    return gemm_fp4_entry(a_codes, a_sf, b_codes, b_sf, alpha, d, out_dtype, m_p, n_p, k_p, m, n, ldd, status, stream, 1);
+    return gemm_fp4_entry(a_codes, a_sf, b_codes, b_sf, alpha, d, out_dtype, m_p, n_p, k_p, m, n, ldd, nullptr, status, stream, 1);
+}
+
+extern "C" int fos_gemm_mxfp4_ex(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                                 const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
+                                 int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, const fos_gemm_opts *opts,
+                                 int32_t *status, void *stream) {
+    return gemm_fp4_entry(a_codes, a_sf, b_codes, b_sf, alpha, d, out_dtype, m_p, n_p, k_p, m, n, ldd, opts, status, stream, 1);
 }
 
 extern "C" int fos_gemm_nvfp4_scatter(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
@@ -1051,6 +1103,6 @@ extern "C" int fos_gemm_nvfp4_scatter(const uint8_t *a_codes, const uint8_t *a_s
                                       int64_t ldd, int32_t *status, void *stream) {
     if (!d_peers) return FOS_ERR_INVALID_ARGUMENT;
     if (out_dtype != FOS_BF16 && out_dtype != FOS_FP16) return FOS_ERR_UNSUPPORTED;
-    return gemm_fp4_entry(a_codes, a_sf, b_codes, b_sf, alpha, nullptr, out_dtype, m_p, n_p, k_p, m, n, ldd, status, stream, 0,
+    return gemm_fp4_entry(a_codes, a_sf, b_codes, b_sf, alpha, nullptr, out_dtype, m_p, n_p, k_p, m, n, ldd, nullptr, status, stream, 0,
                           d_peers, world, rank);
 }

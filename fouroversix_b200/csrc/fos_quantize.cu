@@ -17,9 +17,6 @@
 #include "fos_dequant.cuh"
 
 namespace fos {
-
-int g_quantize_variant = 0;   // FOS_OPT_QUANTIZE_VARIANT
-
 namespace {
 
 constexpr int KIND_STATIC = 0;    // NVFP4, one candidate (static_6 / static_4)
@@ -44,6 +41,8 @@ struct QuantParams {
     int sf_tiled;
     int exact_only;
     int vec_bytes;               // 32, 16 or 0: widest aligned load usable on x
+    int variant;                 // 0: kernel chosen by the input; 1: never a TMA-fed kernel (FOS_QUANTIZE_NO_TMA);
+                                 // 2: the general TMA-fed kernel where a specialised one exists (FOS_QUANTIZE_GENERAL_KERNEL)
     int x_is_ready;              // x was complete before the previous kernel in the stream started
     int rht;                     // rotate every block of 16 (random Hadamard transform) before quantizing
     int stochastic;              // stochastic rounding (1-D blocks, NVFP4, TMA-fed kernels only)
@@ -53,9 +52,6 @@ struct QuantParams {
     int64_t fake_ld;
     float fake_divisor;
 };
-
-// Site of the first bounded wait that gave up, 0 if none did (never expected to change).
-__device__ int32_t g_wait_failures = 0;
 
 
 // ------------------------------------------------------------------------------------
@@ -1011,9 +1007,7 @@ constexpr int FEED_TILE_ROWS = 128;
 #ifndef FOS_UNPACK_BY_ADD
 #define FOS_UNPACK_BY_ADD 1
 #endif
-#ifndef FOS_EARLY_PDL
-#define FOS_EARLY_PDL 0
-#endif
+
 
 #ifndef FOS_FEED_STAGES
 #define FOS_FEED_STAGES 4
@@ -1309,11 +1303,6 @@ quantize_rows_mse_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-#if FOS_EARLY_PDL
-    // every CTA of this grid is resident by now (the grid is at most one wave), so a dependent grid can
-    // be admitted already: its CTAs take the slots of CTAs of this grid as they exit
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-#endif
 
     // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ... in row-major tile order
     const int my_tiles = static_cast<int>((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
@@ -1429,9 +1418,6 @@ quantize_rows_mse_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
                 // subnormal scale, exact-only run, amax out of range) take the per-lane exact sequence.
                 const bool coop_ok = fminf(ea.w, eb.w) >= 0.0f;
                 unsigned pending = __ballot_sync(FULL, undecided && coop_ok);
-#ifdef FOS_COUNT_SLOW
-                if (lane == 0) atomicAdd(&g_wait_failures, FOS_COUNT_SLOW == 1 ? 1 : __popc(pending));
-#endif
                 while (pending) {
                     const int src = __ffs(pending) - 1;
                     pending &= pending - 1;
@@ -1460,9 +1446,7 @@ quantize_rows_mse_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
         s_off += FEED_STAGE_BYTES;
         if (++s_idx == FEED_STAGES) { s_idx = 0; s_off = 0; parity ^= 1u; }
     }
-#if !FOS_EARLY_PDL
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-#endif
 }
 
 // ------------------------------------------------------------------------------------
@@ -1663,11 +1647,11 @@ cudaError_t launch_rows_tma(const QuantParams &p, cudaStream_t stream, bool *lau
 
 template <typename T, int KIND>
 cudaError_t launch_rows(const QuantParams &p, cudaStream_t stream) {
-    if (g_quantize_variant != 1) {
+    if (p.variant != 1) {
         bool launched = false;
         if constexpr (KIND == KIND_ADAPTIVE) {
             // the default configuration (mean-squared error, round to nearest, no rotation) has a kernel of its own
-            if (p.rule == FOS_RULE_MSE && !p.rht && !p.stochastic && g_quantize_variant != 2) {
+            if (p.rule == FOS_RULE_MSE && !p.rht && !p.stochastic && p.variant != 2) {
                 const cudaError_t e = launch_rows_tma_impl<T, KIND, false, false, false, false, true>(p, stream, &launched);
                 if (e != cudaSuccess || launched) return e;
             }
@@ -1720,7 +1704,7 @@ cudaError_t launch_kind(const QuantParams &p, bool two_d, bool transposed, cudaS
 template <typename T, int KIND>
 cudaError_t launch_fed(const QuantParams &p, bool two_d, bool transposed, cudaStream_t stream, bool *launched) {
     *launched = false;
-    if (g_quantize_variant == 1) return cudaSuccess;
+    if (p.variant == 1) return cudaSuccess;
     if (two_d) {
         return transposed ? launch_rows_tma<T, KIND, true, false, true>(p, stream, launched)
                           : launch_rows_tma<T, KIND, false, false, true>(p, stream, launched);
@@ -1868,7 +1852,7 @@ static int quantize_entry(const void *x, int x_dtype, int64_t rows, int64_t cols
     if (stochastic) {
         // stochastic rounding lives in the TMA-fed kernels only: NVFP4, 1-D blocks, aligned input
         if (format != FOS_NVFP4 || block_2d) return FOS_ERR_UNSUPPORTED;
-        if (g_quantize_variant == 1 || reinterpret_cast<uintptr_t>(x) % 16 != 0 || (ld * 2) % 16 != 0) return FOS_ERR_UNSUPPORTED;
+        if ((flags & FOS_QUANTIZE_NO_TMA) || reinterpret_cast<uintptr_t>(x) % 16 != 0 || (ld * 2) % 16 != 0) return FOS_ERR_UNSUPPORTED;
         if (transpose && (reinterpret_cast<uintptr_t>(codes) % 16 != 0 || reinterpret_cast<uintptr_t>(sf) % 2 != 0))
             return FOS_ERR_UNSUPPORTED;
     }
@@ -1907,6 +1891,7 @@ static int quantize_entry(const void *x, int x_dtype, int64_t rows, int64_t cols
     p.rule = scale_rule;
     p.sf_tiled = sf_layout == FOS_SF_TILED;
     p.exact_only = (flags & FOS_QUANTIZE_EXACT_ONLY) != 0;
+    p.variant = (flags & FOS_QUANTIZE_NO_TMA) ? 1 : ((flags & FOS_QUANTIZE_GENERAL_KERNEL) ? 2 : 0);
     p.rht = (flags & FOS_QUANTIZE_RHT) != 0;
     if (p.rht && p.out_cols % 16 != 0) return FOS_ERR_INVALID_ARGUMENT;   // blocks of 16 along the quantized axis
     p.stochastic = stochastic;
@@ -1939,9 +1924,19 @@ static int quantize_entry(const void *x, int x_dtype, int64_t rows, int64_t cols
     return FOS_OK;
 }
 
-extern "C" int fos_wait_failure_site(int32_t *site) {
-    if (!site) return FOS_ERR_INVALID_ARGUMENT;
-    FOS_CUDA_TRY(cudaMemcpyFromSymbol(site, fos::g_wait_failures, sizeof(int32_t)));
+cudaError_t fos::quantize_wait_failures(int32_t *host_value) { return fos::read_wait_failures(host_value); }
+
+extern "C" int fos_amax(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, float *amax_out, void *stream_) {
+    using namespace fos;
+    if (!x || !amax_out) return FOS_ERR_INVALID_ARGUMENT;
+    if (rows <= 0 || cols <= 0 || ld < cols) return FOS_ERR_INVALID_ARGUMENT;
+    if (x_dtype != FOS_BF16 && x_dtype != FOS_FP16) return FOS_ERR_INVALID_ARGUMENT;
+    const int st = check_device();
+    if (st != FOS_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const bool vec16 = reinterpret_cast<uintptr_t>(x) % 16 == 0 && (ld * 2) % 16 == 0 && cols % 8 == 0;
+    FOS_CUDA_TRY(x_dtype == FOS_BF16 ? launch_amax<__nv_bfloat16>(x, rows, cols, ld, vec16, amax_out, stream)
+                                     : launch_amax<__half>(x, rows, cols, ld, vec16, amax_out, stream));
     return FOS_OK;
 }
 

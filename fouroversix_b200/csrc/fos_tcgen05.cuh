@@ -3,6 +3,7 @@
 
 #include <cuda.h>
 
+#include <mutex>
 #include <type_traits>
 
 #include "fos_common.cuh"
@@ -13,6 +14,50 @@ namespace {
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // waits timed with the global timer give up after 2 s
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;         // waits timed in SM cycles: about 2 s at 2 GHz, 4 s at 1 GHz
 constexpr int TMEM_COLS = 512;
+
+// Site of the first bounded device-side wait that ever gave up in a kernel of this translation unit on
+// this device, 0 if none did (never expected to change). Sticky: nothing resets it, so a launch whose
+// caller passed no status word of its own still leaves a trace that fos_wait_failure_site reports.
+__device__ int32_t g_wait_failures = 0;
+
+// Runs `init` once per device (the first call with that device current), under a lock: for
+// cudaFuncSetAttribute and the like, whose results the launch paths cache per device.
+struct OncePerDevice {
+    std::mutex mu;
+    bool done[64] = {};
+    template <typename F> cudaError_t run(int dev, F init) {
+        if (dev < 0 || dev >= 64) return init();
+        std::lock_guard<std::mutex> lock(mu);
+        if (done[dev]) return cudaSuccess;
+        const cudaError_t e = init();
+        if (e == cudaSuccess) done[dev] = true;
+        return e;
+    }
+};
+
+// Device address of this translation unit's g_wait_failures on the current device.
+inline cudaError_t wait_failures_ptr(int32_t **out) {
+    static std::mutex mu;
+    static int32_t *ptrs[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const int slot = (dev >= 0 && dev < 64) ? dev : 0;
+    std::lock_guard<std::mutex> lock(mu);
+    if (ptrs[slot] == nullptr || dev != slot) {
+        void *ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_wait_failures);
+        if (e != cudaSuccess) return e;
+        if (dev != slot) { *out = static_cast<int32_t *>(ptr); return cudaSuccess; }
+        ptrs[slot] = static_cast<int32_t *>(ptr);
+    }
+    *out = ptrs[slot];
+    return cudaSuccess;
+}
+
+inline cudaError_t read_wait_failures(int32_t *host_value) {
+    return cudaMemcpyFromSymbol(host_value, g_wait_failures, sizeof(int32_t));
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -75,9 +120,24 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// mbar_wait that polls instead of letting the hardware suspend the thread. For barriers that
-// another CTA of the cluster arrives on: a thread suspended in try_wait is not woken by such
-// an arrival before the suspension runs out, which costs over a microsecond per hand-over.
+// try_wait whose suspension is limited to about `ns` nanoseconds.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p; }\n"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
+
+constexpr uint32_t POLL_SUSPEND_NS = 100;   // longest suspension of one probe in mbar_wait_poll
+
+// mbar_wait for barriers that another CTA of the cluster arrives on. A thread suspended in a plain
+// try_wait was not woken promptly by such an arrival (over a microsecond per hand-over), and probing
+// with test_wait in a tight loop from a dozen threads takes shared-memory cycles from the copies and
+// the MMAs (the CTA-pair GEMM ran a tenth faster without it): each probe here is a try_wait whose
+// suspension is limited to POLL_SUSPEND_NS.
 __device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                                int32_t *status, int where) {
     const long long t0 = clock64();
@@ -85,7 +145,7 @@ __device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, vo
     while (true) {
 #pragma unroll 1
         for (int i = 0; i < 256; ++i)
-            if (mbar_test_wait(bar, parity)) return true;
+            if (mbar_try_wait_hint(bar, parity, POLL_SUSPEND_NS)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;

@@ -60,9 +60,13 @@ class B200MatmulBackend:
 
     @classmethod
     def quantized_matmul(cls, input: QuantizedTensor, other: QuantizedTensor, *, out_dtype: DataType,
-                         out: torch.Tensor | None = None, check_status: bool = False) -> torch.Tensor:
+                         out: torch.Tensor | None = None, check_status: bool = False, variant: int = 0,
+                         max_ctas: int = 0) -> torch.Tensor:
         """`input @ other.T`, cropped to (input rows, other rows).  `check_status` reads the
-        kernel's device status word back (one synchronisation) and raises on a timeout."""
+        kernel's device status word back (one synchronisation) and raises on a timeout; without it a
+        wait that gives up leaves its site in the library's sticky word (`_native.raise_on_wait_failure`).
+        `variant` / `max_ctas` are the per-call options of the FP4 kernels (fos_gemm_opts): which
+        kernel, and how many CTAs at most (to leave SMs to a collective running beside the GEMM)."""
         reason = cls.unsupported_reason(input, other, out_dtype=out_dtype)
         if reason is not None:
             raise ValueError(f"B200 matmul: {reason}")
@@ -88,12 +92,13 @@ class B200MatmulBackend:
         with torch.cuda.device(dev):
             lib, stream = _native.lib(), _native.stream_ptr(dev)
             status_ptr = 0 if status is None else status.data_ptr()
+            opts = _native.gemm_opts(variant, max_ctas)
             if fa == _native.FOS_MXFP4:
                 alpha.fill_(1.0)
-                _native.check(lib.fos_gemm_mxfp4(
+                _native.check(lib.fos_gemm_mxfp4_ex(
                     a_vals.data_ptr(), a_sf.data_ptr(), b_vals.data_ptr(), b_sf.data_ptr(), alpha.data_ptr(),
                     out.data_ptr(), _native.elem_code(torch_out), m_p, n_p, k_p, m, n, out.stride(0),
-                    status_ptr, stream), "fos_gemm_mxfp4")
+                    opts, status_ptr, stream), "fos_gemm_mxfp4")
                 if status is not None and int(status.item()) != 0:
                     raise _native.NativeLibraryError(
                         f"fos_gemm_mxfp4: a bounded device-side wait timed out (site {int(status.item())})")
@@ -102,10 +107,10 @@ class B200MatmulBackend:
                 input.amax.data_ptr(), fa, input.scale_rule.cuda_id,
                 other.amax.data_ptr(), fb, other.scale_rule.cuda_id, alpha.data_ptr(), stream), "fos_gemm_alpha")
             if native_fp4:
-                _native.check(lib.fos_gemm_nvfp4(
+                _native.check(lib.fos_gemm_nvfp4_ex(
                     a_vals.data_ptr(), a_sf.data_ptr(), b_vals.data_ptr(), b_sf.data_ptr(), alpha.data_ptr(),
                     out.data_ptr(), _native.elem_code(torch_out), m_p, n_p, k_p, m, n, out.stride(0),
-                    status_ptr, stream), "fos_gemm_nvfp4")
+                    opts, status_ptr, stream), "fos_gemm_nvfp4")
             else:
                 nbytes = int(lib.fos_gemm_if4_workspace_bytes(m_p, n_p, k_p))
                 workspace = torch.empty(nbytes, dtype=torch.uint8, device=dev)

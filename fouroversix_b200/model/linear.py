@@ -72,6 +72,13 @@ class FourOverSixLinearFunction(torch.autograd.Function):
         cfg: ModuleQuantizationConfig = ctx.config
         if cfg.quartet_ii_dtype is not None:
             raise NotImplementedError("the Quartet-II backward pass is not implemented")
+        # settings of the reference's backward pass (src/fouroversix/model/modules/linear.py:213-229, 258-268)
+        # that this layer does not implement are refused rather than silently ignored
+        if getattr(cfg, "wgrad_nvint4", False):
+            raise NotImplementedError("wgrad_nvint4 is not implemented")
+        if isinstance(cfg.disable_dgrad_quantization, str):
+            raise NotImplementedError(
+                f"disable_dgrad_quantization={cfg.disable_dgrad_quantization!r} is not implemented (True / False are)")
         if cfg.gradient_round_style == RoundStyle.stochastic_unbiased and not (
                 cfg.disable_dgrad_quantization and cfg.disable_wgrad_quantization):
             raise NotImplementedError(

@@ -74,11 +74,13 @@ class B200QuantizeBackend:
 
     @classmethod
     def quantize(cls, x: torch.Tensor, config: QuantizationConfig, *, amax: torch.Tensor | None = None,
-                 exact_only: bool = False, seed: int | None = None) -> QuantizedTensor:
+                 exact_only: bool = False, seed: int | None = None, kernel: str = "auto") -> QuantizedTensor:
         """Quantize `x` (or its transpose). `amax`, when given, is a CUDA fp32 tensor that
         already holds max|x| and saves the extra pass that computes it. With stochastic rounding,
         `seed` selects the noise (default: drawn from torch's CPU generator, so torch.manual_seed
-        makes a run repeatable)."""
+        makes a run repeatable). `kernel` is a testing aid (every kernel writes the same bytes):
+        "no_tma" = never a kernel fed by the TMA unit, "general" = the general TMA-fed kernel also
+        where a specialised one exists."""
         reason = cls.unsupported_reason(x, config)
         if reason is not None:
             raise ValueError(f"B200 quantize: {reason}")
@@ -99,7 +101,8 @@ class B200QuantizeBackend:
                 int(config.transpose), _native.FOS_SF_TILED if tiled else _native.FOS_SF_ROWMAJOR,
                 0 if amax is None else amax.data_ptr(), values.data_ptr(), scales.data_ptr(),
                 amax_out.data_ptr(),
-                (_native.FOS_QUANTIZE_EXACT_ONLY if exact_only else 0) | (_native.FOS_QUANTIZE_RHT if config.rht else 0))
+                (_native.FOS_QUANTIZE_EXACT_ONLY if exact_only else 0) | (_native.FOS_QUANTIZE_RHT if config.rht else 0)
+                | {"auto": 0, "no_tma": _native.FOS_QUANTIZE_NO_TMA, "general": _native.FOS_QUANTIZE_GENERAL_KERNEL}[kernel])
         with torch.cuda.device(dev):
             if config.round_style == RoundStyle.stochastic:
                 if seed is None:
@@ -114,6 +117,20 @@ class B200QuantizeBackend:
             values, _scale_view(scales, config.dtype), amax_out, config.dtype, out_shape,
             config.scale_rule, config.round_style, (rows_p, cols_p),
             scale_factors_are_in_blackwell_layout=tiled)
+
+    @classmethod
+    def amax(cls, x: torch.Tensor) -> torch.Tensor:
+        """max |x| of a 2-D bf16 / fp16 CUDA tensor as a 1-element fp32 tensor (fos_amax): the first pass of
+        `quantize` on its own, for callers that quantize one tensor in pieces with a common amax."""
+        if x.ndim != 2 or x.device.type != "cuda" or x.dtype not in (torch.bfloat16, torch.float16):
+            raise ValueError("B200 amax: input must be a 2-D bfloat16 / float16 CUDA tensor")
+        if x.stride(1) != 1:
+            x = x.contiguous()
+        out = torch.empty(1, dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            _native.check(_native.lib().fos_amax(x.data_ptr(), _native.elem_code(x.dtype), x.shape[0], x.shape[1],
+                                                 x.stride(0), out.data_ptr(), _native.stream_ptr(x.device)), "fos_amax")
+        return out
 
     @classmethod
     def can_dequantize(cls, tensor: QuantizedTensor) -> bool:

@@ -18,6 +18,14 @@ shard's GEMM at large token counts, so the token dimension is cut into chunks: t
 all-reduce of chunk i runs on a communication stream while the GEMM of chunk i+1 runs
 on the compute stream.
 
+A row-parallel layer that feeds a column-parallel one (o_proj -> gate / up, down_proj -> the next
+block's qkv) can hand its output over as ROW SLABS instead of a full tensor (`scatter_output=True` /
+`scattered_input=True`): the partial products are reduce-scattered (every rank ends with tokens / g
+rows, half the link traffic of an all-reduce), the ranks agree on the slabs' common amax (4 bytes),
+each quantizes its own slab with it - the bytes of those rows of the unsharded quantization - and
+the PACKED slabs (0.5625 bytes per value instead of 2) are all-gathered. Nothing is quantized g
+times over, and whatever works row by row (a norm, a residual) runs on the slab.
+
 Two ways to obtain shards:
   * quantize each shard by itself (`quantize(w_shard)`), the reference's behaviour; or
   * slice an already quantized tensor (`slice_rows`, `slice_cols`): bit-identical to the
@@ -98,17 +106,17 @@ class TensorParallelLinear(nn.Module):
     `matmul_fn(x, w, input_config=..., out_dtype=...)` defaults to the FP4 GEMM; tests of
     the host logic substitute a CPU stand-in. `chunks` and `comm_sms` shape the overlap of a
     row-parallel layer: the tokens are cut into `chunks` pieces, and while pieces are in flight the
-    GEMM leaves `comm_sms` SMs idle, because a persistent grid on every SM would keep the
-    collective's kernel waiting until the GEMM has finished (the option is process-wide:
-    one row-parallel layer at a time per process). 32 is what NCCL's all-reduce launches on a
+    GEMM leaves `comm_sms` SMs idle (a per-call argument of the GEMM), because a persistent grid on
+    every SM would keep the collective's kernel waiting until the GEMM has finished. 32 is what NCCL's all-reduce launches on a
     pair of B200s; with fewer free SMs part of its grid still waits for the GEMM.
     """
 
     def __init__(self, weight: torch.Tensor | QuantizedTensor, config: ModuleQuantizationConfig, mode: str, *,
                  group: dist.ProcessGroup | None = None, bias: torch.Tensor | None = None, chunks: int = 4,
                  comm_sms: int = 32, fused: bool | None = None, peer_mode: str = "scatter",
+                 scatter_output: bool = False, scattered_input: bool = False,
                  matmul_fn: MatmulFn | None = None,
-                 quantize_fn: Callable | None = None) -> None:
+                 quantize_fn: Callable | None = None, amax_fn: Callable | None = None) -> None:
         super().__init__()
         if mode not in ("column", "row"):
             raise ValueError("mode must be 'column' or 'row'")
@@ -130,9 +138,18 @@ class TensorParallelLinear(nn.Module):
         if peer_mode not in ("pull", "scatter"):
             raise ValueError("peer_mode must be 'pull' or 'scatter'")
         self.peer_mode = peer_mode
+        # Row slabs between a row-parallel layer and the column-parallel layer after it (module docstring).
+        # Rank r's slab of a [tokens, n] tensor cut into `chunks` pieces is [chunks][tokens / (chunks * g)][n]:
+        # of every chunk of tokens / chunks rows, the r-th part (`scatter_rows` builds it from a full tensor).
+        if scatter_output and mode != "row":
+            raise ValueError("scatter_output belongs to a row-parallel layer")
+        if scattered_input and mode != "column":
+            raise ValueError("scattered_input belongs to a column-parallel layer")
+        self.scatter_output, self.scattered_input = scatter_output, scattered_input
         self._peer: dict | None = None
         self._matmul = matmul_fn or quantized_matmul
         self._quantize = quantize_fn or quantize
+        self._amax = amax_fn
         self.weight = weight if isinstance(weight, QuantizedTensor) else self._quantize(weight, config.get_weight_config())
         self.bias = bias
         self._comm_stream: torch.cuda.Stream | None = None
@@ -142,21 +159,120 @@ class TensorParallelLinear(nn.Module):
         return dist.get_world_size(self.group) if dist.is_initialized() else 1
 
     def _gemm(self, x: torch.Tensor | QuantizedTensor, act_cfg: QuantizationConfig,
-              out: torch.Tensor | None = None) -> torch.Tensor:
+              out: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
         extra = {} if out is None else {"out": out}
+        if max_ctas:
+            extra["max_ctas"] = max_ctas          # per call: nothing process-wide is touched
         return self._matmul(x, self.weight, input_config=act_cfg, out_dtype=self.config.output_dtype, **extra)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
         x2d = x.reshape(-1, x.shape[-1])
         act_cfg = self.config.get_activation_config()
-        if self.mode == "column" or self.world_size == 1:
+        if self.world_size == 1:
             out = self._gemm(x2d, act_cfg)
+        elif self.mode == "column":
+            out = self._gemm(self._gather_quantized(x2d, act_cfg) if self.scattered_input else x2d, act_cfg)
+        elif self.scatter_output:
+            out = self._row_parallel_scattered(x2d, act_cfg)
         else:
             out = self._row_parallel(x2d, act_cfg)
         if self.bias is not None:
+            if self.mode == "row" and self.scatter_output and self.world_size > 1:
+                raise ValueError("a bias on a scattered output is the caller's to add (once, by the rows' owner)")
             out = out + self.bias
+        if out.shape[0] != x2d.shape[0]:
+            return out                    # slab hand-off: the rows are not the input's rows (2-D in, 2-D out)
         return out.reshape(*lead, out.shape[-1])
+
+    # ------------------------------------------------------------------ row slabs between two layers
+
+    def _slab_chunks(self, tokens: int) -> int:
+        """How many chunks a tensor of `tokens` rows is cut into for the slab hand-off: the largest number not
+        above `chunks` for which every rank's part of a chunk is a whole number of 128-row blocks."""
+        world, n_chunks = self.world_size, self.chunks
+        while n_chunks > 1 and tokens % (128 * world * n_chunks):
+            n_chunks -= 1
+        if tokens % (128 * world * n_chunks):
+            raise ValueError(f"the slab hand-off needs tokens ({tokens}) to be a multiple of 128 * world size")
+        return n_chunks
+
+    def _row_parallel_scattered(self, x2d: torch.Tensor, act_cfg: QuantizationConfig) -> torch.Tensor:
+        """Row-parallel layer whose result stays scattered: per chunk of tokens the partial product, then a
+        reduce-scatter of the chunk on the communication stream while the next chunk's GEMM runs. Returns this
+        rank's slab [tokens / g, n] (layout: see __init__)."""
+        world, tokens = self.world_size, x2d.shape[0]
+        n_chunks = self._slab_chunks(tokens)
+        step, piece = tokens // n_chunks, tokens // (n_chunks * world)
+        n_out = self.weight.original_shape[0]
+        dtype = DataType(self.config.output_dtype).torch_dtype
+        xq = self._quantize(x2d, act_cfg)
+        partial = torch.empty(tokens, n_out, dtype=dtype, device=x2d.device)
+        slab = torch.empty(n_chunks * piece, n_out, dtype=dtype, device=x2d.device)
+        on_gpu = x2d.device.type == "cuda"
+        works = []
+        max_ctas = 0
+        if on_gpu:
+            if self._comm_stream is None:
+                self._comm_stream = torch.cuda.Stream(device=x2d.device)
+            compute = torch.cuda.current_stream(x2d.device)
+            if self.comm_sms > 0 and n_chunks > 1:
+                max_ctas = max(1, torch.cuda.get_device_properties(x2d.device).multi_processor_count - self.comm_sms)
+        for i in range(n_chunks):
+            part = partial[i * step: (i + 1) * step]
+            self._gemm(slice_rows(xq, i * step, (i + 1) * step), act_cfg, out=part, max_ctas=max_ctas)
+            mine = slab[i * piece: (i + 1) * piece]
+            if on_gpu:
+                done = torch.cuda.Event()
+                done.record(compute)
+                with torch.cuda.stream(self._comm_stream):
+                    self._comm_stream.wait_event(done)
+                    dist.reduce_scatter_tensor(mine, part, group=self.group)
+            else:
+                works.append(dist.reduce_scatter_tensor(mine, part, group=self.group, async_op=True))
+        if on_gpu:
+            compute.wait_stream(self._comm_stream)
+            partial.record_stream(self._comm_stream)
+        for w in works:
+            w.wait()
+        return slab
+
+    def _gather_quantized(self, slab: torch.Tensor, act_cfg: QuantizationConfig) -> QuantizedTensor:
+        """The quantized full activation from every rank's row slab: the ranks take the maximum of their slabs'
+        amax, each quantizes its slab with it (the bytes of those rows of the unsharded quantization: blocks of
+        16 along a row depend on nothing else), and codes and scales are all-gathered chunk by chunk into the
+        layout the GEMM reads."""
+        world = self.world_size
+        if act_cfg.block_scale_2d or act_cfg.transpose or act_cfg.rht or DataType(act_cfg.dtype) != DataType.nvfp4:
+            raise ValueError("the slab hand-off quantizes activations to NVFP4 with 1-D blocks, untransposed")
+        rows, k = slab.shape
+        tokens = rows * world
+        n_chunks = self._slab_chunks(tokens)
+        step, piece = tokens // n_chunks, rows // n_chunks
+        if self._amax is not None:
+            amax = self._amax(slab)
+        else:
+            from fouroversix_b200.quantize.backend import B200QuantizeBackend
+            amax = B200QuantizeBackend.amax(slab)
+        dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=self.group)
+        if self._quantize is quantize:
+            from fouroversix_b200.quantize.backend import B200QuantizeBackend
+            q = B200QuantizeBackend.quantize(slab, act_cfg, amax=amax)
+        else:
+            q = self._quantize(slab, act_cfg, amax=amax)
+        k_p = q.padded_shape[1]
+        codes = torch.empty(tokens, k_p // 2, dtype=torch.uint8, device=slab.device)
+        scales = torch.empty(tokens * k_p // 16, dtype=torch.uint8, device=slab.device)
+        sf_local = q.scale_factors.view(torch.uint8).reshape(-1)
+        per_row = k_p // 16                                  # scale bytes per row; 128-row groups are contiguous
+        for i in range(n_chunks):
+            dist.all_gather_into_tensor(codes[i * step: (i + 1) * step], q.values[i * piece: (i + 1) * piece].contiguous(),
+                                        group=self.group)
+            dist.all_gather_into_tensor(scales[i * step * per_row: (i + 1) * step * per_row],
+                                        sf_local[i * piece * per_row: (i + 1) * piece * per_row].contiguous(), group=self.group)
+        return QuantizedTensor(codes, scales.view(q.scale_factors.dtype), amax, q.dtype, (tokens, k), q.scale_rule,
+                               q.round_style, (tokens, k_p),
+                               scale_factors_are_in_blackwell_layout=q.scale_factors_are_in_blackwell_layout)
 
     def _peer_buffers(self, tokens: int, n_out: int, dtype: torch.dtype, dev: torch.device) -> dict:
         """Staging [world][tokens / world][n_out] and output [tokens][n_out] of this rank in symmetric
@@ -206,13 +322,26 @@ class TensorParallelLinear(nn.Module):
             k_local = self.weight.original_shape[1]
             if k_local * 1.5e-4 * world / (world - 1) < 2.0:
                 return None
-        try:
-            buf = self._peer_buffers(tokens, n_out, out_dtype.torch_dtype, x2d.device)
-        except Exception:                                  # symmetric memory is not available here
-            if self.fused:
-                raise
-            self.fused = False
-            return None
+        # Every rank must take the same path: one that falls back to NCCL while the others wait at a
+        # symmetric-memory barrier would hang the group. So the ranks agree (once per shape) on whether
+        # ALL of them could set the buffers up.
+        key = (tokens, n_out, out_dtype.torch_dtype)
+        if self._peer is None or self._peer["key"] != key:
+            failure: Exception | None = None
+            try:
+                self._peer_buffers(tokens, n_out, out_dtype.torch_dtype, x2d.device)
+            except Exception as exc:                       # symmetric memory is not available here
+                failure = exc
+            ok = torch.tensor([0 if failure else 1], dtype=torch.int32, device=x2d.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+            if int(ok.item()) == 0:
+                self._peer = None
+                if self.fused:
+                    raise RuntimeError("TensorParallelLinear: the peer-memory exchange could not be set up on every "
+                                       "rank") from failure
+                self.fused = False
+                return None
+        buf = self._peer
         rank = dist.get_rank(self.group)
         xq = self._quantize(x2d, act_cfg)
         if self.peer_mode == "pull":
@@ -263,18 +392,12 @@ class TensorParallelLinear(nn.Module):
             if self._comm_stream is None:
                 self._comm_stream = torch.cuda.Stream(device=x2d.device)
             compute = torch.cuda.current_stream(x2d.device)
-        limit_sms = on_gpu and self.comm_sms > 0 and self._matmul is quantized_matmul
-        if limit_sms:
-            sms = torch.cuda.get_device_properties(x2d.device).multi_processor_count
-            _native.lib().fos_set_option(_native.FOS_OPT_GEMM_MAX_CTAS, max(1, sms - self.comm_sms))
+        max_ctas = 0
+        if on_gpu and self.comm_sms > 0 and self._matmul is quantized_matmul:
+            max_ctas = max(1, torch.cuda.get_device_properties(x2d.device).multi_processor_count - self.comm_sms)
         for i in range(n_chunks):
             part = out[i * step: (i + 1) * step]
-            try:
-                self._gemm(slice_rows(xq, i * step, (i + 1) * step), act_cfg, out=part)
-            except BaseException:
-                if limit_sms:
-                    _native.lib().fos_set_option(_native.FOS_OPT_GEMM_MAX_CTAS, 0)
-                raise
+            self._gemm(slice_rows(xq, i * step, (i + 1) * step), act_cfg, out=part, max_ctas=max_ctas)
             if on_gpu:
                 done = torch.cuda.Event()
                 done.record(compute)
@@ -283,13 +406,29 @@ class TensorParallelLinear(nn.Module):
                     dist.all_reduce(part, group=self.group)
             else:
                 works.append(dist.all_reduce(part, group=self.group, async_op=True))
-        if limit_sms:
-            _native.lib().fos_set_option(_native.FOS_OPT_GEMM_MAX_CTAS, 0)
         if on_gpu:
             compute.wait_stream(self._comm_stream)
         for w in works:
             w.wait()
         return out
+
+
+def scatter_rows(x: torch.Tensor, rank: int, world: int, chunks: int = 1) -> torch.Tensor:
+    """Rank `rank`'s row slab of a full [tokens, n] tensor in the layout of the slab hand-off: of every
+    chunk of tokens / chunks rows the rank-th part, the parts stacked in chunk order."""
+    tokens = x.shape[0]
+    if tokens % (chunks * world):
+        raise ValueError(f"{tokens} rows do not split into {chunks} chunks of {world} parts")
+    piece = tokens // (chunks * world)
+    return x.reshape(chunks, world, piece, *x.shape[1:])[:, rank].reshape(chunks * piece, *x.shape[1:])
+
+
+def gather_rows(slabs: list[torch.Tensor], chunks: int = 1) -> torch.Tensor:
+    """Inverse of `scatter_rows`: the full tensor from the slabs of all ranks (rank order)."""
+    world = len(slabs)
+    piece = slabs[0].shape[0] // chunks
+    stacked = torch.stack([t.reshape(chunks, piece, *t.shape[1:]) for t in slabs], dim=1)   # [chunks, world, piece, ...]
+    return stacked.reshape(chunks * world * piece, *slabs[0].shape[1:])
 
 
 def shard_linear_weight(weight: torch.Tensor, mode: str, rank: int, world: int) -> torch.Tensor:

@@ -16,7 +16,8 @@
  *              (FOS_SF_TILED) or row-major [rows_p, cols_p / 16] (FOS_SF_ROWMAJOR)
  *       amax   one float, max |x| of the source tensor
  *     with rows_p = rows rounded up to 128 and cols_p = cols rounded up to 64.
- *   - The entry points are re-entrant; calls on different streams may overlap.
+ *   - The entry points are re-entrant and the library has no settings: what varies per call is an
+ *     argument. Calls on different streams or host threads may overlap.
  *
  * The "replaces" notes cite the reference project (mit-han-lab/fouroversix) by path.
  */
@@ -64,6 +65,10 @@ extern "C" {
                                           16-point random Hadamard transform (QuantizationConfig.rht,
                                           src/fouroversix/quantize/utils.py:19-85) before quantizing; the length of
                                           that axis (cols, or rows when transposing) must be a multiple of 16 */
+#define FOS_QUANTIZE_NO_TMA 4          /* kernel choice (testing aid; every kernel writes the same bytes): never a kernel
+                                          fed by the TMA unit, i.e. treat x as if it were not 16-byte aligned */
+#define FOS_QUANTIZE_GENERAL_KERNEL 8  /* kernel choice (testing aid): the general TMA-fed kernel also for the
+                                          configuration that has a kernel of its own (NVFP4 4/6 MSE, 1-D blocks) */
 
 int fos_version(void);
 const char *fos_status_string(int status);
@@ -98,6 +103,17 @@ int fos_quantize(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t
                  int format, int scale_rule, int block_2d, int transpose, int sf_layout,
                  const float *amax_in, uint8_t *codes, uint8_t *sf, float *amax_out,
                  int flags, void *stream);
+
+/*
+ * amax_out[0] = max |x| over x[rows, cols] (bf16 or fp16, row stride `ld` elements): the pass that
+ * fos_quantize runs when it is given no amax, on its own. For callers that quantize one tensor in
+ * pieces (row slabs on different GPUs): take the maximum of the pieces' values, pass it to every
+ * fos_quantize call as amax_in, and the pieces carry the bytes the whole tensor would.
+ *
+ * Replaces: x.abs().max() of src/fouroversix/quantize/pytorch/reference.py:573-578 and the first pass
+ * of the reference's CUDA kernel, src/fouroversix/csrc/include/fp4_quant_kernel.h:133-215.
+ */
+int fos_amax(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, float *amax_out, void *stream);
 
 /*
  * Dequantize Y (padded shape rows_p x cols_p) into out[rows, cols] (row stride
@@ -140,6 +156,27 @@ int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b
                    int32_t *status, void *stream);
 
 /*
+ * Per-call options of the FP4 GEMMs (the library keeps no process-wide settings). NULL = all zero.
+ *   variant   0 = choose the kernel per problem; 128 / 256 = single-CTA kernel with 128 x 128 /
+ *             128 x 256 tiles; 2 = CTA-pair kernel (256 x 256 tiles, cta_group::2) where the padded
+ *             M and N are multiples of 256, else the single-CTA kernel. Every variant computes the
+ *             same product (fp32 sums in a different order).
+ *   max_ctas  0 = one persistent CTA per SM; n > 0 = at most n CTAs, which leaves SMs free for a
+ *             kernel that must run beside the GEMM (a collective on another stream: a persistent
+ *             grid over every SM would keep it waiting until the GEMM has finished).
+ * No counterpart in the reference (its CUTLASS kernel has one tile shape and takes the whole GPU,
+ * src/fouroversix/csrc/fp4_gemm.cu:166-172).
+ */
+typedef struct fos_gemm_opts {
+    int32_t variant;
+    int32_t max_ctas;
+} fos_gemm_opts;
+int fos_gemm_nvfp4_ex(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                      const uint8_t *b_sf, const float *alpha, void *d, int out_dtype,
+                      int64_t m_p, int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd,
+                      const fos_gemm_opts *opts, int32_t *status, void *stream);
+
+/*
  * The same GEMM for two MXFP4 operands (E8M0 scale per 32 values, scales in the 128 x 4 tile
  * order as fos_quantize(FOS_MXFP4, FOS_SF_TILED) writes them): tcgen05.mma kind::mxf4 with
  * scale_vec::2X. k_p must be a multiple of 128; everything else as for fos_gemm_nvfp4. The
@@ -152,6 +189,10 @@ int fos_gemm_mxfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b
                    const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
                    int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, int32_t *status,
                    void *stream);
+int fos_gemm_mxfp4_ex(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                      const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,
+                      int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd,
+                      const fos_gemm_opts *opts, int32_t *status, void *stream);
 
 /*
  * Row-parallel layers over `world` GPUs of one node (2..8), in two kernels with a barrier between the ranks
@@ -214,9 +255,11 @@ int fos_gemm_if4(const uint8_t *a_codes, const uint8_t *a_sf, int a_format, int 
 
 /*
  * fos_gemm_if4 without a workspace argument, for callers that have no way to obtain device
- * scratch: code that runs where allocating is forbidden or impossible - inside a host callback
- * or another library's plug-in hook, under a memory pool that is already fully handed out, or in
- * a process whose allocator belongs to a different runtime. The expanded fp16 operands are kept
+ * scratch: code that runs where allocating is forbidden or impossible - in another library's
+ * plug-in hook that may launch kernels but must not touch the allocator, under a memory pool that
+ * is already fully handed out, or in a process whose allocator belongs to a different runtime.
+ * (It still makes CUDA runtime calls - kernel launches - so it is not for cudaLaunchHostFunc
+ * callbacks, which may make none.) The expanded fp16 operands are kept
  * in a buffer of FOS_GEMM_IF4_STATIC_WORKSPACE_BYTES that is part of the library image (each GPU
  * that loads the library holds that much memory until the process exits). The caller still passes
  * every input and output; the call performs no cudaMalloc / cudaFree and uses no allocating
@@ -265,29 +308,6 @@ int fos_quantize_stochastic(const void *x, int x_dtype, int64_t rows, int64_t co
 int fos_pseudo_quantize(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int format,
                         int scale_rule, const float *amax_in, void *out, int64_t ld_out, float *amax_out,
                         int flags, void *stream);
-
-/*
- * Process-wide tuning / testing knobs. No counterpart in the reference.
- *   FOS_OPT_GEMM_VARIANT   0 = choose the GEMM kernel per problem (default);
- *                          128 / 256 = single-CTA kernel with 128 x 128 / 128 x 256 tiles;
- *                          2 = CTA-pair kernel (256 x 256 tiles, cta_group::2) where the
- *                          padded M and N are multiples of 256, else the single-CTA kernel
- *   FOS_OPT_GEMM_DEBUG     timing experiments that make the GEMM's RESULT WRONG: bit 0 skips the
- *                          scale copies, bit 1 the operand loads, bit 2 the output stores.
- *                          Default 0. Only the profiling scripts set it.
- *   FOS_OPT_GEMM_MAX_CTAS  0 = one persistent CTA per SM (default); n > 0 = at most n CTAs, which leaves
- *                          SMs free for kernels that must run beside the GEMM (a collective on another
- *                          stream: a persistent grid over every SM would keep it waiting)
- *   FOS_OPT_QUANTIZE_VARIANT  0 = 1-D, untransposed inputs that are 16-byte aligned (base and row
- *                          stride) go through the kernel fed by the TMA unit, the rest through
- *                          the kernel that loads from registers (default); 1 = never the
- *                          TMA-fed kernel. Both produce the same bytes.
- */
-#define FOS_OPT_GEMM_VARIANT 1
-#define FOS_OPT_GEMM_DEBUG 2
-#define FOS_OPT_QUANTIZE_VARIANT 3
-#define FOS_OPT_GEMM_MAX_CTAS 4
-int fos_set_option(int key, int value);
 
 /*
  * Diagnostics for the quantize kernels, which have no status argument: *site (host memory)

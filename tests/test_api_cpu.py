@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     assert not missing, missing
     # the Python binding table and the header agree
     assert declared == set(_native.SIGNATURES), declared ^ set(_native.SIGNATURES)
-    assert lib.fos_version() >= 100
+    assert lib.fos_version() >= 200
     assert lib.fos_status_string(0) == b"ok"
     assert b"invalid" in lib.fos_status_string(-1)
 
@@ -35,8 +35,11 @@ def test_argument_validation_needs_no_gpu():
     lib = _native.lib()
     # NULL pointers and bad enums are rejected before any CUDA call
     assert lib.fos_quantize(0, 0, 128, 64, 64, 0, 3, 0, 0, 1, 0, 0, 0, 0, 0, 0) == -1
-    assert lib.fos_set_option(1, 192) == -1
-    assert lib.fos_set_option(1, 0) == 0
+    # a kernel variant that does not exist is rejected before anything else is looked at
+    bad = _native.GemmOpts(192, 0)
+    import ctypes
+    assert lib.fos_gemm_nvfp4_ex(0, 0, 0, 0, 0, 0, 0, 128, 128, 64, 128, 128, 128, ctypes.byref(bad), 0, 0) == -1
+    assert not hasattr(lib, "fos_set_option")      # the library has no process-wide settings
 
 
 def test_enums_and_config_coercion():
@@ -106,3 +109,22 @@ def test_module_config_inherits_defaults():
         block_scale_2d=True, scale_rule="static_6", transpose=True)
     assert c.get_gradient_config().round_style is fos.RoundStyle.stochastic
     assert isinstance(fos.ModelQuantizationConfig().__hash__(), str)
+
+
+def test_backward_refuses_settings_it_does_not_implement():
+    """Settings the reference's backward pass acts on (src/fouroversix/model/modules/linear.py:213-229,
+    258-268) and this layer does not are refused, not silently ignored."""
+    import torch
+
+    from fouroversix_b200.model.linear import FourOverSixLinearFunction
+
+    x, w, dy = torch.zeros(16, 64), torch.zeros(32, 64), torch.zeros(16, 32)
+    for kwargs in (dict(wgrad_nvint4=True), dict(disable_dgrad_quantization="quantize_grad_only"),
+                   dict(quartet_ii_dtype="nvfp4"), dict(gradient_round_style="stochastic_unbiased")):
+        class Ctx:
+            saved_tensors = (x, w, None)
+            config = fos.ModuleQuantizationConfig(**kwargs)
+            needs_input_grad = (False, True, True, False)
+
+        with pytest.raises(NotImplementedError):
+            FourOverSixLinearFunction.backward(Ctx, dy)

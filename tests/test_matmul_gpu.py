@@ -66,12 +66,10 @@ def test_hand_built_operands(block_n):
     """All ones times all ones is K; then random codes and scales catch a wrong scale-tile or
     swizzle mapping. `block_n` selects the kernel: single-CTA 128- or 256-wide tiles, or 2 =
     the CTA-pair kernel."""
-    lib = _native.lib()
-    assert lib.fos_set_option(1, block_n) == 0
     try:
         m, n, k = 256, 256, 512
         a, b = _synthetic(m, k, 0x22, 0x38), _synthetic(n, k, 0x22, 0x38)     # 1.0 values, 1.0 scales
-        out = B200MatmulBackend.quantized_matmul(a, b, out_dtype=fos.DataType.float32, check_status=True)
+        out = B200MatmulBackend.quantized_matmul(a, b, out_dtype=fos.DataType.float32, check_status=True, variant=block_n)
         assert torch.equal(out, torch.full((m, n), float(k), device=DEV))
 
         g = torch.Generator().manual_seed(0)
@@ -80,33 +78,29 @@ def test_hand_built_operands(block_n):
         # positive, finite E4M3 scales between 2^-3 and 8
         a.scale_factors.view(torch.uint8).copy_(torch.randint(0x20, 0x50, (m * k // 16,), generator=g, dtype=torch.uint8))
         b.scale_factors.view(torch.uint8).copy_(torch.randint(0x20, 0x50, (n * k // 16,), generator=g, dtype=torch.uint8))
-        out = B200MatmulBackend.quantized_matmul(a, b, out_dtype=fos.DataType.float32, check_status=True)
+        out = B200MatmulBackend.quantized_matmul(a, b, out_dtype=fos.DataType.float32, check_status=True, variant=block_n)
         ref = _dense_reference(a, b)
         # every product is exactly representable and the sums stay below 2^24 ulps: tight bound
         assert ((out - ref).abs().max() / ref.abs().max()).item() < 1e-5
     finally:
-        lib.fos_set_option(1, 0)
+        pass
 
 
 @pytest.mark.parametrize(("m", "n", "k"), list(itertools.product([256, 512, 1024], repeat=3)))
 @pytest.mark.parametrize("scale_rule", ["static_6", "static_4", "mse"])
 @pytest.mark.parametrize("variant", [0, 2], ids=["auto", "cta-pair"])
 def test_matmul_against_oracle(oracle, m, n, k, scale_rule, variant):
-    _native.lib().fos_set_option(1, variant)
-    try:
-        _matmul_against_oracle(oracle, m, n, k, scale_rule)
-    finally:
-        _native.lib().fos_set_option(1, 0)
+    _matmul_against_oracle(oracle, m, n, k, scale_rule, variant)
 
 
-def _matmul_against_oracle(oracle, m, n, k, scale_rule):
+def _matmul_against_oracle(oracle, m, n, k, scale_rule, variant=0):
     for seed in range(2):
         g = torch.Generator().manual_seed(seed)
         x = torch.randn(m, k, generator=g).bfloat16()
         y = torch.randn(n, k, generator=g).bfloat16()
         cfg = fos.QuantizationConfig(scale_rule=scale_rule)
         qx, qy = fos.quantize(x.to(DEV), cfg), fos.quantize(y.to(DEV), cfg)
-        out = B200MatmulBackend.quantized_matmul(qx, qy, out_dtype=fos.DataType.bfloat16, check_status=True)
+        out = B200MatmulBackend.quantized_matmul(qx, qy, out_dtype=fos.DataType.bfloat16, check_status=True, variant=variant)
         ox, oy = oracle.quantize(x, scale_rule=scale_rule), oracle.quantize(y, scale_rule=scale_rule)
         want = oracle.matmul(ox, oy, torch.bfloat16) if m * n * k <= 256 * 512 * 1024 else None
         ref32 = _dense_reference(qx, qy)
@@ -139,11 +133,7 @@ def test_ragged_shapes_and_output_types(shape, out_dtype):
     y = (torch.randn(n, k, generator=g) * 0.05).bfloat16().to(DEV)
     qx, qy = fos.quantize(x), fos.quantize(y)
     for block_n in (128, 256, 2):
-        _native.lib().fos_set_option(1, block_n)
-        try:
-            out = B200MatmulBackend.quantized_matmul(qx, qy, out_dtype=fos.DataType(out_dtype), check_status=True)
-        finally:
-            _native.lib().fos_set_option(1, 0)
+        out = B200MatmulBackend.quantized_matmul(qx, qy, out_dtype=fos.DataType(out_dtype), check_status=True, variant=block_n)
         ref32 = _dense_reference(qx, qy)
         if out_dtype == "float32":
             assert ((out - ref32).abs().max() / ref32.abs().max()).item() < 1e-5
@@ -265,11 +255,7 @@ def test_mxfp4_matmul_against_oracle(oracle, m, n, k, out_dtype):
     qa, qb = fos.quantize(a.to(DEV), cfg), fos.quantize(b.to(DEV), cfg)
     ref32 = _dense_reference(qa, qb)
     for block_n in (128, 256):
-        _native.lib().fos_set_option(1, block_n)
-        try:
-            out = B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType(out_dtype), check_status=True)
-        finally:
-            _native.lib().fos_set_option(1, 0)
+        out = B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType(out_dtype), check_status=True, variant=block_n)
         what = f"mxfp4 {m}x{n}x{k} {out_dtype} block_n={block_n}"
         if out_dtype == "float32":
             assert ((out - ref32).abs().max() / ref32.abs().max()).item() < 1e-5, what

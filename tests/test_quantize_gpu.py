@@ -165,10 +165,11 @@ def test_full_size_configs_bit_exact(oracle, name, shape, seed, cfg):
     assert (back - xf).abs().max() <= 0.26 * x.float().abs().max()
 
 
-@pytest.mark.parametrize("variant", [0, 1], ids=["tma-fed", "register-loads"])
-def test_both_row_kernels_match_the_oracle(oracle, variant):
-    """1-D untransposed inputs have two kernels (fed by the TMA unit / loading into registers);
-    both must give the reference's bytes, with and without a caller-supplied amax (the first
+@pytest.mark.parametrize("kernel", ["auto", "general", "no_tma"], ids=["specialised", "tma-fed", "register-loads"])
+def test_both_row_kernels_match_the_oracle(oracle, kernel):
+    """1-D untransposed inputs have three kernels (the one for NVFP4 4/6 MSE alone, the general one fed by
+    the TMA unit, the one loading into registers; a per-call flag picks one);
+    all must give the reference's bytes, with and without a caller-supplied amax (the first
     walks the tiles forwards, the second backwards), on full, ragged and tiny shapes."""
     import ctypes
 
@@ -177,7 +178,6 @@ def test_both_row_kernels_match_the_oracle(oracle, variant):
     lib = _native.lib()
     g = torch.Generator().manual_seed(21)
     shapes = [(8, 16), (100, 80), (129, 72), (128, 64), (640, 4096), (1000, 328), (257, 8200)]
-    assert lib.fos_set_option(3, variant) == 0
     try:
         for shape in shapes:
             x = torch.randn(shape, generator=g).bfloat16()
@@ -189,7 +189,7 @@ def test_both_row_kernels_match_the_oracle(oracle, variant):
                         dict(block_scale_2d=True, scale_rule="static_6"), dict(block_scale_2d=True, dtype="if4")):
                 ref = oracle.quantize(x, **cfg)
                 for given in (None, amax):
-                    q = B200QuantizeBackend.quantize(xd, fos.QuantizationConfig(**cfg), amax=given)
+                    q = B200QuantizeBackend.quantize(xd, fos.QuantizationConfig(**cfg), amax=given, kernel=kernel)
                     _assert_same(q, ref.values, ref.scale_factors, ref.amax, f"{shape} {cfg} amax given={given is not None}")
         # transposed inputs have the same pair of kernels (sizes the reference accepts: multiples of 128)
         for shape in [(128, 256), (640, 4096), (1152, 384)]:
@@ -202,14 +202,14 @@ def test_both_row_kernels_match_the_oracle(oracle, variant):
                         dict(transpose=True, block_scale_2d=True, scale_rule="mae")):
                 ref = oracle.quantize(x, **cfg)
                 for given in (None, amax):
-                    q = B200QuantizeBackend.quantize(xd, fos.QuantizationConfig(**cfg), amax=given)
+                    q = B200QuantizeBackend.quantize(xd, fos.QuantizationConfig(**cfg), amax=given, kernel=kernel)
                     _assert_same(q, ref.values, ref.scale_factors, ref.amax, f"{shape} {cfg} amax given={given is not None}")
         xh = torch.randn(300, 264, generator=g).half()
         ref = oracle.quantize(xh)
-        q = fos.quantize(xh.to(DEV), fos.QuantizationConfig())
+        q = B200QuantizeBackend.quantize(xh.to(DEV), fos.QuantizationConfig(), kernel=kernel)
         _assert_same(q, ref.values, ref.scale_factors, ref.amax, "fp16 300x264")
     finally:
-        lib.fos_set_option(3, 0)
+        pass
     site = ctypes.c_int32(-1)
     assert lib.fos_wait_failure_site(ctypes.byref(site)) == 0 and site.value == 0
 
@@ -237,8 +237,8 @@ def test_fused_fake_quantization_equals_quantize_then_dequantize(oracle):
             assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16)), (tuple(x.shape), x.dtype, cfg)
 
 
-@pytest.mark.parametrize("variant", [0, 1], ids=["tma-fed", "register-loads"])
-def test_random_hadamard_transform_matches_reference_and_oracle(oracle, variant):
+@pytest.mark.parametrize("kernel", ["auto", "no_tma"], ids=["tma-fed", "register-loads"])
+def test_random_hadamard_transform_matches_reference_and_oracle(oracle, kernel):
     """QuantizationConfig.rht: the committed vectors of the reference (rotation + quantization on
     CPU) and larger seeded inputs against the oracle, plain and transposed, with both kernel families."""
     import io
@@ -249,12 +249,10 @@ def test_random_hadamard_transform_matches_reference_and_oracle(oracle, variant)
 
     raw = lzma.decompress((Path(__file__).parent / "golden" / "reference_golden_rht.pt.xz").read_bytes())
     gold = torch.load(io.BytesIO(raw), weights_only=False)
-    lib = _native.lib()
-    assert lib.fos_set_option(3, variant) == 0
     try:
         for case in gold["cases"]:
             x = gold["inputs"][case["input"]]
-            q = fos.quantize(x.to(DEV), fos.QuantizationConfig(rht=True, **case["config"]))
+            q = B200QuantizeBackend.quantize(x.to(DEV), fos.QuantizationConfig(rht=True, **case["config"]), kernel=kernel)
             torch.cuda.synchronize()
             v = case["values"]
             assert torch.equal(q.values.cpu()[: v.shape[0], : v.shape[1]], v), (case["input"], case["config"])
@@ -268,10 +266,10 @@ def test_random_hadamard_transform_matches_reference_and_oracle(oracle, variant)
             for cfg in (dict(), dict(transpose=True), dict(transpose=True, scale_rule="static_6"), dict(dtype="if4"),
                         dict(transpose=True, block_scale_2d=True)):
                 ref = oracle.quantize(x, rht=True, **cfg)
-                q = fos.quantize(xd, fos.QuantizationConfig(rht=True, **cfg))
+                q = B200QuantizeBackend.quantize(xd, fos.QuantizationConfig(rht=True, **cfg), kernel=kernel)
                 _assert_same(q, ref.values, ref.scale_factors, ref.amax, f"rht {shape} {cfg}")
     finally:
-        lib.fos_set_option(3, 0)
+        pass
 
 
 def test_stochastic_rounding_statistics():

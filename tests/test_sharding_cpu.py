@@ -17,14 +17,14 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 import fouroversix_b200 as fos
-from fouroversix_b200.sharding import (TensorParallelLinear, shard_bounds, shard_linear_weight, slice_cols,
-                                       slice_rows)
+from fouroversix_b200.sharding import (TensorParallelLinear, gather_rows, scatter_rows, shard_bounds,
+                                       shard_linear_weight, slice_cols, slice_rows)
 from oracle import fos_oracle
 
 
-def cpu_quantize(x: torch.Tensor, config: fos.QuantizationConfig) -> fos.QuantizedTensor:
+def cpu_quantize(x: torch.Tensor, config: fos.QuantizationConfig, amax: torch.Tensor | None = None) -> fos.QuantizedTensor:
     ref = fos_oracle.quantize(x.contiguous(), dtype=config.dtype, scale_rule=config.scale_rule,
-                              block_scale_2d=config.block_scale_2d, transpose=config.transpose)
+                              block_scale_2d=config.block_scale_2d, transpose=config.transpose, amax=amax)
     return fos.QuantizedTensor(ref.values, ref.scale_factors.view(torch.float8_e4m3fn), ref.amax, config.dtype,
                                ref.original_shape, config.scale_rule, config.round_style, ref.padded_shape,
                                scale_factors_are_in_blackwell_layout=ref.tiled)
@@ -78,19 +78,22 @@ def _worker(rank: int, world: int, port: int, results):
     try:
         torch.set_num_threads(2)
         g = torch.Generator().manual_seed(1)
-        tokens, hidden, inner = 512, 256, 512
+        tokens, hidden, inner = 1024, 256, 512
         x = torch.randn(tokens, hidden, generator=g).bfloat16()
         w_up = (torch.randn(inner, hidden, generator=g) * 0.05).bfloat16()      # column parallel
         w_down = (torch.randn(hidden, inner, generator=g) * 0.05).bfloat16()    # row parallel
+        w_next = (torch.randn(inner, hidden, generator=g) * 0.05).bfloat16()    # column parallel, fed by row slabs
         cfg = fos.ModuleQuantizationConfig(output_dtype="float32")
-        kw = dict(matmul_fn=cpu_matmul, quantize_fn=cpu_quantize)
+        kw = dict(matmul_fn=cpu_matmul, quantize_fn=cpu_quantize, amax_fn=lambda t: t.abs().max().float().reshape(1))
         up = TensorParallelLinear(shard_linear_weight(w_up, "column", rank, world), cfg, "column", **kw)
-        down = TensorParallelLinear(shard_linear_weight(w_down, "row", rank, world), cfg, "row", chunks=2, **kw)
+        w_down_shard = shard_linear_weight(w_down, "row", rank, world)
+        down = TensorParallelLinear(w_down_shard, cfg, "row", chunks=2, **kw)
         h = up(x)                                        # [tokens, inner / world], stays sharded
         assert h.shape == (tokens, inner // world)
         y = down(h.bfloat16())                           # all-reduced: identical on every rank
 
-        # the same computation without torch.distributed: per-shard products summed in fp32
+        # the oracle's answer without torch.distributed: per-shard fp32 products (each shard quantized by itself,
+        # with its own amax and alpha), row-parallel partials summed in fp32
         want = torch.zeros(tokens, hidden)
         for r in range(world):
             h_r = cpu_matmul(x, cpu_quantize(shard_linear_weight(w_up, "column", r, world), cfg.get_weight_config()),
@@ -101,13 +104,32 @@ def _worker(rank: int, world: int, port: int, results):
         gathered = [torch.empty_like(y) for _ in range(world)]
         dist.all_gather(gathered, y)
         same = all(torch.equal(gathered[0], t) for t in gathered)
-        results[rank] = (err, same, tuple(y.shape))
+
+        # the slab hand-off: the same row-parallel layer leaves its result scattered by rows, the next
+        # column-parallel layer quantizes its slab with the common amax and gathers the packed slabs
+        chunks = 2
+        down_s = TensorParallelLinear(w_down_shard, cfg, "row", chunks=chunks, scatter_output=True, **kw)
+        nxt = TensorParallelLinear(shard_linear_weight(w_next, "column", rank, world), cfg, "column", chunks=chunks,
+                                   scattered_input=True, **kw)
+        slab = down_s(h.bfloat16())
+        slab_err = ((slab - scatter_rows(want, rank, world, chunks)).abs().max() / want.abs().max()).item()
+        slabs = [torch.empty_like(slab) for _ in range(world)]
+        dist.all_gather(slabs, slab)
+        full = gather_rows(slabs, chunks).bfloat16()     # what an all-reduce would have left on every rank
+        xq = nxt._gather_quantized(slab.bfloat16(), cfg.get_activation_config())
+        ref = fos_oracle.quantize(full)                  # the unsharded quantization of the full activation
+        packed_equal = (torch.equal(xq.values, ref.values) and torch.equal(xq.amax, ref.amax)
+                        and torch.equal(xq.scale_factors.view(torch.uint8).flatten(), ref.scale_factors))
+        z = nxt(slab.bfloat16())
+        z_want = cpu_matmul(full, cpu_quantize(shard_linear_weight(w_next, "column", rank, world), cfg.get_weight_config()),
+                            out_dtype=fos.DataType.float32)
+        results[rank] = (err, same, tuple(y.shape), slab_err, packed_equal, torch.equal(z, z_want), tuple(slab.shape))
     finally:
         dist.destroy_process_group()
 
 
-def test_column_then_row_parallel_matches_unsharded_sum():
-    world = 2
+@pytest.mark.parametrize("world", [2, 4])
+def test_column_then_row_parallel_matches_unsharded_sum(world):
     ctx = mp.get_context("spawn")
     results = ctx.Manager().dict()
     port = _free_port()
@@ -115,13 +137,33 @@ def test_column_then_row_parallel_matches_unsharded_sum():
     for p in procs:
         p.start()
     for p in procs:
-        p.join(180)
-        assert p.exitcode == 0
+        p.join(240)
+    stuck = [p for p in procs if p.is_alive()]
+    for p in stuck:
+        p.terminate()
+    assert not stuck, "a rank did not finish"
+    assert all(p.exitcode == 0 for p in procs)
     for r in range(world):
-        err, same, shape = results[r]
-        assert shape == (512, 256)
+        err, same, shape, slab_err, packed_equal, z_equal, slab_shape = results[r]
+        assert shape == (1024, 256)
         assert same, "ranks disagree after the all-reduce"
-        assert err < 1e-5, err
+        assert err < 1e-5, err                   # fp32 partials, fp32 sum: only the order of the additions differs
+        assert slab_shape == (1024 // world, 256)
+        assert slab_err < 1e-5, slab_err
+        assert packed_equal, "slabs quantized with the common amax must carry the bytes of the unsharded quantization"
+        assert z_equal
+
+
+def test_scatter_and_gather_rows_are_inverse():
+    x = torch.arange(48 * 3, dtype=torch.float32).reshape(48, 3)
+    for world, chunks in ((2, 1), (4, 3), (3, 2)):
+        slabs = [scatter_rows(x, r, world, chunks) for r in range(world)]
+        assert slabs[0].shape == (48 // world, 3)
+        assert torch.equal(gather_rows(slabs, chunks), x)
+    # rank 1 of 2 with 2 chunks of 24 rows owns rows 12..23 and 36..47
+    assert torch.equal(scatter_rows(x, 1, 2, 2)[:, 0] / 3, torch.cat([torch.arange(12, 24), torch.arange(36, 48)]).float())
+    with pytest.raises(ValueError):
+        scatter_rows(x, 0, 5, 1)
 
 
 def test_layer_rejects_unknown_exchange_and_column_slices_follow_the_block_size():
@@ -130,6 +172,10 @@ def test_layer_rejects_unknown_exchange_and_column_slices_follow_the_block_size(
         TensorParallelLinear(w, fos.ModuleQuantizationConfig(), "row", peer_mode="ring", quantize_fn=cpu_quantize)
     with pytest.raises(ValueError, match="mode"):
         TensorParallelLinear(w, fos.ModuleQuantizationConfig(), "diagonal", quantize_fn=cpu_quantize)
+    with pytest.raises(ValueError, match="scatter_output"):
+        TensorParallelLinear(w, fos.ModuleQuantizationConfig(), "column", scatter_output=True, quantize_fn=cpu_quantize)
+    with pytest.raises(ValueError, match="scattered_input"):
+        TensorParallelLinear(w, fos.ModuleQuantizationConfig(), "row", scattered_input=True, quantize_fn=cpu_quantize)
     # MXFP4: a 512-byte scale tile covers 128 columns, so column slices come in multiples of 128
     ref = fos_oracle.quantize(torch.randn(128, 256).bfloat16(), dtype="mxfp4", scale_rule="static_6")
     q = fos.QuantizedTensor(ref.values, ref.scale_factors.view(torch.float8_e8m0fnu), ref.amax, "mxfp4", ref.original_shape,

@@ -1,9 +1,16 @@
-"""Tensor-parallel FP4 linear layers on 2 GPUs over NCCL (skipped with fewer than 2 GPUs).
+"""Tensor-parallel FP4 linear layers on 2, 4 and 8 GPUs over NCCL (each case is skipped with fewer GPUs).
 
-Column-parallel then row-parallel, the way a transformer MLP is split; the row-parallel
-output after the chunk-overlapped all-reduce must equal the sum of the per-shard products
-computed on one GPU, and shards sliced out of a quantized tensor must reproduce the
-unsharded GEMM.
+Column-parallel then row-parallel, the way a transformer MLP is split. The expectation comes from the
+ORACLE, shard by shard, as the reference behaves under vLLM's tensor parallelism
+(src/fouroversix/integrations/vllm_quantization.py:100-124: every rank quantizes its own shard with its
+own amax): oracle.quantize + oracle.matmul(out fp32) on each shard's tensors, the row-parallel partials
+summed in fp32. Every form of the exchange is compared with it: NCCL all-reduce beside the GEMM, the two
+peer-memory forms, and the row-slab hand-off (reduce-scatter, common amax, all-gather of packed slabs).
+
+Tolerances. Against the fp32 sum of fp32 partials the layers differ by (a) the rounding of every partial
+to bf16 (2^-9 relative each), (b) the order of the fp32 additions inside the GEMM, (c) for NCCL, sums
+taken in bf16: max |error| <= 2e-2 * max |want| for NCCL paths, 1e-2 for the peer-memory paths (one
+rounding of each partial, fp32 sum by the owner). Packed slabs of the hand-off: bit-exact.
 """
 
 from __future__ import annotations
@@ -18,6 +25,8 @@ import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
 
+TOKENS, HIDDEN, INNER = 2048, 512, 2048
+
 
 def _free_port() -> int:
     with socket.socket() as s:
@@ -25,73 +34,113 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
+def _inputs():
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(TOKENS, HIDDEN, generator=g).bfloat16()
+    w_up = (torch.randn(INNER, HIDDEN, generator=g) * 0.05).bfloat16()
+    w_down = (torch.randn(HIDDEN, INNER, generator=g) * 0.05).bfloat16()
+    w_next = (torch.randn(INNER, HIDDEN, generator=g) * 0.05).bfloat16()
+    return x, w_up, w_down, w_next
+
+
+def _oracle_expectation(world: int):
+    """What the reference computes shard by shard (CPU): h_r = bf16(q(x) @ q(w_up_r)^T),
+    want = sum_r fp32(q(h_r) @ q(w_down_r)^T), plus the column-parallel layer after it on the bf16 sum."""
+    from fouroversix_b200.sharding import shard_linear_weight
+    from oracle import fos_oracle
+
+    x, w_up, w_down, w_next = _inputs()
+    ox = fos_oracle.quantize(x)
+    want = torch.zeros(TOKENS, HIDDEN)
+    hs = []
+    for r in range(world):
+        h_r = fos_oracle.matmul(ox, fos_oracle.quantize(shard_linear_weight(w_up, "column", r, world).contiguous()), torch.bfloat16)
+        hs.append(h_r)
+        want += fos_oracle.matmul(fos_oracle.quantize(h_r),
+                                  fos_oracle.quantize(shard_linear_weight(w_down, "row", r, world).contiguous()), torch.float32)
+    return hs, want
+
+
 def _worker(rank: int, world: int, port: int, results):
     import fouroversix_b200 as fos
-    from fouroversix_b200.sharding import TensorParallelLinear, shard_bounds, shard_linear_weight, slice_cols, slice_rows
+    from fouroversix_b200.sharding import (TensorParallelLinear, gather_rows, scatter_rows, shard_bounds,
+                                           shard_linear_weight, slice_cols, slice_rows)
+    from oracle import fos_oracle
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         dev = torch.device("cuda", rank)
-        g = torch.Generator().manual_seed(1)
-        tokens, hidden, inner = 1024, 512, 1024
-        x = torch.randn(tokens, hidden, generator=g).bfloat16().to(dev)
-        w_up = (torch.randn(inner, hidden, generator=g) * 0.05).bfloat16().to(dev)
-        w_down = (torch.randn(hidden, inner, generator=g) * 0.05).bfloat16().to(dev)
+        x, w_up, w_down, w_next = (t.to(dev) for t in _inputs())
+        hs, want = _oracle_expectation(world)
+        want = want.to(dev)
+        scale = want.abs().max()
         cfg = fos.ModuleQuantizationConfig()
         up = TensorParallelLinear(shard_linear_weight(w_up, "column", rank, world), cfg, "column")
         w_down_shard = shard_linear_weight(w_down, "row", rank, world).contiguous()
-        down = TensorParallelLinear(w_down_shard, cfg, "row", chunks=4, fused=False)      # NCCL beside the GEMM
-        down_peer, down_scatter = (TensorParallelLinear(w_down_shard, cfg, "row", fused=True, peer_mode=mode)
-                                   for mode in ("pull", "scatter"))                         # the exchange over peer memory, both forms
         h = up(x)
-        y = down(h)
-        try:
-            y_peer = down_peer(h).clone()
-            y_peer_again = down_peer(h).clone()            # the buffers are reused
-            y_scatter = down_scatter(h).clone()
-            peer_used = True
-        except (RuntimeError, OSError, AttributeError, ImportError) as exc:   # symmetric memory cannot be set up on this machine
-            print(f"rank {rank}: peer-memory exchange unavailable: {exc}")
-            y_peer = y_peer_again = y_scatter = y.clone()
-            peer_used = False
-        torch.cuda.synchronize()
+        out = {"h_equal": torch.equal(h.cpu(), hs[rank])}          # column-parallel output: the oracle's bf16 bits?
+        h_frac = (h.cpu() != hs[rank]).float().mean().item()
+        out["h_frac"] = h_frac
 
-        # the same on this GPU alone: per-shard products in bf16 (what each rank contributes), summed
-        want = torch.zeros(tokens, hidden, dtype=torch.float32, device=dev)
-        for r in range(world):
-            h_r = fos.quantized_matmul(x, shard_linear_weight(w_up, "column", r, world))
-            want += fos.quantized_matmul(h_r, shard_linear_weight(w_down, "row", r, world).contiguous()).float()
-        err = ((y.float() - want).abs().max() / want.abs().max()).item()
-        peer_err = ((y_peer.float() - want).abs().max() / want.abs().max()).item()
-        # both forms add the same bf16 partials in the same order
-        peer_repeatable = torch.equal(y_peer, y_peer_again) and torch.equal(y_peer, y_scatter)
-        # every rank must hold the same bits: only a slab's owner computes it
-        gathered = [torch.empty_like(y_peer) for _ in range(world)]
-        dist.all_gather(gathered, y_peer)
-        peer_same = all(torch.equal(gathered[0], t) for t in gathered)
+        def rel(y):
+            return ((y.float() - want).abs().max() / scale).item()
+
+        down = TensorParallelLinear(w_down_shard, cfg, "row", chunks=4, fused=False)      # NCCL beside the GEMM
+        out["nccl"] = rel(down(h))
+        for mode in ("pull", "scatter"):
+            layer = TensorParallelLinear(w_down_shard, cfg, "row", fused=True, peer_mode=mode)
+            try:
+                y1 = layer(h).clone()
+                y2 = layer(h).clone()                                 # the buffers are reused
+            except RuntimeError as exc:                               # every rank raises together (collective decision)
+                out[mode] = f"unavailable: {str(exc)[:120]}"
+                continue
+            gathered = [torch.empty_like(y1) for _ in range(world)]
+            dist.all_gather(gathered, y1)
+            out[mode] = (rel(y1), torch.equal(y1, y2), all(torch.equal(gathered[0], t) for t in gathered))
+
+        # row-slab hand-off into the next column-parallel layer
+        chunks = 2
+        down_s = TensorParallelLinear(w_down_shard, cfg, "row", chunks=chunks, scatter_output=True)
+        nxt = TensorParallelLinear(shard_linear_weight(w_next, "column", rank, world), cfg, "column", chunks=chunks,
+                                   scattered_input=True)
+        slab = down_s(h)
+        out["slab"] = ((slab.float() - scatter_rows(want, rank, world, chunks)).abs().max() / scale).item()
+        slabs = [torch.empty_like(slab) for _ in range(world)]
+        dist.all_gather(slabs, slab)
+        full = gather_rows(slabs, chunks)
+        xq = nxt._gather_quantized(slab, cfg.get_activation_config())
+        ref = fos_oracle.quantize(full.cpu())                        # the unsharded quantization of the same rows
+        out["packed_equal"] = (torch.equal(xq.values.cpu(), ref.values) and torch.equal(xq.amax.cpu(), ref.amax)
+                               and torch.equal(xq.scale_factors.view(torch.uint8).flatten().cpu(), ref.scale_factors))
+        z = nxt(slab)
+        z_want = fos.quantized_matmul(full, shard_linear_weight(w_next, "column", rank, world))
+        out["next_equal"] = torch.equal(z, z_want)
 
         # shard-after-quantize: slices of one quantized weight reproduce the unsharded GEMM exactly
         qw = fos.quantize(w_up)
-        full = fos.quantized_matmul(x, qw, out_dtype=fos.DataType.float32)
-        lo, hi = shard_bounds(inner, rank, world, 128)
+        full_mm = fos.quantized_matmul(x, qw, out_dtype=fos.DataType.float32)
+        lo, hi = shard_bounds(INNER, rank, world, 128)
         part = fos.quantized_matmul(x, slice_rows(qw, lo, hi), out_dtype=fos.DataType.float32)
-        rows_equal = torch.equal(part, full[:, lo:hi])
+        out["rows_equal"] = torch.equal(part, full_mm[:, lo:hi])
         qx = fos.quantize(x)
-        klo, khi = shard_bounds(hidden, rank, world, 64)
+        klo, khi = shard_bounds(HIDDEN, rank, world, 64)
         partial = fos.quantized_matmul(slice_cols(qx, klo, khi), slice_cols(qw, klo, khi), out_dtype=fos.DataType.float32)
         dist.all_reduce(partial)
-        k_err = ((partial - full).abs().max() / full.abs().max()).item()
-        results[rank] = (err, rows_equal, k_err, tuple(y.shape), peer_used, peer_err, peer_repeatable, peer_same)
+        out["k_err"] = ((partial - full_mm).abs().max() / full_mm.abs().max()).item()
+        from fouroversix_b200 import _native
+        out["wait_failure_site"] = _native.wait_failure_site()
+        results[rank] = out
     finally:
         dist.destroy_process_group()
 
 
-def test_column_then_row_parallel_on_two_gpus():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    world = 2
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_column_then_row_parallel(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     results = ctx.Manager().dict()
     port = _free_port()
@@ -99,16 +148,45 @@ def test_column_then_row_parallel_on_two_gpus():
     for p in procs:
         p.start()
     for p in procs:
-        p.join(300)
-        assert p.exitcode == 0
+        p.join(600)
+    stuck = [p for p in procs if p.is_alive()]
+    for p in stuck:
+        p.terminate()
+    assert not stuck, "a rank did not finish"
+    assert all(p.exitcode == 0 for p in procs)
+    peer_seen = 0
     for r in range(world):
-        err, rows_equal, k_err, shape, peer_used, peer_err, peer_repeatable, peer_same = results[r]
-        assert shape == (1024, 512)
-        # the exchange over peer memory (or, where symmetric memory cannot be set up, its NCCL fallback):
-        # partials rounded to bf16 once, summed in binary32 by the slab's owner
-        print(f"rank {r}: peer-memory exchange used: {peer_used}, error {peer_err:.2e}")
-        assert peer_err < 1e-2, peer_err
-        assert peer_repeatable and peer_same
-        assert err < 2e-2, err            # bf16 partials summed in bf16 by the all-reduce
-        assert rows_equal
-        assert k_err < 1e-5, k_err
+        out = results[r]
+        print(f"world {world} rank {r}: {out}")
+        # the column-parallel shard is the oracle's matmul of the oracle's operands (<= 0.1 % of bf16 outputs differ)
+        assert out["h_frac"] <= 1e-3, out["h_frac"]
+        assert out["nccl"] < 2e-2, out["nccl"]
+        for mode in ("pull", "scatter"):
+            if isinstance(out[mode], str):
+                continue                                       # symmetric memory could not be set up on this machine
+            err, repeatable, same = out[mode]
+            peer_seen += 1
+            assert err < 1e-2, (mode, err)
+            assert repeatable and same, mode
+        assert out["slab"] < 2e-2, out["slab"]
+        assert out["packed_equal"], "slabs quantized with the common amax must equal the unsharded quantization"
+        assert out["next_equal"]
+        assert out["rows_equal"]
+        assert out["k_err"] < 1e-5, out["k_err"]
+        assert out["wait_failure_site"] == 0
+    if peer_seen == 0:
+        pytest.skip("NCCL paths and the slab hand-off checked; the peer-memory exchange was unavailable (no symmetric memory)")
+
+
+def test_one_rank_reproduces_the_unsharded_layer():
+    """g = 1: a 'sharded' layer is the plain layer, bit for bit, in both modes."""
+    import fouroversix_b200 as fos
+    from fouroversix_b200.sharding import TensorParallelLinear
+
+    x, w_up, w_down, _ = (t.to("cuda") for t in _inputs())
+    cfg = fos.ModuleQuantizationConfig()
+    h = TensorParallelLinear(w_up, cfg, "column")(x)
+    assert torch.equal(h, fos.quantized_matmul(x, fos.quantize(w_up, cfg.get_weight_config())))
+    for kwargs in (dict(), dict(scatter_output=True)):
+        y = TensorParallelLinear(w_down, cfg, "row", **kwargs)(h)
+        assert torch.equal(y, fos.quantized_matmul(h, fos.quantize(w_down, cfg.get_weight_config())))

@@ -1,12 +1,13 @@
 """The IF4 GEMM entry point that takes no workspace (`fos_gemm_if4_static`).
 
 Some callers cannot give the library scratch memory: they run where allocating device memory
-is not allowed (a host callback, a plug-in hook of another framework, a memory pool that has
-already been handed out completely). For them the library keeps a fixed 32 MiB buffer inside
+is not allowed (a plug-in hook of another framework that may launch kernels but must leave the
+allocator alone, a memory pool that has already been handed out completely). For them the library keeps a fixed 32 MiB buffer inside
 its own image. This test calls that entry point through the C ABI, twice in a row on different
 data, and requires bit-identical results to `fos_gemm_if4` with a caller-provided workspace
-(the same kernels run in both, so there is no tolerance to apply); it also checks that a
-problem beyond the fixed buffer is refused with FOS_ERR_TOO_LARGE.
+(the same kernels run in both, so there is no tolerance to apply); it measures that the call
+leaves the device's free memory and torch's allocator untouched; and it checks that a problem
+beyond the fixed buffer is refused with FOS_ERR_TOO_LARGE.
 
 The file name makes pytest collect it last, so a run that stops at the first failure has
 already executed every other test.
@@ -61,8 +62,16 @@ def test_static_workspace_entry_matches_the_workspace_entry_twice():
         want = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
         got = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
         assert _call(False, qa, qb, want, alpha, workspace) == 0
+        if seed == 0:
+            assert _call(True, qa, qb, got, alpha) == 0        # the first call on a device does the one-time set-up
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        torch_before = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
         assert _call(True, qa, qb, got, alpha) == 0
         torch.cuda.synchronize()
+        # nothing was allocated, by the driver or by torch's caching allocator
+        assert torch.cuda.mem_get_info()[0] == free_before
+        assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == torch_before
         assert torch.isfinite(want.float()).all()
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"case {seed}"
 
