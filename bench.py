@@ -47,8 +47,16 @@ B_SHAPE = (4096, 4096)
 BYTES_PER_ELEM = 2.0 + 0.5 + 1.0 / 16.0
 N_ROTATE = 4
 NOMINAL_FP4_TFLOPS = 9000.0
-# DRAM bytes (read + write) of one launch of the quantize kernel on the 8192x4096 tensor, from ncu
-QUANTIZE_KERNEL_DRAM_BYTES = 70.64e6   # 67.16 MB read + 3.48 MB written (the rest of the output is still in L2)
+# DRAM bytes (read + write) of one launch of the quantize kernel on the 8192x4096 tensor: a constant taken from one
+# ncu capture of that kernel (67.16 MB read + 3.05 MB written; the rest of the output is still in L2 when the kernel
+# ends), not something this script can measure while it runs
+QUANTIZE_KERNEL_DRAM_BYTES = 70.21e6
+WORKLOAD = "quantize A 8192x4096 bf16 (N(0,1), 1% K-channels x20) to NVFP4 4/6-MSE, 1x16 blocks (one A per GPU)"
+CONFIG = {
+    "workload": WORKLOAD,
+    "l2": f"GPU arm: {N_ROTATE} rotating copies of A (256 MiB > L2) so each step reads HBM-cold input; "
+          "CPU arm: one copy in host memory (64 MiB, larger than the host caches)",
+}
 
 
 def load_peaks() -> dict:
@@ -199,7 +207,7 @@ def run_reference(args, rank: int) -> None:
         "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "quantize A 8192x4096 bf16 (N(0,1), 1% K-channels x20) to NVFP4 4/6-MSE, 1x16 blocks"},
+        "config": CONFIG,
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": "every step is one full 8192x4096 quantization by the C oracle"},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -246,6 +254,28 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     value = BYTES_PER_ELEM * n_elem * world / (ms * 1e-3) / 1e9
+    modes = {}
+
+    if rank == 0:
+        # configs[0]: one 4096 x 4096 N(0,1) tensor (32 MiB: it fits on chip, and four rotating copies fit in L2)
+        g1 = torch.Generator().manual_seed(0)
+        c1_sets = [torch.randn(4096, 4096, generator=g1).bfloat16().to(dev) for _ in range(N_ROTATE)]
+        t = time_graphs(lambda i: fos.quantize(c1_sets[i % N_ROTATE], cfg_mse), N_ROTATE, max(args.steps, 10), 3)
+        modes["c1_4096x4096_mse"] = {"ms": t, "GB/s": BYTES_PER_ELEM * 4096 * 4096 / (t * 1e-3) / 1e9,
+                                     "note": "whole call; 4 rotating 32 MiB inputs (128 MiB, about the size of L2)"}
+        del c1_sets
+
+    # end to end with host buffers, on every rank (each rank feeds its own GPU); the slowest rank defines the time
+    if world > 1:
+        dist.barrier()
+    e2e_ms, serial_ms, h2d, d2h = e2e_section(args, fos, cfg_mse, a_cpu, a_sets[0])
+    if world > 1:
+        t = torch.tensor([e2e_ms, serial_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms, serial_ms = float(t[0].item()), float(t[1].item())
+    e2e_value = BYTES_PER_ELEM * n_elem * world / (e2e_ms * 1e-3) / 1e9
+    e2e_serial_value = BYTES_PER_ELEM * n_elem * world / (serial_ms * 1e-3) / 1e9
+    h2d, d2h = h2d * world, d2h * world
 
     if rank != 0:
         # the other ranks still take part in the sharded GEMM section below
@@ -263,7 +293,6 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     kernel_ms = time_graphs(four_kernels, 1, max(args.steps, 20), 3) / N_ROTATE
 
     # other quantize modes of the same tensor (each: the whole call, both launches)
-    modes = {}
     for name, c in (("static_6", fos.QuantizationConfig(scale_rule="static_6")),
                     ("mse_amax_given", None),
                     ("if4_mse", fos.QuantizationConfig(dtype="if4")),
@@ -279,13 +308,105 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         per_elem = 2.0 + 0.5 + 1.0 / 32 if name.startswith("mxfp4") else BYTES_PER_ELEM   # one scale byte per 32 values
         modes[name] = {"ms": t, "GB/s": per_elem * n_elem / (t * 1e-3) / 1e9}
 
-    # end to end through the public API with host buffers
+    gemm = gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks)
+    stack = stack_section(args, fos, dev, rank, world)
+
+    # the configuration as a whole: quantize both operands (activation 4/6 MSE per call, weight too)
+    # and multiply, through the public front end; plus the other kernels of the path on the same tensor
+    b_dev = make_b(2).to(dev)
+    pipeline = {}
+    t = time_graphs(lambda i: fos.quantized_matmul(a_sets[i % N_ROTATE], b_dev), N_ROTATE, max(args.steps, 10), 3)
+    pipeline["quantize_both_and_multiply"] = {
+        "ms": t, "shape": "A 8192x4096 @ B(4096x4096)^T",
+        "note": "fouroversix_b200.quantized_matmul on two bf16 tensors: 2 x (zero, amax, quantize) + alpha + GEMM"}
+    qb = fos.quantize(b_dev)
+    t = time_graphs(lambda i: fos.quantized_matmul(a_sets[i % N_ROTATE], qb), N_ROTATE, max(args.steps, 10), 3)
+    pipeline["quantize_activation_and_multiply"] = {"ms": t, "note": "weight quantized once, outside the timed region"}
+    # static_6 activations: the same pair un-fused and with the quantization inside the GEMM (fos_gemm_nvfp4_fused_a:
+    # every CTA that shares rows of A quantizes them again, n / 256 = 16 times here, so fusing costs time at this width)
+    cfg_s6 = fos.QuantizationConfig(scale_rule="static_6")
+    t = time_graphs(lambda i: fos.quantized_matmul(a_sets[i % N_ROTATE], qb, input_config=cfg_s6), N_ROTATE, max(args.steps, 10), 3)
+    pipeline["quantize_activation_static6_and_multiply"] = {"ms": t, "note": "amax pass + quantize kernel + GEMM"}
+    t = time_graphs(lambda i: fos.quantized_matmul(a_sets[i % N_ROTATE], qb, input_config=cfg_s6, fuse_input_quantization=True),
+                    N_ROTATE, max(args.steps, 10), 3)
+    pipeline["fused_static6_prologue_gemm"] = {"ms": t, "note": "amax pass + GEMM that quantizes its A tiles itself; same bits"}
+    b_narrow = fos.quantize(make_b(2)[:256].contiguous().to(dev))
+    t0 = time_graphs(lambda i: fos.quantized_matmul(a_sets[i % N_ROTATE], b_narrow, input_config=cfg_s6), N_ROTATE, max(args.steps, 10), 3)
+    t1 = time_graphs(lambda i: fos.quantized_matmul(a_sets[i % N_ROTATE], b_narrow, input_config=cfg_s6, fuse_input_quantization=True),
+                     N_ROTATE, max(args.steps, 10), 3)
+    pipeline["fused_static6_prologue_gemm_n256"] = {"ms": t1, "unfused_ms": t0, "shape": "A 8192x4096 @ B(256x4096)^T"}
+    q_sets = [fos.quantize(x, cfg_mse) for x in a_sets]
+    t = time_graphs(lambda i: fos.dequantize(q_sets[i % N_ROTATE]), N_ROTATE, max(args.steps, 10), 3)
+    pipeline["dequantize"] = {"ms": t, "GB/s": BYTES_PER_ELEM * n_elem / (t * 1e-3) / 1e9}
+    cfg_fake = fos.QuantizationConfig(scale_rule="mse", pseudo_quantize=True)
+    t = time_graphs(lambda i: fos.quantize(a_sets[i % N_ROTATE], cfg_fake), N_ROTATE, max(args.steps, 10), 3)
+    pipeline["pseudo_quantize"] = {"ms": t, "GB/s": 4.0 * n_elem / (t * 1e-3) / 1e9,
+                                   "note": "fused fake quantization, 2 B read + 2 B written per element"}
+    del q_sets
+
+    cpu = cpu_baseline_quantize(a_cpu) if world == 1 else None
+
+    achieved = BYTES_PER_ELEM * n_elem / (kernel_ms * 1e-3) / 1e9
+    step_rate = value / world
+    line = {
+        "metric": "quantize GB/s (frac of HBM peak); FP4 GEMM TFLOP/s at 8192^3 (frac of FP4 peak)",
+        "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": CONFIG,
+        "method": {
+            "bytes_per_element": BYTES_PER_ELEM,
+            "timing": "each step is one CUDA-graph replay of the library call (3 kernels: zero amax, amax pass, quantize); "
+                      "ms_per_step_eager is the same call launched from Python",
+        },
+        "ms_per_step_eager": eager_ms,
+        "roofline": {
+            "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": achieved / peaks["hbm_gbs"], "frac_of_nominal_8TBps": achieved / 8000.0,
+            "peak_source": peaks["source"],
+            "kernel": "quantize_rows_mse_kernel<bf16> (the longer of the step's two kernels), launched alone "
+                      "with amax given",
+            "kernel_us": kernel_ms * 1e3,
+            "algorithmic_bytes_per_launch": BYTES_PER_ELEM * n_elem,
+            "traffic": QUANTIZE_KERNEL_DRAM_BYTES,
+            "traffic_source": "a constant of this script: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of "
+                              "this kernel on this tensor shape (not measured in this run)",
+            "whole_step": {"achieved": step_rate, "frac": step_rate / peaks["hbm_gbs"],
+                           "note": "amax pass + quantize kernel together (= value per GPU)"},
+        },
+        "quantize_modes": modes,
+        "gemm": gemm,
+        "decoder_linear_stack": stack,
+        "pipeline": pipeline,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms,
+                "how": "fouroversix_b200.quantize() on a staging tensor; every step copies its input from pinned host "
+                       "memory and its codes, scales and amax back; steps are software-pipelined over three streams "
+                       "(copy-in of step i+1 and copy-out of step i-1 overlap step i)",
+                "serial_value": e2e_serial_value, "serial_ms_per_step": serial_ms},
+        "gpu_launches": 3 * args.steps,
+        "clocks": clocks,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    # the multi-GPU number that matters, once more and compactly at the END of the line (log tails keep it)
+    line["stack_ms"] = {"n_gpus": world, "total": round(stack["ms"], 4),
+                        **{k: round(v["ms"], 4) for k, v in stack["layers"].items()}}
+    if "allreduce_form" in stack:
+        line["stack_ms"]["allreduce_form_total"] = round(stack["allreduce_form"]["ms"], 4)
+    print(json.dumps(line), flush=True)
+
+
+def e2e_section(args, fos, cfg_mse, a_cpu, a_dev):
+    """The metric end to end through the public API with HOST buffers: every step copies its input from pinned
+    host memory, quantizes, and copies codes, scales and amax back. Returns (pipelined ms per step, serial ms per
+    step, host-to-device bytes per step, device-to-host bytes per step) of this rank."""
     pinned_in = a_cpu.pin_memory()
-    q0 = fos.quantize(a_sets[0], cfg_mse)
+    q0 = fos.quantize(a_dev, cfg_mse)
     host_vals = [torch.empty(q0.values.shape, dtype=torch.uint8).pin_memory() for _ in range(2)]
     host_sf = [torch.empty(q0.scale_factors.numel(), dtype=torch.uint8).pin_memory() for _ in range(2)]
     host_amax = [torch.empty(1, dtype=torch.float32).pin_memory() for _ in range(2)]
-    staging = [torch.empty_like(a_sets[0]) for _ in range(2)]
+    staging = [torch.empty_like(a_dev) for _ in range(2)]
 
     # (a) one step after the other on one stream: copy in, quantize, copy out
     def e2e_step(i):
@@ -341,117 +462,73 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
     h2d = a_cpu.numel() * 2
     d2h = host_vals[0].numel() + host_sf[0].numel() + 4
-    e2e_value = BYTES_PER_ELEM * n_elem / (e2e_ms * 1e-3) / 1e9
-    e2e_serial_value = BYTES_PER_ELEM * n_elem / (serial_ms * 1e-3) / 1e9
-
-    gemm = gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks)
-    stack = stack_section(args, fos, dev, rank, world)
-
-    # the configuration as a whole: quantize both operands (activation 4/6 MSE per call, weight too)
-    # and multiply, through the public front end; plus the other kernels of the path on the same tensor
-    b_dev = make_b(2).to(dev)
-    pipeline = {}
-    t = time_graphs(lambda i: fos.quantized_matmul(a_sets[i % N_ROTATE], b_dev), N_ROTATE, max(args.steps, 10), 3)
-    pipeline["quantize_both_and_multiply"] = {
-        "ms": t, "shape": "A 8192x4096 @ B(4096x4096)^T",
-        "note": "fouroversix_b200.quantized_matmul on two bf16 tensors: 2 x (zero, amax, quantize) + alpha + GEMM"}
-    qb = fos.quantize(b_dev)
-    t = time_graphs(lambda i: fos.quantized_matmul(a_sets[i % N_ROTATE], qb), N_ROTATE, max(args.steps, 10), 3)
-    pipeline["quantize_activation_and_multiply"] = {"ms": t, "note": "weight quantized once, outside the timed region"}
-    q_sets = [fos.quantize(x, cfg_mse) for x in a_sets]
-    t = time_graphs(lambda i: fos.dequantize(q_sets[i % N_ROTATE]), N_ROTATE, max(args.steps, 10), 3)
-    pipeline["dequantize"] = {"ms": t, "GB/s": BYTES_PER_ELEM * n_elem / (t * 1e-3) / 1e9}
-    cfg_fake = fos.QuantizationConfig(scale_rule="mse", pseudo_quantize=True)
-    t = time_graphs(lambda i: fos.quantize(a_sets[i % N_ROTATE], cfg_fake), N_ROTATE, max(args.steps, 10), 3)
-    pipeline["pseudo_quantize"] = {"ms": t, "GB/s": 4.0 * n_elem / (t * 1e-3) / 1e9,
-                                   "note": "fused fake quantization, 2 B read + 2 B written per element"}
-    del q_sets
-
-    cpu = cpu_baseline_quantize(a_cpu) if world == 1 else None
-
-    achieved = BYTES_PER_ELEM * n_elem / (kernel_ms * 1e-3) / 1e9
-    step_rate = value / world
-    line = {
-        "metric": "quantize GB/s (frac of HBM peak); FP4 GEMM TFLOP/s at 8192^3 (frac of FP4 peak)",
-        "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic",
-        "config": {
-            "workload": "quantize A 8192x4096 bf16 (N(0,1), 1% K-channels x20) to NVFP4 4/6-MSE, 1x16 blocks; "
-                        "per rank when n_gpus > 1",
-            "l2": f"{N_ROTATE} rotating copies of A (256 MiB) so each step reads HBM-cold input",
-            "bytes_per_element": BYTES_PER_ELEM,
-            "timing": "each step is one CUDA-graph replay of the library call (3 kernels: zero amax, amax pass, quantize); "
-                      "ms_per_step_eager is the same call launched from Python",
-        },
-        "ms_per_step_eager": eager_ms,
-        "roofline": {
-            "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-            "frac": achieved / peaks["hbm_gbs"], "frac_of_nominal_8TBps": achieved / 8000.0,
-            "peak_source": peaks["source"],
-            "kernel": "quantize_rows_tma_kernel<bf16, adaptive> (the longer of the step's two kernels), launched alone "
-                      "with amax given",
-            "kernel_us": kernel_ms * 1e3,
-            "algorithmic_bytes_per_launch": BYTES_PER_ELEM * n_elem,
-            "traffic": QUANTIZE_KERNEL_DRAM_BYTES,
-            "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel on this "
-                              "tensor shape (profiles/quantize_rows_tma_kernel_8192x4096_mse.md)",
-            "whole_step": {"achieved": step_rate, "frac": step_rate / peaks["hbm_gbs"],
-                           "note": "amax pass + quantize kernel together (= value per GPU)"},
-        },
-        "quantize_modes": modes,
-        "gemm": gemm,
-        "decoder_linear_stack": stack,
-        "pipeline": pipeline,
-        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms,
-                "how": "fouroversix_b200.quantize() on a staging tensor; every step copies its input from pinned host "
-                       "memory and its codes, scales and amax back; steps are software-pipelined over three streams "
-                       "(copy-in of step i+1 and copy-out of step i-1 overlap step i)",
-                "serial_value": e2e_serial_value, "serial_ms_per_step": serial_ms},
-        "gpu_launches": 3 * args.steps,
-        "clocks": clocks,
-    }
-    if cpu is not None:
-        line["cpu_baseline"] = cpu
-    print(json.dumps(line), flush=True)
+    return e2e_ms, serial_ms, h2d, d2h
 
 
 def gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks):
-    """FP4 GEMM numbers: 8192^3 (and the 8192x4096x4096 of the configuration) on one GPU;
-    with more GPUs the N dimension of B is split across ranks (column parallel, no
-    collective) and the slowest rank defines the time."""
+    """FP4 GEMM numbers: 8192^3 (and the 8192x4096x4096 of the configuration) on one GPU, NVFP4 and MXFP4, and the
+    IF4 GEMM at the Llama-3-8B MLP shapes (4096 tokens, 4096 -> 14336 and 14336 -> 4096; fp16 tensor cores, so its
+    roofline is the measured bf16 peak); with more GPUs the N dimension of B is split across ranks (column
+    parallel, no collective) and the slowest rank defines the time. The GEMM runs power-limited, so every
+    entry carries the median SM clock sampled while it ran and ms x MHz, which compares across boxes."""
     out = {}
     mx = fos.QuantizationConfig(dtype="mxfp4", scale_rule="static_6")
-    for name, (m, n, k) in (("square_8192", (8192, 8192, 8192)), ("act_x_weight", (8192, 4096, 4096)),
-                            ("square_8192_mxfp4", (8192, 8192, 8192))):
+    if4 = fos.QuantizationConfig(dtype="if4")
+    cases = (("square_8192", (8192, 8192, 8192), None), ("act_x_weight", (8192, 4096, 4096), None),
+             ("square_8192_mxfp4", (8192, 8192, 8192), mx), ("if4_mlp_up", (4096, 14336, 4096), if4),
+             ("if4_mlp_down", (4096, 4096, 14336), if4))
+    for name, (m, n, k), qcfg in cases:
         n_local = n // world
         g = torch.Generator(device=dev).manual_seed(3 + rank)
         a = torch.randn(m, k, generator=g, device=dev).bfloat16()
-        b = (torch.randn(n_local, k, generator=g, device=dev) * (0.02 if name == "act_x_weight" else 1.0)).bfloat16()
-        qa, qb = (fos.quantize(a, mx), fos.quantize(b, mx)) if name.endswith("mxfp4") else (fos.quantize(a), fos.quantize(b))
+        b = (torch.randn(n_local, k, generator=g, device=dev) * (1.0 if name.startswith("square") else 0.02)).bfloat16()
+        qa, qb = (fos.quantize(a, qcfg), fos.quantize(b, qcfg)) if qcfg is not None else (fos.quantize(a), fos.quantize(b))
         d = torch.empty(m, n_local, dtype=torch.bfloat16, device=dev)
         del a, b
         fn = lambda i: B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType.bfloat16, out=d)  # noqa: E731
         if world > 1:
             dist.barrier()
         ms = time_graphs(fn, 1, max(args.steps, 10), max(args.warmup, 3))
+        clocks = None
+        if rank == 0:
+            # the same call back to back for half a second, so that the clock sampler sees it under load
+            sampler = ClockSampler(dev.index or 0)
+            sampler.start()
+            t_end = time.perf_counter() + 0.5
+            while time.perf_counter() < t_end:
+                for i in range(20):
+                    fn(i)
+                torch.cuda.synchronize()
+            clocks = sampler.stop()
         if world > 1:
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         tflops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
-        derived = NOMINAL_FP4_TFLOPS * peaks["bf16_tflops"] / 2250.0
+        is_if4 = name.startswith("if4")
+        if is_if4:
+            roofline = {"bound": "tensor", "achieved": tflops / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                        "frac": tflops / world / peaks["bf16_tflops"],
+                        "peak_source": f"{peaks['source']} dense bf16 (the IF4 GEMM expands to fp16 and runs kind::f16 MMAs)",
+                        "frac_of_nominal_2250": tflops / world / 2250.0}
+        else:
+            derived = NOMINAL_FP4_TFLOPS * peaks["bf16_tflops"] / 2250.0
+            roofline = {"bound": "tensor", "achieved": tflops / world, "peak": NOMINAL_FP4_TFLOPS,
+                        "unit": "TFLOP/s", "frac": tflops / world / NOMINAL_FP4_TFLOPS,
+                        "peak_source": "nominal dense FP4 (no measured FP4 figure exists)",
+                        "frac_of_bf16_scaled_peak": tflops / world / derived,
+                        "bf16_scaled_peak": derived}
         out[name] = {
             "value": tflops, "unit": "TFLOP/s", "ms": ms, "m": m, "n": n, "k": k, "n_gpus": world,
             "sharding": "none" if world == 1 else f"column-parallel, N/{world} per rank, no collective",
-            "roofline": {"bound": "tensor", "achieved": tflops / world, "peak": NOMINAL_FP4_TFLOPS,
-                         "unit": "TFLOP/s", "frac": tflops / world / NOMINAL_FP4_TFLOPS,
-                         "peak_source": "nominal dense FP4 (no measured FP4 figure exists)",
-                         "frac_of_bf16_scaled_peak": tflops / world / derived,
-                         "bf16_scaled_peak": derived},
-            "gpu_launches_per_step": 2, "l2": "operands + output (200 MiB at 8192^3) exceed L2",
+            "roofline": roofline,
+            "sm_mhz": None if clocks is None else clocks["sm_mhz"],
+            "ms_x_mhz": None if clocks is None or clocks["sm_mhz"] is None else ms * clocks["sm_mhz"],
+            "clock_reasons": None if clocks is None else clocks["reasons"],
+            "gpu_launches_per_step": 4 if is_if4 else 2, "l2": "operands + output exceed L2",
         }
+        del qa, qb, d
+        torch.cuda.empty_cache()
     return out
 
 
@@ -467,16 +544,19 @@ STACK_LAYERS = (  # name, parallelism, out features N, in features K: the linear
 
 def stack_section(args, fos, dev, rank, world):
     """The linear layers of one Llama-3-70B-shaped decoder block on 16 x 2048 tokens, tensor parallel over the
-    ranks: NVFP4 4/6 weights quantized once per shard, activations quantized on every call (4/6 MSE),
-    column-parallel layers without a collective, row-parallel layers followed by an all-reduce that
-    overlaps the GEMM chunk by chunk. Every layer gets its own random input of the right shape (this is
-    the stack of GEMMs, not a transformer). Per layer: time of the whole call (max over ranks), and for
-    row-parallel layers the GEMM part and the all-reduce part on their own."""
+    ranks: NVFP4 4/6 weights quantized once per shard, activations quantized on every call (4/6 MSE). Every
+    layer gets its own random input of the right shape (this is the stack of GEMMs, not a transformer).
+
+    With more than one rank the layers hand activations over as ROW SLABS (sharding.TensorParallelLinear with
+    scatter_output / scattered_input): a row-parallel layer reduce-scatters its partial products (chunk by
+    chunk, beside the next chunk's GEMM), the column-parallel layer after it quantizes its slab with the
+    ranks' common amax and all-gathers the packed slabs. `allreduce_form` times the same layers the other
+    way (full activations on every rank, NCCL all-reduce after the row-parallel layers, every rank
+    quantizing the whole activation). Per layer: time of the whole call, max over ranks."""
     from fouroversix_b200.sharding import TensorParallelLinear, shard_bounds
 
     cfg = fos.ModuleQuantizationConfig()
     steps, warm = max(5, min(args.steps, 10)), 3
-    layers, total_ms, total_flop = {}, 0.0, 0.0
 
     def timed(fn):
         if world > 1:
@@ -488,45 +568,71 @@ def stack_section(args, fos, dev, rank, world):
             ms = float(t.item())
         return ms
 
-    for idx, (name, mode, n, k) in enumerate(STACK_LAYERS):
-        g = torch.Generator(device=dev).manual_seed(12 + idx + 100 * rank)
-        if mode == "column":
-            lo, hi = shard_bounds(n, rank, world, 128)
-            w_shape, k_local = (hi - lo, k), k
-        else:
-            lo, hi = shard_bounds(k, rank, world, 64)
-            w_shape, k_local = (n, hi - lo), hi - lo
-        w = (torch.randn(*w_shape, generator=g, device=dev) * 0.02).bfloat16()
-        x = torch.randn(STACK_TOKENS, k_local, generator=g, device=dev).bfloat16()
-        layer = TensorParallelLinear(w, cfg, mode)
-        del w
-        ms = timed(lambda: layer(x))
-        flop = 2.0 * STACK_TOKENS * n * k
-        entry = {"mode": mode, "n": n, "k": k, "ms": ms, "TFLOP/s": flop / (ms * 1e-3) / 1e12}
-        if mode == "row" and world > 1:
-            entry["exchange"] = ("peer memory: scatter from the GEMM's epilogue, then reduce + gather by the owners"
-                                 if layer._peer is not None else "NCCL all-reduce on a second stream, 4 chunks of tokens")
-            act_cfg = cfg.get_activation_config()
-            entry["ms_quantize_and_gemm"] = timed(lambda: layer._gemm(x, act_cfg))
-            out = torch.empty(STACK_TOKENS, n, dtype=torch.bfloat16, device=dev)
-            entry["ms_all_reduce"] = timed(lambda: dist.all_reduce(out))
-            nbytes = out.numel() * 2
-            entry["all_reduce_bytes"] = nbytes
-            entry["all_reduce_bus_GB/s"] = 2.0 * (world - 1) / world * nbytes / (entry["ms_all_reduce"] * 1e-3) / 1e9
-            entry["nvlink_bound_ms"] = 2.0 * (world - 1) / world * nbytes / 900e9 * 1e3
-            del out
-        layers[name] = entry
-        total_ms += ms
-        total_flop += flop
-        del layer, x
-        torch.cuda.empty_cache()
-    return {
+    def run(handoff: bool):
+        layers, total_ms, total_flop = {}, 0.0, 0.0
+        for idx, (name, mode, n, k) in enumerate(STACK_LAYERS):
+            g = torch.Generator(device=dev).manual_seed(12 + idx + 100 * rank)
+            if mode == "column":
+                lo, hi = shard_bounds(n, rank, world, 128)
+                w_shape, k_local = (hi - lo, k), k
+            else:
+                lo, hi = shard_bounds(k, rank, world, 64)
+                w_shape, k_local = (n, hi - lo), hi - lo
+            w = (torch.randn(*w_shape, generator=g, device=dev) * 0.02).bfloat16()
+            rows = STACK_TOKENS // world if (handoff and mode == "column") else STACK_TOKENS
+            x = torch.randn(rows, k_local, generator=g, device=dev).bfloat16()
+            kw = {}
+            if handoff:
+                kw = dict(scattered_input=True) if mode == "column" else dict(scatter_output=True)
+            layer = TensorParallelLinear(w, cfg, mode, chunks=2 if handoff else 4, **kw)
+            del w
+            if name == "up_proj":
+                # gate_proj and up_proj read the same activation: its quantization (and gather) is counted once,
+                # in gate_proj; up_proj takes the quantized activation as it is
+                xq = layer.quantize_input(x)
+                ms = timed(lambda: layer(xq))
+                del xq
+            else:
+                ms = timed(lambda: layer(x))
+            flop = 2.0 * STACK_TOKENS * n * k
+            entry = {"mode": mode, "n": n, "k": k, "ms": ms, "TFLOP/s": flop / (ms * 1e-3) / 1e12}
+            if mode == "row" and world > 1 and not handoff:
+                entry["exchange"] = ("peer memory: scatter from the GEMM's epilogue, then reduce + gather by the owners"
+                                     if layer._peer is not None else "NCCL all-reduce on a second stream, 4 chunks of tokens")
+            layers[name] = entry
+            total_ms += ms
+            total_flop += flop
+            del layer, x
+            torch.cuda.empty_cache()
+        return layers, total_ms, total_flop
+
+    layers, total_ms, total_flop = run(handoff=world > 1)
+    out = {
         "tokens": STACK_TOKENS, "n_gpus": world, "layers": layers, "ms": total_ms,
         "TFLOP/s": total_flop / (total_ms * 1e-3) / 1e12,
+        "form": ("one GPU" if world == 1 else
+                 "row-slab hand-off: reduce-scatter after row-parallel layers (NCCL, 2 chunks beside the GEMM), common amax, "
+                 "slab quantization, all-gather of packed codes + scales before column-parallel layers"),
         "how": "eager calls of sharding.TensorParallelLinear.forward (dynamic activation quantization + FP4 GEMM "
-               "[+ the row-parallel exchange named per layer]); CUDA events, max over ranks; weights "
-               "quantized per shard outside the timed region",
+               "[+ the exchange]); CUDA events, max over ranks; weights quantized per shard outside the timed region",
     }
+    if world > 1:
+        ar_layers, ar_ms, _ = run(handoff=False)
+        nbytes = STACK_TOKENS * 8192 * 2
+        buf = torch.empty(STACK_TOKENS, 8192, dtype=torch.bfloat16, device=dev)
+        ms_ar = timed(lambda: dist.all_reduce(buf))
+        half = torch.empty(STACK_TOKENS // world, 8192, dtype=torch.bfloat16, device=dev)
+        ms_rs = timed(lambda: dist.reduce_scatter_tensor(half, buf))
+        del buf, half
+        out["allreduce_form"] = {"ms": ar_ms, "layers": {k: round(v["ms"], 4) for k, v in ar_layers.items()},
+                                 "exchange": {k: v["exchange"] for k, v in ar_layers.items() if "exchange" in v}}
+        out["collectives_alone"] = {
+            "bytes": nbytes, "all_reduce_ms": ms_ar, "reduce_scatter_ms": ms_rs,
+            "all_reduce_bus_GB/s": 2.0 * (world - 1) / world * nbytes / (ms_ar * 1e-3) / 1e9,
+            "reduce_scatter_bus_GB/s": (world - 1) / world * nbytes / (ms_rs * 1e-3) / 1e9,
+            "nvlink_bound_ms": {"all_reduce": 2.0 * (world - 1) / world * nbytes / 900e9 * 1e3,
+                                "reduce_scatter": (world - 1) / world * nbytes / 900e9 * 1e3}}
+    return out
 
 
 def run_case(args) -> None:

@@ -131,6 +131,58 @@ __device__ __forceinline__ float div6_exact(float a) {
     return __fmaf_rn(__fmaf_rn(-6.0f, q0, a), y, q0);
 }
 
+// E2M1 codes of v[i] * r. The reference multiplies the rounded magnitude by sign(x_scaled),
+// which is 0 for a zero of either sign, so a scaled value of -0.0 must encode as +0 (code
+// 0x0, not 0x8). fma(v, r, +0.0) rounds exactly like v * r and turns (-0.0) * r into +0.0;
+// `guard` adds +0.0 once more for a NEGATIVE product that underflows to -0.0.
+__device__ __forceinline__ void encode_e2m1(const float (&v)[16], float r, bool guard, uint32_t &lo, uint32_t &hi) {
+    float xs[16];
+    const uint64_t r2 = pack2(r, r), zero2 = pack2(0.0f, 0.0f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) unpack2f(fma2(pack2(v[2 * k], v[2 * k + 1]), r2, zero2), xs[2 * k], xs[2 * k + 1]);
+    if (guard) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) xs[i] = __fadd_rn(xs[i], 0.0f);
+    }
+    lo = cvt_e2m1x8(xs);
+    hi = cvt_e2m1x8(xs + 8);
+}
+
+// ---- NVFP4 with a static scale rule, one block of 16 values ----
+//
+// The reference's sequence for scale_rule static_6 / static_4 (src/fouroversix/quantize/pytorch/
+// reference.py:184-241, 555-679), as the quantize kernels run it: per tensor encode = (maxq * 448) / amax
+// and decode = 1 / encode; per block the scale byte E4M3(bmax / maxq * encode) and the codes of
+// x * (1 / (decode * scale)). `lut` maps a scale byte to {scale, 1 / (decode * scale)}.
+struct StaticQuantConsts {
+    float encode0;   // encode, or 0 when amax is 0 (every scale is then 0)
+    float decode;
+    bool six;        // static_6 (else static_4)
+};
+__device__ __forceinline__ StaticQuantConsts static_quant_consts(float amax, int rule) {
+    StaticQuantConsts c;
+    c.six = rule != FOS_RULE_STATIC_4;
+    const float encode = __fdiv_rn((c.six ? 6.0f : 4.0f) * 448.0f, amax);
+    c.decode = __frcp_rn(encode);
+    c.encode0 = amax == 0.0f ? 0.0f : encode;
+    return c;
+}
+__device__ __forceinline__ float2 static_scale_entry(uint32_t sfb, float decode) {
+    const float s = e4m3_to_float(sfb);
+    return make_float2(s, __frcp_rn(__fmul_rn(decode, s)));
+}
+__device__ __forceinline__ void quantize_block_static(const float (&v)[16], const StaticQuantConsts &c, const float2 *lut,
+                                                      uint32_t &lo, uint32_t &hi, uint32_t &sf_byte) {
+    float bmax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(v[i]));
+    const float q = c.six ? div6_exact(bmax) : __fmul_rn(bmax, 0.25f);
+    sf_byte = cvt_e4m3(__fmul_rn(q, c.encode0));
+    const float2 e = lut[sf_byte];
+    lo = hi = 0u;
+    if (e.x != 0.0f) encode_e2m1(v, e.y, e.y < 0x1p-16f, lo, hi);
+}
+
 // ---- memory ----
 
 __device__ __forceinline__ uint4 ldg_nc_16(const void *p) {

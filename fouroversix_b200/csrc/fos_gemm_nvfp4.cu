@@ -111,6 +111,14 @@ struct GemmParams {
     // rows) belongs to rank mb % scatter_world and is block mb / scatter_world of that rank's slab of
     // `slab_rows` rows; its staging buffer d_peer[o] (a peer mapping unless o is this rank) is
     // [world][slab_rows][ldd], and this rank writes plane scatter_rank.
+    // Fused activation quantization (gemm_nvfp4_kernel<.., FUSED_A>): A is not read packed but made in the
+    // kernel from x[m, k] (bf16 / fp16, row stride x_ld elements) with NVFP4 static_6 / static_4 and the
+    // per-tensor amax at x_amax; a_sf is unused.
+    const void *x;
+    int64_t x_ld;
+    const float *x_amax;
+    int x_rule;
+    int x_is_fp16;
     int scatter_world;       // 0: plain store to d
     int scatter_rank;
     int64_t slab_rows;
@@ -191,7 +199,7 @@ __device__ __forceinline__ uint32_t mma_idesc_mx(uint32_t idesc, uint32_t sf_byt
 
 // ---------------------------------------------------------------------------- kernel
 
-template <int BLOCK_N, typename OUT>
+template <int BLOCK_N, typename OUT, bool FUSED_A = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
@@ -216,12 +224,13 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
+        // FUSED_A: besides the copy engine (B, B's scales), the eight warps that make A and its scales arrive
         for (int s = 0; s < C::STAGES; ++s) {
-            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(full_bar + 8 * s, FUSED_A ? 9 : 1);
             mbar_init(empty_bar + 8 * s, 1);
         }
         for (int j = 0; j < C::SF_SLOTS; ++j) {
-            mbar_init(sf_full_bar + 8 * j, 1);
+            mbar_init(sf_full_bar + 8 * j, FUSED_A ? 9 : 1);
             mbar_init(sf_ready_bar + 8 * j, SF_BY_CP ? 1 : 4);    // one arrival per scale-mover warp (or one commit)
         }
         for (int a = 0; a < C::ACC_STAGES; ++a) {
@@ -267,8 +276,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 if (!ok) break;
                 const uint32_t stage = smem_base + s * C::STAGE_BYTES, bar = full_bar + 8 * s;
                 // rows beyond N and bytes beyond K are zero-filled by the TMA unit and still counted
-                mbar_expect_tx(bar, C::STAGE_BYTES);
-                tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), m0, bar);
+                mbar_expect_tx(bar, FUSED_A ? C::B_BYTES : C::STAGE_BYTES);
+                if (!FUSED_A) tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), m0, bar);
                 tma_load_2d(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES), n0, bar);
                 if (++s == C::STAGES) { s = 0; ph ^= 1u; }
             }
@@ -301,8 +310,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             // (MXFP4: a tile spans two K-blocks, so the box of its maps is two tiles per group)
             const int kb0 = static_cast<int>(f_kt * (p.mx ? KB_PER_STAGE / 2 : KB_PER_STAGE));
             const uint32_t dst = sf_base + slot * C::SF_SLOT_BYTES, bar = sf_full_bar + 8 * slot;
-            mbar_expect_tx(bar, p.mx ? C::SF_SLOT_BYTES / 2 : C::SF_SLOT_BYTES);   // MXFP4 maps fetch two tiles per group
-            tma_load_3d(dst, &map_sfa, 0, kb0, a_group, bar);
+            if (FUSED_A) {
+                mbar_expect_tx(bar, C::SFB_BYTES);
+            } else {
+                mbar_expect_tx(bar, p.mx ? C::SF_SLOT_BYTES / 2 : C::SF_SLOT_BYTES);   // MXFP4 maps fetch two tiles per group
+                tma_load_3d(dst, &map_sfa, 0, kb0, a_group, bar);
+            }
             tma_load_3d(dst + SFA_BYTES, &map_sfb, 0, kb0, b_group, bar);
             if (++slot == C::SF_SLOTS) slot = 0;
             if (++f_kt == k_tiles) {
@@ -390,9 +403,81 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const bool vec32_ok = FOS_GEMM_ST256 && (reinterpret_cast<uintptr_t>(out) % 32 == 0) && ((p.ldd * sizeof(OUT)) % 32 == 0);
         uint32_t tile_i = 0;
         bool ok = true;
+        // FUSED_A: these eight warps are idle while a tile's MMAs run (one accumulator: the epilogue and the
+        // next main loop do not overlap anyway), so they make the A operand: thread e owns row e / 2 of the
+        // stage and 8 of its 16 blocks (128 values, 256 contiguous bytes of x).
+        __shared__ float2 a_lut[FUSED_A ? 128 : 1];
+        StaticQuantConsts qc{};
+        uint32_t a_s = 0, a_ph = 0, a_j = 0;
+        const int e_tid = static_cast<int>(threadIdx.x) - 64, a_row = e_tid >> 1, a_half = e_tid & 1;
+        if constexpr (FUSED_A) {
+            qc = static_quant_consts(__ldg(p.x_amax), p.x_rule);
+            if (e_tid < 128) a_lut[e_tid] = static_scale_entry(e_tid, qc.decode);
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
             int64_t mb, nb;
             tile_coords(t, num_m, num_n, mb, nb);
+            if constexpr (FUSED_A) {
+                const int64_t x_row = mb * BLOCK_M + a_row;
+                for (int64_t kt = 0; kt < k_tiles && ok; ++kt) {
+                    // the values first (the loads do not depend on the stage), then the stage
+                    uint32_t w[8][8];
+                    const int64_t col0 = kt * 256 + a_half * 128;
+#pragma unroll
+                    for (int b = 0; b < 8; ++b) {
+                        const int64_t col = col0 + 16 * b;
+                        if (x_row < p.m && col < p.k_p) {
+                            ldg_nc_32(static_cast<const uint16_t *>(p.x) + x_row * p.x_ld + col, w[b]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) w[b][i] = 0u;
+                        }
+                    }
+                    ok = mbar_wait(empty_bar + 8 * a_s, a_ph ^ 1u, abort_flag, p.status, 8);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    const uint32_t a_stage = smem_base + a_s * C::STAGE_BYTES + a_row * 128;
+                    const uint32_t sfa_slot = sf_base + a_j * C::SF_SLOT_BYTES + (a_row & 31) * 16 + (a_row >> 5) * 4;
+                    uint32_t sf_word = 0u, codes[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                    for (int b = 0; b < 8; ++b) {
+                        float v[16];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float2 f = p.x_is_fp16 ? unpack2<__half>(w[b][i]) : unpack2<__nv_bfloat16>(w[b][i]);
+                            v[2 * i] = f.x;
+                            v[2 * i + 1] = f.y;
+                        }
+                        uint32_t lo, hi, sfb;
+                        quantize_block_static(v, qc, a_lut, lo, hi, sfb);
+                        codes[2 * (b & 1)] = lo;
+                        codes[2 * (b & 1) + 1] = hi;
+                        sf_word |= sfb << (8 * (b & 3));
+                        if (b & 1) {
+                            // blocks 2c, 2c + 1 of the row are its 16-byte chunk c, stored where the 128-byte swizzle puts it
+                            const int chunk = a_half * 4 + (b >> 1);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                         ::"r"(a_stage + ((chunk ^ (a_row & 7)) << 4)), "r"(codes[0]), "r"(codes[1]), "r"(codes[2]), "r"(codes[3]) : "memory");
+                        }
+                        if ((b & 3) == 3) {
+                            // the four scales of one K-block (64 values): one word of that K-block's 512-byte tile
+                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfa_slot + (a_half * 2 + (b >> 2)) * SF_TILE_BYTES), "r"(sf_word) : "memory");
+                            sf_word = 0u;
+                        }
+                    }
+                    // what these threads wrote is read by the tensor core and by tcgen05.cp: make it visible to that proxy
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(full_bar + 8 * a_s);
+                        mbar_arrive(sf_full_bar + 8 * a_j);
+                    }
+                    if (++a_s == C::STAGES) { a_s = 0; a_ph ^= 1u; }
+                    if (++a_j == C::SF_SLOTS) a_j = 0;
+                }
+                if (!ok) break;
+            }
             const int64_t row = mb * BLOCK_M + quad * 32 + lane, n0 = nb * BLOCK_N + half * COLS;
             if (p.scatter_world > 1) {
                 // row block mb belongs to rank mb % world (interleaved, so that the peer traffic is spread
@@ -937,11 +1022,11 @@ int launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap 
     return FOS_OK;
 }
 
-template <int BLOCK_N, typename OUT>
+template <int BLOCK_N, typename OUT, bool FUSED_A = false>
 int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &msa, const CUtensorMap &msb,
            const GemmParams &p, int sms, cudaStream_t stream) {
     using C = Cfg<BLOCK_N>;
-    auto kernel = gemm_nvfp4_kernel<BLOCK_N, OUT>;
+    auto kernel = gemm_nvfp4_kernel<BLOCK_N, OUT, FUSED_A>;
     static OncePerDevice configured;   // per instantiation
     int dev = 0;
     FOS_CUDA_TRY(cudaGetDevice(&dev));
@@ -955,12 +1040,12 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &msa,
     return FOS_OK;
 }
 
-template <int BLOCK_N>
+template <int BLOCK_N, bool FUSED_A = false>
 int launch_out(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &msa, const CUtensorMap &msb,
                const GemmParams &p, int sms, cudaStream_t stream) {
-    if (p.out_dtype == FOS_BF16) return launch<BLOCK_N, __nv_bfloat16>(ma, mb, msa, msb, p, sms, stream);
-    if (p.out_dtype == FOS_FP16) return launch<BLOCK_N, __half>(ma, mb, msa, msb, p, sms, stream);
-    return launch<BLOCK_N, float>(ma, mb, msa, msb, p, sms, stream);
+    if (p.out_dtype == FOS_BF16) return launch<BLOCK_N, __nv_bfloat16, FUSED_A>(ma, mb, msa, msb, p, sms, stream);
+    if (p.out_dtype == FOS_FP16) return launch<BLOCK_N, __half, FUSED_A>(ma, mb, msa, msb, p, sms, stream);
+    return launch<BLOCK_N, float, FUSED_A>(ma, mb, msa, msb, p, sms, stream);
 }
 
 #ifdef FOS_GEMM_DEBUG
@@ -1018,7 +1103,8 @@ static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uin
 #else
     const int debug_bits = 0;
 #endif
-    GemmParams p{a_sf, b_sf, alpha, d, status, m_p, n_p, k_p, m, n, ldd, out_dtype, debug_bits, mx, 0, 0, 0, {}};
+    GemmParams p{a_sf, b_sf, alpha, d, status, m_p, n_p, k_p, m, n, ldd, out_dtype, debug_bits, mx, nullptr, 0, nullptr, 0, 0,
+                 0, 0, 0, {}};
     if (d_peers) {
         p.scatter_world = world;
         p.scatter_rank = rank;
@@ -1081,6 +1167,44 @@ extern "C" int fos_gemm_nvfp4_ex(const uint8_t *a_codes, const uint8_t *a_sf, co
                                  int64_t n_p, int64_t k_p, int64_t m, int64_t n, int64_t ldd, const fos_gemm_opts *opts,
                                  int32_t *status, void *stream) {
     return gemm_fp4_entry(a_codes, a_sf, b_codes, b_sf, alpha, d, out_dtype, m_p, n_p, k_p, m, n, ldd, opts, status, stream, 0);
+}
+
+extern "C" int fos_gemm_nvfp4_fused_a(const void *x, int x_dtype, int64_t x_ld, const float *x_amax, int x_rule,
+                                      const uint8_t *b_codes, const uint8_t *b_sf, const float *alpha, void *d,
+                                      int out_dtype, int64_t m, int64_t n_p, int64_t k, int64_t n, int64_t ldd,
+                                      int32_t *status, void *stream_) {
+    using namespace fos;
+    if (!x || !x_amax || !b_codes || !b_sf || !alpha || !d) return FOS_ERR_INVALID_ARGUMENT;
+    if (x_dtype != FOS_BF16 && x_dtype != FOS_FP16) return FOS_ERR_INVALID_ARGUMENT;
+    if (x_rule != FOS_RULE_STATIC_6 && x_rule != FOS_RULE_STATIC_4) return FOS_ERR_UNSUPPORTED;   // 4/6 stays un-fused
+    if (m <= 0 || n_p <= 0 || k < 64 || n_p % 128 || n <= 0 || n > n_p || ldd < n || x_ld < k) return FOS_ERR_INVALID_ARGUMENT;
+    if (k % 64) return FOS_ERR_UNSUPPORTED;          // whole scale tiles only: pad K, or quantize first
+    if (out_dtype != FOS_BF16 && out_dtype != FOS_FP16 && out_dtype != FOS_FP32) return FOS_ERR_INVALID_ARGUMENT;
+    if (reinterpret_cast<uintptr_t>(x) % 32 || (x_ld * 2) % 32) return FOS_ERR_MISALIGNED;   // 32-byte loads of x
+    if (reinterpret_cast<uintptr_t>(b_codes) % 16 || reinterpret_cast<uintptr_t>(b_sf) % 16) return FOS_ERR_MISALIGNED;
+    const int64_t m_p = round_up64(m, 128);
+    if (m_p > INT32_MAX || n_p > INT32_MAX || k / 2 > INT32_MAX) return FOS_ERR_TOO_LARGE;
+    int st = check_device();
+    if (st != FOS_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int dev = 0, sms = 0;
+    FOS_CUDA_TRY(cudaGetDevice(&dev));
+    FOS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    GemmParams p{nullptr, b_sf, alpha, d, status, m_p, n_p, k, m, n, ldd, out_dtype, 0, 0, x, x_ld, x_amax, x_rule,
+                 x_dtype == FOS_FP16 ? 1 : 0, 0, 0, 0, {}};
+    if (status) {
+        FOS_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    } else {
+        FOS_CUDA_TRY(wait_failures_ptr(&p.status));
+    }
+    const int64_t tiles_256 = (m_p / BLOCK_M) * ((n_p + 255) / 256);
+    const bool wide = n_p >= 256 && tiles_256 * 2 > sms;
+    CUtensorMap map_b, map_sfb;
+    if ((st = make_operand_map(&map_b, b_codes, n_p, k / 2, wide ? 256 : 128)) != FOS_OK) return st;
+    if ((st = make_scale_map(&map_sfb, b_sf, n_p / 128, k / 64, wide ? 2 : 1, KB_PER_STAGE)) != FOS_OK) return st;
+    // (the kernel never touches the A maps in this mode; B's stand in for them)
+    return wide ? launch_out<256, true>(map_b, map_b, map_sfb, map_sfb, p, sms, stream)
+                : launch_out<128, true>(map_b, map_b, map_sfb, map_sfb, p, sms, stream);
 }
 
 extern "C" int fos_gemm_mxfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,

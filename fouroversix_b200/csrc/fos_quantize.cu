@@ -226,23 +226,6 @@ __global__ void __launch_bounds__(256) amax_rht_kernel(const T *__restrict__ x, 
 // building blocks
 // ------------------------------------------------------------------------------------
 
-// E2M1 codes of v[i] * r. The reference multiplies the rounded magnitude by sign(x_scaled),
-// which is 0 for a zero of either sign, so a scaled value of -0.0 must encode as +0 (code
-// 0x0, not 0x8). fma(v, r, +0.0) rounds exactly like v * r and turns (-0.0) * r into +0.0;
-// `guard` adds +0.0 once more for a NEGATIVE product that underflows to -0.0.
-__device__ __forceinline__ void encode_e2m1(const float (&v)[16], float r, bool guard, uint32_t &lo, uint32_t &hi) {
-    float xs[16];
-    const uint64_t r2 = pack2(r, r), zero2 = pack2(0.0f, 0.0f);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) unpack2f(fma2(pack2(v[2 * k], v[2 * k + 1]), r2, zero2), xs[2 * k], xs[2 * k + 1]);
-    if (guard) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) xs[i] = __fadd_rn(xs[i], 0.0f);
-    }
-    lo = cvt_e2m1x8(xs);
-    hi = cvt_e2m1x8(xs + 8);
-}
-
 // E2M1 codes of eight scaled values v[i] * r (as encode_e2m1 without the guard) and the
 // rounding residuals t[i] = q[i] - v[i] * r, each one IEEE subtraction of the binary32
 // scaled value from the binary16 code value.

@@ -125,6 +125,63 @@ class B200MatmulBackend:
         return out
 
     @classmethod
+    def fused_quantize_matmul(cls, x: torch.Tensor, other: QuantizedTensor, config, *, out_dtype: DataType,
+                              amax: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                              check_status: bool = False) -> torch.Tensor:
+        """`quantize(x, config) @ other.T` with the quantization of x done inside the GEMM
+        (fos_gemm_nvfp4_fused_a): the packed activation is never written to memory. For NVFP4 with a static
+        scale rule, 1-D blocks, round to nearest; bit-identical to the two calls it replaces (the un-fused pair
+        of src/fouroversix/matmul/frontend.py:95-102). `amax` (max |x|, a CUDA fp32 tensor) is computed with
+        one pass over x when it is not given. Raises ValueError for what the fused kernel does not take: the
+        caller then quantizes first."""
+        from fouroversix_b200.utils import RoundStyle, ScaleRule
+
+        if (DataType(config.dtype) != DataType.nvfp4 or ScaleRule(config.scale_rule) not in (ScaleRule.static_6, ScaleRule.static_4)
+                or config.block_scale_2d or config.transpose or config.rht or RoundStyle(config.round_style) != RoundStyle.nearest):
+            raise ValueError("B200 fused matmul: the activation must be NVFP4 with static_6 / static_4, 1-D blocks, "
+                             "round to nearest (the 4/6 rules are not fused)")
+        if other.dtype != DataType.nvfp4 or not other.scale_factors_are_in_blackwell_layout:
+            raise ValueError("B200 fused matmul: the second operand must be NVFP4 with tiled scales")
+        if x.ndim != 2 or x.device.type != "cuda" or x.dtype not in (torch.bfloat16, torch.float16):
+            raise ValueError("B200 fused matmul: x must be a 2-D bfloat16 / float16 CUDA tensor")
+        if x.stride(1) != 1:
+            x = x.contiguous()
+        m, k = x.shape
+        n = other.original_shape[0]
+        n_p, k_p = other.padded_shape
+        if other.original_shape[1] != k:
+            raise ValueError("The first input must be in row-major layout, the second input must be"
+                             "in column-major layout, and both inputs must have the same inner "
+                             "dimension")
+        if k % 64 or k_p != k or x.data_ptr() % 32 or (x.stride(0) * 2) % 32:
+            raise ValueError("B200 fused matmul: K must be a multiple of 64 and x 32-byte aligned (base and row stride)")
+        dev = x.device
+        torch_out = _OUT[DataType(out_dtype)]
+        if out is None:
+            out = torch.empty(m, n, dtype=torch_out, device=dev)
+        elif out.shape != (m, n) or out.dtype != torch_out or out.stride(1) != 1:
+            raise ValueError("B200 matmul: `out` has the wrong shape, dtype or layout")
+        if amax is None:
+            amax = B200QuantizeBackend.amax(x)
+        amax = amax.detach().reshape(1).to(device=dev, dtype=torch.float32)
+        alpha = torch.empty(1, dtype=torch.float32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev) if check_status else None
+        rule = ScaleRule(config.scale_rule).cuda_id
+        with torch.cuda.device(dev):
+            lib, stream = _native.lib(), _native.stream_ptr(dev)
+            _native.check(lib.fos_gemm_alpha(amax.data_ptr(), _native.FOS_NVFP4, rule, other.amax.data_ptr(), _native.FOS_NVFP4,
+                                             other.scale_rule.cuda_id, alpha.data_ptr(), stream), "fos_gemm_alpha")
+            _native.check(lib.fos_gemm_nvfp4_fused_a(
+                x.data_ptr(), _native.elem_code(x.dtype), x.stride(0), amax.data_ptr(), rule,
+                other.values.contiguous().data_ptr(), other.scale_factors.contiguous().data_ptr(), alpha.data_ptr(),
+                out.data_ptr(), _native.elem_code(torch_out), m, n_p, k, n, out.stride(0),
+                0 if status is None else status.data_ptr(), stream), "fos_gemm_nvfp4_fused_a")
+        if status is not None and int(status.item()) != 0:
+            raise _native.NativeLibraryError(
+                f"fos_gemm_nvfp4_fused_a: a bounded device-side wait timed out (site {int(status.item())})")
+        return out
+
+    @classmethod
     def quantized_matmul_scatter(cls, input: QuantizedTensor, other: QuantizedTensor, *, out_dtype: DataType,
                                  d_peers, world: int, rank: int) -> None:
         """First half of a row-parallel layer's exchange: this rank's partial product `input @ other.T`, each

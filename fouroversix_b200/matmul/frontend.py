@@ -27,14 +27,24 @@ def quantized_matmul(
     input_config: QuantizationConfig | None = None,
     other_config: QuantizationConfig | None = None,
     out_dtype: DataType = DataType.bfloat16,
+    fuse_input_quantization: bool = False,
     **kwargs: Any,
 ) -> torch.Tensor:
     """`input @ other.T` in FP4.  Either operand may be a high-precision CUDA tensor, in
-    which case it is quantized with the matching config (default: NVFP4, 4/6 MSE)."""
-    if isinstance(input, torch.Tensor):
-        input = quantize(input, input_config or QuantizationConfig())
+    which case it is quantized with the matching config (default: NVFP4, 4/6 MSE).
+    `fuse_input_quantization=True` (not in the reference) quantizes a high-precision `input`
+    inside the GEMM when its config allows (NVFP4, static_6 / static_4, 1-D blocks): same bits,
+    no packed activation in memory; other configs take the usual two steps."""
     if isinstance(other, torch.Tensor):
         other = quantize(other, other_config or QuantizationConfig())
+    if fuse_input_quantization and isinstance(input, torch.Tensor) and backend in (None, MatmulBackend.cutlass):
+        try:
+            return B200MatmulBackend.fused_quantize_matmul(input, other, input_config or QuantizationConfig(),
+                                                           out_dtype=DataType(out_dtype), **kwargs)
+        except ValueError:
+            pass                                   # not a case of the fused kernel: quantize first
+    if isinstance(input, torch.Tensor):
+        input = quantize(input, input_config or QuantizationConfig())
 
     impl = B200MatmulBackend if backend is None else AVAILABLE_BACKENDS.get(MatmulBackend(backend))
     if impl is None:

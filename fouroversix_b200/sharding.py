@@ -165,14 +165,22 @@ class TensorParallelLinear(nn.Module):
             extra["max_ctas"] = max_ctas          # per call: nothing process-wide is touched
         return self._matmul(x, self.weight, input_config=act_cfg, out_dtype=self.config.output_dtype, **extra)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor | QuantizedTensor) -> torch.Tensor:
+        act_cfg = self.config.get_activation_config()
+        if isinstance(x, QuantizedTensor):
+            # an activation that is already quantized (and, for scattered_input layers, already gathered):
+            # layers that read the same activation (gate_proj / up_proj, or q / k / v kept apart) share one
+            # quantization or one gather (`quantize_input`)
+            if self.mode != "column" and self.world_size > 1:
+                raise ValueError("a row-parallel layer quantizes its own K shard")
+            out = self._gemm(x, act_cfg)
+            return out if self.bias is None else out + self.bias
         lead = x.shape[:-1]
         x2d = x.reshape(-1, x.shape[-1])
-        act_cfg = self.config.get_activation_config()
         if self.world_size == 1:
             out = self._gemm(x2d, act_cfg)
         elif self.mode == "column":
-            out = self._gemm(self._gather_quantized(x2d, act_cfg) if self.scattered_input else x2d, act_cfg)
+            out = self._column_from_slab(x2d, act_cfg) if self.scattered_input else self._gemm(x2d, act_cfg)
         elif self.scatter_output:
             out = self._row_parallel_scattered(x2d, act_cfg)
         else:
@@ -184,6 +192,16 @@ class TensorParallelLinear(nn.Module):
         if out.shape[0] != x2d.shape[0]:
             return out                    # slab hand-off: the rows are not the input's rows (2-D in, 2-D out)
         return out.reshape(*lead, out.shape[-1])
+
+    def quantize_input(self, x: torch.Tensor) -> QuantizedTensor:
+        """The quantized activation this column-parallel layer would build from `x` (the full activation, or this
+        rank's row slab for a scattered_input layer): pass it to `forward` of every layer that reads the same
+        activation."""
+        act_cfg = self.config.get_activation_config()
+        x2d = x.reshape(-1, x.shape[-1])
+        if self.scattered_input and self.world_size > 1:
+            return self._gather_quantized(x2d, act_cfg)
+        return self._quantize(x2d, act_cfg)
 
     # ------------------------------------------------------------------ row slabs between two layers
 
@@ -231,8 +249,10 @@ class TensorParallelLinear(nn.Module):
             else:
                 works.append(dist.reduce_scatter_tensor(mine, part, group=self.group, async_op=True))
         if on_gpu:
+            # the compute stream now follows everything the communication stream did, so the buffers it used
+            # can be reused in stream order (no record_stream: that would keep 512 MiB blocks from the
+            # allocator's free list until the side stream's events are polled)
             compute.wait_stream(self._comm_stream)
-            partial.record_stream(self._comm_stream)
         for w in works:
             w.wait()
         return slab
@@ -242,6 +262,16 @@ class TensorParallelLinear(nn.Module):
         amax, each quantizes its slab with it (the bytes of those rows of the unsharded quantization: blocks of
         16 along a row depend on nothing else), and codes and scales are all-gathered chunk by chunk into the
         layout the GEMM reads."""
+        xq, events = self._start_gather(slab, act_cfg)
+        if events:
+            compute = torch.cuda.current_stream(slab.device)
+            for ev in events:
+                compute.wait_event(ev)
+        return xq
+
+    def _start_gather(self, slab: torch.Tensor, act_cfg: QuantizationConfig):
+        """Quantizes the slab and starts the all-gathers of its chunks on the communication stream. Returns the
+        full QuantizedTensor (complete on a CPU group; on a GPU chunk i is complete once events[i] has fired)."""
         world = self.world_size
         if act_cfg.block_scale_2d or act_cfg.transpose or act_cfg.rht or DataType(act_cfg.dtype) != DataType.nvfp4:
             raise ValueError("the slab hand-off quantizes activations to NVFP4 with 1-D blocks, untransposed")
@@ -265,14 +295,58 @@ class TensorParallelLinear(nn.Module):
         scales = torch.empty(tokens * k_p // 16, dtype=torch.uint8, device=slab.device)
         sf_local = q.scale_factors.view(torch.uint8).reshape(-1)
         per_row = k_p // 16                                  # scale bytes per row; 128-row groups are contiguous
+        on_gpu = slab.device.type == "cuda"
+        events = []
+        if on_gpu:
+            if self._comm_stream is None:
+                self._comm_stream = torch.cuda.Stream(device=slab.device)
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream(slab.device))
+            self._comm_stream.wait_event(ready)
         for i in range(n_chunks):
-            dist.all_gather_into_tensor(codes[i * step: (i + 1) * step], q.values[i * piece: (i + 1) * piece].contiguous(),
-                                        group=self.group)
-            dist.all_gather_into_tensor(scales[i * step * per_row: (i + 1) * step * per_row],
-                                        sf_local[i * piece * per_row: (i + 1) * piece * per_row].contiguous(), group=self.group)
-        return QuantizedTensor(codes, scales.view(q.scale_factors.dtype), amax, q.dtype, (tokens, k), q.scale_rule,
-                               q.round_style, (tokens, k_p),
-                               scale_factors_are_in_blackwell_layout=q.scale_factors_are_in_blackwell_layout)
+            src_codes = q.values[i * piece: (i + 1) * piece]
+            src_sf = sf_local[i * piece * per_row: (i + 1) * piece * per_row]
+            dst_codes = codes[i * step: (i + 1) * step]
+            dst_sf = scales[i * step * per_row: (i + 1) * step * per_row]
+            if on_gpu:
+                with torch.cuda.stream(self._comm_stream):
+                    dist.all_gather_into_tensor(dst_codes, src_codes, group=self.group)
+                    dist.all_gather_into_tensor(dst_sf, src_sf, group=self.group)
+                    ev = torch.cuda.Event()
+                    ev.record(self._comm_stream)
+                events.append(ev)
+            else:
+                dist.all_gather_into_tensor(dst_codes, src_codes.contiguous(), group=self.group)
+                dist.all_gather_into_tensor(dst_sf, src_sf.contiguous(), group=self.group)
+        # (callers wait for the last event on the compute stream before they return, which orders every later
+        # use of these buffers after the gathers)
+        xq = QuantizedTensor(codes, scales.view(q.scale_factors.dtype), amax, q.dtype, (tokens, k), q.scale_rule,
+                             q.round_style, (tokens, k_p),
+                             scale_factors_are_in_blackwell_layout=q.scale_factors_are_in_blackwell_layout)
+        return xq, events
+
+    def _column_from_slab(self, slab: torch.Tensor, act_cfg: QuantizationConfig) -> torch.Tensor:
+        """Column-parallel layer fed by row slabs: the GEMM of chunk i runs as soon as its packed rows have been
+        gathered, while the gathers of the later chunks are still on the links."""
+        xq, events = self._start_gather(slab, act_cfg)
+        if len(events) <= 1:
+            if events:
+                torch.cuda.current_stream(slab.device).wait_event(events[0])
+            return self._gemm(xq, act_cfg)
+        tokens = xq.original_shape[0]
+        step = tokens // len(events)
+        n_out = self.weight.original_shape[0]
+        out = torch.empty(tokens, n_out, dtype=DataType(self.config.output_dtype).torch_dtype, device=slab.device)
+        compute = torch.cuda.current_stream(slab.device)
+        max_ctas = 0
+        if self.comm_sms > 0 and self._matmul is quantized_matmul:
+            max_ctas = max(1, torch.cuda.get_device_properties(slab.device).multi_processor_count - self.comm_sms)
+        for i, ev in enumerate(events):
+            compute.wait_event(ev)
+            last = i + 1 == len(events)
+            self._gemm(slice_rows(xq, i * step, (i + 1) * step), act_cfg, out=out[i * step: (i + 1) * step],
+                       max_ctas=0 if last else max_ctas)
+        return out
 
     def _peer_buffers(self, tokens: int, n_out: int, dtype: torch.dtype, dev: torch.device) -> dict:
         """Staging [world][tokens / world][n_out] and output [tokens][n_out] of this rank in symmetric

@@ -177,6 +177,26 @@ int fos_gemm_nvfp4_ex(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t
                       const fos_gemm_opts *opts, int32_t *status, void *stream);
 
 /*
+ * Activation quantization fused into the GEMM: D[m, n] = alpha[0] * sum_k q(x)[m, k] * B[n, k], where q is the
+ * NVFP4 quantization of x[m, k] (bf16 / fp16, row stride x_ld elements) with scale rule static_6 or static_4 and
+ * the per-tensor amax at x_amax (a device float: fos_amax, or a value the caller knows). The warps that would
+ * wait for the tile's epilogue build the packed A tile and its scale tiles in shared memory, so the codes and
+ * scales of x are never written to memory. Bit-identical to fos_quantize(x, static rule, amax_in = x_amax)
+ * followed by fos_gemm_nvfp4. alpha as for fos_gemm_nvfp4 (fos_gemm_alpha with x_amax and the rule).
+ * k must be a multiple of 64, x 32-byte aligned (base and row stride); the rows of A are padded to 128 in the
+ * kernel. Every CTA that shares rows of x quantizes them again (n_p / 256 times), so this pays for narrow outputs
+ * and costs time for wide ones; the 4/6 rules (two candidates per block) are not offered fused:
+ * FOS_ERR_UNSUPPORTED, quantize first.
+ *
+ * Replaces: the un-fused pair quantize(input) -> quantized_matmul of
+ * src/fouroversix/matmul/frontend.py:95-102 for static-rule activations.
+ */
+int fos_gemm_nvfp4_fused_a(const void *x, int x_dtype, int64_t x_ld, const float *x_amax, int x_rule,
+                           const uint8_t *b_codes, const uint8_t *b_sf, const float *alpha, void *d,
+                           int out_dtype, int64_t m, int64_t n_p, int64_t k, int64_t n, int64_t ldd,
+                           int32_t *status, void *stream);
+
+/*
  * The same GEMM for two MXFP4 operands (E8M0 scale per 32 values, scales in the 128 x 4 tile
  * order as fos_quantize(FOS_MXFP4, FOS_SF_TILED) writes them): tcgen05.mma kind::mxf4 with
  * scale_vec::2X. k_p must be a multiple of 128; everything else as for fos_gemm_nvfp4. The

@@ -178,6 +178,37 @@ def test_full_size_configs(name, m, n, k, rule):
     assert torch.equal(out2.float(), out.float() * 2)
 
 
+@pytest.mark.parametrize(("name", "m", "n", "k"), [("ragged", 200, 320, 192), ("one-tile", 128, 256, 64),
+                                                   ("narrow", 1000, 128, 1024), ("c2-act-x-weight", 8192, 4096, 4096),
+                                                   ("c5-qkv", 2048, 10240, 8192)])
+@pytest.mark.parametrize("rule", ["static_6", "static_4"])
+def test_fused_activation_quantization_equals_the_two_kernels(name, m, n, k, rule):
+    """fos_gemm_nvfp4_fused_a quantizes the activation tile by tile inside the GEMM: the output must be
+    bit-identical to fos_quantize (same static rule, same amax) followed by fos_gemm_nvfp4 with the same tile
+    width, for bf16 and fp16 activations and all three output types."""
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(m, k, generator=g)
+    x[:, torch.randperm(k, generator=g)[: max(1, k // 100)]] *= 20
+    w = (torch.randn(n, k, generator=g) * 0.02).bfloat16().to(DEV)
+    qw = fos.quantize(w)                                             # 4/6 weights, as in the decoder stack
+    cfg = fos.QuantizationConfig(scale_rule=rule)
+    for x_dtype, out_dtype in ((torch.bfloat16, "bfloat16"), (torch.float16, "float16"), (torch.bfloat16, "float32")):
+        xd = x.to(x_dtype).to(DEV)
+        want = B200MatmulBackend.quantized_matmul(fos.quantize(xd, cfg), qw, out_dtype=fos.DataType(out_dtype), check_status=True)
+        got = B200MatmulBackend.fused_quantize_matmul(xd, qw, cfg, out_dtype=fos.DataType(out_dtype), check_status=True)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"{name} {rule} {x_dtype} -> {out_dtype}"
+        if m > 4096:
+            break                                                    # the big shapes once
+    # through the front end; a 4/6 activation falls back to the two kernels
+    y = fos.quantized_matmul(xd, qw, input_config=cfg, fuse_input_quantization=True, out_dtype=fos.DataType(out_dtype))
+    assert torch.equal(y, got)
+    y46 = fos.quantized_matmul(xd, qw, fuse_input_quantization=True)
+    assert torch.equal(y46, fos.quantized_matmul(xd, qw))
+    with pytest.raises(ValueError, match="4/6"):
+        B200MatmulBackend.fused_quantize_matmul(xd, qw, fos.QuantizationConfig(), out_dtype=fos.DataType.bfloat16)
+
+
 # the linear layers of a Llama-3-70B-shaped decoder block (hidden 8192, MLP 28672, grouped-query qkv 10240):
 # out features N, in features K; gate_proj and up_proj have the same shape
 DECODER_LAYERS = [("qkv_proj", 10240, 8192), ("o_proj", 8192, 8192), ("gate_up_proj", 28672, 8192),

@@ -9,8 +9,8 @@ peer-memory forms, and the row-slab hand-off (reduce-scatter, common amax, all-g
 
 Tolerances. Against the fp32 sum of fp32 partials the layers differ by (a) the rounding of every partial
 to bf16 (2^-9 relative each), (b) the order of the fp32 additions inside the GEMM, (c) for NCCL, sums
-taken in bf16: max |error| <= 2e-2 * max |want| for NCCL paths, 1e-2 for the peer-memory paths (one
-rounding of each partial, fp32 sum by the owner). Packed slabs of the hand-off: bit-exact.
+taken in bf16: max |error| <= 2e-2 * max |want| on every path (a partial can be several times larger than
+the sum it goes into, and its bf16 rounding is relative to the partial). Packed slabs of the hand-off: bit-exact.
 """
 
 from __future__ import annotations
@@ -166,7 +166,7 @@ def test_column_then_row_parallel(world):
                 continue                                       # symmetric memory could not be set up on this machine
             err, repeatable, same = out[mode]
             peer_seen += 1
-            assert err < 1e-2, (mode, err)
+            assert err < 2e-2, (mode, err)
             assert repeatable and same, mode
         assert out["slab"] < 2e-2, out["slab"]
         assert out["packed_equal"], "slabs quantized with the common amax must equal the unsharded quantization"
