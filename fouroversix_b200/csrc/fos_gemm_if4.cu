@@ -144,8 +144,12 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int64_t num_tiles = num_m * num_n;
     const int64_t k_tiles = p.k_p / 64;
 
-    if (warp == 0 && lane == 0) {
+    // The producer and the MMA issuer run as whole warps with one elected lane issuing: with every value of the
+    // loop the same in all lanes the compiler keeps addresses and descriptors in uniform registers, which the
+    // TMA and tcgen05 instructions take directly; a lone thread pays for moving every operand over.
+    if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
+        const bool issue = elect_one();
         uint32_t it = 0;
         bool ok = true;
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
@@ -153,21 +157,25 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             tile_coords(t, num_m, num_n, mb, nb);
             for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                ok = mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 1);
+                ok = __all_sync(0xffffffffu, mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 1));
                 if (!ok) break;
                 const uint32_t stage = smem_base + s * STAGE_BYTES, bar = full_bar + 8 * s;
-                mbar_expect_tx(bar, STAGE_BYTES);   // rows past n_p are zero-filled and still counted
-                tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), static_cast<int>(mb * BLOCK_M), bar);
-                tma_load_2d(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES),
-                            static_cast<int>(nb * BLOCK_N), bar);
+                if (issue) {
+                    mbar_expect_tx(bar, STAGE_BYTES);   // rows past n_p are zero-filled and still counted
+                    tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), static_cast<int>(mb * BLOCK_M), bar);
+                    tma_load_2d(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES),
+                                static_cast<int>(nb * BLOCK_N), bar);
+                }
+                __syncwarp();
             }
         }
         if (!ok) {
             const unsigned long long t0 = global_timer_ns();
             while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
         }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
+        const bool issue = elect_one();
         uint32_t it = 0, tile_i = 0;
         bool ok = true;
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
@@ -176,23 +184,26 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int64_t n0 = nb * BLOCK_N;
             const uint32_t idesc = f16_idesc(static_cast<int>((p.n_p - n0) < BLOCK_N ? (p.n_p - n0) : BLOCK_N));
             const uint32_t acc = tile_i % ACC_STAGES, acc_ph = (tile_i / ACC_STAGES) & 1u;
-            ok = mbar_wait(acc_empty_bar + 8 * acc, acc_ph ^ 1u, abort_flag, p.status, 3);
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_empty_bar + 8 * acc, acc_ph ^ 1u, abort_flag, p.status, 3));
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
             for (int64_t kt = 0; kt < k_tiles; ++kt, ++it) {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
+                ok = __all_sync(0xffffffffu, mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2));
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t stage = smem_base + s * STAGE_BYTES;
                 const uint64_t a_desc = smem_desc(stage, 16, 1024, 2), b_desc = smem_desc(stage + A_BYTES, 16, 1024, 2);
+                if (issue) {
 #pragma unroll
-                for (int j = 0; j < MMAS_PER_STAGE; ++j)
-                    tc_mma_f16(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, (kt > 0 || j > 0) ? 1u : 0u);
-                tc_commit(empty_bar + 8 * s);
+                    for (int j = 0; j < MMAS_PER_STAGE; ++j)
+                        tc_mma_f16(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, (kt > 0 || j > 0) ? 1u : 0u);
+                    tc_commit(empty_bar + 8 * s);
+                }
+                __syncwarp();
             }
-            if (ok) tc_commit(acc_full_bar + 8 * acc);
+            if (ok && issue) tc_commit(acc_full_bar + 8 * acc);
         }
     } else if (warp >= 2) {
         // ------------------------------------------------------------------ epilogue

@@ -2,15 +2,19 @@
 //
 // Both operands are K-major packed E2M1 with one UE4M3 scale per 16 values, stored as
 // fos_quantize writes them (scales in 128-row x 4-block tiles of 512 bytes). The kernel
-// is persistent (one CTA per SM, static tile schedule) and warp specialised:
+// is persistent (one CTA per SM, static tile schedule) and warp specialised. Every role that
+// issues TMA or tcgen05 instructions runs as a WHOLE warp with one elected lane issuing: with
+// every value of its loop the same in all lanes the compiler keeps addresses and descriptors in
+// uniform registers, which those instructions take directly; a lone thread's values live in
+// ordinary registers and each instruction pays for moving its operands over (the single change
+// from "one thread" to "one warp, one elected lane" took 8192^3 from 256 to 235 us, and the MMA
+// rate of the CTA-pair kernel from 182 to 152 us).
 //
-//   warp 0      one lane issues the TMA loads of the A / B tiles (128-byte swizzle, no multicast)
-//               into a ring of shared-memory stages guarded by full / empty mbarriers
-//   warp 11     (15 with FOS_GEMM_SF_CP=0) one lane issues the TMA loads of the scale tiles (two tensor copies per stage)
-//               into a ring of its own, one slot longer than the operand ring and one stage
-//               ahead of it. A separate thread because a thread issues a copy every hundred
-//               cycles or so: with all copies of a stage on one thread, that thread set the pace.
-//   warp 1      allocates tensor memory; one lane issues tcgen05.mma kind::mxf4nvf4.block_scale
+//   warp 0      TMA loads: per stage the A / B tiles (128-byte swizzle, no multicast) into a ring of
+//               shared-memory stages guarded by full / empty mbarriers, and - one stage AHEAD of
+//               them, because their way into the MMA is longer - the two tensor copies of the
+//               scale tiles into a ring of their own that is one slot longer
+//   warp 1      allocates tensor memory; issues tcgen05.mma kind::mxf4nvf4.block_scale
 //               (K = 64 per instruction) with the fp32 accumulator in tensor memory;
 //               tcgen05.commit releases the stage
 //   warps 2..9  epilogue: tcgen05.ld the accumulator (each warp owns the 32 lanes of its
@@ -18,27 +22,20 @@
 //               rows < m and columns < n. 16-bit outputs are packed while they are read, so the
 //               warp's whole row segment sits in registers and the accumulator is handed back
 //               to the MMA warp before the first store; stores are 32 bytes per lane.
-//   warp 10     one lane copies each stage's scale tiles shared -> tensor memory with
-//               tcgen05.cp 32x128b.warpx4 (a 512-byte tile is 32 rows of 16 bytes, which every
-//               32-lane quadrant of tensor memory needs: the copy broadcasts it) into a ring of
-//               scale columns, one slot per scale stage, and tcgen05.commit's the slot's `ready`
-//               barrier. Issued from THIS thread the copies overlap the MMAs; issued from the MMA
-//               thread they ran in line with them (about 30 ns each) and cost a third of the run
-//               time. The alternative kept behind FOS_GEMM_SF_CP=0: four mover warps, ld.shared +
-//               tcgen05.st per quadrant, which reads every tile four times from shared memory.
-//               (Also measured slower: scales straight from global memory in mover warps; operand
-//               loads split over two issuing threads changed nothing; a second copying thread
-//               changed nothing.)
-//   12 warps in all (16 with FOS_GEMM_SF_CP=0, whose mover warps are 10..13): with 384 threads the
-//               epilogue's 64 packed registers fit without spills
+//               (FUSED_A: the same warps first build the A tiles and their scales, see below.)
+//   warps 10-11 copy each stage's scale tiles shared -> tensor memory with tcgen05.cp
+//               32x128b.warpx4 (a 512-byte tile is 32 rows of 16 bytes, which every 32-lane
+//               quadrant of tensor memory needs: the copy broadcasts it) into a ring of scale
+//               columns, one slot per scale stage, taking stages in turn, and tcgen05.commit
+//               the slot's `ready` barrier. Issued from the MMA warp the copies queue up in
+//               line with the MMAs (372 us at 8192^3); from warps of their own they overlap
+//               them, and two warps issue them faster than one (235 -> 219 us).
 //
-// What bounds the kernel: shared-memory bandwidth. Per K-block of 64 values the TMA unit writes
-// 13.5 KB (A 4, B 8, scales 1.5), the MMA reads 12 KB and the scale copy 1.5 KB (the movers: four
-// times that): 27 KB (31.5) at 128 bytes per cycle are 211 (246) cycles, against about 150 for the MMA itself.
-// The measured times with parts switched off follow that sum to a few percent, and the kernel
-// runs at nine tenths of it. (A CTA pair moves a third less per MMA: see the pair kernel.)
-// Shorter stages do not help: the single threads that issue copies and MMAs need a few hundred
-// cycles per stage whatever its size.
+// What bounds the kernel now (8192^3, parts switched off in a -DFOS_GEMM_DEBUG build): MMAs alone
+// 150 us, loads alone 148, loads + MMAs 176, everything 219. The scale copies are the largest
+// single cost: twelve per stage, each about 30 ns of the copying warp and about 14 cycles of the
+// tensor pipe that no MMA gets. Loads and MMAs together lose 26 us to the round trip of a stage
+// (four 48 KB stages cannot cover it) and to the shared-memory port both use.
 //
 // Every mbarrier wait is bounded (in SM cycles). A wait that gives up records where
 // in *status, raises a CTA-wide abort flag, and all roles fall through to the common exit,
@@ -62,14 +59,8 @@ constexpr int SF_LEAD = FOS_GEMM_SF_LEAD;   // 0 or 1: how many stages the scale
 #define FOS_GEMM_ST256 1
 #endif
 
-#ifndef FOS_GEMM_SF_CP
-#define FOS_GEMM_SF_CP 1
-#endif
-// 1: the scales reach tensor memory by tcgen05.cp issued from ONE thread of warp 10 (not the MMA
-// thread) instead of the four mover warps: shared memory is read once per tile instead of four times.
-constexpr bool SF_BY_CP = FOS_GEMM_SF_CP != 0;
-constexpr int SF_CP_THREADS = FOS_GEMM_SF_CP == 2 ? 2 : 1;     // issuing threads, taking stages in turn
-constexpr int NUM_THREADS = SF_BY_CP ? 384 : 512;                   // warps: 0 TMA (operands), 1 MMA, 2-9 epilogue, 10-13 scale movers, 14 spare, 15 TMA (scales)
+constexpr int SF_CP_WARPS = 2;                     // warps 10 and 11 issue the scale copies, taking stages in turn
+constexpr int NUM_THREADS = 384;                   // warps: 0 TMA, 1 MMA, 2-9 epilogue (FUSED_A: also the A operand), 10-11 scale copies
 constexpr int SF_COL0 = 256;                       // tensor-memory columns: accumulators first, then per
                                                    // stage 16 columns of A scales and N/8 of B scales
 
@@ -231,7 +222,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
         for (int j = 0; j < C::SF_SLOTS; ++j) {
             mbar_init(sf_full_bar + 8 * j, FUSED_A ? 9 : 1);
-            mbar_init(sf_ready_bar + 8 * j, SF_BY_CP ? 1 : 4);    // one arrival per scale-mover warp (or one commit)
+            mbar_init(sf_ready_bar + 8 * j, 1);                   // one commit by the warp that copied the slot
         }
         for (int a = 0; a < C::ACC_STAGES; ++a) {
             mbar_init(acc_full_bar + 8 * a, 1);
@@ -263,36 +254,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 #else
     constexpr bool dbg_no_sf = false, dbg_no_load = false, dbg_no_store = false, dbg_no_mma = false;
 #endif
-    if (warp == 0 && lane == 0 && !dbg_no_load) {
-        // ------------------------------------------------------------------ TMA producer: operands
-        uint32_t s = 0, ph = 0;
-        bool ok = true;
-        for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-            int64_t mb, nb;
-            tile_coords(t, num_m, num_n, mb, nb);
-            const int m0 = static_cast<int>(mb * BLOCK_M), n0 = static_cast<int>(nb * BLOCK_N);
-            for (int64_t kt = 0; kt < k_tiles; ++kt) {
-                ok = mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 1);
-                if (!ok) break;
-                const uint32_t stage = smem_base + s * C::STAGE_BYTES, bar = full_bar + 8 * s;
-                // rows beyond N and bytes beyond K are zero-filled by the TMA unit and still counted
-                mbar_expect_tx(bar, FUSED_A ? C::B_BYTES : C::STAGE_BYTES);
-                if (!FUSED_A) tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), m0, bar);
-                tma_load_2d(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES), n0, bar);
-                if (++s == C::STAGES) { s = 0; ph ^= 1u; }
-            }
-        }
-        if (!ok) {
-            // give copies that are still in flight time to land before the CTA exits
-            const unsigned long long t0 = global_timer_ns();
-            while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
-        }
-    } else if (warp == (SF_BY_CP ? 11 : 15) && lane == 0 && !dbg_no_load && !dbg_no_sf) {
-        // ------------------------------------------------------------------ TMA producer: scales
-        // A thread of its own (one thread issues a copy every hundred cycles or so, and five copies
-        // per stage from a single thread set the pace of the pipeline when measured), and SF_LEAD
-        // stages ahead of the operands: the scales' way into the MMA is longer (shared memory ->
-        // mover warps -> tensor memory), and with the same start they arrive last.
+    if (warp == 0 && !dbg_no_load) {
+        // ------------------------------------------------------------------ TMA producer: operands and scales
+        // One warp, one elected lane: per stage the two operand tiles and, SF_LEAD stages ahead of them (their
+        // way into the MMA is longer: shared memory -> tcgen05.cp -> tensor memory), the two scale copies into
+        // a ring of their own that is one slot longer.
+        const bool issue = elect_one();
         int64_t f_t = blockIdx.x, f_kt = 0;          // the stage whose scales are requested next
         uint32_t slot = 0;
         int a_group = 0, b_group = 0;
@@ -303,20 +270,22 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             a_group = static_cast<int>(mb);
             b_group = static_cast<int>(nb * C::N_GROUPS);
         };
-        auto issue_next = [&]() {
-            if (f_t >= num_tiles) return;
-            // two tensor copies per stage: [K-blocks kb0 .. kb0+3] x [one / N_GROUPS row groups] of
-            // 512-byte tiles; what lies beyond K or N is zero-filled and still counted
-            // (MXFP4: a tile spans two K-blocks, so the box of its maps is two tiles per group)
+        auto issue_next_scales = [&]() {
+            if (f_t >= num_tiles || dbg_no_sf) return;
+            // two tensor copies per stage: [K-blocks kb0 .. kb0+3] x [one / N_GROUPS row groups] of 512-byte tiles;
+            // what lies beyond K or N is zero-filled and still counted (MXFP4: a tile spans two K-blocks, so the
+            // box of its maps is two tiles per group)
             const int kb0 = static_cast<int>(f_kt * (p.mx ? KB_PER_STAGE / 2 : KB_PER_STAGE));
             const uint32_t dst = sf_base + slot * C::SF_SLOT_BYTES, bar = sf_full_bar + 8 * slot;
-            if (FUSED_A) {
-                mbar_expect_tx(bar, C::SFB_BYTES);
-            } else {
-                mbar_expect_tx(bar, p.mx ? C::SF_SLOT_BYTES / 2 : C::SF_SLOT_BYTES);   // MXFP4 maps fetch two tiles per group
-                tma_load_3d(dst, &map_sfa, 0, kb0, a_group, bar);
+            if (issue) {
+                if (FUSED_A) {
+                    mbar_expect_tx(bar, C::SFB_BYTES);
+                } else {
+                    mbar_expect_tx(bar, p.mx ? C::SF_SLOT_BYTES / 2 : C::SF_SLOT_BYTES);
+                    tma_load_3d(dst, &map_sfa, 0, kb0, a_group, bar);
+                }
+                tma_load_3d(dst + SFA_BYTES, &map_sfb, 0, kb0, b_group, bar);
             }
-            tma_load_3d(dst + SFA_BYTES, &map_sfb, 0, kb0, b_group, bar);
             if (++slot == C::SF_SLOTS) slot = 0;
             if (++f_kt == k_tiles) {
                 f_kt = 0;
@@ -325,25 +294,42 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
         };
         enter_tile();
-        for (int i = 0; i < SF_LEAD; ++i) issue_next();
+        for (int i = 0; i < SF_LEAD; ++i) issue_next_scales();
         uint32_t s = 0, ph = 0;
         bool ok = true;
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            int64_t mb, nb;
+            tile_coords(t, num_m, num_n, mb, nb);
+            const int m0 = static_cast<int>(mb * BLOCK_M), n0 = static_cast<int>(nb * BLOCK_N);
             for (int64_t kt = 0; kt < k_tiles; ++kt) {
-                // when the MMAs of the iteration STAGES back are done, the scale slot of the iteration
-                // SF_LEAD ahead of this one (SF_SLOTS = STAGES + SF_LEAD back from it) is free
-                ok = mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 7);
+                // the stage is free; so is the scale slot of the iteration SF_LEAD ahead (SF_SLOTS = STAGES +
+                // SF_LEAD back from it: its MMAs were done before this stage's)
+                ok = __all_sync(0xffffffffu, mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 1));
                 if (!ok) break;
-                issue_next();
+                const uint32_t stage = smem_base + s * C::STAGE_BYTES, bar = full_bar + 8 * s;
+                // rows beyond N and bytes beyond K are zero-filled by the TMA unit and still counted
+                if (issue) {
+                    mbar_expect_tx(bar, FUSED_A ? C::B_BYTES : C::STAGE_BYTES);
+                    if (!FUSED_A) tma_load_2d(stage, &map_a, static_cast<int>(kt * BLOCK_K_BYTES), m0, bar);
+                    tma_load_2d(stage + A_BYTES, &map_b, static_cast<int>(kt * BLOCK_K_BYTES), n0, bar);
+                }
+                issue_next_scales();
+                __syncwarp();
                 if (++s == C::STAGES) { s = 0; ph ^= 1u; }
             }
         }
         if (!ok) {
+            // give copies that are still in flight time to land before the CTA exits
             const unsigned long long t0 = global_timer_ns();
             while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
         }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
+        // (The whole warp runs this loop and one elected lane issues. With every value of the loop the same in
+        // all lanes the compiler keeps descriptors and addresses in uniform registers, which the tcgen05
+        // instructions take directly; a lone thread's values live in ordinary registers and every instruction
+        // pays for moving its operands over: 256 -> 235 us at 8192^3, the CTA-pair kernel 343 -> 249 us.)
+        const bool issue = elect_one();
         uint32_t s = 0, ph = 0, j = 0, jph = 0, tile_i = 0;      // operand stage / scale slot and their phases
         bool ok = true;
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
@@ -354,6 +340,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const uint32_t idesc = mma_idesc(n_valid);
             const uint32_t acc = tile_i % C::ACC_STAGES, acc_ph = (tile_i / C::ACC_STAGES) & 1u;
             ok = mbar_wait(acc_empty_bar + 8 * acc, acc_ph ^ 1u, abort_flag, p.status, 3);
+            ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
@@ -362,6 +349,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     ok = mbar_wait(full_bar + 8 * s, ph, abort_flag, p.status, 2);
                     if (ok && !dbg_no_sf) ok = mbar_wait(sf_ready_bar + 8 * j, jph, abort_flag, p.status, 5);
                 }
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 const int64_t kb0 = kt * KB_PER_STAGE;
@@ -373,7 +361,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const uint64_t b_desc = smem_desc(stage + A_BYTES, 16, 1024, 2);
                 const uint32_t sfa_tmem = tmem_base + SF_COL0 + j * C::SF_STAGE_COLS, sfb_tmem = sfa_tmem + 16;
                 if (p.mx) {
-                    for (int kb = 0; kb < nkb && !dbg_no_mma; ++kb)
+                    for (int kb = 0; kb < nkb && !dbg_no_mma && issue; ++kb)
                         tc_mma_mxf4(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, mma_idesc_mx(idesc, (kb & 1) * 2),
                                     sfa_tmem + 4 * (kb >> 1), sfb_tmem + (BLOCK_N / 32) * (kb >> 1),
                                     (kt > 0 || kb > 0) ? 1u : 0u);
@@ -381,16 +369,17 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     const uint32_t a_lo = desc_lo(stage, 16), b_lo = desc_lo(stage + A_BYTES, 16);
 #pragma unroll
                     for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
-                        if (kb < nkb && !dbg_no_mma)
+                        if (kb < nkb && !dbg_no_mma && issue)
                             tc_mma_nvf4_lo(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_tmem + 4 * kb,
                                            sfb_tmem + (BLOCK_N / 32) * kb, (kt > 0 || kb > 0) ? 1u : 0u);
                     }
                 }
-                tc_commit(empty_bar + 8 * s);          // stage (and scale slot) reusable once these MMAs are done
+                if (issue) tc_commit(empty_bar + 8 * s);          // stage (and scale slot) reusable once these MMAs are done
+                __syncwarp();
                 if (++s == C::STAGES) { s = 0; ph ^= 1u; }
                 if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
             }
-            if (ok) tc_commit(acc_full_bar + 8 * acc);  // accumulator complete
+            if (ok && issue) tc_commit(acc_full_bar + 8 * acc);  // accumulator complete
         }
     } else if (warp >= 2 && warp < 10) {
         // ------------------------------------------------------------------ epilogue
@@ -549,17 +538,19 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
             }
         }
-    } else if (SF_BY_CP && warp >= 10 && warp < 10 + SF_CP_THREADS && lane == 0 && !dbg_no_load && !dbg_no_sf) {
+    } else if (warp >= 10 && warp < 10 + SF_CP_WARPS && !dbg_no_load && !dbg_no_sf) {
         // ------------------------------------------------------------------ scale copies by tcgen05.cp
+        const bool issue = elect_one();
         uint32_t j = 0, jph = 0, turn = 0;
         bool ok = true;
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             for (int64_t kt = 0; kt < k_tiles; ++kt) {
-                if (SF_CP_THREADS > 1 && (turn++ & 1u) != static_cast<uint32_t>(warp - 10)) {
+                if (SF_CP_WARPS > 1 && (turn++ & 1u) != static_cast<uint32_t>(warp - 10)) {
                     if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
                     continue;
                 }
                 ok = mbar_wait(sf_full_bar + 8 * j, jph, abort_flag, p.status, 6);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t src = sf_base + j * C::SF_SLOT_BYTES, dst = tmem_base + SF_COL0 + j * C::SF_STAGE_COLS;
@@ -569,63 +560,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const uint32_t src_lo = desc_lo(src);
 #pragma unroll
                 for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
-                    if (kb >= ntile) break;
+                    if (kb >= ntile || !issue) break;
                     tc_copy_sf_lo(dst + 4 * kb, src_lo + ((kb * SF_TILE_BYTES) >> 4));
 #pragma unroll
                     for (int g = 0; g < C::N_GROUPS; ++g)
                         tc_copy_sf_lo(dst + 16 + (BLOCK_N / 32) * kb + 4 * g,
                                       src_lo + ((SFA_BYTES + (g * ntile + kb) * SF_TILE_BYTES) >> 4));
                 }
-                tc_commit(sf_ready_bar + 8 * j);     // arrives when the copies above are done
-                if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
-            }
-        }
-    } else if (!SF_BY_CP && warp >= 10 && warp < 14 && !dbg_no_load && !dbg_no_sf) {
-        // ------------------------------------------------------------------ scale movers
-        const int quad = warp & 3;
-        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-        uint32_t j = 0, jph = 0;
-        bool ok = true;
-        for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-            int64_t mb, nb;
-            tile_coords(t, num_m, num_n, mb, nb);
-            const int64_t n0 = nb * BLOCK_N;
-            for (int64_t kt = 0; kt < k_tiles; ++kt) {
-                ok = mbar_wait(sf_full_bar + 8 * j, jph, abort_flag, p.status, 6);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                const int64_t kb0 = kt * KB_PER_STAGE;
-                int nkb = static_cast<int>((k_blocks - kb0) < KB_PER_STAGE ? (k_blocks - kb0) : KB_PER_STAGE);
-                if (p.mx) nkb = (nkb + 1) >> 1;          // scale tiles in use: one per two K-blocks
-                const uint32_t sfa_smem = sf_base + j * C::SF_SLOT_BYTES + lane * 16, sfb_smem = sfa_smem + SFA_BYTES;
-                const uint32_t slot = lane_base + SF_COL0 + j * C::SF_STAGE_COLS;
-                uint32_t r[16];
-                // A: four columns per K-block = the 16 bytes of row `lane` of that K-block's tile
-#pragma unroll
-                for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
-                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                    if (kb < nkb) v = lds_16(sfa_smem + kb * SF_TILE_BYTES);
-                    r[4 * kb] = v.x; r[4 * kb + 1] = v.y; r[4 * kb + 2] = v.z; r[4 * kb + 3] = v.w;
-                }
-                tc_store_16cols(slot, r);
-                // B: per K-block N/32 columns, the row groups of 128 side by side
-#pragma unroll
-                for (int half = 0; half < C::SFB_COLS / 16; ++half) {
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int col = half * 16 + q * 4;                 // column inside the B part
-                        const int kb = col / (BLOCK_N / 32), g = (col % (BLOCK_N / 32)) / 4;
-                        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                        if (kb < nkb && n0 + 128 * g < p.n_p)
-                            v = lds_16(sfb_smem + (g * (p.mx ? KB_PER_STAGE / 2 : KB_PER_STAGE) + kb) * SF_TILE_BYTES);
-                        r[4 * q] = v.x; r[4 * q + 1] = v.y; r[4 * q + 2] = v.z; r[4 * q + 3] = v.w;
-                    }
-                    tc_store_16cols(slot + 16 + half * 16, r);
-                }
-                tc_wait_store();
-                tc_fence_before();
+                if (issue) tc_commit(sf_ready_bar + 8 * j);     // arrives when the copies above are done
                 __syncwarp();
-                if (lane == 0) mbar_arrive(sf_ready_bar + 8 * j);
                 if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
             }
         }
@@ -672,7 +615,7 @@ constexpr int STAGES = 6;
 constexpr int SF_SLOTS = 5;                                               // what tensor memory has room for
 constexpr int BARRIER_BYTES = 512;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SF_SLOTS * SF_SLOT_BYTES + 1024 + BARRIER_BYTES;
-constexpr int THREADS = 512;
+constexpr int THREADS = 384;                                              // warps: 0 TMA (operands), 1 MMA, 2-9 epilogue, 10 scale copies, 11 TMA (scales)
 constexpr int SF_STAGE_COLS = 16 + 32;                                    // A scales, B scales
 static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
 static_assert(SF_COL0 + SF_SLOTS * SF_STAGE_COLS <= TMEM_COLS, "scale ring does not fit tensor memory");
@@ -786,7 +729,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             const unsigned long long t0 = global_timer_ns();
             while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
         }
-    } else if (warp == 15 && lane == 0 && !dbg_no_load && !dbg_no_sf) {
+    } else if (warp == 11 && lane == 0 && !dbg_no_load && !dbg_no_sf) {
         // ------------------------------------------------------------------ TMA producer: scales (both CTAs)
         // Each CTA fetches the scales of its own 128 rows of A and of all 256 rows of B into its own
         // shared memory; both complete on the LEADER's barrier, like the operand copies.
@@ -820,13 +763,15 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             const unsigned long long t0 = global_timer_ns();
             while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
         }
-    } else if (warp == 1 && lane == 0 && leader) {
+    } else if (warp == 1 && leader) {
         // ------------------------------------------------------------------ MMA issuer (leader only)
+        const bool issue = elect_one();
         const uint32_t idesc = mma_idesc(TILE_N, 256);
         uint32_t s = 0, ph = 0, j = 0, jph = 0, tile_i = 0;
         bool ok = true;
         for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs, ++tile_i) {
             ok = mbar_wait_poll(acc_empty_bar, (tile_i & 1u) ^ 1u, abort_flag, p.status, 3);
+            ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
             for (int64_t kt = 0; kt < k_tiles; ++kt) {
@@ -834,26 +779,26 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     ok = mbar_wait_poll(full_bar + 8 * s, ph, abort_flag, p.status, 2);
                     if (ok && !dbg_no_sf) ok = mbar_wait_poll(sf_ready_bar + 8 * j, jph, abort_flag, p.status, 5);
                 }
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 const int64_t kb0 = kt * KB_PER_STAGE;
                 const int nkb = static_cast<int>((k_blocks - kb0) < KB_PER_STAGE ? (k_blocks - kb0) : KB_PER_STAGE);
                 const uint32_t stage = smem_base + s * STAGE_BYTES;
-                const uint64_t a_desc = smem_desc(stage, 16, 1024, 2);
-                const uint64_t b_desc = smem_desc(stage + A_BYTES, 16, 1024, 2);
                 const uint32_t sfa_tmem = tmem_base + SF_COL0 + j * SF_STAGE_COLS, sfb_tmem = sfa_tmem + 16;
                 const uint32_t a_lo = desc_lo(stage, 16), b_lo = desc_lo(stage + A_BYTES, 16);
 #pragma unroll
                 for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
-                    if (kb < nkb && !dbg_no_mma)
+                    if (kb < nkb && !dbg_no_mma && issue)
                         tc_mma_nvf4_pair_lo(tmem_base, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_tmem + 4 * kb,
                                             sfb_tmem + 8 * kb, (kt > 0 || kb > 0) ? 1u : 0u);
                 }
-                tc_commit_pair(empty_bar + 8 * s);
+                if (issue) tc_commit_pair(empty_bar + 8 * s);
+                __syncwarp();
                 if (++s == STAGES) { s = 0; ph ^= 1u; }
                 if (++j == SF_SLOTS) { j = 0; jph ^= 1u; }
             }
-            if (ok) tc_commit_pair(acc_full_bar);
+            if (ok && issue) tc_commit_pair(acc_full_bar);
         }
     } else if (warp >= 2 && warp < 10) {
         // ------------------------------------------------------------------ epilogue (both CTAs)
@@ -929,29 +874,33 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 }
             }
         }
-    } else if (warp == 10 && lane == 0 && leader && !dbg_no_load && !dbg_no_sf) {
+    } else if (warp == 10 && leader && !dbg_no_load && !dbg_no_sf) {
         // ------------------------------------------------------------------ scale copies (leader, for both CTAs)
         // tcgen05.cp with cta_group::2 copies, in each CTA, from that CTA's shared memory into its
         // tensor memory: one thread of the pair moves the scales of both, and no warp of the peer
         // has to report back.
+        const bool issue = elect_one();
         uint32_t j = 0, jph = 0;
         bool ok = true;
         for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
             for (int64_t kt = 0; kt < k_tiles; ++kt) {
                 ok = mbar_wait_poll(sf_full_bar + 8 * j, jph, abort_flag, p.status, 6);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t src = sf_base + j * SF_SLOT_BYTES, dst = tmem_base + SF_COL0 + j * SF_STAGE_COLS;
                 const uint32_t src_lo = desc_lo(src);
 #pragma unroll
                 for (int kb = 0; kb < KB_PER_STAGE; ++kb) {
+                    if (!issue) break;
                     tc_copy_sf_pair_lo(dst + 4 * kb, src_lo + ((kb * SF_TILE_BYTES) >> 4));
 #pragma unroll
                     for (int g = 0; g < 2; ++g)
                         tc_copy_sf_pair_lo(dst + 16 + 8 * kb + 4 * g,
                                            src_lo + ((SFA_BYTES + (g * KB_PER_STAGE + kb) * SF_TILE_BYTES) >> 4));
                 }
-                tc_commit_pair_local(sf_ready_bar + 8 * j);
+                if (issue) tc_commit_pair_local(sf_ready_bar + 8 * j);
+                __syncwarp();
                 if (++j == SF_SLOTS) { j = 0; jph ^= 1u; }
             }
         }

@@ -170,6 +170,15 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t is_elected;
+    asm volatile("{ .reg .pred p;\n"
+                 "elect.sync _|p, 0xffffffff;\n"
+                 "selp.u32 %0, 1, 0, p; }" : "=r"(is_elected));
+    return is_elected != 0;
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
