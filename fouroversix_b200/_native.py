@@ -53,6 +53,8 @@ SIGNATURES = {
                                      _c_ptr, _c_int, _c_ptr]),
     "fos_dequantize": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_i64,
                                 _c_ptr, _c_int, _c_i64, _c_ptr]),
+    "fos_dequantize_ex": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_i64,
+                                   _c_ptr, _c_int, _c_i64, _c_int, _c_int, _c_ptr]),
     "fos_gemm_alpha": (_c_int, [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr]),
     "fos_gemm_nvfp4": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_i64, _c_i64,
                                 _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),

@@ -20,7 +20,11 @@ struct DequantParams {
 };
 
 // One thread per 16-value block: 8 bytes of codes and one scale in, 16 values out. A CTA takes
-// runs of 256 blocks of one row at a time (contiguous codes in, contiguous values out).
+// runs of 256 blocks of one row (contiguous codes in, contiguous values out), DEPTH runs at a time: the
+// loads of all of them are issued before the first block is decoded, so a thread has DEPTH loads in
+// flight instead of one (with one, the kernel waited a memory latency per run: 29 us for 8192 x 4096).
+constexpr int DEQUANT_DEPTH = 4;
+
 template <typename OUT>
 __global__ void __launch_bounds__(256) dequantize_kernel(const DequantParams p) {
     const int64_t n_cb = p.cols_p >> 4;
@@ -28,27 +32,114 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantParams p) 
     const int chunks = (cb_used + 255) >> 8;
     const int64_t units = p.rows * chunks;
     const DequantConsts k = dequant_consts(__ldg(p.amax), p.divisor);
-    for (int64_t u = blockIdx.x; u < units; u += gridDim.x) {
-        const int64_t r = u / chunks;
-        const int cb = static_cast<int>(u - r * chunks) * 256 + static_cast<int>(threadIdx.x);
-        if (cb >= cb_used) continue;
-        const uint2 c = *reinterpret_cast<const uint2 *>(p.codes + r * (p.cols_p >> 1) + cb * 8);
-        const uint32_t sfb = p.sf[sf_offset(r, cb, n_cb, p.sf_tiled != 0)];
-        float v[16];
-        dequantize_block(c, sfb, p.format == FOS_IF4, k, v);
-        OUT *dst = static_cast<OUT *>(p.out) + r * p.ld_out + cb * 16;
-        const int64_t left = p.cols - static_cast<int64_t>(cb) * 16;
-        if (left >= 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-            __align__(16) OUT tmp[16];
+    for (int64_t u0 = blockIdx.x; u0 < units; u0 += static_cast<int64_t>(gridDim.x) * DEQUANT_DEPTH) {
+        uint2 c[DEQUANT_DEPTH];
+        uint32_t sfb[DEQUANT_DEPTH];
+        int64_t row[DEQUANT_DEPTH];
+        int col_block[DEQUANT_DEPTH];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) tmp[i] = to_out<OUT>(v[i]);
-            const uint4 *src4 = reinterpret_cast<const uint4 *>(tmp);
+        for (int d = 0; d < DEQUANT_DEPTH; ++d) {
+            const int64_t u = u0 + static_cast<int64_t>(d) * gridDim.x;
+            const int64_t r = u / chunks;
+            const int cb = static_cast<int>(u - r * chunks) * 256 + static_cast<int>(threadIdx.x);
+            row[d] = r;
+            col_block[d] = (u < units && cb < cb_used) ? cb : -1;
+            c[d] = make_uint2(0u, 0u);
+            sfb[d] = 0u;
+            if (col_block[d] >= 0) {
+                c[d] = *reinterpret_cast<const uint2 *>(p.codes + r * (p.cols_p >> 1) + cb * 8);
+                sfb[d] = p.sf[sf_offset(r, cb, n_cb, p.sf_tiled != 0)];
+            }
+        }
 #pragma unroll
-            for (int i = 0; i < static_cast<int>(sizeof(OUT)); ++i) reinterpret_cast<uint4 *>(dst)[i] = src4[i];
+        for (int d = 0; d < DEQUANT_DEPTH; ++d) {
+            const int cb = col_block[d];
+            if (cb < 0) continue;
+            float v[16];
+            dequantize_block(c[d], sfb[d], p.format == FOS_IF4, k, v);
+            OUT *dst = static_cast<OUT *>(p.out) + row[d] * p.ld_out + cb * 16;
+            const int64_t left = p.cols - static_cast<int64_t>(cb) * 16;
+            if (left >= 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                __align__(16) OUT tmp[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) tmp[i] = to_out<OUT>(v[i]);
+                const uint4 *src4 = reinterpret_cast<const uint4 *>(tmp);
+#pragma unroll
+                for (int i = 0; i < static_cast<int>(sizeof(OUT)); ++i) reinterpret_cast<uint4 *>(dst)[i] = src4[i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    if (i < left) dst[i] = to_out<OUT>(v[i]);
+            }
+        }
+    }
+}
+
+// The general form, for what the fast kernels above do not cover: a float32 intermediate
+// (QuantizeBackendBase.dequantize(..., intermediate_dtype=torch.float32), src/fouroversix/quantize/backend.py:
+// 88-160) and the raw values alone (dequantize_values, :164-189). One thread per block of 16 values, every
+// step one IEEE operation in the reference's order:
+//   value  E2M1 code as a number (exact in any type), or for an IF4 integer block I(int * fl32(6/7))
+//   scale  E4M3 / E8M0 byte converted to I
+//   I(value * scale), then for NVFP4 / IF4 (fp32 * amax) / divisor, then the cast to the output type
+// with I = fp16 or fp32. `values_only` stops after the first line (and writes the padded tensor).
+struct GeneralDequantParams {
+    const uint8_t *codes;
+    const uint8_t *sf;
+    const float *amax;
+    void *out;
+    int64_t rows_p, cols_p, rows, cols, ld_out;
+    int format, sf_tiled, intermediate_fp32, values_only;
+    float divisor;
+};
+
+__device__ __forceinline__ float round_to_intermediate(float v, bool fp32) { return fp32 ? v : as_fp16(v); }
+
+template <typename OUT>
+__global__ void __launch_bounds__(256) dequantize_general_kernel(const GeneralDequantParams p) {
+    const int block = p.format == FOS_MXFP4 ? 32 : 16;
+    const int64_t n_cb = p.cols_p / block;                      // scale bytes per row
+    const int64_t runs_per_row = (p.cols + 15) / 16, total = p.rows * runs_per_row;
+    const float amax = (p.amax != nullptr && !p.values_only) ? __ldg(p.amax) : 1.0f;
+    const float six_sevenths = static_cast<float>(6.0 / 7.0);
+    const bool f32 = p.intermediate_fp32 != 0;
+    OUT *out = static_cast<OUT *>(p.out);
+    for (int64_t u = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; u < total;
+         u += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = u / runs_per_row, col = (u - r * runs_per_row) * 16;
+        const uint2 c = *reinterpret_cast<const uint2 *>(p.codes + r * (p.cols_p >> 1) + (col >> 1));
+        uint32_t sfb = p.sf[sf_offset(r, col / block, n_cb, p.sf_tiled != 0)];
+        const bool is_int = p.format == FOS_IF4 && (sfb & 0x80u);
+        if (p.format == FOS_IF4) sfb &= 0x7fu;
+        float scale;
+        if (p.format == FOS_MXFP4) {
+            scale = sfb == 255u ? __uint_as_float(0x7fc00000u) : (sfb == 0u ? 0x1p-127f : __uint_as_float(sfb << 23));
         } else {
+            scale = e4m3_to_float(sfb);
+        }
+        scale = round_to_intermediate(scale, f32);              // (E8M0 -> fp16 overflows / underflows like the reference's cast)
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-                if (i < left) dst[i] = to_out<OUT>(v[i]);
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t byte = ((j < 4 ? c.x : c.y) >> ((j & 3) * 8)) & 0xffu;
+            float2 q;
+            if (is_int) {
+                q.x = __fmul_rn(static_cast<float>(static_cast<int>(byte << 28) >> 28), six_sevenths);
+                q.y = __fmul_rn(static_cast<float>(static_cast<int>(byte << 24) >> 28), six_sevenths);
+            } else {
+                q = e2m1x2_to_float2(byte);
+            }
+            float v[2] = {q.x, q.y};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float y;
+                if (p.values_only) {
+                    y = v[h];                                    // rounded once, to the output type, below
+                } else {
+                    y = round_to_intermediate(__fmul_rn(round_to_intermediate(v[h], f32), scale), f32);
+                    if (p.format != FOS_MXFP4) y = __fdiv_rn(__fmul_rn(y, amax), p.divisor);
+                }
+                if (col + 2 * j + h < p.cols) out[r * p.ld_out + col + 2 * j + h] = to_out<OUT>(y);
+            }
         }
     }
 }
@@ -96,6 +187,40 @@ extern "C" int fos_dequantize(const uint8_t *codes, const uint8_t *sf, const flo
     if (out_dtype == FOS_BF16) dequantize_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(p);
     else if (out_dtype == FOS_FP16) dequantize_kernel<__half><<<g, 256, 0, stream>>>(p);
     else dequantize_kernel<float><<<g, 256, 0, stream>>>(p);
+    FOS_CUDA_TRY(cudaGetLastError());
+    return FOS_OK;
+}
+
+extern "C" int fos_dequantize_ex(const uint8_t *codes, const uint8_t *sf, const float *amax, int format,
+                                 int scale_rule, int sf_layout, int64_t rows_p, int64_t cols_p, int64_t rows,
+                                 int64_t cols, void *out, int out_dtype, int64_t ld_out, int intermediate_dtype,
+                                 int values_only, void *stream_) {
+    using namespace fos;
+    if (intermediate_dtype != FOS_FP16 && intermediate_dtype != FOS_FP32) return FOS_ERR_UNSUPPORTED;
+    if (intermediate_dtype == FOS_FP16 && !values_only)
+        return fos_dequantize(codes, sf, amax, format, scale_rule, sf_layout, rows_p, cols_p, rows, cols, out, out_dtype,
+                              ld_out, stream_);
+    if (!codes || !sf || !out) return FOS_ERR_INVALID_ARGUMENT;
+    if (format != FOS_NVFP4 && format != FOS_IF4 && format != FOS_MXFP4) return FOS_ERR_INVALID_ARGUMENT;
+    if (!values_only && format != FOS_MXFP4 && !amax) return FOS_ERR_INVALID_ARGUMENT;
+    if (scale_rule < FOS_RULE_STATIC_6 || scale_rule > FOS_RULE_ABS_MAX) return FOS_ERR_INVALID_ARGUMENT;
+    if (sf_layout != FOS_SF_ROWMAJOR && sf_layout != FOS_SF_TILED) return FOS_ERR_INVALID_ARGUMENT;
+    if (rows_p <= 0 || cols_p <= 0 || rows_p % 128 != 0 || cols_p % (format == FOS_MXFP4 ? 128 : 64) != 0) return FOS_ERR_INVALID_ARGUMENT;
+    if (rows <= 0 || cols <= 0 || rows > rows_p || cols > cols_p || ld_out < cols) return FOS_ERR_INVALID_ARGUMENT;
+    if (out_dtype != FOS_BF16 && out_dtype != FOS_FP16 && out_dtype != FOS_FP32) return FOS_ERR_INVALID_ARGUMENT;
+    if (reinterpret_cast<uintptr_t>(codes) % 8 != 0) return FOS_ERR_MISALIGNED;
+    const int st = check_device();
+    if (st != FOS_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    GeneralDequantParams p{codes, sf, amax, out, rows_p, cols_p, rows, cols, ld_out, format, sf_layout == FOS_SF_TILED,
+                           intermediate_dtype == FOS_FP32, values_only != 0,
+                           format == FOS_MXFP4 ? 1.0f : dequant_divisor(format, scale_rule)};
+    int64_t blocks = (rows * ((cols + 15) / 16) + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    const unsigned g = static_cast<unsigned>(blocks);
+    if (out_dtype == FOS_BF16) dequantize_general_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(p);
+    else if (out_dtype == FOS_FP16) dequantize_general_kernel<__half><<<g, 256, 0, stream>>>(p);
+    else dequantize_general_kernel<float><<<g, 256, 0, stream>>>(p);
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;
 }

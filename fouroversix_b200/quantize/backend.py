@@ -145,8 +145,8 @@ class B200QuantizeBackend:
             raise ValueError(f"B200 dequantize: dtype {tensor.dtype.value} is not implemented")
         if tensor.device.type != "cuda":
             raise ValueError("B200 dequantize: tensor must live on a CUDA device (there is no CPU path)")
-        if intermediate_dtype != torch.float16:
-            raise ValueError("B200 dequantize: only the float16 intermediate is implemented")
+        if intermediate_dtype not in (torch.float16, torch.float32):
+            raise ValueError("B200 dequantize: the intermediate type must be float16 or float32")
         if tensor.dtype.scale_type in (ScaleType.nv, ScaleType.nv_if) and tensor.amax is None:
             raise ValueError("B200 dequantize: amax is required")
         rows, cols = tensor.original_shape
@@ -157,13 +157,35 @@ class B200QuantizeBackend:
         scales = tensor.scale_factors.contiguous()
         amax = None if tensor.amax is None else tensor.amax.to(device=dev, dtype=torch.float32)
         with torch.cuda.device(dev):
-            status = _native.lib().fos_dequantize(
+            status = _native.lib().fos_dequantize_ex(
                 values.data_ptr(), scales.data_ptr(), 0 if amax is None else amax.data_ptr(), _FORMATS[tensor.dtype],
                 tensor.scale_rule.cuda_id,
                 _native.FOS_SF_TILED if tensor.scale_factors_are_in_blackwell_layout else _native.FOS_SF_ROWMAJOR,
                 rows_p, cols_p, rows, cols, out.data_ptr(), _native.elem_code(dtype), out.stride(0),
-                _native.stream_ptr(dev))
+                _native.elem_code(intermediate_dtype), 0, _native.stream_ptr(dev))
         _native.check(status, "fos_dequantize")
+        return out
+
+    @classmethod
+    def dequantize_values(cls, tensor: QuantizedTensor, *, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """The raw values of a quantized tensor in `dtype`, padded shape, no scales applied (the reference's
+        QuantizeBackendBase.dequantize_values, src/fouroversix/quantize/backend.py:164-189): E2M1 codes as numbers,
+        IF4 integer blocks as integer * 6/7."""
+        if tensor.dtype not in _FORMATS:
+            raise ValueError(f"B200 dequantize: dtype {tensor.dtype.value} is not implemented")
+        if tensor.device.type != "cuda":
+            raise ValueError("B200 dequantize: tensor must live on a CUDA device (there is no CPU path)")
+        rows_p, cols_p = tensor.padded_shape
+        dev = tensor.device
+        out = torch.empty(rows_p, cols_p, dtype=dtype, device=dev)
+        with torch.cuda.device(dev):
+            status = _native.lib().fos_dequantize_ex(
+                tensor.values.contiguous().data_ptr(), tensor.scale_factors.contiguous().data_ptr(), 0,
+                _FORMATS[tensor.dtype], tensor.scale_rule.cuda_id,
+                _native.FOS_SF_TILED if tensor.scale_factors_are_in_blackwell_layout else _native.FOS_SF_ROWMAJOR,
+                rows_p, cols_p, rows_p, cols_p, out.data_ptr(), _native.elem_code(dtype), out.stride(0),
+                _native.FOS_FP16, 1, _native.stream_ptr(dev))
+        _native.check(status, "fos_dequantize_ex")
         return out
 
     @classmethod

@@ -130,6 +130,22 @@ int fos_dequantize(const uint8_t *codes, const uint8_t *sf, const float *amax, i
                    void *stream);
 
 /*
+ * fos_dequantize with the two options of the reference's back-end interface it leaves out:
+ *   intermediate_dtype  FOS_FP16 (what fos_dequantize does) or FOS_FP32: the type in which value and scale are
+ *                       represented and multiplied (QuantizeBackendBase.dequantize(..., intermediate_dtype=...),
+ *                       src/fouroversix/quantize/backend.py:88-160; the reference's tests use float32,
+ *                       tests/test_quantize.py:442)
+ *   values_only         non-zero: only the raw values (E2M1 codes as numbers, IF4 integer blocks times 6/7), no scale,
+ *                       no amax (QuantizeBackendBase.dequantize_values, src/fouroversix/quantize/backend.py:164-189);
+ *                       pass rows = rows_p and cols = cols_p for the padded tensor the reference returns
+ * amax may be NULL for FOS_MXFP4 or with values_only.
+ */
+int fos_dequantize_ex(const uint8_t *codes, const uint8_t *sf, const float *amax, int format,
+                      int scale_rule, int sf_layout, int64_t rows_p, int64_t cols_p,
+                      int64_t rows, int64_t cols, void *out, int out_dtype, int64_t ld_out,
+                      int intermediate_dtype, int values_only, void *stream);
+
+/*
  * alpha[0] = amax_a[0] * amax_b[0] / (divisor(format_a, rule_a) * divisor(format_b, rule_b))
  * computed on the device (no host synchronisation).
  *

@@ -373,3 +373,38 @@ def test_mxfp4_matches_reference_and_oracle(oracle):
     cfg = fos.QuantizationConfig(dtype="mxfp4", scale_rule="static_6")
     fake = fos.quantize(x, fos.QuantizationConfig(dtype="mxfp4", scale_rule="static_6", pseudo_quantize=True))
     assert torch.equal(fake.view(torch.int16), fos.dequantize(fos.quantize(x, cfg), torch.bfloat16).view(torch.int16))
+
+
+def test_float32_intermediate_and_raw_values_match_the_reference():
+    """`dequantize(..., intermediate_dtype=torch.float32)` (what the reference's own pseudo-quantize test uses,
+    tests/test_quantize.py:442) and `dequantize_values`, bit for bit against outputs of the reference's PyTorch
+    backend on tensors it quantized itself (tests/golden/make_golden_dequant32.py)."""
+    import io
+    import lzma
+    from pathlib import Path
+
+    raw = lzma.decompress((Path(__file__).parent / "golden" / "reference_golden_dequant32.pt.xz").read_bytes())
+    gold = torch.load(io.BytesIO(raw), weights_only=False)
+    assert len(gold["cases"]) == 20
+    for case in gold["cases"]:
+        cfg = case["config"]
+        scale_dtype = torch.float8_e8m0fnu if cfg["dtype"] == "mxfp4" else torch.float8_e4m3fn
+        q = fos.QuantizedTensor(case["values"].to(DEV), case["scale_factors"].to(DEV).view(scale_dtype),
+                                None if case["amax"] is None else case["amax"].to(DEV), cfg["dtype"], case["original_shape"],
+                                case["scale_rule"], "nearest", case["padded_shape"],
+                                scale_factors_are_in_blackwell_layout=case["tiled"])
+        what = (case["input"], cfg)
+        for dtype, key in ((torch.bfloat16, "dequant32_bf16"), (torch.float32, "dequant32_fp32")):
+            got = fos.dequantize(q, dtype, intermediate_dtype=torch.float32)
+            want = case[key]
+            assert got.shape == want.shape and got.dtype == want.dtype, what
+            assert torch.equal(got.cpu().view(torch.int16 if dtype == torch.bfloat16 else torch.int32),
+                               want.view(torch.int16 if dtype == torch.bfloat16 else torch.int32)), (what, key)
+        for dtype, key in ((torch.float16, "values_fp16"), (torch.float32, "values_fp32")):
+            got = B200QuantizeBackend.dequantize_values(q, dtype=dtype)
+            want = case[key]
+            assert got.shape == want.shape, what
+            assert torch.equal(got.cpu().view(torch.int16 if dtype == torch.float16 else torch.int32),
+                               want.view(torch.int16 if dtype == torch.float16 else torch.int32)), (what, key)
+    with pytest.raises(ValueError, match="intermediate"):
+        fos.dequantize(q, torch.bfloat16, intermediate_dtype=torch.bfloat16)
