@@ -22,6 +22,8 @@ FOS_QUANTIZE_EXACT_ONLY = 1
 FOS_QUANTIZE_RHT = 2
 FOS_QUANTIZE_NO_TMA = 4
 FOS_QUANTIZE_GENERAL_KERNEL = 8
+FOS_QUANTIZE_UNBIASED = 16
+FOS_DEQUANT_VALUES_ONLY, FOS_DEQUANT_UNBIASED = 1, 2
 
 _c_i64, _c_int, _c_ptr = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
 
@@ -56,6 +58,7 @@ SIGNATURES = {
     "fos_dequantize_ex": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_i64,
                                    _c_ptr, _c_int, _c_i64, _c_int, _c_int, _c_ptr]),
     "fos_gemm_alpha": (_c_int, [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr]),
+    "fos_gemm_alpha_ex": (_c_int, [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]),
     "fos_gemm_nvfp4": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_i64, _c_i64,
                                 _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
     "fos_gemm_nvfp4_fused_a": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,

@@ -194,10 +194,12 @@ extern "C" int fos_dequantize(const uint8_t *codes, const uint8_t *sf, const flo
 extern "C" int fos_dequantize_ex(const uint8_t *codes, const uint8_t *sf, const float *amax, int format,
                                  int scale_rule, int sf_layout, int64_t rows_p, int64_t cols_p, int64_t rows,
                                  int64_t cols, void *out, int out_dtype, int64_t ld_out, int intermediate_dtype,
-                                 int values_only, void *stream_) {
+                                 int flags, void *stream_) {
     using namespace fos;
+    const int values_only = flags & FOS_DEQUANT_VALUES_ONLY;
+    const bool unbiased = (flags & FOS_DEQUANT_UNBIASED) != 0;
     if (intermediate_dtype != FOS_FP16 && intermediate_dtype != FOS_FP32) return FOS_ERR_UNSUPPORTED;
-    if (intermediate_dtype == FOS_FP16 && !values_only)
+    if (intermediate_dtype == FOS_FP16 && !values_only && !unbiased)
         return fos_dequantize(codes, sf, amax, format, scale_rule, sf_layout, rows_p, cols_p, rows, cols, out, out_dtype,
                               ld_out, stream_);
     if (!codes || !sf || !out) return FOS_ERR_INVALID_ARGUMENT;
@@ -215,6 +217,9 @@ extern "C" int fos_dequantize_ex(const uint8_t *codes, const uint8_t *sf, const 
     GeneralDequantParams p{codes, sf, amax, out, rows_p, cols_p, rows, cols, ld_out, format, sf_layout == FOS_SF_TILED,
                            intermediate_dtype == FOS_FP32, values_only != 0,
                            format == FOS_MXFP4 ? 1.0f : dequant_divisor(format, scale_rule)};
+    // stochastic_unbiased tensors carry maxima scaled by 16/17: the product is formed in double, as the reference
+    // forms it as a Python float, and rounded to binary32 once
+    if (unbiased && format != FOS_MXFP4) p.divisor = static_cast<float>(static_cast<double>(p.divisor) * (16.0 / 17.0));
     int64_t blocks = (rows * ((cols + 15) / 16) + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     const unsigned g = static_cast<unsigned>(blocks);
@@ -227,13 +232,20 @@ extern "C" int fos_dequantize_ex(const uint8_t *codes, const uint8_t *sf, const 
 
 extern "C" int fos_gemm_alpha(const float *amax_a, int format_a, int rule_a, const float *amax_b, int format_b,
                               int rule_b, float *alpha, void *stream_) {
+    return fos_gemm_alpha_ex(amax_a, format_a, rule_a, 0, amax_b, format_b, rule_b, 0, alpha, stream_);
+}
+
+extern "C" int fos_gemm_alpha_ex(const float *amax_a, int format_a, int rule_a, int unbiased_a, const float *amax_b,
+                                 int format_b, int rule_b, int unbiased_b, float *alpha, void *stream_) {
     using namespace fos;
     if (!amax_a || !amax_b || !alpha) return FOS_ERR_INVALID_ARGUMENT;
     int st = check_device();
     if (st != FOS_OK) return st;
-    // the reference multiplies the integer constants exactly before the one division
-    const float denom = static_cast<float>(static_cast<double>(dequant_divisor(format_a, rule_a)) *
-                                           static_cast<double>(dequant_divisor(format_b, rule_b)));
+    // the reference multiplies the constants as Python numbers (exactly, for the integers) before the one division
+    double product = static_cast<double>(dequant_divisor(format_a, rule_a)) * static_cast<double>(dequant_divisor(format_b, rule_b));
+    if (unbiased_a) product *= 16.0 / 17.0;
+    if (unbiased_b) product *= 16.0 / 17.0;
+    const float denom = static_cast<float>(product);
     alpha_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream_)>>>(amax_a, amax_b, denom, alpha);
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;

@@ -46,6 +46,7 @@ struct QuantParams {
     int x_is_ready;              // x was complete before the previous kernel in the stream started
     int rht;                     // rotate every block of 16 (random Hadamard transform) before quantizing
     int stochastic;              // stochastic rounding (1-D blocks, NVFP4, TMA-fed kernels only)
+    int unbiased;                // with it: every maximum is scaled by 16/17 (RoundStyle.stochastic_unbiased)
     uint32_t seed_lo, seed_hi;
     // fused fake quantization (quantize_rows_tma_kernel<.., true>): dequantized values instead of codes
     void *fake_out;              // [rows][fake_ld] elements of x's type
@@ -416,14 +417,29 @@ __device__ __forceinline__ float block_error(const float (&e)[16], int rule, flo
 struct TensorConsts {
     float amax, maxq, encode, decode;
     float encode0;    // encode, or 0 when amax is 0 (every block scale is then 0)
+    float block_div;  // 0: the block maximum is divided by maxq with the exact fast forms; else by this (maxq * 16/17)
     bool filter_ok;   // amax is in the range where the fast pre-filter's error bound holds
 };
 
+// `unbiased`: RoundStyle.stochastic_unbiased of the reference (src/fouroversix/utils.py:223-247): the largest
+// value and the product (largest value * largest scale) are multiplied by 16/17, as Python floats, before they
+// become binary32 tensors (src/fouroversix/quantize/pytorch/reference.py:203-218), which leaves the stochastically
+// rounded maximum room below the clamp.
 template <int KIND>
-__device__ __forceinline__ TensorConsts tensor_consts(float amax, int rule) {
+__device__ __forceinline__ TensorConsts tensor_consts(float amax, int rule, bool unbiased = false) {
     TensorConsts c;
     c.amax = amax;
     c.maxq = (KIND == KIND_STATIC && rule == FOS_RULE_STATIC_4) ? 4.0f : 6.0f;
+    c.block_div = 0.0f;
+    if (unbiased) {
+        const float maxsf_u = (KIND == KIND_ADAPTIVE) ? 256.0f : 448.0f;
+        c.block_div = static_cast<float>(static_cast<double>(c.maxq) * (16.0 / 17.0));
+        c.encode = __fdiv_rn(static_cast<float>(static_cast<double>(c.maxq) * maxsf_u * (16.0 / 17.0)), amax);
+        c.decode = __frcp_rn(c.encode);
+        c.encode0 = amax == 0.0f ? 0.0f : c.encode;
+        c.filter_ok = false;
+        return c;
+    }
     const float maxsf = (KIND == KIND_ADAPTIVE) ? 256.0f : 448.0f;
     c.encode = __fdiv_rn(c.maxq * maxsf, amax);
     c.decode = __frcp_rn(c.encode);
@@ -506,7 +522,8 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
 #pragma unroll
     for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(v[i]));
     bmax = block_max<TWO_D, TRANSPOSED>(bmax);
-    const float q = tc.maxq == 6.0f ? div6_exact(bmax) : __fmul_rn(bmax, 0.25f);   // bmax / maxq
+    const float q = tc.block_div != 0.0f ? __fdiv_rn(bmax, tc.block_div)
+                                         : (tc.maxq == 6.0f ? div6_exact(bmax) : __fmul_rn(bmax, 0.25f));   // bmax / maxq
     const float hp = __fmul_rn(q, tc.encode0);
     const bool filter_allowed = !TWO_D && rule == FOS_RULE_MSE && !exact_only && tc.filter_ok;   // unused with a table
 
@@ -1070,7 +1087,7 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
     // amax comes from the previous kernel in the stream; with programmatic dependent launch this
     // CTA may be running before that kernel has finished.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(p.amax), p.rule);
+    const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(p.amax), p.rule, EXTRAS && p.unbiased);
     if (p.amax_store != nullptr && threadIdx.x == 0 && blockIdx.x == 0) *p.amax_store = tc.amax;
     if (threadIdx.x < 128)
         lut[threadIdx.x] = scale_entry(threadIdx.x, tc, p.rule == FOS_RULE_MSE && !p.exact_only && tc.filter_ok);
@@ -1505,7 +1522,7 @@ quantize_cols_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
 
     // ---------------- consumers ----------------
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(p.amax), p.rule);
+    const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(p.amax), p.rule, EXTRAS && p.unbiased);
     if (p.amax_store != nullptr && threadIdx.x == 0 && blockIdx.x == 0) *p.amax_store = tc.amax;
     if (threadIdx.x < 128)
         lut[threadIdx.x] = scale_entry(threadIdx.x, tc, p.rule == FOS_RULE_MSE && !p.exact_only && tc.filter_ok);
@@ -1878,6 +1895,7 @@ static int quantize_entry(const void *x, int x_dtype, int64_t rows, int64_t cols
     p.rht = (flags & FOS_QUANTIZE_RHT) != 0;
     if (p.rht && p.out_cols % 16 != 0) return FOS_ERR_INVALID_ARGUMENT;   // blocks of 16 along the quantized axis
     p.stochastic = stochastic;
+    p.unbiased = stochastic && (flags & FOS_QUANTIZE_UNBIASED) != 0;
     p.seed_lo = static_cast<uint32_t>(seed);
     p.seed_hi = static_cast<uint32_t>(seed >> 32);
     const uintptr_t addr = reinterpret_cast<uintptr_t>(x);

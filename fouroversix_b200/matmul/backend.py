@@ -14,7 +14,7 @@ import torch
 from fouroversix_b200 import _native
 from fouroversix_b200.quantize import QuantizedTensor
 from fouroversix_b200.quantize.backend import B200QuantizeBackend
-from fouroversix_b200.utils import DataType
+from fouroversix_b200.utils import DataType, RoundStyle
 
 _OUT = {DataType.bfloat16: torch.bfloat16, DataType.float16: torch.float16, DataType.float32: torch.float32}
 _FORMATS = {DataType.nvfp4: _native.FOS_NVFP4, DataType.if4: _native.FOS_IF4, DataType.mxfp4: _native.FOS_MXFP4}
@@ -103,9 +103,10 @@ class B200MatmulBackend:
                     raise _native.NativeLibraryError(
                         f"fos_gemm_mxfp4: a bounded device-side wait timed out (site {int(status.item())})")
                 return out
-            _native.check(lib.fos_gemm_alpha(
-                input.amax.data_ptr(), fa, input.scale_rule.cuda_id,
-                other.amax.data_ptr(), fb, other.scale_rule.cuda_id, alpha.data_ptr(), stream), "fos_gemm_alpha")
+            _native.check(lib.fos_gemm_alpha_ex(
+                input.amax.data_ptr(), fa, input.scale_rule.cuda_id, int(input.round_style == RoundStyle.stochastic_unbiased),
+                other.amax.data_ptr(), fb, other.scale_rule.cuda_id, int(other.round_style == RoundStyle.stochastic_unbiased),
+                alpha.data_ptr(), stream), "fos_gemm_alpha")
             if native_fp4:
                 _native.check(lib.fos_gemm_nvfp4_ex(
                     a_vals.data_ptr(), a_sf.data_ptr(), b_vals.data_ptr(), b_sf.data_ptr(), alpha.data_ptr(),

@@ -79,10 +79,6 @@ class FourOverSixLinearFunction(torch.autograd.Function):
         if isinstance(cfg.disable_dgrad_quantization, str):
             raise NotImplementedError(
                 f"disable_dgrad_quantization={cfg.disable_dgrad_quantization!r} is not implemented (True / False are)")
-        if cfg.gradient_round_style == RoundStyle.stochastic_unbiased and not (
-                cfg.disable_dgrad_quantization and cfg.disable_wgrad_quantization):
-            raise NotImplementedError(
-                "stochastic_unbiased gradient rounding is not implemented; use 'stochastic' or 'nearest'")
 
         dy = grad_output.reshape(-1, grad_output.shape[-1])     # [tokens, out]
         x = input.reshape(-1, input.shape[-1])                   # [tokens, in]

@@ -54,9 +54,7 @@ class B200QuantizeBackend:
             return f"dtype {config.dtype.value} is not implemented (nvfp4, if4 and mxfp4 are)"
         if config.scale_rule not in config.dtype.supported_scale_rules:
             return f"scale rule {config.scale_rule.value} is not defined for {config.dtype.value}"
-        if config.round_style == RoundStyle.stochastic_unbiased:
-            return "stochastic_unbiased rounding is not implemented (nearest and stochastic are)"
-        if config.round_style == RoundStyle.stochastic and (config.dtype != DataType.nvfp4 or config.block_scale_2d):
+        if config.round_style.is_stochastic and (config.dtype != DataType.nvfp4 or config.block_scale_2d):
             return "stochastic rounding is implemented for NVFP4 with 1-D blocks"
         if config.rht and config.dtype == DataType.mxfp4:
             return "the random Hadamard transform is not implemented for mxfp4"
@@ -102,9 +100,10 @@ class B200QuantizeBackend:
                 0 if amax is None else amax.data_ptr(), values.data_ptr(), scales.data_ptr(),
                 amax_out.data_ptr(),
                 (_native.FOS_QUANTIZE_EXACT_ONLY if exact_only else 0) | (_native.FOS_QUANTIZE_RHT if config.rht else 0)
-                | {"auto": 0, "no_tma": _native.FOS_QUANTIZE_NO_TMA, "general": _native.FOS_QUANTIZE_GENERAL_KERNEL}[kernel])
+                | {"auto": 0, "no_tma": _native.FOS_QUANTIZE_NO_TMA, "general": _native.FOS_QUANTIZE_GENERAL_KERNEL}[kernel]
+                | (_native.FOS_QUANTIZE_UNBIASED if config.round_style == RoundStyle.stochastic_unbiased else 0))
         with torch.cuda.device(dev):
-            if config.round_style == RoundStyle.stochastic:
+            if config.round_style.is_stochastic:
                 if seed is None:
                     seed = int(torch.randint(0, 2 ** 62, (1,)).item())
                 status = _native.lib().fos_quantize_stochastic(*args, seed, _native.stream_ptr(dev))
@@ -162,7 +161,9 @@ class B200QuantizeBackend:
                 tensor.scale_rule.cuda_id,
                 _native.FOS_SF_TILED if tensor.scale_factors_are_in_blackwell_layout else _native.FOS_SF_ROWMAJOR,
                 rows_p, cols_p, rows, cols, out.data_ptr(), _native.elem_code(dtype), out.stride(0),
-                _native.elem_code(intermediate_dtype), 0, _native.stream_ptr(dev))
+                _native.elem_code(intermediate_dtype),
+                _native.FOS_DEQUANT_UNBIASED if tensor.round_style == RoundStyle.stochastic_unbiased else 0,
+                _native.stream_ptr(dev))
         _native.check(status, "fos_dequantize")
         return out
 
@@ -184,7 +185,7 @@ class B200QuantizeBackend:
                 _FORMATS[tensor.dtype], tensor.scale_rule.cuda_id,
                 _native.FOS_SF_TILED if tensor.scale_factors_are_in_blackwell_layout else _native.FOS_SF_ROWMAJOR,
                 rows_p, cols_p, rows_p, cols_p, out.data_ptr(), _native.elem_code(dtype), out.stride(0),
-                _native.FOS_FP16, 1, _native.stream_ptr(dev))
+                _native.FOS_FP16, _native.FOS_DEQUANT_VALUES_ONLY, _native.stream_ptr(dev))
         _native.check(status, "fos_dequantize_ex")
         return out
 

@@ -67,6 +67,9 @@ extern "C" {
                                           that axis (cols, or rows when transposing) must be a multiple of 16 */
 #define FOS_QUANTIZE_NO_TMA 4          /* kernel choice (testing aid; every kernel writes the same bytes): never a kernel
                                           fed by the TMA unit, i.e. treat x as if it were not 16-byte aligned */
+#define FOS_QUANTIZE_UNBIASED 16        /* fos_quantize_stochastic only: RoundStyle.stochastic_unbiased, every maximum scaled by 16/17
+                                          (src/fouroversix/utils.py:223-247); the same factor then belongs into
+                                          fos_dequantize_ex (FOS_DEQUANT_UNBIASED) and fos_gemm_alpha_ex */
 #define FOS_QUANTIZE_GENERAL_KERNEL 8  /* kernel choice (testing aid): the general TMA-fed kernel also for the
                                           configuration that has a kernel of its own (NVFP4 4/6 MSE, 1-D blocks) */
 
@@ -135,15 +138,20 @@ int fos_dequantize(const uint8_t *codes, const uint8_t *sf, const float *amax, i
  *                       represented and multiplied (QuantizeBackendBase.dequantize(..., intermediate_dtype=...),
  *                       src/fouroversix/quantize/backend.py:88-160; the reference's tests use float32,
  *                       tests/test_quantize.py:442)
- *   values_only         non-zero: only the raw values (E2M1 codes as numbers, IF4 integer blocks times 6/7), no scale,
- *                       no amax (QuantizeBackendBase.dequantize_values, src/fouroversix/quantize/backend.py:164-189);
- *                       pass rows = rows_p and cols = cols_p for the padded tensor the reference returns
- * amax may be NULL for FOS_MXFP4 or with values_only.
+ *   flags               FOS_DEQUANT_VALUES_ONLY: only the raw values (E2M1 codes as numbers, IF4 integer blocks times
+ *                       6/7), no scale, no amax (QuantizeBackendBase.dequantize_values,
+ *                       src/fouroversix/quantize/backend.py:164-189); pass rows = rows_p and cols = cols_p for the
+ *                       padded tensor the reference returns.
+ *                       FOS_DEQUANT_UNBIASED: the tensor was quantized with FOS_QUANTIZE_UNBIASED, so the divisor
+ *                       carries the factor 16/17 (round_style.adjustment_factor, backend.py:146-154)
+ * amax may be NULL for FOS_MXFP4 or with FOS_DEQUANT_VALUES_ONLY.
  */
+#define FOS_DEQUANT_VALUES_ONLY 1
+#define FOS_DEQUANT_UNBIASED 2
 int fos_dequantize_ex(const uint8_t *codes, const uint8_t *sf, const float *amax, int format,
                       int scale_rule, int sf_layout, int64_t rows_p, int64_t cols_p,
                       int64_t rows, int64_t cols, void *out, int out_dtype, int64_t ld_out,
-                      int intermediate_dtype, int values_only, void *stream);
+                      int intermediate_dtype, int flags, void *stream);
 
 /*
  * alpha[0] = amax_a[0] * amax_b[0] / (divisor(format_a, rule_a) * divisor(format_b, rule_b))
@@ -153,6 +161,10 @@ int fos_dequantize_ex(const uint8_t *codes, const uint8_t *sf, const float *amax
  */
 int fos_gemm_alpha(const float *amax_a, int format_a, int rule_a, const float *amax_b,
                    int format_b, int rule_b, float *alpha, void *stream);
+/* The same with the factor 16/17 per operand that was quantized with FOS_QUANTIZE_UNBIASED
+ * (src/fouroversix/matmul/cutlass/backend.py:95-96). */
+int fos_gemm_alpha_ex(const float *amax_a, int format_a, int rule_a, int unbiased_a, const float *amax_b,
+                      int format_b, int rule_b, int unbiased_b, float *alpha, void *stream);
 
 /*
  * D[m, n] = alpha[0] * sum_k A[m, k] * B[n, k]   ("TN": both operands K-major)

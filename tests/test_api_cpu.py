@@ -120,7 +120,7 @@ def test_backward_refuses_settings_it_does_not_implement():
 
     x, w, dy = torch.zeros(16, 64), torch.zeros(32, 64), torch.zeros(16, 32)
     for kwargs in (dict(wgrad_nvint4=True), dict(disable_dgrad_quantization="quantize_grad_only"),
-                   dict(quartet_ii_dtype="nvfp4"), dict(gradient_round_style="stochastic_unbiased")):
+                   dict(quartet_ii_dtype="nvfp4")):
         class Ctx:
             saved_tensors = (x, w, None)
             config = fos.ModuleQuantizationConfig(**kwargs)

@@ -152,13 +152,26 @@ def test_default_backward_uses_stochastic_gradient_rounding():
         assert cos > 0.95, cos
 
 
-def test_unbiased_stochastic_rounding_is_refused_clearly():
-    lin = nn.Linear(128, 128, bias=False, device=DEV, dtype=torch.bfloat16)
+def test_unbiased_stochastic_rounding_backward():
+    """gradient_round_style="stochastic_unbiased": the gradients' scale factors are computed against
+    16/17 of the format's range and the factor is undone in the GEMM's alpha, so the backward GEMMs
+    still estimate the true products (reference: quantize/reference.py:331-343, 430-440)."""
+    g = torch.Generator().manual_seed(4)
+    lin = nn.Linear(512, 256, bias=False, device=DEV, dtype=torch.bfloat16)
     layer = fos.FourOverSixLinear(
         lin, fos.ModuleQuantizationConfig(keep_master_weights=True, gradient_round_style="stochastic_unbiased"))
-    x = torch.randn(1, 128, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
-    with pytest.raises(NotImplementedError, match="stochastic_unbiased"):
-        layer(x).sum().backward()
+    x0 = torch.randn(1, 1024, 512, generator=g).bfloat16().to(DEV)
+    dy = (torch.randn(1, 1024, 256, generator=g) * 1e-3).bfloat16().to(DEV)
+    torch.manual_seed(1)
+    x = x0.clone().requires_grad_(True)
+    layer(x).backward(dy)
+    true_dx = _fp32_matmul(dy.reshape(-1, 256), lin.weight.data).reshape(1, 1024, 512)
+    true_dw = _fp32_matmul(dy.reshape(-1, 256).T, x0.reshape(-1, 512))
+    for got, true in ((x.grad, true_dx), (lin.weight.grad, true_dw)):
+        cos = torch.nn.functional.cosine_similarity(got.float().flatten(), true.flatten(), dim=0).item()
+        ratio = (got.float().norm() / true.norm()).item()
+        assert cos > 0.95, cos
+        assert 0.9 < ratio < 1.1, ratio
 
 
 def test_mxfp4_linear_forward():

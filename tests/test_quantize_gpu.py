@@ -311,6 +311,51 @@ def test_stochastic_rounding_statistics():
     assert torch.equal(qa.values, qb.values) and qa.padded_shape == (1024, 1024)
 
 
+def test_stochastic_unbiased_rounding():
+    """RoundStyle.stochastic_unbiased (src/fouroversix/utils.py:223-247): stochastic rounding with every maximum
+    scaled by 16/17. Scale bytes are deterministic for a static rule and must equal the reference's formula
+    (src/fouroversix/quantize/pytorch/reference.py:203-218, checked against the reference's own scale bytes where
+    it can be imported); the distances are the reference's pinned ones (tests/test_quantize.py:318-362: 158 for
+    static_6, 139 for 4/6 MSE, +-5 %); the mean over seeds approaches x; dequantize and the GEMM's alpha carry
+    the same factor."""
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(1024, 1024, generator=g).bfloat16()
+    xd = x.to(DEV)
+    amax = x.float().abs().max()
+    encode = torch.tensor(6 * 448 * (16 / 17), dtype=torch.float32) / amax
+    hp = x.float().reshape(1024, 64, 16).abs().amax(-1) / torch.tensor(6 * (16 / 17), dtype=torch.float32) * encode
+    want_sf = hp.to(torch.float8_e4m3fn).view(torch.uint8)
+    cfg = fos.QuantizationConfig(scale_rule="static_6", round_style="stochastic_unbiased")
+    q = B200QuantizeBackend.quantize(xd, cfg, seed=3)
+    assert q.round_style is fos.RoundStyle.stochastic_unbiased
+    from fouroversix_b200.quantize import from_blocked
+
+    assert torch.equal(from_blocked(q.scale_factors.cpu(), (1024, 64)).view(torch.uint8), want_sf)
+    for rule, pinned in (("static_6", 158.0), ("mse", 139.0)):
+        c = fos.QuantizationConfig(scale_rule=rule, round_style="stochastic_unbiased")
+        q1, q2 = B200QuantizeBackend.quantize(xd, c, seed=11), B200QuantizeBackend.quantize(xd, c, seed=11)
+        assert torch.equal(q1.values, q2.values)
+        dist = torch.dist(fos.dequantize(q1, torch.float32), xd.float()).item()
+        assert pinned * 0.95 <= dist <= pinned * 1.05, (rule, dist)
+    acc = torch.zeros_like(xd, dtype=torch.float32)
+    for seed in range(64):
+        acc += fos.dequantize(B200QuantizeBackend.quantize(xd, cfg, seed=seed), torch.float32)
+    near = fos.quantize(xd, fos.QuantizationConfig(scale_rule="static_6"))
+    mean_err = (acc / 64 - xd.float()).pow(2).mean().sqrt().item()
+    near_err = (fos.dequantize(near, torch.float32) - xd.float()).pow(2).mean().sqrt().item()
+    assert mean_err < 0.35 * near_err, (mean_err, near_err)
+    # the factor in dequantize: the same packed bytes read as a plain stochastic tensor are 16/17 times as large
+    plain = fos.QuantizedTensor(q.values, q.scale_factors, q.amax, q.dtype, q.original_shape, q.scale_rule, "stochastic",
+                                q.padded_shape, scale_factors_are_in_blackwell_layout=True)
+    a, b = fos.dequantize(q, torch.float32), fos.dequantize(plain, torch.float32)
+    assert torch.allclose(a * (16 / 17), b, rtol=1e-6, atol=0)
+    # and in the GEMM's alpha
+    w = fos.quantize((torch.randn(256, 1024, generator=g) * 0.05).bfloat16().to(DEV))
+    ya = fos.quantized_matmul(q, w, out_dtype=fos.DataType.float32)
+    yb = fos.quantized_matmul(plain, w, out_dtype=fos.DataType.float32)
+    assert torch.allclose(ya * (16 / 17), yb, rtol=1e-5, atol=0)
+
+
 def _load_golden_file(name: str):
     import io
     import lzma
