@@ -59,10 +59,15 @@ SIGNATURES = {
                                    _c_ptr, _c_int, _c_i64, _c_int, _c_int, _c_ptr]),
     "fos_gemm_alpha": (_c_int, [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr]),
     "fos_gemm_alpha_ex": (_c_int, [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]),
+    "fos_gemm_alpha_grouped": (_c_int, [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr]),
     "fos_gemm_nvfp4": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_i64, _c_i64,
                                 _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
     "fos_gemm_nvfp4_fused_a": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
                                         _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
+    "fos_quantize_grouped": (_c_int, [_c_ptr, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr, _c_int,
+                                      _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr]),
+    "fos_gemm_nvfp4_grouped": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
+                                        _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr]),
     "fos_gemm_mxfp4": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_i64, _c_i64,
                                 _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
     "fos_gemm_nvfp4_ex": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_i64, _c_i64,

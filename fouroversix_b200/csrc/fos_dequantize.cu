@@ -144,8 +144,9 @@ __global__ void __launch_bounds__(256) dequantize_general_kernel(const GeneralDe
     }
 }
 
-__global__ void alpha_kernel(const float *amax_a, const float *amax_b, float denom, float *alpha) {
-    alpha[0] = __fdiv_rn(__fmul_rn(amax_a[0], amax_b[0]), denom);
+__global__ void alpha_kernel(const float *amax_a, const float *amax_b, float denom, float *alpha, int count) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x)
+        alpha[i] = __fdiv_rn(__fmul_rn(amax_a[i], amax_b[i]), denom);
 }
 
 }  // namespace
@@ -237,8 +238,13 @@ extern "C" int fos_gemm_alpha(const float *amax_a, int format_a, int rule_a, con
 
 extern "C" int fos_gemm_alpha_ex(const float *amax_a, int format_a, int rule_a, int unbiased_a, const float *amax_b,
                                  int format_b, int rule_b, int unbiased_b, float *alpha, void *stream_) {
+    return fos_gemm_alpha_grouped(amax_a, format_a, rule_a, unbiased_a, amax_b, format_b, rule_b, unbiased_b, alpha, 1, stream_);
+}
+
+extern "C" int fos_gemm_alpha_grouped(const float *amax_a, int format_a, int rule_a, int unbiased_a, const float *amax_b,
+                                      int format_b, int rule_b, int unbiased_b, float *alpha, int count, void *stream_) {
     using namespace fos;
-    if (!amax_a || !amax_b || !alpha) return FOS_ERR_INVALID_ARGUMENT;
+    if (!amax_a || !amax_b || !alpha || count <= 0) return FOS_ERR_INVALID_ARGUMENT;
     int st = check_device();
     if (st != FOS_OK) return st;
     // the reference multiplies the constants as Python numbers (exactly, for the integers) before the one division
@@ -246,7 +252,8 @@ extern "C" int fos_gemm_alpha_ex(const float *amax_a, int format_a, int rule_a, 
     if (unbiased_a) product *= 16.0 / 17.0;
     if (unbiased_b) product *= 16.0 / 17.0;
     const float denom = static_cast<float>(product);
-    alpha_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream_)>>>(amax_a, amax_b, denom, alpha);
+    const int threads = count < 256 ? ((count + 31) / 32) * 32 : 256;
+    alpha_kernel<<<(count + threads - 1) / threads, threads, 0, static_cast<cudaStream_t>(stream_)>>>(amax_a, amax_b, denom, alpha, count);
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;
 }

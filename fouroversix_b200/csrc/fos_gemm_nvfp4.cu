@@ -61,6 +61,7 @@ constexpr int SF_LEAD = FOS_GEMM_SF_LEAD;   // 0 or 1: how many stages the scale
 
 constexpr int SF_CP_WARPS = 2;                     // warps 10 and 11 issue the scale copies, taking stages in turn
 constexpr int NUM_THREADS = 384;                   // warps: 0 TMA, 1 MMA, 2-9 epilogue (FUSED_A: also the A operand), 10-11 scale copies
+constexpr int MAX_GROUPS = 256;                    // of a grouped launch (their row ranges are kept in shared memory)
 constexpr int SF_COL0 = 256;                       // tensor-memory columns: accumulators first, then per
                                                    // stage 16 columns of A scales and N/8 of B scales
 
@@ -114,6 +115,13 @@ struct GemmParams {
     int scatter_rank;
     int64_t slab_rows;
     void *d_peer[8];
+    // Grouped problems (gemm_nvfp4_kernel<.., GROUPED>): A, its scales and D are the groups' rows one after
+    // the other, group g at rows group_start[g] .. group_start[g + 1] (multiples of 128, read on the device: the
+    // host need not know them) of which the first group_rows[g] are written to D; B and its scales are
+    // num_groups matrices of n_p rows each, one after the other; alpha has one entry per group.
+    const int32_t *group_start;
+    const int32_t *group_rows;
+    int num_groups;
 };
 
 // ---------------------------------------------------------------------------- MMA wrappers
@@ -190,7 +198,7 @@ __device__ __forceinline__ uint32_t mma_idesc_mx(uint32_t idesc, uint32_t sf_byt
 
 // ---------------------------------------------------------------------------- kernel
 
-template <int BLOCK_N, typename OUT, bool FUSED_A = false>
+template <int BLOCK_N, typename OUT, bool FUSED_A = false, bool GROUPED = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
@@ -213,6 +221,21 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // GROUPED: first row of every group (and one past the last group), and one past each group's last valid row
+    __shared__ int32_t grp_start[GROUPED ? MAX_GROUPS + 1 : 1], grp_end[GROUPED ? MAX_GROUPS : 1];
+    if constexpr (GROUPED) {
+        const int32_t cap = static_cast<int32_t>(p.m_p);
+        for (int g = threadIdx.x; g <= p.num_groups; g += NUM_THREADS) {
+            int32_t s0 = __ldg(p.group_start + g);
+            s0 = (s0 < 0 ? 0 : (s0 > cap ? cap : s0)) & ~127;                 // never beyond the buffers
+            grp_start[g] = s0;
+            if (g < p.num_groups) {
+                const int32_t r = __ldg(p.group_rows + g), e = s0 + (r < 0 ? 0 : r);
+                grp_end[g] = e > cap ? cap : e;
+            }
+        }
+    }
 
     if (threadIdx.x == 0) {
         // FUSED_A: besides the copy engine (B, B's scales), the eight warps that make A and its scales arrive
@@ -242,8 +265,19 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int64_t num_m = p.m_p / BLOCK_M;
+    const int64_t num_m = GROUPED ? grp_start[p.num_groups] / BLOCK_M : p.m_p / BLOCK_M;
     const int64_t num_n = (p.n_p + BLOCK_N - 1) / BLOCK_N;
+    // GROUPED: the group that row block mb lies in (the last g with grp_start[g] <= row; empty groups are skipped)
+    auto group_of = [&](int64_t mb) -> int {
+        if constexpr (!GROUPED) return 0;
+        const int32_t row = static_cast<int32_t>(mb * BLOCK_M);
+        int lo = 0, hi = p.num_groups - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (grp_start[mid] <= row) lo = mid; else hi = mid - 1;
+        }
+        return lo;
+    };
     const int64_t num_tiles = num_m * num_n;
     const int64_t k_blocks = p.k_p / 64;                       // MMA K-blocks in the problem
     const int64_t k_tiles = (k_blocks + KB_PER_STAGE - 1) / KB_PER_STAGE;
@@ -268,7 +302,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             int64_t mb, nb;
             tile_coords(f_t, num_m, num_n, mb, nb);
             a_group = static_cast<int>(mb);
-            b_group = static_cast<int>(nb * C::N_GROUPS);
+            b_group = static_cast<int>(nb * C::N_GROUPS) + group_of(mb) * static_cast<int>(p.n_p / 128);
         };
         auto issue_next_scales = [&]() {
             if (f_t >= num_tiles || dbg_no_sf) return;
@@ -300,7 +334,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             int64_t mb, nb;
             tile_coords(t, num_m, num_n, mb, nb);
-            const int m0 = static_cast<int>(mb * BLOCK_M), n0 = static_cast<int>(nb * BLOCK_N);
+            const int m0 = static_cast<int>(mb * BLOCK_M);
+            const int n0 = static_cast<int>(nb * BLOCK_N) + group_of(mb) * static_cast<int>(p.n_p);   // row of B
             for (int64_t kt = 0; kt < k_tiles; ++kt) {
                 // the stage is free; so is the scale slot of the iteration SF_LEAD ahead (SF_SLOTS = STAGES +
                 // SF_LEAD back from it: its MMAs were done before this stage's)
@@ -386,7 +421,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const int quad = warp & 3;                       // tensor-memory lanes 32*quad .. +31
         constexpr int COLS = BLOCK_N / 2;                // columns per warp: left or right half
         const int half = (warp - 2) >> 2;
-        const float alpha = __ldg(p.alpha);
+        float alpha = GROUPED ? 0.0f : __ldg(p.alpha);
+        int64_t row_end = p.m;
         OUT *out = static_cast<OUT *>(p.d);
         const bool vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((p.ldd * sizeof(OUT)) % 16 == 0);
         const bool vec32_ok = FOS_GEMM_ST256 && (reinterpret_cast<uintptr_t>(out) % 32 == 0) && ((p.ldd * sizeof(OUT)) % 32 == 0);
@@ -468,6 +504,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 if (!ok) break;
             }
             const int64_t row = mb * BLOCK_M + quad * 32 + lane, n0 = nb * BLOCK_N + half * COLS;
+            if constexpr (GROUPED) {
+                const int grp = group_of(mb);
+                alpha = __ldg(p.alpha + grp);
+                row_end = grp_end[grp];
+            }
             if (p.scatter_world > 1) {
                 // row block mb belongs to rank mb % world (interleaved, so that the peer traffic is spread
                 // over the whole run instead of coming in one burst per slab) and is block mb / world of
@@ -482,7 +523,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BLOCK_N + half * COLS;
-            const bool row_ok = row < p.m && !dbg_no_store;
+            const bool row_ok = row < row_end && !dbg_no_store;
             if constexpr (sizeof(OUT) == 2) {
                 // 16-bit outputs: scale, convert and pack while reading, so that the warp's whole
                 // row segment fits in registers and the accumulator goes back to the MMA warp
@@ -971,11 +1012,11 @@ int launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap 
     return FOS_OK;
 }
 
-template <int BLOCK_N, typename OUT, bool FUSED_A = false>
+template <int BLOCK_N, typename OUT, bool FUSED_A = false, bool GROUPED = false>
 int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &msa, const CUtensorMap &msb,
            const GemmParams &p, int sms, cudaStream_t stream) {
     using C = Cfg<BLOCK_N>;
-    auto kernel = gemm_nvfp4_kernel<BLOCK_N, OUT, FUSED_A>;
+    auto kernel = gemm_nvfp4_kernel<BLOCK_N, OUT, FUSED_A, GROUPED>;
     static OncePerDevice configured;   // per instantiation
     int dev = 0;
     FOS_CUDA_TRY(cudaGetDevice(&dev));
@@ -989,12 +1030,12 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &msa,
     return FOS_OK;
 }
 
-template <int BLOCK_N, bool FUSED_A = false>
+template <int BLOCK_N, bool FUSED_A = false, bool GROUPED = false>
 int launch_out(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &msa, const CUtensorMap &msb,
                const GemmParams &p, int sms, cudaStream_t stream) {
-    if (p.out_dtype == FOS_BF16) return launch<BLOCK_N, __nv_bfloat16, FUSED_A>(ma, mb, msa, msb, p, sms, stream);
-    if (p.out_dtype == FOS_FP16) return launch<BLOCK_N, __half, FUSED_A>(ma, mb, msa, msb, p, sms, stream);
-    return launch<BLOCK_N, float, FUSED_A>(ma, mb, msa, msb, p, sms, stream);
+    if (p.out_dtype == FOS_BF16) return launch<BLOCK_N, __nv_bfloat16, FUSED_A, GROUPED>(ma, mb, msa, msb, p, sms, stream);
+    if (p.out_dtype == FOS_FP16) return launch<BLOCK_N, __half, FUSED_A, GROUPED>(ma, mb, msa, msb, p, sms, stream);
+    return launch<BLOCK_N, float, FUSED_A, GROUPED>(ma, mb, msa, msb, p, sms, stream);
 }
 
 #ifdef FOS_GEMM_DEBUG
@@ -1154,6 +1195,56 @@ extern "C" int fos_gemm_nvfp4_fused_a(const void *x, int x_dtype, int64_t x_ld, 
     // (the kernel never touches the A maps in this mode; B's stand in for them)
     return wide ? launch_out<256, true>(map_b, map_b, map_sfb, map_sfb, p, sms, stream)
                 : launch_out<128, true>(map_b, map_b, map_sfb, map_sfb, p, sms, stream);
+}
+
+extern "C" int fos_gemm_nvfp4_grouped(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                                      const uint8_t *b_sf, const float *alpha, void *d, int out_dtype,
+                                      const int32_t *group_start, const int32_t *group_rows, int num_groups,
+                                      int64_t rows_capacity, int64_t n_p, int64_t k_p, int64_t n, int64_t ldd,
+                                      const fos_gemm_opts *opts, int32_t *status, void *stream_) {
+    using namespace fos;
+    const int variant = opts ? opts->variant : 0, max_ctas = opts ? opts->max_ctas : 0;
+    if ((variant != 0 && variant != 128 && variant != 256) || max_ctas < 0) return FOS_ERR_INVALID_ARGUMENT;
+    if (!a_codes || !a_sf || !b_codes || !b_sf || !alpha || !d || !group_start || !group_rows) return FOS_ERR_INVALID_ARGUMENT;
+    if (num_groups <= 0 || num_groups > MAX_GROUPS) return FOS_ERR_INVALID_ARGUMENT;
+    if (rows_capacity <= 0 || rows_capacity % 128 || n_p <= 0 || n_p % 128 || k_p < 64 || k_p % 64) return FOS_ERR_INVALID_ARGUMENT;
+    if (n <= 0 || n > n_p || ldd < n) return FOS_ERR_INVALID_ARGUMENT;
+    if (out_dtype != FOS_BF16 && out_dtype != FOS_FP16 && out_dtype != FOS_FP32) return FOS_ERR_INVALID_ARGUMENT;
+    if (reinterpret_cast<uintptr_t>(a_codes) % 16 || reinterpret_cast<uintptr_t>(b_codes) % 16 ||
+        reinterpret_cast<uintptr_t>(a_sf) % 16 || reinterpret_cast<uintptr_t>(b_sf) % 16)
+        return FOS_ERR_MISALIGNED;
+    const int64_t b_rows = n_p * num_groups;
+    if (rows_capacity > INT32_MAX || b_rows > INT32_MAX || k_p / 2 > INT32_MAX) return FOS_ERR_TOO_LARGE;
+    int st = check_device();
+    if (st != FOS_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int dev = 0, sms = 0;
+    FOS_CUDA_TRY(cudaGetDevice(&dev));
+    FOS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+    GemmParams p{a_sf, b_sf, alpha, d, status, rows_capacity, n_p, k_p, rows_capacity, n, ldd, out_dtype, 0, 0, nullptr, 0,
+                 nullptr, 0, 0, 0, 0, 0, {}};
+    p.group_start = group_start;
+    p.group_rows = group_rows;
+    p.num_groups = num_groups;
+    if (status) {
+        FOS_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    } else {
+        FOS_CUDA_TRY(wait_failures_ptr(&p.status));
+    }
+    // how many row blocks are in use is known on the device only: the grid is sized for the buffers, and
+    // CTAs that find no tile leave at once
+    const int64_t tiles_256 = (rows_capacity / BLOCK_M) * ((n_p + 255) / 256);
+    bool wide = n_p >= 256 && tiles_256 * 2 > sms;
+    if (variant == 128) wide = false;
+    if (variant == 256 && n_p >= 256) wide = true;
+    CUtensorMap map_a, map_b, map_sfa, map_sfb;
+    if ((st = make_operand_map(&map_a, a_codes, rows_capacity, k_p / 2, BLOCK_M)) != FOS_OK) return st;
+    if ((st = make_operand_map(&map_b, b_codes, b_rows, k_p / 2, wide ? 256 : 128)) != FOS_OK) return st;
+    if ((st = make_scale_map(&map_sfa, a_sf, rows_capacity / 128, k_p / 64, 1, KB_PER_STAGE)) != FOS_OK) return st;
+    if ((st = make_scale_map(&map_sfb, b_sf, b_rows / 128, k_p / 64, wide ? 2 : 1, KB_PER_STAGE)) != FOS_OK) return st;
+    return wide ? launch_out<256, false, true>(map_a, map_b, map_sfa, map_sfb, p, sms, stream)
+                : launch_out<128, false, true>(map_a, map_b, map_sfa, map_sfb, p, sms, stream);
 }
 
 extern "C" int fos_gemm_mxfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,

@@ -52,6 +52,10 @@ struct QuantParams {
     void *fake_out;              // [rows][fake_ld] elements of x's type
     int64_t fake_ld;
     float fake_divisor;
+    // grouped launch (TMA-fed row kernels, grid.y = group): group g is rows group_start[g] .. group_start[g + 1]
+    // (device values, multiples of 128) of x and of the outputs, quantized as a tensor of its own with amax[g]
+    const int32_t *group_start;
+    int num_groups;
 };
 
 
@@ -149,6 +153,41 @@ __global__ void __launch_bounds__(256) amax_kernel(const T *__restrict__ x, int6
         for (int w = 1; w < 8; ++w) m = fmaxf(m, warp_max[w]);
         // non-negative floats order like their bit patterns
         atomicMax(reinterpret_cast<int *>(amax), __float_as_int(m));
+    }
+}
+
+// One amax per group of rows: CTA (x, g) takes a share of rows group_start[g] .. + group_rows[g] and ends with an
+// atomicMax on amax[g] (zeroed by the caller in the stream before the launch).
+template <typename T>
+__global__ void __launch_bounds__(256) amax_grouped_kernel(const T *__restrict__ x, int64_t capacity, int64_t cols, int64_t ld,
+                                                           int vec, const int32_t *__restrict__ group_start,
+                                                           const int32_t *__restrict__ group_rows, float *amax) {
+    int64_t r0 = __ldg(group_start + blockIdx.y), rows = __ldg(group_rows + blockIdx.y);
+    r0 = r0 < 0 ? 0 : (r0 > capacity ? capacity : r0);
+    rows = rows < 0 ? 0 : (rows > capacity - r0 ? capacity - r0 : rows);
+    const T *base = x + r0 * ld;
+    const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    float m = 0.0f;
+    if (vec == 32) {
+        m = amax_chunks<T, 32>(base, rows, cols, ld, tid, stride);
+    } else if (vec == 16) {
+        m = amax_chunks<T, 16>(base, rows, cols, ld, tid, stride);
+    } else {
+        const int64_t total = rows * cols;
+        for (int64_t i = tid; i < total; i += stride) {
+            const int64_t r = i / cols, c = i - r * cols;
+            m = fmaxf(m, fabsf(elem_to_float<T>(base[r * ld + c])));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(FULL, m, o));
+    __shared__ float warp_max[8];
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) m = fmaxf(m, warp_max[w]);
+        if (m > 0.0f) atomicMax(reinterpret_cast<int *>(amax + blockIdx.y), __float_as_int(m));
     }
 }
 
@@ -1023,6 +1062,19 @@ constexpr int FEED_SMEM_BYTES = FEED_STAGES * FEED_STAGE_BYTES + 1024;
 
 // EXTRAS: the instantiation that can rotate blocks (random Hadamard transform) and round
 // stochastically; the plain one carries neither code path, which keeps its register count down.
+// Grouped launch: the tile rows of group blockIdx.y and its amax word. (The row ranges come from device
+// memory that earlier work in the stream wrote; grouped launches are ordinary launches, not programmatic
+// dependents, so that work is complete.) Ranges are clipped to the buffers.
+__device__ __forceinline__ void group_tiles(const QuantParams &p, int &tile_r0, int &tiles_r, const float *&amax_ptr) {
+    const int all = static_cast<int>(p.rows_p >> 7);
+    int t0 = __ldg(p.group_start + blockIdx.y) >> 7, t1 = __ldg(p.group_start + blockIdx.y + 1) >> 7;
+    t0 = t0 < 0 ? 0 : (t0 > all ? all : t0);
+    t1 = t1 < t0 ? t0 : (t1 > all ? all : t1);
+    tile_r0 = t0;
+    tiles_r = t1 - t0;
+    amax_ptr += blockIdx.y;
+}
+
 template <typename T, int KIND, bool FAKE = false, bool TWO_D = false, bool EXTRAS = false>
 __global__ void __launch_bounds__(FEED_THREADS, FOS_FEED_CTAS)
 quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantParams p) {
@@ -1037,7 +1089,10 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
 
     const uint32_t stage0 = (smem_u32(feed_smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_c = static_cast<int>(p.cols_p >> 6), tiles_r = static_cast<int>(p.rows_p >> 7);
+    const int tiles_c = static_cast<int>(p.cols_p >> 6);
+    int tiles_r = static_cast<int>(p.rows_p >> 7), tile_r0 = 0;
+    const float *amax_ptr = p.amax;
+    if (!FAKE && p.group_start != nullptr) group_tiles(p, tile_r0, tiles_r, amax_ptr);
     const int64_t n_tiles = static_cast<int64_t>(tiles_c) * tiles_r;
 
     if (threadIdx.x == 0) {
@@ -1051,9 +1106,9 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
     }
     __syncthreads();
 
-    // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ... in row-major tile order
+    // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ... in row-major tile order (of its group)
     const int step_r = static_cast<int>(gridDim.x) / tiles_c, step_c = static_cast<int>(gridDim.x) % tiles_c;
-    int tr = static_cast<int>(blockIdx.x) / tiles_c, tc_ = static_cast<int>(blockIdx.x) % tiles_c;
+    int tr = tile_r0 + static_cast<int>(blockIdx.x) / tiles_c, tc_ = static_cast<int>(blockIdx.x) % tiles_c;
     const int my_tiles = static_cast<int>((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
 
     if (warp == FEED_CONSUMERS / 32) {
@@ -1087,7 +1142,7 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
     // amax comes from the previous kernel in the stream; with programmatic dependent launch this
     // CTA may be running before that kernel has finished.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(p.amax), p.rule, EXTRAS && p.unbiased);
+    const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(amax_ptr), p.rule, EXTRAS && p.unbiased);
     if (p.amax_store != nullptr && threadIdx.x == 0 && blockIdx.x == 0) *p.amax_store = tc.amax;
     if (threadIdx.x < 128)
         lut[threadIdx.x] = scale_entry(threadIdx.x, tc, p.rule == FOS_RULE_MSE && !p.exact_only && tc.filter_ok);
@@ -1115,7 +1170,8 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
     const int64_t sf_step = p.sf_tiled ? static_cast<int64_t>(gridDim.x) * 512 : static_cast<int64_t>(step_r) * 128 * n_cb + step_c * 4;
     const int64_t sf_wrap = p.sf_tiled ? 0 : 127 * n_cb;
     int64_t code_off = static_cast<int64_t>(tr) * 128 * code_ld + tc_ * 32;
-    int64_t sf_off = p.sf_tiled ? static_cast<int64_t>(blockIdx.x) * 512 : static_cast<int64_t>(tr) * 128 * n_cb + tc_ * 4;
+    int64_t sf_off = p.sf_tiled ? (static_cast<int64_t>(tile_r0) * tiles_c + blockIdx.x) * 512
+                                : static_cast<int64_t>(tr) * 128 * n_cb + tc_ * 4;
 
     int fake_tr = tr;                                   // tile row of the current tile
     const DequantConsts dk = dequant_consts(tc.amax, p.fake_divisor);
@@ -1289,7 +1345,10 @@ quantize_rows_mse_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
 
     const uint32_t stage0 = (smem_u32(feed_smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_c = static_cast<int>(p.cols_p >> 6), tiles_r = static_cast<int>(p.rows_p >> 7);
+    const int tiles_c = static_cast<int>(p.cols_p >> 6);
+    int tiles_r = static_cast<int>(p.rows_p >> 7), tile_r0 = 0;
+    const float *amax_ptr = p.amax;
+    if (p.group_start != nullptr) group_tiles(p, tile_r0, tiles_r, amax_ptr);
     const int64_t n_tiles = static_cast<int64_t>(tiles_c) * tiles_r;
     const int64_t code_ld = p.cols_p >> 1, n_cb = p.cols_p >> 4;
 
@@ -1311,8 +1370,8 @@ quantize_rows_mse_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
         // ---------------- producer ----------------
         if (lane != 0) return;
         const int step_r = static_cast<int>(gridDim.x) / tiles_c, step_c = static_cast<int>(gridDim.x) % tiles_c;
-        int tr = static_cast<int>(blockIdx.x) / tiles_c, tc_ = static_cast<int>(blockIdx.x) % tiles_c;
-        int64_t tile = blockIdx.x;
+        int tr = tile_r0 + static_cast<int>(blockIdx.x) / tiles_c, tc_ = static_cast<int>(blockIdx.x) % tiles_c;
+        int64_t tile = static_cast<int64_t>(tile_r0) * tiles_c + blockIdx.x;
         if (!p.x_is_ready) asm volatile("griddepcontrol.wait;" ::: "memory");
         int issued = 0, s = 0;
         uint32_t parity = 1;   // of the "stage is free" barrier; the first round finds every stage free
@@ -1342,7 +1401,7 @@ quantize_rows_mse_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
 
     // ---------------- consumers ----------------
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const TensorConsts tc = tensor_consts<KIND_ADAPTIVE>(*reinterpret_cast<const volatile float *>(p.amax), p.rule);
+    const TensorConsts tc = tensor_consts<KIND_ADAPTIVE>(*reinterpret_cast<const volatile float *>(amax_ptr), p.rule);
     if (p.amax_store != nullptr && threadIdx.x == 0 && blockIdx.x == 0) *p.amax_store = tc.amax;
     if (threadIdx.x < 128)
         lut[threadIdx.x] = scale_entry(threadIdx.x, tc, p.rule == FOS_RULE_MSE && !p.exact_only && tc.filter_ok);
@@ -1621,9 +1680,16 @@ cudaError_t launch_rows_tma_impl(const QuantParams &p, cudaStream_t stream, bool
     }
     const int64_t n_tiles = (p.rows_p >> 7) * (p.cols_p >> 6);
     int64_t grid = static_cast<int64_t>(ctas_per_sm[slot]) * sm_count[slot];
+    const bool grouped = p.group_start != nullptr;
+    if (grouped) {
+        // how the rows are spread over the groups is known on the device only: every group gets twice its even
+        // share of the resident CTAs (at least 8), and a CTA whose group has fewer tiles than that leaves at once
+        grid = 2 * grid / p.num_groups;
+        if (grid < 8) grid = 8;
+    }
     if (grid > n_tiles) grid = n_tiles;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), grouped ? static_cast<unsigned>(p.num_groups) : 1u);
     cfg.blockDim = dim3(FEED_THREADS);
     cfg.dynamicSmemBytes = FEED_SMEM_BYTES;
     cfg.stream = stream;
@@ -1631,7 +1697,7 @@ cudaError_t launch_rows_tma_impl(const QuantParams &p, cudaStream_t stream, bool
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = grouped ? 0 : 1;      // (a grouped launch reads row ranges written by earlier work: a full dependency)
     e = cudaLaunchKernelEx(&cfg, kernel, map, p);
     if (e == cudaSuccess) *launched = true;
     return e;
@@ -1939,6 +2005,88 @@ extern "C" int fos_amax(const void *x, int x_dtype, int64_t rows, int64_t cols, 
     FOS_CUDA_TRY(x_dtype == FOS_BF16 ? launch_amax<__nv_bfloat16>(x, rows, cols, ld, vec16, amax_out, stream)
                                      : launch_amax<__half>(x, rows, cols, ld, vec16, amax_out, stream));
     return FOS_OK;
+}
+
+template <typename T, int KIND>
+cudaError_t launch_rows_grouped(const fos::QuantParams &p, cudaStream_t stream, bool *launched) {
+    using namespace fos;
+    if constexpr (KIND == KIND_ADAPTIVE) {
+        if (p.rule == FOS_RULE_MSE && p.variant != 2) return launch_rows_tma_impl<T, KIND, false, false, false, false, true>(p, stream, launched);
+    }
+    return launch_rows_tma_impl<T, KIND, false, false, false, false>(p, stream, launched);
+}
+
+extern "C" int fos_quantize_grouped(const void *x, int x_dtype, int64_t rows_capacity, int64_t cols, int64_t ld, int format,
+                                    int scale_rule, const int32_t *group_start, const int32_t *group_rows, int num_groups,
+                                    const float *amax_in, uint8_t *codes, uint8_t *sf, float *amax_out, int flags,
+                                    void *stream_) {
+    using namespace fos;
+    if (!x || !codes || !sf || !amax_out || !group_start || !group_rows) return FOS_ERR_INVALID_ARGUMENT;
+    if (num_groups <= 0 || num_groups > 65535) return FOS_ERR_INVALID_ARGUMENT;
+    if (rows_capacity <= 0 || rows_capacity % 128 || cols <= 0 || ld < cols) return FOS_ERR_INVALID_ARGUMENT;
+    if (x_dtype != FOS_BF16 && x_dtype != FOS_FP16) return FOS_ERR_INVALID_ARGUMENT;
+    if (scale_rule < FOS_RULE_STATIC_6 || scale_rule > FOS_RULE_ABS_MAX) return FOS_ERR_INVALID_ARGUMENT;
+    if (format != FOS_NVFP4 && format != FOS_IF4) return format == FOS_MXFP4 ? FOS_ERR_UNSUPPORTED : FOS_ERR_INVALID_ARGUMENT;
+    const bool is_static = scale_rule == FOS_RULE_STATIC_6 || scale_rule == FOS_RULE_STATIC_4;
+    if (format == FOS_IF4 && is_static) return FOS_ERR_UNSUPPORTED;
+    if (flags & (FOS_QUANTIZE_RHT | FOS_QUANTIZE_NO_TMA | FOS_QUANTIZE_UNBIASED)) return FOS_ERR_UNSUPPORTED;
+    // the TMA-fed kernels only: whole 64-value scale tiles per row, 16-byte aligned rows
+    if (cols % 64 != 0 || reinterpret_cast<uintptr_t>(x) % 16 != 0 || (ld * 2) % 16 != 0) return FOS_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(codes) % 8 != 0) return FOS_ERR_MISALIGNED;
+    if (rows_capacity >= (int64_t(1) << 31)) return FOS_ERR_TOO_LARGE;
+    int st = check_device();
+    if (st != FOS_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+    QuantParams p{};
+    p.x = x;
+    p.rows = rows_capacity; p.cols = cols; p.ld = ld;
+    p.out_rows = rows_capacity; p.out_cols = cols;
+    p.rows_p = rows_capacity; p.cols_p = cols;
+    p.codes = codes; p.sf = sf;
+    p.rule = scale_rule;
+    p.sf_tiled = 1;
+    p.exact_only = (flags & FOS_QUANTIZE_EXACT_ONLY) != 0;
+    p.variant = (flags & FOS_QUANTIZE_GENERAL_KERNEL) ? 2 : 0;
+    p.vec_bytes = (reinterpret_cast<uintptr_t>(x) % 32 == 0 && (ld * 2) % 32 == 0) ? 32 : 16;
+    p.x_is_ready = 1;
+    p.group_start = group_start;
+    p.num_groups = num_groups;
+    if (amax_in) {
+        if (amax_in != amax_out)
+            FOS_CUDA_TRY(cudaMemcpyAsync(amax_out, amax_in, sizeof(float) * num_groups, cudaMemcpyDeviceToDevice, stream));
+    } else {
+        FOS_CUDA_TRY(cudaMemsetAsync(amax_out, 0, sizeof(float) * num_groups, stream));
+        int dev = 0, sms = 0;
+        FOS_CUDA_TRY(cudaGetDevice(&dev));
+        FOS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        int per_group = 8 * sms / num_groups;
+        per_group = per_group < 4 ? 4 : per_group;
+        const dim3 grid(static_cast<unsigned>(per_group), static_cast<unsigned>(num_groups));
+        const int vec = cols % 16 == 0 ? p.vec_bytes : (cols % 8 == 0 ? 16 : 0);
+        if (x_dtype == FOS_BF16)
+            amax_grouped_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x), rows_capacity, cols, ld,
+                                                                        vec, group_start, group_rows, amax_out);
+        else
+            amax_grouped_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half *>(x), rows_capacity, cols, ld, vec,
+                                                                 group_start, group_rows, amax_out);
+        FOS_CUDA_TRY(cudaGetLastError());
+    }
+    p.amax = amax_out;
+    p.amax_store = nullptr;
+    bool launched = false;
+    const int kind = format == FOS_IF4 ? KIND_IF4 : (is_static ? KIND_STATIC : KIND_ADAPTIVE);
+    cudaError_t e;
+    if (x_dtype == FOS_BF16)
+        e = kind == KIND_IF4 ? launch_rows_grouped<__nv_bfloat16, KIND_IF4>(p, stream, &launched)
+            : kind == KIND_STATIC ? launch_rows_grouped<__nv_bfloat16, KIND_STATIC>(p, stream, &launched)
+                                  : launch_rows_grouped<__nv_bfloat16, KIND_ADAPTIVE>(p, stream, &launched);
+    else
+        e = kind == KIND_IF4 ? launch_rows_grouped<__half, KIND_IF4>(p, stream, &launched)
+            : kind == KIND_STATIC ? launch_rows_grouped<__half, KIND_STATIC>(p, stream, &launched)
+                                  : launch_rows_grouped<__half, KIND_ADAPTIVE>(p, stream, &launched);
+    FOS_CUDA_TRY(e);
+    return launched ? FOS_OK : FOS_ERR_UNSUPPORTED;
 }
 
 extern "C" int fos_quantize(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int format,

@@ -1,0 +1,112 @@
+"""FP4 experts of a mixture-of-experts layer on the grouped kernels.
+
+The arithmetic of the reference's GPT-OSS experts module (src/fouroversix/model/modules/gpt_oss.py:270-335):
+per expert, quantize the routed tokens as one tensor, `quantized_matmul` with the expert's gate-up weight, bias,
+clamped SwiGLU, quantize again, `quantized_matmul` with the down weight, bias, weight by the routing score and
+add into the token's output row. The reference walks the experts in a host loop and reads the routed indices
+back from the device for each; here the routed rows are sorted by expert on the device, laid out in one padded
+buffer, and each of the two projections is one grouped quantize launch and one grouped GEMM launch for all
+experts. Nothing is read back, so the layer can be captured in a CUDA graph.
+
+Buffers carry the reference's names (`quantized_{gate_up,down}_proj_{values,scale_factors,amax,metadata}`,
+src/fouroversix/model/modules/gpt_oss.py:108-196) so that a packed checkpoint loads into either.
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from fouroversix_b200.matmul.grouped import (GroupLayout, StackedQuantizedTensor, grouped_quantize,
+                                             grouped_quantized_matmul)
+from fouroversix_b200.quantize import quantize
+from fouroversix_b200.utils import DataType
+
+from .config import ModuleQuantizationConfig
+
+
+class FourOverSixExperts(nn.Module):
+    """`gate_up_proj` [experts, 2 * intermediate, hidden] and `down_proj` [experts, hidden, intermediate] in the
+    (out_features, in_features) orientation the reference stores them in after quantization; biases
+    [experts, 2 * intermediate] and [experts, hidden]. Gate and up columns are interleaved (even / odd), as in
+    the reference."""
+
+    def __init__(self, gate_up_proj: torch.Tensor, gate_up_proj_bias: torch.Tensor, down_proj: torch.Tensor,
+                 down_proj_bias: torch.Tensor, config: ModuleQuantizationConfig | None = None, *,
+                 alpha: float = 1.702, limit: float = 7.0) -> None:
+        super().__init__()
+        self.config = config or ModuleQuantizationConfig()
+        if DataType(self.config.dtype) != DataType.nvfp4:
+            raise NotImplementedError("the grouped kernels take nvfp4 operands")
+        self.num_experts, two_i, self.hidden_size = gate_up_proj.shape
+        self.intermediate_size = two_i // 2
+        if down_proj.shape != (self.num_experts, self.hidden_size, self.intermediate_size):
+            raise ValueError("down_proj must be [experts, hidden, intermediate]")
+        self.alpha, self.limit = alpha, limit
+        self.gate_up_proj_bias = nn.Parameter(gate_up_proj_bias.detach().clone(), requires_grad=False)
+        self.down_proj_bias = nn.Parameter(down_proj_bias.detach().clone(), requires_grad=False)
+        weight_config = self.config.get_weight_config()
+        for prefix, weight in (("gate_up", gate_up_proj), ("down", down_proj)):
+            tensors = [quantize(weight[e].contiguous(), weight_config) for e in range(self.num_experts)]
+            stacked = StackedQuantizedTensor.stack(tensors)
+            self.register_buffer(f"quantized_{prefix}_proj_values", stacked.values)
+            self.register_buffer(f"quantized_{prefix}_proj_scale_factors", stacked.scale_factors)
+            self.register_buffer(f"quantized_{prefix}_proj_amax", stacked.amax.reshape(-1, 1))
+            meta = torch.tensor([[*stacked.original_shape, *stacked.padded_shape, 1, 1]] * self.num_experts, dtype=torch.int32)
+            self.register_buffer(f"quantized_{prefix}_proj_metadata", meta.to(weight.device))
+
+    def quantized_weights(self) -> tuple[StackedQuantizedTensor, StackedQuantizedTensor]:
+        """(down, gate_up), the order of the reference's method of the same name."""
+        rule = self.config.get_weight_config().scale_rule
+        out = []
+        for prefix in ("down", "gate_up"):
+            shape = (self.hidden_size, self.intermediate_size) if prefix == "down" else (2 * self.intermediate_size, self.hidden_size)
+            values = getattr(self, f"quantized_{prefix}_proj_values")
+            padded = (values.shape[1], values.shape[2] * 2)
+            out.append(StackedQuantizedTensor(values, getattr(self, f"quantized_{prefix}_proj_scale_factors"),
+                                              getattr(self, f"quantized_{prefix}_proj_amax").reshape(-1),
+                                              DataType.nvfp4, rule, shape, padded))
+        return out[0], out[1]
+
+    def route(self, routing_indices: torch.Tensor) -> tuple[GroupLayout, torch.Tensor, torch.Tensor, torch.Tensor]:
+        """Sorts the (token, slot) pairs by expert on the device. Returns the row layout, for every sorted pair
+        its row in the padded buffer, its token and its position in the flattened routing tensors."""
+        tokens, top_k = routing_indices.shape
+        flat = routing_indices.reshape(-1)
+        pairs = flat.numel()
+        counts = torch.zeros(self.num_experts, dtype=torch.int64, device=flat.device)
+        counts.scatter_add_(0, flat, torch.ones_like(flat, dtype=torch.int64))
+        layout = GroupLayout.from_counts(counts, pairs)
+        order = torch.argsort(flat, stable=True)
+        expert = flat[order]
+        first = torch.cumsum(counts, 0) - counts                          # first sorted position of each expert
+        rows = layout.group_start.to(torch.int64)[expert] + (torch.arange(pairs, device=flat.device) - first[expert])
+        return layout, rows, order // top_k, order
+
+    def forward(self, hidden_states: torch.Tensor, routing_indices: torch.Tensor, routing_weights: torch.Tensor) -> torch.Tensor:
+        """hidden_states [batch, seq, hidden] (or [tokens, hidden]); routing_indices / routing_weights
+        [tokens, top_k]: the experts each token goes to and the weight of each."""
+        shape = hidden_states.shape
+        x = hidden_states.reshape(-1, self.hidden_size)
+        down, gate_up = self.quantized_weights()
+        act_config = self.config.get_activation_config()
+        out_dtype = self.config.output_dtype
+        layout, rows, token, order = self.route(routing_indices)
+        expert = routing_indices.reshape(-1)[order]
+
+        padded = torch.zeros(layout.capacity, self.hidden_size, dtype=x.dtype, device=x.device)
+        padded[rows] = x[token]
+        gu = grouped_quantized_matmul(grouped_quantize(padded, layout, act_config), gate_up, out_dtype=out_dtype)
+        gu = gu[rows] + self.gate_up_proj_bias[expert]
+        gate, up = gu[..., ::2], gu[..., 1::2]
+        gate = gate.clamp(min=None, max=self.limit)
+        up = up.clamp(min=-self.limit, max=self.limit)
+        gated = (up + 1) * (gate * torch.sigmoid(gate * self.alpha))
+
+        padded2 = torch.zeros(layout.capacity, self.intermediate_size, dtype=x.dtype, device=x.device)
+        padded2[rows] = gated.to(x.dtype)
+        y = grouped_quantized_matmul(grouped_quantize(padded2, layout, act_config), down, out_dtype=out_dtype)
+        y = (y[rows] + self.down_proj_bias[expert]) * routing_weights.reshape(-1)[order, None]
+        result = torch.zeros_like(x)
+        result.index_add_(0, token, y.to(x.dtype))
+        return result.reshape(shape)

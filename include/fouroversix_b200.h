@@ -165,6 +165,9 @@ int fos_gemm_alpha(const float *amax_a, int format_a, int rule_a, const float *a
  * (src/fouroversix/matmul/cutlass/backend.py:95-96). */
 int fos_gemm_alpha_ex(const float *amax_a, int format_a, int rule_a, int unbiased_a, const float *amax_b,
                       int format_b, int rule_b, int unbiased_b, float *alpha, void *stream);
+/* The same for `count` pairs: alpha[i] from amax_a[i] and amax_b[i] (the groups of fos_gemm_nvfp4_grouped). */
+int fos_gemm_alpha_grouped(const float *amax_a, int format_a, int rule_a, int unbiased_a, const float *amax_b,
+                           int format_b, int rule_b, int unbiased_b, float *alpha, int count, void *stream);
 
 /*
  * D[m, n] = alpha[0] * sum_k A[m, k] * B[n, k]   ("TN": both operands K-major)
@@ -223,6 +226,39 @@ int fos_gemm_nvfp4_fused_a(const void *x, int x_dtype, int64_t x_ld, const float
                            const uint8_t *b_codes, const uint8_t *b_sf, const float *alpha, void *d,
                            int out_dtype, int64_t m, int64_t n_p, int64_t k, int64_t n, int64_t ldd,
                            int32_t *status, void *stream);
+
+/*
+ * Grouped problems in one launch: num_groups GEMMs that share n, k and the output type, each with its own A rows,
+ * its own B and its own alpha - what a mixture-of-experts layer does after routing, where the reference loops over
+ * the experts on the host (one quantize + one GEMM per expert, the row counts read back from the device).
+ *
+ * Layout. The rows of all groups lie one after the other in one padded buffer of rows_capacity rows (a multiple of
+ * 128): group g occupies rows group_start[g] .. group_start[g + 1] (num_groups + 1 int32 values in DEVICE memory,
+ * multiples of 128, non-decreasing), of which the first group_rows[g] (device int32) are real and the rest padding.
+ * The host never needs to know how the rows are spread: it sizes the buffers for the worst case
+ * (sum of rows + 127 * num_groups, rounded up to 128). a_codes / a_sf / d are [rows_capacity, ...] as for
+ * fos_gemm_nvfp4 (scales in 128 x 4 tiles; a group starts on a tile boundary); b_codes is
+ * [num_groups][n_p][k_p / 2] and b_sf the groups' tiled scales one after the other; alpha has num_groups entries.
+ * Only rows group_start[g] .. + group_rows[g] of d are written. An empty group costs nothing. num_groups <= 256.
+ *
+ * fos_quantize_grouped quantizes such a buffer of bf16 / fp16 rows: every group as a tensor of its own with its
+ * own amax (amax_out[g]; computed here unless amax_in gives num_groups values), 1-D blocks, untransposed, tiled
+ * scales, NVFP4 or IF4, any scale rule the format has - the bits fos_quantize gives for the group's rows alone.
+ * Padding rows inside a group's range must be zero in x (they quantize to zero codes). cols must be a multiple of
+ * 64 and x 16-byte aligned (base and row stride): FOS_ERR_UNSUPPORTED otherwise.
+ *
+ * Replaces: the per-expert loop of quantized_matmul calls in
+ * src/fouroversix/model/modules/gpt_oss.py:297-335.
+ */
+int fos_quantize_grouped(const void *x, int x_dtype, int64_t rows_capacity, int64_t cols, int64_t ld, int format,
+                         int scale_rule, const int32_t *group_start, const int32_t *group_rows, int num_groups,
+                         const float *amax_in, uint8_t *codes, uint8_t *sf, float *amax_out, int flags,
+                         void *stream);
+int fos_gemm_nvfp4_grouped(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                           const uint8_t *b_sf, const float *alpha, void *d, int out_dtype,
+                           const int32_t *group_start, const int32_t *group_rows, int num_groups,
+                           int64_t rows_capacity, int64_t n_p, int64_t k_p, int64_t n, int64_t ldd,
+                           const fos_gemm_opts *opts, int32_t *status, void *stream);
 
 /*
  * The same GEMM for two MXFP4 operands (E8M0 scale per 32 values, scales in the 128 x 4 tile

@@ -40,6 +40,23 @@ def test_argument_validation_needs_no_gpu():
     import ctypes
     assert lib.fos_gemm_nvfp4_ex(0, 0, 0, 0, 0, 0, 0, 128, 128, 64, 128, 128, 128, ctypes.byref(bad), 0, 0) == -1
     assert not hasattr(lib, "fos_set_option")      # the library has no process-wide settings
+    # grouped entries: NULL buffers, too many groups
+    assert lib.fos_quantize_grouped(0, 0, 128, 64, 64, 0, 3, 0, 0, 4, 0, 0, 0, 0, 0, 0) == -1
+    assert lib.fos_gemm_nvfp4_grouped(0, 0, 0, 0, 0, 0, 0, 0, 0, 4, 128, 128, 64, 128, 128, 0, 0, 0) == -1
+    assert lib.fos_gemm_alpha_grouped(0, 0, 3, 0, 0, 0, 3, 0, 0, 0, 0) == -1
+
+
+def test_group_layout_is_computed_without_reading_the_counts_back():
+    import torch
+
+    from fouroversix_b200.matmul import GroupLayout
+
+    layout = GroupLayout.from_counts(torch.tensor([5, 0, 300, 128]), 433)
+    assert layout.group_start.tolist() == [0, 128, 128, 512, 640] and layout.group_start.dtype == torch.int32
+    assert layout.group_rows.tolist() == [5, 0, 300, 128]
+    assert layout.capacity == 1024 and layout.capacity >= 640        # worst case for 433 rows in 4 groups
+    with pytest.raises(ValueError):
+        GroupLayout.from_counts(torch.zeros(300, dtype=torch.int64), 0)
 
 
 def test_enums_and_config_coercion():

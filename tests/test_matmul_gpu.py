@@ -154,6 +154,31 @@ def test_output_is_cropped_and_nothing_else_is_written():
     _check(view, _dense_reference(qx, qy), "cropped")
 
 
+def test_calls_with_different_options_on_two_streams():
+    """Options travel with each call (CTA limit, kernel variant): two GEMMs in flight on two streams
+    with different options give the bits each gives alone."""
+    g = torch.Generator().manual_seed(11)
+    qx = fos.quantize(torch.randn(2048, 1024, generator=g).bfloat16().to(DEV))
+    qa = fos.quantize(torch.randn(1536, 1024, generator=g).bfloat16().to(DEV))
+    qb = fos.quantize(torch.randn(1024, 1024, generator=g).bfloat16().to(DEV))
+    kw_a, kw_b = dict(max_ctas=40), dict(max_ctas=100, variant=128)
+    alone_a = B200MatmulBackend.quantized_matmul(qx, qa, out_dtype=fos.DataType.bfloat16, **kw_a).clone()
+    alone_b = B200MatmulBackend.quantized_matmul(qx, qb, out_dtype=fos.DataType.bfloat16, **kw_b).clone()
+    assert torch.equal(alone_a, B200MatmulBackend.quantized_matmul(qx, qa, out_dtype=fos.DataType.bfloat16))
+    cur = torch.cuda.current_stream()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    for _ in range(5):
+        s1.wait_stream(cur)
+        s2.wait_stream(cur)
+        with torch.cuda.stream(s1):
+            ya = B200MatmulBackend.quantized_matmul(qx, qa, out_dtype=fos.DataType.bfloat16, **kw_a)
+        with torch.cuda.stream(s2):
+            yb = B200MatmulBackend.quantized_matmul(qx, qb, out_dtype=fos.DataType.bfloat16, **kw_b)
+        cur.wait_stream(s1)
+        cur.wait_stream(s2)
+        assert torch.equal(ya, alone_a) and torch.equal(yb, alone_b)
+
+
 @pytest.mark.parametrize("name,m,n,k,rule", [
     ("c2-act-x-weight-static6", 8192, 4096, 4096, "static_6"),
     ("c2-act-x-weight-4over6", 8192, 4096, 4096, "mse"),

@@ -130,6 +130,26 @@ def _worker(rank: int, world: int, port: int, results):
         partial = fos.quantized_matmul(slice_cols(qx, klo, khi), slice_cols(qw, klo, khi), out_dtype=fos.DataType.float32)
         dist.all_reduce(partial)
         out["k_err"] = ((partial - full_mm).abs().max() / full_mm.abs().max()).item()
+        # two row-parallel layers in flight at once on two streams (each GEMM call carries its own CTA limit;
+        # the library keeps no setting between calls): the same bits as one after the other
+        w_other = shard_linear_weight(w_down.flip(0), "row", rank, world).contiguous()
+        la = TensorParallelLinear(w_down_shard, cfg, "row", chunks=4, fused=False)
+        lb = TensorParallelLinear(w_other, cfg, "row", chunks=2, fused=False, comm_sms=32)
+        serial_a, serial_b = la(h).clone(), lb(h).clone()
+        cur = torch.cuda.current_stream(dev)
+        s1, s2 = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        same = True
+        for _ in range(3):
+            s1.wait_stream(cur)
+            s2.wait_stream(cur)
+            with torch.cuda.stream(s1):
+                ya = la(h)
+            with torch.cuda.stream(s2):
+                yb = lb(h)
+            cur.wait_stream(s1)
+            cur.wait_stream(s2)
+            same = same and torch.equal(ya, serial_a) and torch.equal(yb, serial_b)
+        out["two_streams_equal"] = same
         from fouroversix_b200 import _native
         out["wait_failure_site"] = _native.wait_failure_site()
         results[rank] = out
@@ -173,6 +193,7 @@ def test_column_then_row_parallel(world):
         assert out["next_equal"]
         assert out["rows_equal"]
         assert out["k_err"] < 1e-5, out["k_err"]
+        assert out["two_streams_equal"], "two layers on two streams must equal their serial results"
         assert out["wait_failure_site"] == 0
     if peer_seen == 0:
         pytest.skip("NCCL paths and the slab hand-off checked; the peer-memory exchange was unavailable (no symmetric memory)")
