@@ -644,6 +644,7 @@ def run_case(args) -> None:
                            [--transpose] [--amax-given] [--kernel auto|general|no_tma]
         --case dequantize  --rows R --cols C [--dtype ...]
         --case gemm        --m M --n N --k K [--dtype nvfp4|mxfp4|if4] [--variant 0|128|256|2]
+        --case experts     --rows TOKENS --experts E --top-k T --k HIDDEN --n INTERMEDIATE (experts_case)
 
     `--graph` times replays of a CUDA graph of the call instead of launches from Python. Inputs are
     N(0,1) (the bench tensor with its outlier channels when the shape is 8192 x 4096)."""
@@ -689,6 +690,9 @@ def run_case(args) -> None:
               f"({'graph replays' if args.graph else 'eager launches'}), "
               f"{per_elem * args.rows * args.cols / (ms * 1e-3) / 1e9:.0f} GB/s algorithmic")
         return
+    if args.case == "experts":
+        experts_case(args, timed)
+        return
     rule = "static_6" if args.dtype == "mxfp4" else "mse"
     g = torch.Generator(device=dev).manual_seed(0)
     a = torch.randn(args.m, args.k, generator=g, device=dev).bfloat16()
@@ -702,18 +706,69 @@ def run_case(args) -> None:
           f"{2.0 * args.m * args.n * args.k / (ms * 1e-3) / 1e12:.0f} TFLOP/s")
 
 
+def experts_case(args, timed) -> dict:
+    """The experts of one mixture-of-experts layer (defaults: the shapes of GPT-OSS-20B, 32 experts, hidden =
+    intermediate = 2880, 4 experts per token) on --rows tokens with uniformly random routing: the grouped
+    launches (one quantize + one GEMM per projection, nothing read back) beside the reference's form, a host
+    loop over the experts with one quantize + one GEMM each
+    (src/fouroversix/model/modules/gpt_oss.py:297-335), both on this repo's kernels."""
+    import fouroversix_b200 as fos
+    from fouroversix_b200.model import FourOverSixExperts
+
+    dev = "cuda"
+    e, h, i, top_k, tokens = args.experts, args.k, args.n, args.top_k, args.rows
+    g = torch.Generator(device=dev).manual_seed(0)
+    layer = FourOverSixExperts(
+        (torch.randn(e, 2 * i, h, generator=g, device=dev) * 0.02).bfloat16(),
+        (torch.randn(e, 2 * i, generator=g, device=dev) * 0.02).bfloat16(),
+        (torch.randn(e, h, i, generator=g, device=dev) * 0.02).bfloat16(),
+        (torch.randn(e, h, generator=g, device=dev) * 0.02).bfloat16())
+    x = torch.randn(tokens, h, generator=g, device=dev).bfloat16()
+    weights, indices = torch.topk(torch.softmax(torch.randn(tokens, e, generator=g, device=dev), -1), top_k, dim=-1)
+    weights = weights.bfloat16()
+    down, gate_up = layer.quantized_weights()
+    cfg = layer.config.get_activation_config()
+
+    def loop():
+        result = torch.zeros_like(x)
+        mask = torch.nn.functional.one_hot(indices, num_classes=e).permute(2, 1, 0)
+        for ex in range(e):
+            top_k_pos, token_idx = torch.where(mask[ex])
+            if token_idx.numel() == 0:
+                continue
+            gu = fos.quantized_matmul(x[token_idx], gate_up[ex], input_config=cfg) + layer.gate_up_proj_bias[ex]
+            gate, up = gu[..., ::2].clamp(max=layer.limit), gu[..., 1::2].clamp(min=-layer.limit, max=layer.limit)
+            out = fos.quantized_matmul((up + 1) * (gate * torch.sigmoid(gate * layer.alpha)), down[ex], input_config=cfg)
+            result.index_add_(0, token_idx, ((out + layer.down_proj_bias[ex]) * weights[token_idx, top_k_pos, None]).to(x.dtype))
+        return result
+
+    ms_grouped = timed(lambda: layer(x, indices, weights))
+    graph = args.graph
+    args.graph = False                                    # the loop reads the routing back: it cannot be captured
+    ms_loop = timed(loop)
+    args.graph = graph
+    flops = 2.0 * tokens * top_k * (2 * i * h + h * i)
+    out = {"tokens": tokens, "experts": e, "top_k": top_k, "hidden": h, "intermediate": i,
+           "grouped_ms": round(ms_grouped, 4), "per_expert_loop_ms": round(ms_loop, 4),
+           "grouped_tflops": round(flops / (ms_grouped * 1e-3) / 1e12, 1)}
+    print(f"experts {json.dumps(out)}")
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--case", default=None, choices=["quantize", "dequantize", "gemm"], help="one kernel on its own (run_case)")
+    ap.add_argument("--case", default=None, choices=["quantize", "dequantize", "gemm", "experts"], help="one kernel on its own (run_case)")
+    ap.add_argument("--experts", type=int, default=32)
+    ap.add_argument("--top-k", type=int, default=4)
     ap.add_argument("--rows", type=int, default=A_SHAPE[0])
     ap.add_argument("--cols", type=int, default=A_SHAPE[1])
-    ap.add_argument("--m", type=int, default=8192)
-    ap.add_argument("--n", type=int, default=8192)
-    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--m", type=int, default=None)
+    ap.add_argument("--n", type=int, default=None)
+    ap.add_argument("--k", type=int, default=None)
     ap.add_argument("--rule", default=None)
     ap.add_argument("--dtype", default="nvfp4")
     ap.add_argument("--two-d", action="store_true")
@@ -724,6 +779,8 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=6)
     ap.add_argument("--graph", action="store_true")
     args = ap.parse_args()
+    side = 2880 if args.case == "experts" else 8192          # default m, n, k of the case
+    args.m, args.n, args.k = (v if v is not None else side for v in (args.m, args.n, args.k))
     if args.case is not None:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py: no CUDA device; the GPU path has no CPU fallback")

@@ -59,6 +59,7 @@ SIGNATURES = {
                                    _c_ptr, _c_int, _c_i64, _c_int, _c_int, _c_ptr]),
     "fos_gemm_alpha": (_c_int, [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr]),
     "fos_gemm_alpha_ex": (_c_int, [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]),
+    "fos_wait_failure_roles": (_c_int, [_c_ptr]),
     "fos_gemm_alpha_grouped": (_c_int, [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr]),
     "fos_gemm_nvfp4": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_i64, _c_i64,
                                 _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
@@ -135,6 +136,13 @@ def wait_failure_site() -> int:
     site = ctypes.c_int32(0)
     check(lib().fos_wait_failure_site(ctypes.byref(site)), "fos_wait_failure_site")
     return int(site.value)
+
+
+def wait_failure_roles() -> tuple[int, int, int]:
+    """Bit masks of the wait sites that were blocked when a CTA gave up: (quantize kernels, FP4 GEMMs, IF4 GEMM)."""
+    roles = (ctypes.c_uint32 * 3)()
+    check(lib().fos_wait_failure_roles(roles), "fos_wait_failure_roles")
+    return int(roles[0]), int(roles[1]), int(roles[2])
 
 
 def raise_on_wait_failure() -> None:

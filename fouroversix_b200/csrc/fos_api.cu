@@ -36,6 +36,14 @@ extern "C" int fos_wait_failure_site(int32_t *site) {
     return FOS_OK;
 }
 
+extern "C" int fos_wait_failure_roles(uint32_t roles[3]) {
+    if (!roles) return FOS_ERR_INVALID_ARGUMENT;
+    FOS_CUDA_TRY(fos::quantize_wait_roles(&roles[0]));
+    FOS_CUDA_TRY(fos::gemm_wait_roles(&roles[1]));
+    FOS_CUDA_TRY(fos::gemm_if4_wait_roles(&roles[2]));
+    return FOS_OK;
+}
+
 extern "C" int fos_last_cuda_error(void) { return fos::g_last_cuda_error; }
 
 extern "C" const char *fos_status_string(int status) {

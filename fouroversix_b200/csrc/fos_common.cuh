@@ -22,6 +22,9 @@ int check_device();
 cudaError_t quantize_wait_failures(int32_t *host_value);
 cudaError_t gemm_wait_failures(int32_t *host_value);
 cudaError_t gemm_if4_wait_failures(int32_t *host_value);
+cudaError_t quantize_wait_roles(uint32_t *host_value);
+cudaError_t gemm_wait_roles(uint32_t *host_value);
+cudaError_t gemm_if4_wait_roles(uint32_t *host_value);
 
 // MXFP4 branches of fos_quantize / fos_dequantize (fos_mxfp4.cu); arguments validated by the callers.
 int quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int scale_rule, int block_2d,

@@ -283,6 +283,7 @@ int launch_expand(const uint8_t *codes, const uint8_t *sf, int format, int sf_la
 }  // namespace fos
 
 cudaError_t fos::gemm_if4_wait_failures(int32_t *host_value) { return fos::read_wait_failures(host_value); }
+cudaError_t fos::gemm_if4_wait_roles(uint32_t *host_value) { return fos::read_wait_roles(host_value); }
 
 extern "C" int64_t fos_gemm_if4_workspace_bytes(int64_t m_p, int64_t n_p, int64_t k_p) {
     if (m_p <= 0 || n_p <= 0 || k_p <= 0) return 0;

@@ -84,7 +84,7 @@ template <int BLOCK_N> struct Cfg {
     static_assert(ACC_STAGES * BLOCK_N <= SF_COL0, "accumulators overlap the scale columns");
     static_assert(SF_COL0 + SF_SLOTS * SF_STAGE_COLS <= TMEM_COLS, "scale ring does not fit tensor memory");
     static_assert(SMEM_BYTES <= 232448, "more shared memory than a CTA can have");
-    static_assert((2 * STAGES + 2 * SF_SLOTS + 2 * ACC_STAGES) * 8 + 8 <= BARRIER_BYTES, "barrier area too small");
+    static_assert((2 * STAGES + (SF_CP_WARPS + 1) * SF_SLOTS + 2 * ACC_STAGES) * 8 + 8 <= BARRIER_BYTES, "barrier area too small");
 };
 
 struct GemmParams {
@@ -213,11 +213,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + C::STAGES * C::STAGE_BYTES + C::SF_SLOTS * C::SF_SLOT_BYTES);
     const uint32_t full_bar = smem_u32(bars);                       // [STAGES] operand tiles landed
     const uint32_t empty_bar = full_bar + 8 * C::STAGES;            // [STAGES] the stage's MMAs are done
-    const uint32_t sf_full_bar = empty_bar + 8 * C::STAGES;         // [SF_SLOTS] scale tiles landed
-    const uint32_t sf_ready_bar = sf_full_bar + 8 * C::SF_SLOTS;    // [SF_SLOTS] scales are in tensor memory
+    const uint32_t sf_full_bar = empty_bar + 8 * C::STAGES;         // [SF_CP_WARPS][SF_SLOTS] scale tiles landed
+    const uint32_t sf_ready_bar = sf_full_bar + 8 * SF_CP_WARPS * C::SF_SLOTS;   // [SF_SLOTS] scales are in tensor memory
     const uint32_t acc_full_bar = sf_ready_bar + 8 * C::SF_SLOTS;   // [ACC_STAGES]
     const uint32_t acc_empty_bar = acc_full_bar + 8 * C::ACC_STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::STAGES + 2 * C::SF_SLOTS + 2 * C::ACC_STAGES);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::STAGES + (SF_CP_WARPS + 1) * C::SF_SLOTS + 2 * C::ACC_STAGES);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -226,15 +226,22 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     __shared__ int32_t grp_start[GROUPED ? MAX_GROUPS + 1 : 1], grp_end[GROUPED ? MAX_GROUPS : 1];
     if constexpr (GROUPED) {
         const int32_t cap = static_cast<int32_t>(p.m_p);
-        for (int g = threadIdx.x; g <= p.num_groups; g += NUM_THREADS) {
-            int32_t s0 = __ldg(p.group_start + g);
-            s0 = (s0 < 0 ? 0 : (s0 > cap ? cap : s0)) & ~127;                 // never beyond the buffers
-            grp_start[g] = s0;
-            if (g < p.num_groups) {
-                const int32_t r = __ldg(p.group_rows + g), e = s0 + (r < 0 ? 0 : r);
-                grp_end[g] = e > cap ? cap : e;
+        // (the same number of rounds in every thread, and the warps converged again before the warp-wide
+        // instructions below - tcgen05.alloc, elect.sync: a loop that only some lanes of a warp enter leaves
+        // the warp split, and those instructions are undefined for a split warp)
+        for (int g0 = 0; g0 <= p.num_groups; g0 += NUM_THREADS) {
+            const int g = g0 + static_cast<int>(threadIdx.x);
+            if (g <= p.num_groups) {
+                int32_t s0 = __ldg(p.group_start + g);
+                s0 = (s0 < 0 ? 0 : (s0 > cap ? cap : s0)) & ~127;             // never beyond the buffers
+                grp_start[g] = s0;
+                if (g < p.num_groups) {
+                    const int32_t r = __ldg(p.group_rows + g), e = s0 + (r < 0 ? 0 : r);
+                    grp_end[g] = e > cap ? cap : e;
+                }
             }
         }
+        __syncwarp();
     }
 
     if (threadIdx.x == 0) {
@@ -244,7 +251,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             mbar_init(empty_bar + 8 * s, 1);
         }
         for (int j = 0; j < C::SF_SLOTS; ++j) {
-            mbar_init(sf_full_bar + 8 * j, FUSED_A ? 9 : 1);
+            for (int w = 0; w < SF_CP_WARPS; ++w) mbar_init(sf_full_bar + 8 * (w * C::SF_SLOTS + j), FUSED_A ? 9 : 1);
             mbar_init(sf_ready_bar + 8 * j, 1);                   // one commit by the warp that copied the slot
         }
         for (int a = 0; a < C::ACC_STAGES; ++a) {
@@ -256,6 +263,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
+        __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -295,7 +303,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // a ring of their own that is one slot longer.
         const bool issue = elect_one();
         int64_t f_t = blockIdx.x, f_kt = 0;          // the stage whose scales are requested next
-        uint32_t slot = 0;
+        uint32_t slot = 0, f_w = 0;                  // its ring slot, and which copying warp will take it
         int a_group = 0, b_group = 0;
         auto enter_tile = [&]() {
             if (f_t >= num_tiles) return;
@@ -310,7 +318,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             // what lies beyond K or N is zero-filled and still counted (MXFP4: a tile spans two K-blocks, so the
             // box of its maps is two tiles per group)
             const int kb0 = static_cast<int>(f_kt * (p.mx ? KB_PER_STAGE / 2 : KB_PER_STAGE));
-            const uint32_t dst = sf_base + slot * C::SF_SLOT_BYTES, bar = sf_full_bar + 8 * slot;
+            const uint32_t dst = sf_base + slot * C::SF_SLOT_BYTES, bar = sf_full_bar + 8 * (f_w * C::SF_SLOTS + slot);
             if (issue) {
                 if (FUSED_A) {
                     mbar_expect_tx(bar, C::SFB_BYTES);
@@ -321,6 +329,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 tma_load_3d(dst + SFA_BYTES, &map_sfb, 0, kb0, b_group, bar);
             }
             if (++slot == C::SF_SLOTS) slot = 0;
+            if (++f_w == SF_CP_WARPS) f_w = 0;
             if (++f_kt == k_tiles) {
                 f_kt = 0;
                 f_t += gridDim.x;
@@ -433,7 +442,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // stage and 8 of its 16 blocks (128 values, 256 contiguous bytes of x).
         __shared__ float2 a_lut[FUSED_A ? 128 : 1];
         StaticQuantConsts qc{};
-        uint32_t a_s = 0, a_ph = 0, a_j = 0;
+        uint32_t a_s = 0, a_ph = 0, a_j = 0, a_w = 0;
         const int e_tid = static_cast<int>(threadIdx.x) - 64, a_row = e_tid >> 1, a_half = e_tid & 1;
         if constexpr (FUSED_A) {
             qc = static_quant_consts(__ldg(p.x_amax), p.x_rule);
@@ -496,10 +505,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     __syncwarp();
                     if (lane == 0) {
                         mbar_arrive(full_bar + 8 * a_s);
-                        mbar_arrive(sf_full_bar + 8 * a_j);
+                        mbar_arrive(sf_full_bar + 8 * (a_w * C::SF_SLOTS + a_j));
                     }
                     if (++a_s == C::STAGES) { a_s = 0; a_ph ^= 1u; }
                     if (++a_j == C::SF_SLOTS) a_j = 0;
+                    if (++a_w == SF_CP_WARPS) a_w = 0;
                 }
                 if (!ok) break;
             }
@@ -582,15 +592,27 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     } else if (warp >= 10 && warp < 10 + SF_CP_WARPS && !dbg_no_load && !dbg_no_sf) {
         // ------------------------------------------------------------------ scale copies by tcgen05.cp
         const bool issue = elect_one();
-        uint32_t j = 0, jph = 0, turn = 0;
+        // The warps take the stages in turn, and every (warp, slot) pair has a landing barrier of its own, which
+        // the producer arms for the warp whose turn the stage will be: each barrier has one waiter, which sees
+        // every one of its phases in order. (With ONE barrier per slot and an odd number of slots, a slot
+        // alternated between the warps: a warp whose own stages had landed could reach its next use of a slot
+        // before the other warp's stage in that slot had landed, take the barrier's not-yet-completed phase for
+        // the one after it - a parity wait cannot tell them apart - and copy stale scales. Loads land out of
+        // order when the kernel is bound by HBM: skinny problems computed with wrong scales and then hung.)
+        const uint32_t me = static_cast<uint32_t>(warp - 10);
+        uint32_t j = 0, turn = 0, seen = 0;          // bit j of `seen`: parity of this warp's next phase of slot j
         bool ok = true;
         for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             for (int64_t kt = 0; kt < k_tiles; ++kt) {
-                if (SF_CP_WARPS > 1 && (turn++ & 1u) != static_cast<uint32_t>(warp - 10)) {
-                    if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
+                const bool mine = turn == me;
+                if (++turn == SF_CP_WARPS) turn = 0;
+                if (!mine) {
+                    if (++j == C::SF_SLOTS) j = 0;
                     continue;
                 }
-                ok = mbar_wait(sf_full_bar + 8 * j, jph, abort_flag, p.status, 6);
+                const uint32_t jph = (seen >> j) & 1u;
+                seen ^= 1u << j;
+                ok = mbar_wait(sf_full_bar + 8 * (me * C::SF_SLOTS + j), jph, abort_flag, p.status, 6);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
@@ -610,7 +632,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
                 if (issue) tc_commit(sf_ready_bar + 8 * j);     // arrives when the copies above are done
                 __syncwarp();
-                if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
+                if (++j == C::SF_SLOTS) j = 0;
             }
         }
     }
@@ -1144,6 +1166,7 @@ static int gemm_fp4_entry(const uint8_t *a_codes, const uint8_t *a_sf, const uin
 }
 
 cudaError_t fos::gemm_wait_failures(int32_t *host_value) { return fos::read_wait_failures(host_value); }
+cudaError_t fos::gemm_wait_roles(uint32_t *host_value) { return fos::read_wait_roles(host_value); }
 
 extern "C" int fos_gemm_nvfp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
                               const uint8_t *b_sf, const float *alpha, void *d, int out_dtype, int64_t m_p,

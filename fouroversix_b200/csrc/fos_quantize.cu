@@ -1992,6 +1992,7 @@ static int quantize_entry(const void *x, int x_dtype, int64_t rows, int64_t cols
 }
 
 cudaError_t fos::quantize_wait_failures(int32_t *host_value) { return fos::read_wait_failures(host_value); }
+cudaError_t fos::quantize_wait_roles(uint32_t *host_value) { return fos::read_wait_roles(host_value); }
 
 extern "C" int fos_amax(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, float *amax_out, void *stream_) {
     using namespace fos;

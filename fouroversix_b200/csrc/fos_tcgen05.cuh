@@ -19,6 +19,9 @@ constexpr int TMEM_COLS = 512;
 // this device, 0 if none did (never expected to change). Sticky: nothing resets it, so a launch whose
 // caller passed no status word of its own still leaves a trace that fos_wait_failure_site reports.
 __device__ int32_t g_wait_failures = 0;
+// Bit `site` is set for every wait that was in progress when its CTA gave up (the wait that timed out and
+// the waits that then saw the CTA's abort flag): which roles of a kernel were blocked, and where.
+__device__ uint32_t g_wait_roles = 0;
 
 // Runs `init` once per device (the first call with that device current), under a lock: for
 // cudaFuncSetAttribute and the like, whose results the launch paths cache per device.
@@ -57,6 +60,9 @@ inline cudaError_t wait_failures_ptr(int32_t **out) {
 
 inline cudaError_t read_wait_failures(int32_t *host_value) {
     return cudaMemcpyFromSymbol(host_value, g_wait_failures, sizeof(int32_t));
+}
+inline cudaError_t read_wait_roles(uint32_t *host_value) {
+    return cudaMemcpyFromSymbol(host_value, g_wait_roles, sizeof(uint32_t));
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -100,10 +106,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 #pragma unroll 1
         for (int i = 0; i < 32; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
+        if (*abort_flag) {
+            atomicOr(&g_wait_roles, 1u << (where & 31));
+            return false;
+        }
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;
             if (status) atomicCAS(status, 0, where);
+            atomicOr(&g_wait_roles, 1u << (where & 31));
             return false;
         }
     }
@@ -146,10 +156,14 @@ __device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, vo
 #pragma unroll 1
         for (int i = 0; i < 256; ++i)
             if (mbar_try_wait_hint(bar, parity, POLL_SUSPEND_NS)) return true;
-        if (*abort_flag) return false;
+        if (*abort_flag) {
+            atomicOr(&g_wait_roles, 1u << (where & 31));
+            return false;
+        }
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;
             if (status) atomicCAS(status, 0, where);
+            atomicOr(&g_wait_roles, 1u << (where & 31));
             return false;
         }
     }

@@ -399,6 +399,12 @@ int fos_pseudo_quantize(const void *x, int x_dtype, int64_t rows, int64_t cols, 
  * gave up on the current device. Synchronises the device. No counterpart in the reference.
  */
 int fos_wait_failure_site(int32_t *site);
+/*
+ * Which waits were in progress when a CTA gave up: roles[0] the quantize kernels, roles[1] the FP4 GEMMs, roles[2]
+ * the IF4 GEMM; bit s is set for wait site s (the numbering of fos_wait_failure_site within each family) if a wait
+ * there timed out or was cut short by its CTA's abort flag. Sticky like the site word; synchronises the device.
+ */
+int fos_wait_failure_roles(uint32_t roles[3]);
 
 #ifdef __cplusplus
 }

@@ -154,6 +154,27 @@ def test_output_is_cropped_and_nothing_else_is_written():
     _check(view, _dense_reference(qx, qy), "cropped")
 
 
+def test_skinny_problem_bound_by_memory():
+    """One row block against a weight far larger than L2, K not a multiple of the stage: every CTA streams
+    its B tiles from HBM and the loads of a stage land out of order. (The scale copies once took a barrier
+    phase of the wrong stage in this regime: stale scales, then a wait that ran out.) Repeated launches stay
+    bit-equal to the first, the two tile widths agree, no wait gives up, and the result is the fp32 product
+    of the dequantized operands."""
+    from fouroversix_b200 import _native
+
+    m, n, k = 128, 98304, 2880
+    g = torch.Generator(device=DEV).manual_seed(2)
+    qa = fos.quantize(torch.randn(m, k, generator=g, device=DEV).bfloat16())
+    w = (torch.randn(n, k, generator=g, device=DEV) * 0.02).bfloat16()
+    qb = fos.quantize(w)
+    first = B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType.bfloat16, variant=256).clone()
+    for _ in range(40):
+        assert torch.equal(B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType.bfloat16, variant=256), first)
+    assert torch.equal(B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType.bfloat16, variant=128), first)
+    assert _native.wait_failure_site() == 0
+    _check(first, _dense_reference(qa, qb), "skinny", mismatch_scale=(k / 1024) ** 0.5)
+
+
 def test_calls_with_different_options_on_two_streams():
     """Options travel with each call (CTA limit, kernel variant): two GEMMs in flight on two streams
     with different options give the bits each gives alone."""
