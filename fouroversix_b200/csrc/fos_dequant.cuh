@@ -7,6 +7,8 @@
 // by 6/7 in fp16 first), then (fp32(product) * amax) / divisor in fp32, then the cast.
 #pragma once
 
+#include <type_traits>
+
 #include "fos_common.cuh"
 
 namespace fos {
@@ -90,6 +92,63 @@ __device__ __forceinline__ void dequantize_block(uint2 c, uint32_t sfb, bool is_
         v[2 * j] = __fdiv_rn(__fmul_rn(as_fp16(__fmul_rn(q.x, s16)), k.amax), k.divisor);
         v[2 * j + 1] = __fdiv_rn(__fmul_rn(as_fp16(__fmul_rn(q.y, s16)), k.amax), k.divisor);
     }
+}
+
+// Two floats -> one word of two 16-bit outputs (`lo` in the lower half), round to nearest even.
+template <typename OUT>
+__device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
+    if constexpr (std::is_same<OUT, __half>::value) {
+        const __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    } else {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
+}
+
+// One NVFP4 block straight to sixteen 16-bit outputs (o[i] = values 2i, 2i + 1), with two multiplications, two
+// divisions and two conversions per BLOCK instead of per value. An E2M1 magnitude is 2^k or 1.5 * 2^k, the product
+// with the E4M3 scale s is exact in fp16 (at most 6 significant bits), and scaling by a power of two commutes with
+// every rounding on the way as long as nothing leaves the normal range:
+//     out(+-2^k)       = +-2^k * OUT(fl32(fl32(s * amax) / divisor))        = +-2^k * Q1
+//     out(+-1.5 * 2^k) = +-2^k * OUT(fl32(fl32(1.5 s * amax) / divisor))    = +-2^k * Q3
+// so the eight magnitudes are Q1 / 2, Q1, Q3, 2 Q1, 2 Q3, 4 Q1, 4 Q3 (exponent-field additions on the 16-bit
+// patterns) and zero; a byte permute looks them up by code, another one supplies the sign bit. The same bits as
+// dequantize_block followed by the cast (compared over whole tensors against the reference's fixtures and the
+// host-side restatement). Returns false, leaving o alone, for a block it does not take: amax outside the range
+// that keeps every step normal (k.fast), a scale byte with the sign bit set or NaN, or - fp16 outputs - a
+// magnitude that would leave fp16's normal range.
+template <typename OUT>
+__device__ __forceinline__ bool dequantize_block_packed(uint2 c, uint32_t sfb, const DequantConsts &k, uint32_t (&o)[8]) {
+    static_assert(sizeof(OUT) == 2, "16-bit outputs");
+    constexpr bool HALF = std::is_same<OUT, __half>::value;
+    constexpr uint32_t E = HALF ? 0x0400u : 0x0080u, E2 = E | (E << 16);       // one step of the exponent field
+    if (!k.fast || (sfb & 0x80u) || sfb == 0x7fu) return false;
+    const float s = e4m3_to_float(sfb);
+    const uint64_t a = fma2(pack2(s, __fmul_rn(s, 1.5f)), pack2(k.amax, k.amax), pack2(0.0f, 0.0f));
+    float q1, q3;
+    unpack2f(div_const2(a, pack2(-k.divisor, -k.divisor), pack2(k.y, k.y)), q1, q3);
+    if (HALF && q1 != 0.0f && !(q1 >= 0x1p-13f && q3 < 16376.0f)) return false;
+    uint32_t t23 = pack16x2<OUT>(q1, q3);                    // [Q1, Q3]
+    uint32_t t01 = (t23 << 16) - (E << 16);                  // [0, Q1 / 2]
+    uint32_t t45 = t23 + E2, t67 = t45 + E2;                 // [2 Q1, 2 Q3], [4 Q1, 4 Q3]
+    if ((t23 & 0xffffu) == 0u) t01 = t23 = t45 = t67 = 0u;   // a zero scale: every magnitude is zero
+    const uint32_t la = __byte_perm(t01, t23, 0x6420), ha = __byte_perm(t01, t23, 0x7531);   // low / high bytes of
+    const uint32_t lb = __byte_perm(t45, t67, 0x6420), hb = __byte_perm(t45, t67, 0x7531);   // magnitudes 0-3, 4-7
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+        const uint32_t cw = w ? c.y : c.x;
+        const uint32_t mag = cw & 0x77777777u, sgn = (cw >> 3) & 0x11111111u;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t sel = h ? mag >> 16 : mag, ss = h ? sgn >> 16 : sgn;
+            const uint32_t lo = __byte_perm(la, lb, sel);
+            const uint32_t hi = __byte_perm(ha, hb, sel) | __byte_perm(0x00008000u, 0u, ss);
+            o[4 * w + 2 * h] = __byte_perm(lo, hi, 0x5140);
+            o[4 * w + 2 * h + 1] = __byte_perm(lo, hi, 0x7362);
+        }
+    }
+    return true;
 }
 
 }  // namespace

@@ -55,10 +55,28 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantParams p) 
         for (int d = 0; d < DEQUANT_DEPTH; ++d) {
             const int cb = col_block[d];
             if (cb < 0) continue;
-            float v[16];
-            dequantize_block(c[d], sfb[d], p.format == FOS_IF4, k, v);
             OUT *dst = static_cast<OUT *>(p.out) + row[d] * p.ld_out + cb * 16;
             const int64_t left = p.cols - static_cast<int64_t>(cb) * 16;
+            if constexpr (sizeof(OUT) == 2) {
+                // NVFP4 to bf16 / fp16: the whole block from two quotients and a byte-permute table
+                uint32_t o[8];
+                if (p.format == FOS_NVFP4 && dequantize_block_packed<OUT>(c[d], sfb[d], k, o)) {
+                    if (left >= 16 && (reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
+                        stg_32(dst, o);                       // one 32-byte store: whole sectors per instruction
+                    } else if (left >= 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                        reinterpret_cast<uint4 *>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                        reinterpret_cast<uint4 *>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                    } else {
+                        uint16_t *d16 = reinterpret_cast<uint16_t *>(dst);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (i < left) d16[i] = static_cast<uint16_t>(o[i >> 1] >> ((i & 1) * 16));
+                    }
+                    continue;
+                }
+            }
+            float v[16];
+            dequantize_block(c[d], sfb[d], p.format == FOS_IF4, k, v);
             if (left >= 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
                 __align__(16) OUT tmp[16];
 #pragma unroll

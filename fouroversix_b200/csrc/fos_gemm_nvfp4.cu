@@ -84,7 +84,7 @@ template <int BLOCK_N> struct Cfg {
     static_assert(ACC_STAGES * BLOCK_N <= SF_COL0, "accumulators overlap the scale columns");
     static_assert(SF_COL0 + SF_SLOTS * SF_STAGE_COLS <= TMEM_COLS, "scale ring does not fit tensor memory");
     static_assert(SMEM_BYTES <= 232448, "more shared memory than a CTA can have");
-    static_assert((2 * STAGES + (SF_CP_WARPS + 1) * SF_SLOTS + 2 * ACC_STAGES) * 8 + 8 <= BARRIER_BYTES, "barrier area too small");
+    static_assert((2 * STAGES + (SF_CP_WARPS + 1) * SF_SLOTS + 2 * ACC_STAGES + 1) * 8 + 8 <= BARRIER_BYTES, "barrier area too small");
 };
 
 struct GemmParams {
@@ -217,7 +217,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const uint32_t sf_ready_bar = sf_full_bar + 8 * SF_CP_WARPS * C::SF_SLOTS;   // [SF_SLOTS] scales are in tensor memory
     const uint32_t acc_full_bar = sf_ready_bar + 8 * C::SF_SLOTS;   // [ACC_STAGES]
     const uint32_t acc_empty_bar = acc_full_bar + 8 * C::ACC_STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::STAGES + (SF_CP_WARPS + 1) * C::SF_SLOTS + 2 * C::ACC_STAGES);
+    const uint32_t drain_bar = acc_empty_bar + 8 * C::ACC_STAGES;   // only used when the CTA gives up
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::STAGES + (SF_CP_WARPS + 1) * C::SF_SLOTS + 2 * C::ACC_STAGES + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -258,6 +259,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             mbar_init(acc_full_bar + 8 * a, 1);
             mbar_init(acc_empty_bar + 8 * a, 8);   // one arrival per epilogue warp
         }
+        mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -424,6 +426,13 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 if (++j == C::SF_SLOTS) { j = 0; jph ^= 1u; }
             }
             if (ok && issue) tc_commit(acc_full_bar + 8 * acc);  // accumulator complete
+        }
+        if (!ok) {
+            // giving up: the MMAs already issued must have finished before tensor memory is released
+            if (issue) tc_commit(drain_bar);
+            __syncwarp();
+            const long long t0 = clock64();
+            while (!mbar_try_wait(drain_bar, 0) && clock64() - t0 < 20000000ll) {}   // about 10 ms
         }
     } else if (warp >= 2 && warp < 10) {
         // ------------------------------------------------------------------ epilogue
