@@ -36,35 +36,114 @@ struct ExpandParams {
 
 __device__ __forceinline__ float as_fp16_value(float v) { return __half2float(__float2half_rn(v)); }
 
-// One thread per 16-value block: 8 bytes of codes + 1 scale byte -> 32 bytes of fp16.
+// The sixteen fp16 outputs of one block (o[i] = values 2i, 2i + 1) from a table of its eight magnitudes.
+// E2M1 blocks: value * scale is exact in fp16 (at most 6 significant bits, never subnormal: the smallest
+// product is 0.5 * 2^-9), so the magnitudes are s / 2, s, 1.5 s, 2 s, 3 s, 4 s, 6 s: two conversions and
+// exponent-field additions. Integer blocks: fp16(fp16(i * 6/7) * s) for i = 1 .. 7, four packed fp16
+// multiplications by the constants fp16(i * fl32(6/7)); the magnitude of a two's-complement nibble is
+// (n ^ m) + sign with m = 15 where the sign bit is set, all eight nibbles of a word at once (-8 does not occur:
+// the quantizer clamps to +-7). A byte permute looks the magnitudes up by code, another one supplies the sign
+// bit. Returns false for a scale byte it does not take (NaN; a set sign bit on an NVFP4 scale).
+__device__ __forceinline__ bool expand_block_packed(uint2 c, uint32_t sfb, bool if4, uint32_t (&o)[8]) {
+    const bool is_int = if4 && (sfb & 0x80u);
+    if (if4) sfb &= 0x7fu;
+    if (sfb >= 0x7fu) return false;
+    const float s = e4m3_to_float(sfb);
+    uint32_t t01, t23, t45, t67, mag[2], sgn[2];
+    sgn[0] = (c.x >> 3) & 0x11111111u;
+    sgn[1] = (c.y >> 3) & 0x11111111u;
+    if (!is_int) {
+        t23 = pack_pair<__half>(s, __fmul_rn(s, 1.5f));
+        t01 = (t23 << 16) - 0x04000000u;
+        t45 = t23 + 0x04000400u;
+        t67 = t45 + 0x04000400u;
+        if ((t23 & 0xffffu) == 0u) t01 = t23 = t45 = t67 = 0u;
+        mag[0] = c.x & 0x77777777u;
+        mag[1] = c.y & 0x77777777u;
+    } else {
+        const __half2 s2 = __float2half2_rn(s);
+        auto times = [&](uint32_t consts) {
+            const __half2 r = __hmul2(*reinterpret_cast<const __half2 *>(&consts), s2);
+            return *reinterpret_cast<const uint32_t *>(&r);
+        };
+        t01 = times(0x3adb0000u);            // fp16(i * fl32(6/7)) for i = 0, 1
+        t23 = times(0x41253edbu);            // 2, 3
+        t45 = times(0x444942dbu);            // 4, 5
+        t67 = times(0x46004525u);            // 6, 7
+        mag[0] = ((c.x ^ (sgn[0] * 15u)) + sgn[0]) & 0x77777777u;
+        mag[1] = ((c.y ^ (sgn[1] * 15u)) + sgn[1]) & 0x77777777u;
+    }
+    const uint32_t la = __byte_perm(t01, t23, 0x6420), ha = __byte_perm(t01, t23, 0x7531);
+    const uint32_t lb = __byte_perm(t45, t67, 0x6420), hb = __byte_perm(t45, t67, 0x7531);
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t sel = h ? mag[w] >> 16 : mag[w], ss = h ? sgn[w] >> 16 : sgn[w];
+            const uint32_t lo = __byte_perm(la, lb, sel);
+            const uint32_t hi = __byte_perm(ha, hb, sel) | __byte_perm(0x00008000u, 0u, ss);
+            o[4 * w + 2 * h] = __byte_perm(lo, hi, 0x5140);
+            o[4 * w + 2 * h + 1] = __byte_perm(lo, hi, 0x7362);
+        }
+    }
+    return true;
+}
+
+// One thread per 16-value block: 8 bytes of codes + 1 scale byte -> 32 bytes of fp16. Four blocks per thread and
+// round, their loads issued before the first is decoded.
+constexpr int EXPAND_DEPTH = 4;
 __global__ void __launch_bounds__(256) expand_kernel(const ExpandParams p) {
     const int64_t n_cb = p.cols_p >> 4;
     const int64_t total = p.rows_p * n_cb;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / n_cb, cb = i - r * n_cb;
-        const uint2 c = *reinterpret_cast<const uint2 *>(p.codes + r * (p.cols_p >> 1) + cb * 8);
-        uint32_t sfb = p.sf[sf_offset(r, cb, n_cb, p.sf_tiled != 0)];
-        const bool is_int = p.format == FOS_IF4 && (sfb & 0x80u);
-        if (p.format == FOS_IF4) sfb &= 0x7fu;
-        const float s16 = e4m3_to_float(sfb);
-        __align__(16) __half h[16];
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i0 = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i0 < total; i0 += stride * EXPAND_DEPTH) {
+        uint2 c[EXPAND_DEPTH];
+        uint32_t sfbs[EXPAND_DEPTH];
+        int64_t offs[EXPAND_DEPTH];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t byte = ((j < 4 ? c.x : c.y) >> ((j & 3) * 8)) & 0xffu;
-            float2 q;
-            if (is_int) {
-                const float six_sevenths = static_cast<float>(6.0 / 7.0);
-                q.x = as_fp16_value(__fmul_rn(static_cast<float>(static_cast<int>(byte << 28) >> 28), six_sevenths));
-                q.y = as_fp16_value(__fmul_rn(static_cast<float>(static_cast<int>(byte << 24) >> 28), six_sevenths));
-            } else {
-                q = e2m1x2_to_float2(byte);
+        for (int d = 0; d < EXPAND_DEPTH; ++d) {
+            const int64_t i = i0 + d * stride;
+            offs[d] = -1;
+            c[d] = make_uint2(0u, 0u);
+            sfbs[d] = 0u;
+            if (i < total) {
+                const int64_t r = i / n_cb, cb = i - r * n_cb;
+                c[d] = *reinterpret_cast<const uint2 *>(p.codes + r * (p.cols_p >> 1) + cb * 8);
+                sfbs[d] = p.sf[sf_offset(r, cb, n_cb, p.sf_tiled != 0)];
+                offs[d] = r * p.cols_p + cb * 16;
             }
-            h[2 * j] = __float2half_rn(__fmul_rn(q.x, s16));
-            h[2 * j + 1] = __float2half_rn(__fmul_rn(q.y, s16));
         }
-        uint4 *dst = reinterpret_cast<uint4 *>(p.out + r * p.cols_p + cb * 16);
-        dst[0] = reinterpret_cast<const uint4 *>(h)[0];
-        dst[1] = reinterpret_cast<const uint4 *>(h)[1];
+#pragma unroll
+        for (int d = 0; d < EXPAND_DEPTH; ++d) {
+            if (offs[d] < 0) continue;
+            uint4 *dst = reinterpret_cast<uint4 *>(p.out + offs[d]);
+            uint32_t o[8];
+            if (expand_block_packed(c[d], sfbs[d], p.format == FOS_IF4, o)) {
+                stg_32(dst, o);
+                continue;
+            }
+            uint32_t sfb = sfbs[d];
+            const bool is_int = p.format == FOS_IF4 && (sfb & 0x80u);
+            if (p.format == FOS_IF4) sfb &= 0x7fu;
+            const float s16 = e4m3_to_float(sfb);
+            __align__(16) __half h[16];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t byte = ((j < 4 ? c[d].x : c[d].y) >> ((j & 3) * 8)) & 0xffu;
+                float2 q;
+                if (is_int) {
+                    const float six_sevenths = static_cast<float>(6.0 / 7.0);
+                    q.x = as_fp16_value(__fmul_rn(static_cast<float>(static_cast<int>(byte << 28) >> 28), six_sevenths));
+                    q.y = as_fp16_value(__fmul_rn(static_cast<float>(static_cast<int>(byte << 24) >> 28), six_sevenths));
+                } else {
+                    q = e2m1x2_to_float2(byte);
+                }
+                h[2 * j] = __float2half_rn(__fmul_rn(q.x, s16));
+                h[2 * j + 1] = __float2half_rn(__fmul_rn(q.y, s16));
+            }
+            dst[0] = reinterpret_cast<const uint4 *>(h)[0];
+            dst[1] = reinterpret_cast<const uint4 *>(h)[1];
+        }
     }
 }
 
