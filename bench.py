@@ -295,6 +295,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     # other quantize modes of the same tensor (each: the whole call, both launches)
     for name, c in (("static_6", fos.QuantizationConfig(scale_rule="static_6")),
                     ("mse_amax_given", None),
+                    ("mae", fos.QuantizationConfig(scale_rule="mae")),
+                    ("abs_max", fos.QuantizationConfig(scale_rule="abs_max")),
                     ("if4_mse", fos.QuantizationConfig(dtype="if4")),
                     ("mse_2d", fos.QuantizationConfig(block_scale_2d=True)),
                     ("mse_transposed", fos.QuantizationConfig(transpose=True)),
@@ -533,6 +535,7 @@ def gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks):
 
 
 STACK_TOKENS = 16 * 2048
+HANDOFF_ROW_CHUNKS, HANDOFF_COL_CHUNKS, HANDOFF_COMM_SMS = 2, 2, 32      # settings of the row-slab hand-off in the stack
 STACK_LAYERS = (  # name, parallelism, out features N, in features K: the linear layers of one Llama-3-70B decoder block
     ("qkv_proj", "column", 10240, 8192),
     ("o_proj", "row", 8192, 8192),
@@ -568,7 +571,7 @@ def stack_section(args, fos, dev, rank, world):
             ms = float(t.item())
         return ms
 
-    def run(handoff: bool):
+    def run(handoff: bool, row_chunks: int = HANDOFF_ROW_CHUNKS, col_chunks: int = HANDOFF_COL_CHUNKS, comm_sms: int = HANDOFF_COMM_SMS):
         layers, total_ms, total_flop = {}, 0.0, 0.0
         for idx, (name, mode, n, k) in enumerate(STACK_LAYERS):
             g = torch.Generator(device=dev).manual_seed(12 + idx + 100 * rank)
@@ -584,7 +587,11 @@ def stack_section(args, fos, dev, rank, world):
             kw = {}
             if handoff:
                 kw = dict(scattered_input=True) if mode == "column" else dict(scatter_output=True)
-            layer = TensorParallelLinear(w, cfg, mode, chunks=2 if handoff else 4, **kw)
+            if handoff:
+                layer = TensorParallelLinear(w, cfg, mode, chunks=col_chunks if mode == "column" else row_chunks,
+                                             comm_sms=comm_sms, **kw)
+            else:
+                layer = TensorParallelLinear(w, cfg, mode, chunks=4, **kw)
             del w
             if name == "up_proj":
                 # gate_proj and up_proj read the same activation: its quantization (and gather) is counted once,
@@ -607,15 +614,24 @@ def stack_section(args, fos, dev, rank, world):
         return layers, total_ms, total_flop
 
     layers, total_ms, total_flop = run(handoff=world > 1)
+    variants = {}
+    if world > 1 and os.environ.get("FOS_STACK_VARIANTS"):
+        # tuning aid: "row_chunks:col_chunks:comm_sms,..." - the hand-off form with other settings, same process
+        for spec in os.environ["FOS_STACK_VARIANTS"].split(","):
+            rc, cc, sm = (int(v) for v in spec.split(":"))
+            v_layers, v_ms, _ = run(True, rc, cc, sm)
+            variants[spec] = {"ms": round(v_ms, 4), "layers": {k: round(v["ms"], 4) for k, v in v_layers.items()}}
     out = {
         "tokens": STACK_TOKENS, "n_gpus": world, "layers": layers, "ms": total_ms,
         "TFLOP/s": total_flop / (total_ms * 1e-3) / 1e12,
         "form": ("one GPU" if world == 1 else
-                 "row-slab hand-off: reduce-scatter after row-parallel layers (NCCL, 2 chunks beside the GEMM), common amax, "
+                 f"row-slab hand-off: reduce-scatter after row-parallel layers (NCCL, {HANDOFF_ROW_CHUNKS} chunks beside the GEMM), common amax, "
                  "slab quantization, all-gather of packed codes + scales before column-parallel layers"),
         "how": "eager calls of sharding.TensorParallelLinear.forward (dynamic activation quantization + FP4 GEMM "
                "[+ the exchange]); CUDA events, max over ranks; weights quantized per shard outside the timed region",
     }
+    if variants:
+        out["variants"] = variants
     if world > 1:
         ar_layers, ar_ms, _ = run(handoff=False)
         nbytes = STACK_TOKENS * 8192 * 2
@@ -761,7 +777,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--case", default=None, choices=["quantize", "dequantize", "gemm", "experts"], help="one kernel on its own (run_case)")
+    ap.add_argument("--case", default=None, choices=["quantize", "dequantize", "gemm", "experts", "stack"], help="one kernel on its own (run_case)")
     ap.add_argument("--experts", type=int, default=32)
     ap.add_argument("--top-k", type=int, default=4)
     ap.add_argument("--rows", type=int, default=A_SHAPE[0])
@@ -781,6 +797,26 @@ def main() -> None:
     args = ap.parse_args()
     side = 2880 if args.case == "experts" else 8192          # default m, n, k of the case
     args.m, args.n, args.k = (v if v is not None else side for v in (args.m, args.n, args.k))
+    if args.case == "stack":
+        # the decoder stack on its own (under torchrun for more than one GPU): python -m torch.distributed.run
+        # --nproc-per-node N bench.py --case stack
+        import fouroversix_b200 as fos
+
+        rank, world, local_rank = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("WORLD_SIZE", "1"), ("LOCAL_RANK", "0")))
+        dev = torch.device("cuda", local_rank)
+        torch.cuda.set_device(dev)
+        if world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=dev)
+        try:
+            out = stack_section(args, fos, dev, rank, world)
+            if rank == 0:
+                print(json.dumps(out))
+        finally:
+            if world > 1:
+                dist.barrier()
+                dist.destroy_process_group()
+        return
     if args.case is not None:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py: no CUDA device; the GPU path has no CPU fallback")

@@ -493,6 +493,14 @@ __device__ __forceinline__ TensorConsts tensor_consts(float amax, int rule, bool
 // caller rules it out (`filter_allowed`: wrong rule, exact-only run, amax out of range), the
 // scale is zero or subnormal, or r is so small that x * r can underflow.
 // The 1-D kernels tabulate this once per CTA for all 128 bytes; other callers compute it.
+// Which configurations have a fast pre-filter: NVFP4 4/6 with 1-D blocks for all three rules (sums of squares,
+// sums of magnitudes, largest magnitude); 2-D blocks and IF4 for the mean-squared error only.
+template <int KIND, bool TWO_D>
+__device__ __forceinline__ bool rule_has_filter(int rule) {
+    if (rule == FOS_RULE_MSE) return true;
+    return KIND == KIND_ADAPTIVE && !TWO_D && (rule == FOS_RULE_MAE || rule == FOS_RULE_ABS_MAX);
+}
+
 __device__ __forceinline__ float4 scale_entry(uint32_t sfb, const TensorConsts &tc, bool filter_allowed) {
     const float s = e4m3_to_float(sfb);
     const float r = __frcp_rn(__fmul_rn(tc.decode, s));
@@ -564,7 +572,7 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
     const float q = tc.block_div != 0.0f ? __fdiv_rn(bmax, tc.block_div)
                                          : (tc.maxq == 6.0f ? div6_exact(bmax) : __fmul_rn(bmax, 0.25f));   // bmax / maxq
     const float hp = __fmul_rn(q, tc.encode0);
-    const bool filter_allowed = !TWO_D && rule == FOS_RULE_MSE && !exact_only && tc.filter_ok;   // unused with a table
+    const bool filter_allowed = !TWO_D && rule_has_filter<KIND, TWO_D>(rule) && !exact_only && tc.filter_ok;   // unused with a table
 
     if (KIND == KIND_STATIC) {
         const uint32_t sfb = cvt_e4m3(hp);
@@ -621,7 +629,34 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
         bool decided = false, pick_b = false;
         uint32_t ca[2] = {0u, 0u}, cb[2] = {0u, 0u};
         float row_a = 0.0f, row_b = 0.0f;                    // 2-D: this row's share of the block's sums
-        if (eligible) {
+        if (eligible && !TWO_D && rule != FOS_RULE_MSE) {
+            // Sums of magnitudes (mae) and largest magnitude (abs_max), 1-D blocks. The reference's term is
+            // |deq - x| = G * |t + eta| with the same eta as above plus the rounding of the subtraction: |eta| <= 64u
+            // generously. Hence sum|t + eta| differs from sum|t| by at most 16 * 64u = 1024u and max|t + eta| from
+            // max|t| by at most 64u (absolute, in units of G); the roundings of either summation, of the residuals
+            // and of G itself add at most 60u relative (8u for the maximum, which is not summed).
+            const uint64_t ra2 = pack2(r_a, r_a), rb2 = pack2(r_b, r_b);
+            const bool is_max = rule == FOS_RULE_ABS_MAX;
+            float m_a = 0.0f, m_b = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 2; ++w) {
+                float ta[8], tb[8];
+                ca[w] = encode8_with_residuals(&v[8 * w], ra2, ta);
+                cb[w] = encode8_with_residuals(&v[8 * w], rb2, tb);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    m_a = is_max ? fmaxf(m_a, fabsf(ta[k])) : m_a + fabsf(ta[k]);
+                    m_b = is_max ? fmaxf(m_b, fabsf(tb[k])) : m_b + fabsf(tb[k]);
+                }
+            }
+            const float g_a = s_a * amax * (1.0f / 1536.0f), g_b = s_b * amax * (1.0f / 1536.0f);
+            const float err_a = m_a * g_a, err_b = m_b * g_b;
+            const float tau = is_max ? 0x1p-24f * 1.5f * (8.0f * (err_a + err_b) + 64.0f * (g_a + g_b))
+                                     : 0x1p-24f * 1.5f * (60.0f * (err_a + err_b) + 1024.0f * (g_a + g_b));
+            const float diff = err_b - err_a;
+            decided = fabsf(diff) > tau;
+            pick_b = diff < 0.0f;
+        } else if (eligible) {
             const uint64_t ra2 = pack2(r_a, r_a), rb2 = pack2(r_b, r_b);
             uint64_t acc_a = pack2(0.0f, 0.0f), acc_b = acc_a;
 #pragma unroll
@@ -695,11 +730,18 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
                 const float s = coop[16 + 2 * cand], r = coop[17 + 2 * cand];
                 const float2 q = e2m1x2_to_float2(cvt_e2m1x2(0.0f, __fmaf_rn(x, r, 0.0f)));
                 const float d = __fsub_rn(__fdiv_rn(__fmul_rn(__fmul_rn(q.x, s), amax), 1536.0f), x);
-                const float e = __fmul_rn(d, d);
-                const float p = __fadd_rn(e, __shfl_down_sync(FULL, e, 8));      // valid in lanes with i < 8
-                float total = __shfl_sync(FULL, p, cand * 16);
+                const float e = rule == FOS_RULE_MSE ? __fmul_rn(d, d) : fabsf(d);
+                float total;
+                if (rule == FOS_RULE_ABS_MAX) {
+                    total = e;                                                   // maximum over the candidate's 16 lanes
 #pragma unroll
-                for (int k = 1; k < 8; ++k) total = __fadd_rn(total, __shfl_sync(FULL, p, cand * 16 + k));
+                    for (int o = 8; o > 0; o >>= 1) total = fmaxf(total, __shfl_xor_sync(FULL, total, o));
+                } else {
+                    const float p = __fadd_rn(e, __shfl_down_sync(FULL, e, 8));  // valid in lanes with i < 8
+                    total = __shfl_sync(FULL, p, cand * 16);
+#pragma unroll
+                    for (int k = 1; k < 8; ++k) total = __fadd_rn(total, __shfl_sync(FULL, p, cand * 16 + k));
+                }
                 const float exact_a = __shfl_sync(FULL, total, 0), exact_b = __shfl_sync(FULL, total, 16);
                 if (lane == src) {
                     decided = true;
@@ -994,7 +1036,7 @@ quantize_rows_kernel(const QuantParams p) {
     const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(p.amax), p.rule);
     if (p.amax_store != nullptr && threadIdx.x == 0 && blockIdx.x == 0) *p.amax_store = tc.amax;
     if (threadIdx.x < 128)
-        lut[threadIdx.x] = scale_entry(threadIdx.x, tc, p.rule == FOS_RULE_MSE && !p.exact_only && tc.filter_ok);
+        lut[threadIdx.x] = scale_entry(threadIdx.x, tc, rule_has_filter<KIND, false>(p.rule) && !p.exact_only && tc.filter_ok);
     __syncthreads();
 
     while (true) {
@@ -1145,7 +1187,7 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
     const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(amax_ptr), p.rule, EXTRAS && p.unbiased);
     if (p.amax_store != nullptr && threadIdx.x == 0 && blockIdx.x == 0) *p.amax_store = tc.amax;
     if (threadIdx.x < 128)
-        lut[threadIdx.x] = scale_entry(threadIdx.x, tc, p.rule == FOS_RULE_MSE && !p.exact_only && tc.filter_ok);
+        lut[threadIdx.x] = scale_entry(threadIdx.x, tc, rule_has_filter<KIND, TWO_D>(p.rule) && !p.exact_only && tc.filter_ok);
     asm volatile("bar.sync 1, %0;" ::"n"(FEED_CONSUMERS) : "memory");
 
     // What depends on the thread alone is computed here once. The empty asm statements make these
@@ -1594,7 +1636,7 @@ quantize_cols_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
     const TensorConsts tc = tensor_consts<KIND>(*reinterpret_cast<const volatile float *>(p.amax), p.rule, EXTRAS && p.unbiased);
     if (p.amax_store != nullptr && threadIdx.x == 0 && blockIdx.x == 0) *p.amax_store = tc.amax;
     if (threadIdx.x < 128)
-        lut[threadIdx.x] = scale_entry(threadIdx.x, tc, p.rule == FOS_RULE_MSE && !p.exact_only && tc.filter_ok);
+        lut[threadIdx.x] = scale_entry(threadIdx.x, tc, rule_has_filter<KIND, TWO_D>(p.rule) && !p.exact_only && tc.filter_ok);
     asm volatile("bar.sync 1, %0;" ::"n"(FEED_CONSUMERS) : "memory");
 
     const int jr = threadIdx.x & 127, pair = threadIdx.x >> 7;          // row of the tile, which two of its four blocks
