@@ -27,11 +27,17 @@ constexpr int DEQUANT_DEPTH = 4;
 
 template <typename OUT>
 __global__ void __launch_bounds__(256) dequantize_kernel(const DequantParams p) {
-    const int64_t n_cb = p.cols_p >> 4;
+    const int n_cb = static_cast<int>(p.cols_p >> 4);
     const int cb_used = static_cast<int>((p.cols + 15) >> 4);
     const int chunks = (cb_used + 255) >> 8;
     const int64_t units = p.rows * chunks;
     const DequantConsts k = dequant_consts(__ldg(p.amax), p.divisor);
+    // a unit is (row, chunk of 256 blocks); this CTA's units are blockIdx.x, + gridDim.x, ...: the pair is advanced
+    // by additions (a division per unit cost more than decoding it)
+    const int step_r = static_cast<int>(gridDim.x) / chunks, step_c = static_cast<int>(gridDim.x) % chunks;
+    int64_t row0 = static_cast<int64_t>(blockIdx.x) / chunks;
+    int ch0 = static_cast<int>(blockIdx.x - row0 * chunks);
+    const int64_t code_ld = p.cols_p >> 1;
     for (int64_t u0 = blockIdx.x; u0 < units; u0 += static_cast<int64_t>(gridDim.x) * DEQUANT_DEPTH) {
         uint2 c[DEQUANT_DEPTH];
         uint32_t sfb[DEQUANT_DEPTH];
@@ -39,17 +45,22 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantParams p) 
         int col_block[DEQUANT_DEPTH];
 #pragma unroll
         for (int d = 0; d < DEQUANT_DEPTH; ++d) {
-            const int64_t u = u0 + static_cast<int64_t>(d) * gridDim.x;
-            const int64_t r = u / chunks;
-            const int cb = static_cast<int>(u - r * chunks) * 256 + static_cast<int>(threadIdx.x);
+            const int64_t r = row0;
+            const int cb = ch0 * 256 + static_cast<int>(threadIdx.x);
             row[d] = r;
-            col_block[d] = (u < units && cb < cb_used) ? cb : -1;
+            col_block[d] = (u0 + static_cast<int64_t>(d) * gridDim.x < units && cb < cb_used) ? cb : -1;
             c[d] = make_uint2(0u, 0u);
             sfb[d] = 0u;
             if (col_block[d] >= 0) {
-                c[d] = *reinterpret_cast<const uint2 *>(p.codes + r * (p.cols_p >> 1) + cb * 8);
-                sfb[d] = p.sf[sf_offset(r, cb, n_cb, p.sf_tiled != 0)];
+                c[d] = *reinterpret_cast<const uint2 *>(p.codes + r * code_ld + cb * 8);
+                const int64_t sf_off = p.sf_tiled
+                    ? ((r >> 7) * (n_cb >> 2) + (cb >> 2)) * 512 + ((static_cast<int>(r) & 31) * 16 + ((static_cast<int>(r) >> 5) & 3) * 4 + (cb & 3))
+                    : r * n_cb + cb;
+                sfb[d] = p.sf[sf_off];
             }
+            row0 += step_r;                      // the next unit of this CTA
+            ch0 += step_c;
+            if (ch0 >= chunks) { ch0 -= chunks; ++row0; }
         }
 #pragma unroll
         for (int d = 0; d < DEQUANT_DEPTH; ++d) {

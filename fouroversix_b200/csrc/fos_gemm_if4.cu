@@ -96,6 +96,7 @@ __global__ void __launch_bounds__(256) expand_kernel(const ExpandParams p) {
     const int64_t n_cb = p.cols_p >> 4;
     const int64_t total = p.rows_p * n_cb;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const bool small = total < (int64_t(1) << 31);
     for (int64_t i0 = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i0 < total; i0 += stride * EXPAND_DEPTH) {
         uint2 c[EXPAND_DEPTH];
         uint32_t sfbs[EXPAND_DEPTH];
@@ -107,7 +108,9 @@ __global__ void __launch_bounds__(256) expand_kernel(const ExpandParams p) {
             c[d] = make_uint2(0u, 0u);
             sfbs[d] = 0u;
             if (i < total) {
-                const int64_t r = i / n_cb, cb = i - r * n_cb;
+                // (a 64-bit division costs about as much as decoding the block)
+                const int64_t r = small ? static_cast<int64_t>(static_cast<uint32_t>(i) / static_cast<uint32_t>(n_cb)) : i / n_cb;
+                const int64_t cb = i - r * n_cb;
                 c[d] = *reinterpret_cast<const uint2 *>(p.codes + r * (p.cols_p >> 1) + cb * 8);
                 sfbs[d] = p.sf[sf_offset(r, cb, n_cb, p.sf_tiled != 0)];
                 offs[d] = r * p.cols_p + cb * 16;
