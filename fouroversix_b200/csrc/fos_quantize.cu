@@ -559,6 +559,37 @@ __device__ __forceinline__ float encode_stochastic(const float (&v)[16], float r
     return sum;
 }
 
+// The integer grid of IF4 under stochastic rounding (src/fouroversix/quantize/pytorch/reference.py:55-63):
+// u = (x * r) * fl(7/6), magnitude rint(|u| + noise) clamped to 7, sign of u. Returns the sum of the squared
+// residuals (6/7) * q - x * r, in the same scaled units as encode_stochastic, so that the two candidates of a block
+// compare directly (they share the scale).
+__device__ __forceinline__ float encode_stochastic_int(const float (&v)[16], float r, const StochasticArgs &sr,
+                                                       uint32_t candidate, uint32_t &lo, uint32_t &hi) {
+    const float to_int = 1.16666666f, from_int = 0.8571428571f;
+    uint32_t w[2] = {0u, 0u};
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+        const uint32_t h = hash32(sr.key ^ (sr.block * 32u + candidate * 16u + i));
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float xs = __fmaf_rn(v[i + k], r, 0.0f);
+            const float u = __fmul_rn(xs, to_int);
+            const uint32_t bits16 = k == 0 ? (h & 0xffffu) : (h >> 16);
+            const float noise = __uint_as_float((bits16 << 7) | 0x3f800040u) - 1.5f;    // uniform in (-0.5, 0.5)
+            const float steps = ((fabsf(u) + noise) + 12582912.0f) - 12582912.0f;       // rint, ties to even
+            const float mag = fminf(fmaxf(steps, 0.0f), 7.0f);
+            const float q = copysignf(mag, u);
+            const float t = __fmaf_rn(q, from_int, -xs);
+            sum = __fmaf_rn(t, t, sum);
+            w[(i + k) >> 3] |= (static_cast<uint32_t>(static_cast<int>(q)) & 0xfu) << (((i + k) & 7) * 4);
+        }
+    }
+    lo = w[0];
+    hi = w[1];
+    return sum;
+}
+
 template <int KIND, bool TWO_D, bool TRANSPOSED>
 __device__ __forceinline__ void quantize_block(const float (&v)[16], const TensorConsts &tc, int rule,
                                                bool exact_only, float *scratch, int lane, const float4 *lut,
@@ -784,6 +815,21 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
     // err_i differs from (6/7)^2 * sum(d^2) * G^2 by at most 2 * 80u * sum|t| <= 640u * sqrt(S_i)
     // <= 320u * (S_i + 1), plus 40u relative for the summations; likewise 188u * (S_f + 1) + 40u.
     // The two candidates share G, so the comparison is made on S_i and S_f themselves.
+    if (KIND == KIND_IF4 && sr.on) {
+        // both grids rounded stochastically with independent noise; the grid with the smaller squared error of THIS
+        // draw wins (the candidates share the scale, so the sums compare as they are)
+        uint32_t lo_f = 0u, hi_f = 0u, lo_i = 0u, hi_i = 0u;
+        bool take_int = false;
+        if (s_a != 0.0f) {
+            const float err_f = encode_stochastic(v, r_a, sr, 0u, lo_f, hi_f);
+            const float err_i = encode_stochastic_int(v, r_a, sr, 1u, lo_i, hi_i);
+            take_int = err_i < err_f;
+        }
+        lo = take_int ? lo_i : lo_f;
+        hi = take_int ? hi_i : hi_f;
+        sf_byte = sfb_a | (take_int ? 0x80u : 0u);
+        return;
+    }
     const bool if4_eligible = KIND == KIND_IF4 && !TWO_D && ea.w >= 0.0f && __fmul_rn(bmax, r_a) <= 6.42f;
     bool if4_decided = false, pick_int_fast = false;
     uint32_t cf[2] = {0u, 0u};
@@ -1969,7 +2015,8 @@ static int quantize_entry(const void *x, int x_dtype, int64_t rows, int64_t cols
     using namespace fos;
     if (stochastic) {
         // stochastic rounding lives in the TMA-fed kernels only: NVFP4, 1-D blocks, aligned input
-        if (format != FOS_NVFP4 || block_2d) return FOS_ERR_UNSUPPORTED;
+        if ((format != FOS_NVFP4 && format != FOS_IF4) || block_2d) return FOS_ERR_UNSUPPORTED;
+        if (format == FOS_IF4 && scale_rule != FOS_RULE_MSE) return FOS_ERR_UNSUPPORTED;   // the noisy candidates are compared by squared error
         if ((flags & FOS_QUANTIZE_NO_TMA) || reinterpret_cast<uintptr_t>(x) % 16 != 0 || (ld * 2) % 16 != 0) return FOS_ERR_UNSUPPORTED;
         if (transpose && (reinterpret_cast<uintptr_t>(codes) % 16 != 0 || reinterpret_cast<uintptr_t>(sf) % 2 != 0))
             return FOS_ERR_UNSUPPORTED;

@@ -15,7 +15,7 @@ import functools
 import torch
 
 from fouroversix_b200 import _native
-from fouroversix_b200.utils import DataType, RoundStyle, ScaleType
+from fouroversix_b200.utils import DataType, ScaleRule, RoundStyle, ScaleType
 
 from .config import QuantizationConfig
 from .quantized_tensor import QuantizedTensor, padded_shape_for
@@ -54,8 +54,11 @@ class B200QuantizeBackend:
             return f"dtype {config.dtype.value} is not implemented (nvfp4, if4 and mxfp4 are)"
         if config.scale_rule not in config.dtype.supported_scale_rules:
             return f"scale rule {config.scale_rule.value} is not defined for {config.dtype.value}"
-        if config.round_style.is_stochastic and (config.dtype != DataType.nvfp4 or config.block_scale_2d):
-            return "stochastic rounding is implemented for NVFP4 with 1-D blocks"
+        if config.round_style.is_stochastic:
+            if config.block_scale_2d or config.dtype not in (DataType.nvfp4, DataType.if4):
+                return "stochastic rounding is implemented for NVFP4 and IF4 with 1-D blocks"
+            if config.dtype == DataType.if4 and config.scale_rule != ScaleRule.mse:
+                return "stochastic rounding of IF4 compares its two grids by squared error (scale rule mse)"
         if config.rht and config.dtype == DataType.mxfp4:
             return "the random Hadamard transform is not implemented for mxfp4"
         if config.rht and x.ndim == 2 and x.shape[0 if config.transpose else 1] % 16 != 0:

@@ -356,6 +356,34 @@ def test_stochastic_unbiased_rounding():
     assert torch.allclose(ya * (16 / 17), yb, rtol=1e-5, atol=0)
 
 
+def test_stochastic_rounding_if4():
+    """IF4 with stochastic rounding: both grids draw independent noise and the smaller squared error of the draw
+    wins. Parity in distribution, by the reference's pinned distances (tests/test_quantize.py:322: 110, and 122 for
+    stochastic_unbiased, +-5 %); the mean over seeds approaches x; same seed, same bytes; both grids are in use."""
+    g = torch.Generator().manual_seed(0)
+    xd = torch.randn(1024, 1024, generator=g).bfloat16().to(DEV)
+    for style, pinned in (("stochastic", 110.0), ("stochastic_unbiased", 122.0)):
+        c = fos.QuantizationConfig(dtype="if4", scale_rule="mse", round_style=style)
+        q1, q2 = B200QuantizeBackend.quantize(xd, c, seed=5), B200QuantizeBackend.quantize(xd, c, seed=5)
+        q3 = B200QuantizeBackend.quantize(xd, c, seed=6)
+        assert torch.equal(q1.values, q2.values) and torch.equal(q1.scale_factors.view(torch.uint8), q2.scale_factors.view(torch.uint8))
+        assert not torch.equal(q1.values, q3.values)
+        dist = torch.dist(fos.dequantize(q1, torch.float32), xd.float()).item()
+        assert pinned * 0.95 <= dist <= pinned * 1.05, (style, dist)
+        int_blocks = (q1.scale_factors.view(torch.uint8) >= 128).float().mean().item()
+        assert 0.05 < int_blocks < 0.95, int_blocks
+    c = fos.QuantizationConfig(dtype="if4", scale_rule="mse", round_style="stochastic")
+    acc = torch.zeros_like(xd, dtype=torch.float32)
+    for seed in range(64):
+        acc += fos.dequantize(B200QuantizeBackend.quantize(xd, c, seed=seed), torch.float32)
+    near = fos.quantize(xd, fos.QuantizationConfig(dtype="if4", scale_rule="mse"))
+    mean_err = (acc / 64 - xd.float()).pow(2).mean().sqrt().item()
+    near_err = (fos.dequantize(near, torch.float32) - xd.float()).pow(2).mean().sqrt().item()
+    assert mean_err < 0.5 * near_err, (mean_err, near_err)
+    with pytest.raises(ValueError):
+        fos.quantize(xd, fos.QuantizationConfig(dtype="if4", scale_rule="mae", round_style="stochastic"))
+
+
 def _load_golden_file(name: str):
     import io
     import lzma
