@@ -123,6 +123,60 @@ __global__ void __launch_bounds__(256) allreduce_pull_kernel(const PullParams p)
     }
 }
 
+// Reduce-scatter over peer memory, for layers that hand row slabs on instead of full activations: every rank has
+// stored its partial product into its own buffer; this rank LOADS rows row0 .. row0 + rows of every rank's buffer
+// (peer loads, a warp reads 512 contiguous bytes), adds them in binary32 in rank order, rounds once and stores the
+// sums into a LOCAL buffer. Nothing is stored to a peer, so per GPU (world - 1) / world of the slab's bytes cross its
+// links inbound, once. The caller puts a barrier between the GEMMs and this kernel, and another one before any
+// rank overwrites its buffer.
+struct ReduceScatterParams {
+    const void *buf_peer[8];
+    void *out;
+    int world;
+    int64_t row0, rows, n, ld, ld_out;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_scatter_peer_kernel(const ReduceScatterParams p) {
+    constexpr int U = 2;                                   // chunks of 16 bytes per thread and round, loaded before any is used
+    const int64_t chunks_per_row = p.n >> 3, total = p.rows * chunks_per_row;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t u0 = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; u0 < total; u0 += U * stride) {
+        int64_t src[U], dst[U];
+        uint4 w[U][8];
+#pragma unroll
+        for (int q = 0; q < U; ++q) {
+            const int64_t u = u0 + q * stride;
+            const int64_t i = u / chunks_per_row, j = (u - i * chunks_per_row) * 8;
+            src[q] = u < total ? (p.row0 + i) * p.ld + j : -1;
+            dst[q] = i * p.ld_out + j;
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                if (s < p.world && src[q] >= 0)
+                    w[q][s] = *reinterpret_cast<const uint4 *>(static_cast<const T *>(p.buf_peer[s]) + src[q]);
+        }
+#pragma unroll
+        for (int q = 0; q < U; ++q) {
+            if (src[q] < 0) continue;
+            float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                if (s >= p.world) break;
+                const uint32_t v[4] = {w[q][s].x, w[q][s].y, w[q][s].z, w[q][s].w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = pair_to_float2<T>(v[k]);
+                    acc[2 * k] += f.x;
+                    acc[2 * k + 1] += f.y;
+                }
+            }
+            *reinterpret_cast<uint4 *>(static_cast<T *>(p.out) + dst[q]) =
+                make_uint4(float2_to_pair<T>(acc[0], acc[1]), float2_to_pair<T>(acc[2], acc[3]),
+                           float2_to_pair<T>(acc[4], acc[5]), float2_to_pair<T>(acc[6], acc[7]));
+        }
+    }
+}
+
 }  // namespace
 }  // namespace fos
 
@@ -177,6 +231,36 @@ extern "C" int fos_allreduce_peer(void *const *buf_peers, int world, int rank, i
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (dtype == FOS_BF16) allreduce_pull_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
     else allreduce_pull_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+    FOS_CUDA_TRY(cudaGetLastError());
+    return FOS_OK;
+}
+
+extern "C" int fos_reduce_scatter_peer(void *const *buf_peers, int world, int64_t row0, int64_t rows, int64_t n, int64_t ld,
+                                       void *out, int64_t ld_out, int dtype, int max_ctas, void *stream_) {
+    using namespace fos;
+    if (!buf_peers || !out || world < 2 || world > 8) return FOS_ERR_INVALID_ARGUMENT;
+    if (row0 < 0 || rows <= 0 || n <= 0 || ld < n || ld_out < n || max_ctas < 0) return FOS_ERR_INVALID_ARGUMENT;
+    if (dtype != FOS_BF16 && dtype != FOS_FP16) return FOS_ERR_UNSUPPORTED;
+    if (n % 8 != 0 || ld % 8 != 0 || ld_out % 8 != 0) return FOS_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(out) % 16 != 0) return FOS_ERR_MISALIGNED;
+    ReduceScatterParams p{};
+    for (int i = 0; i < world; ++i) {
+        if (!buf_peers[i]) return FOS_ERR_INVALID_ARGUMENT;
+        if (reinterpret_cast<uintptr_t>(buf_peers[i]) % 16 != 0) return FOS_ERR_MISALIGNED;
+        p.buf_peer[i] = buf_peers[i];
+    }
+    p.out = out;
+    p.world = world;
+    p.row0 = row0; p.rows = rows; p.n = n; p.ld = ld; p.ld_out = ld_out;
+    const int st = check_device();
+    if (st != FOS_OK) return st;
+    const int64_t total = rows * (n >> 3);
+    int64_t blocks = (total + 511) / 512;
+    const int64_t cap = max_ctas > 0 ? max_ctas : 148 * 8;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (dtype == FOS_BF16) reduce_scatter_peer_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+    else reduce_scatter_peer_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;
 }

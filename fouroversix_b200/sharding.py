@@ -111,10 +111,12 @@ class TensorParallelLinear(nn.Module):
     pair of B200s; with fewer free SMs part of its grid still waits for the GEMM.
     """
 
+    PEER_SCATTER_MAX_WORLD = 2      # group sizes on which the peer-memory reduce-scatter is the default
+
     def __init__(self, weight: torch.Tensor | QuantizedTensor, config: ModuleQuantizationConfig, mode: str, *,
                  group: dist.ProcessGroup | None = None, bias: torch.Tensor | None = None, chunks: int = 4,
                  comm_sms: int = 32, fused: bool | None = None, peer_mode: str = "scatter",
-                 scatter_output: bool = False, scattered_input: bool = False,
+                 scatter_output: bool = False, scattered_input: bool = False, peer_scatter: bool | None = None,
                  matmul_fn: MatmulFn | None = None,
                  quantize_fn: Callable | None = None, amax_fn: Callable | None = None) -> None:
         super().__init__()
@@ -146,6 +148,10 @@ class TensorParallelLinear(nn.Module):
         if scattered_input and mode != "column":
             raise ValueError("scattered_input belongs to a column-parallel layer")
         self.scatter_output, self.scattered_input = scatter_output, scattered_input
+        # scatter_output layers: the reduce-scatter over peer memory (fos_reduce_scatter_peer: every rank loads its
+        # slab's rows from all ranks' partial products and adds them) instead of NCCL's. None = when every rank can
+        # set the symmetric buffers up and the group is no larger than PEER_SCATTER_MAX_WORLD; True = require it.
+        self.peer_scatter = peer_scatter
         self._peer: dict | None = None
         self._matmul = matmul_fn or quantized_matmul
         self._quantize = quantize_fn or quantize
@@ -225,9 +231,20 @@ class TensorParallelLinear(nn.Module):
         n_out = self.weight.original_shape[0]
         dtype = DataType(self.config.output_dtype).torch_dtype
         xq = self._quantize(x2d, act_cfg)
-        partial = torch.empty(tokens, n_out, dtype=dtype, device=x2d.device)
-        slab = torch.empty(n_chunks * piece, n_out, dtype=dtype, device=x2d.device)
         on_gpu = x2d.device.type == "cuda"
+        # over peer memory when asked for, or when it can be had (a collective decision, taken once per shape)
+        use_peer = False
+        if (on_gpu and self.peer_scatter is not False and self._matmul is quantized_matmul and n_out % 8 == 0
+                and dtype in (torch.bfloat16, torch.float16)
+                and (self.peer_scatter or world <= self.PEER_SCATTER_MAX_WORLD)):
+            use_peer = self._agree_on_peer_buffers(tokens, n_out, dtype, x2d.device, required=bool(self.peer_scatter))
+            if not use_peer:
+                self.peer_scatter = False
+        elif self.peer_scatter:
+            raise ValueError("TensorParallelLinear: this call does not fit the peer-memory reduce-scatter")
+        partial = self._peer["out"] if use_peer else torch.empty(tokens, n_out, dtype=dtype, device=x2d.device)
+        slab = torch.empty(n_chunks * piece, n_out, dtype=dtype, device=x2d.device)
+        rank = dist.get_rank(self.group)
         works = []
         max_ctas = 0
         if on_gpu:
@@ -245,13 +262,24 @@ class TensorParallelLinear(nn.Module):
                 done.record(compute)
                 with torch.cuda.stream(self._comm_stream):
                     self._comm_stream.wait_event(done)
-                    dist.reduce_scatter_tensor(mine, part, group=self.group)
+                    if use_peer:
+                        self._peer["h_out"].barrier(channel=0)       # every rank's GEMM of this chunk is complete
+                        with torch.cuda.device(x2d.device):
+                            _native.check(_native.lib().fos_reduce_scatter_peer(
+                                self._peer["out_ptrs"], world, i * step + rank * piece, piece, n_out, n_out,
+                                mine.data_ptr(), n_out, _native.elem_code(dtype), 0,
+                                _native.stream_ptr(x2d.device)), "fos_reduce_scatter_peer")
+                    else:
+                        dist.reduce_scatter_tensor(mine, part, group=self.group)
             else:
                 works.append(dist.reduce_scatter_tensor(mine, part, group=self.group, async_op=True))
         if on_gpu:
             # the compute stream now follows everything the communication stream did, so the buffers it used
             # can be reused in stream order (no record_stream: that would keep 512 MiB blocks from the
             # allocator's free list until the side stream's events are polled)
+            if use_peer:
+                with torch.cuda.stream(self._comm_stream):
+                    self._peer["h_out"].barrier(channel=0)           # no rank overwrites its buffer while a peer reads it
             compute.wait_stream(self._comm_stream)
         for w in works:
             w.wait()
@@ -366,11 +394,33 @@ class TensorParallelLinear(nn.Module):
         out = symm.empty((tokens, n_out), dtype=dtype, device=dev)
         h_out = symm.rendezvous(out, group)
         self._peer = {"key": key, "out": out, "h_out": h_out, "out_ptrs": pointers(h_out)}
-        if self.peer_mode == "scatter":
+        if self.peer_mode == "scatter" and not self.scatter_output:
             staging = symm.empty((world, tokens // world, n_out), dtype=dtype, device=dev)
             h_staging = symm.rendezvous(staging, group)
             self._peer.update(staging=staging, h_staging=h_staging, staging_ptrs=pointers(h_staging))
         return self._peer
+
+    def _agree_on_peer_buffers(self, tokens: int, n_out: int, dtype: torch.dtype, dev: torch.device, *,
+                               required: bool) -> bool:
+        """Sets the symmetric buffers up (once per shape) and lets the ranks agree on whether ALL of them could:
+        one that falls back to NCCL while the others wait at a symmetric-memory barrier would hang the group."""
+        key = (tokens, n_out, dtype)
+        if self._peer is not None and self._peer["key"] == key:
+            return True
+        failure: Exception | None = None
+        try:
+            self._peer_buffers(tokens, n_out, dtype, dev)
+        except Exception as exc:                           # symmetric memory is not available here
+            failure = exc
+        ok = torch.tensor([0 if failure else 1], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            self._peer = None
+            if required:
+                raise RuntimeError("TensorParallelLinear: the peer-memory exchange could not be set up on every "
+                                   "rank") from failure
+            return False
+        return True
 
     def _row_parallel_fused(self, x2d: torch.Tensor, act_cfg: QuantizationConfig) -> torch.Tensor | None:
         """The exchange over peer memory, in one of two forms (`peer_mode`). "pull": the GEMM stores this rank's
@@ -399,22 +449,9 @@ class TensorParallelLinear(nn.Module):
         # Every rank must take the same path: one that falls back to NCCL while the others wait at a
         # symmetric-memory barrier would hang the group. So the ranks agree (once per shape) on whether
         # ALL of them could set the buffers up.
-        key = (tokens, n_out, out_dtype.torch_dtype)
-        if self._peer is None or self._peer["key"] != key:
-            failure: Exception | None = None
-            try:
-                self._peer_buffers(tokens, n_out, out_dtype.torch_dtype, x2d.device)
-            except Exception as exc:                       # symmetric memory is not available here
-                failure = exc
-            ok = torch.tensor([0 if failure else 1], dtype=torch.int32, device=x2d.device)
-            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
-            if int(ok.item()) == 0:
-                self._peer = None
-                if self.fused:
-                    raise RuntimeError("TensorParallelLinear: the peer-memory exchange could not be set up on every "
-                                       "rank") from failure
-                self.fused = False
-                return None
+        if not self._agree_on_peer_buffers(tokens, n_out, out_dtype.torch_dtype, x2d.device, required=bool(self.fused)):
+            self.fused = False
+            return None
         buf = self._peer
         rank = dist.get_rank(self.group)
         xq = self._quantize(x2d, act_cfg)

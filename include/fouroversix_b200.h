@@ -318,6 +318,19 @@ int fos_allreduce_peer(void *const *buf_peers, int world, int rank, int64_t rows
                        int dtype, void *stream);
 
 /*
+ * Reduce-scatter over peer memory, for a row-parallel layer that hands ROW SLABS on to the next layer instead of
+ * the full activation: every rank has stored its partial product into its own buffer buf_peers[rank] ([.][ld],
+ * bf16 or fp16); the caller's rank loads rows row0 .. row0 + rows of EVERY rank's buffer (peer loads), adds them
+ * in binary32 in rank order, rounds once and stores the sums into its LOCAL buffer out[rows][ld_out]. Nothing is
+ * stored to a peer: (world - 1) / world of the slab's bytes cross this GPU's links inbound, once. n, ld, ld_out
+ * multiples of 8. max_ctas > 0 caps the grid (the kernel usually runs beside the next chunk's GEMM). A barrier
+ * between the ranks (in stream order) is needed after the GEMMs that filled the buffers and before any rank
+ * overwrites its buffer. No counterpart in the reference (see fos_gemm_nvfp4_scatter).
+ */
+int fos_reduce_scatter_peer(void *const *buf_peers, int world, int64_t row0, int64_t rows, int64_t n, int64_t ld,
+                            void *out, int64_t ld_out, int dtype, int max_ctas, void *stream);
+
+/*
  * D[m, n] = alpha[0] * sum_k A[m, k] * B[n, k] for operands in FOS_IF4 or FOS_NVFP4 (any mix),
  * scales in either layout. Each element is expanded to fp16(value) * fp16(|scale|) (integer
  * blocks: fp16(int * 6/7) first), the fp16 matrices are multiplied on the tensor cores

@@ -108,6 +108,17 @@ def _worker(rank: int, world: int, port: int, results):
                                    scattered_input=True)
         slab = down_s(h)
         out["slab"] = ((slab.float() - scatter_rows(want, rank, world, chunks)).abs().max() / scale).item()
+        # the same reduce-scatter over peer memory (every rank loads its slab's rows from all partial products)
+        down_p = TensorParallelLinear(w_down_shard, cfg, "row", chunks=chunks, scatter_output=True, peer_scatter=True)
+        down_n = TensorParallelLinear(w_down_shard, cfg, "row", chunks=chunks, scatter_output=True, peer_scatter=False)
+        try:
+            p1 = down_p(h).clone()
+            p2 = down_p(h).clone()                                # the symmetric buffer is reused
+            out["slab_peer"] = (((p1.float() - scatter_rows(want, rank, world, chunks)).abs().max() / scale).item(),
+                                torch.equal(p1, p2))
+        except RuntimeError as exc:                               # every rank raises together (collective decision)
+            out["slab_peer"] = f"unavailable: {str(exc)[:120]}"
+        out["slab_nccl"] = ((down_n(h).float() - scatter_rows(want, rank, world, chunks)).abs().max() / scale).item()
         slabs = [torch.empty_like(slab) for _ in range(world)]
         dist.all_gather(slabs, slab)
         full = gather_rows(slabs, chunks)
@@ -189,6 +200,9 @@ def test_column_then_row_parallel(world):
             assert err < 2e-2, (mode, err)
             assert repeatable and same, mode
         assert out["slab"] < 2e-2, out["slab"]
+        assert out["slab_nccl"] < 2e-2, out["slab_nccl"]
+        if not isinstance(out["slab_peer"], str):
+            assert out["slab_peer"][0] < 2e-2 and out["slab_peer"][1], out["slab_peer"]
         assert out["packed_equal"], "slabs quantized with the common amax must equal the unsharded quantization"
         assert out["next_equal"]
         assert out["rows_equal"]
