@@ -535,7 +535,7 @@ def gemm_section(args, fos, B200MatmulBackend, dev, rank, world, peaks):
 
 
 STACK_TOKENS = 16 * 2048
-HANDOFF_ROW_CHUNKS, HANDOFF_COL_CHUNKS, HANDOFF_COMM_SMS = 2, 2, 32      # settings of the row-slab hand-off in the stack
+HANDOFF_ROW_CHUNKS, HANDOFF_COL_CHUNKS, HANDOFF_COMM_SMS = 4, 2, 32      # settings of the row-slab hand-off in the stack
 STACK_LAYERS = (  # name, parallelism, out features N, in features K: the linear layers of one Llama-3-70B decoder block
     ("qkv_proj", "column", 10240, 8192),
     ("o_proj", "row", 8192, 8192),
@@ -571,7 +571,8 @@ def stack_section(args, fos, dev, rank, world):
             ms = float(t.item())
         return ms
 
-    def run(handoff: bool, row_chunks: int = HANDOFF_ROW_CHUNKS, col_chunks: int = HANDOFF_COL_CHUNKS, comm_sms: int = HANDOFF_COMM_SMS):
+    def run(handoff: bool, row_chunks: int = HANDOFF_ROW_CHUNKS, col_chunks: int = HANDOFF_COL_CHUNKS, comm_sms: int = HANDOFF_COMM_SMS,
+            peer_scatter: bool | None = None):
         layers, total_ms, total_flop = {}, 0.0, 0.0
         for idx, (name, mode, n, k) in enumerate(STACK_LAYERS):
             g = torch.Generator(device=dev).manual_seed(12 + idx + 100 * rank)
@@ -588,6 +589,8 @@ def stack_section(args, fos, dev, rank, world):
             if handoff:
                 kw = dict(scattered_input=True) if mode == "column" else dict(scatter_output=True)
             if handoff:
+                if mode == "row":
+                    kw["peer_scatter"] = peer_scatter
                 layer = TensorParallelLinear(w, cfg, mode, chunks=col_chunks if mode == "column" else row_chunks,
                                              comm_sms=comm_sms, **kw)
             else:
@@ -616,10 +619,11 @@ def stack_section(args, fos, dev, rank, world):
     layers, total_ms, total_flop = run(handoff=world > 1)
     variants = {}
     if world > 1 and os.environ.get("FOS_STACK_VARIANTS"):
-        # tuning aid: "row_chunks:col_chunks:comm_sms,..." - the hand-off form with other settings, same process
+        # tuning aid: "row_chunks:col_chunks:comm_sms:peer,..." - the hand-off form with other settings, same process
+        # (peer: 1 = reduce-scatter over peer memory, 0 = NCCL)
         for spec in os.environ["FOS_STACK_VARIANTS"].split(","):
-            rc, cc, sm = (int(v) for v in spec.split(":"))
-            v_layers, v_ms, _ = run(True, rc, cc, sm)
+            rc, cc, sm, peer = (int(v) for v in spec.split(":"))
+            v_layers, v_ms, _ = run(True, rc, cc, sm, bool(peer))
             variants[spec] = {"ms": round(v_ms, 4), "layers": {k: round(v["ms"], 4) for k, v in v_layers.items()}}
     out = {
         "tokens": STACK_TOKENS, "n_gpus": world, "layers": layers, "ms": total_ms,

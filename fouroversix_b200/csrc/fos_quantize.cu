@@ -830,8 +830,9 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
         sf_byte = sfb_a | (take_int ? 0x80u : 0u);
         return;
     }
-    const bool if4_eligible = KIND == KIND_IF4 && !TWO_D && ea.w >= 0.0f && __fmul_rn(bmax, r_a) <= 6.42f;
+    const bool if4_eligible = KIND == KIND_IF4 && ea.w >= 0.0f && __fmul_rn(bmax, r_a) <= 6.42f;
     bool if4_decided = false, pick_int_fast = false;
+    float row_f = 0.0f, row_i = 0.0f;                  // 2-D: this row's share of the block's sums
     uint32_t cf[2] = {0u, 0u};
     if (if4_eligible) {
         const uint64_t r2 = pack2(r_a, r_a), zero2 = pack2(0.0f, 0.0f), one2 = pack2(1.0f, 1.0f), minus2 = pack2(-1.0f, -1.0f);
@@ -857,15 +858,36 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
         unpack2f(acc_f, f0, f1);
         unpack2f(acc_i, i0, i1);
         const float from_int = 0.8571428571f;
-        const float s_f = f0 + f1, s_i = (i0 + i1) * (from_int * from_int);
-        const float tau = 0x1p-24f * 1.5f * (360.0f * s_i + 228.0f * s_f + 508.0f);
-        const float diff = s_i - s_f;
-        if4_decided = fabsf(diff) > tau;
+        float s_f = f0 + f1, s_i = (i0 + i1) * (from_int * from_int);
+        if (!TWO_D) {
+            const float tau = 0x1p-24f * 1.5f * (360.0f * s_i + 228.0f * s_f + 508.0f);
+            const float diff = s_i - s_f;
+            if4_decided = fabsf(diff) > tau;
+            pick_int_fast = diff < 0.0f;
+        } else {
+            row_f = s_f;
+            row_i = s_i;
+        }
+    }
+    if (KIND == KIND_IF4 && TWO_D) {
+        // 16 x 16 blocks: the 16 lanes that hold a block's rows add their row sums (any order: this is the estimate).
+        // Same per-element bounds over 256 terms: 2 * 80u * 16 * sqrt(S_i) <= 1280u * (S_i + 1) and
+        // 2 * 47u * 16 * sqrt(S_f) <= 752u * (S_f + 1), plus 100u relative for the roundings of the 256-term
+        // summations. The block's lanes share the scale, so eligibility is uniform over them; the exact path below
+        // is collective over the warp, so it is taken by the whole warp as soon as one of its two blocks needs it.
+#pragma unroll
+        for (int sh = 0; sh < 4; ++sh) {
+            row_f += __shfl_xor_sync(FULL, row_f, LaneMap<TWO_D, TRANSPOSED>::XOR0 << sh);
+            row_i += __shfl_xor_sync(FULL, row_i, LaneMap<TWO_D, TRANSPOSED>::XOR0 << sh);
+        }
+        const float tau = 0x1p-24f * 1.5f * (1380.0f * row_i + 852.0f * row_f + 2032.0f);
+        const float diff = row_i - row_f;
         pick_int_fast = diff < 0.0f;
+        if4_decided = __all_sync(FULL, if4_eligible && fabsf(diff) > tau);
     }
     // undecided blocks (ties, mostly): the whole warp evaluates one block at a time exactly, lane
     // 16c + i taking element i under candidate c (0: float grid, 1: integer grid), as for NVFP4
-    if (KIND == KIND_IF4 && coop != nullptr) {
+    if (KIND == KIND_IF4 && !TWO_D && coop != nullptr) {
         unsigned pending = __ballot_sync(FULL, if4_eligible && !if4_decided);
         while (pending) {
             const int src = __ffs(pending) - 1;
