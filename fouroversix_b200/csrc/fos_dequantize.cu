@@ -25,37 +25,41 @@ struct DequantParams {
 // flight instead of one (with one, the kernel waited a memory latency per run: 29 us for 8192 x 4096).
 constexpr int DEQUANT_DEPTH = 4;
 
-template <typename OUT>
+// SMALL: every offset (bytes of codes and scales, elements of the output) fits 32 bits, so the address arithmetic
+// of a block is 32-bit (a third of the kernel's instructions were 64-bit multiplies and compares).
+template <typename OUT, bool SMALL>
 __global__ void __launch_bounds__(256) dequantize_kernel(const DequantParams p) {
+    using idx_t = typename std::conditional<SMALL, uint32_t, int64_t>::type;
     const int n_cb = static_cast<int>(p.cols_p >> 4);
     const int cb_used = static_cast<int>((p.cols + 15) >> 4);
     const int chunks = (cb_used + 255) >> 8;
-    const int64_t units = p.rows * chunks;
+    const idx_t units = static_cast<idx_t>(p.rows * chunks);
     const DequantConsts k = dequant_consts(__ldg(p.amax), p.divisor);
     // a unit is (row, chunk of 256 blocks); this CTA's units are blockIdx.x, + gridDim.x, ...: the pair is advanced
     // by additions (a division per unit cost more than decoding it)
     const int step_r = static_cast<int>(gridDim.x) / chunks, step_c = static_cast<int>(gridDim.x) % chunks;
-    int64_t row0 = static_cast<int64_t>(blockIdx.x) / chunks;
+    idx_t row0 = static_cast<idx_t>(blockIdx.x) / static_cast<idx_t>(chunks);
     int ch0 = static_cast<int>(blockIdx.x - row0 * chunks);
-    const int64_t code_ld = p.cols_p >> 1;
-    for (int64_t u0 = blockIdx.x; u0 < units; u0 += static_cast<int64_t>(gridDim.x) * DEQUANT_DEPTH) {
+    const idx_t code_ld = static_cast<idx_t>(p.cols_p >> 1), ld_out = static_cast<idx_t>(p.ld_out);
+    for (idx_t u0 = blockIdx.x; u0 < units; u0 += static_cast<idx_t>(gridDim.x) * DEQUANT_DEPTH) {
         uint2 c[DEQUANT_DEPTH];
         uint32_t sfb[DEQUANT_DEPTH];
-        int64_t row[DEQUANT_DEPTH];
+        idx_t row[DEQUANT_DEPTH];
         int col_block[DEQUANT_DEPTH];
 #pragma unroll
         for (int d = 0; d < DEQUANT_DEPTH; ++d) {
-            const int64_t r = row0;
+            const idx_t r = row0;
             const int cb = ch0 * 256 + static_cast<int>(threadIdx.x);
             row[d] = r;
-            col_block[d] = (u0 + static_cast<int64_t>(d) * gridDim.x < units && cb < cb_used) ? cb : -1;
+            col_block[d] = (u0 + static_cast<idx_t>(d) * gridDim.x < units && cb < cb_used) ? cb : -1;
             c[d] = make_uint2(0u, 0u);
             sfb[d] = 0u;
             if (col_block[d] >= 0) {
                 c[d] = *reinterpret_cast<const uint2 *>(p.codes + r * code_ld + cb * 8);
-                const int64_t sf_off = p.sf_tiled
-                    ? ((r >> 7) * (n_cb >> 2) + (cb >> 2)) * 512 + ((static_cast<int>(r) & 31) * 16 + ((static_cast<int>(r) >> 5) & 3) * 4 + (cb & 3))
-                    : r * n_cb + cb;
+                const idx_t sf_off = p.sf_tiled
+                    ? ((r >> 7) * static_cast<idx_t>(n_cb >> 2) + static_cast<idx_t>(cb >> 2)) * 512 +
+                          static_cast<idx_t>((static_cast<int>(r) & 31) * 16 + ((static_cast<int>(r) >> 5) & 3) * 4 + (cb & 3))
+                    : r * static_cast<idx_t>(n_cb) + static_cast<idx_t>(cb);
                 sfb[d] = p.sf[sf_off];
             }
             row0 += step_r;                      // the next unit of this CTA
@@ -66,7 +70,7 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantParams p) 
         for (int d = 0; d < DEQUANT_DEPTH; ++d) {
             const int cb = col_block[d];
             if (cb < 0) continue;
-            OUT *dst = static_cast<OUT *>(p.out) + row[d] * p.ld_out + cb * 16;
+            OUT *dst = static_cast<OUT *>(p.out) + (row[d] * ld_out + static_cast<idx_t>(cb * 16));
             const int64_t left = p.cols - static_cast<int64_t>(cb) * 16;
             if constexpr (sizeof(OUT) == 2) {
                 // NVFP4 to bf16 / fp16: the whole block from two quotients and a byte-permute table
@@ -214,9 +218,17 @@ extern "C" int fos_dequantize(const uint8_t *codes, const uint8_t *sf, const flo
     int64_t blocks = units;
     if (blocks > 148 * 8) blocks = 148 * 8;
     const unsigned g = static_cast<unsigned>(blocks);
-    if (out_dtype == FOS_BF16) dequantize_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(p);
-    else if (out_dtype == FOS_FP16) dequantize_kernel<__half><<<g, 256, 0, stream>>>(p);
-    else dequantize_kernel<float><<<g, 256, 0, stream>>>(p);
+    // 32-bit offsets when the padded tensor has fewer than 2^31 elements and the output fits the same bound
+    const bool small = rows_p * cols_p < (int64_t(1) << 31) && rows * ld_out < (int64_t(1) << 31) && units + 4 * blocks < (int64_t(1) << 31);
+    if (small) {
+        if (out_dtype == FOS_BF16) dequantize_kernel<__nv_bfloat16, true><<<g, 256, 0, stream>>>(p);
+        else if (out_dtype == FOS_FP16) dequantize_kernel<__half, true><<<g, 256, 0, stream>>>(p);
+        else dequantize_kernel<float, true><<<g, 256, 0, stream>>>(p);
+    } else {
+        if (out_dtype == FOS_BF16) dequantize_kernel<__nv_bfloat16, false><<<g, 256, 0, stream>>>(p);
+        else if (out_dtype == FOS_FP16) dequantize_kernel<__half, false><<<g, 256, 0, stream>>>(p);
+        else dequantize_kernel<float, false><<<g, 256, 0, stream>>>(p);
+    }
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;
 }
