@@ -97,7 +97,11 @@ quantize_mx_kernel(const MxParams p) {
     const int64_t x_it = 32 * p.ld, code_it = 32 * code_ld, sf_it = p.sf_tiled ? 4 : 32 * n_cb;
 
     for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-        const int64_t i0 = (t / tiles_c) * MX_TILE, j0 = (t % tiles_c) * MX_TILE;   // tile origin in Y
+        // tile origin in Y (a 32-bit division when the tile count allows it, which is always in practice: the
+        // 64-bit form costs about as much as quantizing one of the thread's four runs)
+        const int64_t t_row = n_tiles < (int64_t(1) << 31) ? static_cast<int64_t>(static_cast<uint32_t>(t) / static_cast<uint32_t>(tiles_c))
+                                                          : t / tiles_c;
+        const int64_t i0 = t_row * MX_TILE, j0 = (t - t_row * tiles_c) * MX_TILE;
 
         if constexpr (STAGED) {
             // copy the tile of Y into shared memory; global reads run along x's rows either way
