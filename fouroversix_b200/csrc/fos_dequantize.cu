@@ -139,7 +139,9 @@ __global__ void __launch_bounds__(256) dequantize_general_kernel(const GeneralDe
     OUT *out = static_cast<OUT *>(p.out);
     for (int64_t u = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; u < total;
          u += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t r = u / runs_per_row, col = (u - r * runs_per_row) * 16;
+        const int64_t r = total < (int64_t(1) << 31) ? static_cast<int64_t>(static_cast<uint32_t>(u) / static_cast<uint32_t>(runs_per_row))
+                                                     : u / runs_per_row;
+        const int64_t col = (u - r * runs_per_row) * 16;
         const uint2 c = *reinterpret_cast<const uint2 *>(p.codes + r * (p.cols_p >> 1) + (col >> 1));
         uint32_t sfb = p.sf[sf_offset(r, col / block, n_cb, p.sf_tiled != 0)];
         const bool is_int = p.format == FOS_IF4 && (sfb & 0x80u);

@@ -240,7 +240,10 @@ dequantize_mx_kernel(const MxDequantParams p) {
     OUT *out = static_cast<OUT *>(p.out);
     for (int64_t u = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; u < total;
          u += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t i = u / runs_per_row, j = (u % runs_per_row) * 16;
+        // (32-bit division whenever the run count allows it: the 64-bit form is a large part of this kernel)
+        const int64_t i = total < (int64_t(1) << 31) ? static_cast<int64_t>(static_cast<uint32_t>(u) / static_cast<uint32_t>(runs_per_row))
+                                                     : u / runs_per_row;
+        const int64_t j = (u - i * runs_per_row) * 16;
         const uint2 c = *reinterpret_cast<const uint2 *>(p.codes + i * (p.cols_p / 2) + j / 2);
         const uint32_t e = p.sf[sf_offset(i, j >> 5, n_cb, p.sf_tiled != 0)];
         // E8M0 -> fp16 as a conversion of the binary32 value: inf above 2^15, 0 below 2^-25, NaN for 255
