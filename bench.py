@@ -48,7 +48,7 @@ BYTES_PER_ELEM = 2.0 + 0.5 + 1.0 / 16.0
 N_ROTATE = 4
 NOMINAL_FP4_TFLOPS = 9000.0
 # DRAM bytes (read + write) of one launch of the quantize kernel on the 8192x4096 tensor: a constant taken from one
-# ncu capture of that kernel (67.16 MB read + 3.05 MB written; the rest of the output is still in L2 when the kernel
+# ncu capture of that kernel (67.15 MB read + 3.25 MB written; the rest of the output is still in L2 when the kernel
 # ends), not something this script can measure while it runs
 QUANTIZE_KERNEL_DRAM_BYTES = 70.40e6
 WORKLOAD = "quantize A 8192x4096 bf16 (N(0,1), 1% K-channels x20) to NVFP4 4/6-MSE, 1x16 blocks (one A per GPU)"
