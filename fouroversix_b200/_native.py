@@ -79,6 +79,7 @@ SIGNATURES = {
                                         _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
     "fos_allreduce_peer": (_c_int, [_c_ptr, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_ptr]),
     "fos_reduce_scatter_peer": (_c_int, [_c_ptr, _c_int, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_i64, _c_int, _c_int, _c_ptr]),
+    "fos_allgather_peer": (_c_int, [_c_ptr, _c_int, _c_i64, _c_i64, _c_ptr, _c_int, _c_ptr]),
     "fos_reduce_gather": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_ptr]),
     "fos_gemm_if4_workspace_bytes": (_c_i64, [_c_i64, _c_i64, _c_i64]),
     "fos_gemm_if4": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int,

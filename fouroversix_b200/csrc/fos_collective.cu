@@ -177,6 +177,40 @@ __global__ void __launch_bounds__(256) reduce_scatter_peer_kernel(const ReduceSc
     }
 }
 
+// All-gather over peer memory: every rank holds its piece (`bytes` bytes at byte offset src_off of its buffer);
+// this rank copies all pieces, in rank order, into a LOCAL buffer: dst[r * bytes ..] = buf_peer[r][src_off ..].
+// Plain 16-byte peer loads, four in flight per thread; nothing is stored to a peer.
+struct AllGatherParams {
+    const void *buf_peer[8];
+    void *dst;
+    int world;
+    int64_t src_off, bytes;
+};
+
+__global__ void __launch_bounds__(256) allgather_peer_kernel(const AllGatherParams p) {
+    constexpr int U = 4;
+    const int64_t per_rank = p.bytes >> 4, total = per_rank * p.world;      // 16-byte chunks
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t u0 = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; u0 < total; u0 += U * stride) {
+        uint4 w[U];
+#pragma unroll
+        for (int q = 0; q < U; ++q) {
+            const int64_t u = u0 + q * stride;
+            if (u < total) {
+                // (total < 2^31 chunks is checked on the host: a 32-bit division)
+                const uint32_t r = static_cast<uint32_t>(u) / static_cast<uint32_t>(per_rank);
+                const int64_t c = u - static_cast<int64_t>(r) * per_rank;
+                w[q] = *reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(p.buf_peer[r]) + p.src_off + (c << 4));
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < U; ++q) {
+            const int64_t u = u0 + q * stride;
+            if (u < total) *reinterpret_cast<uint4 *>(static_cast<uint8_t *>(p.dst) + (u << 4)) = w[q];
+        }
+    }
+}
+
 }  // namespace
 }  // namespace fos
 
@@ -261,6 +295,34 @@ extern "C" int fos_reduce_scatter_peer(void *const *buf_peers, int world, int64_
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (dtype == FOS_BF16) reduce_scatter_peer_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
     else reduce_scatter_peer_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+    FOS_CUDA_TRY(cudaGetLastError());
+    return FOS_OK;
+}
+
+extern "C" int fos_allgather_peer(void *const *buf_peers, int world, int64_t src_off, int64_t bytes, void *dst,
+                                  int max_ctas, void *stream_) {
+    using namespace fos;
+    if (!buf_peers || !dst || world < 2 || world > 8 || src_off < 0 || bytes <= 0 || max_ctas < 0) return FOS_ERR_INVALID_ARGUMENT;
+    if (bytes % 16 != 0 || src_off % 16 != 0) return FOS_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(dst) % 16 != 0) return FOS_ERR_MISALIGNED;
+    if ((bytes >> 4) * world >= (int64_t(1) << 31)) return FOS_ERR_TOO_LARGE;
+    AllGatherParams p{};
+    for (int i = 0; i < world; ++i) {
+        if (!buf_peers[i]) return FOS_ERR_INVALID_ARGUMENT;
+        if (reinterpret_cast<uintptr_t>(buf_peers[i]) % 16 != 0) return FOS_ERR_MISALIGNED;
+        p.buf_peer[i] = buf_peers[i];
+    }
+    p.dst = dst;
+    p.world = world;
+    p.src_off = src_off;
+    p.bytes = bytes;
+    const int st = check_device();
+    if (st != FOS_OK) return st;
+    const int64_t total = (bytes >> 4) * world;
+    int64_t blocks = (total + 1023) / 1024;
+    const int64_t cap = max_ctas > 0 ? max_ctas : 148 * 8;
+    if (blocks > cap) blocks = cap;
+    allgather_peer_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream_)>>>(p);
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;
 }

@@ -117,7 +117,7 @@ class TensorParallelLinear(nn.Module):
                  group: dist.ProcessGroup | None = None, bias: torch.Tensor | None = None, chunks: int = 4,
                  comm_sms: int = 32, fused: bool | None = None, peer_mode: str = "scatter",
                  scatter_output: bool = False, scattered_input: bool = False, peer_scatter: bool | None = None,
-                 matmul_fn: MatmulFn | None = None,
+                 peer_gather: bool | None = None, matmul_fn: MatmulFn | None = None,
                  quantize_fn: Callable | None = None, amax_fn: Callable | None = None) -> None:
         super().__init__()
         if mode not in ("column", "row"):
@@ -152,6 +152,10 @@ class TensorParallelLinear(nn.Module):
         # slab's rows from all ranks' partial products and adds them) instead of NCCL's. None = when every rank can
         # set the symmetric buffers up and the group is no larger than PEER_SCATTER_MAX_WORLD; True = require it.
         self.peer_scatter = peer_scatter
+        # scattered_input layers: the all-gather of the packed slabs over peer memory (fos_allgather_peer: every rank
+        # copies all ranks' pieces out of their symmetric buffers) instead of NCCL's. None / True / False as above.
+        self.peer_gather = peer_gather
+        self._gather_peer: dict | None = None
         self._peer: dict | None = None
         self._matmul = matmul_fn or quantized_matmul
         self._quantize = quantize_fn or quantize
@@ -325,12 +329,30 @@ class TensorParallelLinear(nn.Module):
         per_row = k_p // 16                                  # scale bytes per row; 128-row groups are contiguous
         on_gpu = slab.device.type == "cuda"
         events = []
+        # over peer memory when asked for, or when it can be had (a collective decision, taken once per shape)
+        use_peer = False
+        if on_gpu and self.peer_gather is not False and self._quantize is quantize and q.values.shape[0] == rows:
+            use_peer = self._agree_on_gather_buffers(rows, k_p, slab.device, required=bool(self.peer_gather))
+            if not use_peer:
+                self.peer_gather = False
+        elif self.peer_gather:
+            raise ValueError("TensorParallelLinear: this call does not fit the peer-memory all-gather")
         if on_gpu:
             if self._comm_stream is None:
                 self._comm_stream = torch.cuda.Stream(device=slab.device)
+            compute = torch.cuda.current_stream(slab.device)
+            if use_peer:
+                gp = self._gather_peer
+                if gp["free"] is not None:
+                    compute.wait_event(gp["free"])           # every rank has finished reading the previous slab
+                gp["codes"].copy_(q.values)
+                gp["scales"].copy_(sf_local)
             ready = torch.cuda.Event()
-            ready.record(torch.cuda.current_stream(slab.device))
+            ready.record(compute)
             self._comm_stream.wait_event(ready)
+            if use_peer:
+                with torch.cuda.stream(self._comm_stream):
+                    gp["h_codes"].barrier(channel=0)         # every rank's packed slab is in its symmetric buffer
         for i in range(n_chunks):
             src_codes = q.values[i * piece: (i + 1) * piece]
             src_sf = sf_local[i * piece * per_row: (i + 1) * piece * per_row]
@@ -338,14 +360,29 @@ class TensorParallelLinear(nn.Module):
             dst_sf = scales[i * step * per_row: (i + 1) * step * per_row]
             if on_gpu:
                 with torch.cuda.stream(self._comm_stream):
-                    dist.all_gather_into_tensor(dst_codes, src_codes, group=self.group)
-                    dist.all_gather_into_tensor(dst_sf, src_sf, group=self.group)
+                    if use_peer:
+                        with torch.cuda.device(slab.device):
+                            lib, stream = _native.lib(), _native.stream_ptr(slab.device)
+                            _native.check(lib.fos_allgather_peer(
+                                gp["codes_ptrs"], world, i * piece * (k_p // 2), piece * (k_p // 2),
+                                dst_codes.data_ptr(), 0, stream), "fos_allgather_peer")
+                            _native.check(lib.fos_allgather_peer(
+                                gp["scales_ptrs"], world, i * piece * per_row, piece * per_row,
+                                dst_sf.data_ptr(), 0, stream), "fos_allgather_peer")
+                    else:
+                        dist.all_gather_into_tensor(dst_codes, src_codes, group=self.group)
+                        dist.all_gather_into_tensor(dst_sf, src_sf, group=self.group)
                     ev = torch.cuda.Event()
                     ev.record(self._comm_stream)
                 events.append(ev)
             else:
                 dist.all_gather_into_tensor(dst_codes, src_codes.contiguous(), group=self.group)
                 dist.all_gather_into_tensor(dst_sf, src_sf.contiguous(), group=self.group)
+        if use_peer:
+            with torch.cuda.stream(self._comm_stream):
+                gp["h_codes"].barrier(channel=0)             # nobody overwrites its slab while a peer still reads it
+                gp["free"] = torch.cuda.Event()
+                gp["free"].record(self._comm_stream)
         # (callers wait for the last event on the compute stream before they return, which orders every later
         # use of these buffers after the gathers)
         xq = QuantizedTensor(codes, scales.view(q.scale_factors.dtype), amax, q.dtype, (tokens, k), q.scale_rule,
@@ -399,6 +436,44 @@ class TensorParallelLinear(nn.Module):
             h_staging = symm.rendezvous(staging, group)
             self._peer.update(staging=staging, h_staging=h_staging, staging_ptrs=pointers(h_staging))
         return self._peer
+
+    def _agree_on_gather_buffers(self, rows: int, k_p: int, dev: torch.device, *, required: bool) -> bool:
+        """Symmetric buffers for this rank's packed slab (codes [rows, k_p / 2], scales rows * k_p / 16 bytes), set up
+        once per shape; the ranks agree on whether ALL of them could (see _agree_on_peer_buffers)."""
+        key = (rows, k_p)
+        if self._gather_peer is not None and self._gather_peer["key"] == key:
+            return True
+        failure: Exception | None = None
+        buf: dict | None = None
+        try:
+            import ctypes
+
+            import torch.distributed._symmetric_memory as symm
+
+            world = self.world_size
+            group = self.group if self.group is not None else dist.group.WORLD
+
+            def pointers(handle):
+                return (ctypes.c_void_p * world)(*[int(ptr) for ptr in handle.buffer_ptrs])
+
+            codes = symm.empty((rows, k_p // 2), dtype=torch.uint8, device=dev)
+            h_codes = symm.rendezvous(codes, group)
+            scales = symm.empty((rows * k_p // 16,), dtype=torch.uint8, device=dev)
+            h_scales = symm.rendezvous(scales, group)
+            buf = {"key": key, "codes": codes, "h_codes": h_codes, "codes_ptrs": pointers(h_codes),
+                   "scales": scales, "h_scales": h_scales, "scales_ptrs": pointers(h_scales), "free": None}
+        except Exception as exc:                           # symmetric memory is not available here
+            failure = exc
+        ok = torch.tensor([0 if failure else 1], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            self._gather_peer = None
+            if required:
+                raise RuntimeError("TensorParallelLinear: the peer-memory all-gather could not be set up on every "
+                                   "rank") from failure
+            return False
+        self._gather_peer = buf
+        return True
 
     def _agree_on_peer_buffers(self, tokens: int, n_out: int, dtype: torch.dtype, dev: torch.device, *,
                                required: bool) -> bool:

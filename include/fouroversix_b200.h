@@ -331,6 +331,16 @@ int fos_reduce_scatter_peer(void *const *buf_peers, int world, int64_t row0, int
                             void *out, int64_t ld_out, int dtype, int max_ctas, void *stream);
 
 /*
+ * All-gather over peer memory, for the packed row slabs of the hand-off: every rank holds its piece (`bytes` bytes
+ * at byte offset src_off of its buffer buf_peers[rank]); the caller's rank copies all pieces in rank order into
+ * its LOCAL buffer, dst[r * bytes ..] = buf_peers[r][src_off ..] (peer loads only). bytes and src_off multiples of
+ * 16. A barrier between the ranks (in stream order) is needed after the pieces were written and before any rank
+ * overwrites its piece. No counterpart in the reference.
+ */
+int fos_allgather_peer(void *const *buf_peers, int world, int64_t src_off, int64_t bytes, void *dst, int max_ctas,
+                       void *stream);
+
+/*
  * D[m, n] = alpha[0] * sum_k A[m, k] * B[n, k] for operands in FOS_IF4 or FOS_NVFP4 (any mix),
  * scales in either layout. Each element is expanded to fp16(value) * fp16(|scale|) (integer
  * blocks: fp16(int * 6/7) first), the fp16 matrices are multiplied on the tensor cores

@@ -127,8 +127,14 @@ def _worker(rank: int, world: int, port: int, results):
         out["packed_equal"] = (torch.equal(xq.values.cpu(), ref.values) and torch.equal(xq.amax.cpu(), ref.amax)
                                and torch.equal(xq.scale_factors.view(torch.uint8).flatten().cpu(), ref.scale_factors))
         z = nxt(slab)
+        z2 = nxt(slab)                                                # the symmetric slab buffers are reused
         z_want = fos.quantized_matmul(full, shard_linear_weight(w_next, "column", rank, world))
-        out["next_equal"] = torch.equal(z, z_want)
+        out["next_equal"] = torch.equal(z, z_want) and torch.equal(z2, z_want)
+        # the same gather over NCCL
+        nxt_n = TensorParallelLinear(shard_linear_weight(w_next, "column", rank, world), cfg, "column", chunks=chunks,
+                                     scattered_input=True, peer_gather=False)
+        out["next_equal_nccl"] = torch.equal(nxt_n(slab), z_want)
+        out["gather_over_peer_memory"] = nxt._gather_peer is not None
 
         # shard-after-quantize: slices of one quantized weight reproduce the unsharded GEMM exactly
         qw = fos.quantize(w_up)
@@ -204,7 +210,7 @@ def test_column_then_row_parallel(world):
         if not isinstance(out["slab_peer"], str):
             assert out["slab_peer"][0] < 2e-2 and out["slab_peer"][1], out["slab_peer"]
         assert out["packed_equal"], "slabs quantized with the common amax must equal the unsharded quantization"
-        assert out["next_equal"]
+        assert out["next_equal"] and out["next_equal_nccl"]
         assert out["rows_equal"]
         assert out["k_err"] < 1e-5, out["k_err"]
         assert out["two_streams_equal"], "two layers on two streams must equal their serial results"
