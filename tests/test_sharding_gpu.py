@@ -130,11 +130,13 @@ def _worker(rank: int, world: int, port: int, results):
         z2 = nxt(slab)                                                # the symmetric slab buffers are reused
         z_want = fos.quantized_matmul(full, shard_linear_weight(w_next, "column", rank, world))
         out["next_equal"] = torch.equal(z, z_want) and torch.equal(z2, z_want)
-        # the same gather over NCCL
-        nxt_n = TensorParallelLinear(shard_linear_weight(w_next, "column", rank, world), cfg, "column", chunks=chunks,
-                                     scattered_input=True, peer_gather=False)
-        out["next_equal_nccl"] = torch.equal(nxt_n(slab), z_want)
-        out["gather_over_peer_memory"] = nxt._gather_peer is not None
+        # the same gather over peer memory (NCCL's is the default: it measured faster)
+        nxt_p = TensorParallelLinear(shard_linear_weight(w_next, "column", rank, world), cfg, "column", chunks=chunks,
+                                     scattered_input=True, peer_gather=True)
+        try:
+            out["next_equal_peer"] = torch.equal(nxt_p(slab), z_want) and torch.equal(nxt_p(slab), z_want)
+        except RuntimeError as exc:                               # every rank raises together (collective decision)
+            out["next_equal_peer"] = f"unavailable: {str(exc)[:120]}"
 
         # shard-after-quantize: slices of one quantized weight reproduce the unsharded GEMM exactly
         qw = fos.quantize(w_up)
@@ -210,7 +212,7 @@ def test_column_then_row_parallel(world):
         if not isinstance(out["slab_peer"], str):
             assert out["slab_peer"][0] < 2e-2 and out["slab_peer"][1], out["slab_peer"]
         assert out["packed_equal"], "slabs quantized with the common amax must equal the unsharded quantization"
-        assert out["next_equal"] and out["next_equal_nccl"]
+        assert out["next_equal"] and out["next_equal_peer"] is not False
         assert out["rows_equal"]
         assert out["k_err"] < 1e-5, out["k_err"]
         assert out["two_streams_equal"], "two layers on two streams must equal their serial results"
