@@ -208,6 +208,17 @@ __device__ __forceinline__ void stg_32(void *p, const uint32_t *v) {
                  ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
 }
 
+// The same store for data that will not be read again soon (a GEMM's output): marked evict-first in L2, so that
+// it does not push the operand tiles, which every CTA of a band re-reads, out of the cache, and not allocated in L1
+// (8192^3: 215 -> 212.5 us, 8192 x 4096 x 4096: 61.7 -> 59.6 us; evict-first alone and .cs measured the same as plain).
+#ifndef FOS_ST_STREAM_HINT
+#define FOS_ST_STREAM_HINT ".L1::no_allocate.L2::evict_first"
+#endif
+__device__ __forceinline__ void stg_32_stream(void *p, const uint32_t *v) {
+    asm volatile("st.global" FOS_ST_STREAM_HINT ".v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
+
 template <typename T> __device__ __forceinline__ float elem_to_float(T v);
 template <> __device__ __forceinline__ float elem_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> __device__ __forceinline__ float elem_to_float<__half>(__half v) { return __half2float(v); }

@@ -567,7 +567,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     if (left >= COLS && vec32_ok) {
                         // 32 bytes per store: every instruction of the warp fills whole 32-byte sectors
 #pragma unroll
-                        for (int i = 0; i < COLS / 16; ++i) stg_32(reinterpret_cast<uint8_t *>(dst) + 32 * i, &pk[8 * i]);
+                        for (int i = 0; i < COLS / 16; ++i) stg_32_stream(reinterpret_cast<uint8_t *>(dst) + 32 * i, &pk[8 * i]);
                     } else if (left >= COLS && vec_ok) {
 #pragma unroll
                         for (int i = 0; i < COLS / 8; ++i)
@@ -915,7 +915,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     OUT *dst = out + row * p.ldd + n0;
                     if (left >= COLS && vec32_ok) {
 #pragma unroll
-                        for (int i = 0; i < COLS / 16; ++i) stg_32(reinterpret_cast<uint8_t *>(dst) + 32 * i, &pk[8 * i]);
+                        for (int i = 0; i < COLS / 16; ++i) stg_32_stream(reinterpret_cast<uint8_t *>(dst) + 32 * i, &pk[8 * i]);
                     } else if (left >= COLS && vec_ok) {
 #pragma unroll
                         for (int i = 0; i < COLS / 8; ++i)
