@@ -119,29 +119,57 @@ __device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
 // that keeps every step normal (k.fast), a scale byte with the sign bit set or NaN, or - fp16 outputs - a
 // magnitude that would leave fp16's normal range.
 template <typename OUT>
-__device__ __forceinline__ bool dequantize_block_packed(uint2 c, uint32_t sfb, const DequantConsts &k, uint32_t (&o)[8]) {
+__device__ __forceinline__ bool dequantize_block_packed(uint2 c, uint32_t sfb, const DequantConsts &k, uint32_t (&o)[8],
+                                                        bool is_if4 = false) {
     static_assert(sizeof(OUT) == 2, "16-bit outputs");
     constexpr bool HALF = std::is_same<OUT, __half>::value;
     constexpr uint32_t E = HALF ? 0x0400u : 0x0080u, E2 = E | (E << 16);       // one step of the exponent field
+    const bool is_int = is_if4 && (sfb & 0x80u);
+    if (is_if4) sfb &= 0x7fu;
     if (!k.fast || (sfb & 0x80u) || sfb == 0x7fu) return false;
     const float s = e4m3_to_float(sfb);
-    const uint64_t a = fma2(pack2(s, __fmul_rn(s, 1.5f)), pack2(k.amax, k.amax), pack2(0.0f, 0.0f));
-    float q1, q3;
-    unpack2f(div_const2(a, pack2(-k.divisor, -k.divisor), pack2(k.y, k.y)), q1, q3);
-    if (HALF && q1 != 0.0f && !(q1 >= 0x1p-13f && q3 < 16376.0f)) return false;
-    uint32_t t23 = pack16x2<OUT>(q1, q3);                    // [Q1, Q3]
-    uint32_t t01 = (t23 << 16) - (E << 16);                  // [0, Q1 / 2]
-    uint32_t t45 = t23 + E2, t67 = t45 + E2;                 // [2 Q1, 2 Q3], [4 Q1, 4 Q3]
-    if ((t23 & 0xffffu) == 0u) t01 = t23 = t45 = t67 = 0u;   // a zero scale: every magnitude is zero
+    const uint64_t amax2 = pack2(k.amax, k.amax), dneg2 = pack2(-k.divisor, -k.divisor), y2 = pack2(k.y, k.y);
+    uint32_t t01, t23, t45, t67, mag[2], sgn[2];
+    sgn[0] = (c.x >> 3) & 0x11111111u;
+    sgn[1] = (c.y >> 3) & 0x11111111u;
+    if (is_int) {
+        // IF4 integer block: the seven magnitudes fp16(fp16(i * 6/7) * s), i = 1 .. 7, each through (x * amax) / divisor
+        // and the cast (no power-of-two structure to exploit: four packed products, quotients and conversions per
+        // block instead of sixteen); the magnitude of a two's-complement nibble is (n ^ m) + sign, m = 15 where the
+        // sign bit is set (-8 does not occur: the quantizer clamps to +-7)
+        const __half2 s2 = __float2half2_rn(s);
+        auto entry = [&](uint32_t consts) {                                  // consts: fp16(i * fl32(6/7)) for two i
+            const float2 p = __half22float2(__hmul2(*reinterpret_cast<const __half2 *>(&consts), s2));
+            float q0, q1;
+            unpack2f(div_const2(fma2(pack2(p.x, p.y), amax2, pack2(0.0f, 0.0f)), dneg2, y2), q0, q1);
+            return pack16x2<OUT>(q0, q1);
+        };
+        t01 = entry(0x3adb0000u);
+        t23 = entry(0x41253edbu);
+        t45 = entry(0x444942dbu);
+        t67 = entry(0x46004525u);
+        mag[0] = ((c.x ^ (sgn[0] * 15u)) + sgn[0]) & 0x77777777u;
+        mag[1] = ((c.y ^ (sgn[1] * 15u)) + sgn[1]) & 0x77777777u;
+    } else {
+        const uint64_t a = fma2(pack2(s, __fmul_rn(s, 1.5f)), amax2, pack2(0.0f, 0.0f));
+        float q1, q3;
+        unpack2f(div_const2(a, dneg2, y2), q1, q3);
+        if (HALF && q1 != 0.0f && !(q1 >= 0x1p-13f && q3 < 16376.0f)) return false;
+        t23 = pack16x2<OUT>(q1, q3);                         // [Q1, Q3]
+        t01 = (t23 << 16) - (E << 16);                       // [0, Q1 / 2]
+        t45 = t23 + E2;                                      // [2 Q1, 2 Q3]
+        t67 = t45 + E2;                                      // [4 Q1, 4 Q3]
+        if ((t23 & 0xffffu) == 0u) t01 = t23 = t45 = t67 = 0u;   // a zero scale: every magnitude is zero
+        mag[0] = c.x & 0x77777777u;
+        mag[1] = c.y & 0x77777777u;
+    }
     const uint32_t la = __byte_perm(t01, t23, 0x6420), ha = __byte_perm(t01, t23, 0x7531);   // low / high bytes of
     const uint32_t lb = __byte_perm(t45, t67, 0x6420), hb = __byte_perm(t45, t67, 0x7531);   // magnitudes 0-3, 4-7
 #pragma unroll
     for (int w = 0; w < 2; ++w) {
-        const uint32_t cw = w ? c.y : c.x;
-        const uint32_t mag = cw & 0x77777777u, sgn = (cw >> 3) & 0x11111111u;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const uint32_t sel = h ? mag >> 16 : mag, ss = h ? sgn >> 16 : sgn;
+            const uint32_t sel = h ? mag[w] >> 16 : mag[w], ss = h ? sgn[w] >> 16 : sgn[w];
             const uint32_t lo = __byte_perm(la, lb, sel);
             const uint32_t hi = __byte_perm(ha, hb, sel) | __byte_perm(0x00008000u, 0u, ss);
             o[4 * w + 2 * h] = __byte_perm(lo, hi, 0x5140);

@@ -73,9 +73,9 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantParams p) 
             OUT *dst = static_cast<OUT *>(p.out) + (row[d] * ld_out + static_cast<idx_t>(cb * 16));
             const int64_t left = p.cols - static_cast<int64_t>(cb) * 16;
             if constexpr (sizeof(OUT) == 2) {
-                // NVFP4 to bf16 / fp16: the whole block from two quotients and a byte-permute table
+                // bf16 / fp16 outputs: the whole block from a table of its eight magnitudes
                 uint32_t o[8];
-                if (p.format == FOS_NVFP4 && dequantize_block_packed<OUT>(c[d], sfb[d], k, o)) {
+                if (dequantize_block_packed<OUT>(c[d], sfb[d], k, o, p.format == FOS_IF4)) {
                     if (left >= 16 && (reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
                         stg_32(dst, o);                       // one 32-byte store: whole sectors per instruction
                     } else if (left >= 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {

@@ -1322,11 +1322,11 @@ quantize_rows_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
                 const int64_t col = (static_cast<int64_t>(tc_) * 4 + cb) * 16;
                 if (row < p.rows && col < p.cols) {
                     T *dst = static_cast<T *>(p.fake_out) + row * p.fake_ld + col;
-                    if constexpr (KIND != KIND_IF4) {
-                        // NVFP4: the block's sixteen outputs from two quotients and a byte-permute table
+                    {
+                        // the block's sixteen outputs from a table of its eight magnitudes
                         uint32_t o[8];
                         if (col + 16 <= p.cols && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 &&
-                            dequantize_block_packed<T>(make_uint2(lo, hi), sf_byte, dk, o)) {
+                            dequantize_block_packed<T>(make_uint2(lo, hi), sf_byte, dk, o, KIND == KIND_IF4)) {
                             reinterpret_cast<uint4 *>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
                             reinterpret_cast<uint4 *>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
                             continue;
