@@ -1965,6 +1965,18 @@ cudaError_t launch_amax(const void *x, int64_t rows, int64_t cols, int64_t ld, b
     const int64_t work = vec ? rows * (cols / (vec / 2)) : rows * cols;
     int64_t blocks = (work + 255) / 256;
     if (blocks > resident[slot]) blocks = resident[slot];
+#ifndef FOS_AMAX_EVEN_ROUNDS
+#define FOS_AMAX_EVEN_ROUNDS 1
+#endif
+    if (FOS_AMAX_EVEN_ROUNDS && vec) {
+        // whole rounds: a thread takes 128 bytes per round, so with a full wave of CTAs the last round is usually
+        // ragged (8192 x 4096: 3.46 rounds, the fourth with half of the loads in flight). Fewer CTAs, all of which
+        // run the same number of full rounds, keep the memory system equally busy to the end.
+        const int64_t per_round = 256 * (128 / vec);                     // chunks one CTA takes per round
+        const int64_t rounds = (work + per_round * resident[slot] - 1) / (per_round * resident[slot]);
+        const int64_t even = (work + per_round * rounds - 1) / (per_round * rounds);
+        if (even >= resident[slot] / 2) blocks = even;                   // (tiny inputs keep one CTA per 256 chunks)
+    }
     if (blocks < 1) blocks = 1;
     cfg = dependent_launch_config(static_cast<unsigned>(blocks), 256, stream, attr);
     return cudaLaunchKernelEx(&cfg, amax_kernel<T>, static_cast<const T *>(x), rows, cols, ld, vec, amax);
