@@ -389,9 +389,11 @@ int fos_gemm_if4_static(const uint8_t *a_codes, const uint8_t *a_sf, int a_forma
  * fos_quantize with stochastic rounding (RoundStyle.stochastic of the reference: uniform noise of
  * +-half a grid step is added to every scaled magnitude before it is rounded; with a 4/6 rule both
  * candidates get independent noise and the better draw wins). `seed` selects the noise: the same
- * call with the same seed writes the same bytes. NVFP4, 1-D blocks, x 16-byte aligned (base and row
+ * call with the same seed writes the same bytes. NVFP4 (any scale rule) or IF4 with the mse rule (both grids, the
+ * E2M1 one and the integer one, draw independent noise and the smaller squared error of the draw wins:
+ * src/fouroversix/quantize/pytorch/reference.py:55-63, 328-425), 1-D blocks, x 16-byte aligned (base and row
  * stride; when transposing also codes 16-byte and sf 2-byte aligned); anything else returns
- * FOS_ERR_UNSUPPORTED. The reference draws its noise from torch's generator, so the two agree in
+ * FOS_ERR_UNSUPPORTED. With FOS_QUANTIZE_UNBIASED every maximum is scaled by 16/17 (RoundStyle.stochastic_unbiased). The reference draws its noise from torch's generator, so the two agree in
  * distribution, not bit for bit.
  *
  * Replaces: the rbits / is_rtn = false path of torch.ops.fouroversix.quantize
