@@ -237,8 +237,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 s0 = (s0 < 0 ? 0 : (s0 > cap ? cap : s0)) & ~127;             // never beyond the buffers
                 grp_start[g] = s0;
                 if (g < p.num_groups) {
+                    // valid rows end inside the group's own range, whatever group_rows claims
+                    int32_t s1 = __ldg(p.group_start + g + 1);
+                    s1 = (s1 < s0 ? s0 : (s1 > cap ? cap : s1)) & ~127;
                     const int32_t r = __ldg(p.group_rows + g), e = s0 + (r < 0 ? 0 : r);
-                    grp_end[g] = e > cap ? cap : e;
+                    grp_end[g] = e > s1 ? s1 : e;
                 }
             }
         }
