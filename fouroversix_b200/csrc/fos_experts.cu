@@ -1,0 +1,244 @@
+// The element-wise steps of a mixture-of-experts layer around the two grouped GEMMs, one kernel each:
+//
+//   fos_experts_gather_rows   routed tokens -> the padded row buffer the grouped quantization reads
+//   fos_experts_glu           gate-up output + bias -> clamped SwiGLU, the input of the down projection
+//   fos_experts_combine       down output + bias, times the routing weight, summed per token
+//
+// The arithmetic follows the reference's GPT-OSS experts module
+// (src/fouroversix/model/modules/gpt_oss.py:297-335), which runs it as a chain of element-wise tensor
+// operations on 16-bit tensors: every operation computes in binary32 and rounds its result to the
+// tensor's type. The kernels keep every one of those roundings (r16 below), so the results are the bits
+// of that chain; what they save is its memory traffic (each operation reads and writes the whole tensor,
+// the gathers materialise the bias per row) and its launches. All three are bound by HBM.
+#include "fos_common.cuh"
+
+namespace fos {
+namespace {
+
+template <typename T> struct Half16;
+template <> struct Half16<__nv_bfloat16> {
+    static __device__ __forceinline__ float lo(uint32_t w) { return __uint_as_float(w << 16); }
+    static __device__ __forceinline__ float hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+    static __device__ __forceinline__ float r16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+    static __device__ __forceinline__ uint32_t pack(float lo_v, float hi_v) {   // values already rounded
+        return (__float_as_uint(lo_v) >> 16) | (__float_as_uint(hi_v) & 0xffff0000u);
+    }
+};
+template <> struct Half16<__half> {
+    static __device__ __forceinline__ float lo(uint32_t w) { return __half2float(__ushort_as_half(static_cast<unsigned short>(w & 0xffffu))); }
+    static __device__ __forceinline__ float hi(uint32_t w) { return __half2float(__ushort_as_half(static_cast<unsigned short>(w >> 16))); }
+    static __device__ __forceinline__ float r16(float v) { return __half2float(__float2half_rn(v)); }
+    static __device__ __forceinline__ uint32_t pack(float lo_v, float hi_v) {
+        return static_cast<uint32_t>(__half_as_ushort(__float2half_rn(lo_v))) |
+               (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(hi_v))) << 16);
+    }
+};
+
+__device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// out[r] = x[row_token[r]], or zeros where row_token[r] < 0. One CTA per row at a time, 16 bytes per thread.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint8_t *__restrict__ x, int64_t ld_x_bytes, const int32_t *__restrict__ row_token,
+                   uint8_t *__restrict__ out, int64_t ld_out_bytes, int rows, int chunks) {
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const int t = __ldg(row_token + r);
+        const uint4 *src = reinterpret_cast<const uint4 *>(x + static_cast<int64_t>(t < 0 ? 0 : t) * ld_x_bytes);
+        uint4 *dst = reinterpret_cast<uint4 *>(out + r * ld_out_bytes);
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x)
+            dst[c] = t < 0 ? make_uint4(0u, 0u, 0u, 0u) : __ldg(src + c);
+    }
+}
+
+// The reference's chain on one (gate, up) pair, every intermediate rounded to the 16-bit type:
+//   g = gate + bias_g; u = up + bias_u; g = min(g, limit); u = min(max(u, -limit), limit)   (NaN passes through)
+//   out = (u + 1) * (g * sigmoid(g * alpha))
+template <typename T>
+__device__ __forceinline__ float glu_pair(float gate, float up, float bias_g, float bias_u, float alpha, float limit) {
+    using H = Half16<T>;
+    float g = H::r16(gate + bias_g), u = H::r16(up + bias_u);
+    if (g == g) g = H::r16(fminf(g, limit));
+    if (u == u) u = H::r16(fminf(fmaxf(u, -limit), limit));
+    const float t = H::r16(g * alpha);
+    const float s = H::r16(1.0f / (1.0f + expf(-t)));
+    const float gl = H::r16(g * s);
+    const float u1 = H::r16(u + 1.0f);
+    return H::r16(u1 * gl);
+}
+
+// gate_up [rows][2 * inter] with gate in the even and up in the odd columns; bias [experts][2 * inter];
+// out [rows][inter]. A thread makes 8 outputs from 32 bytes of gate_up and 32 bytes of bias.
+template <typename T>
+__global__ void __launch_bounds__(256)
+glu_kernel(const uint8_t *__restrict__ gate_up, int64_t ld_gu_bytes, const uint8_t *__restrict__ bias, int64_t ld_bias_bytes,
+           const int32_t *__restrict__ row_expert, uint8_t *__restrict__ out, int64_t ld_out_bytes, int rows, int chunks,
+           float alpha, float limit) {
+    using H = Half16<T>;
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const int e = __ldg(row_expert + r);
+        uint4 *dst = reinterpret_cast<uint4 *>(out + r * ld_out_bytes);
+        if (e < 0) {
+            for (int c = threadIdx.x; c < chunks; c += blockDim.x) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+            continue;
+        }
+        const uint4 *src = reinterpret_cast<const uint4 *>(gate_up + r * ld_gu_bytes);
+        const uint4 *b = reinterpret_cast<const uint4 *>(bias + e * ld_bias_bytes);
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+            const uint4 v0 = ldg_stream(src + 2 * c), v1 = ldg_stream(src + 2 * c + 1);
+            const uint4 b0 = __ldg(b + 2 * c), b1 = __ldg(b + 2 * c + 1);
+            const uint32_t v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+            const uint32_t bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                o[i] = glu_pair<T>(H::lo(v[i]), H::hi(v[i]), H::lo(bb[i]), H::hi(bb[i]), alpha, limit);
+            dst[c] = make_uint4(H::pack(o[0], o[1]), H::pack(o[2], o[3]), H::pack(o[4], o[5]), H::pack(o[6], o[7]));
+        }
+    }
+}
+
+constexpr int MAX_TOP_K = 8;
+
+// out[t] = sum over the token's experts, in ascending order of the expert's index (the order in which the
+// reference's host loop adds them into the 16-bit result), of (y[row] + bias[expert]) * weight, every
+// operation rounded to the 16-bit type, the running sum too.
+template <typename T>
+__global__ void __launch_bounds__(256)
+combine_kernel(const uint8_t *__restrict__ y, int64_t ld_y_bytes, const uint8_t *__restrict__ bias, int64_t ld_bias_bytes,
+               const int32_t *__restrict__ pair_row, const int32_t *__restrict__ pair_expert,
+               const T *__restrict__ pair_weight, int top_k, uint8_t *__restrict__ out, int64_t ld_out_bytes, int tokens,
+               int chunks) {
+    using H = Half16<T>;
+    for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
+        int row[MAX_TOP_K], ex[MAX_TOP_K];
+        float w[MAX_TOP_K];
+#pragma unroll
+        for (int k = 0; k < MAX_TOP_K; ++k) {
+            const bool have = k < top_k;
+            row[k] = have ? __ldg(pair_row + static_cast<int64_t>(t) * top_k + k) : 0;
+            ex[k] = have ? __ldg(pair_expert + static_cast<int64_t>(t) * top_k + k) : 0x7fffffff;
+            w[k] = have ? static_cast<float>(pair_weight[static_cast<int64_t>(t) * top_k + k]) : 0.0f;
+        }
+        // odd-even transposition sort by expert (eight fixed rounds: stays in registers); absent slots sort last
+#pragma unroll
+        for (int round = 0; round < MAX_TOP_K; ++round) {
+#pragma unroll
+            for (int k = round & 1; k + 1 < MAX_TOP_K; k += 2) {
+                if (ex[k] > ex[k + 1]) {
+                    const int te = ex[k]; ex[k] = ex[k + 1]; ex[k + 1] = te;
+                    const int tr = row[k]; row[k] = row[k + 1]; row[k + 1] = tr;
+                    const float tw = w[k]; w[k] = w[k + 1]; w[k + 1] = tw;
+                }
+            }
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(out + t * ld_out_bytes);
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int k = 0; k < MAX_TOP_K; ++k) {
+                if (k < top_k) {
+                    const uint4 v = ldg_stream(reinterpret_cast<const uint4 *>(y + row[k] * ld_y_bytes) + c);
+                    const uint4 b = __ldg(reinterpret_cast<const uint4 *>(bias + ex[k] * ld_bias_bytes) + c);
+                    const uint32_t vv[4] = {v.x, v.y, v.z, v.w}, bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float s0 = H::r16(H::r16(H::lo(vv[i]) + H::lo(bb[i])) * w[k]);
+                        const float s1 = H::r16(H::r16(H::hi(vv[i]) + H::hi(bb[i])) * w[k]);
+                        acc[2 * i] = H::r16(acc[2 * i] + s0);
+                        acc[2 * i + 1] = H::r16(acc[2 * i + 1] + s1);
+                    }
+                }
+            }
+            dst[c] = make_uint4(H::pack(acc[0], acc[1]), H::pack(acc[2], acc[3]), H::pack(acc[4], acc[5]), H::pack(acc[6], acc[7]));
+        }
+    }
+}
+
+inline bool aligned16(const void *p, int64_t ld_bytes) {
+    return reinterpret_cast<uintptr_t>(p) % 16 == 0 && ld_bytes % 16 == 0;
+}
+
+inline unsigned grid_for(int64_t rows) {
+    const int64_t cap = 148 * 8;
+    return static_cast<unsigned>(rows < cap ? rows : cap);
+}
+
+}  // namespace
+}  // namespace fos
+
+extern "C" int fos_experts_gather_rows(const void *x, int dtype, int64_t ld_x, const int32_t *row_token, void *out,
+                                       int64_t ld_out, int64_t rows_capacity, int64_t cols, void *stream_) {
+    using namespace fos;
+    if (!x || !row_token || !out || rows_capacity <= 0 || cols <= 0 || ld_x < cols || ld_out < cols) return FOS_ERR_INVALID_ARGUMENT;
+    if (dtype != FOS_BF16 && dtype != FOS_FP16) return FOS_ERR_UNSUPPORTED;
+    if (cols % 8 != 0 || rows_capacity >= (int64_t(1) << 31)) return FOS_ERR_UNSUPPORTED;
+    if (!aligned16(x, ld_x * 2) || !aligned16(out, ld_out * 2)) return FOS_ERR_MISALIGNED;
+    const int st = check_device();
+    if (st != FOS_OK) return st;
+    gather_rows_kernel<<<grid_for(rows_capacity), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+        static_cast<const uint8_t *>(x), ld_x * 2, row_token, static_cast<uint8_t *>(out), ld_out * 2,
+        static_cast<int>(rows_capacity), static_cast<int>(cols / 8));
+    FOS_CUDA_TRY(cudaGetLastError());
+    return FOS_OK;
+}
+
+extern "C" int fos_experts_glu(const void *gate_up, int dtype, int64_t ld_gate_up, const void *bias, const int32_t *row_expert,
+                               void *out, int64_t ld_out, int64_t rows_capacity, int64_t intermediate, float alpha,
+                               float limit, void *stream_) {
+    using namespace fos;
+    if (!gate_up || !bias || !row_expert || !out || rows_capacity <= 0 || intermediate <= 0 ||
+        ld_gate_up < 2 * intermediate || ld_out < intermediate)
+        return FOS_ERR_INVALID_ARGUMENT;
+    if (dtype != FOS_BF16 && dtype != FOS_FP16) return FOS_ERR_UNSUPPORTED;
+    if (intermediate % 8 != 0 || rows_capacity >= (int64_t(1) << 31)) return FOS_ERR_UNSUPPORTED;
+    if (!aligned16(gate_up, ld_gate_up * 2) || !aligned16(out, ld_out * 2) || !aligned16(bias, 2 * intermediate * 2))
+        return FOS_ERR_MISALIGNED;
+    const int st = check_device();
+    if (st != FOS_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const unsigned g = grid_for(rows_capacity);
+    const int rows = static_cast<int>(rows_capacity), chunks = static_cast<int>(intermediate / 8);
+    if (dtype == FOS_BF16)
+        glu_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const uint8_t *>(gate_up), ld_gate_up * 2,
+                                                           static_cast<const uint8_t *>(bias), 2 * intermediate * 2, row_expert,
+                                                           static_cast<uint8_t *>(out), ld_out * 2, rows, chunks, alpha, limit);
+    else
+        glu_kernel<__half><<<g, 256, 0, stream>>>(static_cast<const uint8_t *>(gate_up), ld_gate_up * 2,
+                                                    static_cast<const uint8_t *>(bias), 2 * intermediate * 2, row_expert,
+                                                    static_cast<uint8_t *>(out), ld_out * 2, rows, chunks, alpha, limit);
+    FOS_CUDA_TRY(cudaGetLastError());
+    return FOS_OK;
+}
+
+extern "C" int fos_experts_combine(const void *y, int dtype, int64_t ld_y, const void *bias, const int32_t *pair_row,
+                                   const int32_t *pair_expert, const void *pair_weight, int top_k, void *out,
+                                   int64_t ld_out, int64_t tokens, int64_t hidden, void *stream_) {
+    using namespace fos;
+    if (!y || !bias || !pair_row || !pair_expert || !pair_weight || !out || tokens <= 0 || hidden <= 0 || top_k <= 0 ||
+        ld_y < hidden || ld_out < hidden)
+        return FOS_ERR_INVALID_ARGUMENT;
+    if (dtype != FOS_BF16 && dtype != FOS_FP16) return FOS_ERR_UNSUPPORTED;
+    if (top_k > MAX_TOP_K || hidden % 8 != 0 || tokens >= (int64_t(1) << 31)) return FOS_ERR_UNSUPPORTED;
+    if (!aligned16(y, ld_y * 2) || !aligned16(out, ld_out * 2) || !aligned16(bias, hidden * 2)) return FOS_ERR_MISALIGNED;
+    const int st = check_device();
+    if (st != FOS_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const unsigned g = grid_for(tokens);
+    const int n = static_cast<int>(tokens), chunks = static_cast<int>(hidden / 8);
+    if (dtype == FOS_BF16)
+        combine_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const uint8_t *>(y), ld_y * 2,
+                                                               static_cast<const uint8_t *>(bias), hidden * 2, pair_row, pair_expert,
+                                                               static_cast<const __nv_bfloat16 *>(pair_weight), top_k,
+                                                               static_cast<uint8_t *>(out), ld_out * 2, n, chunks);
+    else
+        combine_kernel<__half><<<g, 256, 0, stream>>>(static_cast<const uint8_t *>(y), ld_y * 2,
+                                                        static_cast<const uint8_t *>(bias), hidden * 2, pair_row, pair_expert,
+                                                        static_cast<const __half *>(pair_weight), top_k,
+                                                        static_cast<uint8_t *>(out), ld_out * 2, n, chunks);
+    FOS_CUDA_TRY(cudaGetLastError());
+    return FOS_OK;
+}

@@ -17,7 +17,8 @@ from __future__ import annotations
 import torch
 from torch import nn
 
-from fouroversix_b200.matmul.grouped import (GroupLayout, StackedQuantizedTensor, grouped_quantize,
+from fouroversix_b200 import _native
+from fouroversix_b200.matmul.grouped import (_OUT, GroupLayout, StackedQuantizedTensor, grouped_quantize,
                                              grouped_quantized_matmul)
 from fouroversix_b200.quantize import quantize
 from fouroversix_b200.utils import DataType
@@ -33,8 +34,9 @@ class FourOverSixExperts(nn.Module):
 
     def __init__(self, gate_up_proj: torch.Tensor, gate_up_proj_bias: torch.Tensor, down_proj: torch.Tensor,
                  down_proj_bias: torch.Tensor, config: ModuleQuantizationConfig | None = None, *,
-                 alpha: float = 1.702, limit: float = 7.0) -> None:
+                 alpha: float = 1.702, limit: float = 7.0, native_elementwise: bool = True) -> None:
         super().__init__()
+        self.native_elementwise = native_elementwise
         self.config = config or ModuleQuantizationConfig()
         if DataType(self.config.dtype) != DataType.nvfp4:
             raise NotImplementedError("the grouped kernels take nvfp4 operands")
@@ -94,6 +96,9 @@ class FourOverSixExperts(nn.Module):
         layout, rows, token, order = self.route(routing_indices)
         expert = routing_indices.reshape(-1)[order]
 
+        if self._native_elementwise(x, routing_weights, out_dtype):
+            return self._forward_native(x, layout, rows, token, order, expert, routing_indices, routing_weights).reshape(shape)
+
         padded = torch.zeros(layout.capacity, self.hidden_size, dtype=x.dtype, device=x.device)
         padded[rows] = x[token]
         gu = grouped_quantized_matmul(grouped_quantize(padded, layout, act_config), gate_up, out_dtype=out_dtype)
@@ -110,3 +115,53 @@ class FourOverSixExperts(nn.Module):
         result = torch.zeros_like(x)
         result.index_add_(0, token, y.to(x.dtype))
         return result.reshape(shape)
+
+    def _native_elementwise(self, x: torch.Tensor, routing_weights: torch.Tensor, out_dtype: DataType) -> bool:
+        """The three element-wise kernels take 16-bit tensors of one type, widths that are multiples of 8 and at
+        most 8 experts per token; anything else runs the same arithmetic as tensor operations."""
+        if not self.native_elementwise:
+            return False
+        same = x.dtype == _OUT[DataType(out_dtype)] == routing_weights.dtype == self.gate_up_proj_bias.dtype == self.down_proj_bias.dtype
+        return (same and x.dtype in (torch.bfloat16, torch.float16) and self.hidden_size % 8 == 0
+                and self.intermediate_size % 8 == 0 and routing_weights.shape[-1] <= 8)
+
+    def _forward_native(self, x, layout, rows, token, order, expert, routing_indices, routing_weights) -> torch.Tensor:
+        """The same layer with `fos_experts_gather_rows`, `fos_experts_glu` and `fos_experts_combine` between the
+        grouped launches: bit-equal to the tensor-operation form when a token has at most two experts, and to the
+        reference's host loop (which adds a token's experts in ascending order) for any number."""
+        down, gate_up = self.quantized_weights()
+        act_config = self.config.get_activation_config()
+        out_dtype = self.config.output_dtype
+        dev, dtype, code = x.device, x.dtype, _native.elem_code(x.dtype)
+        lib, stream = _native.lib(), _native.stream_ptr(x.device)
+        tokens, top_k = routing_indices.shape
+        x = x if x.stride(-1) == 1 else x.contiguous()
+        rows32 = rows.to(torch.int32)
+        row_token = torch.full((layout.capacity,), -1, dtype=torch.int32, device=dev)
+        row_token[rows] = token.to(torch.int32)
+        row_expert = torch.full((layout.capacity,), -1, dtype=torch.int32, device=dev)
+        row_expert[rows] = expert.to(torch.int32)
+        pair_row = torch.empty(tokens * top_k, dtype=torch.int32, device=dev)
+        pair_row[order] = rows32
+        pair_expert = routing_indices.reshape(-1).to(torch.int32)
+        weights = routing_weights.reshape(-1).contiguous()
+        gate_up_bias, down_bias = self.gate_up_proj_bias.contiguous(), self.down_proj_bias.contiguous()
+
+        padded = torch.empty(layout.capacity, self.hidden_size, dtype=dtype, device=dev)
+        _native.check(lib.fos_experts_gather_rows(x.data_ptr(), code, x.stride(0), row_token.data_ptr(), padded.data_ptr(),
+                                                  padded.stride(0), layout.capacity, self.hidden_size, stream),
+                      "fos_experts_gather_rows")
+        # padding rows of the two GEMM outputs are neither written nor read: no zero fill
+        gu = torch.empty(layout.capacity, 2 * self.intermediate_size, dtype=dtype, device=dev)
+        grouped_quantized_matmul(grouped_quantize(padded, layout, act_config), gate_up, out_dtype=out_dtype, out=gu)
+        gated = torch.empty(layout.capacity, self.intermediate_size, dtype=dtype, device=dev)
+        _native.check(lib.fos_experts_glu(gu.data_ptr(), code, gu.stride(0), gate_up_bias.data_ptr(), row_expert.data_ptr(),
+                                          gated.data_ptr(), gated.stride(0), layout.capacity, self.intermediate_size,
+                                          float(self.alpha), float(self.limit), stream), "fos_experts_glu")
+        y = torch.empty(layout.capacity, self.hidden_size, dtype=dtype, device=dev)
+        grouped_quantized_matmul(grouped_quantize(gated, layout, act_config), down, out_dtype=out_dtype, out=y)
+        result = torch.empty(tokens, self.hidden_size, dtype=dtype, device=dev)
+        _native.check(lib.fos_experts_combine(y.data_ptr(), code, y.stride(0), down_bias.data_ptr(), pair_row.data_ptr(),
+                                              pair_expert.data_ptr(), weights.data_ptr(), top_k, result.data_ptr(),
+                                              result.stride(0), tokens, self.hidden_size, stream), "fos_experts_combine")
+        return result

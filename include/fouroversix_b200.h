@@ -261,6 +261,38 @@ int fos_gemm_nvfp4_grouped(const uint8_t *a_codes, const uint8_t *a_sf, const ui
                            const fos_gemm_opts *opts, int32_t *status, void *stream);
 
 /*
+ * The element-wise steps of a mixture-of-experts layer around the two grouped GEMMs, one launch each, on 16-bit
+ * tensors (dtype FOS_BF16 or FOS_FP16 for every tensor of a call). The reference runs them as a chain of
+ * element-wise tensor operations, each rounding its result to the tensors' type; these kernels keep every one of
+ * those roundings, so the bits are the chain's. Row counts and leading dimensions in elements; widths must be
+ * multiples of 8 and all tensors 16-byte aligned (base and row stride): FOS_ERR_UNSUPPORTED / FOS_ERR_MISALIGNED.
+ *
+ * fos_experts_gather_rows: out[r][0..cols) = x[row_token[r]][0..cols), zeros where row_token[r] < 0
+ *   (row_token: rows_capacity int32 values in device memory). Fills the padded row buffer fos_quantize_grouped
+ *   reads, padding rows included.
+ * fos_experts_glu: gate_up [rows_capacity][2 * intermediate] with gate in the even and up in the odd columns,
+ *   bias [experts][2 * intermediate], row_expert[r] the expert of row r or < 0 for a padding row (whose output row
+ *   is zeros and whose input is not read):
+ *     g = gate + bias; u = up + bias; g = min(g, limit); u = min(max(u, -limit), limit);
+ *     out = (u + 1) * (g * sigmoid(g * alpha))                       out [rows_capacity][intermediate]
+ * fos_experts_combine: for token t with slots k < top_k (top_k <= 8): pair_row[t * top_k + k] the row of y that
+ *   holds the slot's result, pair_expert[...] its expert, pair_weight[...] its routing weight (16-bit, same type):
+ *     out[t] = sum over the slots, in ascending order of the expert index, of (y[row] + bias[expert]) * weight
+ *   with the running sum rounded to the 16-bit type after every addition - the order and the roundings of the
+ *   reference's host loop over the experts, whatever order the slots are listed in.
+ *
+ * Replaces: the element-wise tensor operations of src/fouroversix/model/modules/gpt_oss.py:310-333.
+ */
+int fos_experts_gather_rows(const void *x, int dtype, int64_t ld_x, const int32_t *row_token, void *out,
+                            int64_t ld_out, int64_t rows_capacity, int64_t cols, void *stream);
+int fos_experts_glu(const void *gate_up, int dtype, int64_t ld_gate_up, const void *bias, const int32_t *row_expert,
+                    void *out, int64_t ld_out, int64_t rows_capacity, int64_t intermediate, float alpha, float limit,
+                    void *stream);
+int fos_experts_combine(const void *y, int dtype, int64_t ld_y, const void *bias, const int32_t *pair_row,
+                        const int32_t *pair_expert, const void *pair_weight, int top_k, void *out, int64_t ld_out,
+                        int64_t tokens, int64_t hidden, void *stream);
+
+/*
  * The same GEMM for two MXFP4 operands (E8M0 scale per 32 values, scales in the 128 x 4 tile
  * order as fos_quantize(FOS_MXFP4, FOS_SF_TILED) writes them): tcgen05.mma kind::mxf4 with
  * scale_vec::2X. k_p must be a multiple of 128; everything else as for fos_gemm_nvfp4. The

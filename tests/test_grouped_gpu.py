@@ -127,30 +127,119 @@ def _reference_style_loop(layer: FourOverSixExperts, hidden, routing_indices, ro
         top_k_pos, token_idx = torch.where(mask[e])
         if token_idx.numel() == 0:
             continue
-        gu = fos.quantized_matmul(x[token_idx], gate_up[e], input_config=cfg) + layer.gate_up_proj_bias[e]
+        od = layer.config.output_dtype
+        gu = fos.quantized_matmul(x[token_idx], gate_up[e], input_config=cfg, out_dtype=od) + layer.gate_up_proj_bias[e]
         gate, up = gu[..., ::2].clamp(max=layer.limit), gu[..., 1::2].clamp(min=-layer.limit, max=layer.limit)
         gated = (up + 1) * (gate * torch.sigmoid(gate * layer.alpha))
-        out = fos.quantized_matmul(gated, down[e], input_config=cfg) + layer.down_proj_bias[e]
+        out = fos.quantized_matmul(gated, down[e], input_config=cfg, out_dtype=od) + layer.down_proj_bias[e]
         result.index_add_(0, token_idx, (out * routing_weights[token_idx, top_k_pos, None]).to(x.dtype))
     return result.reshape(hidden.shape)
 
 
-def test_experts_layer_equals_the_per_expert_loop():
-    g = torch.Generator().manual_seed(31)
-    experts, hidden, inter, tokens, top_k = 8, 256, 192, 300, 2
+def _experts_case(seed, experts, hidden, inter, tokens, top_k, dtype=torch.bfloat16, **kwargs):
+    from fouroversix_b200.model.config import ModuleQuantizationConfig
+    from fouroversix_b200.utils import DataType
+
+    g = torch.Generator().manual_seed(seed)
+    cfg = ModuleQuantizationConfig(output_dtype=DataType.bfloat16 if dtype == torch.bfloat16 else DataType.float16)
     layer = FourOverSixExperts(
-        (torch.randn(experts, 2 * inter, hidden, generator=g) * 0.05).bfloat16().to(DEV),
-        (torch.randn(experts, 2 * inter, generator=g) * 0.1).bfloat16().to(DEV),
-        (torch.randn(experts, hidden, inter, generator=g) * 0.05).bfloat16().to(DEV),
-        (torch.randn(experts, hidden, generator=g) * 0.1).bfloat16().to(DEV))
-    x = torch.randn(2, tokens // 2, hidden, generator=g).bfloat16().to(DEV)
+        (torch.randn(experts, 2 * inter, hidden, generator=g) * 0.05).to(dtype).to(DEV),
+        (torch.randn(experts, 2 * inter, generator=g) * 0.1).to(dtype).to(DEV),
+        (torch.randn(experts, hidden, inter, generator=g) * 0.05).to(dtype).to(DEV),
+        (torch.randn(experts, hidden, generator=g) * 0.1).to(dtype).to(DEV), cfg, **kwargs)
+    x = torch.randn(2, tokens // 2, hidden, generator=g).to(dtype).to(DEV)
     scores = torch.randn(tokens, experts, generator=g)
-    scores[:, 5] = -1e9                                           # an expert nobody is routed to
+    scores[:, min(5, experts - 1)] = -1e9                         # an expert nobody is routed to
     weights, indices = torch.topk(torch.softmax(scores, -1), top_k, dim=-1)
-    indices, weights = indices.to(DEV), weights.bfloat16().to(DEV)
+    return layer, x, indices.to(DEV), weights.to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("native", [True, False], ids=["kernels", "tensor-ops"])
+def test_experts_layer_equals_the_per_expert_loop(native):
+    layer, x, indices, weights = _experts_case(31, 8, 256, 192, 300, 2, native_elementwise=native)
     got = layer(x, indices, weights)
     want = _reference_style_loop(layer, x, indices, weights)
-    # every step is bit-equal group by group, and with two experts per token the two bf16 additions into a
-    # token's row commute: the whole layer is bit-equal
+    # every step is bit-equal group by group, and with two experts per token the two 16-bit additions into a
+    # token's row commute: the whole layer is bit-equal in either form
     assert (got.float() - want.float()).abs().max() <= 2 ** -7 * want.float().abs().max()
+    assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+def test_experts_layer_four_experts_per_token(dtype):
+    """With more than two experts per token the order of the additions into a token's row matters: the combine
+    kernel adds in ascending order of the expert, as the host loop does (whose index_add_ calls are one per
+    expert), so the layer stays bit-equal. GPT-OSS widths (2880: a multiple of 8, not of 128)."""
+    layer, x, indices, weights = _experts_case(37, 12, 2880, 2880, 96, 4, dtype)
+    got = layer(x, indices, weights)
+    want = _reference_style_loop(layer, x, indices, weights)
+    assert torch.equal(got, want)
+
+
+def _op_chain_glu(gu, bias, alpha, limit):
+    gu = gu + bias
+    gate, up = gu[..., ::2].clamp(min=None, max=limit), gu[..., 1::2].clamp(min=-limit, max=limit)
+    return (up + 1) * (gate * torch.sigmoid(gate * alpha))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+def test_glu_kernel_keeps_every_rounding_of_the_operation_chain(dtype):
+    """fos_experts_glu against the chain of tensor operations it replaces, on every 16-bit gate value there is
+    (so every rounding of the sigmoid is seen), and on limits and factors that are not 16-bit numbers."""
+    from fouroversix_b200 import _native
+
+    bits = torch.arange(-32768, 32768, dtype=torch.int32).to(torch.int16).to(DEV)
+    gates = bits.view(dtype)                                      # all 65536 patterns: NaNs, infinities, subnormals
+    g = torch.Generator().manual_seed(3)
+    ups = (torch.randn(65536, generator=g) * 4).to(dtype).to(DEV)
+    rows, inter = 128, 512
+    gu = torch.stack([gates, ups], dim=1).reshape(rows, 2 * inter).contiguous()
+    bias = (torch.randn(3, 2 * inter, generator=g) * 0.5).to(dtype).to(DEV)
+    bias[0] = 0
+    row_expert = (torch.arange(rows, device=DEV) % 4 - 1).to(torch.int32)          # -1: a padding row
+    for alpha, limit in ((1.702, 7.0), (0.3333, 2.7182818)):
+        out = torch.full((rows, inter), 9, dtype=dtype, device=DEV)
+        _native.check(_native.lib().fos_experts_glu(gu.data_ptr(), _native.elem_code(dtype), gu.stride(0), bias.data_ptr(),
+                                                    row_expert.data_ptr(), out.data_ptr(), out.stride(0), rows, inter,
+                                                    alpha, limit, _native.stream_ptr(gu.device)), "fos_experts_glu")
+        real = row_expert >= 0
+        want = _op_chain_glu(gu[real], bias[row_expert[real].long()], alpha, limit)
+        assert (out[~real] == 0).all()
+        got = out[real]
+        same = (got == want) | (got.isnan() & want.isnan())
+        assert same.all(), (alpha, limit, int((~same).sum()))
+
+
+def test_gather_and_combine_kernels():
+    """fos_experts_gather_rows and fos_experts_combine against index operations, slots listed in any order."""
+    from fouroversix_b200 import _native
+
+    g = torch.Generator().manual_seed(9)
+    tokens, top_k, hidden, experts, cap = 50, 3, 136, 6, 512
+    lib, code = _native.lib(), _native.FOS_BF16
+    x = torch.randn(tokens, hidden, generator=g).bfloat16().to(DEV)
+    row_token = torch.full((cap,), -1, dtype=torch.int32)
+    rows = torch.randperm(cap, generator=g)[:tokens * top_k]
+    row_token[rows] = (torch.arange(tokens * top_k) // top_k).to(torch.int32)
+    row_token = row_token.to(DEV)
+    out = torch.full((cap, hidden), 5, dtype=torch.bfloat16, device=DEV)
+    _native.check(lib.fos_experts_gather_rows(x.data_ptr(), code, x.stride(0), row_token.data_ptr(), out.data_ptr(),
+                                              out.stride(0), cap, hidden, _native.stream_ptr(x.device)), "gather")
+    want = torch.where(row_token[:, None] >= 0, x[row_token.clamp(min=0).long()], torch.zeros_like(out))
+    assert torch.equal(out, want)
+
+    y = torch.randn(cap, hidden, generator=g).bfloat16().to(DEV)
+    bias = torch.randn(experts, hidden, generator=g).bfloat16().to(DEV)
+    pair_expert = torch.stack([torch.randperm(experts, generator=g)[:top_k] for _ in range(tokens)]).to(torch.int32).to(DEV)
+    pair_row = rows.to(torch.int32).to(DEV)
+    weight = torch.rand(tokens * top_k, generator=g).bfloat16().to(DEV)
+    got = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=DEV)
+    _native.check(lib.fos_experts_combine(y.data_ptr(), code, y.stride(0), bias.data_ptr(), pair_row.data_ptr(),
+                                          pair_expert.data_ptr(), weight.data_ptr(), top_k, got.data_ptr(), got.stride(0),
+                                          tokens, hidden, _native.stream_ptr(x.device)), "combine")
+    want = torch.zeros(tokens, hidden, dtype=torch.bfloat16, device=DEV)
+    flat_e, token = pair_expert.reshape(-1).long(), torch.arange(tokens * top_k, device=DEV) // top_k
+    for e in range(experts):                                      # ascending experts, one 16-bit addition each
+        sel = (flat_e == e).nonzero().reshape(-1)
+        want.index_add_(0, token[sel], (y[pair_row[sel].long()] + bias[e]) * weight[sel, None])
     assert torch.equal(got, want)
