@@ -17,22 +17,27 @@ namespace {
 
 template <typename T> struct Half16;
 template <> struct Half16<__nv_bfloat16> {
+    using Pair = __nv_bfloat162;
     static __device__ __forceinline__ float lo(uint32_t w) { return __uint_as_float(w << 16); }
     static __device__ __forceinline__ float hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
     static __device__ __forceinline__ float r16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-    static __device__ __forceinline__ uint32_t pack(float lo_v, float hi_v) {   // values already rounded
-        return (__float_as_uint(lo_v) >> 16) | (__float_as_uint(hi_v) & 0xffff0000u);
+    static __device__ __forceinline__ uint32_t pack(float lo_v, float hi_v) {   // round and pack
+        Pair p = __floats2bfloat162_rn(lo_v, hi_v);
+        return *reinterpret_cast<uint32_t *>(&p);
     }
 };
 template <> struct Half16<__half> {
+    using Pair = __half2;
     static __device__ __forceinline__ float lo(uint32_t w) { return __half2float(__ushort_as_half(static_cast<unsigned short>(w & 0xffffu))); }
     static __device__ __forceinline__ float hi(uint32_t w) { return __half2float(__ushort_as_half(static_cast<unsigned short>(w >> 16))); }
     static __device__ __forceinline__ float r16(float v) { return __half2float(__float2half_rn(v)); }
     static __device__ __forceinline__ uint32_t pack(float lo_v, float hi_v) {
-        return static_cast<uint32_t>(__half_as_ushort(__float2half_rn(lo_v))) |
-               (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(hi_v))) << 16);
+        Pair p = __floats2half2_rn(lo_v, hi_v);
+        return *reinterpret_cast<uint32_t *>(&p);
     }
 };
+template <typename P> __device__ __forceinline__ P as_pair(uint32_t w) { return *reinterpret_cast<P *>(&w); }
+template <typename P> __device__ __forceinline__ uint32_t as_word(P p) { return *reinterpret_cast<uint32_t *>(&p); }
 
 __device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
     uint4 v;
@@ -57,17 +62,28 @@ gather_rows_kernel(const uint8_t *__restrict__ x, int64_t ld_x_bytes, const int3
 // The reference's chain on one (gate, up) pair, every intermediate rounded to the 16-bit type:
 //   g = gate + bias_g; u = up + bias_u; g = min(g, limit); u = min(max(u, -limit), limit)   (NaN passes through)
 //   out = (u + 1) * (g * sigmoid(g * alpha))
+// A (gate, up) pair is one 32-bit word, and a packed 16-bit addition, multiplication or fused multiply-add
+// rounds once from the exact result, which is what "compute in binary32, round to the type" gives for sums and
+// products of 16-bit numbers (their exact value fits binary32, or lies so far from a rounding boundary of the
+// 16-bit type that the first rounding cannot move it across). Only g * alpha (alpha is a binary32 number) and
+// the sigmoid run in binary32. The _rn forms of the packed operations keep the compiler from contracting a
+// multiplication and the addition after it into one fused operation, which would drop a rounding. limit2 = (r, r), floor2 = (-inf, -r) with r the limit rounded to the type:
+// comparing with r selects the same values as comparing with the limit itself, because no number of the type
+// lies between the two. Returns the output in the low half.
 template <typename T>
-__device__ __forceinline__ float glu_pair(float gate, float up, float bias_g, float bias_u, float alpha, float limit) {
+__device__ __forceinline__ uint32_t glu_word(uint32_t gate_up, uint32_t bias, float alpha,
+                                             typename Half16<T>::Pair limit2, typename Half16<T>::Pair floor2,
+                                             typename Half16<T>::Pair tail2) {
     using H = Half16<T>;
-    float g = H::r16(gate + bias_g), u = H::r16(up + bias_u);
-    if (g == g) g = H::r16(fminf(g, limit));
-    if (u == u) u = H::r16(fminf(fmaxf(u, -limit), limit));
-    const float t = H::r16(g * alpha);
-    const float s = H::r16(1.0f / (1.0f + expf(-t)));
-    const float gl = H::r16(g * s);
-    const float u1 = H::r16(u + 1.0f);
-    return H::r16(u1 * gl);
+    using P = typename H::Pair;
+    P v = __hadd2_rn(as_pair<P>(gate_up), as_pair<P>(bias));
+    v = __hmax2_nan(__hmin2_nan(v, limit2), floor2);
+    const float t = H::r16(H::lo(as_word(v)) * alpha);
+    const float s = 1.0f / (1.0f + expf(-t));
+    // (g, u) * (s, 1) + (-0, 1) = (g * s, u + 1): adding -0 keeps the sign of a zero product
+    const uint32_t s1 = (H::pack(s, 0.0f) & 0xffffu) | (as_word(tail2) & 0xffff0000u);
+    const P w = __hfma2(v, as_pair<P>(s1), as_pair<P>((as_word(tail2) & 0xffff0000u) | 0x8000u));
+    return as_word(__hmul2_rn(w, __lowhigh2highlow(w)));
 }
 
 // gate_up [rows][2 * inter] with gate in the even and up in the odd columns; bias [experts][2 * inter];
@@ -78,25 +94,28 @@ glu_kernel(const uint8_t *__restrict__ gate_up, int64_t ld_gu_bytes, const uint8
            const int32_t *__restrict__ row_expert, uint8_t *__restrict__ out, int64_t ld_out_bytes, int rows, int chunks,
            float alpha, float limit) {
     using H = Half16<T>;
-    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
-        const int e = __ldg(row_expert + r);
-        uint4 *dst = reinterpret_cast<uint4 *>(out + r * ld_out_bytes);
+    using P = typename H::Pair;
+    const float r = H::r16(limit);
+    const P limit2 = as_pair<P>(H::pack(r, r)), floor2 = as_pair<P>(H::pack(-INFINITY, -r)), tail2 = as_pair<P>(H::pack(1.0f, 1.0f));
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int e = __ldg(row_expert + row);
+        uint4 *dst = reinterpret_cast<uint4 *>(out + row * ld_out_bytes);
         if (e < 0) {
             for (int c = threadIdx.x; c < chunks; c += blockDim.x) dst[c] = make_uint4(0u, 0u, 0u, 0u);
             continue;
         }
-        const uint4 *src = reinterpret_cast<const uint4 *>(gate_up + r * ld_gu_bytes);
+        const uint4 *src = reinterpret_cast<const uint4 *>(gate_up + row * ld_gu_bytes);
         const uint4 *b = reinterpret_cast<const uint4 *>(bias + e * ld_bias_bytes);
         for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
             const uint4 v0 = ldg_stream(src + 2 * c), v1 = ldg_stream(src + 2 * c + 1);
             const uint4 b0 = __ldg(b + 2 * c), b1 = __ldg(b + 2 * c + 1);
             const uint32_t v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
             const uint32_t bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-            float o[8];
+            uint32_t o[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-                o[i] = glu_pair<T>(H::lo(v[i]), H::hi(v[i]), H::lo(bb[i]), H::hi(bb[i]), alpha, limit);
-            dst[c] = make_uint4(H::pack(o[0], o[1]), H::pack(o[2], o[3]), H::pack(o[4], o[5]), H::pack(o[6], o[7]));
+            for (int i = 0; i < 8; ++i) o[i] = glu_word<T>(v[i], bb[i], alpha, limit2, floor2, tail2);
+            dst[c] = make_uint4(__byte_perm(o[0], o[1], 0x5410), __byte_perm(o[2], o[3], 0x5410),
+                                __byte_perm(o[4], o[5], 0x5410), __byte_perm(o[6], o[7], 0x5410));
         }
     }
 }
@@ -105,57 +124,56 @@ constexpr int MAX_TOP_K = 8;
 
 // out[t] = sum over the token's experts, in ascending order of the expert's index (the order in which the
 // reference's host loop adds them into the 16-bit result), of (y[row] + bias[expert]) * weight, every
-// operation rounded to the 16-bit type, the running sum too.
+// operation rounded to the 16-bit type, the running sum too (packed 16-bit arithmetic: see glu_word).
 template <typename T>
 __global__ void __launch_bounds__(256)
 combine_kernel(const uint8_t *__restrict__ y, int64_t ld_y_bytes, const uint8_t *__restrict__ bias, int64_t ld_bias_bytes,
                const int32_t *__restrict__ pair_row, const int32_t *__restrict__ pair_expert,
-               const T *__restrict__ pair_weight, int top_k, uint8_t *__restrict__ out, int64_t ld_out_bytes, int tokens,
+               const uint16_t *__restrict__ pair_weight, int top_k, uint8_t *__restrict__ out, int64_t ld_out_bytes, int tokens,
                int chunks) {
-    using H = Half16<T>;
+    using P = typename Half16<T>::Pair;
+    __shared__ int s_row[MAX_TOP_K], s_ex[MAX_TOP_K];
+    __shared__ uint32_t s_w[MAX_TOP_K];
     for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
-        int row[MAX_TOP_K], ex[MAX_TOP_K];
-        float w[MAX_TOP_K];
-#pragma unroll
-        for (int k = 0; k < MAX_TOP_K; ++k) {
-            const bool have = k < top_k;
-            row[k] = have ? __ldg(pair_row + static_cast<int64_t>(t) * top_k + k) : 0;
-            ex[k] = have ? __ldg(pair_expert + static_cast<int64_t>(t) * top_k + k) : 0x7fffffff;
-            w[k] = have ? static_cast<float>(pair_weight[static_cast<int64_t>(t) * top_k + k]) : 0.0f;
-        }
-        // odd-even transposition sort by expert (eight fixed rounds: stays in registers); absent slots sort last
-#pragma unroll
-        for (int round = 0; round < MAX_TOP_K; ++round) {
-#pragma unroll
-            for (int k = round & 1; k + 1 < MAX_TOP_K; k += 2) {
-                if (ex[k] > ex[k + 1]) {
-                    const int te = ex[k]; ex[k] = ex[k + 1]; ex[k + 1] = te;
-                    const int tr = row[k]; row[k] = row[k + 1]; row[k + 1] = tr;
-                    const float tw = w[k]; w[k] = w[k + 1]; w[k + 1] = tw;
-                }
+        __syncthreads();                                  // the previous token's slots have been read
+        if (threadIdx.x == 0) {                           // insertion sort of the token's slots by expert
+            for (int k = 0; k < top_k; ++k) {
+                const int64_t i = static_cast<int64_t>(t) * top_k + k;
+                const int e = __ldg(pair_expert + i), r = __ldg(pair_row + i);
+                const uint32_t w = __ldg(pair_weight + i);
+                int j = k;
+                for (; j > 0 && s_ex[j - 1] > e; --j) { s_ex[j] = s_ex[j - 1]; s_row[j] = s_row[j - 1]; s_w[j] = s_w[j - 1]; }
+                s_ex[j] = e; s_row[j] = r; s_w[j] = w | (w << 16);
             }
         }
+        __syncthreads();
         uint4 *dst = reinterpret_cast<uint4 *>(out + t * ld_out_bytes);
         for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            uint32_t acc[4] = {0u, 0u, 0u, 0u};
+            for (int k = 0; k < top_k; ++k) {
+                const uint4 v = ldg_stream(reinterpret_cast<const uint4 *>(y + s_row[k] * ld_y_bytes) + c);
+                const uint4 b = __ldg(reinterpret_cast<const uint4 *>(bias + s_ex[k] * ld_bias_bytes) + c);
+                const P w2 = as_pair<P>(s_w[k]);
+                const uint32_t vv[4] = {v.x, v.y, v.z, v.w}, bb[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-            for (int k = 0; k < MAX_TOP_K; ++k) {
-                if (k < top_k) {
-                    const uint4 v = ldg_stream(reinterpret_cast<const uint4 *>(y + row[k] * ld_y_bytes) + c);
-                    const uint4 b = __ldg(reinterpret_cast<const uint4 *>(bias + ex[k] * ld_bias_bytes) + c);
-                    const uint32_t vv[4] = {v.x, v.y, v.z, v.w}, bb[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float s0 = H::r16(H::r16(H::lo(vv[i]) + H::lo(bb[i])) * w[k]);
-                        const float s1 = H::r16(H::r16(H::hi(vv[i]) + H::hi(bb[i])) * w[k]);
-                        acc[2 * i] = H::r16(acc[2 * i] + s0);
-                        acc[2 * i + 1] = H::r16(acc[2 * i + 1] + s1);
-                    }
-                }
+                for (int i = 0; i < 4; ++i)
+                    acc[i] = as_word(__hadd2_rn(as_pair<P>(acc[i]), __hmul2_rn(__hadd2_rn(as_pair<P>(vv[i]), as_pair<P>(bb[i])), w2)));
             }
-            dst[c] = make_uint4(H::pack(acc[0], acc[1]), H::pack(acc[2], acc[3]), H::pack(acc[4], acc[5]), H::pack(acc[6], acc[7]));
+            dst[c] = make_uint4(acc[0], acc[1], acc[2], acc[3]);
         }
     }
+}
+
+// Threads per CTA for rows of `chunks` 16-byte pieces: the multiple of 32 up to 256 that leaves the fewest
+// idle threads in a row's last round (the larger on a tie).
+inline unsigned threads_for(int chunks) {
+    unsigned best = 256;
+    double best_eff = 0.0;
+    for (unsigned t = 64; t <= 256; t += 32) {
+        const double eff = static_cast<double>(chunks) / (static_cast<double>((chunks + t - 1) / t) * t);
+        if (eff >= best_eff) { best_eff = eff; best = t; }
+    }
+    return best;
 }
 
 inline bool aligned16(const void *p, int64_t ld_bytes) {
@@ -179,7 +197,7 @@ extern "C" int fos_experts_gather_rows(const void *x, int dtype, int64_t ld_x, c
     if (!aligned16(x, ld_x * 2) || !aligned16(out, ld_out * 2)) return FOS_ERR_MISALIGNED;
     const int st = check_device();
     if (st != FOS_OK) return st;
-    gather_rows_kernel<<<grid_for(rows_capacity), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+    gather_rows_kernel<<<grid_for(rows_capacity), threads_for(static_cast<int>(cols / 8)), 0, static_cast<cudaStream_t>(stream_)>>>(
         static_cast<const uint8_t *>(x), ld_x * 2, row_token, static_cast<uint8_t *>(out), ld_out * 2,
         static_cast<int>(rows_capacity), static_cast<int>(cols / 8));
     FOS_CUDA_TRY(cudaGetLastError());
@@ -203,11 +221,11 @@ extern "C" int fos_experts_glu(const void *gate_up, int dtype, int64_t ld_gate_u
     const unsigned g = grid_for(rows_capacity);
     const int rows = static_cast<int>(rows_capacity), chunks = static_cast<int>(intermediate / 8);
     if (dtype == FOS_BF16)
-        glu_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const uint8_t *>(gate_up), ld_gate_up * 2,
+        glu_kernel<__nv_bfloat16><<<g, threads_for(chunks), 0, stream>>>(static_cast<const uint8_t *>(gate_up), ld_gate_up * 2,
                                                            static_cast<const uint8_t *>(bias), 2 * intermediate * 2, row_expert,
                                                            static_cast<uint8_t *>(out), ld_out * 2, rows, chunks, alpha, limit);
     else
-        glu_kernel<__half><<<g, 256, 0, stream>>>(static_cast<const uint8_t *>(gate_up), ld_gate_up * 2,
+        glu_kernel<__half><<<g, threads_for(chunks), 0, stream>>>(static_cast<const uint8_t *>(gate_up), ld_gate_up * 2,
                                                     static_cast<const uint8_t *>(bias), 2 * intermediate * 2, row_expert,
                                                     static_cast<uint8_t *>(out), ld_out * 2, rows, chunks, alpha, limit);
     FOS_CUDA_TRY(cudaGetLastError());
@@ -230,14 +248,14 @@ extern "C" int fos_experts_combine(const void *y, int dtype, int64_t ld_y, const
     const unsigned g = grid_for(tokens);
     const int n = static_cast<int>(tokens), chunks = static_cast<int>(hidden / 8);
     if (dtype == FOS_BF16)
-        combine_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const uint8_t *>(y), ld_y * 2,
+        combine_kernel<__nv_bfloat16><<<g, threads_for(chunks), 0, stream>>>(static_cast<const uint8_t *>(y), ld_y * 2,
                                                                static_cast<const uint8_t *>(bias), hidden * 2, pair_row, pair_expert,
-                                                               static_cast<const __nv_bfloat16 *>(pair_weight), top_k,
+                                                               static_cast<const uint16_t *>(pair_weight), top_k,
                                                                static_cast<uint8_t *>(out), ld_out * 2, n, chunks);
     else
-        combine_kernel<__half><<<g, 256, 0, stream>>>(static_cast<const uint8_t *>(y), ld_y * 2,
+        combine_kernel<__half><<<g, threads_for(chunks), 0, stream>>>(static_cast<const uint8_t *>(y), ld_y * 2,
                                                         static_cast<const uint8_t *>(bias), hidden * 2, pair_row, pair_expert,
-                                                        static_cast<const __half *>(pair_weight), top_k,
+                                                        static_cast<const uint16_t *>(pair_weight), top_k,
                                                         static_cast<uint8_t *>(out), ld_out * 2, n, chunks);
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;

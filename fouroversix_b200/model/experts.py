@@ -79,7 +79,9 @@ class FourOverSixExperts(nn.Module):
         counts = torch.zeros(self.num_experts, dtype=torch.int64, device=flat.device)
         counts.scatter_add_(0, flat, torch.ones_like(flat, dtype=torch.int64))
         layout = GroupLayout.from_counts(counts, pairs)
-        order = torch.argsort(flat, stable=True)
+        # the radix sort makes one pass per byte of the key: sort the narrowest type that holds an expert's index
+        key = torch.uint8 if self.num_experts <= 256 else torch.int16 if self.num_experts <= 32768 else torch.int32
+        order = torch.argsort(flat.to(key), stable=True)
         expert = flat[order]
         first = torch.cumsum(counts, 0) - counts                          # first sorted position of each expert
         rows = layout.group_start.to(torch.int64)[expert] + (torch.arange(pairs, device=flat.device) - first[expert])
