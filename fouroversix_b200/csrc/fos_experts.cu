@@ -151,6 +151,7 @@ combine_kernel(const uint8_t *__restrict__ y, int64_t ld_y_bytes, const uint8_t 
         for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
             uint32_t acc[4] = {0u, 0u, 0u, 0u};
             for (int k = 0; k < top_k; ++k) {
+                if (s_row[k] < 0) continue;               // a slot whose expert index was out of range
                 const uint4 v = ldg_stream(reinterpret_cast<const uint4 *>(y + s_row[k] * ld_y_bytes) + c);
                 const uint4 b = __ldg(reinterpret_cast<const uint4 *>(bias + s_ex[k] * ld_bias_bytes) + c);
                 const P w2 = as_pair<P>(s_w[k]);
@@ -161,6 +162,74 @@ combine_kernel(const uint8_t *__restrict__ y, int64_t ld_y_bytes, const uint8_t 
             }
             dst[c] = make_uint4(acc[0], acc[1], acc[2], acc[3]);
         }
+    }
+}
+
+constexpr int ROUTE_THREADS = 1024, ROUTE_WARPS = ROUTE_THREADS / 32, ROUTE_MAX_EXPERTS = 256;
+
+// The routing tables of one layer call, by one CTA: a stable counting sort of the (token, slot) pairs by expert.
+//   group_rows[e]   pairs routed to expert e           group_start[e]  first row of expert e in the padded buffer
+//   pair_row[p]     the row pair p was given (ascending in p within an expert), -1 for an index outside [0, experts)
+//   row_token[r], row_expert[r]   the token and the expert of row r, -1 for padding rows
+// Pairs are taken 1024 at a time: a warp ranks its 32 pairs among themselves with match_any, the per-warp
+// counts per expert go through shared memory, and a running count per expert carries over to the next round.
+template <typename IDX>
+__global__ void __launch_bounds__(ROUTE_THREADS, 1)
+route_kernel(const IDX *__restrict__ routing, int pairs, int top_k, int experts, int rows_capacity,
+             int32_t *__restrict__ group_start, int32_t *__restrict__ group_rows, int32_t *__restrict__ row_token,
+             int32_t *__restrict__ row_expert, int32_t *__restrict__ pair_row, int32_t *__restrict__ pair_expert) {
+    __shared__ int s_count[ROUTE_MAX_EXPERTS], s_start[ROUTE_MAX_EXPERTS + 1], s_running[2][ROUTE_MAX_EXPERTS];
+    __shared__ uint16_t s_warp[ROUTE_WARPS][ROUTE_MAX_EXPERTS];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < ROUTE_MAX_EXPERTS) { s_count[tid] = 0; s_running[0][tid] = 0; }
+    __syncthreads();
+    for (int p = tid; p < pairs; p += ROUTE_THREADS) {
+        const long long e = static_cast<long long>(routing[p]);
+        if (e >= 0 && e < experts) atomicAdd(&s_count[static_cast<int>(e)], 1);
+    }
+    for (int r = tid; r < rows_capacity; r += ROUTE_THREADS) { row_token[r] = -1; row_expert[r] = -1; }
+    __syncthreads();
+    if (tid == 0) {
+        int at = 0;
+        for (int e = 0; e < experts; ++e) {
+            s_start[e] = at;
+            group_start[e] = at;
+            group_rows[e] = s_count[e];
+            at += (s_count[e] + 127) / 128 * 128;
+        }
+        group_start[experts] = at;
+    }
+    int cur = 0;
+    for (int base = 0; base < pairs; base += ROUTE_THREADS, cur ^= 1) {
+        uint32_t *zero = reinterpret_cast<uint32_t *>(&s_warp[0][0]);
+        for (int i = tid; i < ROUTE_WARPS * ROUTE_MAX_EXPERTS / 2; i += ROUTE_THREADS) zero[i] = 0u;
+        __syncthreads();                                  // also orders s_start and the -1 fill before their use
+        const int p = base + tid;
+        long long idx = -1;
+        if (p < pairs) idx = static_cast<long long>(routing[p]);
+        const int e = (idx >= 0 && idx < experts) ? static_cast<int>(idx) : -1;
+        const uint32_t same = __match_any_sync(0xffffffffu, e);
+        const int rank = __popc(same & ((1u << lane) - 1u));
+        if (e >= 0 && rank == 0) s_warp[warp][e] = static_cast<uint16_t>(__popc(same));
+        __syncthreads();
+        if (e >= 0) {
+            int before = s_running[cur][e];
+            for (int w = 0; w < warp; ++w) before += s_warp[w][e];
+            const int row = s_start[e] + before + rank;
+            pair_row[p] = row;
+            pair_expert[p] = e;
+            row_token[row] = p / top_k;
+            row_expert[row] = e;
+        } else if (p < pairs) {
+            pair_row[p] = -1;
+            pair_expert[p] = -1;
+        }
+        if (tid < experts) {
+            int total = s_running[cur][tid];
+            for (int w = 0; w < ROUTE_WARPS; ++w) total += s_warp[w][tid];
+            s_running[cur ^ 1][tid] = total;
+        }
+        __syncthreads();
     }
 }
 
@@ -257,6 +326,33 @@ extern "C" int fos_experts_combine(const void *y, int dtype, int64_t ld_y, const
                                                         static_cast<const uint8_t *>(bias), hidden * 2, pair_row, pair_expert,
                                                         static_cast<const uint16_t *>(pair_weight), top_k,
                                                         static_cast<uint8_t *>(out), ld_out * 2, n, chunks);
+    FOS_CUDA_TRY(cudaGetLastError());
+    return FOS_OK;
+}
+
+extern "C" int fos_experts_route(const void *routing_indices, int index_bytes, int64_t tokens, int top_k, int num_experts,
+                                 int64_t rows_capacity, int32_t *group_start, int32_t *group_rows, int32_t *row_token,
+                                 int32_t *row_expert, int32_t *pair_row, int32_t *pair_expert, void *stream_) {
+    using namespace fos;
+    if (!routing_indices || !group_start || !group_rows || !row_token || !row_expert || !pair_row || !pair_expert ||
+        tokens <= 0 || top_k <= 0 || num_experts <= 0 || (index_bytes != 4 && index_bytes != 8))
+        return FOS_ERR_INVALID_ARGUMENT;
+    if (num_experts > ROUTE_MAX_EXPERTS) return FOS_ERR_UNSUPPORTED;
+    const int64_t pairs = tokens * top_k;
+    if (pairs >= (int64_t(1) << 30) || rows_capacity >= (int64_t(1) << 31)) return FOS_ERR_TOO_LARGE;
+    if (rows_capacity % 128 != 0 || rows_capacity < round_up64(pairs + 127 * static_cast<int64_t>(num_experts), 128))
+        return FOS_ERR_INVALID_ARGUMENT;
+    const int st = check_device();
+    if (st != FOS_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (index_bytes == 8)
+        route_kernel<int64_t><<<1, ROUTE_THREADS, 0, stream>>>(static_cast<const int64_t *>(routing_indices), static_cast<int>(pairs),
+                                                               top_k, num_experts, static_cast<int>(rows_capacity), group_start,
+                                                               group_rows, row_token, row_expert, pair_row, pair_expert);
+    else
+        route_kernel<int32_t><<<1, ROUTE_THREADS, 0, stream>>>(static_cast<const int32_t *>(routing_indices), static_cast<int>(pairs),
+                                                               top_k, num_experts, static_cast<int>(rows_capacity), group_start,
+                                                               group_rows, row_token, row_expert, pair_row, pair_expert);
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;
 }

@@ -95,12 +95,11 @@ class FourOverSixExperts(nn.Module):
         down, gate_up = self.quantized_weights()
         act_config = self.config.get_activation_config()
         out_dtype = self.config.output_dtype
+        if self._native_elementwise(x, routing_weights, out_dtype):
+            return self._forward_native(x, routing_indices, routing_weights).reshape(shape)
+
         layout, rows, token, order = self.route(routing_indices)
         expert = routing_indices.reshape(-1)[order]
-
-        if self._native_elementwise(x, routing_weights, out_dtype):
-            return self._forward_native(x, layout, rows, token, order, expert, routing_indices, routing_weights).reshape(shape)
-
         padded = torch.zeros(layout.capacity, self.hidden_size, dtype=x.dtype, device=x.device)
         padded[rows] = x[token]
         gu = grouped_quantized_matmul(grouped_quantize(padded, layout, act_config), gate_up, out_dtype=out_dtype)
@@ -127,25 +126,43 @@ class FourOverSixExperts(nn.Module):
         return (same and x.dtype in (torch.bfloat16, torch.float16) and self.hidden_size % 8 == 0
                 and self.intermediate_size % 8 == 0 and routing_weights.shape[-1] <= 8)
 
-    def _forward_native(self, x, layout, rows, token, order, expert, routing_indices, routing_weights) -> torch.Tensor:
-        """The same layer with `fos_experts_gather_rows`, `fos_experts_glu` and `fos_experts_combine` between the
-        grouped launches: bit-equal to the tensor-operation form when a token has at most two experts, and to the
-        reference's host loop (which adds a token's experts in ascending order) for any number."""
+    def route_native(self, routing_indices: torch.Tensor) -> tuple[GroupLayout, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+        """`fos_experts_route`: the row layout and the tables of the element-wise kernels (row -> token, row ->
+        expert, pair -> row, pair -> expert) in one launch."""
+        tokens, top_k = routing_indices.shape
+        dev = routing_indices.device
+        if routing_indices.dtype not in (torch.int32, torch.int64):
+            routing_indices = routing_indices.to(torch.int64)
+        routing_indices = routing_indices.contiguous()
+        capacity = (tokens * top_k + 127 * self.num_experts + 127) // 128 * 128
+        tables = torch.empty(2 * self.num_experts + 1 + 2 * capacity + 2 * tokens * top_k, dtype=torch.int32, device=dev)
+        group_start, group_rows, row_token, row_expert, pair_row, pair_expert = torch.split(
+            tables, [self.num_experts + 1, self.num_experts, capacity, capacity, tokens * top_k, tokens * top_k])
+        _native.check(_native.lib().fos_experts_route(
+            routing_indices.data_ptr(), routing_indices.element_size(), tokens, top_k, self.num_experts, capacity,
+            group_start.data_ptr(), group_rows.data_ptr(), row_token.data_ptr(), row_expert.data_ptr(),
+            pair_row.data_ptr(), pair_expert.data_ptr(), _native.stream_ptr(dev)), "fos_experts_route")
+        return GroupLayout(group_start, group_rows, capacity, self.num_experts), row_token, row_expert, pair_row, pair_expert
+
+    def _forward_native(self, x: torch.Tensor, routing_indices: torch.Tensor, routing_weights: torch.Tensor) -> torch.Tensor:
+        """The same layer on `fos_experts_route`, `fos_experts_gather_rows`, `fos_experts_glu` and
+        `fos_experts_combine` around the grouped launches (nine launches in all): bit-equal to the
+        tensor-operation form when a token has at most two experts, and to the reference's host loop (which adds
+        a token's experts in ascending order) for any number."""
         down, gate_up = self.quantized_weights()
         act_config = self.config.get_activation_config()
         out_dtype = self.config.output_dtype
         dev, dtype, code = x.device, x.dtype, _native.elem_code(x.dtype)
-        lib, stream = _native.lib(), _native.stream_ptr(x.device)
         tokens, top_k = routing_indices.shape
         x = x if x.stride(-1) == 1 else x.contiguous()
-        rows32 = rows.to(torch.int32)
-        row_token = torch.full((layout.capacity,), -1, dtype=torch.int32, device=dev)
-        row_token[rows] = token.to(torch.int32)
-        row_expert = torch.full((layout.capacity,), -1, dtype=torch.int32, device=dev)
-        row_expert[rows] = expert.to(torch.int32)
-        pair_row = torch.empty(tokens * top_k, dtype=torch.int32, device=dev)
-        pair_row[order] = rows32
-        pair_expert = routing_indices.reshape(-1).to(torch.int32)
+        with torch.cuda.device(dev):
+            return self._run_native(x, routing_indices, routing_weights, down, gate_up, act_config, out_dtype, dev, dtype,
+                                    code, tokens, top_k)
+
+    def _run_native(self, x, routing_indices, routing_weights, down, gate_up, act_config, out_dtype, dev, dtype, code,
+                    tokens, top_k) -> torch.Tensor:
+        lib, stream = _native.lib(), _native.stream_ptr(dev)
+        layout, row_token, row_expert, pair_row, pair_expert = self.route_native(routing_indices)
         weights = routing_weights.reshape(-1).contiguous()
         gate_up_bias, down_bias = self.gate_up_proj_bias.contiguous(), self.down_proj_bias.contiguous()
 

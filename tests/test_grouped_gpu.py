@@ -243,3 +243,37 @@ def test_gather_and_combine_kernels():
         sel = (flat_e == e).nonzero().reshape(-1)
         want.index_add_(0, token[sel], (y[pair_row[sel].long()] + bias[e]) * weight[sel, None])
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("index_dtype", [torch.int64, torch.int32], ids=["int64", "int32"])
+@pytest.mark.parametrize("tokens,top_k,experts", [(300, 2, 8), (8192, 4, 32), (5, 1, 256), (1500, 8, 13)])
+def test_route_kernel_tables(tokens, top_k, experts, index_dtype):
+    """fos_experts_route against counts, a padded running sum and the definition of its tables."""
+    g = torch.Generator().manual_seed(tokens + experts)
+    scores = torch.rand(tokens, experts, generator=g)
+    if experts > 2:
+        scores[:, 1] = -1                                         # an expert nobody is routed to
+    indices = torch.topk(scores, top_k, dim=-1).indices.to(index_dtype).to(DEV)
+    layer = FourOverSixExperts.__new__(FourOverSixExperts)
+    torch.nn.Module.__init__(layer)
+    layer.num_experts = experts
+    layout, row_token, row_expert, pair_row, pair_expert = layer.route_native(indices)
+    flat = indices.reshape(-1).long()
+    counts = torch.bincount(flat, minlength=experts)
+    assert torch.equal(layout.group_rows.long(), counts)
+    padded = (counts + 127) // 128 * 128
+    assert torch.equal(layout.group_start.long(), torch.cat([torch.zeros(1, dtype=torch.int64, device=DEV), padded.cumsum(0)]))
+    assert layout.capacity % 128 == 0 and layout.capacity >= int(padded.sum())
+    assert torch.equal(pair_expert.long(), flat)
+    rows = pair_row.long()
+    start = layout.group_start.long()[flat]
+    assert ((rows >= start) & (rows < start + counts[flat])).all()
+    assert rows.unique().numel() == rows.numel()
+    assert torch.equal(row_expert[rows].long(), flat)
+    assert torch.equal(row_token[rows].long(), torch.arange(flat.numel(), device=DEV) // top_k)
+    other = torch.ones(layout.capacity, dtype=torch.bool, device=DEV)
+    other[rows] = False
+    assert (row_token[other] == -1).all() and (row_expert[other] == -1).all()
+    for e in range(experts):                                      # stable: ascending pairs get ascending rows
+        mine = rows[flat == e]
+        assert (mine[1:] > mine[:-1]).all()
