@@ -796,6 +796,14 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], const Tenso
             return;
         }
 
+        if (!TWO_D && s_a == 0.0f && s_b == 0.0f) {
+            // an all-zero block (or one whose scales underflow to zero): nothing is encoded and both candidates
+            // carry a zero scale byte, whichever wins; padding rows of grouped tensors are full of these
+            lo = 0u;
+            hi = 0u;
+            sf_byte = sfb_a;
+            return;
+        }
         uint32_t lo_a = 0u, hi_a = 0u, lo_b = 0u, hi_b = 0u;
         if (s_a != 0.0f) encode_e2m1(v, r_a, true, lo_a, hi_a);
         if (s_b != 0.0f) encode_e2m1(v, r_b, true, lo_b, hi_b);
@@ -1616,13 +1624,20 @@ quantize_rows_mse_kernel(const __grid_constant__ CUtensorMap map_x, const QuantP
                     }
                 }
                 if (undecided && !coop_ok) {
-                    Block16 blk;
+                    if (both == 0u) {
+                        // both scales are zero (an all-zero block: the padding rows of grouped tensors are full
+                        // of them): the exact sequence encodes nothing and picks between two zero scale bytes
+                        lo = 0u;
+                        hi = 0u;
+                    } else {
+                        Block16 blk;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) blk.v[i] = v[i];
-                    const uint4 r = exact_pick_nvfp4(blk, ea.x, ea.y, eb.x, eb.y, tc.amax, rule, both & 0xffu, both >> 8);
-                    lo = r.x;
-                    hi = r.y;
-                    sf_byte = r.z;
+                        for (int i = 0; i < 16; ++i) blk.v[i] = v[i];
+                        const uint4 r = exact_pick_nvfp4(blk, ea.x, ea.y, eb.x, eb.y, tc.amax, rule, both & 0xffu, both >> 8);
+                        lo = r.x;
+                        hi = r.y;
+                        sf_byte = r.z;
+                    }
                 }
             }
             *reinterpret_cast<uint2 *>(codes + j * code_half) = make_uint2(lo, hi);
