@@ -345,6 +345,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     pipeline["pseudo_quantize"] = {"ms": t, "GB/s": 4.0 * n_elem / (t * 1e-3) / 1e9,
                                    "note": "fused fake quantization, 2 B read + 2 B written per element"}
     del q_sets
+    if world == 1:
+        pipeline["experts_layer"] = experts_pipeline(dev, max(args.steps, 10))
 
     cpu = cpu_baseline_quantize(a_cpu) if world == 1 else None
 
@@ -724,6 +726,29 @@ def run_case(args) -> None:
     ms = timed(lambda: B200MatmulBackend.quantized_matmul(qa, qb, out_dtype=fos.DataType.bfloat16, out=out, variant=args.variant))
     print(f"gemm {args.m}x{args.n}x{args.k} {args.dtype} variant {args.variant}: {ms * 1e3:.1f} us per call, "
           f"{2.0 * args.m * args.n * args.k / (ms * 1e-3) / 1e12:.0f} TFLOP/s")
+
+
+def experts_pipeline(dev, steps: int) -> dict:
+    """The grouped experts layer (32 experts of GPT-OSS-20B shape, 4 per token, uniformly random routing) as CUDA-graph
+    replays: routing tables, gather, 2 x (amax, quantize, alpha, grouped GEMM), SwiGLU, combine - twelve kernels of the
+    library and no read-back."""
+    from fouroversix_b200.model import FourOverSixExperts
+
+    e, h, i, top_k = 32, 2880, 2880, 4
+    g = torch.Generator(device=dev).manual_seed(0)
+    layer = FourOverSixExperts(
+        (torch.randn(e, 2 * i, h, generator=g, device=dev) * 0.02).bfloat16(),
+        (torch.randn(e, 2 * i, generator=g, device=dev) * 0.02).bfloat16(),
+        (torch.randn(e, h, i, generator=g, device=dev) * 0.02).bfloat16(),
+        (torch.randn(e, h, generator=g, device=dev) * 0.02).bfloat16())
+    out = {"experts": e, "top_k": top_k, "hidden": h, "intermediate": i}
+    for tokens in (256, 8192):
+        x = torch.randn(tokens, h, generator=g, device=dev).bfloat16()
+        weights, indices = torch.topk(torch.softmax(torch.randn(tokens, e, generator=g, device=dev), -1), top_k, dim=-1)
+        weights = weights.bfloat16()
+        ms = time_graphs(lambda _: layer(x, indices, weights), 1, steps, 3)
+        out[f"tokens_{tokens}"] = {"ms": round(ms, 4), "tflops": round(2.0 * tokens * top_k * 3 * i * h / (ms * 1e-3) / 1e12, 1)}
+    return out
 
 
 def experts_case(args, timed) -> dict:

@@ -146,7 +146,7 @@ class FourOverSixExperts(nn.Module):
 
     def _forward_native(self, x: torch.Tensor, routing_indices: torch.Tensor, routing_weights: torch.Tensor) -> torch.Tensor:
         """The same layer on `fos_experts_route`, `fos_experts_gather_rows`, `fos_experts_glu` and
-        `fos_experts_combine` around the grouped launches (nine launches in all): bit-equal to the
+        `fos_experts_combine` around the grouped launches (twelve kernels in all): bit-equal to the
         tensor-operation form when a token has at most two experts, and to the reference's host loop (which adds
         a token's experts in ascending order) for any number."""
         down, gate_up = self.quantized_weights()
