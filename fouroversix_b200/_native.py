@@ -71,9 +71,9 @@ SIGNATURES = {
                                         _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr]),
     "fos_experts_route": (_c_int, [_c_ptr, _c_int, _c_i64, _c_int, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                                    _c_ptr]),
-    "fos_experts_gather_rows": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr]),
+    "fos_experts_gather_rows": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr]),
     "fos_experts_glu": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, ctypes.c_float,
-                                 ctypes.c_float, _c_ptr]),
+                                 ctypes.c_float, _c_ptr, _c_ptr]),
     "fos_experts_combine": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_i64, _c_i64,
                                      _c_i64, _c_ptr]),
     "fos_gemm_mxfp4": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_i64, _c_i64,

@@ -46,16 +46,55 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
     return v;
 }
 
+// max |value| of the eight 16-bit numbers of a 16-byte piece, folded into a running packed maximum
+// (NaNs are skipped, as fmaxf skips them in the amax pass of the quantization).
+template <typename P> __device__ __forceinline__ P fold_abs_max(P m, uint4 v) {
+    m = __hmax2(m, __habs2(as_pair<P>(v.x)));
+    m = __hmax2(m, __habs2(as_pair<P>(v.y)));
+    m = __hmax2(m, __habs2(as_pair<P>(v.z)));
+    return __hmax2(m, __habs2(as_pair<P>(v.w)));
+}
+
+// The CTA's maximum of the threads' packed running maxima, raised into amax[0] (a non-negative float, zeroed by the
+// caller before the launch, compared as an integer). The words written are the ones the grouped amax pass would
+// write: the largest magnitude of the group's values, exactly, as a float. Called by all threads of the CTA.
+template <typename T>
+__device__ __forceinline__ void raise_amax(typename Half16<T>::Pair m2, float *amax, float *warp_max) {
+    using H = Half16<T>;
+    float m = fmaxf(H::lo(as_word(m2)), H::hi(as_word(m2)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __syncthreads();                                      // the previous row's values have been read
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w) m = fmaxf(m, warp_max[w]);
+        // (a stale smaller value read here only costs an atomic that changes nothing)
+        if (m > 0.0f && m > *reinterpret_cast<volatile float *>(amax)) atomicMax(reinterpret_cast<int *>(amax), __float_as_int(m));
+    }
+}
+
 // out[r] = x[row_token[r]], or zeros where row_token[r] < 0. One CTA per row at a time, 16 bytes per thread.
+// With amax != nullptr also amax[row_expert[r]] = max(amax[..], max |out[r]|): the per-expert maxima the grouped
+// quantization of `out` needs, so that it can skip its own pass over the buffer.
+template <typename T>
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint8_t *__restrict__ x, int64_t ld_x_bytes, const int32_t *__restrict__ row_token,
-                   uint8_t *__restrict__ out, int64_t ld_out_bytes, int rows, int chunks) {
+                   uint8_t *__restrict__ out, int64_t ld_out_bytes, int rows, int chunks,
+                   const int32_t *__restrict__ row_expert, float *__restrict__ amax) {
+    using P = typename Half16<T>::Pair;
+    __shared__ float warp_max[8];
     for (int r = blockIdx.x; r < rows; r += gridDim.x) {
         const int t = __ldg(row_token + r);
         const uint4 *src = reinterpret_cast<const uint4 *>(x + static_cast<int64_t>(t < 0 ? 0 : t) * ld_x_bytes);
         uint4 *dst = reinterpret_cast<uint4 *>(out + r * ld_out_bytes);
-        for (int c = threadIdx.x; c < chunks; c += blockDim.x)
-            dst[c] = t < 0 ? make_uint4(0u, 0u, 0u, 0u) : __ldg(src + c);
+        P m2 = as_pair<P>(0u);
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+            const uint4 v = t < 0 ? make_uint4(0u, 0u, 0u, 0u) : __ldg(src + c);
+            dst[c] = v;
+            m2 = fold_abs_max<P>(m2, v);
+        }
+        if (amax != nullptr && t >= 0) raise_amax<T>(m2, amax + __ldg(row_expert + r), warp_max);
     }
 }
 
@@ -92,9 +131,10 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 glu_kernel(const uint8_t *__restrict__ gate_up, int64_t ld_gu_bytes, const uint8_t *__restrict__ bias, int64_t ld_bias_bytes,
            const int32_t *__restrict__ row_expert, uint8_t *__restrict__ out, int64_t ld_out_bytes, int rows, int chunks,
-           float alpha, float limit) {
+           float alpha, float limit, float *__restrict__ amax) {
     using H = Half16<T>;
     using P = typename H::Pair;
+    __shared__ float warp_max[8];
     const float r = H::r16(limit);
     const P limit2 = as_pair<P>(H::pack(r, r)), floor2 = as_pair<P>(H::pack(-INFINITY, -r)), tail2 = as_pair<P>(H::pack(1.0f, 1.0f));
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -106,6 +146,7 @@ glu_kernel(const uint8_t *__restrict__ gate_up, int64_t ld_gu_bytes, const uint8
         }
         const uint4 *src = reinterpret_cast<const uint4 *>(gate_up + row * ld_gu_bytes);
         const uint4 *b = reinterpret_cast<const uint4 *>(bias + e * ld_bias_bytes);
+        P m2 = as_pair<P>(0u);
         for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
             const uint4 v0 = ldg_stream(src + 2 * c), v1 = ldg_stream(src + 2 * c + 1);
             const uint4 b0 = __ldg(b + 2 * c), b1 = __ldg(b + 2 * c + 1);
@@ -114,9 +155,12 @@ glu_kernel(const uint8_t *__restrict__ gate_up, int64_t ld_gu_bytes, const uint8
             uint32_t o[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[i] = glu_word<T>(v[i], bb[i], alpha, limit2, floor2, tail2);
-            dst[c] = make_uint4(__byte_perm(o[0], o[1], 0x5410), __byte_perm(o[2], o[3], 0x5410),
-                                __byte_perm(o[4], o[5], 0x5410), __byte_perm(o[6], o[7], 0x5410));
+            const uint4 packed = make_uint4(__byte_perm(o[0], o[1], 0x5410), __byte_perm(o[2], o[3], 0x5410),
+                                            __byte_perm(o[4], o[5], 0x5410), __byte_perm(o[6], o[7], 0x5410));
+            dst[c] = packed;
+            m2 = fold_abs_max<P>(m2, packed);
         }
+        if (amax != nullptr) raise_amax<T>(m2, amax + e, warp_max);     // (e is the same for the whole CTA: no divergence)
     }
 }
 
@@ -258,24 +302,33 @@ inline unsigned grid_for(int64_t rows) {
 }  // namespace fos
 
 extern "C" int fos_experts_gather_rows(const void *x, int dtype, int64_t ld_x, const int32_t *row_token, void *out,
-                                       int64_t ld_out, int64_t rows_capacity, int64_t cols, void *stream_) {
+                                       int64_t ld_out, int64_t rows_capacity, int64_t cols, const int32_t *row_expert,
+                                       float *amax, void *stream_) {
     using namespace fos;
     if (!x || !row_token || !out || rows_capacity <= 0 || cols <= 0 || ld_x < cols || ld_out < cols) return FOS_ERR_INVALID_ARGUMENT;
+    if ((amax != nullptr) != (row_expert != nullptr)) return FOS_ERR_INVALID_ARGUMENT;
     if (dtype != FOS_BF16 && dtype != FOS_FP16) return FOS_ERR_UNSUPPORTED;
     if (cols % 8 != 0 || rows_capacity >= (int64_t(1) << 31)) return FOS_ERR_UNSUPPORTED;
     if (!aligned16(x, ld_x * 2) || !aligned16(out, ld_out * 2)) return FOS_ERR_MISALIGNED;
     const int st = check_device();
     if (st != FOS_OK) return st;
-    gather_rows_kernel<<<grid_for(rows_capacity), threads_for(static_cast<int>(cols / 8)), 0, static_cast<cudaStream_t>(stream_)>>>(
-        static_cast<const uint8_t *>(x), ld_x * 2, row_token, static_cast<uint8_t *>(out), ld_out * 2,
-        static_cast<int>(rows_capacity), static_cast<int>(cols / 8));
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const unsigned g = grid_for(rows_capacity), threads = threads_for(static_cast<int>(cols / 8));
+    if (dtype == FOS_BF16)
+        gather_rows_kernel<__nv_bfloat16><<<g, threads, 0, stream>>>(static_cast<const uint8_t *>(x), ld_x * 2, row_token,
+                                                                     static_cast<uint8_t *>(out), ld_out * 2, static_cast<int>(rows_capacity),
+                                                                     static_cast<int>(cols / 8), row_expert, amax);
+    else
+        gather_rows_kernel<__half><<<g, threads, 0, stream>>>(static_cast<const uint8_t *>(x), ld_x * 2, row_token,
+                                                              static_cast<uint8_t *>(out), ld_out * 2, static_cast<int>(rows_capacity),
+                                                              static_cast<int>(cols / 8), row_expert, amax);
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;
 }
 
 extern "C" int fos_experts_glu(const void *gate_up, int dtype, int64_t ld_gate_up, const void *bias, const int32_t *row_expert,
                                void *out, int64_t ld_out, int64_t rows_capacity, int64_t intermediate, float alpha,
-                               float limit, void *stream_) {
+                               float limit, float *amax, void *stream_) {
     using namespace fos;
     if (!gate_up || !bias || !row_expert || !out || rows_capacity <= 0 || intermediate <= 0 ||
         ld_gate_up < 2 * intermediate || ld_out < intermediate)
@@ -292,11 +345,11 @@ extern "C" int fos_experts_glu(const void *gate_up, int dtype, int64_t ld_gate_u
     if (dtype == FOS_BF16)
         glu_kernel<__nv_bfloat16><<<g, threads_for(chunks), 0, stream>>>(static_cast<const uint8_t *>(gate_up), ld_gate_up * 2,
                                                            static_cast<const uint8_t *>(bias), 2 * intermediate * 2, row_expert,
-                                                           static_cast<uint8_t *>(out), ld_out * 2, rows, chunks, alpha, limit);
+                                                           static_cast<uint8_t *>(out), ld_out * 2, rows, chunks, alpha, limit, amax);
     else
         glu_kernel<__half><<<g, threads_for(chunks), 0, stream>>>(static_cast<const uint8_t *>(gate_up), ld_gate_up * 2,
                                                     static_cast<const uint8_t *>(bias), 2 * intermediate * 2, row_expert,
-                                                    static_cast<uint8_t *>(out), ld_out * 2, rows, chunks, alpha, limit);
+                                                    static_cast<uint8_t *>(out), ld_out * 2, rows, chunks, alpha, limit, amax);
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;
 }

@@ -146,7 +146,7 @@ class FourOverSixExperts(nn.Module):
 
     def _forward_native(self, x: torch.Tensor, routing_indices: torch.Tensor, routing_weights: torch.Tensor) -> torch.Tensor:
         """The same layer on `fos_experts_route`, `fos_experts_gather_rows`, `fos_experts_glu` and
-        `fos_experts_combine` around the grouped launches (twelve kernels in all): bit-equal to the
+        `fos_experts_combine` around the grouped launches (ten kernels in all): bit-equal to the
         tensor-operation form when a token has at most two experts, and to the reference's host loop (which adds
         a token's experts in ascending order) for any number."""
         down, gate_up = self.quantized_weights()
@@ -166,19 +166,21 @@ class FourOverSixExperts(nn.Module):
         weights = routing_weights.reshape(-1).contiguous()
         gate_up_bias, down_bias = self.gate_up_proj_bias.contiguous(), self.down_proj_bias.contiguous()
 
+        # the kernels that fill the two padded buffers also leave their per-expert maxima (no amax pass of its own)
+        amax = torch.zeros(2, self.num_experts, dtype=torch.float32, device=dev)
         padded = torch.empty(layout.capacity, self.hidden_size, dtype=dtype, device=dev)
         _native.check(lib.fos_experts_gather_rows(x.data_ptr(), code, x.stride(0), row_token.data_ptr(), padded.data_ptr(),
-                                                  padded.stride(0), layout.capacity, self.hidden_size, stream),
-                      "fos_experts_gather_rows")
+                                                  padded.stride(0), layout.capacity, self.hidden_size, row_expert.data_ptr(),
+                                                  amax[0].data_ptr(), stream), "fos_experts_gather_rows")
         # padding rows of the two GEMM outputs are neither written nor read: no zero fill
         gu = torch.empty(layout.capacity, 2 * self.intermediate_size, dtype=dtype, device=dev)
-        grouped_quantized_matmul(grouped_quantize(padded, layout, act_config), gate_up, out_dtype=out_dtype, out=gu)
+        grouped_quantized_matmul(grouped_quantize(padded, layout, act_config, amax=amax[0]), gate_up, out_dtype=out_dtype, out=gu)
         gated = torch.empty(layout.capacity, self.intermediate_size, dtype=dtype, device=dev)
         _native.check(lib.fos_experts_glu(gu.data_ptr(), code, gu.stride(0), gate_up_bias.data_ptr(), row_expert.data_ptr(),
                                           gated.data_ptr(), gated.stride(0), layout.capacity, self.intermediate_size,
-                                          float(self.alpha), float(self.limit), stream), "fos_experts_glu")
+                                          float(self.alpha), float(self.limit), amax[1].data_ptr(), stream), "fos_experts_glu")
         y = torch.empty(layout.capacity, self.hidden_size, dtype=dtype, device=dev)
-        grouped_quantized_matmul(grouped_quantize(gated, layout, act_config), down, out_dtype=out_dtype, out=y)
+        grouped_quantized_matmul(grouped_quantize(gated, layout, act_config, amax=amax[1]), down, out_dtype=out_dtype, out=y)
         result = torch.empty(tokens, self.hidden_size, dtype=dtype, device=dev)
         _native.check(lib.fos_experts_combine(y.data_ptr(), code, y.stride(0), down_bias.data_ptr(), pair_row.data_ptr(),
                                               pair_expert.data_ptr(), weights.data_ptr(), top_k, result.data_ptr(),

@@ -270,6 +270,10 @@ int fos_gemm_nvfp4_grouped(const uint8_t *a_codes, const uint8_t *a_sf, const ui
  * fos_experts_gather_rows: out[r][0..cols) = x[row_token[r]][0..cols), zeros where row_token[r] < 0
  *   (row_token: rows_capacity int32 values in device memory). Fills the padded row buffer fos_quantize_grouped
  *   reads, padding rows included.
+ * Both of the calls above and below that write such a buffer can also leave its per-expert maxima: with amax != NULL
+ *   (num_experts floats, ZEROED by the caller in the stream before the call; gather_rows then also needs
+ *   row_expert) amax[e] is raised to the largest |value| written for expert e - the words fos_quantize_grouped
+ *   computes in a pass of its own unless they are handed to it as amax_in.
  * fos_experts_glu: gate_up [rows_capacity][2 * intermediate] with gate in the even and up in the odd columns,
  *   bias [experts][2 * intermediate], row_expert[r] the expert of row r or < 0 for a padding row (whose output row
  *   is zeros and whose input is not read):
@@ -298,10 +302,11 @@ int fos_experts_route(const void *routing_indices, int index_bytes, int64_t toke
                       int64_t rows_capacity, int32_t *group_start, int32_t *group_rows, int32_t *row_token,
                       int32_t *row_expert, int32_t *pair_row, int32_t *pair_expert, void *stream);
 int fos_experts_gather_rows(const void *x, int dtype, int64_t ld_x, const int32_t *row_token, void *out,
-                            int64_t ld_out, int64_t rows_capacity, int64_t cols, void *stream);
+                            int64_t ld_out, int64_t rows_capacity, int64_t cols, const int32_t *row_expert, float *amax,
+                            void *stream);
 int fos_experts_glu(const void *gate_up, int dtype, int64_t ld_gate_up, const void *bias, const int32_t *row_expert,
                     void *out, int64_t ld_out, int64_t rows_capacity, int64_t intermediate, float alpha, float limit,
-                    void *stream);
+                    float *amax, void *stream);
 int fos_experts_combine(const void *y, int dtype, int64_t ld_y, const void *bias, const int32_t *pair_row,
                         const int32_t *pair_expert, const void *pair_weight, int top_k, void *out, int64_t ld_out,
                         int64_t tokens, int64_t hidden, void *stream);

@@ -199,15 +199,19 @@ def test_glu_kernel_keeps_every_rounding_of_the_operation_chain(dtype):
     row_expert = (torch.arange(rows, device=DEV) % 4 - 1).to(torch.int32)          # -1: a padding row
     for alpha, limit in ((1.702, 7.0), (0.3333, 2.7182818)):
         out = torch.full((rows, inter), 9, dtype=dtype, device=DEV)
+        amax = torch.zeros(3, dtype=torch.float32, device=DEV)
         _native.check(_native.lib().fos_experts_glu(gu.data_ptr(), _native.elem_code(dtype), gu.stride(0), bias.data_ptr(),
                                                     row_expert.data_ptr(), out.data_ptr(), out.stride(0), rows, inter,
-                                                    alpha, limit, _native.stream_ptr(gu.device)), "fos_experts_glu")
+                                                    alpha, limit, amax.data_ptr(), _native.stream_ptr(gu.device)), "fos_experts_glu")
         real = row_expert >= 0
         want = _op_chain_glu(gu[real], bias[row_expert[real].long()], alpha, limit)
         assert (out[~real] == 0).all()
         got = out[real]
         same = (got == want) | (got.isnan() & want.isnan())
         assert same.all(), (alpha, limit, int((~same).sum()))
+        for e in range(3):                                        # the per-expert maxima, NaNs skipped
+            mine = out[row_expert == e].float().abs()
+            assert amax[e].item() == mine[~mine.isnan()].max().item()
 
 
 def test_gather_and_combine_kernels():
@@ -223,10 +227,19 @@ def test_gather_and_combine_kernels():
     row_token[rows] = (torch.arange(tokens * top_k) // top_k).to(torch.int32)
     row_token = row_token.to(DEV)
     out = torch.full((cap, hidden), 5, dtype=torch.bfloat16, device=DEV)
+    row_expert = torch.where(row_token >= 0, row_token % experts, row_token)
+    amax = torch.zeros(experts, dtype=torch.float32, device=DEV)
     _native.check(lib.fos_experts_gather_rows(x.data_ptr(), code, x.stride(0), row_token.data_ptr(), out.data_ptr(),
-                                              out.stride(0), cap, hidden, _native.stream_ptr(x.device)), "gather")
+                                              out.stride(0), cap, hidden, row_expert.data_ptr(), amax.data_ptr(),
+                                              _native.stream_ptr(x.device)), "gather")
     want = torch.where(row_token[:, None] >= 0, x[row_token.clamp(min=0).long()], torch.zeros_like(out))
     assert torch.equal(out, want)
+    for e in range(experts):
+        assert amax[e].item() == want[row_expert == e].float().abs().max().item()
+    out2 = torch.empty_like(out)
+    _native.check(lib.fos_experts_gather_rows(x.data_ptr(), code, x.stride(0), row_token.data_ptr(), out2.data_ptr(),
+                                              out2.stride(0), cap, hidden, 0, 0, _native.stream_ptr(x.device)), "gather")
+    assert torch.equal(out2, want)
 
     y = torch.randn(cap, hidden, generator=g).bfloat16().to(DEV)
     bias = torch.randn(experts, hidden, generator=g).bfloat16().to(DEV)
