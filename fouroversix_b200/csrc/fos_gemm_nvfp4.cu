@@ -568,6 +568,17 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 if (row_ok && left > 0) {
                     OUT *dst = out + row * p.ldd + n0;
                     if (left >= COLS && vec32_ok) {
+#ifdef FOS_GEMM_DEBUG
+                        if (p.debug & 8) {
+                            // timing experiment (values land in the wrong places): the same bytes stored so that
+                            // every instruction of the warp fills four whole 256-byte row segments
+                            uint8_t *wbase = reinterpret_cast<uint8_t *>(out + (row - lane) * p.ldd + n0);
+#pragma unroll
+                            for (int i = 0; i < COLS / 16; ++i)
+                                if (row - lane + 4 * i + (lane >> 3) < row_end)
+                                    stg_32_stream(wbase + (4 * i + (lane >> 3)) * p.ldd * sizeof(OUT) + (lane & 7) * 32, &pk[8 * i]);
+                        } else
+#endif
                         // 32 bytes per store: every instruction of the warp fills whole 32-byte sectors
 #pragma unroll
                         for (int i = 0; i < COLS / 16; ++i) stg_32_stream(reinterpret_cast<uint8_t *>(dst) + 32 * i, &pk[8 * i]);
