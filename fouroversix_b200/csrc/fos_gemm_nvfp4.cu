@@ -680,9 +680,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 //   full[s]      leader's barrier: one arrive.expect_tx by the leader's producer for the bytes of
 //                BOTH CTAs; the peer's TMA loads complete on it too (cta_group::2 form of the copy)
 //   empty[s]     one per CTA, released in both CTAs by the leader's multicast tcgen05.commit
-//   sf_full[j]   leader's barrier: the scale tiles of both CTAs have landed (each in its own CTA's
-//                shared memory), announced and completed like full[s]
-//   sf_ready[j]  leader's barrier: the leader's copying thread has moved the slot's scales into
+//   sf_full[w][j] leader's barriers, one per (copying warp, slot) as in the single-CTA kernel: the scale
+//                tiles of both CTAs have landed (each in its own CTA's shared memory), announced and
+//                completed like full[s]
+//   sf_ready[j]  leader's barrier: one of the leader's two copying warps has moved the slot's scales into
 //                the tensor memory of both CTAs (tcgen05.cp with cta_group::2, one commit)
 //   acc_full     one per CTA, multicast commit
 //   acc_empty    leader's barrier, 16 arrivals: 8 epilogue warps of each CTA
@@ -701,13 +702,14 @@ constexpr int STAGES = 6;
 constexpr int SF_SLOTS = 5;                                               // what tensor memory has room for
 constexpr int BARRIER_BYTES = 512;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SF_SLOTS * SF_SLOT_BYTES + 1024 + BARRIER_BYTES;
-constexpr int THREADS = 384;                                              // warps: 0 TMA (operands), 1 MMA, 2-9 epilogue, 10 scale copies, 11 TMA (scales)
+constexpr int THREADS = 384;                                              // warps: 0 TMA (operands and scales), 1 MMA, 2-9 epilogue, 10-11 scale copies
+constexpr int CP_WARPS = 2;                                               // they take the stages in turn (leader only)
 constexpr int SF_STAGE_COLS = 16 + 32;                                    // A scales, B scales
 static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
 static_assert(SF_COL0 + SF_SLOTS * SF_STAGE_COLS <= TMEM_COLS, "scale ring does not fit tensor memory");
 static_assert(SMEM_BYTES <= 232448, "more shared memory than a CTA can have");
-static_assert((2 * STAGES + 2 * SF_SLOTS + 2) * 8 + 8 <= BARRIER_BYTES, "barrier area too small");
-static_assert(SF_SLOTS <= STAGES, "the scale producer's wait assumes no more slots than stages");
+static_assert((2 * STAGES + (CP_WARPS + 1) * SF_SLOTS + 2) * 8 + 8 <= BARRIER_BYTES, "barrier area too small");
+static_assert(SF_SLOTS < STAGES, "the producer requests a stage's scales one iteration after its operands");
 
 // 3-D form of the same (scale tiles).
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t cluster_bar) {
@@ -740,11 +742,11 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + STAGES * STAGE_BYTES + SF_SLOTS * SF_SLOT_BYTES);
     const uint32_t full_bar = smem_u32(bars);                 // [STAGES], used in the leader only
     const uint32_t empty_bar = full_bar + 8 * STAGES;         // [STAGES]
-    const uint32_t sf_full_bar = empty_bar + 8 * STAGES;      // [SF_SLOTS]
-    const uint32_t sf_ready_bar = sf_full_bar + 8 * SF_SLOTS; // [SF_SLOTS], used in the leader only
+    const uint32_t sf_full_bar = empty_bar + 8 * STAGES;      // [CP_WARPS][SF_SLOTS], used in the leader only
+    const uint32_t sf_ready_bar = sf_full_bar + 8 * CP_WARPS * SF_SLOTS; // [SF_SLOTS], used in the leader only
     const uint32_t acc_full_bar = sf_ready_bar + 8 * SF_SLOTS;
     const uint32_t acc_empty_bar = acc_full_bar + 8;          // used in the leader only
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2 * SF_SLOTS + 2);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + (CP_WARPS + 1) * SF_SLOTS + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -757,7 +759,8 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             mbar_init(empty_bar + 8 * s, 1);
         }
         for (int j = 0; j < SF_SLOTS; ++j) {
-            mbar_init(sf_full_bar + 8 * j, 1);     // used in the leader only: the scale tiles of BOTH CTAs have landed
+            for (int w = 0; w < CP_WARPS; ++w)
+                mbar_init(sf_full_bar + 8 * (w * SF_SLOTS + j), 1);   // the scale tiles of BOTH CTAs have landed
             mbar_init(sf_ready_bar + 8 * j, 1);    // one commit after the copies into tensor memory
         }
         mbar_init(acc_full_bar, 1);
@@ -790,17 +793,53 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 #endif
 
     if (warp == 0 && lane == 0 && !dbg_no_load) {
-        // ------------------------------------------------------------------ TMA producer: operands (both CTAs)
-        const uint32_t leader_full = map_to_cta(full_bar, 0);
+        // ------------------------------------------------------------------ TMA producer: operands and scales (both CTAs)
+        // Each CTA fetches its 128 rows of A and of B, and the scales of its own rows of A and of all 256 rows of B,
+        // into its own shared memory; everything completes on the LEADER's barriers. The scale ring has one slot
+        // less than the operand ring (tensor memory has room for five), so a stage's scales are requested one
+        // iteration AFTER its operands: the wait that frees operand stage i (the MMAs of iteration i - STAGES are
+        // done) also frees the scale slot of iteration i - 1. The first SF_SLOTS requests need no wait.
+        const uint32_t leader_full = map_to_cta(full_bar, 0), leader_sf_full = map_to_cta(sf_full_bar, 0);
+        int64_t f_t = pair_id, f_kt = 0;             // the stage whose scales are requested next
+        uint32_t slot = 0, f_w = 0;                  // its ring slot, and which copying warp will take it
+        int a_group = 0, b_group = 0;
+        int64_t requested = 0, i = 0;                // scale requests and operand stages issued so far
+        auto enter_tile = [&]() {
+            if (f_t >= num_tiles) return;
+            int64_t mb, nb;
+            tile_coords(f_t, num_m, num_n, mb, nb);
+            a_group = static_cast<int>(mb * 2 + rank);
+            b_group = static_cast<int>(nb * 2);
+        };
+        auto issue_next_scales = [&]() {
+            ++requested;
+            if (f_t >= num_tiles || dbg_no_sf) return;
+            const int kb0 = static_cast<int>(f_kt * KB_PER_STAGE);
+            const uint32_t idx = 8 * (f_w * SF_SLOTS + slot);
+            const uint32_t dst = sf_base + slot * SF_SLOT_BYTES, bar = leader_sf_full + idx;
+            if (leader) mbar_expect_tx(sf_full_bar + idx, 2 * SF_SLOT_BYTES);
+            tma_load_3d_pair(dst, &map_sfa, 0, kb0, a_group, bar);
+            tma_load_3d_pair(dst + SFA_BYTES, &map_sfb, 0, kb0, b_group, bar);
+            if (++slot == SF_SLOTS) slot = 0;
+            if (++f_w == CP_WARPS) f_w = 0;
+            if (++f_kt == k_tiles) {
+                f_kt = 0;
+                f_t += num_pairs;
+                enter_tile();
+            }
+        };
+        enter_tile();
         uint32_t s = 0, ph = 0;
         bool ok = true;
         for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
             int64_t mb, nb;
             tile_coords(t, num_m, num_n, mb, nb);
             const int m0 = static_cast<int>(mb * 256 + rank * 128), n0 = static_cast<int>(nb * TILE_N + rank * 128);
-            for (int64_t kt = 0; kt < k_tiles; ++kt) {
+            for (int64_t kt = 0; kt < k_tiles; ++kt, ++i) {
+                if (i < SF_SLOTS) issue_next_scales();
                 ok = mbar_wait_poll(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 1);
                 if (!ok) break;
+                if (i >= STAGES) issue_next_scales();
                 const uint32_t stage = smem_base + s * STAGE_BYTES, bar = leader_full + 8 * s;
                 // out-of-range parts of a box are zero-filled and still counted: fixed byte counts.
                 // The leader announces the bytes of both CTAs; its barrier may see the peer's bytes
@@ -811,39 +850,13 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 if (++s == STAGES) { s = 0; ph ^= 1u; }
             }
         }
-        if (!ok) {
-            const unsigned long long t0 = global_timer_ns();
-            while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
-        }
-    } else if (warp == 11 && lane == 0 && !dbg_no_load && !dbg_no_sf) {
-        // ------------------------------------------------------------------ TMA producer: scales (both CTAs)
-        // Each CTA fetches the scales of its own 128 rows of A and of all 256 rows of B into its own
-        // shared memory; both complete on the LEADER's barrier, like the operand copies.
-        const uint32_t leader_sf_full = map_to_cta(sf_full_bar, 0);
-        uint32_t j = 0;
-        bool ok = true;
-        int64_t i = 0;                                   // stage counter over all tiles of this pair
-        for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
-            int64_t mb, nb;
-            tile_coords(t, num_m, num_n, mb, nb);
-            const int a_group = static_cast<int>(mb * 2 + rank), b_group = static_cast<int>(nb * 2);
-            for (int64_t kt = 0; kt < k_tiles; ++kt, ++i) {
-                if (i >= SF_SLOTS) {
-                    // the slot is free when the MMAs of the stage SF_SLOTS back are done; the next
-                    // completion of that stage's barrier needs the scales requested here, so the
-                    // parity cannot be lapped
-                    const int64_t k = i - SF_SLOTS;
-                    ok = mbar_wait_poll(empty_bar + 8 * static_cast<uint32_t>(k % STAGES),
-                                        static_cast<uint32_t>(k / STAGES) & 1u, abort_flag, p.status, 7);
-                    if (!ok) break;
-                }
-                const int kb0 = static_cast<int>(kt * KB_PER_STAGE);
-                const uint32_t dst = sf_base + j * SF_SLOT_BYTES, bar = leader_sf_full + 8 * j;
-                if (leader) mbar_expect_tx(sf_full_bar + 8 * j, 2 * SF_SLOT_BYTES);
-                tma_load_3d_pair(dst, &map_sfa, 0, kb0, a_group, bar);
-                tma_load_3d_pair(dst + SFA_BYTES, &map_sfb, 0, kb0, b_group, bar);
-                if (++j == SF_SLOTS) j = 0;
-            }
+        // the scales of the last iteration (when there were more than SF_SLOTS): their slot is free once the
+        // operand stage that would come next is
+        while (ok && requested < i) {
+            ok = mbar_wait_poll(empty_bar + 8 * s, ph ^ 1u, abort_flag, p.status, 7);
+            if (!ok) break;
+            issue_next_scales();
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
         if (!ok) {
             const unsigned long long t0 = global_timer_ns();
@@ -960,17 +973,27 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 }
             }
         }
-    } else if (warp == 10 && leader && !dbg_no_load && !dbg_no_sf) {
+    } else if (warp >= 10 && warp < 10 + CP_WARPS && leader && !dbg_no_load && !dbg_no_sf) {
         // ------------------------------------------------------------------ scale copies (leader, for both CTAs)
         // tcgen05.cp with cta_group::2 copies, in each CTA, from that CTA's shared memory into its
         // tensor memory: one thread of the pair moves the scales of both, and no warp of the peer
-        // has to report back.
+        // has to report back. Two warps take the stages in turn (one alone cannot issue twelve copies
+        // per stage as fast as the MMAs consume them), each with a landing barrier of its own per slot.
         const bool issue = elect_one();
-        uint32_t j = 0, jph = 0;
+        const uint32_t me = static_cast<uint32_t>(warp - 10);
+        uint32_t j = 0, turn = 0, seen = 0;          // bit j of `seen`: parity of this warp's next phase of slot j
         bool ok = true;
         for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
             for (int64_t kt = 0; kt < k_tiles; ++kt) {
-                ok = mbar_wait_poll(sf_full_bar + 8 * j, jph, abort_flag, p.status, 6);
+                const bool mine = turn == me;
+                if (++turn == CP_WARPS) turn = 0;
+                if (!mine) {
+                    if (++j == SF_SLOTS) j = 0;
+                    continue;
+                }
+                const uint32_t jph = (seen >> j) & 1u;
+                seen ^= 1u << j;
+                ok = mbar_wait_poll(sf_full_bar + 8 * (me * SF_SLOTS + j), jph, abort_flag, p.status, 6);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
@@ -987,7 +1010,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 }
                 if (issue) tc_commit_pair_local(sf_ready_bar + 8 * j);
                 __syncwarp();
-                if (++j == SF_SLOTS) { j = 0; jph ^= 1u; }
+                if (++j == SF_SLOTS) j = 0;
             }
         }
     }
