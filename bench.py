@@ -730,7 +730,7 @@ def run_case(args) -> None:
 
 def experts_pipeline(dev, steps: int) -> dict:
     """The grouped experts layer (32 experts of GPT-OSS-20B shape, 4 per token, uniformly random routing) as CUDA-graph
-    replays: routing tables, gather, 2 x (quantize, alpha, grouped GEMM), SwiGLU, combine - ten kernels of the
+    replays: routing tables (2 kernels), gather, 2 x (quantize, alpha, grouped GEMM), SwiGLU, combine - eleven kernels of the
     library and no read-back."""
     from fouroversix_b200.model import FourOverSixExperts
 

@@ -16,6 +16,7 @@ _LIB_PATH = Path(__file__).resolve().parent / "libfouroversix_b200.so"
 _lib: ctypes.CDLL | None = None
 
 FOS_BF16, FOS_FP16, FOS_FP32 = 0, 1, 2
+EXPERTS_ROUTE_WORKSPACE_INTS = 128                 # FOS_EXPERTS_ROUTE_WORKSPACE_INTS: per expert, for fos_experts_route
 FOS_NVFP4, FOS_IF4, FOS_MXFP4 = 0, 1, 2
 FOS_SF_ROWMAJOR, FOS_SF_TILED = 0, 1
 FOS_QUANTIZE_EXACT_ONLY = 1
@@ -70,7 +71,7 @@ SIGNATURES = {
     "fos_gemm_nvfp4_grouped": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
                                         _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr]),
     "fos_experts_route": (_c_int, [_c_ptr, _c_int, _c_i64, _c_int, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
-                                   _c_ptr]),
+                                   _c_ptr, _c_ptr]),
     "fos_experts_gather_rows": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr]),
     "fos_experts_glu": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, ctypes.c_float,
                                  ctypes.c_float, _c_ptr, _c_ptr]),

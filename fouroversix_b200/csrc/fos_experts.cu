@@ -209,71 +209,127 @@ combine_kernel(const uint8_t *__restrict__ y, int64_t ld_y_bytes, const uint8_t 
     }
 }
 
-constexpr int ROUTE_THREADS = 1024, ROUTE_WARPS = ROUTE_THREADS / 32, ROUTE_MAX_EXPERTS = 256;
+constexpr int ROUTE_THREADS = 256, ROUTE_WARPS = ROUTE_THREADS / 32, ROUTE_MAX_EXPERTS = 256, ROUTE_MAX_SEGMENTS = 128;
 
-// The routing tables of one layer call, by one CTA: a stable counting sort of the (token, slot) pairs by expert.
+// The routing tables of one layer call: a stable counting sort of the (token, slot) pairs by expert, in two
+// launches of one CTA per SEGMENT of the pairs (contiguous, `seg` pairs each).
 //   group_rows[e]   pairs routed to expert e           group_start[e]  first row of expert e in the padded buffer
 //   pair_row[p]     the row pair p was given (ascending in p within an expert), -1 for an index outside [0, experts)
 //   row_token[r], row_expert[r]   the token and the expert of row r, -1 for padding rows
-// Pairs are taken 1024 at a time: a warp ranks its 32 pairs among themselves with match_any, the per-warp
-// counts per expert go through shared memory, and a running count per expert carries over to the next round.
+// route_count_kernel: every CTA counts its segment per expert into seg_count[segment][expert], and the CTAs
+// together fill the row tables with -1. route_place_kernel: every CTA adds up the counts of all segments (totals,
+// hence the experts' first rows) and of the segments before its own (hence its own first row per expert), splits
+// its segment over its warps the same way (count, running sum), and then each warp walks its pairs 32 at a
+// time, ranks the pairs of one expert among themselves with match_any and advances its own counters. Rows
+// ascend with the pair index because segments, warps and lanes do.
 template <typename IDX>
-__global__ void __launch_bounds__(ROUTE_THREADS, 1)
-route_kernel(const IDX *__restrict__ routing, int pairs, int top_k, int experts, int rows_capacity,
-             int32_t *__restrict__ group_start, int32_t *__restrict__ group_rows, int32_t *__restrict__ row_token,
-             int32_t *__restrict__ row_expert, int32_t *__restrict__ pair_row, int32_t *__restrict__ pair_expert) {
-    __shared__ int s_count[ROUTE_MAX_EXPERTS], s_start[ROUTE_MAX_EXPERTS + 1], s_running[2][ROUTE_MAX_EXPERTS];
-    __shared__ uint16_t s_warp[ROUTE_WARPS][ROUTE_MAX_EXPERTS];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid < ROUTE_MAX_EXPERTS) { s_count[tid] = 0; s_running[0][tid] = 0; }
-    __syncthreads();
-    for (int p = tid; p < pairs; p += ROUTE_THREADS) {
-        const long long e = static_cast<long long>(routing[p]);
-        if (e >= 0 && e < experts) atomicAdd(&s_count[static_cast<int>(e)], 1);
+__device__ __forceinline__ int route_expert_of(const IDX *__restrict__ routing, int p, int end, int experts) {
+    if (p >= end) return -1;
+    const long long e = static_cast<long long>(routing[p]);
+    return (e >= 0 && e < experts) ? static_cast<int>(e) : -1;
+}
+
+template <typename IDX>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_count_kernel(const IDX *__restrict__ routing, int pairs, int seg, int experts, int rows_capacity,
+                   int32_t *__restrict__ seg_count, int32_t *__restrict__ row_token, int32_t *__restrict__ row_expert) {
+    __shared__ int s_count[ROUTE_MAX_EXPERTS];
+    const int tid = threadIdx.x;
+    s_count[tid] = 0;
+    for (int r = blockIdx.x * ROUTE_THREADS + tid; r < rows_capacity; r += gridDim.x * ROUTE_THREADS) {
+        row_token[r] = -1;
+        row_expert[r] = -1;
     }
-    for (int r = tid; r < rows_capacity; r += ROUTE_THREADS) { row_token[r] = -1; row_expert[r] = -1; }
+    __syncthreads();
+    const int p0 = blockIdx.x * seg, p1 = min(pairs, p0 + seg);
+    for (int base = p0; base < p1; base += 4 * ROUTE_THREADS) {       // four independent loads in flight per thread
+        int e[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) e[u] = route_expert_of(routing, base + u * ROUTE_THREADS + tid, p1, experts);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (e[u] >= 0) atomicAdd(&s_count[e[u]], 1);
+    }
+    __syncthreads();
+    if (tid < experts) seg_count[blockIdx.x * experts + tid] = s_count[tid];
+}
+
+template <typename IDX>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_place_kernel(const IDX *__restrict__ routing, int pairs, int seg, int top_k, int experts,
+                   const int32_t *__restrict__ seg_count, int32_t *__restrict__ group_start,
+                   int32_t *__restrict__ group_rows, int32_t *__restrict__ row_token, int32_t *__restrict__ row_expert,
+                   int32_t *__restrict__ pair_row, int32_t *__restrict__ pair_expert) {
+    __shared__ int s_at[ROUTE_WARPS][ROUTE_MAX_EXPERTS];     // counts, then next rows, per (warp, expert)
+    __shared__ int s_total[ROUTE_MAX_EXPERTS], s_first[ROUTE_MAX_EXPERTS];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int w = 0; w < ROUTE_WARPS; ++w) s_at[w][tid] = 0;
+    int before = 0;
+    if (tid < experts) {
+        int total = 0;
+        for (int sgm = 0; sgm < static_cast<int>(gridDim.x); ++sgm) {
+            const int n = __ldg(seg_count + sgm * experts + tid);
+            total += n;
+            if (sgm < static_cast<int>(blockIdx.x)) before += n;
+        }
+        s_total[tid] = total;
+    }
     __syncthreads();
     if (tid == 0) {
         int at = 0;
         for (int e = 0; e < experts; ++e) {
-            s_start[e] = at;
-            group_start[e] = at;
-            group_rows[e] = s_count[e];
-            at += (s_count[e] + 127) / 128 * 128;
+            s_first[e] = at;
+            if (blockIdx.x == 0) {
+                group_start[e] = at;
+                group_rows[e] = s_total[e];
+            }
+            at += (s_total[e] + 127) / 128 * 128;
         }
-        group_start[experts] = at;
+        if (blockIdx.x == 0) group_start[experts] = at;
     }
-    int cur = 0;
-    for (int base = 0; base < pairs; base += ROUTE_THREADS, cur ^= 1) {
-        uint32_t *zero = reinterpret_cast<uint32_t *>(&s_warp[0][0]);
-        for (int i = tid; i < ROUTE_WARPS * ROUTE_MAX_EXPERTS / 2; i += ROUTE_THREADS) zero[i] = 0u;
-        __syncthreads();                                  // also orders s_start and the -1 fill before their use
-        const int p = base + tid;
-        long long idx = -1;
-        if (p < pairs) idx = static_cast<long long>(routing[p]);
-        const int e = (idx >= 0 && idx < experts) ? static_cast<int>(idx) : -1;
+    // this CTA's segment over its warps: count ...
+    const int p0 = blockIdx.x * seg, p1 = min(pairs, p0 + seg);
+    const int wseg = ((p1 > p0 ? p1 - p0 : 0) + ROUTE_WARPS - 1) / ROUTE_WARPS;
+    const int w0 = p0 + warp * wseg, w1 = min(p1, w0 + wseg);
+    for (int base = w0; base < w1; base += 128) {
+        int e[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) e[u] = route_expert_of(routing, base + 32 * u + lane, w1, experts);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (e[u] >= 0) atomicAdd(&s_at[warp][e[u]], 1);
+    }
+    __syncthreads();
+    // ... running sum from the expert's first row and the rows of the segments before this one ...
+    if (tid < experts) {
+        int at = s_first[tid] + before;
+        for (int w = 0; w < ROUTE_WARPS; ++w) {
+            const int n = s_at[w][tid];
+            s_at[w][tid] = at;
+            at += n;
+        }
+    }
+    __syncthreads();
+    // ... and place
+    int e_next = route_expert_of(routing, w0 + lane, w1, experts);
+    for (int base = w0; base < w1; base += 32) {
+        const int p = base + lane, e = e_next;
+        e_next = route_expert_of(routing, p + 32, w1, experts);      // the next round's load overlaps this round's work
         const uint32_t same = __match_any_sync(0xffffffffu, e);
         const int rank = __popc(same & ((1u << lane) - 1u));
-        if (e >= 0 && rank == 0) s_warp[warp][e] = static_cast<uint16_t>(__popc(same));
-        __syncthreads();
-        if (e >= 0) {
-            int before = s_running[cur][e];
-            for (int w = 0; w < warp; ++w) before += s_warp[w][e];
-            const int row = s_start[e] + before + rank;
+        int row = -1;
+        if (e >= 0) row = s_at[warp][e] + rank;
+        __syncwarp();
+        if (e >= 0 && rank == 0) s_at[warp][e] += __popc(same);
+        __syncwarp();
+        if (p < w1) {
             pair_row[p] = row;
             pair_expert[p] = e;
-            row_token[row] = p / top_k;
-            row_expert[row] = e;
-        } else if (p < pairs) {
-            pair_row[p] = -1;
-            pair_expert[p] = -1;
+            if (e >= 0) {
+                row_token[row] = p / top_k;
+                row_expert[row] = e;
+            }
         }
-        if (tid < experts) {
-            int total = s_running[cur][tid];
-            for (int w = 0; w < ROUTE_WARPS; ++w) total += s_warp[w][tid];
-            s_running[cur ^ 1][tid] = total;
-        }
-        __syncthreads();
     }
 }
 
@@ -385,27 +441,37 @@ extern "C" int fos_experts_combine(const void *y, int dtype, int64_t ld_y, const
 
 extern "C" int fos_experts_route(const void *routing_indices, int index_bytes, int64_t tokens, int top_k, int num_experts,
                                  int64_t rows_capacity, int32_t *group_start, int32_t *group_rows, int32_t *row_token,
-                                 int32_t *row_expert, int32_t *pair_row, int32_t *pair_expert, void *stream_) {
+                                 int32_t *row_expert, int32_t *pair_row, int32_t *pair_expert, int32_t *workspace,
+                                 void *stream_) {
     using namespace fos;
     if (!routing_indices || !group_start || !group_rows || !row_token || !row_expert || !pair_row || !pair_expert ||
-        tokens <= 0 || top_k <= 0 || num_experts <= 0 || (index_bytes != 4 && index_bytes != 8))
+        !workspace || tokens <= 0 || top_k <= 0 || num_experts <= 0 || (index_bytes != 4 && index_bytes != 8))
         return FOS_ERR_INVALID_ARGUMENT;
     if (num_experts > ROUTE_MAX_EXPERTS) return FOS_ERR_UNSUPPORTED;
-    const int64_t pairs = tokens * top_k;
-    if (pairs >= (int64_t(1) << 30) || rows_capacity >= (int64_t(1) << 31)) return FOS_ERR_TOO_LARGE;
-    if (rows_capacity % 128 != 0 || rows_capacity < round_up64(pairs + 127 * static_cast<int64_t>(num_experts), 128))
+    const int64_t pairs64 = tokens * top_k;
+    if (pairs64 >= (int64_t(1) << 30) || rows_capacity >= (int64_t(1) << 31)) return FOS_ERR_TOO_LARGE;
+    if (rows_capacity % 128 != 0 || rows_capacity < round_up64(pairs64 + 127 * static_cast<int64_t>(num_experts), 128))
         return FOS_ERR_INVALID_ARGUMENT;
     const int st = check_device();
     if (st != FOS_OK) return st;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if (index_bytes == 8)
-        route_kernel<int64_t><<<1, ROUTE_THREADS, 0, stream>>>(static_cast<const int64_t *>(routing_indices), static_cast<int>(pairs),
-                                                               top_k, num_experts, static_cast<int>(rows_capacity), group_start,
-                                                               group_rows, row_token, row_expert, pair_row, pair_expert);
-    else
-        route_kernel<int32_t><<<1, ROUTE_THREADS, 0, stream>>>(static_cast<const int32_t *>(routing_indices), static_cast<int>(pairs),
-                                                               top_k, num_experts, static_cast<int>(rows_capacity), group_start,
-                                                               group_rows, row_token, row_expert, pair_row, pair_expert);
+    // segments of at least 512 pairs, at most ROUTE_MAX_SEGMENTS of them
+    const int pairs = static_cast<int>(pairs64), cap = static_cast<int>(rows_capacity);
+    int segments = (pairs + 511) / 512;
+    if (segments > ROUTE_MAX_SEGMENTS) segments = ROUTE_MAX_SEGMENTS;
+    const int seg = (pairs + segments - 1) / segments;
+    segments = (pairs + seg - 1) / seg;
+    if (index_bytes == 8) {
+        const int64_t *idx = static_cast<const int64_t *>(routing_indices);
+        route_count_kernel<int64_t><<<segments, ROUTE_THREADS, 0, stream>>>(idx, pairs, seg, num_experts, cap, workspace, row_token, row_expert);
+        route_place_kernel<int64_t><<<segments, ROUTE_THREADS, 0, stream>>>(idx, pairs, seg, top_k, num_experts, workspace, group_start,
+                                                                            group_rows, row_token, row_expert, pair_row, pair_expert);
+    } else {
+        const int32_t *idx = static_cast<const int32_t *>(routing_indices);
+        route_count_kernel<int32_t><<<segments, ROUTE_THREADS, 0, stream>>>(idx, pairs, seg, num_experts, cap, workspace, row_token, row_expert);
+        route_place_kernel<int32_t><<<segments, ROUTE_THREADS, 0, stream>>>(idx, pairs, seg, top_k, num_experts, workspace, group_start,
+                                                                            group_rows, row_token, row_expert, pair_row, pair_expert);
+    }
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;
 }

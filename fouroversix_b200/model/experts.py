@@ -128,25 +128,26 @@ class FourOverSixExperts(nn.Module):
 
     def route_native(self, routing_indices: torch.Tensor) -> tuple[GroupLayout, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
         """`fos_experts_route`: the row layout and the tables of the element-wise kernels (row -> token, row ->
-        expert, pair -> row, pair -> expert) in one launch."""
+        expert, pair -> row, pair -> expert) in two launches."""
         tokens, top_k = routing_indices.shape
         dev = routing_indices.device
         if routing_indices.dtype not in (torch.int32, torch.int64):
             routing_indices = routing_indices.to(torch.int64)
         routing_indices = routing_indices.contiguous()
         capacity = (tokens * top_k + 127 * self.num_experts + 127) // 128 * 128
-        tables = torch.empty(2 * self.num_experts + 1 + 2 * capacity + 2 * tokens * top_k, dtype=torch.int32, device=dev)
-        group_start, group_rows, row_token, row_expert, pair_row, pair_expert = torch.split(
-            tables, [self.num_experts + 1, self.num_experts, capacity, capacity, tokens * top_k, tokens * top_k])
+        work = _native.EXPERTS_ROUTE_WORKSPACE_INTS * self.num_experts
+        tables = torch.empty(2 * self.num_experts + 1 + 2 * capacity + 2 * tokens * top_k + work, dtype=torch.int32, device=dev)
+        group_start, group_rows, row_token, row_expert, pair_row, pair_expert, workspace = torch.split(
+            tables, [self.num_experts + 1, self.num_experts, capacity, capacity, tokens * top_k, tokens * top_k, work])
         _native.check(_native.lib().fos_experts_route(
             routing_indices.data_ptr(), routing_indices.element_size(), tokens, top_k, self.num_experts, capacity,
             group_start.data_ptr(), group_rows.data_ptr(), row_token.data_ptr(), row_expert.data_ptr(),
-            pair_row.data_ptr(), pair_expert.data_ptr(), _native.stream_ptr(dev)), "fos_experts_route")
+            pair_row.data_ptr(), pair_expert.data_ptr(), workspace.data_ptr(), _native.stream_ptr(dev)), "fos_experts_route")
         return GroupLayout(group_start, group_rows, capacity, self.num_experts), row_token, row_expert, pair_row, pair_expert
 
     def _forward_native(self, x: torch.Tensor, routing_indices: torch.Tensor, routing_weights: torch.Tensor) -> torch.Tensor:
         """The same layer on `fos_experts_route`, `fos_experts_gather_rows`, `fos_experts_glu` and
-        `fos_experts_combine` around the grouped launches (ten kernels in all): bit-equal to the
+        `fos_experts_combine` around the grouped launches (eleven kernels in all): bit-equal to the
         tensor-operation form when a token has at most two experts, and to the reference's host loop (which adds
         a token's experts in ascending order) for any number."""
         down, gate_up = self.quantized_weights()

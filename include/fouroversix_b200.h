@@ -286,21 +286,23 @@ int fos_gemm_nvfp4_grouped(const uint8_t *a_codes, const uint8_t *a_sf, const ui
  *   reference's host loop over the experts, whatever order the slots are listed in.
  *
  * fos_experts_route: the tables the three calls above and the grouped calls take, from the layer's routing
- *   indices [tokens][top_k] (int32 or int64: index_bytes 4 or 8; device memory), in one launch and without a
+ *   indices [tokens][top_k] (int32 or int64: index_bytes 4 or 8; device memory), in two launches and without a
  *   read-back: a stable counting sort of the (token, slot) pairs by expert. Writes group_rows[e] (pairs routed to
  *   expert e), group_start[e] (num_experts + 1 values: every expert starts on a multiple of 128 rows),
  *   pair_row[p] (the row of pair p = token * top_k + slot; ascending in p within an expert), pair_expert[p] (the
  *   index as int32), and row_token[r] / row_expert[r] for all rows_capacity rows (-1 for padding rows).
  *   rows_capacity must be a multiple of 128 and at least tokens * top_k + 127 * num_experts rounded up to 128 (the
  *   worst case, known without the counts). An index outside [0, num_experts) gives its pair the row -1, which
- *   fos_experts_combine skips. num_experts <= 256: FOS_ERR_UNSUPPORTED above.
+ *   fos_experts_combine skips. num_experts <= 256: FOS_ERR_UNSUPPORTED above. workspace: FOS_EXPERTS_ROUTE_WORKSPACE_INTS
+ *   * num_experts int32 values of device memory that the call may overwrite (per-segment counts).
  *
  * Replaces: the element-wise tensor operations of src/fouroversix/model/modules/gpt_oss.py:310-333 and the
  * routing mask and its per-expert read-back of lines 286-303.
  */
+#define FOS_EXPERTS_ROUTE_WORKSPACE_INTS 128
 int fos_experts_route(const void *routing_indices, int index_bytes, int64_t tokens, int top_k, int num_experts,
                       int64_t rows_capacity, int32_t *group_start, int32_t *group_rows, int32_t *row_token,
-                      int32_t *row_expert, int32_t *pair_row, int32_t *pair_expert, void *stream);
+                      int32_t *row_expert, int32_t *pair_row, int32_t *pair_expert, int32_t *workspace, void *stream);
 int fos_experts_gather_rows(const void *x, int dtype, int64_t ld_x, const int32_t *row_token, void *out,
                             int64_t ld_out, int64_t rows_capacity, int64_t cols, const int32_t *row_expert, float *amax,
                             void *stream);
