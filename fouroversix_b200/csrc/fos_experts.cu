@@ -1,5 +1,6 @@
-// The element-wise steps of a mixture-of-experts layer around the two grouped GEMMs, one kernel each:
+// The steps of a mixture-of-experts layer around the two grouped GEMMs:
 //
+//   fos_experts_route         routing indices -> row ranges per expert and the tables the other kernels take
 //   fos_experts_gather_rows   routed tokens -> the padded row buffer the grouped quantization reads
 //   fos_experts_glu           gate-up output + bias -> clamped SwiGLU, the input of the down projection
 //   fos_experts_combine       down output + bias, times the routing weight, summed per token
@@ -7,9 +8,10 @@
 // The arithmetic follows the reference's GPT-OSS experts module
 // (src/fouroversix/model/modules/gpt_oss.py:297-335), which runs it as a chain of element-wise tensor
 // operations on 16-bit tensors: every operation computes in binary32 and rounds its result to the
-// tensor's type. The kernels keep every one of those roundings (r16 below), so the results are the bits
-// of that chain; what they save is its memory traffic (each operation reads and writes the whole tensor,
-// the gathers materialise the bias per row) and its launches. All three are bound by HBM.
+// tensor's type. The kernels keep every one of those roundings, so the results are the bits of that
+// chain; what they save is its memory traffic (each operation reads and writes the whole tensor, the
+// gathers materialise the bias per row) and its launches. Gather and combine are bound by HBM, the SwiGLU
+// by its arithmetic (a sigmoid with an IEEE division and six roundings per output).
 #include "fos_common.cuh"
 
 namespace fos {
