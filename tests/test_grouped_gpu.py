@@ -197,7 +197,10 @@ def test_glu_kernel_keeps_every_rounding_of_the_operation_chain(dtype):
     bias = (torch.randn(3, 2 * inter, generator=g) * 0.5).to(dtype).to(DEV)
     bias[0] = 0
     row_expert = (torch.arange(rows, device=DEV) % 4 - 1).to(torch.int32)          # -1: a padding row
-    for alpha, limit in ((1.702, 7.0), (0.3333, 2.7182818)):
+    # alpha = 1 with no bias and no effective limit feeds every 16-bit pattern to the sigmoid itself (expert 0)
+    for alpha, limit in ((1.702, 7.0), (0.3333, 2.7182818), (1.0, 3.0e38)):
+        if alpha == 1.0:
+            bias.zero_()
         out = torch.full((rows, inter), 9, dtype=dtype, device=DEV)
         amax = torch.zeros(3, dtype=torch.float32, device=DEV)
         _native.check(_native.lib().fos_experts_glu(gu.data_ptr(), _native.elem_code(dtype), gu.stride(0), bias.data_ptr(),
