@@ -70,6 +70,10 @@ SIGNATURES = {
                                       _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr]),
     "fos_gemm_nvfp4_grouped": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
                                         _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr]),
+    "fos_experts_workspace_bytes": (_c_i64, [_c_i64, _c_int, _c_int, _c_i64, _c_i64]),
+    "fos_experts_forward": (_c_int, [_c_ptr, _c_int, _c_i64, _c_i64, _c_i64, _c_ptr, _c_int, _c_ptr, _c_int, _c_int,
+                                     _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_int,
+                                     ctypes.c_float, ctypes.c_float, _c_ptr, _c_i64, _c_ptr, _c_i64, _c_ptr, _c_ptr]),
     "fos_experts_route": (_c_int, [_c_ptr, _c_int, _c_i64, _c_int, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                                    _c_ptr, _c_ptr]),
     "fos_experts_gather_rows": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr]),

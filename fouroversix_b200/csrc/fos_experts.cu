@@ -477,3 +477,110 @@ extern "C" int fos_experts_route(const void *routing_indices, int index_bytes, i
     FOS_CUDA_TRY(cudaGetLastError());
     return FOS_OK;
 }
+
+// ---------------------------------------------------------------------------- the whole layer in one call
+
+namespace fos {
+namespace {
+
+struct ExpertsWorkspace {
+    int64_t capacity, pairs;
+    // byte offsets into the workspace, each a multiple of 256
+    int64_t group_start, group_rows, row_token, row_expert, pair_row, pair_expert, route_work, amax, alpha;
+    int64_t rows_x, codes_x, sf_x, gate_up, gated, codes_g, sf_g, y, total;
+};
+
+ExpertsWorkspace experts_workspace(int64_t tokens, int top_k, int num_experts, int64_t hidden, int64_t intermediate) {
+    ExpertsWorkspace w{};
+    w.pairs = tokens * top_k;
+    w.capacity = round_up64(w.pairs + 127 * static_cast<int64_t>(num_experts), 128);
+    int64_t at = 0;
+    auto take = [&](int64_t bytes) { const int64_t here = at; at += round_up64(bytes, 256); return here; };
+    w.group_start = take(4 * (num_experts + 1));
+    w.group_rows = take(4 * num_experts);
+    w.row_token = take(4 * w.capacity);
+    w.row_expert = take(4 * w.capacity);
+    w.pair_row = take(4 * w.pairs);
+    w.pair_expert = take(4 * w.pairs);
+    w.route_work = take(4 * static_cast<int64_t>(FOS_EXPERTS_ROUTE_WORKSPACE_INTS) * num_experts);
+    w.amax = take(4 * 2 * num_experts);
+    w.alpha = take(4 * 2 * num_experts);
+    w.rows_x = take(2 * w.capacity * hidden);
+    w.codes_x = take(w.capacity * hidden / 2);
+    w.sf_x = take(w.capacity * hidden / 16);
+    w.gate_up = take(2 * w.capacity * 2 * intermediate);
+    w.gated = take(2 * w.capacity * intermediate);
+    w.codes_g = take(w.capacity * intermediate / 2);
+    w.sf_g = take(w.capacity * intermediate / 16);
+    w.y = take(2 * w.capacity * hidden);
+    w.total = at;
+    return w;
+}
+
+}  // namespace
+}  // namespace fos
+
+extern "C" int64_t fos_experts_workspace_bytes(int64_t tokens, int top_k, int num_experts, int64_t hidden, int64_t intermediate) {
+    if (tokens <= 0 || top_k <= 0 || num_experts <= 0 || hidden <= 0 || intermediate <= 0) return FOS_ERR_INVALID_ARGUMENT;
+    return fos::experts_workspace(tokens, top_k, num_experts, hidden, intermediate).total;
+}
+
+extern "C" int fos_experts_forward(const void *x, int dtype, int64_t tokens, int64_t hidden, int64_t ld_x,
+                                   const void *routing_indices, int index_bytes, const void *routing_weights, int top_k,
+                                   int num_experts, const uint8_t *gate_up_codes, const uint8_t *gate_up_sf,
+                                   const float *gate_up_amax, const void *gate_up_bias, const uint8_t *down_codes,
+                                   const uint8_t *down_sf, const float *down_amax, const void *down_bias,
+                                   int64_t intermediate, int weight_rule, int activation_rule, float alpha, float limit,
+                                   void *out, int64_t ld_out, void *workspace, int64_t workspace_bytes, int32_t *status,
+                                   void *stream_) {
+    using namespace fos;
+    if (!x || !routing_indices || !routing_weights || !gate_up_codes || !gate_up_sf || !gate_up_amax || !gate_up_bias ||
+        !down_codes || !down_sf || !down_amax || !down_bias || !out || !workspace || tokens <= 0 || hidden <= 0 ||
+        intermediate <= 0 || top_k <= 0 || num_experts <= 0)
+        return FOS_ERR_INVALID_ARGUMENT;
+    if (dtype != FOS_BF16 && dtype != FOS_FP16) return FOS_ERR_UNSUPPORTED;
+    // whole 64-value scale tiles along both reduction dimensions (the packed weights are then not padded along K)
+    if (hidden % 64 != 0 || intermediate % 64 != 0 || num_experts > 256 || top_k > MAX_TOP_K) return FOS_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return FOS_ERR_MISALIGNED;
+    const ExpertsWorkspace w = experts_workspace(tokens, top_k, num_experts, hidden, intermediate);
+    if (workspace_bytes < w.total) return FOS_ERR_INVALID_ARGUMENT;
+    uint8_t *base = static_cast<uint8_t *>(workspace);
+    auto ints = [&](int64_t off) { return reinterpret_cast<int32_t *>(base + off); };
+    float *amax = reinterpret_cast<float *>(base + w.amax), *alphas = reinterpret_cast<float *>(base + w.alpha);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const int64_t gate_up_rows = round_up64(2 * intermediate, 128), down_rows = round_up64(hidden, 128);
+
+    int st = fos_experts_route(routing_indices, index_bytes, tokens, top_k, num_experts, w.capacity, ints(w.group_start),
+                               ints(w.group_rows), ints(w.row_token), ints(w.row_expert), ints(w.pair_row),
+                               ints(w.pair_expert), ints(w.route_work), stream_);
+    if (st != FOS_OK) return st;
+    FOS_CUDA_TRY(cudaMemsetAsync(amax, 0, sizeof(float) * 2 * num_experts, stream));
+    st = fos_experts_gather_rows(x, dtype, ld_x, ints(w.row_token), base + w.rows_x, hidden, w.capacity, hidden,
+                                 ints(w.row_expert), amax, stream_);
+    if (st != FOS_OK) return st;
+    st = fos_quantize_grouped(base + w.rows_x, dtype, w.capacity, hidden, hidden, FOS_NVFP4, activation_rule, ints(w.group_start),
+                              ints(w.group_rows), num_experts, amax, base + w.codes_x, base + w.sf_x, amax, 0, stream_);
+    if (st != FOS_OK) return st;
+    st = fos_gemm_alpha_grouped(amax, FOS_NVFP4, activation_rule, 0, gate_up_amax, FOS_NVFP4, weight_rule, 0, alphas, num_experts, stream_);
+    if (st != FOS_OK) return st;
+    st = fos_gemm_nvfp4_grouped(base + w.codes_x, base + w.sf_x, gate_up_codes, gate_up_sf, alphas, base + w.gate_up, dtype,
+                                ints(w.group_start), ints(w.group_rows), num_experts, w.capacity, gate_up_rows, hidden,
+                                2 * intermediate, 2 * intermediate, nullptr, status, stream_);
+    if (st != FOS_OK) return st;
+    st = fos_experts_glu(base + w.gate_up, dtype, 2 * intermediate, gate_up_bias, ints(w.row_expert), base + w.gated, intermediate,
+                         w.capacity, intermediate, alpha, limit, amax + num_experts, stream_);
+    if (st != FOS_OK) return st;
+    st = fos_quantize_grouped(base + w.gated, dtype, w.capacity, intermediate, intermediate, FOS_NVFP4, activation_rule,
+                              ints(w.group_start), ints(w.group_rows), num_experts, amax + num_experts, base + w.codes_g,
+                              base + w.sf_g, amax + num_experts, 0, stream_);
+    if (st != FOS_OK) return st;
+    st = fos_gemm_alpha_grouped(amax + num_experts, FOS_NVFP4, activation_rule, 0, down_amax, FOS_NVFP4, weight_rule, 0,
+                                alphas + num_experts, num_experts, stream_);
+    if (st != FOS_OK) return st;
+    st = fos_gemm_nvfp4_grouped(base + w.codes_g, base + w.sf_g, down_codes, down_sf, alphas + num_experts, base + w.y, dtype,
+                                ints(w.group_start), ints(w.group_rows), num_experts, w.capacity, down_rows, intermediate,
+                                hidden, hidden, nullptr, status, stream_);
+    if (st != FOS_OK) return st;
+    return fos_experts_combine(base + w.y, dtype, hidden, down_bias, ints(w.pair_row), ints(w.pair_expert), routing_weights,
+                               top_k, out, ld_out, tokens, hidden, stream_);
+}

@@ -21,7 +21,7 @@ from fouroversix_b200 import _native
 from fouroversix_b200.matmul.grouped import (_OUT, GroupLayout, StackedQuantizedTensor, grouped_quantize,
                                              grouped_quantized_matmul)
 from fouroversix_b200.quantize import quantize
-from fouroversix_b200.utils import DataType
+from fouroversix_b200.utils import DataType, RoundStyle, ScaleRule
 
 from .config import ModuleQuantizationConfig
 
@@ -34,9 +34,10 @@ class FourOverSixExperts(nn.Module):
 
     def __init__(self, gate_up_proj: torch.Tensor, gate_up_proj_bias: torch.Tensor, down_proj: torch.Tensor,
                  down_proj_bias: torch.Tensor, config: ModuleQuantizationConfig | None = None, *,
-                 alpha: float = 1.702, limit: float = 7.0, native_elementwise: bool = True) -> None:
+                 alpha: float = 1.702, limit: float = 7.0, native_elementwise: bool = True, single_call: bool = True) -> None:
         super().__init__()
         self.native_elementwise = native_elementwise
+        self.single_call = single_call            # fos_experts_forward where the shapes allow; else one call per kernel
         self.config = config or ModuleQuantizationConfig()
         if DataType(self.config.dtype) != DataType.nvfp4:
             raise NotImplementedError("the grouped kernels take nvfp4 operands")
@@ -163,6 +164,27 @@ class FourOverSixExperts(nn.Module):
     def _run_native(self, x, routing_indices, routing_weights, down, gate_up, act_config, out_dtype, dev, dtype, code,
                     tokens, top_k) -> torch.Tensor:
         lib, stream = _native.lib(), _native.stream_ptr(dev)
+        if (self.single_call and self.hidden_size % 64 == 0 and self.intermediate_size % 64 == 0
+                and DataType(act_config.dtype) == DataType.nvfp4 and not act_config.block_scale_2d and not act_config.rht
+                and RoundStyle(act_config.round_style) == RoundStyle.nearest):
+            # one host call for the eleven launches (fos_experts_forward); the workspace is the call's only scratch
+            if routing_indices.dtype not in (torch.int32, torch.int64):
+                routing_indices = routing_indices.to(torch.int64)
+            routing_indices = routing_indices.contiguous()
+            weights = routing_weights.reshape(-1).contiguous()
+            gate_up_bias, down_bias = self.gate_up_proj_bias.contiguous(), self.down_proj_bias.contiguous()
+            need = lib.fos_experts_workspace_bytes(tokens, top_k, self.num_experts, self.hidden_size, self.intermediate_size)
+            workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+            result = torch.empty(tokens, self.hidden_size, dtype=dtype, device=dev)
+            _native.check(lib.fos_experts_forward(
+                x.data_ptr(), code, tokens, self.hidden_size, x.stride(0), routing_indices.data_ptr(),
+                routing_indices.element_size(), weights.data_ptr(), top_k, self.num_experts,
+                gate_up.values.data_ptr(), gate_up.scale_factors.data_ptr(), gate_up.amax.data_ptr(), gate_up_bias.data_ptr(),
+                down.values.data_ptr(), down.scale_factors.data_ptr(), down.amax.data_ptr(), down_bias.data_ptr(),
+                self.intermediate_size, gate_up.scale_rule.cuda_id, ScaleRule(act_config.scale_rule).cuda_id,
+                float(self.alpha), float(self.limit), result.data_ptr(), result.stride(0), workspace.data_ptr(), need, 0,
+                stream), "fos_experts_forward")
+            return result
         layout, row_token, row_expert, pair_row, pair_expert = self.route_native(routing_indices)
         weights = routing_weights.reshape(-1).contiguous()
         gate_up_bias, down_bias = self.gate_up_proj_bias.contiguous(), self.down_proj_bias.contiguous()

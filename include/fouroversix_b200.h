@@ -299,6 +299,30 @@ int fos_gemm_nvfp4_grouped(const uint8_t *a_codes, const uint8_t *a_sf, const ui
  * Replaces: the element-wise tensor operations of src/fouroversix/model/modules/gpt_oss.py:310-333 and the
  * routing mask and its per-expert read-back of lines 286-303.
  */
+/*
+ * fos_experts_forward: the whole layer in one host call - the four calls above around two fos_quantize_grouped /
+ * fos_gemm_alpha_grouped / fos_gemm_nvfp4_grouped chains, eleven kernels enqueued on `stream` without a read-back:
+ *   out[t] = sum over the token's experts e (ascending) of
+ *            (glu(x[t] @ gate_up[e]^T + gate_up_bias[e]) @ down[e]^T + down_bias[e]) * routing_weights[t][slot]
+ * with both products in NVFP4 (activations quantized per expert with `activation_rule`, the weights packed
+ * beforehand with `weight_rule`: codes [num_experts][n rounded up to 128][k / 2], tiled scales and one amax per
+ * expert, as fos_quantize writes them for each expert's matrix) and every element-wise step as described above.
+ * x, out, the biases and routing_weights are 16-bit tensors of type `dtype`; hidden and intermediate must be
+ * multiples of 64, top_k <= 8, num_experts <= 256 (FOS_ERR_UNSUPPORTED otherwise). workspace: device memory of
+ * fos_experts_workspace_bytes(...) bytes, 256-byte aligned, the call's only scratch (the library does not
+ * allocate). status as for fos_gemm_nvfp4.
+ *
+ * Replaces: GptOssExperts.forward of src/fouroversix/model/modules/gpt_oss.py:270-335 after weight packing.
+ */
+int64_t fos_experts_workspace_bytes(int64_t tokens, int top_k, int num_experts, int64_t hidden, int64_t intermediate);
+int fos_experts_forward(const void *x, int dtype, int64_t tokens, int64_t hidden, int64_t ld_x,
+                        const void *routing_indices, int index_bytes, const void *routing_weights, int top_k,
+                        int num_experts, const uint8_t *gate_up_codes, const uint8_t *gate_up_sf,
+                        const float *gate_up_amax, const void *gate_up_bias, const uint8_t *down_codes,
+                        const uint8_t *down_sf, const float *down_amax, const void *down_bias, int64_t intermediate,
+                        int weight_rule, int activation_rule, float alpha, float limit, void *out, int64_t ld_out,
+                        void *workspace, int64_t workspace_bytes, int32_t *status, void *stream);
+
 #define FOS_EXPERTS_ROUTE_WORKSPACE_INTS 128
 int fos_experts_route(const void *routing_indices, int index_bytes, int64_t tokens, int top_k, int num_experts,
                       int64_t rows_capacity, int32_t *group_start, int32_t *group_rows, int32_t *row_token,

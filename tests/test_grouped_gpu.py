@@ -154,9 +154,11 @@ def _experts_case(seed, experts, hidden, inter, tokens, top_k, dtype=torch.bfloa
     return layer, x, indices.to(DEV), weights.to(dtype).to(DEV)
 
 
-@pytest.mark.parametrize("native", [True, False], ids=["kernels", "tensor-ops"])
-def test_experts_layer_equals_the_per_expert_loop(native):
-    layer, x, indices, weights = _experts_case(31, 8, 256, 192, 300, 2, native_elementwise=native)
+@pytest.mark.parametrize("how", [dict(), dict(single_call=False), dict(native_elementwise=False)],
+                         ids=["one-call", "kernels", "tensor-ops"])
+def test_experts_layer_equals_the_per_expert_loop(how):
+    """fos_experts_forward; the same kernels called one by one; the element-wise steps as tensor operations."""
+    layer, x, indices, weights = _experts_case(31, 8, 256, 192, 300, 2, **how)
     got = layer(x, indices, weights)
     want = _reference_style_loop(layer, x, indices, weights)
     # every step is bit-equal group by group, and with two experts per token the two 16-bit additions into a
