@@ -44,6 +44,16 @@ def test_argument_validation_needs_no_gpu():
     assert lib.fos_quantize_grouped(0, 0, 128, 64, 64, 0, 3, 0, 0, 4, 0, 0, 0, 0, 0, 0) == -1
     assert lib.fos_gemm_nvfp4_grouped(0, 0, 0, 0, 0, 0, 0, 0, 0, 4, 128, 128, 64, 128, 128, 0, 0, 0) == -1
     assert lib.fos_gemm_alpha_grouped(0, 0, 3, 0, 0, 0, 3, 0, 0, 0, 0) == -1
+    # experts entries: NULL buffers; the workspace size is plain host arithmetic
+    assert lib.fos_experts_route(0, 8, 16, 2, 4, 1024, 0, 0, 0, 0, 0, 0, 0, 0) == -1
+    assert lib.fos_experts_gather_rows(0, 0, 64, 0, 0, 64, 128, 64, 0, 0, 0) == -1
+    assert lib.fos_experts_glu(0, 0, 128, 0, 0, 0, 64, 128, 64, 1.702, 7.0, 0, 0) == -1
+    assert lib.fos_experts_combine(0, 0, 64, 0, 0, 0, 0, 2, 0, 64, 16, 64, 0) == -1
+    assert lib.fos_experts_forward(*([0] * 19), 1, 1, 1.702, 7.0, 0, 0, 0, 0, 0, 0) == -1
+    need = lib.fos_experts_workspace_bytes(256, 4, 32, 2880, 2880)
+    capacity = (256 * 4 + 127 * 32 + 127) // 128 * 128
+    assert need % 256 == 0 and need >= capacity * (2 * 2880 * 2 + 2 * 2 * 2880 + 2 * 2880 + 2 * (2880 // 2 + 2880 // 16))
+    assert lib.fos_experts_workspace_bytes(0, 4, 32, 2880, 2880) == -1
 
 
 def test_group_layout_is_computed_without_reading_the_counts_back():
