@@ -70,6 +70,9 @@ SIGNATURES = {
                                       _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr]),
     "fos_gemm_nvfp4_grouped": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
                                         _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr]),
+    "fos_linear_workspace_bytes": (_c_i64, [_c_i64, _c_i64]),
+    "fos_linear_forward": (_c_int, [_c_ptr, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64,
+                                    _c_ptr, _c_int, _c_i64, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_ptr]),
     "fos_experts_workspace_bytes": (_c_i64, [_c_i64, _c_int, _c_int, _c_i64, _c_i64]),
     "fos_experts_forward": (_c_int, [_c_ptr, _c_int, _c_i64, _c_i64, _c_i64, _c_ptr, _c_int, _c_ptr, _c_int, _c_int,
                                      _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_int,

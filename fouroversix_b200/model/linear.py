@@ -25,9 +25,12 @@ from typing import Any
 import torch
 import torch.nn as nn
 
+from fouroversix_b200 import _native
 from fouroversix_b200.matmul import quantized_matmul
 from fouroversix_b200.quantize import QuantizedTensor, dequantize, quantize
-from fouroversix_b200.utils import RoundStyle
+from fouroversix_b200.utils import DataType, MatmulBackend, QuantizeBackend, RoundStyle
+
+_TORCH_OUT = {DataType.bfloat16: torch.bfloat16, DataType.float16: torch.float16, DataType.float32: torch.float32}
 
 from .config import ModuleQuantizationConfig
 from .quantize import QuantizedModule
@@ -202,4 +205,54 @@ class FourOverSixLinear(nn.Linear):
         return dequantize(w, dtype) if isinstance(w, QuantizedTensor) else w.data.to(dtype)
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
+        if self._one_call_forward_applies(input):
+            return self._forward_one_call(input)
         return FourOverSixLinearFunction.apply(self.config, input, self.quantized_weight(), self.bias)
+
+    def _one_call_forward_applies(self, input: torch.Tensor) -> bool:
+        """Inference on a packed NVFP4 weight with the plain activation settings (NVFP4, 1-D blocks, round to
+        nearest): the case `fos_linear_forward` covers. Everything else (training, master weights, other formats,
+        fake quantization) goes through the autograd function."""
+        cfg = self.config
+        if (cfg.keep_master_weights or cfg.disable_fprop_quantization or cfg.pseudo_quantize
+                or cfg.activation_dtype != DataType.nvfp4 or cfg.activation_round_style != RoundStyle.nearest
+                or cfg.matmul_backend not in (None, MatmulBackend.cutlass)
+                or cfg.quantize_backend not in (None, QuantizeBackend.cuda)):
+            return False
+        if (torch.is_grad_enabled() and input.requires_grad) or not input.is_cuda:
+            return False
+        if input.dtype not in (torch.bfloat16, torch.float16) or input.shape[-1] != self.in_features or input.numel() == 0:
+            return False
+        w = self.quantized_weight()
+        return (isinstance(w, QuantizedTensor) and w.dtype == DataType.nvfp4 and w.scale_factors_are_in_blackwell_layout
+                and w.round_style != RoundStyle.stochastic_unbiased and w.values.is_contiguous()
+                and w.scale_factors.is_contiguous())
+
+    def _forward_one_call(self, input: torch.Tensor) -> torch.Tensor:
+        """`fos_linear_forward`: amax pass, activation quantization, alpha and the GEMM enqueued by one host call
+        (the bits of `quantized_matmul(input, weight)`; at decode sizes the call-by-call form is bound by the
+        interpreter)."""
+        w = self.quantized_weight()
+        x = input.reshape(-1, self.in_features)
+        if x.stride(-1) != 1:
+            x = x.contiguous()
+        dev, rows = x.device, x.shape[0]
+        out_dtype = _TORCH_OUT[DataType(self.config.output_dtype)]
+        lib = _native.lib()
+        need = lib.fos_linear_workspace_bytes(rows, self.in_features)
+        workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        out = torch.empty(rows, self.out_features, dtype=out_dtype, device=dev)
+        def launch() -> None:
+            _native.check(lib.fos_linear_forward(
+                x.data_ptr(), _native.elem_code(x.dtype), rows, self.in_features, x.stride(0),
+                self.config.activation_scale_rule.cuda_id, w.values.data_ptr(), w.scale_factors.data_ptr(),
+                w.amax.data_ptr(), w.scale_rule.cuda_id, self.out_features, out.data_ptr(), _native.elem_code(out_dtype),
+                out.stride(0), workspace.data_ptr(), need, None, 0, _native.stream_ptr(dev)), "fos_linear_forward")
+
+        if dev.index is None or dev.index == torch.cuda.current_device():
+            launch()                                  # (entering a device context costs microseconds a decode step feels)
+        else:
+            with torch.cuda.device(dev):
+                launch()
+        out = out.reshape(*input.shape[:-1], self.out_features)
+        return out if self.bias is None else out + self.bias

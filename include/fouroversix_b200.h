@@ -228,6 +228,23 @@ int fos_gemm_nvfp4_fused_a(const void *x, int x_dtype, int64_t x_ld, const float
                            int32_t *status, void *stream);
 
 /*
+ * A linear layer's forward pass on a packed weight as ONE host call: out[rows, out_features] = Q(x) @ W^T with x
+ * [rows, in_features] (bf16 / fp16, row stride ld_x) quantized here (NVFP4, 1-D blocks, `activation_rule`, its amax
+ * computed by the library) and W packed beforehand by fos_quantize (NVFP4, tiled scales, `weight_rule`, padded to
+ * 128 rows and 64 columns). Enqueues what fos_quantize, fos_gemm_alpha and fos_gemm_nvfp4_ex enqueue, with the
+ * packed activation, its amax and alpha in `workspace` (fos_linear_workspace_bytes(rows, in_features) bytes of
+ * device memory, 256-byte aligned): same bits as the three calls. opts may be NULL; status as for fos_gemm_nvfp4.
+ *
+ * Replaces: FourOverSixLinearFunction.forward of src/fouroversix/model/modules/linear.py:40-110 for packed weights
+ * (quantize the input, quantized_matmul), without its bias addition.
+ */
+int64_t fos_linear_workspace_bytes(int64_t rows, int64_t in_features);
+int fos_linear_forward(const void *x, int x_dtype, int64_t rows, int64_t in_features, int64_t ld_x, int activation_rule,
+                       const uint8_t *w_codes, const uint8_t *w_sf, const float *w_amax, int weight_rule,
+                       int64_t out_features, void *out, int out_dtype, int64_t ld_out, void *workspace,
+                       int64_t workspace_bytes, const fos_gemm_opts *opts, int32_t *status, void *stream);
+
+/*
  * Grouped problems in one launch: num_groups GEMMs that share n, k and the output type, each with its own A rows,
  * its own B and its own alpha - what a mixture-of-experts layer does after routing, where the reference loops over
  * the experts on the host (one quantize + one GEMM per expert, the row counts read back from the device).

@@ -49,6 +49,28 @@ def test_ptq_linear_forward_matches_dequantized_matmul():
     assert torch.equal(q.dequantized_weight(torch.float32), wq)
 
 
+@pytest.mark.parametrize("shape,k,n,rule,out", [((16,), 8192, 8192, "mse", "bfloat16"), ((3, 41), 520, 392, "static_6", "float16"),
+                                                ((300,), 1024, 2880, "mae", "float32")])
+def test_one_call_forward_equals_the_call_by_call_forward(shape, k, n, rule, out):
+    """Inference on a packed weight takes `fos_linear_forward` (one host call); the autograd function quantizes and
+    multiplies call by call. Same kernels, same bits - ragged rows, a width that is not a multiple of 64, a bias."""
+    from fouroversix_b200.model.linear import FourOverSixLinearFunction
+
+    torch.manual_seed(1)
+    lin = nn.Linear(k, n, bias=True, device=DEV, dtype=torch.bfloat16)
+    cfg = fos.ModuleQuantizationConfig(scale_rule=rule, output_dtype=out)
+    q = fos.FourOverSixLinear(lin, cfg).quantize_weight_()
+    x = torch.randn(*shape, k, device=DEV, dtype=torch.bfloat16)
+    with torch.no_grad():
+        assert q._one_call_forward_applies(x)
+        got = q(x)
+        want = FourOverSixLinearFunction.apply(cfg, x, q.quantized_weight(), q.bias)
+    assert got.shape == (*shape, n) and got.dtype == want.dtype
+    assert torch.equal(got, want)
+    # an input that needs a gradient goes through the autograd function
+    assert not q._one_call_forward_applies(x.clone().requires_grad_())
+
+
 def test_packed_state_dict_round_trips_between_modules():
     torch.manual_seed(1)
     src = fos.FourOverSixLinear(nn.Linear(256, 128, bias=False, device=DEV, dtype=torch.bfloat16),
