@@ -54,6 +54,11 @@ def test_argument_validation_needs_no_gpu():
     capacity = (256 * 4 + 127 * 32 + 127) // 128 * 128
     assert need % 256 == 0 and need >= capacity * (2 * 2880 * 2 + 2 * 2 * 2880 + 2 * 2880 + 2 * (2880 // 2 + 2880 // 16))
     assert lib.fos_experts_workspace_bytes(0, 4, 32, 2880, 2880) == -1
+    # a linear layer as one call: NULL buffers; the workspace holds the packed activation of the padded shape
+    assert lib.fos_linear_forward(0, 0, 16, 8192, 8192, 3, 0, 0, 0, 3, 8192, 0, 0, 8192, 0, 0, None, 0, 0) == -1
+    need = lib.fos_linear_workspace_bytes(16, 8200)
+    assert need % 256 == 0 and need >= 128 * 8256 // 2 + 128 * 8256 // 16 + 8
+    assert lib.fos_linear_workspace_bytes(16, 0) == -1
 
 
 def test_group_layout_is_computed_without_reading_the_counts_back():
