@@ -36,6 +36,7 @@ Two ways to obtain shards:
 
 from __future__ import annotations
 
+import contextlib
 from collections.abc import Callable
 
 import torch
@@ -45,7 +46,7 @@ import torch.nn as nn
 from fouroversix_b200 import _native
 from fouroversix_b200.matmul import quantized_matmul
 from fouroversix_b200.quantize import QuantizationConfig, QuantizedTensor, quantize
-from fouroversix_b200.utils import DataType
+from fouroversix_b200.utils import DataType, RoundStyle
 
 from .model.config import ModuleQuantizationConfig
 
@@ -166,10 +167,64 @@ class TensorParallelLinear(nn.Module):
         self.weight = weight if isinstance(weight, QuantizedTensor) else self._quantize(weight, config.get_weight_config())
         self.bias = bias
         self._comm_stream: torch.cuda.Stream | None = None
+        self._sms: int | None = None               # SM count of the device (looked up once)
 
     @property
     def world_size(self) -> int:
         return dist.get_world_size(self.group) if dist.is_initialized() else 1
+
+    def _sm_count(self, dev: torch.device) -> int:
+        if self._sms is None:
+            self._sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        return self._sms
+
+    def _alpha_for(self, xq: QuantizedTensor) -> torch.Tensor | None:
+        """alpha of `xq @ weight.T` (fos_gemm_alpha_ex), once per forward for all its chunks - or None when the row
+        ranges of this activation do not go through the native calls of `_gemm_rows`."""
+        w = self.weight
+        if not (self._matmul is quantized_matmul and xq.values.is_cuda and xq.dtype == w.dtype == DataType.nvfp4
+                and xq.scale_factors_are_in_blackwell_layout and w.scale_factors_are_in_blackwell_layout
+                and w.padded_shape[1] == xq.padded_shape[1] and xq.values.is_contiguous()
+                and xq.scale_factors.is_contiguous()):
+            return None
+        dev = xq.values.device
+        alpha = torch.empty(1, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _native.check(_native.lib().fos_gemm_alpha_ex(
+                xq.amax.data_ptr(), _native.FOS_NVFP4, xq.scale_rule.cuda_id, int(xq.round_style == RoundStyle.stochastic_unbiased),
+                w.amax.data_ptr(), _native.FOS_NVFP4, w.scale_rule.cuda_id, int(w.round_style == RoundStyle.stochastic_unbiased),
+                alpha.data_ptr(), _native.stream_ptr(dev)), "fos_gemm_alpha")
+        return alpha
+
+    def _gemm_rows(self, xq: QuantizedTensor, lo: int, hi: int, act_cfg: QuantizationConfig, out: torch.Tensor,
+                   max_ctas: int = 0, alpha: torch.Tensor | None = None) -> torch.Tensor:
+        """out = xq[lo:hi] @ weight.T for a row range on 128-row boundaries of a packed activation. With an `alpha`
+        from `_alpha_for` this is the native GEMM call itself (fos_gemm_nvfp4_ex) on offsets into the packed
+        buffers - the layers of a sharded stack are called thousands of times a second, and the front end's checks
+        and the row-slice objects cost more host time than the call; anything else goes through `_gemm` on a
+        `slice_rows` view."""
+        w = self.weight
+        rows = hi - lo
+        if (alpha is None or lo % 128 or rows % 128 or out.stride(1) != 1 or out.shape != (rows, w.original_shape[0])
+                or out.dtype != DataType(self.config.output_dtype).torch_dtype):
+            return self._gemm(slice_rows(xq, lo, hi), act_cfg, out=out, max_ctas=max_ctas)
+        dev = out.device
+        k_p = xq.padded_shape[1]
+        lib, stream = _native.lib(), _native.stream_ptr(dev)
+
+        def launch() -> None:
+            _native.check(lib.fos_gemm_nvfp4_ex(
+                xq.values.data_ptr() + lo * (k_p // 2), xq.scale_factors.data_ptr() + lo * (k_p // 16),
+                w.values.data_ptr(), w.scale_factors.data_ptr(), alpha.data_ptr(), out.data_ptr(),
+                _native.elem_code(out.dtype), rows, w.padded_shape[0], k_p, rows, w.original_shape[0], out.stride(0),
+                _native.gemm_opts(0, max_ctas), 0, stream), "fos_gemm_nvfp4")
+
+        if dev.index is None or dev.index == torch.cuda.current_device():
+            launch()
+        else:
+            with torch.cuda.device(dev):
+                launch()
+        return out
 
     def _gemm(self, x: torch.Tensor | QuantizedTensor, act_cfg: QuantizationConfig,
               out: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
@@ -259,10 +314,11 @@ class TensorParallelLinear(nn.Module):
                 self._comm_stream = torch.cuda.Stream(device=x2d.device)
             compute = torch.cuda.current_stream(x2d.device)
             if self.comm_sms > 0 and n_chunks > 1:
-                max_ctas = max(1, torch.cuda.get_device_properties(x2d.device).multi_processor_count - self.comm_sms)
+                max_ctas = max(1, self._sm_count(x2d.device) - self.comm_sms)
+        alpha = self._alpha_for(xq) if on_gpu else None
         for i in range(n_chunks):
             part = partial[i * step: (i + 1) * step]
-            self._gemm(slice_rows(xq, i * step, (i + 1) * step), act_cfg, out=part, max_ctas=max_ctas)
+            self._gemm_rows(xq, i * step, (i + 1) * step, act_cfg, part, max_ctas, alpha)
             mine = slab[i * piece: (i + 1) * piece]
             if on_gpu:
                 done = torch.cuda.Event()
@@ -356,13 +412,14 @@ class TensorParallelLinear(nn.Module):
             if use_peer:
                 with torch.cuda.stream(self._comm_stream):
                     gp["h_codes"].barrier(channel=0)         # every rank's packed slab is in its symmetric buffer
-        for i in range(n_chunks):
-            src_codes = q.values[i * piece: (i + 1) * piece]
-            src_sf = sf_local[i * piece * per_row: (i + 1) * piece * per_row]
-            dst_codes = codes[i * step: (i + 1) * step]
-            dst_sf = scales[i * step * per_row: (i + 1) * step * per_row]
-            if on_gpu:
-                with torch.cuda.stream(self._comm_stream):
+        # (one stream context around the whole loop: entering one per chunk costs host time the layer feels)
+        with (torch.cuda.stream(self._comm_stream) if on_gpu else contextlib.nullcontext()):
+            for i in range(n_chunks):
+                src_codes = q.values[i * piece: (i + 1) * piece]
+                src_sf = sf_local[i * piece * per_row: (i + 1) * piece * per_row]
+                dst_codes = codes[i * step: (i + 1) * step]
+                dst_sf = scales[i * step * per_row: (i + 1) * step * per_row]
+                if on_gpu:
                     if use_peer:
                         with torch.cuda.device(slab.device):
                             lib, stream = _native.lib(), _native.stream_ptr(slab.device)
@@ -377,10 +434,10 @@ class TensorParallelLinear(nn.Module):
                         dist.all_gather_into_tensor(dst_sf, src_sf, group=self.group)
                     ev = torch.cuda.Event()
                     ev.record(self._comm_stream)
-                events.append(ev)
-            else:
-                dist.all_gather_into_tensor(dst_codes, src_codes.contiguous(), group=self.group)
-                dist.all_gather_into_tensor(dst_sf, src_sf.contiguous(), group=self.group)
+                    events.append(ev)
+                else:
+                    dist.all_gather_into_tensor(dst_codes, src_codes.contiguous(), group=self.group)
+                    dist.all_gather_into_tensor(dst_sf, src_sf.contiguous(), group=self.group)
         if use_peer:
             with torch.cuda.stream(self._comm_stream):
                 gp["h_codes"].barrier(channel=0)             # nobody overwrites its slab while a peer still reads it
@@ -408,12 +465,12 @@ class TensorParallelLinear(nn.Module):
         compute = torch.cuda.current_stream(slab.device)
         max_ctas = 0
         if self.comm_sms > 0 and self._matmul is quantized_matmul:
-            max_ctas = max(1, torch.cuda.get_device_properties(slab.device).multi_processor_count - self.comm_sms)
+            max_ctas = max(1, self._sm_count(slab.device) - self.comm_sms)
+        alpha = self._alpha_for(xq)
         for i, ev in enumerate(events):
             compute.wait_event(ev)
             last = i + 1 == len(events)
-            self._gemm(slice_rows(xq, i * step, (i + 1) * step), act_cfg, out=out[i * step: (i + 1) * step],
-                       max_ctas=0 if last else max_ctas)
+            self._gemm_rows(xq, i * step, (i + 1) * step, act_cfg, out[i * step: (i + 1) * step], 0 if last else max_ctas, alpha)
         return out
 
     def _peer_buffers(self, tokens: int, n_out: int, dtype: torch.dtype, dev: torch.device) -> dict:
@@ -583,10 +640,11 @@ class TensorParallelLinear(nn.Module):
             compute = torch.cuda.current_stream(x2d.device)
         max_ctas = 0
         if on_gpu and self.comm_sms > 0 and self._matmul is quantized_matmul:
-            max_ctas = max(1, torch.cuda.get_device_properties(x2d.device).multi_processor_count - self.comm_sms)
+            max_ctas = max(1, self._sm_count(x2d.device) - self.comm_sms)
+        alpha = self._alpha_for(xq) if on_gpu else None
         for i in range(n_chunks):
             part = out[i * step: (i + 1) * step]
-            self._gemm(slice_rows(xq, i * step, (i + 1) * step), act_cfg, out=part, max_ctas=max_ctas)
+            self._gemm_rows(xq, i * step, (i + 1) * step, act_cfg, part, max_ctas, alpha)
             if on_gpu:
                 done = torch.cuda.Event()
                 done.record(compute)
