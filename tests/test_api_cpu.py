@@ -160,3 +160,31 @@ def test_backward_refuses_settings_it_does_not_implement():
 
         with pytest.raises(NotImplementedError):
             FourOverSixLinearFunction.backward(Ctx, dy)
+
+
+def test_experts_routing_tables_on_the_host():
+    """The tensor-operation form of the experts layer's routing (`FourOverSixExperts.route`) needs no GPU: every
+    (token, slot) pair gets a row of its expert's range, rows ascend with the pair inside an expert."""
+    import torch
+
+    from fouroversix_b200.model import FourOverSixExperts
+
+    layer = FourOverSixExperts.__new__(FourOverSixExperts)
+    torch.nn.Module.__init__(layer)
+    layer.num_experts = 6
+    g = torch.Generator().manual_seed(4)
+    scores = torch.rand(37, 6, generator=g)
+    scores[:, 2] = -1                                             # an expert nobody is routed to
+    indices = torch.topk(scores, 3, dim=-1).indices
+    layout, rows, token, order = layer.route(indices)
+    flat = indices.reshape(-1)
+    counts = torch.bincount(flat, minlength=6)
+    assert layout.group_rows.tolist() == counts.tolist() and counts[2] == 0
+    assert layout.group_start.tolist() == [0, *((counts + 127) // 128 * 128).cumsum(0).tolist()]
+    expert = flat[order]
+    start = layout.group_start.long()[expert]
+    assert ((rows >= start) & (rows < start + counts[expert])).all() and rows.unique().numel() == rows.numel()
+    assert torch.equal(token, order // 3)
+    for e in range(6):
+        mine, pairs = rows[expert == e], order[expert == e]
+        assert (mine[1:] > mine[:-1]).all() and (pairs[1:] > pairs[:-1]).all()
